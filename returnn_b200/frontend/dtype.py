@@ -1,0 +1,20 @@
+"""
+Default dtypes.  Parity: returnn/frontend/dtype.py.
+"""
+
+from __future__ import annotations
+from ._utils import (get_default_float_dtype, set_default_float_dtype, get_default_int_dtype,
+                     get_default_array_index_dtype)
+
+__all__ = ["get_default_float_dtype", "set_default_float_dtype", "get_default_int_dtype", "get_default_array_index_dtype",
+           "is_float_dtype", "is_int_dtype"]
+
+
+def is_float_dtype(dtype: str) -> bool:
+    """float16/bfloat16/float32/float64"""
+    return dtype.startswith("float") or dtype == "bfloat16"
+
+
+def is_int_dtype(dtype: str) -> bool:
+    """signed or unsigned int"""
+    return dtype.startswith("int") or dtype.startswith("uint")
