@@ -108,7 +108,7 @@ def ctc_loss(*, logits: Tensor, logits_normalized: bool = False, targets: Tensor
     if lraw.is_cuda:
         from ..ops import ctc as _ctc
 
-        if _ctc.available():
+        if _ctc.available() and _ctc.supports(lraw, traw):
             loss = _ctc.ctc_loss(lraw, traw, in_lens.to(lraw.device), tgt_lens.to(lraw.device), blank_index=blank_index,
                                  logits_normalized=logits_normalized)
             return wrap(loss, [bd])

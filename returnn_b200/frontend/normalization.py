@@ -12,7 +12,7 @@ from ..tensor import Tensor, Dim
 from .module import Module
 from .parameter import Parameter
 from ._utils import wrap, axis_of
-from . import reduce as _red
+from .reduce import reduce_sum as _reduce_sum, reduce_mean as _reduce_mean
 from . import math_ as _m
 from .run_ctx import get_run_ctx
 
@@ -32,8 +32,8 @@ def moments(x: Tensor, axis: Union[Dim, Sequence[Dim]], *, use_mask: bool = True
         from ..torch.util.distributed import all_reduce_differentiable
 
         x32 = x if x.dtype in ("float32", "float64") else wrap(x._raw_tensor.float(), x._dims)
-        s = _red.reduce_sum(x32, axis=axes, use_mask=use_mask)
-        sq = _red.reduce_sum(x32 * x32, axis=axes, use_mask=use_mask)
+        s = _reduce_sum(x32, axis=axes, use_mask=use_mask)
+        sq = _reduce_sum(x32 * x32, axis=axes, use_mask=use_mask)
         n = float(num_elements_of_shape(axes, use_mask=use_mask))
         packed = torch.cat([s._raw_tensor.reshape(-1), sq._raw_tensor.reshape(-1), torch.tensor([n], device=s._raw_tensor.device, dtype=s._raw_tensor.dtype)])
         packed = all_reduce_differentiable(packed, "sum")
@@ -44,15 +44,15 @@ def moments(x: Tensor, axis: Union[Dim, Sequence[Dim]], *, use_mask: bool = True
         if correction:
             var_raw = var_raw * (n_tot / (n_tot - correction))
         return wrap(mean_raw.to(x._raw_tensor.dtype), s._dims), wrap(var_raw.clamp_min(0).to(x._raw_tensor.dtype), s._dims)
-    mean = _red.reduce_mean(x, axis=axes, use_mask=use_mask)
+    mean = _reduce_mean(x, axis=axes, use_mask=use_mask)
     diff = x - mean
     if correction:
         from .array_ import num_elements_of_shape
 
         n = num_elements_of_shape(axes, use_mask=use_mask)
-        var = _red.reduce_sum(diff * diff, axis=axes, use_mask=use_mask) / (n - correction)
+        var = _reduce_sum(diff * diff, axis=axes, use_mask=use_mask) / (n - correction)
     else:
-        var = _red.reduce_mean(diff * diff, axis=axes, use_mask=use_mask)
+        var = _reduce_mean(diff * diff, axis=axes, use_mask=use_mask)
     return mean, var
 
 
@@ -102,7 +102,7 @@ class RMSNorm(Module):
 
             out = _ln.rms_norm(x._raw_tensor, self.scale._raw_tensor, self.bias._raw_tensor if self.bias is not None else None, self.eps)
             return wrap(out, x._dims, like=x)
-        var = _red.reduce_mean(_m.square(x), axis=self.in_dim)
+        var = _reduce_mean(_m.square(x), axis=self.in_dim)
         out = x * _m.rsqrt(var + self.eps) * self.scale
         return out + self.bias if self.bias is not None else out
 

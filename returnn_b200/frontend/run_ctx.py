@@ -198,7 +198,7 @@ class Loss:
         """sum over all valid elements, scalar"""
         if self._summed_loss_cached is not None:
             return self._summed_loss_cached
-        from . import reduce as _r
+        from .reduce import reduce_sum as _reduce_sum
         from .array_ import cast
 
         loss = self.loss
@@ -210,7 +210,7 @@ class Loss:
         if self._mean_loss_cached is not None:
             self._summed_loss_cached = self._mean_loss_cached * self.get_inv_norm_factor()
         else:
-            self._summed_loss_cached = _r.reduce_sum(loss, axis=loss.dims)
+            self._summed_loss_cached = _reduce_sum(loss, axis=loss.dims)
         return self._summed_loss_cached
 
     def get_mean_loss(self) -> Tensor:
@@ -230,9 +230,9 @@ class Loss:
         if self.custom_inv_norm_factor is not None:
             f = self.custom_inv_norm_factor
             if isinstance(f, Tensor) and f.dims:
-                from . import reduce as _r
+                from .reduce import reduce_sum as _reduce_sum
 
-                f = _r.reduce_sum(f, axis=f.dims)
+                f = _reduce_sum(f, axis=f.dims)
             return f
         from .array_ import num_elements_of_shape
 

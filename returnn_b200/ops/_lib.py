@@ -108,23 +108,16 @@ def check(status: int, what: str):
 
 
 def _declare(lib: ctypes.CDLL):
-    """argtypes/restype for every exported function present in the library"""
-    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
-    sigs = {
-        "rb200_layer_norm_fwd": [vp, vp, vp, vp, vp, vp, i64, i32, f32, i32, i32, vp],
-        "rb200_layer_norm_bwd": [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, vp],
-        "rb200_adamw_step": [vp, vp, vp, vp, vp, i64, f32, f32, f32, f32, f32, vp, vp, f32, f32, i32, vp],
-        "rb200_sumsq_partials": [vp, i64, i32, vp, i32, vp],
-        "rb200_gemm_bf16": [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i64, i64, i64, i32, f32, vp, vp],
-        "rb200_softmax_ce_fwd": [vp, vp, vp, vp, vp, i64, i32, f32, i32, vp],
-        "rb200_softmax_ce_bwd": [vp, vp, vp, vp, vp, i64, i32, f32, i32, vp],
-        "rb200_dropout_bf16": [vp, vp, i64, f32, i64, i64, vp],
-        "rb200_bias_act_bf16": [vp, vp, vp, vp, i64, i32, i32, f32, i64, i64, vp],
-        "rb200_ctc_loss": [vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
-        "rb200_ctc_loss_noalloc": [vp, i32, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp],
-    }
-    for name, args in sigs.items():
-        if hasattr(lib, name):
-            fn = getattr(lib, name)
-            fn.argtypes = args
-            fn.restype = ctypes.c_int
+    """every entry point returns an int status; argument types are declared by the wrapper modules"""
+    return
+
+
+def bind(name: str, argtypes):
+    """look up an entry point and set its signature (idempotent)"""
+    lib = get_lib(required=True)
+    fn = getattr(lib, name)
+    if getattr(fn, "_rb_bound", False) is not True:
+        fn.argtypes = argtypes
+        fn.restype = ctypes.c_int
+        fn._rb_bound = True
+    return fn

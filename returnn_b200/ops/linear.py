@@ -1,0 +1,45 @@
+"""
+Linear layer op: ``y = x @ W (+ bias) (+ activation)`` with ``W`` stored ``[in, out]``.
+
+On B200 (bf16 activations): forward and both backward GEMMs run on the tcgen05 GEMM kernel
+(:mod:`returnn_b200.ops.gemm`) with bias/activation fused into the epilogue. Elsewhere: ``torch.matmul``.
+"""
+
+from __future__ import annotations
+from typing import Optional
+import torch
+from . import _lib
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> torch.Tensor:
+    """
+    :param x: [..., in]
+    :param weight: [in, out]
+    :param bias: [out]
+    :param activation: None, "relu", "silu", "gelu"
+    """
+    if x.is_cuda and x.dtype == torch.bfloat16 or (x.is_cuda and torch.is_autocast_enabled() and x.is_floating_point()):
+        from . import gemm as _gemm
+
+        if _gemm.available(x) and _gemm.ENABLED and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 == 0:
+            return _gemm.linear_bf16(x, weight, bias, activation)
+    w = weight
+    if not torch.is_autocast_enabled() and w.dtype != x.dtype:
+        w = w.to(x.dtype)
+        bias = bias.to(x.dtype) if bias is not None else None
+    if bias is not None and x.dim() == 2 and activation is None and not torch.is_autocast_enabled():
+        return torch.addmm(bias, x, w)
+    y = torch.matmul(x, w)
+    if bias is not None:
+        y = y + bias
+    if activation is not None:
+        y = _ACT[activation](y)
+    return y
+
+
+_ACT = {
+    "relu": torch.relu,
+    "silu": torch.nn.functional.silu,
+    "swish": torch.nn.functional.silu,
+    "gelu": torch.nn.functional.gelu,
+}

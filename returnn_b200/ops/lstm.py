@@ -1,0 +1,92 @@
+"""
+LSTM sequence op (gate order i, f, g, o; weights ``[4H, in]`` and ``[4H, H]``).
+
+``lstm(x[T,B,in], lens[B], ...)``: frames ``t >= lens[b]`` give zero output and leave the state untouched;
+``reverse=True`` runs every sequence from its own last frame to its first.
+
+CUDA path: the input projection for all frames is one tcgen05 GEMM; the recurrence runs in the persistent kernel of
+``csrc/lstm.cu`` (:mod:`returnn_b200.ops.lstm_native`). CPU path: torch's packed-sequence LSTM.
+"""
+
+from __future__ import annotations
+from typing import Optional, Tuple
+import torch
+
+
+def lstm_reference(x, lens, w_ff, w_rec, bias, h0, c0, reverse: bool = False):
+    """step-by-step torch implementation with explicit masking (oracle)"""
+    T, B, _ = x.shape
+    H = w_rec.shape[1]
+    z_in = torch.matmul(x, w_ff.t().to(x.dtype))
+    if bias is not None:
+        z_in = z_in + bias.to(x.dtype)
+    h, c = h0.to(x.dtype), c0.to(x.dtype)
+    ys = [None] * T
+    steps = range(T - 1, -1, -1) if reverse else range(T)
+    wr = w_rec.t().to(x.dtype)
+    for t in steps:
+        z = z_in[t] + torch.matmul(h, wr)
+        i, f, g, o = torch.chunk(z, 4, dim=-1)
+        c_new = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(g)
+        h_new = torch.sigmoid(o) * torch.tanh(c_new)
+        if lens is not None:
+            m = (lens.to(x.device) > t).unsqueeze(-1)
+            c = torch.where(m, c_new, c)
+            h = torch.where(m, h_new, h)
+            ys[t] = torch.where(m, h_new, torch.zeros_like(h_new))
+        else:
+            c, h = c_new, h_new
+            ys[t] = h_new
+    return torch.stack(ys, dim=0) if T else x.new_zeros(0, B, H), h, c
+
+
+def _reverse_padded(x: torch.Tensor, lens: Optional[torch.Tensor]) -> torch.Tensor:
+    """reverse each sequence within its own length; x [T,B,...]"""
+    T = x.shape[0]
+    if lens is None:
+        return torch.flip(x, [0])
+    pos = torch.arange(T, device=x.device)[:, None]
+    l = lens.to(x.device).to(torch.int64)[None, :]
+    idx = torch.where(pos < l, l - 1 - pos, pos)
+    return torch.gather(x, 0, idx.reshape(T, -1, *([1] * (x.dim() - 2))).expand_as(x))
+
+
+def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_rec: torch.Tensor, bias: Optional[torch.Tensor],
+         h0: torch.Tensor, c0: torch.Tensor, reverse: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """
+    :param x: [T, B, in]
+    :param lens: [B] int32 (on any device) or None
+    :return: y [T, B, H], h_T [B, H], c_T [B, H]
+    """
+    if x.is_cuda:
+        from . import lstm_native as _n
+
+        if _n.available(x) and _n.supports(x, w_rec):
+            return _n.lstm(x, lens, w_ff, w_rec, bias, h0, c0, reverse=reverse)
+    T, B, _ = x.shape
+    H = w_rec.shape[1]
+    if T == 0:
+        return x.new_zeros(0, B, H), h0, c0
+    dt = x.dtype
+    if torch.is_autocast_enabled() and x.is_cuda:
+        dt = torch.get_autocast_dtype("cuda")
+    ws = [w_ff.to(dt), w_rec.to(dt)]
+    if bias is not None:
+        ws += [bias.to(dt), torch.zeros_like(bias, dtype=dt)]
+    xx = x.to(dt)
+    if reverse:
+        xx = _reverse_padded(xx, lens)
+    if lens is not None:
+        packed = torch.nn.utils.rnn.pack_padded_sequence(xx, lens.cpu().to(torch.int64), enforce_sorted=False)
+        out, hT, cT = torch.lstm(packed.data, packed.batch_sizes, (h0.unsqueeze(0).to(dt), c0.unsqueeze(0).to(dt)), ws,
+                                 bias is not None, 1, 0.0, False, False)
+        y, _ = torch.nn.utils.rnn.pad_packed_sequence(
+            torch.nn.utils.rnn.PackedSequence(out, packed.batch_sizes, packed.sorted_indices, packed.unsorted_indices), total_length=T)
+        if packed.unsorted_indices is not None:
+            hT = hT.index_select(1, packed.unsorted_indices)
+            cT = cT.index_select(1, packed.unsorted_indices)
+    else:
+        y, hT, cT = torch.lstm(xx, (h0.unsqueeze(0).to(dt), c0.unsqueeze(0).to(dt)), ws, bias is not None, 1, 0.0, False, False, False)
+    if reverse:
+        y = _reverse_padded(y, lens)
+    return y, hT[0], cT[0]

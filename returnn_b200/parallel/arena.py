@@ -1,0 +1,117 @@
+"""
+Flat parameter arena: all parameters of a model live in one contiguous buffer per dtype (each ``nn.Parameter`` becomes a
+view), and so do their gradients. Everything that touches "all weights" is then one pass over one pointer:
+gradient all-reduce per bucket (a bucket is a contiguous slice), global grad norm, fused AdamW, parameter averaging.
+
+Bucket order is reverse registration order (roughly the order in which autograd produces gradients), identical on
+all ranks because it only depends on the module definition.
+"""
+
+from __future__ import annotations
+from typing import Dict, Iterable, List, Optional, Sequence, Tuple
+import torch
+
+_ALIGN = 128  # elements; keeps every tensor 512-byte aligned in fp32 (vector loads, TMA-able slices)
+
+
+class ArenaSlot:
+    """where one parameter lives"""
+
+    __slots__ = ("name", "param", "offset", "numel", "shape", "bucket")
+
+    def __init__(self, name: str, param: torch.nn.Parameter, offset: int, numel: int):
+        self.name = name
+        self.param = param
+        self.offset = offset
+        self.numel = numel
+        self.shape = tuple(param.shape)
+        self.bucket = -1
+
+
+class ParamArena:
+    """
+    Owns ``flat_param`` and ``flat_grad`` (same dtype and size) and re-points ``param.data`` / ``param.grad`` into them.
+    """
+
+    def __init__(self, named_params: Iterable[Tuple[str, torch.nn.Parameter]], *, bucket_bytes: int = 32 << 20,
+                 grad_dtype: Optional[torch.dtype] = None):
+        params = [(n, p) for n, p in named_params if p.requires_grad]
+        assert params, "ParamArena: no trainable parameters"
+        self.device = params[0][1].device
+        self.dtype = params[0][1].dtype
+        for n, p in params:
+            assert p.device == self.device and p.dtype == self.dtype, "ParamArena: mixed device/dtype at %r" % n
+        self.slots: List[ArenaSlot] = []
+        seen = set()
+        offset = 0
+        for n, p in params:
+            if id(p) in seen:
+                continue
+            seen.add(id(p))
+            numel = p.numel()
+            self.slots.append(ArenaSlot(n, p, offset, numel))
+            offset += (numel + _ALIGN - 1) // _ALIGN * _ALIGN
+        self.total = offset
+        self.flat_param = torch.zeros(self.total, dtype=self.dtype, device=self.device)
+        self.grad_dtype = grad_dtype or self.dtype
+        self.flat_grad = torch.zeros(self.total, dtype=self.grad_dtype, device=self.device)
+        with torch.no_grad():
+            for s in self.slots:
+                view = self.flat_param[s.offset: s.offset + s.numel].view(s.shape)
+                view.copy_(s.param.data)
+                s.param.data = view
+                if self.grad_dtype == self.dtype:
+                    s.param.grad = self.flat_grad[s.offset: s.offset + s.numel].view(s.shape)
+        # buckets: contiguous ranges, in reverse slot order
+        elem = self.flat_grad.element_size()
+        self.buckets: List[Tuple[int, int]] = []  # (start, end) element offsets, ordered by expected readiness
+        end = self.total
+        cur_end = end
+        cur_bytes = 0
+        n_in_bucket = 0
+        for s in reversed(self.slots):
+            cur_bytes += s.numel * elem
+            n_in_bucket += 1
+            if cur_bytes >= bucket_bytes:
+                self.buckets.append((s.offset, cur_end))
+                cur_end = s.offset
+                cur_bytes = 0
+                n_in_bucket = 0
+        if cur_end > 0 and (n_in_bucket > 0 or not self.buckets):
+            self.buckets.append((0, cur_end))
+        for b, (lo, hi) in enumerate(self.buckets):
+            for s in self.slots:
+                if lo <= s.offset < hi:
+                    s.bucket = b
+        self.bucket_num_params = [sum(1 for s in self.slots if s.bucket == b) for b in range(len(self.buckets))]
+
+    def zero_grad(self):
+        """one memset for all gradients"""
+        self.flat_grad.zero_()
+
+    def relink_grads(self):
+        """make sure every ``param.grad`` is the arena view (autograd may have replaced it when it was None)"""
+        if self.grad_dtype != self.dtype:
+            return
+        for s in self.slots:
+            g = s.param.grad
+            view = self.flat_grad[s.offset: s.offset + s.numel].view(s.shape)
+            if g is None:
+                s.param.grad = view
+            elif g.data_ptr() != view.data_ptr():
+                view.copy_(g)
+                s.param.grad = view
+
+    def bucket_grad(self, b: int) -> torch.Tensor:
+        """gradient slice of bucket b"""
+        lo, hi = self.buckets[b]
+        return self.flat_grad[lo:hi]
+
+    def bucket_param(self, b: int) -> torch.Tensor:
+        """parameter slice of bucket b"""
+        lo, hi = self.buckets[b]
+        return self.flat_param[lo:hi]
+
+    def nbytes(self) -> int:
+        """bytes of one flat buffer"""
+        return self.total * self.flat_param.element_size()

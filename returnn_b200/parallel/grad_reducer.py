@@ -1,0 +1,99 @@
+"""
+Bucketed gradient all-reduce overlapped with backward (``reduce_type="grad"``).
+
+A post-accumulate-grad hook per parameter counts down its bucket; when the bucket is complete, the reduction of that
+contiguous gradient slice is launched on a side stream while autograd continues with earlier layers. On B200 with
+peer access the reduction is the fused NVLink kernel of :mod:`returnn_b200.parallel.fused_allreduce` (peer loads,
+scale by 1/N, running sum of squares for the global grad norm); otherwise ``torch.distributed.all_reduce`` (NCCL/Gloo).
+``finish()`` joins the side stream and returns the squared global gradient norm when the fused path produced it.
+"""
+
+from __future__ import annotations
+from typing import List, Optional
+import torch
+import torch.distributed as dist
+from .arena import ParamArena
+
+
+class BucketedGradReducer:
+    """drives per-bucket reductions from autograd hooks"""
+
+    def __init__(self, arena: ParamArena, *, process_group=None, fused=None, average: bool = True):
+        self.arena = arena
+        self.pg = process_group
+        self.world = dist.get_world_size(process_group) if dist.is_initialized() else 1
+        self.average = average
+        self.fused = fused  # object with reduce_bucket(b, lo, hi, stream) / finish(), or None
+        self._pending = list(arena.bucket_num_params)
+        self._works: List = []
+        self._enabled = True
+        self._stream: Optional[torch.cuda.Stream] = torch.cuda.Stream(device=arena.device) if arena.device.type == "cuda" else None
+        self._handles = []
+        self._launched = [False] * len(arena.buckets)
+        for s in arena.slots:
+            self._handles.append(s.param.register_post_accumulate_grad_hook(self._make_hook(s.bucket)))
+
+    def _make_hook(self, b: int):
+        def hook(param):
+            if not self._enabled or self.world == 1:
+                return
+            self._pending[b] -= 1
+            if self._pending[b] == 0:
+                self._launch(b)
+
+        return hook
+
+    def set_enabled(self, enabled: bool):
+        """False during gradient accumulation micro-steps (no_sync)"""
+        self._enabled = enabled
+
+    def prepare_backward(self):
+        """reset the per-bucket counters"""
+        self._pending = list(self.arena.bucket_num_params)
+        self._works = []
+        self._launched = [False] * len(self.arena.buckets)
+
+    def _launch(self, b: int):
+        self._launched[b] = True
+        lo, hi = self.arena.buckets[b]
+        g = self.arena.flat_grad[lo:hi]
+        if self.fused is not None:
+            self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream):
+                self.fused.reduce_bucket(b, lo, hi)
+            return
+        if self._stream is not None:
+            self._stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self._stream):
+                if self.average:
+                    g.div_(self.world)
+                self._works.append(dist.all_reduce(g, group=self.pg, async_op=True))
+        else:
+            if self.average:
+                g.div_(self.world)
+            self._works.append(dist.all_reduce(g, group=self.pg, async_op=True))
+
+    def finish(self) -> Optional[torch.Tensor]:
+        """
+        Wait for all bucket reductions; buckets whose hooks never fired (unused parameters) are reduced now.
+        :return: squared global grad norm (device scalar) if the fused path computed it, else None
+        """
+        if self.world == 1 or not self._enabled:
+            return None
+        for b, done in enumerate(self._launched):
+            if not done:
+                self._launch(b)
+        for w in self._works:
+            w.wait()
+        self._works = []
+        if self._stream is not None:
+            torch.cuda.current_stream().wait_stream(self._stream)
+        if self.fused is not None:
+            return self.fused.finish()
+        return None
+
+    def remove(self):
+        """unregister hooks"""
+        for h in self._handles:
+            h.remove()
+        self._handles = []

@@ -478,6 +478,9 @@ class Dim:
     # -- arithmetic --------------------------------------------------------------------------------
     @staticmethod
     def _derive(kind: str, inputs: Sequence[Union["Dim", int]], attribs=None, name: Optional[str] = None) -> "Dim":
+        simp = Dim._simplify(kind, inputs)
+        if simp is not None:
+            return simp
         op = _DimOp(kind, inputs, attribs)
         key = op.key()
         res = _derived_cache.get(key)
@@ -521,6 +524,38 @@ class Dim:
             res.capacity = int(cap)
         _derived_cache[key] = res
         return res
+
+    @staticmethod
+    def _simplify(kind: str, inputs) -> Optional["Dim"]:
+        """inverse operations cancel: (c*d)//c -> d, (a+b)-b -> a, (a-b)+b -> a"""
+        if len(inputs) != 2 or not isinstance(inputs[0], Dim):
+            return None
+        a, b = inputs
+        op = a.get_same_base().derived_from_op
+        if op is None or len(op.inputs) != 2:
+            return None
+        x, y = op.inputs
+
+        def same(p, q):
+            if isinstance(p, Dim) and isinstance(q, Dim):
+                return p == q
+            if isinstance(p, Dim) or isinstance(q, Dim):
+                return False
+            return p == q
+
+        if kind in ("floordiv", "ceildiv") and op.kind == "mul":
+            if same(x, b) and isinstance(y, Dim):
+                return y
+            if same(y, b) and isinstance(x, Dim):
+                return x
+        if kind == "sub" and op.kind == "add":
+            if same(y, b) and isinstance(x, Dim):
+                return x
+            if same(x, b) and isinstance(y, Dim):
+                return y
+        if kind == "add" and op.kind == "sub" and same(y, b) and isinstance(x, Dim):
+            return x
+        return None
 
     def __add__(self, other):
         if isinstance(other, int) and other == 0:
