@@ -1,0 +1,257 @@
+// LayerNorm / RMSNorm over the last axis.
+//
+// Forward: one warp per row, the row is held in registers (n <= 2048) or re-read from L2 (larger n);
+// statistics in fp32; saves mean and rstd. Backward: one warp per row for dx; every CTA accumulates its
+// rows' contributions to dgamma/dbeta in registers and writes one partial per CTA into scratch memory,
+// which a second kernel reduces. No atomics, so results are deterministic.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarpsPerCta = 4;
+constexpr int kMaxChunks = 8;  // 8 chunks * 32 lanes * 8 elems = 2048 elements in registers
+
+template <int CHUNKS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+ln_fwd_kernel(const void* __restrict__ x, const void* __restrict__ gamma, const void* __restrict__ beta,
+              void* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+              int64_t rows, int n, float eps, int x_bf16, int w_bf16, int rms) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t base = row * (int64_t)n;
+  F8 v[CHUNKS];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    int col = (c * 32 + lane) * 8;
+    if (col < n) {
+      v[c] = load8(x, base + col, x_bf16);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[c].v[i];
+    }
+  }
+  float mean = rms ? 0.f : warp_sum(s) / (float)n;
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    int col = (c * 32 + lane) * 8;
+    if (col < n) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float d = v[c].v[i] - mean;
+        q += d * d;
+      }
+    }
+  }
+  float rstd = rsqrtf(warp_sum(q) / (float)n + eps);
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    int col = (c * 32 + lane) * 8;
+    if (col < n) {
+      F8 g = load8(gamma, col, w_bf16);
+      F8 o;
+      if (beta) {
+        F8 b = load8(beta, col, w_bf16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o.v[i] = (v[c].v[i] - mean) * rstd * g.v[i] + b.v[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o.v[i] = (v[c].v[i] - mean) * rstd * g.v[i];
+      }
+      store8(y, base + col, o, x_bf16);
+    }
+  }
+}
+
+// general n: re-reads the row (second and third pass hit L1/L2)
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+ln_fwd_kernel_big(const void* __restrict__ x, const void* __restrict__ gamma, const void* __restrict__ beta,
+                  void* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                  int64_t rows, int n, float eps, int x_bf16, int w_bf16, int rms) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int64_t base = row * (int64_t)n;
+  float s = 0.f;
+  for (int col = lane * 8; col < n; col += 256) {
+    F8 a = load8(x, base + col, x_bf16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += a.v[i];
+  }
+  float mean = rms ? 0.f : warp_sum(s) / (float)n;
+  float q = 0.f;
+  for (int col = lane * 8; col < n; col += 256) {
+    F8 a = load8(x, base + col, x_bf16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float d = a.v[i] - mean;
+      q += d * d;
+    }
+  }
+  float rstd = rsqrtf(warp_sum(q) / (float)n + eps);
+  if (lane == 0) {
+    mean_out[row] = mean;
+    rstd_out[row] = rstd;
+  }
+  for (int col = lane * 8; col < n; col += 256) {
+    F8 a = load8(x, base + col, x_bf16);
+    F8 g = load8(gamma, col, w_bf16);
+    F8 o;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o.v[i] = (a.v[i] - mean) * rstd * g.v[i];
+    if (beta) {
+      F8 b = load8(beta, col, w_bf16);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o.v[i] += b.v[i];
+    }
+    store8(y, base + col, o, x_bf16);
+  }
+}
+
+// Backward. grid = n_part CTAs; CTA c handles rows c*4+w, stepping by n_part*4.
+// part layout: [2][n_part][n] (dgamma partials, then dbeta partials).
+template <int CHUNKS>
+__global__ void __launch_bounds__(kWarpsPerCta * 32)
+ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const void* __restrict__ gamma,
+              const float* __restrict__ mean_in, const float* __restrict__ rstd_in, void* __restrict__ dx,
+              float* __restrict__ part, int64_t rows, int n, int n_part, int x_bf16, int w_bf16, int rms) {
+  extern __shared__ float smem[];  // [kWarpsPerCta][2][n]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  F8 g[CHUNKS];
+  F8 acc_g[CHUNKS], acc_b[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    int col = (c * 32 + lane) * 8;
+    if (col < n) g[c] = load8(gamma, col, w_bf16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      acc_g[c].v[i] = 0.f;
+      acc_b[c].v[i] = 0.f;
+    }
+  }
+  for (int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + warp; row < rows; row += (int64_t)n_part * kWarpsPerCta) {
+    const int64_t base = row * (int64_t)n;
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    F8 xh[CHUNKS], d[CHUNKS];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      int col = (c * 32 + lane) * 8;
+      if (col < n) {
+        xh[c] = load8(x, base + col, x_bf16);
+        d[c] = load8(dy, base + col, x_bf16);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[c].v[i] = (xh[c].v[i] - mean) * rstd;
+          float gd = g[c].v[i] * d[c].v[i];
+          s1 += gd;
+          s2 += gd * xh[c].v[i];
+          acc_g[c].v[i] += d[c].v[i] * xh[c].v[i];
+          acc_b[c].v[i] += d[c].v[i];
+        }
+      }
+    }
+    s1 = rms ? 0.f : warp_sum(s1) / (float)n;
+    s2 = warp_sum(s2) / (float)n;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      int col = (c * 32 + lane) * 8;
+      if (col < n) {
+        F8 o;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o.v[i] = rstd * (g[c].v[i] * d[c].v[i] - s1 - xh[c].v[i] * s2);
+        store8(dx, base + col, o, x_bf16);
+      }
+    }
+  }
+  // reduce the 4 warps of the CTA through shared memory
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    int col = (c * 32 + lane) * 8;
+    if (col < n) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        smem[(warp * 2 + 0) * n + col + i] = acc_g[c].v[i];
+        smem[(warp * 2 + 1) * n + col + i] = acc_b[c].v[i];
+      }
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < n; col += blockDim.x) {
+    float sg = 0.f, sb = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarpsPerCta; ++w) {
+      sg += smem[(w * 2 + 0) * n + col];
+      sb += smem[(w * 2 + 1) * n + col];
+    }
+    part[((int64_t)0 * n_part + blockIdx.x) * n + col] = sg;
+    part[((int64_t)1 * n_part + blockIdx.x) * n + col] = sb;
+  }
+}
+
+__global__ void ln_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                     int n, int n_part) {
+  int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= n) return;
+  float sg = 0.f, sb = 0.f;
+  for (int p = 0; p < n_part; ++p) {
+    sg += part[((int64_t)0 * n_part + p) * n + col];
+    sb += part[((int64_t)1 * n_part + p) * n + col];
+  }
+  dgamma[col] = sg;
+  dbeta[col] = sb;
+}
+
+}  // namespace
+
+RB_EXPORT int rb200_layer_norm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+                                   long long rows, int n, float eps, int x_bf16, int w_bf16, int rms, cudaStream_t stream) {
+  if (rows <= 0) return RB_OK;
+  if (n % 8 != 0 || n <= 0) {
+    rb_set_error("layer_norm: n=%d must be a positive multiple of 8", n);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta)), block(kWarpsPerCta * 32);
+  int chunks = (n + 255) / 256;
+#define LN_FWD(C) ln_fwd_kernel<C><<<grid, block, 0, stream>>>(x, gamma, beta, y, mean, rstd, rows, n, eps, x_bf16, w_bf16, rms)
+  if (chunks <= 1) LN_FWD(1);
+  else if (chunks <= 2) LN_FWD(2);
+  else if (chunks <= 4) LN_FWD(4);
+  else if (chunks <= 8) LN_FWD(8);
+  else ln_fwd_kernel_big<<<grid, block, 0, stream>>>(x, gamma, beta, y, mean, rstd, rows, n, eps, x_bf16, w_bf16, rms);
+#undef LN_FWD
+  return rb_check_launch("layer_norm_fwd");
+}
+
+RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                                   void* dx, float* part, float* dgamma, float* dbeta, long long rows, int n, int n_part,
+                                   int x_bf16, int w_bf16, int rms, cudaStream_t stream) {
+  if (n % 8 != 0 || n <= 0 || n > kMaxChunks * 256) {
+    rb_set_error("layer_norm_bwd: n=%d must be a multiple of 8 and <= %d", n, kMaxChunks * 256);
+    return RB_ERR_ARG;
+  }
+  if (n_part <= 0) return RB_ERR_ARG;
+  dim3 grid(n_part), block(kWarpsPerCta * 32);
+  size_t smem = (size_t)kWarpsPerCta * 2 * n * sizeof(float);
+  int chunks = (n + 255) / 256;
+#define LN_BWD(C)                                                                                          \
+  do {                                                                                                     \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(ln_bwd_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    ln_bwd_kernel<C><<<grid, block, smem, stream>>>(x, dy, gamma, mean, rstd, dx, part, rows, n, n_part, x_bf16, w_bf16, rms); \
+  } while (0)
+  if (chunks <= 1) LN_BWD(1);
+  else if (chunks <= 2) LN_BWD(2);
+  else if (chunks <= 4) LN_BWD(4);
+  else LN_BWD(8);
+#undef LN_BWD
+  int st = rb_check_launch("layer_norm_bwd");
+  if (st) return st;
+  ln_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, dgamma, dbeta, n, n_part);
+  return rb_check_launch("layer_norm_bwd_reduce");
+}

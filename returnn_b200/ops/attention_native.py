@@ -34,3 +34,13 @@ def sdpa(q, k, v, *, kv_lens, scale, causal, dropout_p):
 def rel_pos_attention(q, k, v, pos, u, vb, lens, *, scale, dropout_p):
     """fused rel-pos attention"""
     raise NotImplementedError
+
+
+def supports_packed(num_heads: int, head_dim: int, max_len: int) -> bool:
+    """shapes handled by the packed rel-pos kernel"""
+    return False
+
+
+def rel_pos_attention_packed(qkv, pos, u, v, pack, *, num_heads, head_dim, scale, dropout_p):
+    """fused packed rel-pos attention"""
+    raise NotImplementedError

@@ -1,11 +1,21 @@
 """
-CTC loss with fused log-softmax (``csrc/ctc.cu``): one CTA per sequence runs the whole alpha and beta recursion in
-shared memory and writes the gradient w.r.t. the logits (softmax - posterior) directly.
+CTC loss with fused log-softmax.
+
+``ctc_loss`` takes padded logits ``[B, T, V]``; ``ctc_loss_packed`` takes packed logits ``[N, V]`` with ``cu_seqlens``.
+On B200 (``csrc/ctc.cu``): one CTA per sequence computes the per-frame log-sum-exp, runs the alpha and beta recursions
+in shared memory over the extended label sequence and writes ``dlogits = softmax - posterior`` in the logits dtype, so
+the ``[T, V]`` log-probabilities are never materialised. Scratch memory (global): per-frame log-sum-exp and the alpha
+lattice ``[T, 2S+1]`` per sequence. Otherwise ``torch.nn.functional.ctc_loss`` in fp32.
 """
 
 from __future__ import annotations
+from typing import Optional
+import ctypes
 import torch
+import torch.nn.functional as F
 from . import _lib
+
+_vp, _i32, _i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
 
 
 def available() -> bool:
@@ -14,11 +24,70 @@ def available() -> bool:
     return lib is not None and hasattr(lib, "rb200_ctc_loss")
 
 
-def ctc_loss(logits, targets, in_lens, tgt_lens, *, blank_index: int, logits_normalized: bool = False):
-    """placeholder until the kernel binding is filled in"""
-    raise NotImplementedError
-
-
 def supports(logits, targets) -> bool:
-    """shapes handled by the kernel"""
-    return False
+    """dtype / size limits of the kernel"""
+    return logits.dtype in (torch.bfloat16, torch.float32) and targets.shape[-1] <= max_target_len()
+
+
+def max_target_len() -> int:
+    """longest label sequence the kernel handles (extended sequence of 2S+1 states in shared memory)"""
+    return 1023
+
+
+class _CtcFn(torch.autograd.Function):
+    """loss and gradient come out of the same kernel launch; backward scales the stored gradient"""
+
+    @staticmethod
+    def forward(ctx, logits_rows, cu, lens, targets, tgt_lens, blank, max_t, max_s):
+        n, v = logits_rows.shape
+        b = lens.shape[0]
+        logits_rows = logits_rows.contiguous()
+        targets = targets.to(torch.int32).contiguous()
+        loss = torch.empty(b, dtype=torch.float32, device=logits_rows.device)
+        grad = torch.empty_like(logits_rows)
+        s_ext = 2 * max_s + 1
+        # scratch: lse [N] + alpha [N, s_ext] floats
+        scratch = torch.empty(n * (1 + s_ext) + 16, dtype=torch.float32, device=logits_rows.device)
+        fn = _lib.bind("rb200_ctc_loss", [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _vp])
+        _lib.check(fn(logits_rows.data_ptr(), 1 if logits_rows.dtype == torch.bfloat16 else 0, cu.data_ptr(), lens.data_ptr(),
+                      targets.data_ptr(), tgt_lens.data_ptr(), loss.data_ptr(), grad.data_ptr(), scratch.data_ptr(),
+                      b, v, targets.shape[1], max_s, blank, scratch.numel(), _lib.stream_ptr()), "ctc_loss")
+        _lib.count_launch()
+        ctx.save_for_backward(grad, cu, lens)
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        grad, cu, lens = ctx.saved_tensors
+        # per-row scale by the sequence's dloss
+        b = lens.shape[0]
+        row_seq = torch.repeat_interleave(torch.arange(b, device=grad.device), lens.to(torch.int64), output_size=grad.shape[0])
+        scale = dloss.to(torch.float32)[row_seq].unsqueeze(-1)
+        return (grad.float() * scale).to(grad.dtype), None, None, None, None, None, None, None
+
+
+def ctc_loss_packed(logits_rows: torch.Tensor, pack, targets: torch.Tensor, tgt_lens_host: torch.Tensor, *, blank_index: int) -> torch.Tensor:
+    """
+    :param logits_rows: [N, V] unnormalised
+    :param pack: PackInfo of the rows
+    :param targets: [B, S] (padded, any int dtype, on the device)
+    :param tgt_lens_host: [B] on the host
+    :return: [B] negative log likelihood (0 for infeasible alignments)
+    """
+    max_s = int(tgt_lens_host.max()) if tgt_lens_host.numel() else 0
+    if logits_rows.is_cuda and _lib.use_native(logits_rows) and available() and supports(logits_rows, targets):
+        tl = tgt_lens_host.to(torch.int32).to(logits_rows.device, non_blocking=True)
+        return _CtcFn.apply(logits_rows, pack.cu, pack.lens, targets, tl, blank_index, pack.max_len, max_s)
+    padded = pack.unpack(logits_rows)  # [B, T, V]
+    log_probs = F.log_softmax(padded.float(), dim=-1).transpose(0, 1)
+    return F.ctc_loss(log_probs, targets.long(), pack.lens_host.long(), tgt_lens_host.long().cpu(), blank=blank_index, reduction="none", zero_infinity=True)
+
+
+def ctc_loss(logits: torch.Tensor, targets: torch.Tensor, in_lens: torch.Tensor, tgt_lens: torch.Tensor, *, blank_index: int,
+             logits_normalized: bool = False) -> torch.Tensor:
+    """padded variant: packs the valid frames and calls the packed kernel"""
+    from ..models.packing import PackInfo
+
+    pack = PackInfo(in_lens.cpu(), logits.device, padded_len=logits.shape[1])
+    rows = pack.pack(logits)
+    return ctc_loss_packed(rows, pack, targets, tgt_lens.cpu(), blank_index=blank_index)

@@ -397,6 +397,8 @@ class Dim:
         base = self.get_same_base()
         if base.dimension is not None:
             return base.dimension
+        if base.derived_from_op is not None:
+            base._maybe_refresh_derived()
         if base._dim_value_cache is not None:
             return base._dim_value_cache
         ext = self.dyn_size_ext

@@ -413,6 +413,49 @@ class Engine(EngineBase):
         if self._epoch_end_func:
             self._epoch_end_func(epoch=self.epoch, step=self.global_train_step, model=self._orig_model, **get_fwd_compat_kwargs())
 
+    def run_train_step(self, extern_data_raw: Dict[str, Any], *, read_losses: bool = True) -> Dict[str, Any]:
+        """
+        One complete training step on one collated batch: host-to-device copy of the inputs, ``train_step`` under
+        autocast, backward with the gradient reduction, optimizer update, and (``read_losses``) one device-to-host read of
+        the summed losses. This is the unit that ``train_epoch`` repeats; it is public so that benchmarks and custom
+        loops can drive the engine batch by batch.
+
+        :param extern_data_raw: output of the data loader / ``collate_batch`` (host tensors; pinned memory makes the copy async)
+        :return: loss name -> float (``read_losses``) or device scalar tensor
+        """
+        dist = self._torch_distributed_ctx
+        self._updater.get_optimizer().zero_grad()
+        extern_data = extern_data_util.raw_dict_to_extern_data(
+            extern_data_raw, extern_data_template=self.extern_data, device=self._device,
+            float_dtype=self._default_float_dtype, with_eval_targets=True)
+        self._run_step(extern_data, train_flag=True, train_func=True)
+        train_ctx = rf.get_run_ctx()
+        total_loss = train_ctx.total_loss()
+        names = list(train_ctx.losses.keys())
+        summed = [train_ctx.losses[n].get_summed_loss().raw_tensor.detach().float().reshape(()) for n in names]
+        if dist:
+            dist.prepare_backward(sync=True)
+        loss_raw = total_loss.raw_tensor
+        if self._grad_scaler is not None:
+            self._grad_scaler.scale(loss_raw).backward()
+        else:
+            loss_raw.backward()
+        if dist:
+            norm_sq = dist.maybe_reduce_grads(self._pt_model)
+            if norm_sq is not None:
+                self._updater.set_precomputed_grad_norm_sq(norm_sq)
+        self._updater.step(grad_scaler=self._grad_scaler)
+        if dist:
+            dist.step_after_param_update(module=self._pt_model, epoch_step_idx=self.global_train_step)
+        self.global_train_step += 1
+        self._updater.set_current_train_step(global_train_step=self.global_train_step, epoch=self.epoch or 1, epoch_continuous=None)
+        if not summed:
+            return {}
+        if read_losses:
+            vals = torch.stack(summed).cpu().tolist()
+            return dict(zip(names, vals))
+        return dict(zip(names, summed))
+
     def _maybe_extend_losses_info(self, losses: NumbersDict) -> NumbersDict:
         if self._calculate_exp_loss and losses.has_values():
             ctx = rf.get_run_ctx()

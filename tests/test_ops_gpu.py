@@ -1,0 +1,147 @@
+"""
+Numerics of the sm_100a kernels against plain PyTorch fp32 references of the same op.
+"""
+
+import math
+import pytest
+import torch
+
+gpu = pytest.mark.gpu
+
+
+def _need_lib():
+    from returnn_b200.ops import _lib
+
+    assert torch.cuda.is_available()
+    assert _lib.get_lib(required=True) is not None
+
+
+@gpu
+@pytest.mark.parametrize("rows,n", [(1, 8), (37, 512), (1000, 512), (129, 2048), (33, 1000), (5, 4096)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("rms", [False, True])
+def test_layer_norm_fwd_bwd(rows, n, dtype, rms):
+    _need_lib()
+    from returnn_b200.ops import layer_norm as ln
+
+    torch.manual_seed(0)
+    x = (torch.randn(rows, n, device="cuda") * 2 + 0.5).to(dtype).requires_grad_(True)
+    g = (torch.rand(n, device="cuda") + 0.5).requires_grad_(True)
+    b = torch.randn(n, device="cuda").requires_grad_(True)
+    dy = torch.randn(rows, n, device="cuda").to(dtype)
+    fn = ln.rms_norm if rms else ln.layer_norm
+    ref_fn = ln.rms_norm_reference if rms else ln.layer_norm_reference
+    n0 = _launches()
+    y = fn(x, g, b, 1e-6)
+    if n <= 2048:
+        assert _launches() > n0, "native kernel did not run"
+    y.backward(dy)
+    dx, dg, db = x.grad.clone(), g.grad.clone(), b.grad.clone()
+    x32 = x.detach().float().requires_grad_(True)
+    g32 = g.detach().clone().requires_grad_(True)
+    b32 = b.detach().clone().requires_grad_(True)
+    y_ref = ref_fn(x32, g32, b32, 1e-6)
+    y_ref.backward(dy.float())
+    tol = 2e-2 if dtype == torch.bfloat16 else 1e-4
+    torch.testing.assert_close(y.float(), y_ref, atol=tol, rtol=tol)
+    torch.testing.assert_close(dx.float(), x32.grad, atol=tol * 4, rtol=tol * 2)
+    scale = max(1.0, math.sqrt(rows))
+    torch.testing.assert_close(dg, g32.grad, atol=tol * scale, rtol=tol * 2)
+    torch.testing.assert_close(db, b32.grad, atol=tol * scale, rtol=tol * 2)
+
+
+def _launches():
+    from returnn_b200.ops import _lib
+
+    return _lib.launch_count()
+
+
+@gpu
+@pytest.mark.parametrize("n", [1, 127, 4096, 1_000_003])
+def test_sum_squares(n):
+    _need_lib()
+    from returnn_b200.ops import optim_native
+
+    torch.manual_seed(1)
+    x = torch.randn(n, device="cuda")
+    scratch = torch.zeros(1100, device="cuda")
+    got = optim_native.sum_squares(x, scratch)
+    ref = x.double().square().sum()
+    assert abs(got.item() - ref.item()) <= 1e-4 * max(1.0, ref.item())
+
+
+@gpu
+@pytest.mark.parametrize("decoupled", [True, False])
+def test_fused_arena_adamw_matches_torch(decoupled):
+    _need_lib()
+    from returnn_b200.torch.optim.fused_adamw import FusedArenaAdamW
+
+    torch.manual_seed(2)
+
+    def make():
+        m = torch.nn.Sequential(torch.nn.Linear(33, 65), torch.nn.LayerNorm(65), torch.nn.Linear(65, 7)).cuda()
+        return m
+
+    m1 = make()
+    m2 = make()
+    m2.load_state_dict(m1.state_dict())
+    wd_names = {"0.weight", "2.weight"}
+    opt1 = FusedArenaAdamW(m1, lr=1e-2, betas=(0.9, 0.98), eps=1e-8, weight_decay=0.1, decoupled=decoupled, weight_decay_param_names=wd_names)
+    cls = torch.optim.AdamW if decoupled else torch.optim.Adam
+    opt2 = cls([{"params": [m2[0].weight, m2[2].weight], "weight_decay": 0.1},
+                {"params": [m2[0].bias, m2[1].weight, m2[1].bias, m2[2].bias], "weight_decay": 0.0}], lr=1e-2, betas=(0.9, 0.98), eps=1e-8)
+    for step in range(5):
+        x = torch.randn(16, 33, device="cuda")
+        for m, opt in ((m1, opt1), (m2, opt2)):
+            opt.zero_grad()
+            m(x).square().mean().backward()
+        if step == 2:
+            norm = opt1.grad_norm()
+            ref_norm = torch.nn.utils.clip_grad_norm_(m2.parameters(), 0.05)
+            torch.testing.assert_close(norm, ref_norm, atol=1e-5, rtol=1e-4)
+            opt1.set_clip(0.05, norm)
+        opt1.step()
+        opt2.step()
+    for (n1, p1), (n2, p2) in zip(m1.named_parameters(), m2.named_parameters()):
+        torch.testing.assert_close(p1, p2, atol=2e-6, rtol=1e-5, msg=lambda s: "%s: %s" % (n1, s))
+    sd = opt1.state_dict()
+    assert set(sd["state"][0].keys()) == {"step", "exp_avg", "exp_avg_sq"}
+
+
+@gpu
+def test_dropout_mask_replay_and_rate():
+    _need_lib()
+    from returnn_b200.ops import elementwise as ew
+
+    x = torch.ones(1 << 20, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = ew.dropout(x, 0.25)
+    keep = (y.float() != 0).float().mean().item()
+    assert abs(keep - 0.75) < 5e-3
+    assert torch.all((y == 0) | ((y.float() - 1.0 / 0.75).abs() < 1e-2))
+    y.backward(torch.ones_like(y))
+    # backward re-creates exactly the forward mask
+    assert torch.equal(x.grad != 0, y != 0)
+    y2 = ew.dropout(x, 0.25)
+    assert not torch.equal(y2 != 0, y != 0), "a second call must draw a new mask"
+
+
+@gpu
+@pytest.mark.parametrize("rows,v", [(7, 10001), (64, 32000), (3, 13)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("smoothing", [0.0, 0.1])
+def test_softmax_ce(rows, v, dtype, smoothing):
+    _need_lib()
+    from returnn_b200.ops import softmax_ce as ce
+
+    torch.manual_seed(3)
+    logits = (torch.randn(rows, v, device="cuda") * 3).to(dtype).requires_grad_(True)
+    tgt = torch.randint(0, v, (rows,), device="cuda", dtype=torch.int32)
+    w = torch.rand(rows, device="cuda")
+    loss = ce.softmax_cross_entropy(logits, tgt, smoothing)
+    (loss * w).sum().backward()
+    l32 = logits.detach().float().requires_grad_(True)
+    ref = ce.softmax_cross_entropy_reference(l32, tgt, smoothing)
+    (ref * w).sum().backward()
+    torch.testing.assert_close(loss, ref, atol=2e-3, rtol=1e-4)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(logits.grad.float(), l32.grad, atol=tol, rtol=tol)
