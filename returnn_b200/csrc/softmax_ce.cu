@@ -40,7 +40,7 @@ ce_fwd_kernel(const void* __restrict__ logits, const int* __restrict__ tgt, floa
   }
   __shared__ float sh_m[8], sh_s[8], sh_t[8];
   float wm = warp_max(mx);
-  float ws = warp_sum(sum * __expf(mx - wm));
+  float ws = warp_sum(mx == -INFINITY ? 0.f : sum * __expf(mx - wm));
   float wt = warp_sum(tot);
   if ((threadIdx.x & 31) == 0) {
     sh_m[threadIdx.x >> 5] = wm;
@@ -53,7 +53,7 @@ ce_fwd_kernel(const void* __restrict__ logits, const int* __restrict__ tgt, floa
     for (int w = 1; w < 8; ++w) m = fmaxf(m, sh_m[w]);
     float s = 0.f, t = 0.f;
     for (int w = 0; w < 8; ++w) {
-      s += sh_s[w] * __expf(sh_m[w] - m);
+      if (sh_m[w] != -INFINITY) s += sh_s[w] * __expf(sh_m[w] - m);
       t += sh_t[w];
     }
     float lse = m + logf(s);

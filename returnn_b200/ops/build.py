@@ -76,7 +76,7 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
                 print(o)
     lib = os.path.join(_BUILD, "librb200.so")
     if jobs or force or _newer(lib, objs):
-        _run([nvcc, "-shared", "-o", lib] + objs + ["-lcudart", "-lcuda"], verbose)
+        _run([nvcc, "-shared", "-o", lib] + objs, verbose)
     return lib
 
 

@@ -90,6 +90,8 @@ class Engine(EngineBase):
             print("Start running torch distributed training on local rank %i." % local_rank, file=log.v2)
             if self._device == "cuda":
                 self._device = "cuda:%i" % (local_rank % max(torch.cuda.device_count(), 1))
+        if self._device == "cuda":
+            self._device = "cuda:%i" % torch.cuda.current_device()
         if self._device.startswith("cuda"):
             torch.cuda.set_device(self._device)
         self._log_memory_usage = config.bool("torch_log_memory_usage", False)

@@ -1,0 +1,73 @@
+"""
+tcgen05 GEMM against an fp32 torch matmul, all four operand layouts, edge sizes, epilogues, and the linear autograd path.
+"""
+
+import pytest
+import torch
+
+gpu = pytest.mark.gpu
+
+
+def _mk(rows, cols, seed):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    return (torch.randn(rows, cols, device="cuda", generator=g) * 0.5).to(torch.bfloat16)
+
+
+@gpu
+@pytest.mark.parametrize("m,n,k", [(128, 128, 64), (256, 384, 512), (200, 136, 72), (6700, 2048, 512), (33, 10008, 512), (1, 8, 8)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (False, False), (True, True), (True, False)])
+def test_gemm_layouts(m, n, k, a_mn, b_mn):
+    from returnn_b200.ops import gemm
+
+    a_log = _mk(m, k, 1)  # logical A [m, k]
+    b_log = _mk(k, n, 2)  # logical B [k, n]
+    a = a_log.t().contiguous() if a_mn else a_log  # stored [k, m] or [m, k]
+    b = b_log if b_mn else b_log.t().contiguous()  # stored [k, n] or [n, k]
+    if (a.stride(0) % 8) or (b.stride(0) % 8):
+        pytest.skip("pitch not a multiple of 8 elements")
+    out = gemm.gemm(a, b, m=m, n=n, k=k, a_mn_major=a_mn, b_mn_major=b_mn)
+    gemm.check_status()
+    ref = a_log.float() @ b_log.float()
+    torch.testing.assert_close(out.float(), ref, atol=0.06 + 2e-3 * k ** 0.5, rtol=2e-2)
+
+
+@gpu
+@pytest.mark.parametrize("act", [None, "relu", "silu", "gelu"])
+def test_gemm_epilogue(act):
+    from returnn_b200.ops import gemm
+
+    m, n, k = 300, 264, 136
+    a, b = _mk(m, k, 3), _mk(k, n, 4)
+    bias = torch.randn(n, device="cuda")
+    z, y = gemm.gemm(a, b, m=m, n=n, k=k, a_mn_major=False, b_mn_major=True, bias=bias, act=act, want_act_output=True)
+    gemm.check_status()
+    zr = a.float() @ b.float() + bias
+    fn = {None: lambda t: t, "relu": torch.relu, "silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu}[act]
+    torch.testing.assert_close(z.float(), zr, atol=0.08, rtol=2e-2)
+    torch.testing.assert_close(y.float(), fn(zr), atol=0.08, rtol=2e-2)
+    out32 = torch.ones(m, n, device="cuda")
+    gemm.gemm(a, b, m=m, n=n, k=k, a_mn_major=False, b_mn_major=True, out=out32, accumulate=True, alpha=0.5)
+    torch.testing.assert_close(out32, 1.0 + 0.5 * (a.float() @ b.float()), atol=0.05, rtol=1e-2)
+
+
+@gpu
+def test_linear_autograd_matches_fp32():
+    from returnn_b200.ops import gemm, linear
+
+    torch.manual_seed(0)
+    x = (torch.randn(5, 77, 512, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(512, 2048, device="cuda") * 0.05).to(torch.bfloat16).requires_grad_(True)
+    b = torch.randn(2048, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(5, 77, 2048, device="cuda").to(torch.bfloat16)
+    assert gemm.ENABLED
+    y = linear.linear(x, w, b, "silu")
+    y.backward(dy)
+    gemm.check_status()
+    xr, wr, br = (t.detach().float().requires_grad_(True) for t in (x, w, b))
+    yr = torch.nn.functional.silu(xr @ wr + br)
+    yr.backward(dy.float())
+    torch.testing.assert_close(y.float(), yr, atol=0.05, rtol=2e-2)
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=0.05, rtol=3e-2)
+    torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.4, rtol=3e-2)
+    torch.testing.assert_close(b.grad.float(), br.grad, atol=0.5, rtol=3e-2)
