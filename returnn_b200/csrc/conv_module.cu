@@ -1,0 +1,381 @@
+// Conformer convolution module core on packed rows: GLU -> depthwise conv along time -> BatchNorm (statistics over the
+// valid frames) -> SiLU, forward and backward.
+//
+// x [N, 2C] bf16 (output of the first pointwise GEMM), packed rows of B sequences (row_batch / row_pos / lens give the
+// sequence, position and length of each row). Depthwise filter [C, K] taps, "same" padding with (K-1)/2 taps to the
+// left, zero outside each sequence.
+//
+//   forward   glu_dwconv_fwd : h = a * sigmoid(g); y[r,c] = bias[c] + sum_k f[c,k] * h[r+k-left, c]; per-CTA partial sums
+//                              of y and y^2 per channel (scratch)
+//             bn_stats       : partials -> mean, rstd (and running statistics)
+//             bn_silu_fwd    : z = silu((y - mean) * rstd * gamma + beta)
+//   backward  bn_silu_bwd_a  : ds = dz * silu'(s); per-CTA partial sums of ds and ds * yhat
+//             bn_bwd_reduce  : partials -> dgamma, dbeta (and the two means used below)
+//             bn_silu_bwd_b  : dy = gamma * rstd * (ds - mean(ds) - yhat * mean(ds * yhat))
+//             glu_dwconv_bwd : dh[r,c] = sum_k f[c,k] * dy[r-k+left, c]; dx = (dh * sigmoid(g), dh * a * sigmoid'(g));
+//                              per-CTA partial sums for dfilter [C,K] and dbias
+// All reductions go through per-CTA partials and a second pass: no atomics, deterministic.
+#include "common.cuh"
+
+namespace {
+
+constexpr int TT = 32;       // output rows per CTA
+constexpr int CC = 64;       // channels per CTA
+constexpr int KMAX = 64;     // maximum number of taps
+constexpr int kThreads = 256;  // 64 channels x 4 row groups of 8 rows
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+// ---------------------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+glu_dwconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ filt, const float* __restrict__ bias,
+                      const int* __restrict__ row_batch, const int* __restrict__ row_pos, const int* __restrict__ lens,
+                      __nv_bfloat16* __restrict__ y, float* __restrict__ part, int n_rows, int C, int K) {
+  __shared__ float sh[(TT + KMAX - 1) * CC];
+  __shared__ float red[2][4][CC];
+  const int left = (K - 1) / 2;
+  const int r0 = blockIdx.x * TT;
+  const int c0 = blockIdx.y * CC;
+  const int n_in = TT + K - 1;
+  // stage h = a * sigmoid(g) for rows r0-left .. r0-left+n_in-1
+  for (int idx = threadIdx.x; idx < n_in * CC; idx += kThreads) {
+    const int s = idx / CC, c = idx % CC;
+    const int r = r0 - left + s;
+    float h = 0.f;
+    if (r >= 0 && r < n_rows) {
+      const float a = __bfloat162float(x[(size_t)r * 2 * C + c0 + c]);
+      const float g = __bfloat162float(x[(size_t)r * 2 * C + C + c0 + c]);
+      h = a * sigmoidf_(g);
+    }
+    sh[s * CC + c] = h;
+  }
+  __syncthreads();
+  const int c = threadIdx.x % CC;
+  const int rg = threadIdx.x / CC;
+  float f[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) f[k] = k < K ? filt[(size_t)(c0 + c) * K + k] : 0.f;
+  const float bv = bias ? bias[c0 + c] : 0.f;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = 0; i < TT / 4; ++i) {
+    const int lr = rg * (TT / 4) + i;
+    const int r = r0 + lr;
+    if (r >= n_rows) break;
+    const int t = row_pos[r];
+    const int L = lens[row_batch[r]];
+    const int k_lo = max(0, left - t);
+    const int k_hi = min(K, L - t + left);
+    float acc = bv;
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      if (k >= k_lo && k < k_hi) acc += f[k] * sh[(lr + k) * CC + c];
+    }
+    const __nv_bfloat16 o = __float2bfloat16(acc);
+    y[(size_t)r * C + c0 + c] = o;
+    const float of = __bfloat162float(o);
+    s1 += of;
+    s2 += of * of;
+  }
+  red[0][rg][c] = s1;
+  red[1][rg][c] = s2;
+  __syncthreads();
+  if (threadIdx.x < CC) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      a += red[0][g][threadIdx.x];
+      b += red[1][g][threadIdx.x];
+    }
+    part[((size_t)blockIdx.x * 2 + 0) * C + c0 + threadIdx.x] = a;
+    part[((size_t)blockIdx.x * 2 + 1) * C + c0 + threadIdx.x] = b;
+  }
+}
+
+// partials [n_tiles][2][C] -> mean, rstd; running stats update (momentum) when given
+__global__ void bn_stats_kernel(const float* __restrict__ part, int n_tiles, int C, float count, float eps, float momentum,
+                                float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ running_mean,
+                                float* __restrict__ running_var) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (int t = 0; t < n_tiles; ++t) {
+    s1 += part[((size_t)t * 2 + 0) * C + c];
+    s2 += part[((size_t)t * 2 + 1) * C + c];
+  }
+  const double m = s1 / count;
+  double var = s2 / count - m * m;
+  if (var < 0.0) var = 0.0;
+  mean[c] = (float)m;
+  rstd[c] = rsqrtf((float)var + eps);
+  if (running_mean) {
+    running_mean[c] += momentum * ((float)m - running_mean[c]);
+    running_var[c] += momentum * ((float)var - running_var[c]);
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_silu_fwd_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean, const float* __restrict__ rstd,
+                   const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ z, long long total, int C) {
+  const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= total) return;
+  const int c = (int)(i8 % C);
+  F8 v = load8(y, i8, 1);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float s = (v.v[k] - mean[c + k]) * rstd[c + k] * (gamma ? gamma[c + k] : 1.f) + (beta ? beta[c + k] : 0.f);
+    v.v[k] = s * sigmoidf_(s);
+  }
+  store8(z, i8, v, 1);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// ds = dz * silu'(s) written to ds_out (bf16); per-CTA partials of sum(ds) and sum(ds*yhat) per channel.
+// grid.x tiles of 64 rows; block 256 = 64 channel-octets?  -> layout: thread handles 8 channels of one row at a time.
+__global__ void __launch_bounds__(256)
+bn_silu_bwd_a_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dz, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     __nv_bfloat16* __restrict__ ds_out, float* __restrict__ part, int n_rows, int C, int rows_per_cta) {
+  // threads: C/8 column groups x (256 / (C/8)) row lanes; requires C/8 <= 256 and 256 % (C/8) == 0
+  extern __shared__ float shm[];  // [row_lanes][2][C]
+  const int groups = C / 8;
+  const int row_lanes = blockDim.x / groups;
+  const int cg = threadIdx.x % groups;
+  const int rl = threadIdx.x / groups;
+  const int c = cg * 8;
+  float a1[8], a2[8];
+#pragma unroll
+  for (int k = 0; k < 8; ++k) a1[k] = a2[k] = 0.f;
+  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_end = min(n_rows, r_begin + rows_per_cta);
+  if (rl < row_lanes) {
+    for (int r = r_begin + rl; r < r_end; r += row_lanes) {
+      F8 yv = load8(y, (long long)r * C + c, 1);
+      F8 dv = load8(dz, (long long)r * C + c, 1);
+      F8 o;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const float yh = (yv.v[k] - mean[c + k]) * rstd[c + k];
+        const float s = yh * (gamma ? gamma[c + k] : 1.f) + (beta ? beta[c + k] : 0.f);
+        const float sg = sigmoidf_(s);
+        const float d = dv.v[k] * (sg * (1.f + s * (1.f - sg)));
+        o.v[k] = d;
+        a1[k] += d;
+        a2[k] += d * yh;
+      }
+      store8(ds_out, (long long)r * C + c, o, 1);
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      shm[(rl * 2 + 0) * C + c + k] = a1[k];
+      shm[(rl * 2 + 1) * C + c + k] = a2[k];
+    }
+  }
+  __syncthreads();
+  for (int cc = threadIdx.x; cc < C; cc += blockDim.x) {
+    float s1 = 0.f, s2 = 0.f;
+    for (int l = 0; l < row_lanes; ++l) {
+      s1 += shm[(l * 2 + 0) * C + cc];
+      s2 += shm[(l * 2 + 1) * C + cc];
+    }
+    part[((size_t)blockIdx.x * 2 + 0) * C + cc] = s1;
+    part[((size_t)blockIdx.x * 2 + 1) * C + cc] = s2;
+  }
+}
+
+// partials -> sum_ds (= dbeta), sum_ds_yhat (= dgamma)
+__global__ void bn_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (int t = 0; t < n_tiles; ++t) {
+    s1 += part[((size_t)t * 2 + 0) * C + c];
+    s2 += part[((size_t)t * 2 + 1) * C + c];
+  }
+  sum_ds[c] = (float)s1;
+  sum_ds_yh[c] = (float)s2;
+}
+
+// dy = gamma * rstd * (ds - sum_ds/count - yhat * sum_ds_yh/count), in place over ds
+__global__ void __launch_bounds__(256)
+bn_silu_bwd_b_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ ds, const float* __restrict__ mean,
+                     const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ sum_ds,
+                     const float* __restrict__ sum_ds_yh, float inv_count, long long total, int C) {
+  const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
+  if (i8 >= total) return;
+  const int c = (int)(i8 % C);
+  F8 yv = load8(y, i8, 1);
+  F8 dv = load8(ds, i8, 1);
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const float yh = (yv.v[k] - mean[c + k]) * rstd[c + k];
+    dv.v[k] = (gamma ? gamma[c + k] : 1.f) * rstd[c + k] * (dv.v[k] - sum_ds[c + k] * inv_count - yh * sum_ds_yh[c + k] * inv_count);
+  }
+  store8(ds, i8, dv, 1);
+}
+
+// depthwise conv backward + GLU backward. part layout: [n_tiles][C][K+1] (K filter taps, then the bias)
+__global__ void __launch_bounds__(kThreads)
+glu_dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ filt,
+                      const int* __restrict__ row_batch, const int* __restrict__ row_pos, const int* __restrict__ lens,
+                      __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int n_rows, int C, int K) {
+  __shared__ float sh_dy[(TT + KMAX - 1) * CC];   // dy rows r0-(K-1-left) .. : used for dh
+  __shared__ float sh_h[(TT + KMAX - 1) * CC];    // h rows r0-left .. : used for dfilter
+  const int left = (K - 1) / 2;
+  const int right = K - 1 - left;
+  const int r0 = blockIdx.x * TT;
+  const int c0 = blockIdx.y * CC;
+  const int n_in = TT + K - 1;
+  for (int idx = threadIdx.x; idx < n_in * CC; idx += kThreads) {
+    const int s = idx / CC, c = idx % CC;
+    // dh[r] = sum_k f[k] * dy[r - k + left]  ->  needs dy rows r0 - right .. r0 + TT - 1 + left
+    const int rd = r0 - right + s;
+    sh_dy[s * CC + c] = (rd >= 0 && rd < n_rows) ? __bfloat162float(dy[(size_t)rd * C + c0 + c]) : 0.f;
+    const int rh = r0 - left + s;
+    float h = 0.f;
+    if (rh >= 0 && rh < n_rows) {
+      const float a = __bfloat162float(x[(size_t)rh * 2 * C + c0 + c]);
+      const float g = __bfloat162float(x[(size_t)rh * 2 * C + C + c0 + c]);
+      h = a * sigmoidf_(g);
+    }
+    sh_h[s * CC + c] = h;
+  }
+  __syncthreads();
+  const int c = threadIdx.x % CC;
+  const int rg = threadIdx.x / CC;
+  float f[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) f[k] = k < K ? filt[(size_t)(c0 + c) * K + k] : 0.f;
+  float df[KMAX];
+#pragma unroll
+  for (int k = 0; k < KMAX; ++k) df[k] = 0.f;
+  float dbias = 0.f;
+  for (int i = 0; i < TT / 4; ++i) {
+    const int lr = rg * (TT / 4) + i;
+    const int r = r0 + lr;
+    if (r >= n_rows) break;
+    const int t = row_pos[r];
+    const int L = lens[row_batch[r]];
+    // dh: contributions from output rows r' = r - k + left (position t - k + left) that lie inside the sequence
+    float dh = 0.f;
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      const int tp = t - k + left;
+      if (k < K && tp >= 0 && tp < L) dh += f[k] * sh_dy[(lr + right - k + left) * CC + c];
+    }
+    const float a = __bfloat162float(x[(size_t)r * 2 * C + c0 + c]);
+    const float g = __bfloat162float(x[(size_t)r * 2 * C + C + c0 + c]);
+    const float sg = sigmoidf_(g);
+    dx[(size_t)r * 2 * C + c0 + c] = __float2bfloat16(dh * sg);
+    dx[(size_t)r * 2 * C + C + c0 + c] = __float2bfloat16(dh * a * sg * (1.f - sg));
+    // dfilter[k] += dy[r] * h[r + k - left] for taps inside the sequence
+    const float dyr = sh_dy[(lr + right) * CC + c];
+    dbias += dyr;
+    const int k_lo = max(0, left - t);
+    const int k_hi = min(K, L - t + left);
+#pragma unroll
+    for (int k = 0; k < KMAX; ++k) {
+      if (k >= k_lo && k < k_hi) df[k] += dyr * sh_h[(lr + k) * CC + c];
+    }
+  }
+  // reduce the 4 row groups through shared memory (reuse sh_h as [K+1][CC] accumulators), then one partial per CTA
+  __syncthreads();
+  float* red = sh_h;
+  for (int g = 0; g < 4; ++g) {
+    if (rg == g) {
+#pragma unroll
+      for (int k = 0; k < KMAX; ++k)
+        if (k < K) red[k * CC + c] = (g == 0 ? 0.f : red[k * CC + c]) + df[k];
+      red[K * CC + c] = (g == 0 ? 0.f : red[K * CC + c]) + dbias;
+    }
+    __syncthreads();
+  }
+  for (int idx = threadIdx.x; idx < (K + 1) * CC; idx += kThreads) {
+    const int k = idx / CC, cc = idx % CC;
+    part[((size_t)blockIdx.x * C + c0 + cc) * (K + 1) + k] = red[k * CC + cc];
+  }
+}
+
+__global__ void dwconv_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, int K, float* __restrict__ dfilt,
+                                         float* __restrict__ dbias) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= C * (K + 1)) return;
+  const int c = idx / (K + 1), k = idx % (K + 1);
+  double s = 0.0;
+  for (int t = 0; t < n_tiles; ++t) s += part[((size_t)t * C + c) * (K + 1) + k];
+  if (k < K) dfilt[(size_t)c * K + k] = (float)s;
+  else if (dbias) dbias[c] = (float)s;
+}
+
+}  // namespace
+
+// scratch `part` sizes (floats): forward ceil(N/32)*2*C; backward-a n_tiles_a*2*C; backward conv ceil(N/32)*C*(K+1)
+RB_EXPORT int rb200_glu_dwconv_fwd(const void* x, const float* filt, const float* bias, const int* row_batch, const int* row_pos,
+                                   const int* lens, void* y, float* part, int n_rows, int C, int K, cudaStream_t stream) {
+  if (n_rows <= 0) return RB_OK;
+  if (C % CC || K > KMAX || K < 1) {
+    rb_set_error("glu_dwconv: C=%d must be a multiple of %d and K=%d <= %d", C, CC, K, KMAX);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((n_rows + TT - 1) / TT, C / CC);
+  glu_dwconv_fwd_kernel<<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, filt, bias, row_batch, row_pos, lens, (__nv_bfloat16*)y, part, n_rows, C, K);
+  return rb_check_launch("glu_dwconv_fwd");
+}
+
+RB_EXPORT int rb200_bn_stats(const float* part, int n_tiles, int C, float count, float eps, float momentum, float* mean, float* rstd,
+                             float* running_mean, float* running_var, cudaStream_t stream) {
+  bn_stats_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, count, eps, momentum, mean, rstd, running_mean, running_var);
+  return rb_check_launch("bn_stats");
+}
+
+RB_EXPORT int rb200_bn_silu_fwd(const void* y, const float* mean, const float* rstd, const float* gamma, const float* beta, void* z,
+                                long long n_rows, int C, cudaStream_t stream) {
+  if (n_rows <= 0) return RB_OK;
+  if (C % 8) return RB_ERR_ARG;
+  long long total = n_rows * C;
+  bn_silu_fwd_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)y, mean, rstd, gamma, beta, (__nv_bfloat16*)z, total, C);
+  return rb_check_launch("bn_silu_fwd");
+}
+
+// ds (bf16 [N,C]) receives ds, later overwritten in place by dy. part: n_tiles*2*C floats.
+RB_EXPORT int rb200_bn_silu_bwd(const void* y, const void* dz, const float* mean, const float* rstd, const float* gamma, const float* beta,
+                                void* ds, float* part, int n_tiles, float* sum_ds, float* sum_ds_yh, long long n_rows, int C,
+                                int training, cudaStream_t stream) {
+  if (n_rows <= 0) return RB_OK;
+  const int groups = C / 8;
+  if (C % 8 || groups > 256 || 256 % groups) {
+    rb_set_error("bn_silu_bwd: C=%d unsupported", C);
+    return RB_ERR_ARG;
+  }
+  const int row_lanes = 256 / groups;
+  const int rows_per_cta = (int)((n_rows + n_tiles - 1) / n_tiles);
+  size_t smem = (size_t)row_lanes * 2 * C * sizeof(float);
+  bn_silu_bwd_a_kernel<<<n_tiles, 256, smem, stream>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)dz, mean, rstd, gamma, beta,
+                                                       (__nv_bfloat16*)ds, part, (int)n_rows, C, rows_per_cta);
+  int st = rb_check_launch("bn_silu_bwd_a");
+  if (st) return st;
+  bn_bwd_reduce_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh);
+  st = rb_check_launch("bn_bwd_reduce");
+  if (st) return st;
+  if (training) {
+    long long total = n_rows * C;
+    bn_silu_bwd_b_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)ds, mean, rstd, gamma,
+                                                                                 sum_ds, sum_ds_yh, 1.f / (float)n_rows, total, C);
+    st = rb_check_launch("bn_silu_bwd_b");
+  }
+  return st;
+}
+
+RB_EXPORT int rb200_glu_dwconv_bwd(const void* x, const void* dy, const float* filt, const int* row_batch, const int* row_pos,
+                                   const int* lens, void* dx, float* part, float* dfilt, float* dbias, int n_rows, int C, int K,
+                                   cudaStream_t stream) {
+  if (n_rows <= 0) return RB_OK;
+  if (C % CC || K > KMAX || K < 1) return RB_ERR_ARG;
+  const int n_tiles = (n_rows + TT - 1) / TT;
+  dim3 grid(n_tiles, C / CC);
+  glu_dwconv_bwd_kernel<<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch, row_pos, lens,
+                                                       (__nv_bfloat16*)dx, part, n_rows, C, K);
+  int st = rb_check_launch("glu_dwconv_bwd");
+  if (st) return st;
+  dwconv_bwd_reduce_kernel<<<(C * (K + 1) + 255) / 256, 256, 0, stream>>>(part, n_tiles, C, K, dfilt, dbias);
+  return rb_check_launch("dwconv_bwd_reduce");
+}

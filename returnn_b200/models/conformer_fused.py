@@ -126,7 +126,9 @@ def conv_block(x, layer, pack: PackInfo, W, p_drop, training, eps):
     h = _ln.layer_norm(x, W(layer.conv_layer_norm.scale), W(layer.conv_layer_norm.bias), eps)
     h = _lin.linear(h, W(cb.positionwise_conv1.weight), W(cb.positionwise_conv1.bias))  # [N, 2D]
     bn = cb.norm
-    h = _cm.glu_dwconv_bn_silu(h, W(cb.depthwise_conv.filter), W(cb.depthwise_conv.bias), bn, pack, training=training)
+    # small fp32 parameters go in as they are: the kernels read fp32 filter / BatchNorm parameters
+    h = _cm.glu_dwconv_bn_silu(h, cb.depthwise_conv.filter.raw_tensor, cb.depthwise_conv.bias.raw_tensor if cb.depthwise_conv.bias is not None else None,
+                               bn, pack, training=training)
     h = _lin.linear(h, W(cb.positionwise_conv2.weight), W(cb.positionwise_conv2.bias))
     return x + _dropout(h, p_drop, training)
 
