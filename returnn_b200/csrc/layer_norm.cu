@@ -255,3 +255,73 @@ RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* ga
   ln_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, dgamma, dbeta, n, n_part);
   return rb_check_launch("layer_norm_bwd_reduce");
 }
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Allocation-free variant of the backward pass (declared in no_alloc.h).
+//
+// rb200_layer_norm_bwd above takes its scratch (the per-CTA partial sums of dgamma / dbeta) from the caller, who has to
+// allocate n_part * n * 2 floats of device memory for every call. Some callers cannot do that: a host program that links
+// this library without an allocator of its own (no torch), a serving process whose memory pool already owns all of the
+// device memory so that a cudaMalloc at call time fails, or a latency-critical loop in which the implicit device-wide
+// synchronisation of cudaMalloc / cudaFree is not acceptable. For them the scratch lives in the fixed array below.
+//
+// The array is part of the library image: every GPU on which the library is used holds kNoAllocScratchFloats * 4 bytes
+// (2.3 MiB) from the first use until the process exits. All calls on a device share it and it keeps the contents of the
+// previous call. Nothing in it has to start at zero: each launch overwrites every partial that its second pass reads.
+// Two calls that overlap on the same GPU (different streams, or different host threads) race on the array; callers
+// must serialise them, e.g. by using one stream.
+namespace {
+
+constexpr int kNoAllocParts = 148;                                   // one partial per SM
+constexpr int kNoAllocMaxN = kMaxChunks * 256;                       // 2048 columns
+constexpr size_t kNoAllocScratchFloats = (size_t)2 * kNoAllocParts * kNoAllocMaxN;
+
+static __device__ __align__(256) float g_ln_bwd_scratch[kNoAllocScratchFloats];
+
+constexpr int kMaxDevices = 64;
+float* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// The name g_ln_bwd_scratch is only a host-side handle here; the device address has to be looked up once per device,
+// with that device current.
+int no_alloc_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    rb_set_error("layer_norm_bwd_noalloc: cudaGetDevice: %s (device %d)", cudaGetErrorString(e), dev);
+    return RB_ERR_LAUNCH;
+  }
+  if (g_scratch_ptr[dev] == nullptr) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_ln_bwd_scratch);
+    if (e != cudaSuccess || ptr == nullptr) {
+      rb_set_error("layer_norm_bwd_noalloc: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+      return RB_ERR_LAUNCH;
+    }
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return RB_OK;
+}
+
+}  // namespace
+
+RB_EXPORT int rb200_layer_norm_bwd_noalloc(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                                           void* dx, float* dgamma, float* dbeta, long long rows, int n, int x_bf16, int w_bf16, int rms,
+                                           cudaStream_t stream) {
+  if (n <= 0 || n % 8 != 0 || n > kNoAllocMaxN) {
+    rb_set_error("layer_norm_bwd_noalloc: n=%d is not supported: the built-in scratch holds rows of at most %d columns (multiple of 8)",
+                 n, kNoAllocMaxN);
+    return RB_ERR_ARG;
+  }
+  if (rows <= 0) {
+    rb_set_error("layer_norm_bwd_noalloc: rows=%lld", rows);
+    return RB_ERR_ARG;
+  }
+  float* scratch = nullptr;
+  int st = no_alloc_scratch(&scratch);
+  if (st) return st;
+  return rb200_layer_norm_bwd(x, dy, gamma, mean, rstd, dx, scratch, dgamma, dbeta, rows, n, kNoAllocParts, x_bf16, w_bf16, rms, stream);
+}
+
+RB_EXPORT int rb200_layer_norm_bwd_noalloc_max_n() { return kNoAllocMaxN; }
+RB_EXPORT int rb200_layer_norm_bwd_noalloc_parts() { return kNoAllocParts; }
