@@ -26,43 +26,43 @@ def available() -> bool:
 
 def supports(logits, targets) -> bool:
     """dtype / size limits of the kernel"""
-    return logits.dtype in (torch.bfloat16, torch.float32) and targets.shape[-1] <= max_target_len()
+    return logits.dtype in (torch.bfloat16, torch.float32) and targets.shape[-1] <= max_target_len() and logits.shape[-1] <= 50000
 
 
 def max_target_len() -> int:
-    """longest label sequence the kernel handles (extended sequence of 2S+1 states in shared memory)"""
-    return 1023
+    """longest label sequence the kernel handles (3 * (2S+1) floats of shared memory per sequence)"""
+    return 4000
 
 
 class _CtcFn(torch.autograd.Function):
-    """loss and gradient come out of the same kernel launch; backward scales the stored gradient"""
+    """loss and gradient come out of the same launches; backward scales the stored gradient by dloss of its sequence"""
 
     @staticmethod
-    def forward(ctx, logits_rows, cu, lens, targets, tgt_lens, blank, max_t, max_s):
+    def forward(ctx, logits_rows, cu, row_batch, lens, targets, tgt_lens, blank, max_s):
         n, v = logits_rows.shape
         b = lens.shape[0]
         logits_rows = logits_rows.contiguous()
         targets = targets.to(torch.int32).contiguous()
+        if targets.dim() == 1:
+            targets = targets.unsqueeze(0)
         loss = torch.empty(b, dtype=torch.float32, device=logits_rows.device)
-        grad = torch.empty_like(logits_rows)
+        need_grad = logits_rows.requires_grad
+        grad = torch.empty_like(logits_rows) if need_grad else None
         s_ext = 2 * max_s + 1
-        # scratch: lse [N] + alpha [N, s_ext] floats
-        scratch = torch.empty(n * (1 + s_ext) + 16, dtype=torch.float32, device=logits_rows.device)
-        fn = _lib.bind("rb200_ctc_loss", [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i64, _vp])
-        _lib.check(fn(logits_rows.data_ptr(), 1 if logits_rows.dtype == torch.bfloat16 else 0, cu.data_ptr(), lens.data_ptr(),
-                      targets.data_ptr(), tgt_lens.data_ptr(), loss.data_ptr(), grad.data_ptr(), scratch.data_ptr(),
-                      b, v, targets.shape[1], max_s, blank, scratch.numel(), _lib.stream_ptr()), "ctc_loss")
-        _lib.count_launch()
-        ctx.save_for_backward(grad, cu, lens)
+        scratch = torch.empty(n * (1 + 2 * s_ext) + b, dtype=torch.float32, device=logits_rows.device)
+        fn = _lib.bind("rb200_ctc_loss", [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp])
+        _lib.check(fn(logits_rows.data_ptr(), 1 if logits_rows.dtype == torch.bfloat16 else 0, cu.data_ptr(), row_batch.data_ptr(),
+                      targets.data_ptr(), tgt_lens.data_ptr(), loss.data_ptr(), grad.data_ptr() if grad is not None else None,
+                      scratch.data_ptr(), b, n, v, targets.shape[1], max_s, blank, scratch.numel(), _lib.stream_ptr()), "ctc_loss")
+        _lib.count_launch(3 if need_grad else 2)
+        if need_grad:
+            ctx.save_for_backward(grad, row_batch)
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
-        grad, cu, lens = ctx.saved_tensors
-        # per-row scale by the sequence's dloss
-        b = lens.shape[0]
-        row_seq = torch.repeat_interleave(torch.arange(b, device=grad.device), lens.to(torch.int64), output_size=grad.shape[0])
-        scale = dloss.to(torch.float32)[row_seq].unsqueeze(-1)
+        grad, row_batch = ctx.saved_tensors
+        scale = dloss.to(torch.float32)[row_batch.long()].unsqueeze(-1)
         return (grad.float() * scale).to(grad.dtype), None, None, None, None, None, None, None
 
 
@@ -77,7 +77,7 @@ def ctc_loss_packed(logits_rows: torch.Tensor, pack, targets: torch.Tensor, tgt_
     max_s = int(tgt_lens_host.max()) if tgt_lens_host.numel() else 0
     if logits_rows.is_cuda and _lib.use_native(logits_rows) and available() and supports(logits_rows, targets):
         tl = tgt_lens_host.to(torch.int32).to(logits_rows.device, non_blocking=True)
-        return _CtcFn.apply(logits_rows, pack.cu, pack.lens, targets, tl, blank_index, pack.max_len, max_s)
+        return _CtcFn.apply(logits_rows, pack.cu, pack.row_batch, pack.lens, targets, tl, blank_index, max_s)
     padded = pack.unpack(logits_rows)  # [B, T, V]
     log_probs = F.log_softmax(padded.float(), dim=-1).transpose(0, 1)
     return F.ctc_loss(log_probs, targets.long(), pack.lens_host.long(), tgt_lens_host.long().cpu(), blank=blank_index, reduction="none", zero_infinity=True)
