@@ -183,7 +183,8 @@ bn_silu_bwd_a_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
 }
 
 // partials -> sum_ds (= dbeta), sum_ds_yhat (= dgamma)
-__global__ void bn_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh) {
+__global__ void bn_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh,
+                                     float* __restrict__ dgamma_acc = nullptr, float* __restrict__ dbeta_acc = nullptr) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= C) return;
   double s1 = 0.0, s2 = 0.0;
@@ -193,6 +194,8 @@ __global__ void bn_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles
   }
   sum_ds[c] = (float)s1;
   sum_ds_yh[c] = (float)s2;
+  if (dgamma_acc) dgamma_acc[c] += (float)s2;
+  if (dbeta_acc) dbeta_acc[c] += (float)s1;
 }
 
 // dy = gamma * rstd * (ds - sum_ds/count - yhat * sum_ds_yh/count), in place over ds
@@ -296,14 +299,19 @@ glu_dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
 }
 
 __global__ void dwconv_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, int K, float* __restrict__ dfilt,
-                                         float* __restrict__ dbias) {
+                                         float* __restrict__ dbias, int accumulate = 0) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= C * (K + 1)) return;
   const int c = idx / (K + 1), k = idx % (K + 1);
   double s = 0.0;
   for (int t = 0; t < n_tiles; ++t) s += part[((size_t)t * C + c) * (K + 1) + k];
-  if (k < K) dfilt[(size_t)c * K + k] = (float)s;
-  else if (dbias) dbias[c] = (float)s;
+  if (accumulate) {
+    if (k < K) dfilt[(size_t)c * K + k] += (float)s;
+    else if (dbias) dbias[c] += (float)s;
+  } else {
+    if (k < K) dfilt[(size_t)c * K + k] = (float)s;
+    else if (dbias) dbias[c] = (float)s;
+  }
 }
 
 }  // namespace
@@ -337,9 +345,10 @@ RB_EXPORT int rb200_bn_silu_fwd(const void* y, const float* mean, const float* r
 }
 
 // ds (bf16 [N,C]) receives ds, later overwritten in place by dy. part: n_tiles*2*C floats.
-RB_EXPORT int rb200_bn_silu_bwd(const void* y, const void* dz, const float* mean, const float* rstd, const float* gamma, const float* beta,
-                                void* ds, float* part, int n_tiles, float* sum_ds, float* sum_ds_yh, long long n_rows, int C,
-                                int training, cudaStream_t stream) {
+// dgamma_acc / dbeta_acc (optional): the parameter gradients are also added there
+RB_EXPORT int rb200_bn_silu_bwd_ex(const void* y, const void* dz, const float* mean, const float* rstd, const float* gamma, const float* beta,
+                                   void* ds, float* part, int n_tiles, float* sum_ds, float* sum_ds_yh, long long n_rows, int C,
+                                   int training, float* dgamma_acc, float* dbeta_acc, cudaStream_t stream) {
   if (n_rows <= 0) return RB_OK;
   const int groups = C / 8;
   if (C % 8 || groups > 256 || 256 % groups) {
@@ -353,7 +362,7 @@ RB_EXPORT int rb200_bn_silu_bwd(const void* y, const void* dz, const float* mean
                                                        (__nv_bfloat16*)ds, part, (int)n_rows, C, rows_per_cta);
   int st = rb_check_launch("bn_silu_bwd_a");
   if (st) return st;
-  bn_bwd_reduce_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh);
+  bn_bwd_reduce_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh, dgamma_acc, dbeta_acc);
   st = rb_check_launch("bn_bwd_reduce");
   if (st) return st;
   if (training) {
@@ -365,9 +374,16 @@ RB_EXPORT int rb200_bn_silu_bwd(const void* y, const void* dz, const float* mean
   return st;
 }
 
-RB_EXPORT int rb200_glu_dwconv_bwd(const void* x, const void* dy, const float* filt, const int* row_batch, const int* row_pos,
-                                   const int* lens, void* dx, float* part, float* dfilt, float* dbias, int n_rows, int C, int K,
-                                   cudaStream_t stream) {
+RB_EXPORT int rb200_bn_silu_bwd(const void* y, const void* dz, const float* mean, const float* rstd, const float* gamma, const float* beta,
+                                void* ds, float* part, int n_tiles, float* sum_ds, float* sum_ds_yh, long long n_rows, int C,
+                                int training, cudaStream_t stream) {
+  return rb200_bn_silu_bwd_ex(y, dz, mean, rstd, gamma, beta, ds, part, n_tiles, sum_ds, sum_ds_yh, n_rows, C, training, nullptr, nullptr, stream);
+}
+
+// accumulate: dfilt / dbias += instead of =
+RB_EXPORT int rb200_glu_dwconv_bwd_ex(const void* x, const void* dy, const float* filt, const int* row_batch, const int* row_pos,
+                                      const int* lens, void* dx, float* part, float* dfilt, float* dbias, int n_rows, int C, int K,
+                                      int accumulate, cudaStream_t stream) {
   if (n_rows <= 0) return RB_OK;
   if (C % CC || K > KMAX || K < 1) return RB_ERR_ARG;
   const int n_tiles = (n_rows + TT - 1) / TT;
@@ -376,6 +392,12 @@ RB_EXPORT int rb200_glu_dwconv_bwd(const void* x, const void* dy, const float* f
                                                        (__nv_bfloat16*)dx, part, n_rows, C, K);
   int st = rb_check_launch("glu_dwconv_bwd");
   if (st) return st;
-  dwconv_bwd_reduce_kernel<<<(C * (K + 1) + 255) / 256, 256, 0, stream>>>(part, n_tiles, C, K, dfilt, dbias);
+  dwconv_bwd_reduce_kernel<<<(C * (K + 1) + 255) / 256, 256, 0, stream>>>(part, n_tiles, C, K, dfilt, dbias, accumulate);
   return rb_check_launch("dwconv_bwd_reduce");
+}
+
+RB_EXPORT int rb200_glu_dwconv_bwd(const void* x, const void* dy, const float* filt, const int* row_batch, const int* row_pos,
+                                   const int* lens, void* dx, float* part, float* dfilt, float* dbias, int n_rows, int C, int K,
+                                   cudaStream_t stream) {
+  return rb200_glu_dwconv_bwd_ex(x, dy, filt, row_batch, row_pos, lens, dx, part, dfilt, dbias, n_rows, C, K, 0, stream);
 }

@@ -119,7 +119,8 @@ template <int CHUNKS>
 __global__ void __launch_bounds__(kWarpsPerCta * 32)
 ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const void* __restrict__ gamma,
               const float* __restrict__ mean_in, const float* __restrict__ rstd_in, void* __restrict__ dx,
-              float* __restrict__ part, int64_t rows, int n, int n_part, int x_bf16, int w_bf16, int rms) {
+              float* __restrict__ part, int64_t rows, int n, int n_part, int x_bf16, int w_bf16, int rms,
+              const void* __restrict__ dres = nullptr) {
   extern __shared__ float smem[];  // [kWarpsPerCta][2][n]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -166,6 +167,12 @@ ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const voi
         F8 o;
 #pragma unroll
         for (int i = 0; i < 8; ++i) o.v[i] = rstd * (g[c].v[i] * d[c].v[i] - s1 - xh[c].v[i] * s2);
+        if (dres) {
+          // gradient that reaches x along the residual branch
+          F8 rr = load8(dres, base + col, x_bf16);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) o.v[i] += rr.v[i];
+        }
         store8(dx, base + col, o, x_bf16);
       }
     }
@@ -196,7 +203,7 @@ ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const voi
 }
 
 __global__ void ln_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamma, float* __restrict__ dbeta,
-                                     int n, int n_part) {
+                                     int n, int n_part, int accumulate = 0) {
   int col = blockIdx.x * blockDim.x + threadIdx.x;
   if (col >= n) return;
   float sg = 0.f, sb = 0.f;
@@ -204,8 +211,13 @@ __global__ void ln_bwd_reduce_kernel(const float* __restrict__ part, float* __re
     sg += part[((int64_t)0 * n_part + p) * n + col];
     sb += part[((int64_t)1 * n_part + p) * n + col];
   }
-  dgamma[col] = sg;
-  dbeta[col] = sb;
+  if (accumulate) {
+    if (dgamma) dgamma[col] += sg;
+    if (dbeta) dbeta[col] += sb;
+  } else {
+    if (dgamma) dgamma[col] = sg;
+    if (dbeta) dbeta[col] = sb;
+  }
 }
 
 }  // namespace
@@ -229,9 +241,10 @@ RB_EXPORT int rb200_layer_norm_fwd(const void* x, const void* gamma, const void*
   return rb_check_launch("layer_norm_fwd");
 }
 
-RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
-                                   void* dx, float* part, float* dgamma, float* dbeta, long long rows, int n, int n_part,
-                                   int x_bf16, int w_bf16, int rms, cudaStream_t stream) {
+// dres (optional, same layout as dx): added to dx; accumulate: dgamma / dbeta += instead of =
+RB_EXPORT int rb200_layer_norm_bwd_ex(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                                      void* dx, float* part, float* dgamma, float* dbeta, long long rows, int n, int n_part,
+                                      int x_bf16, int w_bf16, int rms, const void* dres, int accumulate, cudaStream_t stream) {
   if (n % 8 != 0 || n <= 0 || n > kMaxChunks * 256) {
     rb_set_error("layer_norm_bwd: n=%d must be a multiple of 8 and <= %d", n, kMaxChunks * 256);
     return RB_ERR_ARG;
@@ -243,7 +256,7 @@ RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* ga
 #define LN_BWD(C)                                                                                          \
   do {                                                                                                     \
     if (smem > 48 * 1024) cudaFuncSetAttribute(ln_bwd_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    ln_bwd_kernel<C><<<grid, block, smem, stream>>>(x, dy, gamma, mean, rstd, dx, part, rows, n, n_part, x_bf16, w_bf16, rms); \
+    ln_bwd_kernel<C><<<grid, block, smem, stream>>>(x, dy, gamma, mean, rstd, dx, part, rows, n, n_part, x_bf16, w_bf16, rms, dres); \
   } while (0)
   if (chunks <= 1) LN_BWD(1);
   else if (chunks <= 2) LN_BWD(2);
@@ -252,8 +265,14 @@ RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* ga
 #undef LN_BWD
   int st = rb_check_launch("layer_norm_bwd");
   if (st) return st;
-  ln_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, dgamma, dbeta, n, n_part);
+  ln_bwd_reduce_kernel<<<(n + 255) / 256, 256, 0, stream>>>(part, dgamma, dbeta, n, n_part, accumulate);
   return rb_check_launch("layer_norm_bwd_reduce");
+}
+
+RB_EXPORT int rb200_layer_norm_bwd(const void* x, const void* dy, const void* gamma, const float* mean, const float* rstd,
+                                   void* dx, float* part, float* dgamma, float* dbeta, long long rows, int n, int n_part,
+                                   int x_bf16, int w_bf16, int rms, cudaStream_t stream) {
+  return rb200_layer_norm_bwd_ex(x, dy, gamma, mean, rstd, dx, part, dgamma, dbeta, rows, n, n_part, x_bf16, w_bf16, rms, nullptr, 0, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------

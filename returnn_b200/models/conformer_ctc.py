@@ -74,10 +74,13 @@ class ConformerCtcModel(rf.Module):
         """fused path: packed logits [N, V+1] in bf16"""
         from ..ops import linear as _lin
 
+        from ..parallel import arena as _arena
+
         rows, pack = conformer_fused.encode_packed(self.encoder, feats, lens_host, training=training)
         w = self.logits.weight.raw_tensor
         b = self.logits.bias.raw_tensor
-        logits = _lin.linear(rows, w.to(rows.dtype), b.to(rows.dtype))
+        ar = _arena.find_arena(w) if (training and torch.is_grad_enabled()) else None
+        logits = conformer_fused.arena_linear(rows, w, b, None, ar, conformer_fused._Weights(rows.dtype))
         return logits, pack
 
 

@@ -145,6 +145,23 @@ def pos_projection(enc, max_len: int, device, dtype, W) -> Optional[torch.Tensor
     return torch.cat([torch.sin(arg), torch.sin(arg + math.pi / 2.0)], dim=-1).to(dtype)
 
 
+def arena_linear(x, weight, bias, act, arena, W):
+    """linear layer through the arena path (bf16 weight copy, gradients accumulated in place) when possible"""
+    from ..ops import gemm as _gemm
+
+    if arena is not None:
+        y = _gemm.linear_arena(x, weight, bias, act, arena)
+        if y is not None:
+            return y
+    return _lin.linear(x, W(weight), W(bias) if bias is not None else None, act)
+
+
+def _att_supports(plan, pack: PackInfo) -> bool:
+    from ..ops import attention_native as _an
+
+    return _an.supports_packed(plan.H, plan.Dh, pack.max_len) and plan.D % 64 == 0 and plan.H * plan.Dh == plan.D and 1 <= plan.conv_k <= 64
+
+
 def supports_fused(enc) -> bool:
     """whether the encoder is in the standard configuration that the fused path implements"""
     from ..frontend.encoder.conformer import ConformerEncoderLayer, ConformerConvSubsample, ConformerPositionwiseFeedForward
@@ -181,15 +198,24 @@ def encode_packed(enc, feats: torch.Tensor, lens_host: torch.Tensor, *, training
     :param lens_host: int32 [B] on the host
     :return: rows [N, D] in compute_dtype, their PackInfo
     """
+    from . import conformer_native as _native
+
     W = _Weights(compute_dtype)
     x_pad, lens2 = frontend_subsample(enc, feats.to(compute_dtype), lens_host, W)
     pack = PackInfo(lens2, feats.device, padded_len=x_pad.shape[1])
     x = pack.pack(x_pad)
-    x = _lin.linear(x, W(enc.input_projection.weight), None)
+    plan = None
+    if training and torch.is_grad_enabled() and compute_dtype == torch.bfloat16 and collected is None and x.is_cuda:
+        plan = _native.get_plan(enc)
+    x = arena_linear(x, enc.input_projection.weight.raw_tensor, None, None, plan.arena if plan is not None else None, W)
     if enc.input_embedding_scale != 1.0:
         x = x * enc.input_embedding_scale
     x = _dropout(x, enc.input_dropout, training)
     sinus = pos_projection(enc, pack.max_len, feats.device, compute_dtype, W)
+    if plan is not None and _att_supports(plan, pack):
+        # the whole layer stack as one native call per pass
+        x = _native.encoder_stack(x, sinus, plan, pack)
+        return x, pack
     for name, layer in enc.layers._get_modules().items():
         eps = layer.ffn1_layer_norm.eps
         p = layer.dropout

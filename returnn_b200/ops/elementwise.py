@@ -58,3 +58,19 @@ class _DropoutFn(torch.autograd.Function):
 def dropout(x: torch.Tensor, p: float) -> torch.Tensor:
     """bf16 dropout, scale 1/(1-p)"""
     return _DropoutFn.apply(x, float(p))
+
+
+def dropout_with_state(x: torch.Tensor, p: float, seed: torch.Tensor, offset: torch.Tensor) -> torch.Tensor:
+    """
+    dropout with an explicit RNG state: int64 device tensors ``seed`` (key) and ``offset`` (counter of element 0).
+    Element ``i`` of the flattened input uses counter ``offset + i``, which is also what the fused GEMM epilogue and the
+    native encoder kernels use, so a mask can be re-created by any of them.
+    """
+    x = x.contiguous()
+    y = torch.empty_like(x)
+    seed = seed.contiguous()
+    offset = offset.contiguous()
+    fn = _lib.bind("rb200_dropout_bf16", [_vp, _vp, _i64, _f32, _vp, _vp, _vp])
+    _lib.check(fn(x.data_ptr(), y.data_ptr(), x.numel(), float(p), seed.data_ptr(), offset.data_ptr(), _lib.stream_ptr()), "dropout")
+    _lib.count_launch()
+    return y

@@ -50,16 +50,28 @@ def check_status(device=None):
             raise RuntimeError("tcgen05 GEMM reported a bounded-wait timeout: role %i, k-block %i" % (v >> 24, v & 0xFFFFFF))
 
 
+KERNEL = os.environ.get("RETURNN_B200_GEMM_KERNEL", "persistent")  # "persistent" | "legacy" (one tile per CTA, plain epilogue)
+_u64 = ctypes.c_ulonglong
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, m: int, n: int, k: int, a_mn_major: bool, b_mn_major: bool,
          bias: Optional[torch.Tensor] = None, act: Optional[str] = None, out: Optional[torch.Tensor] = None,
          out_dtype: torch.dtype = torch.bfloat16, accumulate: bool = False, alpha: float = 1.0,
-         out_act: Optional[torch.Tensor] = None, want_act_output: bool = False):
+         out_act: Optional[torch.Tensor] = None, want_act_output: bool = False,
+         dact_z: Optional[torch.Tensor] = None, dropout_p: float = 0.0, dropout_seed: Optional[torch.Tensor] = None,
+         dropout_offset: Optional[torch.Tensor] = None, dropout_site: int = 0,
+         resid: Optional[torch.Tensor] = None, res_scale: float = 1.0, atomic: bool = False, split_k: int = 0):
     """
-    ``D[m,n] = alpha * A·B (+ bias) (act)``.
+    ``D[m,n] = epilogue(alpha * A·B)``; epilogue order: ``+ bias``, ``* act'(dact_z)`` or ``act``, dropout, ``resid + res_scale *``.
 
     :param a: bf16 2-D, stored ``[m, k]`` (``a_mn_major=False``) or ``[k, m]`` (True); last dim contiguous
     :param b: bf16 2-D, stored ``[n, k]`` (``b_mn_major=False``) or ``[k, n]`` (True)
-    :param want_act_output: return ``(pre_activation, activated)`` instead of only the activated result
+    :param want_act_output: return ``(pre_activation, final)`` instead of only the final result
+    :param dact_z: bf16 ``[m, n]`` (same pitch as out): multiply by the derivative of ``act`` at ``dact_z`` (nothing is activated then)
+    :param dropout_p: drop the (activated) value with a counter-based mask: element ``(r, c)`` uses counter
+        ``dropout_offset[0] + dropout_site + r*pitch + c`` under key ``dropout_seed[0]`` (int64 device tensors)
+    :param resid: bf16 ``[m, n]``: ``resid + res_scale * value``
+    :param atomic: fp32 out only: add into ``out`` with atomics; the contraction may then be split over CTAs (``split_k``, 0 = auto)
     """
     assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
     assert a.stride(1) == 1 and b.stride(1) == 1
@@ -69,16 +81,34 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, m: int, n: int, k: int, a_mn_major
     if b.shape[0] == 1:
         ldb = b.shape[1]
     if out is None:
+        assert not atomic
         out = torch.empty(m, n, dtype=out_dtype, device=a.device)
     c2 = None
     if want_act_output:
         c2 = out_act if out_act is not None else torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
-    fn = _lib.bind("rb200_gemm_bf16", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp])
     st = status_tensor(a.device)
-    _lib.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), c2.data_ptr() if c2 is not None else None,
-                  bias.data_ptr() if bias is not None else None, m, n, k, lda, ldb, out.stride(0), 1 if a_mn_major else 0,
-                  1 if b_mn_major else 0, 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0, _ACT[act],
-                  1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, float(alpha), st.data_ptr(), _lib.stream_ptr()), "gemm_bf16")
+    extended = dact_z is not None or dropout_p > 0.0 or resid is not None or atomic
+    bias_bf16 = 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0
+    if KERNEL == "legacy" and not extended:
+        fn = _lib.bind("rb200_gemm_bf16", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp])
+        _lib.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), c2.data_ptr() if c2 is not None else None,
+                      bias.data_ptr() if bias is not None else None, m, n, k, lda, ldb, out.stride(0), 1 if a_mn_major else 0,
+                      1 if b_mn_major else 0, bias_bf16, _ACT[act],
+                      1 if out.dtype == torch.float32 else 0, 1 if accumulate else 0, float(alpha), st.data_ptr(), _lib.stream_ptr()), "gemm_bf16")
+    else:
+        for t in (dact_z, resid):
+            assert t is None or (t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.stride(0) == out.stride(0))
+        fn = _lib.bind("rb200_gemm_bf16_ex", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
+                                              _vp, _f32, _vp, _vp, _u64, _vp, _f32, _i32, _vp, _vp])
+        _lib.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), c2.data_ptr() if c2 is not None else None,
+                      bias.data_ptr() if bias is not None else None, m, n, k, lda, ldb, out.stride(0), 1 if a_mn_major else 0,
+                      1 if b_mn_major else 0, bias_bf16, _ACT[act], 1 if out.dtype == torch.float32 else 0,
+                      2 if atomic else (1 if accumulate else 0), float(alpha),
+                      dact_z.data_ptr() if dact_z is not None else None, float(dropout_p),
+                      dropout_seed.data_ptr() if dropout_seed is not None else None,
+                      dropout_offset.data_ptr() if dropout_offset is not None else None, int(dropout_site),
+                      resid.data_ptr() if resid is not None else None, float(res_scale), int(split_k), st.data_ptr(), _lib.stream_ptr()),
+                   "gemm_bf16_ex")
     _lib.count_launch()
     if want_act_output:
         return out, c2
@@ -137,6 +167,82 @@ class _LinearFn(torch.autograd.Function):
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = dy.float().sum(dim=0).to(ctx.bias_dtype)
         return dx, dw, db, None
+
+
+class _ArenaLinearFn(torch.autograd.Function):
+    """
+    Linear layer whose weight lives in a parameter arena: the forward reads the bf16 copy of the weight, the backward adds the
+    weight / bias gradients straight into the fp32 gradient arena (split-K GEMM with atomics, column-sum kernel) and returns
+    only the input gradient, so no gradient tensors are created and nothing is cast.
+    """
+
+    @staticmethod
+    def forward(ctx, x2, w16, bias32, gw32, gb32, act):
+        m, k = x2.shape
+        n = w16.shape[1]
+        if act is not None:
+            z, y = gemm(x2, w16, m=m, n=n, k=k, a_mn_major=False, b_mn_major=True, bias=bias32, act=act, want_act_output=True)
+        else:
+            z, y = None, gemm(x2, w16, m=m, n=n, k=k, a_mn_major=False, b_mn_major=True, bias=bias32)
+        ctx.save_for_backward(x2, w16, z)
+        ctx.act, ctx.gw32, ctx.gb32 = act, gw32, gb32
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w16, z = ctx.saved_tensors
+        m, k = x2.shape
+        n = w16.shape[1]
+        dy = dy.contiguous()
+        if ctx.act is not None:
+            dy = _act_grad(z, dy, ctx.act)
+        dx = gemm(dy, w16, m=m, n=k, k=n, a_mn_major=False, b_mn_major=False) if ctx.needs_input_grad[0] else None
+        if ctx.gw32 is not None:
+            gemm(x2, dy, m=k, n=n, k=m, a_mn_major=True, b_mn_major=True, out=ctx.gw32, atomic=True)
+        if ctx.gb32 is not None:
+            fn = _lib.bind("rb200_colsum_bf16", [_vp, _vp, _i32, _i32, _vp])
+            _lib.check(fn(dy.data_ptr(), ctx.gb32.data_ptr(), m, n, _lib.stream_ptr()), "colsum")
+            _lib.count_launch()
+        return dx, None, None, None, None, None
+
+
+def linear_arena(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation: Optional[str], arena) -> Optional[torch.Tensor]:
+    """
+    ``x @ weight (+ bias)`` for fp32 parameters that live in ``arena`` (a :class:`returnn_b200.parallel.arena.ParamArena`
+    with fp32 gradients); returns None when this path does not apply (caller falls back to :func:`linear_bf16`).
+    The parameter gradients do not pass through autograd: they are accumulated into ``arena.flat_grad``.
+    """
+    if arena is None or not x.requires_grad or weight.dtype != torch.float32 or arena.grad_dtype != torch.float32 or weight.dim() != 2:
+        return None
+    if not available(x) or not weight.is_contiguous() or weight.shape[0] % 8 or weight.shape[1] % 8:
+        return None
+
+    def _views(p):
+        off = (p.data_ptr() - arena.flat_param.data_ptr()) // 4
+        if not (0 <= off < arena.total):
+            return None, None
+        sh = arena.shadow_bf16()[off: off + p.numel()].view(p.shape)
+        g = arena.flat_grad[off: off + p.numel()].view(p.shape) if p.requires_grad else None
+        return sh, g
+
+    w16, gw = _views(weight)
+    if w16 is None:
+        return None
+    gb = None
+    if bias is not None:
+        if bias.dtype != torch.float32:
+            return None
+        _, gb = _views(bias)
+        if gb is None and bias.requires_grad:
+            return None
+    arena.sync_shadow()
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _ArenaLinearFn.apply(x2, w16, bias, gw, gb, activation)
+    return y.reshape(*x.shape[:-1], w16.shape[1])
 
 
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation: Optional[str]) -> torch.Tensor:

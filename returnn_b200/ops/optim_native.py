@@ -33,12 +33,17 @@ def sum_squares(x: torch.Tensor, scratch: torch.Tensor) -> torch.Tensor:
     return out[0]
 
 
-def adamw_arena(p, g, m, v, wd_flags, *, lr, b1, b2, eps, wd, bc1, bc2, decoupled, clip, norm: Optional[torch.Tensor]):
-    """in-place fused AdamW; clip > 0 with norm given: gradients scaled by min(1, clip/(norm+1e-6)) on the fly"""
+def adamw_arena(p, g, m, v, wd_flags, *, lr, b1, b2, eps, wd, bc1, bc2, decoupled, clip, norm: Optional[torch.Tensor],
+                p_bf16: Optional[torch.Tensor] = None):
+    """
+    in-place fused AdamW; clip > 0 with norm given: gradients scaled by min(1, clip/(norm+1e-6)) on the fly;
+    ``p_bf16`` (same numel): also receives the updated weights rounded to bf16
+    """
     fn = _lib.bind("rb200_adamw_arena", [_vp, _vp, _vp, _vp, _vp, _i64, _i32, _f32, _f32, _f32, _f32, _f32, _f32, _f32, _i32, _f32, _vp, _vp, _vp])
     _lib.check(fn(p.data_ptr(), g.data_ptr(), m.data_ptr(), v.data_ptr(), wd_flags.data_ptr(), p.numel(),
                   {torch.float32: 0, torch.bfloat16: 1}[g.dtype], lr, b1, b2, eps, wd, bc1, bc2, 1 if decoupled else 0, clip,
-                  norm.data_ptr() if norm is not None else None, None, _lib.stream_ptr()), "adamw_arena")
+                  norm.data_ptr() if norm is not None else None, p_bf16.data_ptr() if p_bf16 is not None else None,
+                  _lib.stream_ptr()), "adamw_arena")
     _lib.count_launch()
 
 

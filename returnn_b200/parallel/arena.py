@@ -11,7 +11,24 @@ from __future__ import annotations
 from typing import Dict, Iterable, List, Optional, Sequence, Tuple
 import torch
 
+import weakref
+
 _ALIGN = 128  # elements; keeps every tensor 512-byte aligned in fp32 (vector loads, TMA-able slices)
+_arenas: "List[weakref.ref]" = []
+
+
+def find_arena(t: torch.Tensor) -> "Optional[ParamArena]":
+    """the live arena whose parameter buffer contains tensor ``t`` (None if there is none)"""
+    addr = t.data_ptr()
+    for ref in list(_arenas):
+        a = ref()
+        if a is None:
+            _arenas.remove(ref)
+            continue
+        lo = a.flat_param.data_ptr()
+        if a.flat_param.device == t.device and lo <= addr < lo + a.flat_param.numel() * a.flat_param.element_size():
+            return a
+    return None
 
 
 class ArenaSlot:
@@ -84,6 +101,37 @@ class ParamArena:
                 if lo <= s.offset < hi:
                     s.bucket = b
         self.bucket_num_params = [sum(1 for s in self.slots if s.bucket == b) for b in range(len(self.buckets))]
+        self._shadow: Optional[torch.Tensor] = None
+        self._shadow_version = -1
+        _arenas.append(weakref.ref(self))
+
+    def shadow_bf16(self) -> torch.Tensor:
+        """bf16 copy of ``flat_param`` (same element offsets): what the tensor-core GEMMs read. Allocated on first use."""
+        if self._shadow is None:
+            self._shadow = torch.empty(self.total, dtype=torch.bfloat16, device=self.device)
+            self._shadow_version = -1
+        return self._shadow
+
+    def sync_shadow(self):
+        """
+        Bring the bf16 copy up to date if the fp32 weights changed through torch since the last sync (checkpoint load,
+        initialisation, parameter averaging). An optimizer kernel that writes both copies itself calls
+        :func:`mark_shadow_synced` instead, so the steady state costs nothing here.
+        """
+        sh = self.shadow_bf16()
+        v = self.flat_param._version
+        if v != self._shadow_version:
+            with torch.no_grad():
+                sh.copy_(self.flat_param)
+            self._shadow_version = self.flat_param._version
+
+    def mark_shadow_synced(self):
+        """the caller has just written fp32 weights and bf16 copy together"""
+        self._shadow_version = self.flat_param._version
+
+    def has_shadow(self) -> bool:
+        """whether a bf16 copy is being maintained"""
+        return self._shadow is not None
 
     def zero_grad(self):
         """one memset for all gradients"""

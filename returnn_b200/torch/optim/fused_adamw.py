@@ -99,7 +99,10 @@ class FusedArenaAdamW(torch.optim.Optimizer):
 
             if optim_native.available():
                 optim_native.adamw_arena(p, g, m, v, self.wd_flags, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, bc1=bc1, bc2=bc2,
-                                         decoupled=self.decoupled, clip=self._clip if self._norm is not None else 0.0, norm=self._norm)
+                                         decoupled=self.decoupled, clip=self._clip if self._norm is not None else 0.0, norm=self._norm,
+                                         p_bf16=self.arena.shadow_bf16() if self.arena.has_shadow() else None)
+                if self.arena.has_shadow():
+                    self.arena.mark_shadow_synced()
                 self._norm = None
                 return loss
         gg = g.float()

@@ -71,3 +71,59 @@ def test_linear_autograd_matches_fp32():
     torch.testing.assert_close(x.grad.float(), xr.grad, atol=0.05, rtol=3e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.4, rtol=3e-2)
     torch.testing.assert_close(b.grad.float(), br.grad, atol=0.5, rtol=3e-2)
+
+
+@gpu
+@pytest.mark.parametrize("m,n,k", [(300, 264, 136), (1000, 512, 2048), (77, 72, 64)])
+def test_gemm_fused_epilogue_resid_dropout(m, n, k):
+    """out = resid + 0.5 * dropout(a·b + bias), mask identical to the stand-alone dropout kernel at the same offset"""
+    from returnn_b200.ops import gemm, elementwise
+
+    a, b = _mk(m, k, 5), _mk(k, n, 6)
+    bias = torch.randn(n, device="cuda")
+    resid = _mk(m, n, 7)
+    seed = torch.tensor([1234, 4096], dtype=torch.int64, device="cuda")
+    off = seed[1:2].clone()
+    site = 8 * 1000
+    out = gemm.gemm(a, b, m=m, n=n, k=k, a_mn_major=False, b_mn_major=True, bias=bias, dropout_p=0.25, dropout_seed=seed[0:1],
+                    dropout_offset=off, dropout_site=site, resid=resid, res_scale=0.5)
+    gemm.check_status()
+    y = (a.float() @ b.float() + bias)
+    # the mask of the stand-alone kernel with the same key and counter base
+    ones = torch.ones(m, n, device="cuda", dtype=torch.bfloat16)
+    mask = elementwise.dropout_with_state(ones, 0.25, seed[0:1], off + site).float()
+    ref = resid.float() + 0.5 * y * mask
+    torch.testing.assert_close(out.float(), ref, atol=0.1, rtol=2e-2)
+    assert 0.6 < float((mask > 0).float().mean()) < 0.9
+
+
+@gpu
+@pytest.mark.parametrize("act", ["relu", "silu", "gelu"])
+def test_gemm_fused_act_grad(act):
+    from returnn_b200.ops import gemm
+
+    m, n, k = 520, 2048, 512
+    dy, w = _mk(m, k, 8), _mk(n, k, 9)  # dA[m,n] = dY[m,k] · W[n,k]^T
+    z = _mk(m, n, 10)
+    out = gemm.gemm(dy, w, m=m, n=n, k=k, a_mn_major=False, b_mn_major=False, act=act, dact_z=z)
+    gemm.check_status()
+    zz = z.float().requires_grad_(True)
+    fn = {"relu": torch.relu, "silu": torch.nn.functional.silu, "gelu": torch.nn.functional.gelu}[act]
+    da = dy.float() @ w.float().t()
+    (g,) = torch.autograd.grad(fn(zz), zz, da)
+    torch.testing.assert_close(out.float(), g, atol=0.15, rtol=3e-2)
+
+
+@gpu
+@pytest.mark.parametrize("m,n,k", [(512, 2048, 6700), (512, 512, 6656), (136, 72, 1000), (512, 10240, 3000)])
+def test_gemm_split_k_atomic(m, n, k):
+    """weight-gradient form dW += X^T·dY with the contraction split over CTAs"""
+    from returnn_b200.ops import gemm
+
+    x, dy = _mk(k, m, 11), _mk(k, n, 12)
+    acc = torch.full((m, n), 2.0, device="cuda")
+    gemm.gemm(x, dy, m=m, n=n, k=k, a_mn_major=True, b_mn_major=True, out=acc, atomic=True)
+    gemm.gemm(x, dy, m=m, n=n, k=k, a_mn_major=True, b_mn_major=True, out=acc, atomic=True, split_k=3)
+    gemm.check_status()
+    ref = 2.0 + 2.0 * (x.float().t() @ dy.float())
+    torch.testing.assert_close(acc, ref, atol=0.05 * k ** 0.5, rtol=2e-2)

@@ -1,0 +1,99 @@
+"""
+Native Conformer encoder executor (one call per pass) against the per-op path on the same weights: outputs, input
+gradient and all parameter gradients, without dropout; with dropout: reproducible for a fixed RNG state and finite.
+"""
+
+import pytest
+import torch
+
+gpu = pytest.mark.gpu
+
+
+def _make(num_layers=2, model_dim=128, heads=2, ff=256, conv_k=7, dropout=0.0):
+    from returnn_b200.tensor import Dim
+    from returnn_b200.models.conformer_ctc import ConformerCtcModel
+    from returnn_b200.torch.frontend.bridge import rf_module_to_pt_module
+    from returnn_b200.parallel.arena import ParamArena
+    from returnn_b200.utils.basic import BehaviorVersion
+
+    BehaviorVersion.set_min_behavior_version(21)
+    torch.manual_seed(1)
+    model = ConformerCtcModel(in_dim=Dim(80, name="feat"), vocab_dim=Dim(55, name="vocab"), num_layers=num_layers, model_dim=model_dim,
+                              num_heads=heads, ff_dim=ff, conv_kernel_size=conv_k, dropout=dropout, att_dropout=dropout,
+                              conv_channels=(8, 16, 16))
+    pt = rf_module_to_pt_module(model).to("cuda")
+    with torch.no_grad():
+        for n, p in pt.named_parameters():
+            if p.dim() == 1 and ("bias" in n or "beta" in n):
+                p.normal_(0.0, 0.1)  # biases are zero-initialised: give them values so that their paths are exercised
+    arena = ParamArena(list(pt.named_parameters()))
+    return model, pt, arena
+
+
+def _run(model, arena, feats, lens, wgt, native: bool):
+    from returnn_b200.models import conformer_fused, conformer_native
+    from returnn_b200.ops.elementwise import _seed_tensor
+
+    conformer_native.ENABLED = native
+    seed = _seed_tensor(feats.device)
+    seed[0] = 777
+    seed[1] = 0
+    arena.zero_grad()
+    f = feats.clone().requires_grad_(True)
+    out, pack = conformer_fused.encode_packed(model.encoder, f, lens, training=True)
+    loss = (out.float() * wgt[: out.shape[0]]).sum()
+    loss.backward()
+    arena.relink_grads()
+    conformer_native.ENABLED = True
+    return out.detach().float(), f.grad.detach().float(), arena.flat_grad.clone()
+
+
+@gpu
+def test_native_encoder_matches_per_op_path():
+    from returnn_b200.models import conformer_fused, conformer_native
+
+    model, pt, arena = _make()
+    assert conformer_fused.supports_fused(model.encoder)
+    assert conformer_native.get_plan(model.encoder) is not None
+    torch.manual_seed(2)
+    lens = torch.tensor([600, 431, 577, 90], dtype=torch.int32)
+    feats = torch.randn(4, 600, 80, device="cuda")
+    wgt = torch.randn(600, 128, device="cuda")
+    o1, gx1, gp1 = _run(model, arena, feats, lens, wgt, native=True)
+    o2, gx2, gp2 = _run(model, arena, feats, lens, wgt, native=False)
+    assert torch.isfinite(o1).all() and torch.isfinite(gp1).all()
+    torch.testing.assert_close(o1, o2, atol=0.08, rtol=0.05)
+    # gradients: compare per parameter relative to the parameter's gradient scale (bf16 paths differ in rounding order)
+    bad = []
+    for s in arena.slots:
+        if s.name.endswith("depthwise_conv.bias"):
+            continue  # a bias in front of BatchNorm has an exactly zero gradient: both paths only produce rounding noise
+        a, b = gp1[s.offset: s.offset + s.numel], gp2[s.offset: s.offset + s.numel]
+        scale = float(b.abs().max()) + 1e-6
+        err = float((a - b).abs().max()) / scale
+        if err >= 0.08:
+            bad.append("%s: rel. max err %.4f (scale %.3g)" % (s.name, err, scale))
+    assert not bad, "parameter gradients differ:\n" + "\n".join(bad)
+    scale = float(gx2.abs().max()) + 1e-6
+    assert float((gx1 - gx2).abs().max()) / scale < 0.08
+
+
+@gpu
+def test_native_encoder_dropout_reproducible():
+    from returnn_b200.models import conformer_native
+
+    model, pt, arena = _make(dropout=0.1)
+    assert conformer_native.get_plan(model.encoder) is not None
+    torch.manual_seed(3)
+    lens = torch.tensor([300, 256], dtype=torch.int32)
+    feats = torch.randn(2, 300, 80, device="cuda")
+    wgt = torch.randn(300, 128, device="cuda")
+    o1, gx1, gp1 = _run(model, arena, feats, lens, wgt, native=True)
+    o2, gx2, gp2 = _run(model, arena, feats, lens, wgt, native=True)
+    assert torch.isfinite(o1).all() and torch.isfinite(gp1).all() and torch.isfinite(gx1).all()
+    torch.testing.assert_close(o1, o2, atol=0.0, rtol=0.0)
+    # atomics make the weight gradients order-dependent in the last bits only
+    torch.testing.assert_close(gp1, gp2, atol=1e-2, rtol=1e-2)
+    from returnn_b200.ops import gemm
+
+    gemm.check_status()
