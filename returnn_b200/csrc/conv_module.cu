@@ -216,68 +216,95 @@ bn_silu_bwd_b_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restr
   store8(ds, i8, dv, 1);
 }
 
-// depthwise conv backward + GLU backward. part layout: [n_tiles][C][K+1] (K filter taps, then the bias)
+// depthwise conv backward + GLU backward. Each CTA owns CC channels and walks over row tiles (tile = blockIdx.x, += gridDim.x),
+// keeping its dfilter / dbias sums in registers; one partial per CTA at the end: part layout [gridDim.x][C][K+1].
+template <int KM>
 __global__ void __launch_bounds__(kThreads)
 glu_dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ filt,
                       const int* __restrict__ row_batch, const int* __restrict__ row_pos, const int* __restrict__ lens,
                       __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int n_rows, int C, int K) {
-  __shared__ float sh_dy[(TT + KMAX - 1) * CC];   // dy rows r0-(K-1-left) .. : used for dh
-  __shared__ float sh_h[(TT + KMAX - 1) * CC];    // h rows r0-left .. : used for dfilter
+  __shared__ float sh_dy[(TT + KM - 1) * CC];   // dy rows r0-(K-1-left) .. : used for dh
+  __shared__ float sh_h[(TT + KM - 1) * CC];    // h rows r0-left .. : used for dfilter
+  __shared__ int sh_t[TT], sh_len[TT];
   const int left = (K - 1) / 2;
   const int right = K - 1 - left;
-  const int r0 = blockIdx.x * TT;
   const int c0 = blockIdx.y * CC;
   const int n_in = TT + K - 1;
-  for (int idx = threadIdx.x; idx < n_in * CC; idx += kThreads) {
-    const int s = idx / CC, c = idx % CC;
-    // dh[r] = sum_k f[k] * dy[r - k + left]  ->  needs dy rows r0 - right .. r0 + TT - 1 + left
-    const int rd = r0 - right + s;
-    sh_dy[s * CC + c] = (rd >= 0 && rd < n_rows) ? __bfloat162float(dy[(size_t)rd * C + c0 + c]) : 0.f;
-    const int rh = r0 - left + s;
-    float h = 0.f;
-    if (rh >= 0 && rh < n_rows) {
-      const float a = __bfloat162float(x[(size_t)rh * 2 * C + c0 + c]);
-      const float g = __bfloat162float(x[(size_t)rh * 2 * C + C + c0 + c]);
-      h = a * sigmoidf_(g);
-    }
-    sh_h[s * CC + c] = h;
-  }
-  __syncthreads();
+  const int n_tiles = (n_rows + TT - 1) / TT;
   const int c = threadIdx.x % CC;
   const int rg = threadIdx.x / CC;
-  float f[KMAX];
+  float f[KM];
 #pragma unroll
-  for (int k = 0; k < KMAX; ++k) f[k] = k < K ? filt[(size_t)(c0 + c) * K + k] : 0.f;
-  float df[KMAX];
+  for (int k = 0; k < KM; ++k) f[k] = k < K ? filt[(size_t)(c0 + c) * K + k] : 0.f;
+  float df[KM];
 #pragma unroll
-  for (int k = 0; k < KMAX; ++k) df[k] = 0.f;
+  for (int k = 0; k < KM; ++k) df[k] = 0.f;
   float dbias = 0.f;
-  for (int i = 0; i < TT / 4; ++i) {
-    const int lr = rg * (TT / 4) + i;
-    const int r = r0 + lr;
-    if (r >= n_rows) break;
-    const int t = row_pos[r];
-    const int L = lens[row_batch[r]];
-    // dh: contributions from output rows r' = r - k + left (position t - k + left) that lie inside the sequence
-    float dh = 0.f;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int r0 = tile * TT;
+    __syncthreads();  // the previous tile's readers are done with the shared arrays
+    // stage dy and h = a * sigmoid(g), 8 channels per thread-iteration
+    for (int idx = threadIdx.x; idx < n_in * (CC / 8); idx += kThreads) {
+      const int s = idx / (CC / 8), cg = (idx % (CC / 8)) * 8;
+      // dh[r] = sum_k f[k] * dy[r - k + left]  ->  needs dy rows r0 - right .. r0 + TT - 1 + left
+      const int rd = r0 - right + s;
+      F8 d;
+      if (rd >= 0 && rd < n_rows) d = load8(dy, (int64_t)rd * C + c0 + cg, 1);
+      else {
 #pragma unroll
-    for (int k = 0; k < KMAX; ++k) {
-      const int tp = t - k + left;
-      if (k < K && tp >= 0 && tp < L) dh += f[k] * sh_dy[(lr + right - k + left) * CC + c];
+        for (int i = 0; i < 8; ++i) d.v[i] = 0.f;
+      }
+      const int rh = r0 - left + s;
+      F8 h;
+      if (rh >= 0 && rh < n_rows) {
+        F8 a = load8(x, (int64_t)rh * 2 * C + c0 + cg, 1);
+        F8 g = load8(x, (int64_t)rh * 2 * C + C + c0 + cg, 1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h.v[i] = a.v[i] * sigmoidf_(g.v[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h.v[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        sh_dy[s * CC + cg + i] = d.v[i];
+        sh_h[s * CC + cg + i] = h.v[i];
+      }
     }
-    const float a = __bfloat162float(x[(size_t)r * 2 * C + c0 + c]);
-    const float g = __bfloat162float(x[(size_t)r * 2 * C + C + c0 + c]);
-    const float sg = sigmoidf_(g);
-    dx[(size_t)r * 2 * C + c0 + c] = __float2bfloat16(dh * sg);
-    dx[(size_t)r * 2 * C + C + c0 + c] = __float2bfloat16(dh * a * sg * (1.f - sg));
-    // dfilter[k] += dy[r] * h[r + k - left] for taps inside the sequence
-    const float dyr = sh_dy[(lr + right) * CC + c];
-    dbias += dyr;
-    const int k_lo = max(0, left - t);
-    const int k_hi = min(K, L - t + left);
+    if (threadIdx.x < TT) {
+      const int r = r0 + threadIdx.x;
+      sh_t[threadIdx.x] = r < n_rows ? row_pos[r] : 0;
+      sh_len[threadIdx.x] = r < n_rows ? lens[row_batch[r]] : 0;
+    }
+    __syncthreads();
+    for (int i = 0; i < TT / 4; ++i) {
+      const int lr = rg * (TT / 4) + i;
+      const int r = r0 + lr;
+      if (r >= n_rows) break;
+      const int t = sh_t[lr];
+      const int L = sh_len[lr];
+      // dh: contributions from output rows r' = r - k + left (position t - k + left) that lie inside the sequence
+      float dh = 0.f;
 #pragma unroll
-    for (int k = 0; k < KMAX; ++k) {
-      if (k >= k_lo && k < k_hi) df[k] += dyr * sh_h[(lr + k) * CC + c];
+      for (int k = 0; k < KM; ++k) {
+        const int tp = t - k + left;
+        if (k < K && tp >= 0 && tp < L) dh += f[k] * sh_dy[(lr + right - k + left) * CC + c];
+      }
+      // a and g of this row: h = a * sig(g) is staged at row lr + left; recover a, g from global (coalesced over c)
+      const float a = __bfloat162float(x[(size_t)r * 2 * C + c0 + c]);
+      const float g = __bfloat162float(x[(size_t)r * 2 * C + C + c0 + c]);
+      const float sg = sigmoidf_(g);
+      dx[(size_t)r * 2 * C + c0 + c] = __float2bfloat16(dh * sg);
+      dx[(size_t)r * 2 * C + C + c0 + c] = __float2bfloat16(dh * a * sg * (1.f - sg));
+      // dfilter[k] += dy[r] * h[r + k - left] for taps inside the sequence
+      const float dyr = sh_dy[(lr + right) * CC + c];
+      dbias += dyr;
+      const int k_lo = max(0, left - t);
+      const int k_hi = min(K, L - t + left);
+#pragma unroll
+      for (int k = 0; k < KM; ++k) {
+        if (k >= k_lo && k < k_hi) df[k] += dyr * sh_h[(lr + k) * CC + c];
+      }
     }
   }
   // reduce the 4 row groups through shared memory (reuse sh_h as [K+1][CC] accumulators), then one partial per CTA
@@ -286,7 +313,7 @@ glu_dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   for (int g = 0; g < 4; ++g) {
     if (rg == g) {
 #pragma unroll
-      for (int k = 0; k < KMAX; ++k)
+      for (int k = 0; k < KM; ++k)
         if (k < K) red[k * CC + c] = (g == 0 ? 0.f : red[k * CC + c]) + df[k];
       red[K * CC + c] = (g == 0 ? 0.f : red[K * CC + c]) + dbias;
     }
@@ -387,12 +414,25 @@ RB_EXPORT int rb200_glu_dwconv_bwd_ex(const void* x, const void* dy, const float
   if (n_rows <= 0) return RB_OK;
   if (C % CC || K > KMAX || K < 1) return RB_ERR_ARG;
   const int n_tiles = (n_rows + TT - 1) / TT;
-  dim3 grid(n_tiles, C / CC);
-  glu_dwconv_bwd_kernel<<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch, row_pos, lens,
-                                                       (__nv_bfloat16*)dx, part, n_rows, C, K);
+  // about four CTAs per SM in total; every CTA leaves one partial
+  int row_ctas = (4 * 148 + C / CC - 1) / (C / CC);
+  if (row_ctas > n_tiles) row_ctas = n_tiles;
+  dim3 grid(row_ctas, C / CC);
+  if (K <= 32) {
+    glu_dwconv_bwd_kernel<32><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch, row_pos, lens,
+                                                             (__nv_bfloat16*)dx, part, n_rows, C, K);
+  } else {
+    static bool attr = false;
+    if (!attr) {
+      cudaFuncSetAttribute(glu_dwconv_bwd_kernel<KMAX>, cudaFuncAttributePreferredSharedMemoryCarveout, 100);
+      attr = true;
+    }
+    glu_dwconv_bwd_kernel<KMAX><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch, row_pos, lens,
+                                                               (__nv_bfloat16*)dx, part, n_rows, C, K);
+  }
   int st = rb_check_launch("glu_dwconv_bwd");
   if (st) return st;
-  dwconv_bwd_reduce_kernel<<<(C * (K + 1) + 255) / 256, 256, 0, stream>>>(part, n_tiles, C, K, dfilt, dbias, accumulate);
+  dwconv_bwd_reduce_kernel<<<(C * (K + 1) + 255) / 256, 256, 0, stream>>>(part, row_ctas, C, K, dfilt, dbias, accumulate);
   return rb_check_launch("dwconv_bwd_reduce");
 }
 

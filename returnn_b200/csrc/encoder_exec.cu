@@ -84,29 +84,42 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
   const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
   const float keep = drop ? scale / (1.f - p_drop) : scale;
   if (col < C) {
-    for (int r = blockIdx.x * rows_per_iter + rs; r < rows; r += gridDim.x * rows_per_iter) {
-      const int64_t idx = (int64_t)r * C + col;
-      F8 v = load8(x, idx, 1);
-      if (y) {
-        if (drop) {
-          const uint64_t c = off + (uint64_t)idx;
-          const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
-          uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-          uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-          const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    const int stride = gridDim.x * rows_per_iter;
+    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
+    // four rows per iteration so that four independent loads are in flight per thread
+    for (int rbase = blockIdx.x * rows_per_iter + rs; rbase < rows; rbase += 4 * stride) {
+      F8 v[4];
+      int64_t idx[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) v.v[i] = rr[i] >= thresh ? v.v[i] * keep : 0.f;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v.v[i] *= keep;
-        }
-        store8(y, idx, v, 1);
-        // sum what was stored (bf16-rounded), so that the bias gradient matches the GEMM operand
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v.v[i] = __bfloat162float(__float2bfloat16(v.v[i]));
+      for (int u = 0; u < 4; ++u) {
+        const int r = rbase + u * stride;
+        idx[u] = (int64_t)r * C + col;
+        if (r < rows) v[u] = load8(x, idx[u], 1);
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += v.v[i];
+      for (int u = 0; u < 4; ++u) {
+        const int r = rbase + u * stride;
+        if (r >= rows) break;
+        if (y) {
+          if (drop) {
+            const uint64_t c = off + (uint64_t)idx[u];
+            uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
+            uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
+            const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[u].v[i] = rr[i] >= thresh ? v[u].v[i] * keep : 0.f;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[u].v[i] *= keep;
+          }
+          store8(y, idx[u], v[u], 1);
+          // sum what was stored (bf16-rounded), so that the bias gradient matches the GEMM operand
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[u].v[i] = __bfloat162float(__float2bfloat16(v[u].v[i]));
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] += v[u].v[i];
+      }
     }
   }
 #pragma unroll
@@ -134,7 +147,7 @@ int colsum(const void* x, void* y, float* out, int rows, int C, float scale, flo
   const int groups = G < 256 ? G : 256;  // a partial last chunk is masked by col < C
   const int rpi = 256 / groups > 0 ? 256 / groups : 1;
   int ctas = (rows + rpi * 8 - 1) / (rpi * 8);
-  const int cap = (296 + chunks - 1) / chunks;
+  const int cap = (592 + chunks - 1) / chunks;
   if (ctas > cap) ctas = cap;
   if (ctas < 1) ctas = 1;
   colsum_kernel<<<dim3(ctas, chunks), groups * rpi, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, out, rows, C, groups, rpi, scale, p_drop,

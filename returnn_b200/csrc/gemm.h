@@ -25,6 +25,14 @@ struct RbGemm {
   const void* resid = nullptr;   // bf16 [m][ldc]: final = resid + res_scale * v
   float res_scale = 1.f;
   int split_k = 0;               // 0: chosen by the launcher (> 1 only with accumulate == 2)
+  // batched form (batch > 0): problem z = b * heads + h reads A from the stored origin (b*a_rb + h*a_rh, b*a_cb + h*a_ch),
+  // B likewise, and writes at element offset b*c_sb + h*c_sh. m / n / k are fixed or lens[b] where the *_from_lens flag is set;
+  // a problem with an empty extent is skipped. a_rows .. b_cols are the extents of the stored matrices.
+  int batch = 0, heads = 1;
+  long long a_rb = 0, a_rh = 0, a_cb = 0, a_ch = 0, b_rb = 0, b_rh = 0, b_cb = 0, b_ch = 0, c_sb = 0, c_sh = 0;
+  long long a_rows = 0, a_cols = 0, b_rows = 0, b_cols = 0;
+  const int* lens = nullptr;
+  int m_from_lens = 0, n_from_lens = 0, k_from_lens = 0;
   int* status = nullptr;         // device word: 0 fine, else (role << 24 | detail) of the wait that gave up
 };
 

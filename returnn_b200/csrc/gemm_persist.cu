@@ -89,11 +89,11 @@ __device__ __forceinline__ void store8_bf16(void* base, size_t off, bool vec, in
 }
 
 // one lane's share of the epilogue: 8 consecutive columns [col, col+8) of one output row
-__device__ __forceinline__ void epilogue_group(const Params& p, int row, int col, float* v) {
+__device__ __forceinline__ void epilogue_group(const Params& p, int row, int col, int n_extent, size_t c_off, float* v) {
   const RbGemm& g = p.g;
-  const int nvalid = min(8, g.n - col);
-  const bool vec = p.vec_ok && nvalid == 8;
-  const size_t off = (size_t)row * g.ldc + col;
+  const int nvalid = min(8, n_extent - col);
+  const bool vec = p.vec_ok && nvalid == 8 && (c_off & 7) == 0;
+  const size_t off = c_off + (size_t)row * g.ldc + col;
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] *= g.alpha;
   if (g.bias) {
@@ -172,6 +172,48 @@ __device__ __forceinline__ void epilogue_group(const Params& p, int row, int col
   }
 }
 
+// one work unit: output tile (m0, n0) of problem z, K blocks [kb0, kb1)
+struct Unit {
+  int m0, n0, kb0, kb1, M, N;
+  int a_r0, a_c0, b_r0, b_c0;
+  size_t c_off;
+  bool valid;
+};
+
+template <int BN>
+__device__ __forceinline__ Unit decode_unit(const Params& p, int u) {
+  const RbGemm& g = p.g;
+  Unit w;
+  const int tiles = p.tiles_m * p.tiles_n;
+  if (g.batch > 0) {
+    const int z = u / tiles, t = u % tiles;
+    const int zb = z / g.heads, zh = z % g.heads;
+    const int len = g.lens ? g.lens[zb] : 0;
+    w.M = g.m_from_lens ? len : g.m;
+    w.N = g.n_from_lens ? len : g.n;
+    const int K = g.k_from_lens ? len : g.k;
+    w.m0 = (t / p.tiles_n) * BM;
+    w.n0 = (t % p.tiles_n) * BN;
+    w.kb0 = 0;
+    w.kb1 = K > 0 ? (K + BK - 1) / BK : 0;
+    w.a_r0 = (int)(zb * g.a_rb + zh * g.a_rh); w.a_c0 = (int)(zb * g.a_cb + zh * g.a_ch);
+    w.b_r0 = (int)(zb * g.b_rb + zh * g.b_rh); w.b_c0 = (int)(zb * g.b_cb + zh * g.b_ch);
+    w.c_off = (size_t)zb * g.c_sb + (size_t)zh * g.c_sh;
+    w.valid = w.m0 < w.M && w.n0 < w.N && w.kb1 > 0;
+  } else {
+    const int sp = u / tiles, t = u % tiles;
+    w.M = g.m; w.N = g.n;
+    w.m0 = (t / p.tiles_n) * BM;
+    w.n0 = (t % p.tiles_n) * BN;
+    w.kb0 = sp * p.kb_per_split;
+    w.kb1 = min(p.num_kb, w.kb0 + p.kb_per_split);
+    w.a_r0 = w.a_c0 = w.b_r0 = w.b_c0 = 0;
+    w.c_off = 0;
+    w.valid = true;
+  }
+  return w;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
@@ -216,18 +258,16 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-  const int tiles = p.tiles_m * p.tiles_n;
-
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer ----------------
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        const int sp = u / tiles, t = u % tiles;
-        const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
-        const int kb0 = sp * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
-        for (int kb = kb0; kb < kb1; ++kb, ++it) {
+        const Unit w = decode_unit<BN>(p, u);
+        if (!w.valid) continue;
+        const int m0 = w.m0, n0 = w.n0;
+        for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1u;
           if (!mbar_wait(&empty_bar[s], ph ^ 1u, abort_flag)) {
@@ -241,16 +281,16 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           mbar_expect_tx(&full_bar[s], kStageBytes);
           const int k0 = kb * BK;
           if (!g.a_mn_major) {
-            tma_load_2d(sa, &tm_a, k0, m0, &full_bar[s]);
+            tma_load_2d(sa, &tm_a, w.a_c0 + k0, w.a_r0 + m0, &full_bar[s]);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tm_a, m0 + 64 * j, k0, &full_bar[s]);
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tm_a, w.a_c0 + m0 + 64 * j, w.a_r0 + k0, &full_bar[s]);
           }
           if (!g.b_mn_major) {
-            tma_load_2d(sb, &tm_b, k0, n0, &full_bar[s]);
+            tma_load_2d(sb, &tm_b, w.b_c0 + k0, w.b_r0 + n0, &full_bar[s]);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, n0 + 64 * j, k0, &full_bar[s]);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tm_b, w.b_c0 + n0 + 64 * j, w.b_r0 + k0, &full_bar[s]);
           }
         }
       }
@@ -262,9 +302,10 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
                              ((uint32_t)(g.b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t it = 0, t_local = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x, ++t_local) {
-        const int sp = u / tiles;
-        const int kb0 = sp * p.kb_per_split, kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+      for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
+        const Unit w = decode_unit<BN>(p, u);
+        if (!w.valid) continue;
+        const int kb0 = w.kb0, kb1 = w.kb1;
         const uint32_t buf = t_local & 1u;
         if (!mbar_wait(&acc_empty[buf], ((t_local >> 1) & 1u) ^ 1u, abort_flag)) {
           *abort_flag = 1;
@@ -296,6 +337,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           umma_commit(&empty_bar[s]);
         }
         if (ok) umma_commit(&acc_full[buf]);
+        ++t_local;
       }
     }
   } else {
@@ -303,9 +345,10 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     const int q = warp & 3;
     float* stg = staging + (warp - 2) * (8192 / 4);
     uint32_t t_local = 0;
-    for (int u = blockIdx.x; u < p.units; u += gridDim.x, ++t_local) {
-      const int t = u % tiles;
-      const int m0 = (t / p.tiles_n) * BM, n0 = (t % p.tiles_n) * BN;
+    for (int u = blockIdx.x; u < p.units; u += gridDim.x) {
+      const Unit w = decode_unit<BN>(p, u);
+      if (!w.valid) continue;
+      const int m0 = w.m0, n0 = w.n0;
       const uint32_t buf = t_local & 1u;
       bool ok = mbar_wait(&acc_full[buf], (t_local >> 1) & 1u, abort_flag);
       if (!ok && lane == 0) {
@@ -346,13 +389,14 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const int row = m0 + q * 32 + rl;
           const float4* rrow = reinterpret_cast<const float4*>(stg + rl * 64);
           float4 a = rrow[(2 * cg) ^ (rl & 7)], b = rrow[(2 * cg + 1) ^ (rl & 7)];
-          if (row < g.m && col < g.n) {
+          if (row < w.M && col < w.N) {
             float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            epilogue_group(p, row, col, v);
+            epilogue_group(p, row, col, w.N, w.c_off, v);
           }
         }
         __syncwarp();
       }
+      ++t_local;
     }
   }
 
@@ -408,12 +452,19 @@ int launch(const RbGemm& g, cudaStream_t stream) {
   p.kb_per_split = (p.num_kb + split - 1) / split;
   p.split = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty slices
   p.units = tiles * p.split;
+  if (g.batch > 0) {
+    p.split = 1;
+    p.units = tiles * g.batch;
+  }
   auto al16 = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   p.vec_ok = (g.ldc % 8 == 0) && al16(g.c) && al16(g.c2) && al16(g.resid) && al16(g.dact_z);
   CUtensorMap tm_a, tm_b;
   int st;
-  const long long a_rows = g.a_mn_major ? g.k : g.m, a_cols = g.a_mn_major ? g.m : g.k;
-  const long long b_rows = g.b_mn_major ? g.k : g.n, b_cols = g.b_mn_major ? g.n : g.k;
+  long long a_rows = g.a_mn_major ? g.k : g.m, a_cols = g.a_mn_major ? g.m : g.k;
+  long long b_rows = g.b_mn_major ? g.k : g.n, b_cols = g.b_mn_major ? g.n : g.k;
+  if (g.batch > 0) {
+    a_rows = g.a_rows; a_cols = g.a_cols; b_rows = g.b_rows; b_cols = g.b_cols;
+  }
   st = g.a_mn_major ? make_map(&tm_a, g.a, a_cols, a_rows, g.lda, 64, BK) : make_map(&tm_a, g.a, a_cols, a_rows, g.lda, BK, BM);
   if (st) return st;
   st = g.b_mn_major ? make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, 64, BK) : make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, BK, BN);
@@ -427,8 +478,12 @@ int launch(const RbGemm& g, cudaStream_t stream) {
 
 int rb_gemm(const RbGemm& g, cudaStream_t stream) {
   if (g.m <= 0 || g.n <= 0) return RB_OK;
-  if (g.k <= 0) {
+  if (g.k <= 0 && !(g.batch > 0 && g.k_from_lens)) {
     rb_set_error("gemm: k=%d", g.k);
+    return RB_ERR_ARG;
+  }
+  if (g.batch > 0 && (g.accumulate == 2 || g.split_k > 1 || g.a_rows <= 0 || g.a_cols <= 0 || g.b_rows <= 0 || g.b_cols <= 0)) {
+    rb_set_error("gemm: the batched form needs the stored extents and supports no split-K");
     return RB_ERR_ARG;
   }
   if ((g.lda % 8) || (g.ldb % 8) || (reinterpret_cast<uintptr_t>(g.a) & 15) || (reinterpret_cast<uintptr_t>(g.b) & 15)) {

@@ -14,6 +14,9 @@
 // Every mbarrier wait is bounded: after kSpinLimit polls the kernel raises an abort flag (shared), writes a status word
 // to global memory, waits for its own TMA copies with a second bound, frees its tensor memory and returns.
 #include "tcgen05.cuh"
+#include "gemm.h"
+#include <cstdlib>
+#include <cstring>
 
 using namespace rbt;
 
@@ -305,6 +308,25 @@ RB_EXPORT int rb200_gemm_bf16_batched(const void* a, const void* b, void* c, con
                                       int batch, int heads, const long long* offs /*a_rb,a_rh,a_cb,a_ch,b_rb,b_rh,b_cb,b_ch,c_sb,c_sh*/,
                                       const int* lens, int m_from_lens, int n_from_lens, int k_from_lens, int* status, cudaStream_t stream) {
   if (m <= 0 || n <= 0 || batch <= 0) return RB_OK;
+  static int legacy = -1;
+  if (legacy < 0) {
+    const char* e = getenv("RETURNN_B200_GEMM_KERNEL");
+    legacy = (e && strcmp(e, "legacy") == 0) ? 1 : 0;
+  }
+  if (!legacy) {
+    RbGemm g;
+    g.a = a; g.b = b; g.c = c; g.bias = bias; g.bias_bf16 = bias_bf16;
+    g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+    g.a_mn_major = a_mn_major; g.b_mn_major = b_mn_major; g.act = act; g.out_fp32 = out_fp32; g.accumulate = accumulate; g.alpha = alpha;
+    g.status = status;
+    g.batch = batch; g.heads = heads > 0 ? heads : 1;
+    g.a_rb = offs[0]; g.a_rh = offs[1]; g.a_cb = offs[2]; g.a_ch = offs[3];
+    g.b_rb = offs[4]; g.b_rh = offs[5]; g.b_cb = offs[6]; g.b_ch = offs[7];
+    g.c_sb = offs[8]; g.c_sh = offs[9];
+    g.a_rows = a_rows; g.a_cols = a_cols; g.b_rows = b_rows; g.b_cols = b_cols;
+    g.lens = lens; g.m_from_lens = m_from_lens; g.n_from_lens = n_from_lens; g.k_from_lens = k_from_lens;
+    return rb_gemm(g, stream);
+  }
   GemmParams p;
   p.c = c;
   p.c2 = nullptr;
