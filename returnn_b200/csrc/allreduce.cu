@@ -1,0 +1,184 @@
+// Fused gradient all-reduce over NVLink peer memory for one node (2..8 GPUs, one process per GPU).
+//
+// One kernel per bucket does what otherwise takes a scale kernel, an NCCL all-reduce and a norm kernel:
+//   1. entry barrier between the same-numbered CTAs of all ranks (flags in symmetric memory, release/acquire at system scope)
+//   2. every rank owns one slice of the bucket: it sums that slice over all ranks
+//        - plain path: 16-byte loads from each peer's buffer (peer pointers), rotated so that the ranks do not all hit
+//          the same peer at once
+//        - multimem path: one multimem.ld_reduce through the NVSwitch multicast mapping (the switch adds)
+//      scales by 1/world, accumulates the sum of squares, and writes the result into every rank's buffer
+//      (peer stores, or one multimem.st)
+//   3. the sum of squares of the slice is added (system-scope atomics) to a norm accumulator on every rank, so that after the
+//      last bucket every rank holds the squared global gradient norm without another pass or collective
+//   4. exit barrier: all pushes have landed before any rank's next kernel reads its buffer
+//
+// Every wait is bounded (kSpinLimit polls with nanosleep, about two seconds): a CTA that gives up writes a status word and
+// skips its data phase; the context stays usable and the host raises an error.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxWorld = 8;
+constexpr int kMaxBlocks = 256;
+constexpr int kThreads = 512;
+constexpr uint32_t kSpinLimit = 1u << 21;
+
+struct ArParams {
+  float* bufs[kMaxWorld];       // the gradient arena of every rank (bufs[rank] is local)
+  uint32_t* flags[kMaxWorld];   // [world][kMaxBlocks] per rank: flags[dst][src * kMaxBlocks + block]
+  float* norm[kMaxWorld];       // norm accumulator of every rank
+  float* mc;                    // multicast mapping of the arena, or null
+  int world, rank;
+  long long lo, n;              // element range of the bucket
+  float scale;
+  uint32_t epoch;               // barrier values epoch (entry) and epoch + 1 (exit); grows by 2 per call on all ranks alike
+  int norm_slot;
+  int* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// barrier between CTA blockIdx.x of all ranks; false = a peer did not arrive in time
+__device__ bool cta_barrier(const ArParams& p, uint32_t val, int* sh_fail, int code) {
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    const int peer = threadIdx.x;
+    __threadfence_system();
+    st_release_sys(p.flags[peer] + (size_t)p.rank * kMaxBlocks + blockIdx.x, val);
+    const uint32_t* mine = p.flags[p.rank] + (size_t)peer * kMaxBlocks + blockIdx.x;
+    bool ok = false;
+    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+      if ((int32_t)(ld_acquire_sys(mine) - val) >= 0) {
+        ok = true;
+        break;
+      }
+      __nanosleep(i < 64 ? 32 : 1000);
+    }
+    if (!ok) {
+      *sh_fail = 1;
+      if (p.status) atomicCAS(p.status, 0, (code << 24) | (peer << 16) | (int)(blockIdx.x & 0xFFFF));
+    }
+  }
+  __syncthreads();
+  return *sh_fail == 0;
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce(const float* addr) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(addr)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st(float* addr, float4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+__global__ void __launch_bounds__(kThreads)
+fused_allreduce_kernel(const ArParams p) {
+  __shared__ int sh_fail;
+  __shared__ float sh_red[kThreads / 32];
+  if (threadIdx.x == 0) sh_fail = 0;
+  if (!cta_barrier(p, p.epoch, &sh_fail, 1)) return;
+
+  // slices of whole float4s; the tail (n % 4 elements) belongs to the last rank
+  const long long n4 = p.n / 4;
+  const long long per = (n4 + p.world - 1) / p.world;
+  const long long s0 = per * p.rank < n4 ? per * p.rank : n4;
+  const long long s1 = s0 + per < n4 ? s0 + per : n4;
+  float ssq = 0.f;
+  const long long stride = (long long)gridDim.x * kThreads;
+  for (long long i = s0 + (long long)blockIdx.x * kThreads + threadIdx.x; i < s1; i += stride) {
+    const long long e = p.lo + i * 4;
+    float4 acc;
+    if (p.mc) {
+      acc = multimem_ld_reduce(p.mc + e);
+    } else {
+      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+      for (int k = 0; k < p.world; ++k) {
+        const int peer = (p.rank + k) % p.world;
+        const float4 v = *reinterpret_cast<const float4*>(p.bufs[peer] + e);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    acc.x *= p.scale; acc.y *= p.scale; acc.z *= p.scale; acc.w *= p.scale;
+    ssq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    if (p.mc) {
+      multimem_st(p.mc + e, acc);
+    } else {
+#pragma unroll 1
+      for (int k = 0; k < p.world; ++k) {
+        const int peer = (p.rank + k) % p.world;
+        *reinterpret_cast<float4*>(p.bufs[peer] + e) = acc;
+      }
+    }
+  }
+  if (p.rank == p.world - 1 && blockIdx.x == 0 && threadIdx.x < (p.n & 3)) {
+    const long long e = p.lo + n4 * 4 + threadIdx.x;
+    float acc = 0.f;
+    for (int k = 0; k < p.world; ++k) acc += p.bufs[k][e];
+    acc *= p.scale;
+    ssq += acc * acc;
+    for (int k = 0; k < p.world; ++k) p.bufs[k][e] = acc;
+  }
+  // sum of squares of this CTA's share -> every rank's accumulator
+  ssq = warp_sum(ssq);
+  if ((threadIdx.x & 31) == 0) sh_red[threadIdx.x >> 5] = ssq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float v = threadIdx.x < kThreads / 32 ? sh_red[threadIdx.x] : 0.f;
+    v = warp_sum(v);
+    if (threadIdx.x == 0 && v != 0.f) {
+      for (int k = 0; k < p.world; ++k) atomicAdd_system(p.norm[k] + p.norm_slot, v);
+    }
+  }
+  cta_barrier(p, p.epoch + 1, &sh_fail, 2);
+}
+
+}  // namespace
+
+// bufs / flags / norm: arrays of `world` device addresses (one per rank, index = rank). The flag buffers hold
+// world * 256 zero-initialised uint32. epoch: 1, 3, 5, ... identical on all ranks for the same call.
+RB_EXPORT int rb200_fused_allreduce(const long long* bufs, const long long* flags, const long long* norm, void* multicast, int world, int rank,
+                                    long long lo, long long n, float scale, unsigned int epoch, int norm_slot, int blocks, int* status,
+                                    cudaStream_t stream) {
+  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world) {
+    rb_set_error("fused_allreduce: world %d rank %d", world, rank);
+    return RB_ERR_ARG;
+  }
+  if (n <= 0) return RB_OK;
+  if (lo % 4) {
+    rb_set_error("fused_allreduce: bucket start %lld must be a multiple of 4 elements", lo);
+    return RB_ERR_ARG;
+  }
+  ArParams p;
+  for (int i = 0; i < kMaxWorld; ++i) {
+    p.bufs[i] = i < world ? reinterpret_cast<float*>(bufs[i]) : nullptr;
+    p.flags[i] = i < world ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
+    p.norm[i] = i < world ? reinterpret_cast<float*>(norm[i]) : nullptr;
+  }
+  p.mc = reinterpret_cast<float*>(multicast);
+  p.world = world;
+  p.rank = rank;
+  p.lo = lo;
+  p.n = n;
+  p.scale = scale;
+  p.epoch = epoch;
+  p.norm_slot = norm_slot;
+  p.status = status;
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p);
+  return rb_check_launch("fused_allreduce");
+}
+
+RB_EXPORT int rb200_fused_allreduce_flag_words() { return kMaxWorld * kMaxBlocks; }

@@ -135,7 +135,11 @@ def convert_to_tensor(value, *, dims: Sequence[Dim] = (), dtype: Optional[str] =
                 dtype = str(value.dtype)
             else:
                 raise TypeError("convert_to_tensor: cannot handle %r" % type(value))
-        raw = torch.as_tensor(value, dtype=torch_dtype(dtype), device=device)
+        if isinstance(value, (bool, int, float)) and device is not None and str(device).startswith("cuda"):
+            # a fill kernel instead of a host-to-device copy of one element (which would synchronise the stream)
+            raw = torch.full((), value, dtype=torch_dtype(dtype), device=device)
+        else:
+            raw = torch.as_tensor(value, dtype=torch_dtype(dtype), device=device)
     assert raw.ndim == len(dims), "convert_to_tensor: value ndim %i but dims %r" % (raw.ndim, dims)
     return wrap(raw, dims, name=name or "const", sparse_dim=sparse_dim, feature_dim=feature_dim)
 

@@ -737,7 +737,7 @@ def where(cond: Union[Tensor, bool], true_: Union[Tensor, int, float, bool], fal
         return res if isinstance(res, Tensor) else _convert_to_tensor(res)
     like = true_ if isinstance(true_, Tensor) else (false_ if isinstance(false_, Tensor) else None)
     t = true_ if isinstance(true_, Tensor) else _convert_to_tensor(true_, like=like, device=cond.device)
-    f = false_ if isinstance(false_, Tensor) else _convert_to_tensor(false_, like=like or t, device=cond.device)
+    f = false_ if isinstance(false_, Tensor) else _convert_to_tensor(false_, like=like if like is not None else t, device=cond.device)
     cands = sorted([cond, t, f], key=lambda x: -len(x._dims))
     out_dims = list(cands[0]._dims)
     for c in cands[1:]:

@@ -58,7 +58,7 @@ class LSTM(Module):
         :param direction: +1 forward in time, -1 backward (each sequence reversed within its own length)
         :return: output {spatial_dim, batch.., out_dim}, final state
         """
-        if not state.h or not state.c:
+        if state.h is None or state.c is None:
             raise ValueError("%s: state.h and state.c need to be set (use default_initial_state)" % self)
         if self.in_dim not in source.dims:
             raise ValueError("%s: input %r does not have in_dim %r" % (self, source, self.in_dim))

@@ -171,12 +171,13 @@ class RunCtx:
     def total_loss(self) -> Union[Tensor, float]:
         """sum over scale * reduced loss of all non-error losses: the value to differentiate"""
         assert self.stage == "train_step"
-        total = 0.0
+        total = None
         for loss in self.losses.values():
             if loss.as_error or loss.scale is None or loss.scale == 0:
                 continue
-            total = total + loss.get_scaled_reduced_loss()
-        return total
+            term = loss.get_scaled_reduced_loss()
+            total = term if total is None else total + term
+        return 0.0 if total is None else total
 
 
 class Loss:

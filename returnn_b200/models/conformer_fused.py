@@ -60,12 +60,27 @@ def frontend_subsample(enc, feats: torch.Tensor, lens_host: torch.Tensor, W: _We
     """
     from ..frontend.conv import _same_pads
 
+    from .packing import host_to_device
+
     il = enc.input_layer
     B, T, Fdim = feats.shape
-    mask = torch.arange(T, device=feats.device)[None, :] < lens_host.to(feats.device)[:, None]
+    # lengths after every stage, computed on the host and sent in one asynchronous copy
+    stage_lens = [lens_host.clone().to(torch.int64)]
+    for i, conv in enumerate(il.conv_layers):
+        fs = tuple(d.dimension for d in conv.filter_size)
+        st = il._strides2[i]
+        lens = stage_lens[-1]
+        if conv.padding == "same":
+            lens = -(-lens // st[0])
+        else:
+            lens = torch.clamp(-(-(lens - fs[0] + 1) // st[0]), min=0)
+        if il.pool_sizes and i < len(il.pool_sizes):
+            lens = -(-lens // il.pool_sizes[i][0])
+        stage_lens.append(lens)
+    lens_dev = host_to_device(torch.stack(stage_lens).to(torch.int32), feats.device)
+    mask = torch.arange(T, device=feats.device)[None, :] < lens_dev[0][:, None]
     x = (feats * mask.unsqueeze(-1).to(feats.dtype)).unsqueeze(1)  # [B,1,T,F]
     x = x.contiguous(memory_format=torch.channels_last)
-    lens = lens_host.clone().to(torch.int64)
     for i, conv in enumerate(il.conv_layers):
         fs = tuple(d.dimension for d in conv.filter_size)
         st = il._strides2[i]
@@ -75,11 +90,7 @@ def frontend_subsample(enc, feats: torch.Tensor, lens_host: torch.Tensor, W: _We
             pads = _same_pads(x.shape[2:], fs, st)
             if any(pads):
                 x = F.pad(x, pads)
-            x = F.conv2d(x, w, b, stride=st)
-            lens = -(-lens // st[0])
-        else:
-            x = F.conv2d(x, w, b, stride=st)
-            lens = torch.clamp(-(-(lens - fs[0] + 1) // st[0]), min=0)
+        x = F.conv2d(x, w, b, stride=st)
         x = torch.relu(x)
         if il.pool_sizes and i < len(il.pool_sizes):
             ps = il.pool_sizes[i]
@@ -87,11 +98,11 @@ def frontend_subsample(enc, feats: torch.Tensor, lens_host: torch.Tensor, W: _We
             if any(pads):
                 x = F.pad(x, pads, value=float("-inf"))
             x = F.max_pool2d(x, kernel_size=ps, stride=ps)
-            lens = -(-lens // ps[0])
         # frames past each sequence's end must be zero for the next conv
         Tn = x.shape[2]
-        m = (torch.arange(Tn, device=x.device)[None, :] < lens.to(x.device)[:, None]).to(x.dtype)
+        m = (torch.arange(Tn, device=x.device)[None, :] < lens_dev[i + 1][:, None]).to(x.dtype)
         x = x * m[:, None, :, None]
+    lens = stage_lens[-1]
     Bc, C, Tn, Fn = x.shape
     out = x.permute(0, 2, 3, 1).reshape(Bc, Tn, Fn * C)
     return out, lens.to(torch.int32)

@@ -108,6 +108,15 @@ class NativeEncoderPlan:
                     tab[li, si, 2] = base_s + off // 2
         self.table = tab
         self.key = (base_p, base_g, base_s)
+        # trainable parameters per layer (for the gradient reducer's bookkeeping)
+        self.layer_params = []
+        for layer in layers:
+            ps = []
+            for path in _SLOTS:
+                p = _get_attr_path(layer, path)
+                if p is not None and p.raw_tensor.requires_grad:
+                    ps.append(p.raw_tensor)
+            self.layer_params.append(ps)
 
     def still_valid(self) -> bool:
         """the arena buffers are the ones the table points into"""
@@ -215,4 +224,11 @@ def encoder_stack(x0: torch.Tensor, sinus: torch.Tensor, plan: NativeEncoderPlan
     :param grad_ready_cb: ``cb(layer_lo, layer_hi)`` called during backward once the parameter gradients of these layers are complete
     :return: [N, D] bf16 output of the last layer
     """
+    if grad_ready_cb is None:
+        from ..parallel import grad_reducer as _gr
+
+        if _gr.get_active() is not None:
+            def grad_ready_cb(lo, hi):
+                for li in range(lo, hi):
+                    _gr.notify_grads_written(plan.layer_params[li])
     return _EncoderStackFn.apply(x0, sinus, plan, pack, grad_ready_cb)

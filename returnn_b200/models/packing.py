@@ -8,6 +8,16 @@ from typing import List, Optional, Tuple
 import torch
 
 
+def host_to_device(t: torch.Tensor, device) -> torch.Tensor:
+    """copy of a host tensor on ``device``; through pinned memory and asynchronous on CUDA (no stream synchronisation)"""
+    device = torch.device(device)
+    if device.type == "cuda" and not t.is_cuda:
+        if not t.is_pinned():
+            t = t.pin_memory()
+        return t.to(device, non_blocking=True)
+    return t.to(device)
+
+
 class PackInfo:
     """
     Layout of one packed batch.
@@ -30,16 +40,20 @@ class PackInfo:
         cu = torch.zeros(self.batch + 1, dtype=torch.int32)
         cu[1:] = torch.cumsum(lens_host, 0)
         self.cu_host = cu
-        # one small H2D for all layout tensors
+        # one H2D copy for all layout tensors, from pinned memory so that it does not synchronise the stream
         T = self.padded_len
-        b_idx = torch.repeat_interleave(torch.arange(self.batch, dtype=torch.int64), lens_host.to(torch.int64))
-        t_idx = torch.arange(self.n, dtype=torch.int64) - cu[:-1].to(torch.int64)[b_idx]
+        b_idx = torch.repeat_interleave(torch.arange(self.batch, dtype=torch.int32), lens_host.to(torch.int64))
+        t_idx = torch.arange(self.n, dtype=torch.int32) - cu[:-1][b_idx.long()]
         gather = b_idx * T + t_idx
-        self.lens = lens_host.to(device, non_blocking=True)
-        self.cu = cu.to(device, non_blocking=True)
-        self.gather_idx = gather.to(device, non_blocking=True)
-        self.row_batch = b_idx.to(torch.int32).to(device, non_blocking=True)
-        self.row_pos = t_idx.to(torch.int32).to(device, non_blocking=True)
+        flat = torch.cat([lens_host, cu, b_idx, t_idx, gather])
+        dev = host_to_device(flat, device)
+        B, n = self.batch, self.n
+        self.lens = dev[:B]
+        self.cu = dev[B: 2 * B + 1]
+        o = 2 * B + 1
+        self.row_batch = dev[o: o + n]
+        self.row_pos = dev[o + n: o + 2 * n]
+        self.gather_idx = dev[o + 2 * n: o + 3 * n].long()
 
     def pack(self, padded: torch.Tensor) -> torch.Tensor:
         """[B, T, ...] -> [N, ...]"""

@@ -76,7 +76,9 @@ def ctc_loss_packed(logits_rows: torch.Tensor, pack, targets: torch.Tensor, tgt_
     """
     max_s = int(tgt_lens_host.max()) if tgt_lens_host.numel() else 0
     if logits_rows.is_cuda and _lib.use_native(logits_rows) and available() and supports(logits_rows, targets):
-        tl = tgt_lens_host.to(torch.int32).to(logits_rows.device, non_blocking=True)
+        from ..models.packing import host_to_device
+
+        tl = host_to_device(tgt_lens_host.to(torch.int32), logits_rows.device)
         return _CtcFn.apply(logits_rows, pack.cu, pack.row_batch, pack.lens, targets, tl, blank_index, max_s)
     padded = pack.unpack(logits_rows)  # [B, T, V]
     log_probs = F.log_softmax(padded.float(), dim=-1).transpose(0, 1)

@@ -203,6 +203,9 @@ class _ArenaLinearFn(torch.autograd.Function):
             fn = _lib.bind("rb200_colsum_bf16", [_vp, _vp, _i32, _i32, _vp])
             _lib.check(fn(dy.data_ptr(), ctx.gb32.data_ptr(), m, n, _lib.stream_ptr()), "colsum")
             _lib.count_launch()
+        from ..parallel import grad_reducer as _gr
+
+        _gr.notify_grads_written([ctx.gw32, ctx.gb32])
         return dx, None, None, None, None, None
 
 

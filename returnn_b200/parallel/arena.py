@@ -133,6 +133,20 @@ class ParamArena:
         """whether a bf16 copy is being maintained"""
         return self._shadow is not None
 
+    def replace_grad_buffer(self, new_flat: torch.Tensor):
+        """
+        Move the gradient arena into ``new_flat`` (same dtype, at least ``total`` elements; e.g. symmetric memory that
+        peer GPUs can address) and re-point every ``param.grad`` into it.
+        """
+        assert new_flat.dtype == self.grad_dtype and new_flat.numel() >= self.total and new_flat.device == self.device
+        new_flat = new_flat[: self.total]
+        with torch.no_grad():
+            new_flat.copy_(self.flat_grad)
+        self.flat_grad = new_flat
+        if self.grad_dtype == self.dtype:
+            for s in self.slots:
+                s.param.grad = self.flat_grad[s.offset: s.offset + s.numel].view(s.shape)
+
     def zero_grad(self):
         """one memset for all gradients"""
         self.flat_grad.zero_()

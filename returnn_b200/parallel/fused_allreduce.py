@@ -1,0 +1,109 @@
+"""
+Fused gradient all-reduce for one node over NVLink (``csrc/allreduce.cu``): the gradient arena lives in symmetric memory
+(every rank can address every rank's copy), and one kernel per bucket sums the ranks' slices through peer pointers or the
+NVSwitch multicast mapping (``multimem.ld_reduce`` / ``multimem.st``), scales by ``1/world``, writes the result to all
+ranks and accumulates the squared global gradient norm, so neither a scale pass, nor NCCL, nor a norm pass is needed.
+
+``try_create`` returns None when the prerequisites are missing (no CUDA, other ranks on other nodes, symmetric memory not
+available, library missing) unless ``required``. Environment: ``RETURNN_B200_ALLREDUCE_MULTIMEM=0`` keeps the kernel
+on plain peer loads and stores (tests that let a rank leave use this, together with ``NCCL_NVLS_ENABLE=0``).
+"""
+
+from __future__ import annotations
+from typing import Optional
+import ctypes
+import os
+import torch
+import torch.distributed as dist
+from ..ops import _lib
+from .arena import ParamArena
+
+_vp, _i32, _i64, _f32, _u32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_uint
+
+
+class FusedAllReduce:
+    """bucket reductions on the arena's gradient buffer"""
+
+    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 64):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert arena.grad_dtype == torch.float32
+        self.arena = arena
+        self.rank, self.world = rank, world
+        self.blocks = blocks
+        dev = arena.device
+        group = group or dist.group.WORLD
+        n = (arena.total + 3) // 4 * 4
+        self._grad = symm_mem.empty(n, dtype=torch.float32, device=dev)
+        self._grad.zero_()
+        self._hdl = symm_mem.rendezvous(self._grad, group)
+        lib = _lib.get_lib(required=True)
+        lib.rb200_fused_allreduce_flag_words.restype = ctypes.c_int
+        words = int(lib.rb200_fused_allreduce_flag_words())
+        self._flags = symm_mem.empty(words, dtype=torch.int32, device=dev)
+        self._flags.zero_()
+        self._hdl_flags = symm_mem.rendezvous(self._flags, group)
+        self._norm = symm_mem.empty(8, dtype=torch.float32, device=dev)
+        self._norm.zero_()
+        self._hdl_norm = symm_mem.rendezvous(self._norm, group)
+        arena.replace_grad_buffer(self._grad)
+        self._bufs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        self._flag_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_flags.buffer_ptrs])
+        self._norm_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_norm.buffer_ptrs])
+        use_mc = os.environ.get("RETURNN_B200_ALLREDUCE_MULTIMEM", "1") == "1"
+        mc = int(getattr(self._hdl, "multicast_ptr", 0) or 0) if use_mc else 0
+        self.multicast_ptr = mc
+        self._epoch = 1
+        self._slot = 0
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._fn = _lib.bind("rb200_fused_allreduce", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _f32, _u32, _i32, _i32, _vp, _vp])
+        # all ranks have zeroed their flags and accumulators before anyone's first kernel signals
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)
+
+    def reduce_bucket(self, b: int, lo: int, hi: int):
+        """average ``flat_grad[lo:hi]`` over the ranks, on the current stream; all ranks must call this in the same order"""
+        _lib.check(self._fn(ctypes.addressof(self._bufs), ctypes.addressof(self._flag_ptrs), ctypes.addressof(self._norm_ptrs),
+                            self.multicast_ptr or None, self.world, self.rank, lo, hi - lo, 1.0 / self.world, self._epoch, self._slot,
+                            self.blocks, self._status.data_ptr(), _lib.stream_ptr()), "fused_allreduce")
+        _lib.count_launch()
+        self._epoch += 2
+
+    def finish(self) -> torch.Tensor:
+        """
+        After the last bucket of a step (on the stream that ran them or one that waits for it): the squared global norm of
+        the averaged gradient as a device scalar. The accumulator alternates between two slots; the one for the next step
+        is cleared here, which is safe because no peer adds to it before its next step's entry barrier with this rank.
+        """
+        norm_sq = self._norm[self._slot].clone()
+        self._slot ^= 1
+        self._norm[self._slot].zero_()
+        return norm_sq
+
+    def check_status(self):
+        """raise if a barrier of an earlier call timed out (synchronises)"""
+        v = int(self._status.item())
+        if v:
+            self._status.zero_()
+            raise RuntimeError("fused all-reduce: rank %i did not see peer %i at the %s barrier of CTA %i within the time limit" % (
+                self.rank, (v >> 16) & 0xFF, "entry" if (v >> 24) == 1 else "exit", v & 0xFFFF))
+
+
+def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedAllReduce]:
+    """the fused reducer, or None if it cannot be used here"""
+    try:
+        if arena.device.type != "cuda" or arena.grad_dtype != torch.float32:
+            raise RuntimeError("needs a CUDA arena with fp32 gradients")
+        lib = _lib.get_lib()
+        if lib is None or not hasattr(lib, "rb200_fused_allreduce"):
+            raise RuntimeError("kernel library without the all-reduce entry point")
+        if os.environ.get("RETURNN_B200_FUSED_ALLREDUCE", "1") != "1":
+            raise RuntimeError("disabled by RETURNN_B200_FUSED_ALLREDUCE")
+        return FusedAllReduce(arena, rank=rank, world=world, group=group)
+    except Exception as exc:
+        if required:
+            raise
+        from ..log import log
+
+        print("Fused NVLink all-reduce not available (%s: %s), using torch.distributed." % (type(exc).__name__, exc), file=log.v3)
+        return None

@@ -15,6 +15,25 @@ import torch.distributed as dist
 from .arena import ParamArena
 
 
+_active: "Optional[BucketedGradReducer]" = None
+
+
+def get_active() -> "Optional[BucketedGradReducer]":
+    """the reducer of this process (there is at most one), for code that writes gradients without autograd hooks"""
+    return _active
+
+
+def notify_grads_written(tensors):
+    """
+    Tell the active reducer that the gradients of these parameters are complete. ``tensors`` are parameters, or views of the
+    gradient arena; used by ops that accumulate into the arena directly, where no post-accumulate-grad hook fires.
+    """
+    r = _active
+    if r is None:
+        return
+    r.mark_ready(tensors)
+
+
 class BucketedGradReducer:
     """drives per-bucket reductions from autograd hooks"""
 
@@ -32,6 +51,36 @@ class BucketedGradReducer:
         self._launched = [False] * len(arena.buckets)
         for s in arena.slots:
             self._handles.append(s.param.register_post_accumulate_grad_hook(self._make_hook(s.bucket)))
+        self._counted = set()
+        global _active
+        _active = self
+
+    def mark_ready(self, tensors):
+        """gradients written outside autograd: parameters (views of ``flat_param``) or gradient views (of ``flat_grad``)"""
+        if not self._enabled or self.world == 1:
+            return
+        a = self.arena
+        p0, g0 = a.flat_param.data_ptr(), a.flat_grad.data_ptr()
+        pe, ge = a.flat_param.element_size(), a.flat_grad.element_size()
+        if not hasattr(self, "_slot_by_offset"):
+            self._slot_by_offset = {s.offset: s for s in a.slots}
+        for t in tensors:
+            if t is None:
+                continue
+            addr = t.data_ptr()
+            if p0 <= addr < p0 + a.total * pe:
+                off = (addr - p0) // pe
+            elif g0 <= addr < g0 + a.total * ge:
+                off = (addr - g0) // ge
+            else:
+                continue
+            s = self._slot_by_offset.get(off)
+            if s is None or off in self._counted:
+                continue
+            self._counted.add(off)
+            self._pending[s.bucket] -= 1
+            if self._pending[s.bucket] == 0 and not self._launched[s.bucket]:
+                self._launch(s.bucket)
 
     def _make_hook(self, b: int):
         def hook(param):
@@ -52,6 +101,7 @@ class BucketedGradReducer:
         self._pending = list(self.arena.bucket_num_params)
         self._works = []
         self._launched = [False] * len(self.arena.buckets)
+        self._counted = set()
 
     def _launch(self, b: int):
         self._launched[b] = True
@@ -94,6 +144,9 @@ class BucketedGradReducer:
 
     def remove(self):
         """unregister hooks"""
+        global _active
         for h in self._handles:
             h.remove()
         self._handles = []
+        if _active is self:
+            _active = None

@@ -352,7 +352,7 @@ class Tensor:
 
     def copy_transpose(self, perm: Sequence[int]) -> "Tensor":
         """permute axes"""
-        perm = list(perm)
+        perm = [self.get_axis_from_description(a) if isinstance(a, Dim) else int(a) for a in perm]
         assert sorted(perm) == list(range(len(self._dims)))
         if perm == list(range(len(self._dims))):
             return self.copy()

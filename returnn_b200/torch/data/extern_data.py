@@ -54,9 +54,11 @@ def raw_dict_to_extern_data(extern_data_raw: Dict[str, Any], *, extern_data_temp
         assert isinstance(raw, torch.Tensor), "extern_data %r: expected torch.Tensor, got %r" % (k, type(raw))
         if extern_data_raw.get("%s:packed" % k):
             raise ValueError("extern_data %r is packed; use packed_tensors handling (rf.pack_import)" % k)
+        # copy first (asynchronous from pinned memory), convert on the device: a conversion on the host would leave
+        # pinned memory and make the copy a synchronising one
+        if str(raw.device) != str(device):
+            raw = raw.to(device, non_blocking=non_blocking)
         if data.dtype != dtype_name(raw.dtype):
-            if float_dtype and data.is_float() and raw.is_floating_point():
-                pass
             raw = raw.to(torch_dtype(data.dtype))
         if float_dtype and raw.is_floating_point() and dtype_name(raw.dtype) != float_dtype:
             raw = raw.to(torch_dtype(float_dtype))

@@ -545,10 +545,15 @@ class NumbersDict:
     def any_compare(self, other, cmp: Callable[[Any, Any], bool]) -> bool:
         """any(cmp(self[k], other[k]))"""
         for key in self.keys():
-            if key in other.keys() and cmp(self[key], other[key]):
-                return True
+            if key in other.keys():
+                if cmp(self[key], other[key]):
+                    return True
+            elif other.value is not None:
+                if cmp(self[key], other.value):
+                    return True
         if self.value is not None and other.value is not None:
-            return cmp(self.value, other.value)
+            if cmp(self.value, other.value):
+                return True
         return False
 
     @staticmethod

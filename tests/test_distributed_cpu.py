@@ -1,0 +1,157 @@
+"""
+Data-parallel logic on CPU with gloo, 2 ranks as child processes: the three reduce types give the documented results,
+the bucketed reducer handles gradients written outside autograd, and a rank that fails is detected by the others
+through a short process-group timeout (the failure is made on the host).
+"""
+
+import os
+import socket
+import sys
+import textwrap
+import subprocess
+import pytest
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _launch(body: str, tmp_path, world=2, timeout=300, expect_ok=True):
+    script = tmp_path / "worker.py"
+    script.write_text("import os, sys\nsys.path.insert(0, %r)\n" % _ROOT + textwrap.dedent(body))
+    port = _free_port()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), LOCAL_RANK=str(r), WORLD_SIZE=str(world), LOCAL_WORLD_SIZE=str(world),
+                   MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), CUDA_VISIBLE_DEVICES="")
+        procs.append(subprocess.Popen([sys.executable, str(script)], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=timeout)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+            out += "\n<killed by the test after %i s>" % timeout
+        outs.append((p.returncode, out))
+    if expect_ok:
+        for rc, out in outs:
+            assert rc == 0, out[-3000:]
+    return outs
+
+
+_COMMON = """
+import torch, torch.distributed as dist
+from returnn_b200.config import Config, set_global_config
+from returnn_b200.torch import distributed as rdist
+
+def make_ctx(opts):
+    cfg = Config({"torch_distributed": opts, "log_verbosity": 3})
+    set_global_config(cfg)
+    return rdist.get_ctx(cfg)
+
+def model():
+    torch.manual_seed(0)
+    return torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 4))
+"""
+
+
+@pytest.mark.parametrize("reduce_type", ["grad", "grad_explicit"])
+def test_grad_reduce_types_average_gradients(tmp_path, reduce_type):
+    outs = _launch(_COMMON + """
+ctx = make_ctx({"reduce_type": %r})
+rank, world = ctx.rank(), ctx.size()
+net = model()
+ctx.setup_grad_reduction(net)
+torch.manual_seed(100 + rank)
+x = torch.randn(5, 8)
+ctx.prepare_backward(sync=True)
+net(x).square().sum().backward()
+ctx.maybe_reduce_grads(net)
+mine = torch.cat([p.grad.reshape(-1) for p in net.parameters()])
+# reference: average of the two ranks' local gradients, recomputed here without any reduction
+ref = 0
+for r in range(world):
+    n2 = model()
+    torch.manual_seed(100 + r)
+    n2(torch.randn(5, 8)).square().sum().backward()
+    ref = ref + torch.cat([p.grad.reshape(-1) for p in n2.parameters()]) / world
+assert torch.allclose(mine, ref, atol=1e-6), (mine - ref).abs().max()
+print("OK", rank)
+dist.destroy_process_group()
+""" % reduce_type, tmp_path)
+    assert all("OK" in o for _, o in outs)
+
+
+def test_param_averaging(tmp_path):
+    outs = _launch(_COMMON + """
+ctx = make_ctx({"reduce_type": "param", "param_sync_step": 2})
+rank, world = ctx.rank(), ctx.size()
+net = model()
+ctx.setup_grad_reduction(net)
+with torch.no_grad():
+    for p in net.parameters():
+        p.add_(float(rank))
+assert not ctx.should_sync_now(epoch_step_idx=0) and ctx.should_sync_now(epoch_step_idx=1)
+ctx.step_after_param_update(module=net, epoch_step_idx=1)
+ref = model()
+for p, q in zip(net.parameters(), ref.parameters()):
+    assert torch.allclose(p, q + 0.5, atol=1e-6)
+print("OK", rank)
+dist.destroy_process_group()
+""", tmp_path)
+    assert all("OK" in o for _, o in outs)
+
+
+def test_reducer_with_gradients_written_outside_autograd(tmp_path):
+    outs = _launch(_COMMON + """
+from returnn_b200.parallel import grad_reducer
+ctx = make_ctx({"reduce_type": "grad", "bucket_cap_mb": 0})
+rank, world = ctx.rank(), ctx.size()
+net = model()
+ctx.setup_grad_reduction(net)
+arena = ctx.arena
+assert arena is not None and len(arena.buckets) >= 2
+ctx.prepare_backward(sync=True)
+# first layer through autograd, second layer's gradients written by hand into the arena and announced
+x = torch.randn(3, 8)
+h = net[1](net[0](x)).sum()
+h.backward()
+w2, b2 = net[2].weight, net[2].bias
+w2.grad.fill_(1.0 + rank)
+b2.grad.fill_(10.0 * (1 + rank))
+grad_reducer.notify_grads_written([w2, b2])
+ctx.maybe_reduce_grads(net)
+assert torch.allclose(w2.grad, torch.full_like(w2.grad, 1.5)), w2.grad
+assert torch.allclose(b2.grad, torch.full_like(b2.grad, 15.0))
+print("OK", rank)
+dist.destroy_process_group()
+""", tmp_path)
+    assert all("OK" in o for _, o in outs)
+
+
+def test_failed_rank_is_detected_by_timeout(tmp_path):
+    outs = _launch("""
+import datetime, time, torch, torch.distributed as dist
+rank = int(os.environ["RANK"])
+dist.init_process_group("gloo", timeout=datetime.timedelta(seconds=5))
+t = torch.ones(4)
+dist.all_reduce(t)
+if rank == 1:
+    print("rank 1 leaves between steps")
+    os._exit(3)
+try:
+    dist.all_reduce(t)
+    print("NO ERROR")
+except Exception as exc:
+    print("DETECTED", type(exc).__name__)
+""", tmp_path, expect_ok=False, timeout=120)
+    rc0, out0 = outs[0]
+    assert "DETECTED" in out0 and "NO ERROR" not in out0, out0
+    assert outs[1][0] == 3

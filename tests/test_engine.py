@@ -1,0 +1,113 @@
+"""
+Engine end to end on CPU through the public entry point: train the 12AX demo, resume from the checkpoint, forward with a
+callback; learning-rate control file; updater options (reference: returnn/torch/engine.py, learning_rate_control.py, torch/updater.py).
+"""
+
+import os
+import subprocess
+import sys
+import numpy
+import pytest
+import torch
+
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(args, cwd):
+    env = dict(os.environ, PYTHONPATH=_ROOT, CUDA_VISIBLE_DEVICES="")
+    p = subprocess.run([sys.executable, os.path.join(_ROOT, "rnn.py")] + args, cwd=cwd, env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stdout[-3000:] + "\n" + p.stderr[-3000:]
+    return p.stdout + p.stderr
+
+
+def test_train_resume_and_lr_file(tmp_path):
+    cfg = os.path.join(_ROOT, "demos", "demo-rf.config")
+    model = str(tmp_path / "model")
+    lr_file = str(tmp_path / "lr.txt")
+    common = [cfg, "++model", model, "++learning_rate_file", lr_file, "++device", "cpu", "++log_verbosity", "4",
+              "++train", "{'class': 'Task12AXDataset', 'num_seqs': 200}", "++dev", "{'class': 'Task12AXDataset', 'num_seqs': 40, 'fixed_random_seed': 1}"]
+    out1 = _run(common + ["++num_epochs", "2"], str(tmp_path))
+    assert os.path.exists(model + ".002.pt") and os.path.exists(model + ".002.opt.pt")
+    txt = open(lr_file).read()
+    assert "EpochData(learningRate=" in txt and "train_loss_ce" in txt and "dev_loss_ce" in txt
+    ck = torch.load(model + ".002.pt", map_location="cpu")
+    assert ck["epoch"] == 2 and "model" in ck and any(k.startswith("layers.0") for k in ck["model"])
+    step_after_2 = ck["step"]
+    out2 = _run(common + ["++num_epochs", "3"], str(tmp_path))
+    assert "epoch 3" in out2.lower() or "Epoch 3" in out2
+    assert os.path.exists(model + ".003.pt")
+    ck3 = torch.load(model + ".003.pt", map_location="cpu")
+    assert ck3["epoch"] == 3 and ck3["step"] > step_after_2
+    # the score history of epochs 1 and 2 survives the restart
+    from returnn_b200.learning_rate_control import load_learning_rate_control_from_config
+    from returnn_b200.config import Config
+
+    lrc = load_learning_rate_control_from_config(Config({"learning_rate_file": lr_file, "learning_rate": 0.01}))
+    assert set(lrc.epoch_data.keys()) >= {1, 2, 3}
+
+
+def test_newbob_decays_on_plateau(tmp_path):
+    from returnn_b200.learning_rate_control import load_learning_rate_control_from_config
+    from returnn_b200.config import Config
+
+    c = Config({"learning_rate": 1.0, "learning_rate_control": "newbob_abs", "newbob_learning_rate_decay": 0.5, "newbob_error_threshold": -0.1,
+                "learning_rate_control_relative_error_relative_lr": False})
+    lrc = load_learning_rate_control_from_config(c)
+    assert lrc.get_learning_rate_for_epoch(1) == 1.0
+    lrc.set_epoch_error(1, {"dev_loss": 2.0})
+    assert lrc.get_learning_rate_for_epoch(2) == 1.0
+    lrc.set_epoch_error(2, {"dev_loss": 1.0})  # improved by 1.0 > threshold: keep
+    assert lrc.get_learning_rate_for_epoch(3) == 1.0
+    lrc.set_epoch_error(3, {"dev_loss": 0.99})  # improved by less than the threshold: decay
+    assert lrc.get_learning_rate_for_epoch(4) == 0.5
+
+
+def test_updater_param_groups_and_dynamic_lr():
+    from returnn_b200.config import Config
+    from returnn_b200.torch.updater import Updater
+
+    net = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.LayerNorm(3))
+    seen = {}
+
+    def dyn_lr(*, global_train_step, epoch, learning_rate, **_kw):
+        seen["step"] = global_train_step
+        return learning_rate * 0.5
+
+    cfg = Config({"optimizer": {"class": "adamw", "weight_decay": 0.1, "epsilon": 1e-8}, "dynamic_learning_rate": dyn_lr,
+                  "gradient_clip_global_norm": 1.0})
+    up = Updater(config=cfg, network=net, device=torch.device("cpu"), initial_learning_rate=0.2)
+    up.create_optimizer()
+    opt = up.get_optimizer()
+    # biases and norm parameters carry no weight decay
+    decays = sorted(set(g["weight_decay"] for g in opt.param_groups))
+    assert decays == [0.0, 0.1]
+    up.set_current_train_step(global_train_step=7, epoch=1, epoch_continuous=0.5)
+    assert seen["step"] == 7 and abs(opt.param_groups[0]["lr"] - 0.1) < 1e-9
+    before = net[0].weight.detach().clone()
+    loss = (net(torch.randn(5, 4)) ** 2).sum() * 100
+    opt.zero_grad()
+    loss.backward()
+    up.step()
+    assert not torch.equal(before, net[0].weight)
+    assert float(up.get_last_grad_norm()) > 1.0  # the norm before clipping is what gets reported
+
+
+def test_fused_arena_adamw_matches_torch_adamw_on_cpu():
+    from returnn_b200.torch.optim.fused_adamw import FusedArenaAdamW
+
+    torch.manual_seed(0)
+    a = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 2))
+    b = torch.nn.Sequential(torch.nn.Linear(6, 5), torch.nn.Linear(5, 2))
+    b.load_state_dict(a.state_dict())
+    oa = FusedArenaAdamW(a, lr=1e-2, weight_decay=0.05)
+    ob = torch.optim.AdamW(b.parameters(), lr=1e-2, weight_decay=0.05)
+    for i in range(5):
+        x = torch.randn(7, 6)
+        for net, opt in ((a, oa), (b, ob)):
+            opt.zero_grad()
+            net(x).square().sum().backward()
+            opt.step()
+    for pa, pb in zip(a.parameters(), b.parameters()):
+        torch.testing.assert_close(pa, pb, atol=1e-6, rtol=1e-5)
+    sd = oa.state_dict()
+    assert set(sd["state"][0].keys()) >= {"exp_avg", "exp_avg_sq", "step"}
