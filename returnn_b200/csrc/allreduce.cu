@@ -96,29 +96,51 @@ fused_allreduce_kernel(const ArParams p) {
   const long long s1 = s0 + per < n4 ? s0 + per : n4;
   float ssq = 0.f;
   const long long stride = (long long)gridDim.x * kThreads;
-  for (long long i = s0 + (long long)blockIdx.x * kThreads + threadIdx.x; i < s1; i += stride) {
-    const long long e = p.lo + i * 4;
-    float4 acc;
+  // four float4 per thread and iteration: all loads of an iteration are issued before the first use, which keeps enough bytes
+  // in flight to cover the NVLink round trip
+  constexpr int U = 4;
+  for (long long i0 = s0 + (long long)blockIdx.x * kThreads + threadIdx.x; i0 < s1; i0 += U * stride) {
+    float4 acc[U];
     if (p.mc) {
-      acc = multimem_ld_reduce(p.mc + e);
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long i = i0 + u * stride;
+        if (i < s1) acc[u] = multimem_ld_reduce(p.mc + p.lo + i * 4);
+      }
     } else {
-      acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < U; ++u) acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 1
       for (int k = 0; k < p.world; ++k) {
         const int peer = (p.rank + k) % p.world;
-        const float4 v = *reinterpret_cast<const float4*>(p.bufs[peer] + e);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        float4 v[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long i = i0 + u * stride;
+          v[u] = i < s1 ? *reinterpret_cast<const float4*>(p.bufs[peer] + p.lo + i * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          acc[u].x += v[u].x; acc[u].y += v[u].y; acc[u].z += v[u].z; acc[u].w += v[u].w;
+        }
       }
     }
-    acc.x *= p.scale; acc.y *= p.scale; acc.z *= p.scale; acc.w *= p.scale;
-    ssq += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
-    if (p.mc) {
-      multimem_st(p.mc + e, acc);
-    } else {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= s1) break;
+      const long long e = p.lo + i * 4;
+      float4 a = acc[u];
+      a.x *= p.scale; a.y *= p.scale; a.z *= p.scale; a.w *= p.scale;
+      ssq += a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w;
+      if (p.mc) {
+        multimem_st(p.mc + e, a);
+      } else {
 #pragma unroll 1
-      for (int k = 0; k < p.world; ++k) {
-        const int peer = (p.rank + k) % p.world;
-        *reinterpret_cast<float4*>(p.bufs[peer] + e) = acc;
+        for (int k = 0; k < p.world; ++k) {
+          const int peer = (p.rank + k) % p.world;
+          *reinterpret_cast<float4*>(p.bufs[peer] + e) = a;
+        }
       }
     }
   }

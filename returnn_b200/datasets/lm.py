@@ -1,0 +1,365 @@
+"""
+Text datasets (reference: returnn/datasets/lm.py): :class:`LmDataset` (one sentence per line, optionally gzipped, turned
+into label sequences by a vocabulary / orthography symbols), :class:`TranslationDataset` (parallel source / target text
+files), :class:`Lexicon` (Bliss XML lexicon) and :class:`PhoneSeqGenerator`.
+"""
+
+from __future__ import annotations
+from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Union
+import gzip
+import os
+import xml.etree.ElementTree as ElementTree
+import numpy
+from .basic import DatasetSeq
+from .cached2 import CachedDataset2
+from .util.vocabulary import Vocabulary
+
+
+def _open_text(filename: str):
+    if filename.endswith(".gz"):
+        return gzip.open(filename, "rt", encoding="utf8")
+    return open(filename, "rt", encoding="utf8")
+
+
+def read_corpus(filename: str, skip_empty_lines: bool = True, decode: bool = True, out_list: Optional[List[str]] = None) -> List[str]:
+    """all lines of a text file (or the ``<orth>`` elements of a Bliss corpus XML)"""
+    out = out_list if out_list is not None else []
+    if filename.endswith(".xml") or filename.endswith(".xml.gz"):
+        iter_corpus(filename, skip_empty_lines=skip_empty_lines, callback=out.append)
+        return out
+    with _open_text(filename) as f:
+        for line in f:
+            line = line.rstrip("\n")
+            if skip_empty_lines and not line.strip():
+                continue
+            out.append(line)
+    return out
+
+
+def iter_corpus(filename: str, callback: Callable[[str], None], skip_empty_lines: bool = True, decode: bool = True):
+    """call ``callback(orth)`` for every sentence"""
+    if filename.endswith(".xml") or filename.endswith(".xml.gz"):
+        with (gzip.open(filename, "rb") if filename.endswith(".gz") else open(filename, "rb")) as f:
+            for _, elem in ElementTree.iterparse(f, events=("end",)):
+                if elem.tag == "orth":
+                    text = (elem.text or "").strip()
+                    if text or not skip_empty_lines:
+                        callback(text)
+                    elem.clear()
+        return
+    for line in read_corpus(filename, skip_empty_lines=skip_empty_lines):
+        callback(line)
+
+
+class LmDataset(CachedDataset2):
+    """
+    Language-model data: every line is one sequence; ``data`` are the label indices (with optional ``seq_end_symbol`` /
+    ``auto_replace_unknown_symbol``), ``delayed`` the same shifted right by ``delayed_seq_data_start_symbol``.
+    """
+
+    def __init__(self, corpus_file: Union[str, Sequence[str], Callable[[], Sequence[str]]], orth_vocab: Optional[Union[Dict[str, Any], Vocabulary]] = None,
+                 orth_symbols_file: Optional[str] = None, orth_symbols_map_file: Optional[str] = None, orth_replace_map_file: Optional[str] = None,
+                 word_based: bool = False, word_end_symbol: Optional[str] = None, seq_end_symbol: Optional[str] = "[END]",
+                 unknown_symbol: Optional[str] = "[UNKNOWN]", parse_orth_opts: Optional[Dict[str, Any]] = None, phone_info: Optional[Dict[str, Any]] = None,
+                 add_random_phone_seqs: int = 0, auto_replace_unknown_symbol: bool = False, log_auto_replace_unknown_symbols: int = 10,
+                 log_skipped_seqs: int = 10, error_on_invalid_seq: bool = True, add_delayed_seq_data: bool = False,
+                 delayed_seq_data_start_symbol: str = "[START]", dtype: Optional[str] = None, tag_prefix: Optional[str] = None, skip_empty_lines: bool = True,
+                 use_cache_manager: bool = False, **kwargs):
+        super().__init__(**kwargs)
+        if callable(corpus_file):
+            corpus_file = corpus_file()
+        self._corpus_files = [corpus_file] if isinstance(corpus_file, str) else list(corpus_file)
+        self.word_based = word_based
+        self.word_end_symbol = word_end_symbol
+        self.seq_end_symbol = seq_end_symbol
+        self.unknown_symbol = unknown_symbol
+        self.auto_replace_unknown_symbol = auto_replace_unknown_symbol
+        self.error_on_invalid_seq = error_on_invalid_seq
+        self.add_delayed_seq_data = add_delayed_seq_data
+        self.delayed_seq_data_start_symbol = delayed_seq_data_start_symbol
+        self.tag_prefix = tag_prefix or "line-"
+        self.orth_vocab: Optional[Vocabulary] = None
+        self.orth_symbols_map: Dict[str, int] = {}
+        if orth_vocab is not None:
+            self.orth_vocab = orth_vocab if isinstance(orth_vocab, Vocabulary) else Vocabulary.create_vocab(**orth_vocab)
+            num_labels = self.orth_vocab.num_labels
+            self.labels["data"] = list(self.orth_vocab.labels)
+        else:
+            if orth_symbols_map_file:
+                for line in read_corpus(orth_symbols_map_file):
+                    sym, idx = line.rsplit(None, 1)
+                    self.orth_symbols_map[sym] = int(idx)
+            elif orth_symbols_file:
+                for i, line in enumerate(read_corpus(orth_symbols_file)):
+                    self.orth_symbols_map[line.strip() if word_based else line.rstrip("\n")] = i
+            else:
+                raise ValueError("%s: need orth_vocab, orth_symbols_file or orth_symbols_map_file" % self)
+            num_labels = max(self.orth_symbols_map.values()) + 1
+            labels = [""] * num_labels
+            for s, i in self.orth_symbols_map.items():
+                labels[i] = s
+            self.labels["data"] = labels
+        if dtype is None:
+            dtype = "int32" if num_labels > 255 else "uint8"
+        self.dtype = dtype
+        self.num_inputs = num_labels
+        self.num_outputs = {"data": (num_labels, 1)}
+        if add_delayed_seq_data:
+            self.num_outputs["delayed"] = (num_labels, 1)
+            self.labels["delayed"] = self.labels["data"]
+        self.orths: List[str] = []
+        for fn in self._corpus_files:
+            read_corpus(fn, skip_empty_lines=skip_empty_lines, out_list=self.orths)
+        self._order: List[int] = []
+        self._num_unknown = 0
+
+    def get_data_keys(self):
+        return ["data"] + (["delayed"] if self.add_delayed_seq_data else [])
+
+    def get_target_list(self):
+        return ["delayed"] if self.add_delayed_seq_data else []
+
+    def get_data_dtype(self, key):
+        return self.dtype
+
+    def is_data_sparse(self, key):
+        return True
+
+    def get_data_dim(self, key):
+        return self.num_outputs[key][0]
+
+    def get_data_shape(self, key):
+        return []
+
+    def get_total_num_seqs(self, *, fast: bool = False) -> int:
+        return len(self.orths)
+
+    def get_all_tags(self):
+        return ["%s%i" % (self.tag_prefix, i) for i in range(len(self.orths))]
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        if seq_order is not None:
+            self._order = list(seq_order)
+        elif seq_list is not None:
+            self._order = [int(t[len(self.tag_prefix):]) for t in seq_list]
+        else:
+            self._order = list(self.get_seq_order_for_epoch(epoch=epoch, num_seqs=len(self.orths), get_seq_len=lambda i: len(self.orths[i])))
+        self._num_seqs = len(self._order)
+        return True
+
+    def supports_seq_order_sorting(self) -> bool:
+        return True
+
+    def get_current_seq_order(self):
+        return list(self._order)
+
+    @property
+    def num_seqs(self) -> int:
+        return self._num_seqs
+
+    def _encode(self, orth: str) -> Optional[List[int]]:
+        if self.orth_vocab is not None:
+            ids = list(self.orth_vocab.get_seq(orth))
+            if self.seq_end_symbol and self.seq_end_symbol in getattr(self.orth_vocab, "_vocab", {}):
+                ids.append(self.orth_vocab.label_to_id(self.seq_end_symbol))
+            return ids
+        syms = orth.split() if self.word_based else list(orth)
+        if self.word_end_symbol and not self.word_based:
+            syms = [self.word_end_symbol if s == " " else s for s in syms]
+        if self.seq_end_symbol:
+            syms.append(self.seq_end_symbol)
+        ids = []
+        for s in syms:
+            if s in self.orth_symbols_map:
+                ids.append(self.orth_symbols_map[s])
+            elif self.auto_replace_unknown_symbol and self.unknown_symbol in self.orth_symbols_map:
+                self._num_unknown += 1
+                ids.append(self.orth_symbols_map[self.unknown_symbol])
+            elif self.error_on_invalid_seq:
+                raise ValueError("%s: symbol %r of %r is not in the symbol table" % (self, s, orth))
+            else:
+                return None
+        return ids
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        while seq_idx < len(self._order):
+            line = self._order[seq_idx]
+            ids = self._encode(self.orths[line])
+            if ids is None:
+                # skipped sequences are replaced by an empty one to keep indices dense
+                ids = []
+            data = numpy.array(ids, dtype=self.dtype)
+            feats = {"data": data}
+            if self.add_delayed_seq_data:
+                start = self.orth_symbols_map.get(self.delayed_seq_data_start_symbol, 0) if self.orth_vocab is None else \
+                    self.orth_vocab.label_to_id(self.delayed_seq_data_start_symbol)
+                feats["delayed"] = numpy.concatenate([numpy.array([start], dtype=self.dtype), data[:-1]])
+            return DatasetSeq(seq_idx=seq_idx, seq_tag="%s%i" % (self.tag_prefix, line), features=feats)
+        return None
+
+
+class TranslationDataset(CachedDataset2):
+    """
+    Parallel text: ``<path>/source.<file_postfix>[.gz]`` and ``target.<file_postfix>[.gz]`` with one sentence per line and
+    vocabularies ``source.vocab.pkl`` / ``target.vocab.pkl`` (pickled ``{symbol: index}``); keys ``data`` and ``classes``.
+    """
+
+    source_file_prefix = "source"
+    target_file_prefix = "target"
+
+    def __init__(self, path: str, file_postfix: str, source_postfix: str = "", target_postfix: str = "", source_only: bool = False,
+                 search_without_reference: bool = False, unknown_label: Optional[Union[str, Dict[str, str]]] = None, seq_list_file: Optional[str] = None,
+                 use_cache_manager: bool = False, **kwargs):
+        super().__init__(**kwargs)
+        import pickle
+
+        self.path, self.file_postfix = path, file_postfix
+        self.source_only = source_only or search_without_reference
+        self._add = {"data": source_postfix, "classes": target_postfix}
+        self._keys = ["data"] if self.source_only else ["data", "classes"]
+        prefix = {"data": self.source_file_prefix, "classes": self.target_file_prefix}
+        self._vocabs: Dict[str, Dict[str, int]] = {}
+        self._lines: Dict[str, List[str]] = {}
+        self._unknown: Dict[str, Optional[str]] = {}
+        for k in self._keys:
+            vfile = os.path.join(path, "%s.vocab.pkl" % prefix[k])
+            self._vocabs[k] = pickle.load(open(vfile, "rb"))
+            fn = os.path.join(path, "%s.%s" % (prefix[k], file_postfix))
+            if not os.path.exists(fn) and os.path.exists(fn + ".gz"):
+                fn += ".gz"
+            self._lines[k] = read_corpus(fn, skip_empty_lines=False)
+            self._unknown[k] = unknown_label.get(k) if isinstance(unknown_label, dict) else unknown_label
+            inv = sorted(self._vocabs[k].items(), key=lambda kv: kv[1])
+            self.labels[k] = [s for s, _ in inv]
+        n = len(self._lines["data"])
+        assert all(len(v) == n for v in self._lines.values()), "%s: source and target differ in the number of lines" % self
+        self.num_outputs = {k: (max(self._vocabs[k].values()) + 1, 1) for k in self._keys}
+        self.num_inputs = self.num_outputs["data"][0]
+        self._order: List[int] = []
+
+    def _encode(self, key: str, line: str) -> numpy.ndarray:
+        words = line.split()
+        if self._add[key]:
+            words += self._add[key].split()
+        v = self._vocabs[key]
+        unk = self._unknown[key]
+        ids = []
+        for w in words:
+            if w in v:
+                ids.append(v[w])
+            elif unk is not None:
+                ids.append(v[unk])
+            else:
+                raise KeyError("%s: %r not in the %s vocabulary and no unknown_label given" % (self, w, key))
+        return numpy.array(ids, dtype="int32")
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        n = len(self._lines["data"])
+        if seq_order is not None:
+            self._order = list(seq_order)
+        elif seq_list is not None:
+            self._order = [int(t.split("-")[-1]) for t in seq_list]
+        else:
+            self._order = list(self.get_seq_order_for_epoch(epoch=epoch, num_seqs=n, get_seq_len=lambda i: len(self._lines["data"][i].split())))
+        self._num_seqs = len(self._order)
+        return True
+
+    def supports_seq_order_sorting(self) -> bool:
+        return True
+
+    @property
+    def num_seqs(self) -> int:
+        return self._num_seqs
+
+    def get_total_num_seqs(self, *, fast: bool = False) -> int:
+        return len(self._lines["data"])
+
+    def get_all_tags(self):
+        return ["line-%i" % i for i in range(len(self._lines["data"]))]
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        if seq_idx >= len(self._order):
+            return None
+        line = self._order[seq_idx]
+        return DatasetSeq(seq_idx=seq_idx, seq_tag="line-%i" % line, features={k: self._encode(k, self._lines[k][line]) for k in self._keys})
+
+    def get_data_keys(self):
+        return list(self._keys)
+
+    def get_target_list(self):
+        return [k for k in self._keys if k != "data"]
+
+    def get_data_dtype(self, key):
+        return "int32"
+
+    def is_data_sparse(self, key):
+        return True
+
+    def get_data_dim(self, key):
+        return self.num_outputs[key][0]
+
+    def get_data_shape(self, key):
+        return []
+
+
+class Lexicon:
+    """Bliss lexicon XML: phoneme inventory and ``orth -> [phoneme sequences]``"""
+
+    def __init__(self, filename: str):
+        self.filename = filename
+        self.phoneme_list: List[str] = []
+        self.phonemes: Dict[str, Dict[str, Any]] = {}
+        self.lemmas: Dict[str, Dict[str, Any]] = {}
+        opener = gzip.open if filename.endswith(".gz") else open
+        with opener(filename, "rb") as f:
+            root = ElementTree.parse(f).getroot()
+        for ph in root.iter("phoneme"):
+            sym = ph.findtext("symbol").strip()
+            var = (ph.findtext("variation") or "context").strip()
+            self.phonemes[sym] = {"index": len(self.phoneme_list), "symbol": sym, "variation": var}
+            self.phoneme_list.append(sym)
+        for lemma in root.iter("lemma"):
+            orths = [(o.text or "").strip() for o in lemma.findall("orth")]
+            phons = [{"phon": (p.text or "").strip(), "score": float(p.attrib.get("score", 0.0))} for p in lemma.findall("phon")]
+            for orth in orths:
+                self.lemmas[orth] = {"orth": orth, "phons": phons}
+
+
+class PhoneSeqGenerator:
+    """random pronunciations of word sequences from a lexicon, with optional silence between words"""
+
+    def __init__(self, lexicon_file: str, allo_num_states: int = 3, allo_context_len: int = 1, state_tying_file: Optional[str] = None,
+                 add_silence_beginning: float = 0.1, add_silence_between_words: float = 0.1, add_silence_end: float = 0.1,
+                 repetition: float = 0.9, silence_repetition: float = 0.95):
+        self.lexicon = Lexicon(lexicon_file)
+        self.phonemes = sorted(self.lexicon.phonemes.keys(), key=lambda s: self.lexicon.phonemes[s]["index"])
+        self.rnd = numpy.random.RandomState(0)
+        self.allo_num_states = allo_num_states
+        self.add_silence_beginning, self.add_silence_between_words, self.add_silence_end = add_silence_beginning, add_silence_between_words, add_silence_end
+        self.si_phone = "[SILENCE]" if "[SILENCE]" in self.lexicon.phonemes else "si"
+
+    def random_seed(self, seed: int):
+        """reseed"""
+        self.rnd.seed(seed)
+
+    def generate_seq(self, orth: str) -> List[str]:
+        """phoneme symbols for the sentence"""
+        out: List[str] = []
+        words = orth.split()
+        if self.rnd.random_sample() < self.add_silence_beginning:
+            out.append(self.si_phone)
+        for i, w in enumerate(words):
+            lemma = self.lexicon.lemmas[w]
+            phon = lemma["phons"][self.rnd.randint(0, len(lemma["phons"]))]["phon"]
+            out.extend(phon.split())
+            if i < len(words) - 1 and self.rnd.random_sample() < self.add_silence_between_words:
+                out.append(self.si_phone)
+        if self.rnd.random_sample() < self.add_silence_end:
+            out.append(self.si_phone)
+        return out
+
+    def seq_to_class_idxs(self, phones: Sequence[str], dtype: str = "int32") -> numpy.ndarray:
+        """phoneme indices"""
+        return numpy.array([self.lexicon.phonemes[p]["index"] for p in phones], dtype=dtype)

@@ -24,7 +24,7 @@ _vp, _i32, _i64, _f32, _u32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, 
 class FusedAllReduce:
     """bucket reductions on the arena's gradient buffer"""
 
-    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 64):
+    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128):
         import torch.distributed._symmetric_memory as symm_mem
 
         assert arena.grad_dtype == torch.float32

@@ -24,7 +24,10 @@ def _raw_dtype_str(raw) -> str:
 
     if isinstance(raw, torch.Tensor):
         return str(raw.dtype).split(".")[-1]
-    return str(numpy.asarray(raw).dtype)
+    dt = numpy.asarray(raw).dtype
+    if dt.kind in "US":
+        return "string"
+    return str(dt)
 
 
 class Tensor:

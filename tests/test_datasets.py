@@ -99,3 +99,88 @@ def test_vocabulary_roundtrip(tmp_path):
     ids = v.get_seq("a b c")
     assert ids == [2, 3, 4]
     assert v.get_seq_labels(ids) == "a b <unk>"
+
+
+def _read_all(ds, epoch=1, keys=("data",)):
+    ds.init_seq_order(epoch=epoch)
+    i, out = 0, []
+    while ds.is_less_than_num_seqs(i):
+        ds.load_seqs(i, i + 1)
+        out.append((ds.get_tag(i),) + tuple(ds.get_data(i, k) for k in keys))
+        i += 1
+    return out
+
+
+def test_meta_and_concat_datasets(tmp_path):
+    rng = numpy.random.RandomState(0)
+    mk = lambda n: [{"data": rng.randn(int(l), 3).astype("float32"), "classes": rng.randint(0, 5, (int(l),)).astype("int32")} for l in rng.randint(2, 9, n)]
+    a = {"class": "StaticDataset", "data": mk(6), "output_dim": {"data": (3, 2), "classes": (5, 1)}}
+    b = {"class": "StaticDataset", "data": mk(6), "output_dim": {"data": (3, 2), "classes": (5, 1)}}
+    meta = init_dataset({"class": "MetaDataset", "datasets": {"x": a, "y": b}, "data_map": {"data": ("x", "data"), "classes": ("y", "classes")},
+                         "seq_order_control_dataset": "x"})
+    seqs = _read_all(meta, keys=("data", "classes"))
+    assert len(seqs) == 6 and seqs[0][1].shape == a["data"][0]["data"].shape and numpy.array_equal(seqs[0][2], b["data"][0]["classes"])
+    assert len(_read_all(init_dataset({"class": "ConcatDataset", "datasets": [a, b]}))) == 12
+    comb = init_dataset({"class": "CombinedDataset", "datasets": {"x": a, "y": b},
+                         "data_map": {("x", "data"): "data", ("y", "data"): "data", ("x", "classes"): "classes"}, "seq_ordering": "random"})
+    got = _read_all(comb, keys=("data", "classes"))
+    assert len(got) == 12 and sum(1 for g in got if g[2].shape[0] == 0) == 6  # dataset y has no "classes": empty arrays
+    lst = tmp_path / "seqs.txt"
+    lst.write_text("seq-0;seq-1\nseq-2;seq-3;seq-4\n")
+    cs = _read_all(init_dataset({"class": "ConcatSeqsDataset", "dataset": a, "seq_list_file": str(lst)}))
+    assert [t for t, _ in cs] == ["seq-0;seq-1", "seq-2;seq-3;seq-4"]
+    assert cs[0][1].shape[0] == a["data"][0]["data"].shape[0] + a["data"][1]["data"].shape[0]
+
+
+def test_npz_writer_dataset_and_distribute_files(tmp_path):
+    from returnn_b200.datasets.hdf import SimpleHDFWriter
+
+    rng = numpy.random.RandomState(0)
+    files = []
+    for f in range(6):
+        fn = str(tmp_path / ("part%i.npz" % f))
+        files.append(fn)
+        with SimpleHDFWriter(fn, dim=2, extra_type={"classes": (5, 1, "int32")}) as w:
+            for i in range(3):
+                n = 2 + f
+                w.insert_seq(rng.randn(n, 2).astype("float32"), "f%i-s%i" % (f, i), extra={"classes": rng.randint(0, 5, (n,)).astype("int32")})
+    one = _read_all(init_dataset({"class": "NpzDataset", "files": files[:2], "seq_ordering": "sorted_reverse"}), keys=("data", "classes"))
+    assert len(one) == 6 and one[0][1].shape == (3, 2) and one[0][2].shape == (3,)
+    seen = {}
+    for rank in (0, 1):
+        ds = init_dataset({"class": "DistributeFilesDataset", "files": files, "get_sub_epoch_dataset": lambda fs: {"class": "NpzDataset", "files": fs},
+                           "partition_epoch": 3, "_distrib_info": {"rank": rank, "size": 2}})
+        for ep in (1, 2, 3):
+            for tag, _ in _read_all(ds, epoch=ep):
+                seen.setdefault(tag, []).append((rank, ep))
+    assert len(seen) == 18 and all(len(v) == 1 for v in seen.values())  # every sequence exactly once over ranks and sub-epochs
+
+
+def test_postprocessing_lm_and_text(tmp_path):
+    from returnn_b200.datasets.postprocessing import LaplaceOrdering
+
+    def double(td, **_kw):
+        td.data["data"].raw_tensor = td.data["data"].raw_tensor * 2
+        return td
+
+    ds = init_dataset({"class": "PostprocessingDataset", "dataset": {"class": "Task12AXDataset", "num_seqs": 10, "fixed_random_seed": 2},
+                       "map_seq": double, "map_seq_stream": LaplaceOrdering(4)})
+    seqs = _read_all(ds)
+    lens = [x.shape[0] for _, x in seqs]
+    assert len(lens) == 10 and lens[:4] == sorted(lens[:4]) and lens[4:8] == sorted(lens[4:8], reverse=True)
+    assert max(x.max() for _, x in seqs) == 2.0
+    corpus = tmp_path / "corpus.txt"
+    corpus.write_text("b a\nab\n\na b a b\n")
+    syms = tmp_path / "syms.txt"
+    syms.write_text("a\nb\n_\n[END]\n")
+    lm = init_dataset({"class": "LmDataset", "corpus_file": str(corpus), "orth_symbols_file": str(syms), "word_end_symbol": "_", "seq_ordering": "sorted"})
+    got = _read_all(lm)
+    assert [x.tolist() for _, x in got] == [[0, 1, 3], [1, 2, 0, 3], [0, 2, 1, 2, 0, 2, 1, 3]]
+
+
+def test_literal_parser_matches_ast():
+    import ast
+    from returnn_b200.utils.literal_py_to_pickle import literal_eval
+
+    txt = "{'a': [1, 2.5, -3, 12345678901234567890, True, None], \"b\\n\": ('x', 'y',), 'c': {'d': 'caf\\u00e9'}, # comment\n 'e': [],}"
+    assert literal_eval(txt) == ast.literal_eval(txt)
