@@ -1,0 +1,121 @@
+"""Sequence utility ops: CPU references against brute force, and the B200 kernels against the references."""
+
+import pytest
+import torch
+
+gpu = pytest.mark.gpu
+
+
+def _ed_data(dev):
+    g = torch.Generator().manual_seed(0)
+    a = torch.randint(0, 6, (9, 40), generator=g)
+    b = torch.randint(0, 6, (9, 70), generator=g)
+    al = torch.tensor([40, 1, 0, 17, 33, 5, 40, 2, 39])
+    bl = torch.tensor([70, 0, 3, 17, 64, 70, 1, 2, 33])
+    b[3, :17] = a[3, :17]
+    return a.to(dev), al, b.to(dev), bl
+
+
+def test_edit_distance_reference_known_cases():
+    from returnn_b200.ops import seq_ops
+
+    a = torch.tensor([[1, 2, 3, 4], [1, 2, 3, 4]])
+    b = torch.tensor([[1, 3, 4, 0], [5, 6, 7, 8]])
+    d = seq_ops.edit_distance(a, torch.tensor([4, 4]), b, torch.tensor([3, 4]))
+    assert d.tolist() == [1, 4]
+
+
+def test_rnnt_reference_matches_brute_force():
+    from returnn_b200.ops import seq_ops
+    import itertools, math
+
+    torch.manual_seed(0)
+    T, U = 3, 2
+    lp = torch.log_softmax(torch.randn(1, T, U + 1, 2), dim=-1)
+    loss = seq_ops.rnnt_loss(lp[..., 0], lp[..., 1], torch.tensor([T]), torch.tensor([U]))
+    # all monotonic paths: sequences of T blanks and U labels ending with a blank
+    total = -math.inf
+    for pos in itertools.combinations(range(T + U - 1), U):
+        t = u = 0
+        s = 0.0
+        for step in range(T + U - 1):
+            if step in pos:
+                s += float(lp[0, t, u, 1]); u += 1
+            else:
+                s += float(lp[0, t, u, 0]); t += 1
+        s += float(lp[0, T - 1, U, 0])
+        total = max(total, s) + math.log1p(math.exp(-abs(total - s))) if total > -math.inf else s
+    assert abs(float(loss) + total) < 1e-4
+
+
+def test_beam_topk_reference_finished_hyps():
+    from returnn_b200.ops import seq_ops
+
+    logits = torch.zeros(1, 2, 4)
+    logits[0, 0, 2] = 5.0
+    prev = torch.tensor([[0.0, -0.1]])
+    fin = torch.tensor([[False, True]])
+    s, back, lab = seq_ops.beam_topk(logits, prev, finished=fin, eos=3, k=2)
+    assert back.tolist() == [[0, 1]] and lab.tolist() == [[2, 3]] and abs(float(s[0, 1]) + 0.1) < 1e-6
+
+
+@gpu
+def test_edit_distance_kernel():
+    from returnn_b200.ops import seq_ops
+
+    a, al, b, bl = _ed_data("cuda")
+    got = seq_ops.edit_distance(a, al, b, bl)
+    ref = seq_ops.edit_distance_reference(a.cpu(), al, b.cpu(), bl)
+    assert got.cpu().tolist() == ref.tolist()
+
+
+@gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("k,beam,V", [(12, 12, 10001), (4, 1, 57), (32, 8, 1000)])
+def test_beam_topk_kernel(dtype, k, beam, V):
+    from returnn_b200.ops import seq_ops
+
+    torch.manual_seed(1)
+    logits = (torch.randn(5, beam, V, device="cuda") * 3).to(dtype)
+    prev = torch.randn(5, beam, device="cuda")
+    fin = torch.rand(5, beam, device="cuda") < 0.2
+    s, back, lab = seq_ops.beam_topk(logits, prev, finished=fin, eos=3, k=k)
+    rs, rback, rlab = seq_ops.beam_topk_reference(logits, prev, fin, 3, k)
+    torch.testing.assert_close(s, rs, atol=2e-3, rtol=1e-4)
+    # indices may differ only where scores tie
+    same = (back == rback) & (lab == rlab)
+    assert bool((same | ((s - rs).abs() < 2e-3)).all())
+    assert float(same.float().mean()) > 0.9
+
+
+@gpu
+def test_rnnt_kernel_loss_and_grad():
+    from returnn_b200.ops import seq_ops
+
+    torch.manual_seed(2)
+    B, T, U, V = 3, 11, 5, 7
+    joint = torch.randn(B, T, U + 1, V, device="cuda", requires_grad=True)
+    targets = torch.randint(1, V, (B, U), device="cuda")
+    t_lens, u_lens = torch.tensor([11, 7, 1]), torch.tensor([5, 2, 0])
+    loss = seq_ops.rnnt_loss_from_joint(joint, targets, t_lens, u_lens)
+    loss.sum().backward()
+    g = joint.grad.clone()
+    joint2 = joint.detach().cpu().requires_grad_(True)
+    ref = seq_ops.rnnt_loss_from_joint(joint2, targets.cpu(), t_lens, u_lens)
+    ref.sum().backward()
+    torch.testing.assert_close(loss.cpu(), ref, atol=1e-3, rtol=1e-4)
+    torch.testing.assert_close(g.cpu(), joint2.grad, atol=1e-3, rtol=1e-3)
+
+
+@gpu
+def test_device_assert_records_failure_without_trap():
+    from returnn_b200.ops import seq_ops
+
+    x = torch.arange(100, device="cuda")
+    seq_ops.device_assert(x >= 0, "all non-negative")
+    seq_ops.check_asserts()
+    seq_ops.device_assert(x != 37, "no 37 allowed")
+    with pytest.raises(AssertionError, match="no 37 allowed.*element 37"):
+        seq_ops.check_asserts()
+    # the context is still usable
+    assert int((x + 1).sum()) == 5050
