@@ -145,3 +145,29 @@ def test_softmax_ce(rows, v, dtype, smoothing):
     torch.testing.assert_close(loss, ref, atol=2e-3, rtol=1e-4)
     tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
     torch.testing.assert_close(logits.grad.float(), l32.grad, atol=tol, rtol=tol)
+
+
+@gpu
+def test_log_mel_kernel_matches_stft_path():
+    """fused log-mel kernel against the RF path (torch.fft) on the same audio"""
+    from returnn_b200.tensor import Tensor, Dim, batch_dim
+    import returnn_b200.frontend as rf
+    from returnn_b200.ops import logmel
+
+    torch.manual_seed(0)
+    audio = torch.randn(3, 16000, device="cuda") * 0.3 + torch.sin(torch.arange(16000, device="cuda") * 0.05)[None]
+    t = Dim(None, name="samples")
+    t.dyn_size_ext = Tensor("l", dims=[batch_dim], dtype="int32", raw_tensor=torch.tensor([16000, 16000, 16000], dtype=torch.int32))
+    x = Tensor("a", dims=[batch_dim, t], dtype="float32", raw_tensor=audio)
+    out_dim = Dim(80, name="mel")
+    got, _ = rf.audio.log_mel_filterbank_from_raw(x, in_spatial_dim=t, out_dim=out_dim)
+    import os
+
+    os.environ["RETURNN_B200_DISABLE_NATIVE"] = "1"
+    try:
+        x_cpu = Tensor("a", dims=[batch_dim, t], dtype="float32", raw_tensor=audio.cpu())
+        ref, _ = rf.audio.log_mel_filterbank_from_raw(x_cpu, in_spatial_dim=t, out_dim=out_dim)
+    finally:
+        del os.environ["RETURNN_B200_DISABLE_NATIVE"]
+    assert tuple(got.raw_tensor.shape) == tuple(ref.raw_tensor.shape) == (3, 98, 80)
+    torch.testing.assert_close(got.raw_tensor.cpu(), ref.raw_tensor, atol=2e-3, rtol=2e-3)
