@@ -15,6 +15,8 @@
 // Every wait is bounded (kSpinLimit polls with nanosleep, about two seconds): a CTA that gives up writes a status word and
 // skips its data phase; the context stays usable and the host raises an error.
 #include "common.cuh"
+#include "adamw.cuh"
+#include <cstring>
 
 namespace {
 
@@ -82,11 +84,17 @@ __device__ __forceinline__ void multimem_st(float* addr, float4 v) {
   asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
 }
 
+// With `adam` set (adam.p != null) the kernel first runs this rank's AdamW update over its whole parameter arena (p.bufs[rank] is
+// then the parameter arena, not the gradient arena), and only then averages: the entry barrier doubles as "every rank has
+// finished its update". This is the parameter-averaging mode (local steps, sync every N): update + average in one launch.
 __global__ void __launch_bounds__(kThreads)
-fused_allreduce_kernel(const ArParams p) {
+fused_allreduce_kernel(const ArParams p, const AdamwArgs adam) {
   __shared__ int sh_fail;
   __shared__ float sh_red[kThreads / 32];
   if (threadIdx.x == 0) sh_fail = 0;
+  if (adam.p != nullptr) {
+    adamw_update_range(adam, (int64_t)blockIdx.x * kThreads + threadIdx.x, (int64_t)gridDim.x * kThreads);
+  }
   if (!cta_barrier(p, p.epoch, &sh_fail, 1)) return;
 
   // slices of whole float4s; the tail (n % 4 elements) belongs to the last rank
@@ -199,8 +207,46 @@ RB_EXPORT int rb200_fused_allreduce(const long long* bufs, const long long* flag
   p.status = status;
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
-  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p);
+  AdamwArgs none;
+  memset(&none, 0, sizeof(none));
+  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p, none);
   return rb_check_launch("fused_allreduce");
+}
+
+// Parameter averaging fused with the optimizer update: AdamW on this rank's parameters (arguments as rb200_adamw_arena), then the
+// average over all ranks written to every rank. bufs: the parameter arenas (symmetric memory).
+RB_EXPORT int rb200_fused_adamw_param_avg(const long long* bufs, const long long* flags, const long long* norm, void* multicast, int world, int rank,
+                                          long long n, unsigned int epoch, int blocks, int* status, const void* g, float* m, float* v,
+                                          const uint8_t* wd_flags, int g_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
+                                          float bc2, int decoupled, float clip, const float* grad_norm, int do_update, cudaStream_t stream) {
+  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0) {
+    rb_set_error("fused_adamw_param_avg: world %d rank %d n %lld", world, rank, n);
+    return RB_ERR_ARG;
+  }
+  ArParams p;
+  for (int i = 0; i < kMaxWorld; ++i) {
+    p.bufs[i] = i < world ? reinterpret_cast<float*>(bufs[i]) : nullptr;
+    p.flags[i] = i < world ? reinterpret_cast<uint32_t*>(flags[i]) : nullptr;
+    p.norm[i] = i < world ? reinterpret_cast<float*>(norm[i]) : nullptr;
+  }
+  p.mc = reinterpret_cast<float*>(multicast);
+  p.world = world;
+  p.rank = rank;
+  p.lo = 0;
+  p.n = n;
+  p.scale = 1.f / (float)world;
+  p.epoch = epoch;
+  p.norm_slot = 7;  // unused accumulator slot
+  p.status = status;
+  AdamwArgs a;
+  memset(&a, 0, sizeof(a));
+  if (do_update) {
+    a = AdamwArgs{p.bufs[rank], g, m, v, wd_flags, (int64_t)n, g_bf16, lr, b1, b2, eps, wd, bc1, bc2, decoupled, clip, grad_norm, nullptr};
+  }
+  if (blocks < 1) blocks = 1;
+  if (blocks > kMaxBlocks) blocks = kMaxBlocks;
+  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p, a);
+  return rb_check_launch("fused_adamw_param_avg");
 }
 
 RB_EXPORT int rb200_fused_allreduce_flag_words() { return kMaxWorld * kMaxBlocks; }

@@ -147,6 +147,21 @@ class ParamArena:
             for s in self.slots:
                 s.param.grad = self.flat_grad[s.offset: s.offset + s.numel].view(s.shape)
 
+    def replace_param_buffer(self, new_flat: torch.Tensor):
+        """move the parameter arena into ``new_flat`` (e.g. symmetric memory) and re-point every ``param.data`` into it"""
+        assert new_flat.dtype == self.dtype and new_flat.numel() >= self.total and new_flat.device == self.device
+        new_flat = new_flat[: self.total]
+        with torch.no_grad():
+            new_flat.copy_(self.flat_param)
+            self.flat_param = new_flat
+            for s in self.slots:
+                s.param.data = self.flat_param[s.offset: s.offset + s.numel].view(s.shape)
+        self._shadow_version = -1
+
+    def invalidate_shadow(self):
+        """the fp32 weights were changed by a kernel that bypasses torch's version counter"""
+        self._shadow_version = -1
+
     def zero_grad(self):
         """one memset for all gradients"""
         self.flat_grad.zero_()

@@ -92,6 +92,96 @@ class FusedAllReduce:
                 self.rank, (v >> 16) & 0xFF, "entry" if (v >> 24) == 1 else "exit", v & 0xFFFF))
 
 
+class FusedParamAverager:
+    """
+    Parameter averaging (``reduce_type="param"``) over NVLink, optionally fused with the AdamW update of the sync step:
+    one kernel updates this rank's parameters, waits for all ranks and writes the average to everyone.
+    The parameter arena moves into symmetric memory.
+    """
+
+    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        assert arena.dtype == torch.float32
+        self.arena, self.rank, self.world, self.blocks = arena, rank, world, blocks
+        dev = arena.device
+        group = group or dist.group.WORLD
+        n = (arena.total + 3) // 4 * 4
+        self._param = symm_mem.empty(n, dtype=torch.float32, device=dev)
+        self._param.zero_()
+        self._hdl = symm_mem.rendezvous(self._param, group)
+        lib = _lib.get_lib(required=True)
+        lib.rb200_fused_allreduce_flag_words.restype = ctypes.c_int
+        self._flags = symm_mem.empty(int(lib.rb200_fused_allreduce_flag_words()), dtype=torch.int32, device=dev)
+        self._flags.zero_()
+        self._hdl_flags = symm_mem.rendezvous(self._flags, group)
+        self._norm = symm_mem.empty(8, dtype=torch.float32, device=dev)
+        self._norm.zero_()
+        self._hdl_norm = symm_mem.rendezvous(self._norm, group)
+        arena.replace_param_buffer(self._param)
+        self._bufs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        self._flag_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_flags.buffer_ptrs])
+        self._norm_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_norm.buffer_ptrs])
+        default_mc = "1" if world > 2 else "0"
+        use_mc = os.environ.get("RETURNN_B200_ALLREDUCE_MULTIMEM", default_mc) == "1"
+        self.multicast_ptr = int(getattr(self._hdl, "multicast_ptr", 0) or 0) if use_mc else 0
+        self._epoch = 1
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.pending = False  # set by the distributed context on sync steps; the optimizer then fuses its update with the average
+        _u8p = ctypes.c_void_p
+        self._fn = _lib.bind("rb200_fused_adamw_param_avg", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _u32, _i32, _vp, _vp, _vp, _vp, _u8p, _i32,
+                                                              _f32, _f32, _f32, _f32, _f32, _f32, _f32, _i32, _f32, _vp, _i32, _vp])
+        torch.cuda.synchronize(dev)
+        dist.barrier(group)
+
+    def average(self, adam: Optional[dict] = None):
+        """
+        Average the parameters over all ranks on the current stream. ``adam``: arguments of the fused AdamW kernel
+        (``g, m, v, wd_flags, lr, b1, b2, eps, wd, bc1, bc2, decoupled, clip, norm``) to run the update in the same launch.
+        """
+        a = adam or {}
+        g = a.get("g")
+        norm = a.get("norm")
+        _lib.check(self._fn(ctypes.addressof(self._bufs), ctypes.addressof(self._flag_ptrs), ctypes.addressof(self._norm_ptrs),
+                            self.multicast_ptr or None, self.world, self.rank, self.arena.total, self._epoch, self.blocks, self._status.data_ptr(),
+                            g.data_ptr() if g is not None else None, a["m"].data_ptr() if adam else None, a["v"].data_ptr() if adam else None,
+                            a["wd_flags"].data_ptr() if adam else None, 1 if (g is not None and g.dtype == torch.bfloat16) else 0,
+                            float(a.get("lr", 0.0)), float(a.get("b1", 0.0)), float(a.get("b2", 0.0)), float(a.get("eps", 0.0)), float(a.get("wd", 0.0)),
+                            float(a.get("bc1", 1.0)), float(a.get("bc2", 1.0)), 1 if a.get("decoupled", True) else 0, float(a.get("clip", 0.0)),
+                            norm.data_ptr() if norm is not None else None, 1 if adam else 0, _lib.stream_ptr()), "fused_adamw_param_avg")
+        _lib.count_launch()
+        self._epoch += 2
+        self.pending = False
+        self.arena.invalidate_shadow()
+
+    def check_status(self):
+        """raise if a barrier timed out (synchronises)"""
+        v = int(self._status.item())
+        if v:
+            self._status.zero_()
+            raise RuntimeError("fused parameter averaging: rank %i did not see peer %i in time" % (self.rank, (v >> 16) & 0xFF))
+
+
+def try_create_param_averager(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedParamAverager]:
+    """the fused averager, or None if it cannot be used here"""
+    try:
+        if arena.device.type != "cuda" or arena.dtype != torch.float32:
+            raise RuntimeError("needs a CUDA arena with fp32 parameters")
+        lib = _lib.get_lib()
+        if lib is None or not hasattr(lib, "rb200_fused_adamw_param_avg"):
+            raise RuntimeError("kernel library without the entry point")
+        if os.environ.get("RETURNN_B200_FUSED_ALLREDUCE", "1") != "1":
+            raise RuntimeError("disabled by RETURNN_B200_FUSED_ALLREDUCE")
+        return FusedParamAverager(arena, rank=rank, world=world, group=group)
+    except Exception as exc:
+        if required:
+            raise
+        from ..log import log
+
+        print("Fused parameter averaging not available (%s: %s), using torch.distributed." % (type(exc).__name__, exc), file=log.v3)
+        return None
+
+
 def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedAllReduce]:
     """the fused reducer, or None if it cannot be used here"""
     try:

@@ -70,6 +70,7 @@ class DistributedContext:
         self._reducer = None
         self._arena = None
         self._fused = None
+        self._param_averager = None
         self._step_after_param_update_module = None
         print("Torch distributed initialized. Hostname %s, pid %i, rank %i / size %i, local rank %s / local size %s, reduce_type %s." % (
             socket.gethostname(), os.getpid(), self._rank, self._size, self._local_rank, self._local_size, self._reduce_type), file=log.v3)
@@ -144,6 +145,14 @@ class DistributedContext:
         for b in module.buffers():
             if b.is_floating_point():
                 dist.broadcast(b.data, src=0)
+        if self._reduce_type == "param" and self._custom_class is None and self.want_fused(module_device(module)):
+            named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
+            if len({p.dtype for _, p in named}) == 1:
+                from ..parallel import fused_allreduce
+
+                self._arena = ParamArena(named, bucket_bytes=int(self._bucket_cap_mb) << 20)
+                self._param_averager = fused_allreduce.try_create_param_averager(self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt))
+            return
         if self._reduce_type not in ("grad", "grad_explicit") or self._custom_class is not None:
             return
         named = [(n, p) for n, p in module.named_parameters() if p.requires_grad]
@@ -222,9 +231,26 @@ class DistributedContext:
             return False
         return epoch_step_idx % self._param_sync_step == self._param_sync_step - 1
 
+    @property
+    def param_averager(self):
+        """the fused parameter averager (``reduce_type="param"`` on one NVLink node), if active"""
+        return self._param_averager
+
+    def before_param_update(self, *, epoch_step_idx: int):
+        """
+        Called before the optimizer step. On sync steps of the fused parameter-averaging mode this marks the averager as pending,
+        so that the arena optimizer runs its update inside the averaging kernel.
+        """
+        if self._param_averager is not None and self.should_sync_now(epoch_step_idx=epoch_step_idx):
+            self._param_averager.pending = True
+
     def step_after_param_update(self, *, module: torch.nn.Module, epoch_step_idx: int):
         """parameter averaging when due"""
         if self._reduce_type == "param" and self.should_sync_now(epoch_step_idx=epoch_step_idx):
+            if self._param_averager is not None:
+                if self._param_averager.pending:  # the optimizer did not fuse it (other optimizer class): average only
+                    self._param_averager.average(None)
+                return
             _sync_params_avg(module=module, sync_on_cpu=self._sync_on_cpu, ctx=self)
 
 

@@ -178,6 +178,9 @@ class Engine(EngineBase):
         if dist is not None and dist.arena is not None:
             self._updater.set_arena(dist.arena)
         self._updater.create_optimizer()
+        if dist is not None and dist.param_averager is not None:
+            # parameter-averaging mode over NVLink: the arena optimizer runs its update inside the averaging kernel on sync steps
+            self._updater.get_optimizer().param_averager = dist.param_averager
         if self._start_epoch > 1:
             self._load_optimizer()
         graph_opts = config.typed_value("torch_cuda_graph", None)
@@ -339,6 +342,8 @@ class Engine(EngineBase):
                             if norm_sq is not None:
                                 self._updater.set_precomputed_grad_norm_sq(norm_sq)
                     with _record("optimizer_step", self._nvtx):
+                        if dist:
+                            dist.before_param_update(epoch_step_idx=step_idx)
                         grad_norm = self._updater.step(grad_scaler=self._grad_scaler)
                     zero_grad_next_step = True
                     if dist:
@@ -446,6 +451,8 @@ class Engine(EngineBase):
             norm_sq = dist.maybe_reduce_grads(self._pt_model)
             if norm_sq is not None:
                 self._updater.set_precomputed_grad_norm_sq(norm_sq)
+        if dist:
+            dist.before_param_update(epoch_step_idx=self.global_train_step)
         self._updater.step(grad_scaler=self._grad_scaler)
         if dist:
             dist.step_after_param_update(module=self._pt_model, epoch_step_idx=self.global_train_step)

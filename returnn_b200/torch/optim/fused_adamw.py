@@ -97,6 +97,13 @@ class FusedArenaAdamW(torch.optim.Optimizer):
         if p.is_cuda:
             from ...ops import optim_native
 
+            avg = getattr(self, "param_averager", None)
+            if avg is not None and avg.pending:
+                # sync step of the parameter-averaging mode: update and average in one kernel over NVLink
+                avg.average(dict(g=g, m=m, v=v, wd_flags=self.wd_flags, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, bc1=bc1, bc2=bc2,
+                                 decoupled=self.decoupled, clip=self._clip if self._norm is not None else 0.0, norm=self._norm))
+                self._norm = None
+                return loss
             if optim_native.available():
                 optim_native.adamw_arena(p, g, m, v, self.wd_flags, lr=lr, b1=b1, b2=b2, eps=eps, wd=wd, bc1=bc1, bc2=bc2,
                                          decoupled=self.decoupled, clip=self._clip if self._norm is not None else 0.0, norm=self._norm,
