@@ -19,6 +19,7 @@
 // leave their loops, the CTA waits for its TMA copies in flight, frees its tensor memory and returns.
 #include "tcgen05.cuh"
 #include "gemm.h"
+#include <cstdlib>
 
 using namespace rbt;
 
@@ -469,7 +470,16 @@ int launch(const RbGemm& g, cudaStream_t stream) {
   if (st) return st;
   st = g.b_mn_major ? make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, 64, BK) : make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, BK, BN);
   if (st) return st;
-  const int grid = p.units < sms ? p.units : sms;
+  int grid = p.units < sms ? p.units : sms;
+  {
+    // tuning knob: cap the number of CTAs (for bandwidth / latency experiments)
+    static int cap = -1;
+    if (cap < 0) {
+      const char* e = getenv("RETURNN_B200_GEMM_MAX_CTAS");
+      cap = e ? atoi(e) : 0;
+    }
+    if (cap > 0 && grid > cap) grid = cap;
+  }
   gemm_persist_kernel<BN><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
   return rb_check_launch("gemm_persist");
 }

@@ -108,6 +108,33 @@ def frontend_subsample(enc, feats: torch.Tensor, lens_host: torch.Tensor, W: _We
     return out, lens.to(torch.int32)
 
 
+def _frontend_native(enc, feats: torch.Tensor, lens_host: torch.Tensor):
+    """conv subsampling through the implicit-GEMM kernels; (None, None) if the configuration is not covered"""
+    from ..ops import frontend_native as _fe
+    from .packing import host_to_device
+
+    il = enc.input_layer
+    if not _fe.available(feats):
+        return None, None
+    convs = list(il.conv_layers)
+    chans = tuple(c.out_dim.dimension for c in convs)
+    fsz = [tuple(d.dimension for d in c.filter_size) for c in convs]
+    strides = [tuple(s) for s in il._strides2]
+    if any(c.padding != "same" for c in convs) or not _fe.supports(feats.shape[-1], chans, fsz, strides, il.pool_sizes):
+        return None, None
+    if convs[0].in_dim.dimension != 1:
+        return None, None
+    lens0 = lens_host.clone().to(torch.int64)
+    lens1 = -(-lens0 // strides[1][0])
+    lens2 = -(-lens1 // strides[2][0])
+    # the padded lengths of the intermediate tensors follow the padded input length, like the torch path
+    pack = PackInfo(lens2.to(torch.int32), feats.device)
+    lens_dev = host_to_device(torch.stack([lens0, lens1, lens2]).to(torch.int32), feats.device)
+    params = [(c.filter.raw_tensor, c.bias.raw_tensor if c.bias is not None else None) for c in convs]
+    x = _fe.conv_subsample_packed(feats.to(torch.bfloat16), lens_dev, pack, params, (strides[1][0], strides[2][0]))
+    return x, pack
+
+
 def ffn_block(x, layer_norm, ff, W, p_drop, training, eps):
     """0.5 * dropout(FFN(LN(x))) + x"""
     h = _ln.layer_norm(x, W(layer_norm.scale), W(layer_norm.bias), eps)
@@ -212,9 +239,13 @@ def encode_packed(enc, feats: torch.Tensor, lens_host: torch.Tensor, *, training
     from . import conformer_native as _native
 
     W = _Weights(compute_dtype)
-    x_pad, lens2 = frontend_subsample(enc, feats.to(compute_dtype), lens_host, W)
-    pack = PackInfo(lens2, feats.device, padded_len=x_pad.shape[1])
-    x = pack.pack(x_pad)
+    x = None
+    if compute_dtype == torch.bfloat16 and feats.is_cuda:
+        x, pack = _frontend_native(enc, feats, lens_host)
+    if x is None:
+        x_pad, lens2 = frontend_subsample(enc, feats.to(compute_dtype), lens_host, W)
+        pack = PackInfo(lens2, feats.device, padded_len=x_pad.shape[1])
+        x = pack.pack(x_pad)
     plan = None
     if training and torch.is_grad_enabled() and compute_dtype == torch.bfloat16 and collected is None and x.is_cuda:
         plan = _native.get_plan(enc)
