@@ -38,3 +38,7 @@ struct RbGemm {
 
 // returns an RB_* status code; the launch is asynchronous on `stream`
 int rb_gemm(const RbGemm& g, cudaStream_t stream);
+
+// CTA-pair kernel (gemm_2cta.cu): rb_gemm routes to it when rb_gemm_pair_wanted says so
+bool rb_gemm_pair_wanted(const RbGemm& g);
+int rb_gemm_pair(const RbGemm& g, cudaStream_t stream);

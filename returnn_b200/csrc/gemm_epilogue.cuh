@@ -1,0 +1,251 @@
+// Epilogue and work-unit decoding shared by the persistent tcgen05 GEMM kernels (one-CTA and CTA-pair variants).
+#pragma once
+#include "tcgen05.cuh"
+#include "gemm.h"
+
+namespace rbg {
+
+using namespace rbt;
+
+constexpr int BK = 64;
+
+struct Params {
+  RbGemm g;
+  int tiles_m, tiles_n, split, kb_per_split, num_kb, units;
+  int vec_ok;    // all epilogue pointers 16-byte aligned and ldc % 8 == 0
+  int bias_vec;  // fp32 bias, 16-byte aligned: read as two float4
+};
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ float act_grad(float z, int act) {
+  if (act == 1) return z > 0.f ? 1.f : 0.f;
+  if (act == 2) {
+    float s = 1.f / (1.f + __expf(-z));
+    return s * (1.f + z * (1.f - s));
+  }
+  if (act == 3) {
+    float cdf = 0.5f * (1.f + erff(z * 0.70710678118654752f));
+    float pdf = __expf(-0.5f * z * z) * 0.3989422804014327f;
+    return cdf + z * pdf;
+  }
+  return 1.f;
+}
+
+__device__ __forceinline__ void load8_bf16(const void* base, size_t off, bool vec, int nvalid, float* out) {
+  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(base) + off;
+  if (vec) {
+    uint4 u = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float2 f = __bfloat1622float2(h[i]);
+      out[2 * i] = f.x;
+      out[2 * i + 1] = f.y;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out[i] = i < nvalid ? __bfloat162float(p[i]) : 0.f;
+  }
+}
+
+__device__ __forceinline__ void store8_bf16(void* base, size_t off, bool vec, int nvalid, const float* v) {
+  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(base) + off;
+  if (vec) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = u;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nvalid) p[i] = __float2bfloat16(v[i]);
+  }
+}
+
+// one lane's share of the epilogue: 8 consecutive columns [col, col+8) of one output row.
+// FULL = false compiles the common case only (scale, bias, activation, store): no activation gradient, dropout or residual,
+// which keeps the instruction stream of the epilogue warps short.
+template <bool FULL>
+__device__ __forceinline__ void epilogue_group(const Params& p, int row, int col, int n_extent, size_t c_off, float* v) {
+  const RbGemm& g = p.g;
+  const int nvalid = min(8, n_extent - col);
+  const bool vec = p.vec_ok && nvalid == 8 && (c_off & 7) == 0;
+  const size_t off = c_off + (size_t)row * g.ldc + col;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] *= g.alpha;
+  if (g.bias && p.bias_vec && nvalid == 8) {
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.bias) + col));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.bias) + col) + 1);
+    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+  } else if (g.bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i < nvalid) {
+        v[i] += g.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g.bias)[col + i])
+                            : __ldg(reinterpret_cast<const float*>(g.bias) + col + i);
+      }
+    }
+  }
+  float pre[8];
+  if (FULL && g.dact_z) {
+    float z[8];
+    load8_bf16(g.dact_z, off, vec, nvalid, z);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], g.act);
+  } else if (g.act) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      pre[i] = v[i];
+      v[i] = apply_act(v[i], g.act);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pre[i] = v[i];
+  }
+  if (FULL && g.drop_p > 0.f) {
+    const uint64_t sd = (uint64_t)g.seed[0];
+    const uint64_t c = (uint64_t)g.offset[0] + g.drop_site + (uint64_t)off;
+    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
+    uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
+    uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
+    const uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    const float scale = 1.f / (1.f - g.drop_p);
+    const uint32_t thresh = (uint32_t)(g.drop_p * 4294967296.0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = r[i] >= thresh ? v[i] * scale : 0.f;
+  }
+  if (FULL && g.resid) {
+    float rs[8];
+    load8_bf16(g.resid, off, vec, nvalid, rs);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = rs[i] + g.res_scale * v[i];
+  }
+  if (g.out_fp32) {
+    float* c = reinterpret_cast<float*>(g.c) + off;
+    if (g.accumulate == 2) {
+      if (vec) {
+        atomicAdd(reinterpret_cast<float4*>(c), make_float4(v[0], v[1], v[2], v[3]));
+        atomicAdd(reinterpret_cast<float4*>(c) + 1, make_float4(v[4], v[5], v[6], v[7]));
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (i < nvalid) atomicAdd(c + i, v[i]);
+      }
+    } else if (vec) {
+      float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
+      if (g.accumulate == 1) {
+        float4 oa = reinterpret_cast<float4*>(c)[0], ob = reinterpret_cast<float4*>(c)[1];
+        a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+        b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
+      }
+      reinterpret_cast<float4*>(c)[0] = a;
+      reinterpret_cast<float4*>(c)[1] = b;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < nvalid) c[i] = g.accumulate == 1 ? c[i] + v[i] : v[i];
+    }
+  } else if (g.c2) {
+    store8_bf16(g.c, off, vec, nvalid, pre);
+    store8_bf16(g.c2, off, vec, nvalid, v);
+  } else {
+    store8_bf16(g.c, off, vec, nvalid, v);
+  }
+}
+
+// one work unit: output tile (m0, n0) of problem z, K blocks [kb0, kb1)
+struct Unit {
+  int m0, n0, kb0, kb1, M, N;
+  int a_r0, a_c0, b_r0, b_c0;
+  size_t c_off;
+  bool valid;
+};
+
+template <int BM, int BN>
+__device__ __forceinline__ Unit decode_unit(const Params& p, int u) {
+  const RbGemm& g = p.g;
+  Unit w;
+  const int tiles = p.tiles_m * p.tiles_n;
+  if (g.batch > 0) {
+    const int z = u / tiles, t = u % tiles;
+    const int zb = z / g.heads, zh = z % g.heads;
+    const int len = g.lens ? g.lens[zb] : 0;
+    w.M = g.m_from_lens ? len : g.m;
+    w.N = g.n_from_lens ? len : g.n;
+    const int K = g.k_from_lens ? len : g.k;
+    w.m0 = (t / p.tiles_n) * BM;
+    w.n0 = (t % p.tiles_n) * BN;
+    w.kb0 = 0;
+    w.kb1 = K > 0 ? (K + BK - 1) / BK : 0;
+    w.a_r0 = (int)(zb * g.a_rb + zh * g.a_rh); w.a_c0 = (int)(zb * g.a_cb + zh * g.a_ch);
+    w.b_r0 = (int)(zb * g.b_rb + zh * g.b_rh); w.b_c0 = (int)(zb * g.b_cb + zh * g.b_ch);
+    w.c_off = (size_t)zb * g.c_sb + (size_t)zh * g.c_sh;
+    w.valid = w.m0 < w.M && w.n0 < w.N && w.kb1 > 0;
+  } else {
+    const int sp = u / tiles, t = u % tiles;
+    w.M = g.m; w.N = g.n;
+    w.m0 = (t / p.tiles_n) * BM;
+    w.n0 = (t % p.tiles_n) * BN;
+    w.kb0 = sp * p.kb_per_split;
+    w.kb1 = min(p.num_kb, w.kb0 + p.kb_per_split);
+    w.a_r0 = w.a_c0 = w.b_r0 = w.b_c0 = 0;
+    w.c_off = 0;
+    w.valid = true;
+  }
+  return w;
+}
+
+// Epilogue of the accumulator columns [c_begin, c_end) of one 128-row tile by one warp (TMEM lane quarter q), in chunks of 16
+// columns: tcgen05.ld -> registers -> this warp's 2 KB staging area (fp32 rows of 64 bytes, 16-byte chunk index xor-swizzled with
+// the row so that neither direction has bank conflicts) -> every lane owns 8 consecutive columns of one row -> epilogue_group.
+// `arrive` is called by lane 0 once the warp's last read of the accumulator has completed (hands the TMEM buffer back to the
+// MMA issuer). Many narrow warps rather than few wide ones: the epilogue is latency-bound per warp (measured about 6 stall
+// cycles per issued instruction), so its throughput scales with the number of warps the schedulers can switch between.
+template <bool FULL, typename Arrive>
+__device__ __forceinline__ void epilogue_columns(const Params& p, const Unit& w, int m0, int n0, uint32_t t_addr, int c_begin, int c_end, float* stg,
+                                                 int lane, int q, Arrive arrive) {
+#pragma unroll 1
+  for (int c0 = c_begin; c0 < c_end; c0 += 16) {
+    uint32_t r[16];
+    tmem_ld16(t_addr + (uint32_t)c0, r);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (c0 + 16 >= c_end) {
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) arrive();
+    }
+    float4* srow = reinterpret_cast<float4*>(stg + lane * 16);
+    const int sw = (lane >> 1) & 3;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      srow[j ^ sw] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]), __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+    }
+    __syncwarp();
+    const int cg = lane & 1;
+    const int col = n0 + c0 + cg * 8;
+#pragma unroll
+    for (int itr = 0; itr < 2; ++itr) {
+      const int rl = itr * 16 + (lane >> 1);
+      const int row = m0 + q * 32 + rl;
+      const float4* rrow = reinterpret_cast<const float4*>(stg + rl * 16);
+      const int sr = (rl >> 1) & 3;
+      const float4 a = rrow[(2 * cg) ^ sr], b = rrow[(2 * cg + 1) ^ sr];
+      if (row < w.M && col < w.N) {
+        float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        epilogue_group<FULL>(p, row, col, w.N, w.c_off, v);
+      }
+    }
+    __syncwarp();
+  }
+}
+
+constexpr int kEpilogueWarps = 16;                        // four per TMEM lane quarter: each takes a quarter of the tile's columns
+constexpr int kGemmThreads = 64 + kEpilogueWarps * 32;    // + TMA producer warp + MMA warp
+constexpr int kStagingBytesPerWarp = 32 * 16 * 4;
+
+}  // namespace rbg

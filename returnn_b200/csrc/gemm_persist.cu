@@ -17,205 +17,23 @@
 //
 // Every mbarrier wait is bounded. A wait that gives up raises the CTA's abort flag and writes a status word; all roles
 // leave their loops, the CTA waits for its TMA copies in flight, frees its tensor memory and returns.
-#include "tcgen05.cuh"
-#include "gemm.h"
+#include "gemm_epilogue.cuh"
 #include <cstdlib>
 
 using namespace rbt;
+using namespace rbg;
 
 namespace {
 
-constexpr int BM = 128, BK = 64;
-constexpr int kThreads = 192;
+constexpr int BM = 128;
+constexpr int kThreads = kGemmThreads;
 constexpr int kRingBytes = 196608;      // operand ring: 4 stages (BN = 256) or 6 stages (BN = 128)
-constexpr int kStagingBytes = 4 * 8192;  // 4 epilogue warps x 32 rows x 64 fp32
+constexpr int kStagingBytes = kEpilogueWarps * kStagingBytesPerWarp;
 constexpr int kBarrierBytes = 256;
 constexpr int kSmemBytes = kRingBytes + kStagingBytes + kBarrierBytes + 1024;
 constexpr int kMaxStages = 6;
 
-struct Params {
-  RbGemm g;
-  int tiles_m, tiles_n, split, kb_per_split, num_kb, units;
-  int vec_ok;  // all epilogue pointers 16-byte aligned and ldc % 8 == 0
-};
-
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-
-__device__ __forceinline__ float act_grad(float z, int act) {
-  if (act == 1) return z > 0.f ? 1.f : 0.f;
-  if (act == 2) {
-    float s = 1.f / (1.f + __expf(-z));
-    return s * (1.f + z * (1.f - s));
-  }
-  if (act == 3) {
-    float cdf = 0.5f * (1.f + erff(z * 0.70710678118654752f));
-    float pdf = __expf(-0.5f * z * z) * 0.3989422804014327f;
-    return cdf + z * pdf;
-  }
-  return 1.f;
-}
-
-__device__ __forceinline__ void load8_bf16(const void* base, size_t off, bool vec, int nvalid, float* out) {
-  const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(base) + off;
-  if (vec) {
-    uint4 u = *reinterpret_cast<const uint4*>(p);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      float2 f = __bfloat1622float2(h[i]);
-      out[2 * i] = f.x;
-      out[2 * i + 1] = f.y;
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) out[i] = i < nvalid ? __bfloat162float(p[i]) : 0.f;
-  }
-}
-
-__device__ __forceinline__ void store8_bf16(void* base, size_t off, bool vec, int nvalid, const float* v) {
-  __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(base) + off;
-  if (vec) {
-    uint4 u;
-    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-    *reinterpret_cast<uint4*>(p) = u;
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-      if (i < nvalid) p[i] = __float2bfloat16(v[i]);
-  }
-}
-
-// one lane's share of the epilogue: 8 consecutive columns [col, col+8) of one output row
-__device__ __forceinline__ void epilogue_group(const Params& p, int row, int col, int n_extent, size_t c_off, float* v) {
-  const RbGemm& g = p.g;
-  const int nvalid = min(8, n_extent - col);
-  const bool vec = p.vec_ok && nvalid == 8 && (c_off & 7) == 0;
-  const size_t off = c_off + (size_t)row * g.ldc + col;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) v[i] *= g.alpha;
-  if (g.bias) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (i < nvalid) {
-        v[i] += g.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g.bias)[col + i])
-                            : __ldg(reinterpret_cast<const float*>(g.bias) + col + i);
-      }
-    }
-  }
-  float pre[8];
-  if (g.dact_z) {
-    float z[8];
-    load8_bf16(g.dact_z, off, vec, nvalid, z);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], g.act);
-  } else if (g.act) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      pre[i] = v[i];
-      v[i] = apply_act(v[i], g.act);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) pre[i] = v[i];
-  }
-  if (g.drop_p > 0.f) {
-    const uint64_t sd = (uint64_t)g.seed[0];
-    const uint64_t c = (uint64_t)g.offset[0] + g.drop_site + (uint64_t)off;
-    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
-    uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-    uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-    const uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    const float scale = 1.f / (1.f - g.drop_p);
-    const uint32_t thresh = (uint32_t)(g.drop_p * 4294967296.0);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = r[i] >= thresh ? v[i] * scale : 0.f;
-  }
-  if (g.resid) {
-    float rs[8];
-    load8_bf16(g.resid, off, vec, nvalid, rs);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = rs[i] + g.res_scale * v[i];
-  }
-  if (g.out_fp32) {
-    float* c = reinterpret_cast<float*>(g.c) + off;
-    if (g.accumulate == 2) {
-      if (vec) {
-        atomicAdd(reinterpret_cast<float4*>(c), make_float4(v[0], v[1], v[2], v[3]));
-        atomicAdd(reinterpret_cast<float4*>(c) + 1, make_float4(v[4], v[5], v[6], v[7]));
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (i < nvalid) atomicAdd(c + i, v[i]);
-      }
-    } else if (vec) {
-      float4 a = make_float4(v[0], v[1], v[2], v[3]), b = make_float4(v[4], v[5], v[6], v[7]);
-      if (g.accumulate == 1) {
-        float4 oa = reinterpret_cast<float4*>(c)[0], ob = reinterpret_cast<float4*>(c)[1];
-        a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
-        b.x += ob.x; b.y += ob.y; b.z += ob.z; b.w += ob.w;
-      }
-      reinterpret_cast<float4*>(c)[0] = a;
-      reinterpret_cast<float4*>(c)[1] = b;
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (i < nvalid) c[i] = g.accumulate == 1 ? c[i] + v[i] : v[i];
-    }
-  } else if (g.c2) {
-    store8_bf16(g.c, off, vec, nvalid, pre);
-    store8_bf16(g.c2, off, vec, nvalid, v);
-  } else {
-    store8_bf16(g.c, off, vec, nvalid, v);
-  }
-}
-
-// one work unit: output tile (m0, n0) of problem z, K blocks [kb0, kb1)
-struct Unit {
-  int m0, n0, kb0, kb1, M, N;
-  int a_r0, a_c0, b_r0, b_c0;
-  size_t c_off;
-  bool valid;
-};
-
-template <int BN>
-__device__ __forceinline__ Unit decode_unit(const Params& p, int u) {
-  const RbGemm& g = p.g;
-  Unit w;
-  const int tiles = p.tiles_m * p.tiles_n;
-  if (g.batch > 0) {
-    const int z = u / tiles, t = u % tiles;
-    const int zb = z / g.heads, zh = z % g.heads;
-    const int len = g.lens ? g.lens[zb] : 0;
-    w.M = g.m_from_lens ? len : g.m;
-    w.N = g.n_from_lens ? len : g.n;
-    const int K = g.k_from_lens ? len : g.k;
-    w.m0 = (t / p.tiles_n) * BM;
-    w.n0 = (t % p.tiles_n) * BN;
-    w.kb0 = 0;
-    w.kb1 = K > 0 ? (K + BK - 1) / BK : 0;
-    w.a_r0 = (int)(zb * g.a_rb + zh * g.a_rh); w.a_c0 = (int)(zb * g.a_cb + zh * g.a_ch);
-    w.b_r0 = (int)(zb * g.b_rb + zh * g.b_rh); w.b_c0 = (int)(zb * g.b_cb + zh * g.b_ch);
-    w.c_off = (size_t)zb * g.c_sb + (size_t)zh * g.c_sh;
-    w.valid = w.m0 < w.M && w.n0 < w.N && w.kb1 > 0;
-  } else {
-    const int sp = u / tiles, t = u % tiles;
-    w.M = g.m; w.N = g.n;
-    w.m0 = (t / p.tiles_n) * BM;
-    w.n0 = (t % p.tiles_n) * BN;
-    w.kb0 = sp * p.kb_per_split;
-    w.kb1 = min(p.num_kb, w.kb0 + p.kb_per_split);
-    w.a_r0 = w.a_c0 = w.b_r0 = w.b_c0 = 0;
-    w.c_off = 0;
-    w.valid = true;
-  }
-  return w;
-}
-
-template <int BN>
+template <int BN, bool FULL>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
   constexpr int kTileBytesA = BM * BK * 2;
@@ -246,7 +64,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[i], kEpilogueWarps);  // one arrival per epilogue warp
     }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -265,7 +83,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t it = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        const Unit w = decode_unit<BN>(p, u);
+        const Unit w = decode_unit<BM, BN>(p, u);
         if (!w.valid) continue;
         const int m0 = w.m0, n0 = w.n0;
         for (int kb = w.kb0; kb < w.kb1; ++kb, ++it) {
@@ -304,7 +122,7 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       uint32_t it = 0, t_local = 0;
       bool ok = true;
       for (int u = blockIdx.x; u < p.units && ok; u += gridDim.x) {
-        const Unit w = decode_unit<BN>(p, u);
+        const Unit w = decode_unit<BM, BN>(p, u);
         if (!w.valid) continue;
         const int kb0 = w.kb0, kb1 = w.kb1;
         const uint32_t buf = t_local & 1u;
@@ -344,10 +162,10 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else {
     // ---------------- epilogue: warps 2..5, TMEM lane quarter = warp % 4 ----------------
     const int q = warp & 3;
-    float* stg = staging + (warp - 2) * (8192 / 4);
+    float* stg = staging + (warp - 2) * (kStagingBytesPerWarp / 4);
     uint32_t t_local = 0;
     for (int u = blockIdx.x; u < p.units; u += gridDim.x) {
-      const Unit w = decode_unit<BN>(p, u);
+      const Unit w = decode_unit<BM, BN>(p, u);
       if (!w.valid) continue;
       const int m0 = w.m0, n0 = w.n0;
       const uint32_t buf = t_local & 1u;
@@ -360,43 +178,8 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 64) {
-        uint32_t r0[32], r1[32];
-        tmem_ld32(t_addr + (uint32_t)c0, r0);
-        tmem_ld32(t_addr + (uint32_t)c0 + 32u, r1);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (c0 + 64 >= BN) {
-          // all of this warp's reads of the accumulator are done: hand the buffer back to the MMA issuer
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&acc_empty[buf]);
-        }
-        // stage: row = lane, 16 chunks of 4 floats, chunk index xor-swizzled with the row
-        float4* srow = reinterpret_cast<float4*>(stg + lane * 64);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          srow[j ^ (lane & 7)] = make_float4(__uint_as_float(r0[4 * j]), __uint_as_float(r0[4 * j + 1]), __uint_as_float(r0[4 * j + 2]),
-                                             __uint_as_float(r0[4 * j + 3]));
-          srow[(8 + j) ^ (lane & 7)] = make_float4(__uint_as_float(r1[4 * j]), __uint_as_float(r1[4 * j + 1]),
-                                                   __uint_as_float(r1[4 * j + 2]), __uint_as_float(r1[4 * j + 3]));
-        }
-        __syncwarp();
-        const int cg = lane & 7;
-        const int col = n0 + c0 + cg * 8;
-#pragma unroll 2
-        for (int itr = 0; itr < 8; ++itr) {
-          const int rl = itr * 4 + (lane >> 3);
-          const int row = m0 + q * 32 + rl;
-          const float4* rrow = reinterpret_cast<const float4*>(stg + rl * 64);
-          float4 a = rrow[(2 * cg) ^ (rl & 7)], b = rrow[(2 * cg + 1) ^ (rl & 7)];
-          if (row < w.M && col < w.N) {
-            float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-            epilogue_group(p, row, col, w.N, w.c_off, v);
-          }
-        }
-        __syncwarp();
-      }
+      const int part = (warp - 2) >> 2;  // four warps per lane quarter, each with a quarter of the columns
+      epilogue_columns<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), (part + 1) * (BN / 4), stg, lane, q, [&]() { mbar_arrive(&acc_empty[buf]); });
       ++t_local;
     }
   }
@@ -429,7 +212,8 @@ template <int BN>
 int launch(const RbGemm& g, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_persist_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(gemm_persist_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_persist_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) {
       rb_set_error("gemm: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
       return RB_ERR_LAUNCH;
@@ -459,6 +243,8 @@ int launch(const RbGemm& g, cudaStream_t stream) {
   }
   auto al16 = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
   p.vec_ok = (g.ldc % 8 == 0) && al16(g.c) && al16(g.c2) && al16(g.resid) && al16(g.dact_z);
+  p.bias_vec = g.bias != nullptr && !g.bias_bf16 && al16(g.bias);
+  const bool full = g.dact_z != nullptr || g.drop_p > 0.f || g.resid != nullptr;
   CUtensorMap tm_a, tm_b;
   int st;
   long long a_rows = g.a_mn_major ? g.k : g.m, a_cols = g.a_mn_major ? g.m : g.k;
@@ -480,7 +266,8 @@ int launch(const RbGemm& g, cudaStream_t stream) {
     }
     if (cap > 0 && grid > cap) grid = cap;
   }
-  gemm_persist_kernel<BN><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
+  if (full) gemm_persist_kernel<BN, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
+  else gemm_persist_kernel<BN, false><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
   return rb_check_launch("gemm_persist");
 }
 
@@ -516,6 +303,7 @@ int rb_gemm(const RbGemm& g, cudaStream_t stream) {
     rb_set_error("gemm: split_k needs accumulate == 2");
     return RB_ERR_ARG;
   }
+  if (rb_gemm_pair_wanted(g)) return rb_gemm_pair(g, stream);
   if (g.n > 128) return launch<256>(g, stream);
   return launch<128>(g, stream);
 }
