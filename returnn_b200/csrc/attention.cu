@@ -12,6 +12,9 @@
 
 namespace {
 
+__device__ __forceinline__ float score_f(float x) { return x; }
+__device__ __forceinline__ float score_f(__nv_bfloat16 x) { return __bfloat162float(x); }
+
 constexpr int kMaxPerLane = 16;  // 32 lanes * 16 = 512 keys
 
 __global__ void __launch_bounds__(256)
@@ -56,8 +59,9 @@ __device__ __forceinline__ uint32_t rng_u32(uint64_t seed, uint64_t idx) {
 }
 
 // grid: (ceil(Lp / warps_per_cta), B*H); one warp per query row
+template <typename TS>
 __global__ void __launch_bounds__(128)
-att_softmax_fwd_kernel(const float* __restrict__ s_ac, const float* __restrict__ g, __nv_bfloat16* __restrict__ w,
+att_softmax_fwd_kernel(const TS* __restrict__ s_ac, const TS* __restrict__ g, __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ wd, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
   const int lane = threadIdx.x & 31;
@@ -74,7 +78,7 @@ att_softmax_fwd_kernel(const float* __restrict__ s_ac, const float* __restrict__
   for (int t = 0; t < kMaxPerLane; ++t) {
     const int j = lane + 32 * t;
     if (j < len) {
-      x[t] = s_ac[srow + j] + g[grow + (j - i + center)];
+      x[t] = score_f(s_ac[srow + j]) + score_f(g[grow + (j - i + center)]);
       mx = fmaxf(mx, x[t]);
     } else {
       x[t] = -INFINITY;
@@ -108,8 +112,9 @@ att_softmax_fwd_kernel(const float* __restrict__ s_ac, const float* __restrict__
   }
 }
 
+template <typename TS>
 __global__ void __launch_bounds__(128)
-att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const float* __restrict__ dwd, __nv_bfloat16* __restrict__ ds,
+att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const TS* __restrict__ dwd, __nv_bfloat16* __restrict__ ds,
                        __nv_bfloat16* __restrict__ dg, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
   const int lane = threadIdx.x & 31;
@@ -132,7 +137,7 @@ att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const float* __restr
     const int j = lane + 32 * t;
     if (j < len) {
       pw[t] = __bfloat162float(w[srow + j]);
-      float d = dwd[srow + j];
+      float d = score_f(dwd[srow + j]);
       if (drop) d = (rng_u32(sd, off + (uint64_t)(srow + j)) >= thresh) ? d * keep_scale : 0.f;
       dw[t] = d;
       delta += pw[t] * d;
@@ -232,25 +237,44 @@ RB_EXPORT int rb200_att_prepare(const void* qkv, const float* u, const float* v,
   return rb_check_launch("att_prepare");
 }
 
-RB_EXPORT int rb200_att_softmax_fwd(const float* s_ac, const float* g, void* w, void* wd, const int* lens, int batch, int heads, int lp,
-                                    int rp, int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
+// scores_bf16: s_ac and g are bf16 (what the batched GEMMs write on the training path) instead of fp32
+RB_EXPORT int rb200_att_softmax_fwd_ex(const void* s_ac, const void* g, int scores_bf16, void* w, void* wd, const int* lens, int batch, int heads,
+                                       int lp, int rp, int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
   if (lp > 32 * kMaxPerLane) {
     rb_set_error("att_softmax: padded length %d > %d", lp, 32 * kMaxPerLane);
     return RB_ERR_UNSUPPORTED;
   }
   dim3 grid((lp + 3) / 4, batch * heads);
-  att_softmax_fwd_kernel<<<grid, 128, 0, stream>>>(s_ac, g, (__nv_bfloat16*)w, (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop,
+  if (scores_bf16)
+    att_softmax_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)s_ac, (const __nv_bfloat16*)g, (__nv_bfloat16*)w,
+                                                                    (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
+  else
+  att_softmax_fwd_kernel<float><<<grid, 128, 0, stream>>>((const float*)s_ac, (const float*)g, (__nv_bfloat16*)w, (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop,
                                                    seed, offset);
   return rb_check_launch("att_softmax_fwd");
 }
 
-RB_EXPORT int rb200_att_softmax_bwd(const void* w, const float* dwd, void* ds, void* dg, const int* lens, int batch, int heads, int lp, int rp,
-                                    int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
+RB_EXPORT int rb200_att_softmax_bwd_ex(const void* w, const void* dwd, int dwd_bf16, void* ds, void* dg, const int* lens, int batch, int heads, int lp,
+                                       int rp, int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
   if (lp > 32 * kMaxPerLane) return RB_ERR_UNSUPPORTED;
   dim3 grid((lp + 3) / 4, batch * heads);
-  att_softmax_bwd_kernel<<<grid, 128, 0, stream>>>((const __nv_bfloat16*)w, dwd, (__nv_bfloat16*)ds, (__nv_bfloat16*)dg, lens, batch, heads, lp,
-                                                   rp, center, p_drop, seed, offset);
+  if (dwd_bf16)
+    att_softmax_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)w, (const __nv_bfloat16*)dwd, (__nv_bfloat16*)ds,
+                                                                    (__nv_bfloat16*)dg, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
+  else
+    att_softmax_bwd_kernel<float><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)w, (const float*)dwd, (__nv_bfloat16*)ds, (__nv_bfloat16*)dg, lens,
+                                                            batch, heads, lp, rp, center, p_drop, seed, offset);
   return rb_check_launch("att_softmax_bwd");
+}
+
+RB_EXPORT int rb200_att_softmax_fwd(const float* s_ac, const float* g, void* w, void* wd, const int* lens, int batch, int heads, int lp, int rp,
+                                    int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
+  return rb200_att_softmax_fwd_ex(s_ac, g, 0, w, wd, lens, batch, heads, lp, rp, center, p_drop, seed, offset, stream);
+}
+
+RB_EXPORT int rb200_att_softmax_bwd(const void* w, const float* dwd, void* ds, void* dg, const int* lens, int batch, int heads, int lp, int rp,
+                                    int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
+  return rb200_att_softmax_bwd_ex(w, dwd, 0, ds, dg, lens, batch, heads, lp, rp, center, p_drop, seed, offset, stream);
 }
 
 RB_EXPORT int rb200_att_redrop(const void* w, void* wd, const int* lens, int batch, int heads, int lp, float p_drop, const long long* seed,

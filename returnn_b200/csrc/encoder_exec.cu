@@ -28,10 +28,10 @@ int rb200_gemm_bf16_batched(const void* a, const void* b, void* c, const void* b
                             int m_from_lens, int n_from_lens, int k_from_lens, int* status, cudaStream_t stream);
 int rb200_att_prepare(const void* qkv, const float* u, const float* v, const int* row_batch, const int* row_pos, void* qu, void* qv, void* k,
                       void* vv, int n_rows, int heads, int dim, int lp, cudaStream_t stream);
-int rb200_att_softmax_fwd(const float* s_ac, const float* g, void* w, void* wd, const int* lens, int batch, int heads, int lp, int rp,
-                          int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream);
-int rb200_att_softmax_bwd(const void* w, const float* dwd, void* ds, void* dg, const int* lens, int batch, int heads, int lp, int rp,
-                          int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream);
+int rb200_att_softmax_fwd_ex(const void* s_ac, const void* g, int scores_bf16, void* w, void* wd, const int* lens, int batch, int heads, int lp, int rp,
+                             int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream);
+int rb200_att_softmax_bwd_ex(const void* w, const void* dwd, int dwd_bf16, void* ds, void* dg, const int* lens, int batch, int heads, int lp, int rp,
+                             int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream);
 int rb200_att_redrop(const void* w, void* wd, const int* lens, int batch, int heads, int lp, float p_drop, const long long* seed,
                      const long long* offset, cudaStream_t stream);
 int rb200_att_pack_dqkv(const void* dqu, const void* dqv, const void* dk, const void* dv, const int* row_batch, const int* row_pos, void* dqkv,
@@ -470,10 +470,11 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
     if (e.ok()) e.run(rb200_att_prepare(t.qkv, e.p32(l, P_POS_U), e.p32(l, P_POS_V), row_batch, row_pos, sv.qu, sv.qv, sv.kk, sv.vv, n, H, Dh, Lp, stream));
     {
       const long long o1[10] = {Lp, 0, 0, Dh, Lp, 0, 0, Dh, (long long)H * Lp * Lp, (long long)Lp * Lp};
+      // scores and bias band in bf16, like the matmul outputs of the reference under autocast: halves the traffic of this stage
       e.bgemm(sv.qu, sv.kk, t.s_ac, Lp, Lp, Dh, 0, 0, HD, HD, Lp, (long long)B * Lp, HD, (long long)B * Lp, HD, o1, B * H, H, lens, 1, 1, 0,
-              d.att_scale, 1);
+              d.att_scale, 0);
       const long long o2[10] = {Lp, 0, 0, Dh, 0, 0, 0, Dh, (long long)Lp * Rp, (long long)B * Lp * Rp};
-      e.bgemm(sv.qv, sv.posp, t.band, Lp, g.R, Dh, 0, 0, HD, HD, Rp, (long long)B * Lp, HD, g.R, HD, o2, B * H, H, lens, 1, 0, 0, d.att_scale, 1);
+      e.bgemm(sv.qv, sv.posp, t.band, Lp, g.R, Dh, 0, 0, HD, HD, Rp, (long long)B * Lp, HD, g.R, HD, o2, B * H, H, lens, 1, 0, 0, d.att_scale, 0);
     }
     e.memset0(sv.w, g.score_elems * sizeof(bf16));
     bf16* wd = sv.w;
@@ -481,7 +482,7 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
       e.memset0(t.wd, g.score_elems * sizeof(bf16));
       wd = t.wd;
     }
-    if (e.ok()) e.run(rb200_att_softmax_fwd(t.s_ac, t.band, sv.w, wd, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
+    if (e.ok()) e.run(rb200_att_softmax_fwd_ex(t.s_ac, t.band, 1, sv.w, wd, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
     {
       const long long o3[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};
       e.bgemm(wd, sv.vv, t.o_pad, Lp, Dh, Lp, 0, 1, Lp, HD, HD, (long long)B * H * Lp, Lp, (long long)B * Lp, HD, o3, B * H, H, lens, 1, 0, 1, 1.f, 0);
@@ -586,13 +587,13 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
     }
     {
       const long long o4[10] = {Lp, 0, 0, Dh, Lp, 0, 0, Dh, (long long)H * Lp * Lp, (long long)Lp * Lp};
-      e.bgemm(t.do_pad, sv.vv, t.dwd, Lp, Lp, Dh, 0, 0, HD, HD, Lp, (long long)B * Lp, HD, (long long)B * Lp, HD, o4, B * H, H, lens, 1, 1, 0, 1.f, 1);
+      e.bgemm(t.do_pad, sv.vv, t.dwd, Lp, Lp, Dh, 0, 0, HD, HD, Lp, (long long)B * Lp, HD, (long long)B * Lp, HD, o4, B * H, H, lens, 1, 1, 0, 1.f, 0);
       const long long o5[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};
       e.bgemm(wd, t.do_pad, t.dv, Lp, Dh, Lp, 1, 1, Lp, HD, HD, (long long)B * H * Lp, Lp, (long long)B * Lp, HD, o5, B * H, H, lens, 1, 0, 1, 1.f, 0);
     }
     e.memset0(t.ds, g.score_elems * sizeof(bf16));
     e.memset0(t.dband, g.band_elems * sizeof(bf16));
-    if (e.ok()) e.run(rb200_att_softmax_bwd(sv.w, t.dwd, t.ds, t.dband, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
+    if (e.ok()) e.run(rb200_att_softmax_bwd_ex(sv.w, t.dwd, 1, t.ds, t.dband, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
     e.memset0(t.dqu, 2 * g.pad_rows * HD * sizeof(bf16));  // dqu, dqv: their column sums run over all padded rows
     {
       const long long o6[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};

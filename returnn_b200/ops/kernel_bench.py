@@ -1,0 +1,162 @@
+"""
+Micro-benchmarks of the non-GEMM kernels at the shapes of the flagship Conformer step (packed rows n ~ 6.7k, D = 512):
+
+    python -m returnn_b200.ops.kernel_bench [--only NAME] [--iters K] [--rows N]
+
+For every op: device time of forward and of forward+backward (CUDA events around ``iters`` calls, a spin kernel in front so
+that the host has queued everything before the first event), the algorithmic bytes it has to move, and the achieved
+fraction of the measured HBM copy bandwidth (``MEASURED_PEAKS.json`` next to the repository root if present, else the
+fallback 6650 GB/s). One JSON line per op. Used for the kernel summaries under ``profiles/`` (also as the small workload
+for ``ncu`` captures: ``--only NAME --iters 2``).
+"""
+
+from __future__ import annotations
+import argparse
+import json
+import os
+import torch
+
+
+def _peak_gbs() -> float:
+    fn = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "MEASURED_PEAKS.json")
+    try:
+        return float(json.load(open(fn))["hbm_gbs"])
+    except Exception:
+        return 6650.0
+
+
+def _time(fn, iters: int) -> float:
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda._sleep(int(2e7))
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rows", type=int, default=6656)
+    ap.add_argument("--iters", type=int, default=30)
+    ap.add_argument("--only", default=None)
+    args = ap.parse_args()
+    dev = torch.device("cuda")
+    n, D, F = args.rows, 512, 2048
+    peak = _peak_gbs()
+    bf = torch.bfloat16
+    from . import layer_norm as ln, elementwise as ew, conv_module as cm, ctc as ctc_op, attention_packed as att, softmax_ce as ce, logmel, seq_ops
+    from ..models.packing import PackInfo
+
+    torch.manual_seed(0)
+    lens = torch.randint(60, 334, (64,))
+    while int(lens.sum()) > n:
+        lens = lens[:-1]
+    lens[-1] += n - int(lens.sum())
+    pack = PackInfo(lens.to(torch.int32), dev)
+    n = pack.n
+    results = []
+
+    def report(name, t_fwd, t_fb, bytes_fwd, bytes_fb, extra=None):
+        r = {"op": name, "fwd_us": round(t_fwd * 1e6, 1), "fwd_bwd_us": round(t_fb * 1e6, 1) if t_fb else None,
+             "fwd_gbs": round(bytes_fwd / t_fwd / 1e9, 1), "fwd_frac_of_measured_hbm": round(bytes_fwd / t_fwd / 1e9 / peak, 3)}
+        if t_fb:
+            r["fwd_bwd_gbs"] = round(bytes_fb / t_fb / 1e9, 1)
+            r["fwd_bwd_frac_of_measured_hbm"] = round(bytes_fb / t_fb / 1e9 / peak, 3)
+        if extra:
+            r.update(extra)
+        results.append(r)
+        print(json.dumps(r), flush=True)
+
+    def want(name):
+        return args.only is None or args.only == name
+
+    if want("layer_norm"):
+        x = torch.randn(n, D, device=dev, dtype=bf, requires_grad=True)
+        g = torch.ones(D, device=dev, requires_grad=True)
+        b = torch.zeros(D, device=dev, requires_grad=True)
+        dy = torch.randn(n, D, device=dev, dtype=bf)
+        fwd = lambda: ln.layer_norm(x, g, b, 1e-6)
+        def fb():
+            y = ln.layer_norm(x, g, b, 1e-6)
+            y.backward(dy)
+        report("layer_norm", _time(fwd, args.iters), _time(fb, args.iters), 2 * n * D * 2, (2 + 3) * n * D * 2)
+    if want("dropout"):
+        x = torch.randn(n, F, device=dev, dtype=bf)
+        report("dropout", _time(lambda: ew.dropout(x, 0.1), args.iters), None, 2 * n * F * 2, 0)
+    if want("conv_module"):
+        from ..tensor import Dim
+        from .. import frontend as rf
+
+        bn = rf.BatchNorm(Dim(D, name="c"), use_mask=True)
+        for p in bn.parameters():
+            p.raw_tensor = p.raw_tensor.to(dev) if p.raw_tensor is not None else None
+        for name in ("running_mean", "running_variance"):
+            t = getattr(bn, name)
+            t.raw_tensor = t.raw_tensor.to(dev)
+        x = torch.randn(n, 2 * D, device=dev, dtype=bf, requires_grad=True)
+        filt = (torch.randn(D, 1, 32, device=dev) * 0.1).requires_grad_(True)
+        bias = torch.zeros(D, device=dev, requires_grad=True)
+        dy = torch.randn(n, D, device=dev, dtype=bf)
+        fwd = lambda: cm.glu_dwconv_bn_silu(x, filt, bias, bn, pack, training=True)
+        def fb():
+            cm.glu_dwconv_bn_silu(x, filt, bias, bn, pack, training=True).backward(dy)
+        # fwd: read [n,2D], write y and z [n,D] each, re-read y;  bwd: read y, dz, x, ds; write ds, dx
+        report("conv_module (GLU+dwconv32+BN+SiLU)", _time(fwd, args.iters), _time(fb, args.iters), (2 + 1 + 1 + 1) * n * D * 2,
+               (5 + 1 + 1 + 1 + 1 + 2 + 1 + 2) * n * D * 2)
+    if want("rel_pos_attention"):
+        H, Dh = 8, 64
+        qkv = (torch.randn(n, 3 * H * Dh, device=dev) * 0.3).to(bf).requires_grad_(True)
+        L = pack.max_len
+        pos = (torch.randn(2 * L - 1, H * Dh, device=dev) * 0.3).to(bf).requires_grad_(True)
+        u = torch.zeros(H, Dh, device=dev, requires_grad=True)
+        v = torch.zeros(H, Dh, device=dev, requires_grad=True)
+        dy = torch.randn(n, H * Dh, device=dev, dtype=bf)
+        fwd = lambda: att.rel_pos_attention_packed(qkv, pos, u, v, pack, num_heads=H, head_dim=Dh, scale=Dh ** -0.5, dropout_p=0.1)
+        def fb():
+            fwd().backward(dy)
+        lp = (L + 63) // 64 * 64
+        score_bytes = pack.batch * H * lp * lp
+        flops = 4.0 * H * Dh * float((lens.double() ** 2).sum()) * 2  # QK^T + bias band + PV, valid part only
+        # fwd traffic: scores fp32 write+read, band fp32 (2x wide) write+read, probabilities bf16 write (+dropped copy) + read
+        report("rel_pos_attention (packed, 8x64)", _time(fwd, args.iters), _time(fb, args.iters), score_bytes * (8 + 16 + 6) + 5 * n * H * Dh * 2,
+               score_bytes * (8 + 16 + 6) * 3, {"fwd_tflops_valid": round(flops / 1e12 / 1.0, 4)})
+    if want("ctc"):
+        V = 10001
+        logits = torch.randn(n, V, device=dev).to(bf).requires_grad_(True)
+        tl = torch.clamp((lens.float() / 5).long(), min=1)
+        targets = torch.randint(0, V - 1, (pack.batch, int(tl.max())), device=dev, dtype=torch.int32)
+        fwd = lambda: ctc_op.ctc_loss_packed(logits, pack, targets, tl, blank_index=V - 1)
+        def fb():
+            fwd().sum().backward()
+        report("ctc (V=10001, packed logits)", _time(fwd, args.iters), _time(fb, args.iters), n * V * 2, n * V * 2 * 3)
+    if want("softmax_ce"):
+        V = 10240
+        logits = torch.randn(n, V, device=dev).to(bf).requires_grad_(True)
+        tg = torch.randint(0, V, (n,), device=dev)
+        fwd = lambda: ce.softmax_cross_entropy(logits, tg, 0.1)
+        def fb():
+            fwd().sum().backward()
+        report("softmax_ce (V=10240, smoothing)", _time(fwd, args.iters), _time(fb, args.iters), n * V * 2, n * V * 2 * 3)
+    if want("log_mel"):
+        audio = torch.randn(64, 16000 * 10, device=dev)
+        fwd = lambda: logmel.log_mel(audio, sampling_rate=16000, window=400, step=160, n_fft=512, n_mel=80, f_min=0.0, f_max=8000.0)
+        frames = (160000 - 400) // 160 + 1
+        report("log_mel (64 x 10 s)", _time(fwd, args.iters), None, 64 * 160000 * 4 + 64 * frames * 80 * 4, 0,
+               {"gflops_dft": round(64 * frames * 257 * 400 * 4 / 1e9, 1)})
+    if want("beam_topk"):
+        logits = torch.randn(64, 12, 10001, device=dev).to(bf)
+        prev = torch.randn(64, 12, device=dev)
+        fwd = lambda: seq_ops.beam_topk(logits, prev, eos=0, k=12)
+        report("beam_topk (64 x 12 x 10001)", _time(fwd, args.iters), None, 64 * 12 * 10001 * 2 * 2, 0)
+    from . import gemm as G
+
+    G.check_status()
+
+
+if __name__ == "__main__":
+    main()
