@@ -91,28 +91,6 @@ glu_dwconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
   }
 }
 
-// partials [n_tiles][2][C] -> mean, rstd; running stats update (momentum) when given
-__global__ void bn_stats_kernel(const float* __restrict__ part, int n_tiles, int C, float count, float eps, float momentum,
-                                float* __restrict__ mean, float* __restrict__ rstd, float* __restrict__ running_mean,
-                                float* __restrict__ running_var) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s1 = 0.0, s2 = 0.0;
-  for (int t = 0; t < n_tiles; ++t) {
-    s1 += part[((size_t)t * 2 + 0) * C + c];
-    s2 += part[((size_t)t * 2 + 1) * C + c];
-  }
-  const double m = s1 / count;
-  double var = s2 / count - m * m;
-  if (var < 0.0) var = 0.0;
-  mean[c] = (float)m;
-  rstd[c] = rsqrtf((float)var + eps);
-  if (running_mean) {
-    running_mean[c] += momentum * ((float)m - running_mean[c]);
-    running_var[c] += momentum * ((float)var - running_var[c]);
-  }
-}
-
 __global__ void __launch_bounds__(256)
 bn_silu_fwd_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean, const float* __restrict__ rstd,
                    const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ z, long long total, int C) {
@@ -180,22 +158,6 @@ bn_silu_bwd_a_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
     part[((size_t)blockIdx.x * 2 + 0) * C + cc] = s1;
     part[((size_t)blockIdx.x * 2 + 1) * C + cc] = s2;
   }
-}
-
-// partials -> sum_ds (= dbeta), sum_ds_yhat (= dgamma)
-__global__ void bn_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh,
-                                     float* __restrict__ dgamma_acc = nullptr, float* __restrict__ dbeta_acc = nullptr) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
-  double s1 = 0.0, s2 = 0.0;
-  for (int t = 0; t < n_tiles; ++t) {
-    s1 += part[((size_t)t * 2 + 0) * C + c];
-    s2 += part[((size_t)t * 2 + 1) * C + c];
-  }
-  sum_ds[c] = (float)s1;
-  sum_ds_yh[c] = (float)s2;
-  if (dgamma_acc) dgamma_acc[c] += (float)s2;
-  if (dbeta_acc) dbeta_acc[c] += (float)s1;
 }
 
 // dy = gamma * rstd * (ds - sum_ds/count - yhat * sum_ds_yh/count), in place over ds
@@ -325,6 +287,335 @@ glu_dwconv_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* 
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Sliding-window versions for K <= 32 taps. A thread owns one channel and RPT consecutive output rows: it walks once over
+// the RPT + 31 staged rows of its window, and every staged value feeds up to RPT accumulators through compile-time filter
+// indices, so the filter and the accumulators stay in registers and each staged value is read from shared memory once
+// (the kernels above read one value per tap and output). Rows of other sequences are masked by comparing sequence ids
+// (packed rows are sorted by sequence); a window that lies inside one sequence takes the unmasked path.
+constexpr int TT2 = 64;  // output rows per tile
+constexpr int KM2 = 32;  // taps (filters with fewer taps are zero-padded)
+constexpr int NST2 = TT2 + KM2 - 1;  // staged rows per tile
+constexpr int NID2 = TT2 + KM2 + 2;  // staged sequence ids per tile
+
+template <int RPT, bool MASKED>
+__device__ __forceinline__ void window_conv(const float* __restrict__ col, const int* __restrict__ ids, const float (&w)[KM2],
+                                            const int (&bo)[RPT], float (&acc)[RPT]) {
+#pragma unroll
+  for (int j = 0; j < RPT + KM2 - 1; ++j) {
+    const float v = col[j * CC];
+    const int b = MASKED ? ids[j] : 0;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      if (j - i >= 0 && j - i < KM2) {
+        if (MASKED) acc[i] = (b == bo[i]) ? fmaf(w[j - i], v, acc[i]) : acc[i];
+        else acc[i] = fmaf(w[j - i], v, acc[i]);
+      }
+    }
+  }
+}
+
+template <int RPT, bool MASKED>
+__device__ __forceinline__ void window_corr(const float* __restrict__ col, const int* __restrict__ ids, const float (&d)[RPT],
+                                            const int (&bo)[RPT], float (&df)[KM2]) {
+#pragma unroll
+  for (int j = 0; j < RPT + KM2 - 1; ++j) {
+    const float v = col[j * CC];
+    const int b = MASKED ? ids[j] : 0;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+      if (j - i >= 0 && j - i < KM2) {
+        if (MASKED) df[j - i] = (b == bo[i]) ? fmaf(d[i], v, df[j - i]) : df[j - i];
+        else df[j - i] = fmaf(d[i], v, df[j - i]);
+      }
+    }
+  }
+}
+
+// sequence id of rows first .. first + n - 1 (a distinct negative number for rows outside the buffer: equal to nothing)
+__device__ __forceinline__ void stage_ids(int* __restrict__ ids, const int* __restrict__ row_batch, int first, int n, int n_rows) {
+  for (int s = threadIdx.x; s < n; s += blockDim.x) {
+    const int r = first + s;
+    ids[s] = (r >= 0 && r < n_rows) ? row_batch[r] : -1 - s;
+  }
+}
+
+constexpr int kFwd2Threads = 256;  // 64 channels x 4 row groups of 16 rows
+constexpr int kFwd2Rpt = 16;
+
+__global__ void __launch_bounds__(kFwd2Threads, 2)
+glu_dwconv_fwd2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ filt, const float* __restrict__ bias,
+                       const int* __restrict__ row_batch, __nv_bfloat16* __restrict__ y, float* __restrict__ part, int n_rows, int C, int K) {
+  __shared__ float sh[NST2 * CC];
+  __shared__ int ids[NID2];
+  __shared__ float red[2][4][CC];
+  const int left = (K - 1) / 2;
+  const int r0 = blockIdx.x * TT2;
+  const int c0 = blockIdx.y * CC;
+  for (int idx = threadIdx.x; idx < NST2 * (CC / 8); idx += kFwd2Threads) {
+    const int s = idx / (CC / 8), cg = (idx % (CC / 8)) * 8;
+    const int r = r0 - left + s;
+    F8 h;
+    if (r >= 0 && r < n_rows) {
+      const F8 a = load8(x, (int64_t)r * 2 * C + c0 + cg, 1);
+      const F8 g = load8(x, (int64_t)r * 2 * C + C + c0 + cg, 1);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h.v[i] = a.v[i] * sigmoidf_(g.v[i]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h.v[i] = 0.f;
+    }
+    float4* dst = reinterpret_cast<float4*>(sh + s * CC + cg);
+    dst[0] = make_float4(h.v[0], h.v[1], h.v[2], h.v[3]);
+    dst[1] = make_float4(h.v[4], h.v[5], h.v[6], h.v[7]);
+  }
+  stage_ids(ids, row_batch, r0 - left, NST2, n_rows);
+  __syncthreads();
+  const int c = threadIdx.x % CC;
+  const int rg = threadIdx.x / CC;
+  const int base = rg * kFwd2Rpt;
+  float f[KM2];
+#pragma unroll
+  for (int k = 0; k < KM2; ++k) f[k] = k < K ? filt[(size_t)(c0 + c) * K + k] : 0.f;
+  const float bv = bias ? bias[c0 + c] : 0.f;
+  float acc[kFwd2Rpt];
+  int bo[kFwd2Rpt];
+#pragma unroll
+  for (int i = 0; i < kFwd2Rpt; ++i) {
+    acc[i] = bv;
+    bo[i] = ids[base + i + left];
+  }
+  const int id_first = ids[base], id_last = ids[base + kFwd2Rpt + KM2 - 2];
+  if (id_first >= 0 && id_first == id_last) window_conv<kFwd2Rpt, false>(sh + base * CC + c, ids + base, f, bo, acc);
+  else window_conv<kFwd2Rpt, true>(sh + base * CC + c, ids + base, f, bo, acc);
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int i = 0; i < kFwd2Rpt; ++i) {
+    const int r = r0 + base + i;
+    if (r < n_rows) {
+      const __nv_bfloat16 o = __float2bfloat16(acc[i]);
+      y[(size_t)r * C + c0 + c] = o;
+      const float of = __bfloat162float(o);
+      s1 += of;
+      s2 += of * of;
+    }
+  }
+  red[0][rg][c] = s1;
+  red[1][rg][c] = s2;
+  __syncthreads();
+  if (threadIdx.x < CC) {
+    float a = 0.f, b = 0.f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      a += red[0][g][threadIdx.x];
+      b += red[1][g][threadIdx.x];
+    }
+    // the partial layout has one slot per 32 rows: this CTA fills two of them
+    const int slot = blockIdx.x * (TT2 / TT);
+    const int n_slots = (n_rows + TT - 1) / TT;
+    part[((size_t)slot * 2 + 0) * C + c0 + threadIdx.x] = a;
+    part[((size_t)slot * 2 + 1) * C + c0 + threadIdx.x] = b;
+    if (slot + 1 < n_slots) {
+      part[((size_t)(slot + 1) * 2 + 0) * C + c0 + threadIdx.x] = 0.f;
+      part[((size_t)(slot + 1) * 2 + 1) * C + c0 + threadIdx.x] = 0.f;
+    }
+  }
+}
+
+constexpr int kBwd2Threads = 512;  // 64 channels x 8 row groups of 8 rows
+constexpr int kBwd2Rpt = 8;
+constexpr size_t kBwd2Smem = (size_t)2 * NST2 * CC * sizeof(float) + NID2 * sizeof(int);
+
+// persistent over row tiles (tile = blockIdx.x, += gridDim.x); dfilter / dbias sums stay in registers; partial per CTA
+// [gridDim.x][C][K+1]
+__global__ void __launch_bounds__(kBwd2Threads, 1)
+glu_dwconv_bwd2_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ filt,
+                       const int* __restrict__ row_batch, __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int n_rows, int C, int K) {
+  extern __shared__ __align__(16) unsigned char smem2[];
+  float* sh_dy = reinterpret_cast<float*>(smem2);  // rows r0 - right ..
+  float* sh_h = sh_dy + NST2 * CC;                 // rows r0 - left ..
+  int* ids = reinterpret_cast<int*>(sh_h + NST2 * CC);  // rows r0 - right ..
+  const int left = (K - 1) / 2;
+  const int right = K - 1 - left;
+  const int c0 = blockIdx.y * CC;
+  const int n_tiles = (n_rows + TT2 - 1) / TT2;
+  const int c = threadIdx.x % CC;
+  const int rg = threadIdx.x / CC;
+  const int base = rg * kBwd2Rpt;
+  float fr[KM2];  // flipped filter: fr[m] = f[K-1-m]
+#pragma unroll
+  for (int m = 0; m < KM2; ++m) fr[m] = m < K ? filt[(size_t)(c0 + c) * K + (K - 1 - m)] : 0.f;
+  float df[KM2];
+#pragma unroll
+  for (int k = 0; k < KM2; ++k) df[k] = 0.f;
+  float dbias = 0.f;
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int r0 = tile * TT2;
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < NST2 * (CC / 8); idx += kBwd2Threads) {
+      const int s = idx / (CC / 8), cg = (idx % (CC / 8)) * 8;
+      const int rd = r0 - right + s;
+      F8 d;
+      if (rd >= 0 && rd < n_rows) d = load8(dy, (int64_t)rd * C + c0 + cg, 1);
+      else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) d.v[i] = 0.f;
+      }
+      const int rh = r0 - left + s;
+      F8 h;
+      if (rh >= 0 && rh < n_rows) {
+        const F8 a = load8(x, (int64_t)rh * 2 * C + c0 + cg, 1);
+        const F8 g = load8(x, (int64_t)rh * 2 * C + C + c0 + cg, 1);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h.v[i] = a.v[i] * sigmoidf_(g.v[i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) h.v[i] = 0.f;
+      }
+      float4* pd = reinterpret_cast<float4*>(sh_dy + s * CC + cg);
+      pd[0] = make_float4(d.v[0], d.v[1], d.v[2], d.v[3]);
+      pd[1] = make_float4(d.v[4], d.v[5], d.v[6], d.v[7]);
+      float4* ph = reinterpret_cast<float4*>(sh_h + s * CC + cg);
+      ph[0] = make_float4(h.v[0], h.v[1], h.v[2], h.v[3]);
+      ph[1] = make_float4(h.v[4], h.v[5], h.v[6], h.v[7]);
+    }
+    stage_ids(ids, row_batch, r0 - right, NID2, n_rows);
+    __syncthreads();
+    int bo[kBwd2Rpt];
+#pragma unroll
+    for (int i = 0; i < kBwd2Rpt; ++i) bo[i] = ids[base + i + right];
+    // one test covers both windows: rows r0+base-right .. r0+base+RPT-1+left+1 (the id array has two spare entries)
+    const int id_first = ids[base], id_last = ids[base + kBwd2Rpt + KM2 - 1];
+    const bool inside = id_first >= 0 && id_first == id_last;
+    {
+      // dh[r] = sum_k f[k] * dy[r - k + left]: staged index of that row is (r - r0) + (K-1) - k
+      float acc[kBwd2Rpt];
+#pragma unroll
+      for (int i = 0; i < kBwd2Rpt; ++i) acc[i] = 0.f;
+      if (inside) window_conv<kBwd2Rpt, false>(sh_dy + base * CC + c, ids + base, fr, bo, acc);
+      else window_conv<kBwd2Rpt, true>(sh_dy + base * CC + c, ids + base, fr, bo, acc);
+#pragma unroll
+      for (int i = 0; i < kBwd2Rpt; ++i) {
+        const int r = r0 + base + i;
+        if (r < n_rows) {
+          const float a = __bfloat162float(x[(size_t)r * 2 * C + c0 + c]);
+          const float g = __bfloat162float(x[(size_t)r * 2 * C + C + c0 + c]);
+          const float sg = sigmoidf_(g);
+          dx[(size_t)r * 2 * C + c0 + c] = __float2bfloat16(acc[i] * sg);
+          dx[(size_t)r * 2 * C + C + c0 + c] = __float2bfloat16(acc[i] * a * sg * (1.f - sg));
+        }
+      }
+    }
+    {
+      // dfilter[k] += dy[r] * h[r + k - left]: staged index of that h row is (r - r0) + k; its id sits at + right - left
+      float d[kBwd2Rpt];
+#pragma unroll
+      for (int i = 0; i < kBwd2Rpt; ++i) {
+        d[i] = sh_dy[(base + i + right) * CC + c];
+        dbias += d[i];
+      }
+      if (inside) window_corr<kBwd2Rpt, false>(sh_h + base * CC + c, ids + base + right - left, d, bo, df);
+      else window_corr<kBwd2Rpt, true>(sh_h + base * CC + c, ids + base + right - left, d, bo, df);
+    }
+  }
+  // sum the 8 row groups in shared memory, one partial per CTA
+  __syncthreads();
+  float* red = sh_h;  // [KM2 + 1][CC]
+  for (int idx = threadIdx.x; idx < (KM2 + 1) * CC; idx += kBwd2Threads) red[idx] = 0.f;
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < KM2; ++k) atomicAdd(&red[k * CC + c], df[k]);
+  atomicAdd(&red[KM2 * CC + c], dbias);
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < (K + 1) * CC; idx += kBwd2Threads) {
+    const int cc = idx / (K + 1), k = idx % (K + 1);
+    part[((size_t)blockIdx.x * C + c0 + cc) * (K + 1) + k] = red[(k < K ? k : KM2) * CC + cc];
+  }
+}
+
+// Reductions of per-CTA partials with 8 tile lanes per output and a shared-memory sum (coalesced over the outputs; the
+// one-thread-per-output loops above take tens of microseconds for a few hundred tiles).
+__device__ __forceinline__ float lane_sum8(float s, float (*sh)[32], int tl, int lane) {
+  sh[tl][lane] = s;
+  __syncthreads();
+  if (tl == 0) {
+#pragma unroll
+    for (int g = 1; g < 8; ++g) s += sh[g][lane];
+  }
+  __syncthreads();
+  return s;
+}
+
+// part [n_tiles][C][K+1] -> dfilt [C][K], dbias [C]
+__global__ void __launch_bounds__(256)
+dwconv_bwd_reduce2_kernel(const float* __restrict__ part, int n_tiles, int C, int K, float* __restrict__ dfilt, float* __restrict__ dbias,
+                          int accumulate) {
+  __shared__ float sh[8][32];
+  const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
+  const int idx = blockIdx.x * 32 + lane;
+  const int n_out = C * (K + 1);
+  float s = 0.f;
+  if (idx < n_out)
+    for (int t = tl; t < n_tiles; t += 8) s += part[(size_t)t * n_out + idx];
+  s = lane_sum8(s, sh, tl, lane);
+  if (tl == 0 && idx < n_out) {
+    const int c = idx / (K + 1), k = idx % (K + 1);
+    if (k < K) dfilt[(size_t)c * K + k] = accumulate ? dfilt[(size_t)c * K + k] + s : s;
+    else if (dbias) dbias[c] = accumulate ? dbias[c] + s : s;
+  }
+}
+
+// part [n_tiles][2][C] -> the two sums per channel (thread tl == 0 of each lane holds them)
+__device__ __forceinline__ void pair_sums(const float* __restrict__ part, int n_tiles, int C, int c, float (*sh)[32], int tl, int lane,
+                                          float& s1, float& s2) {
+  s1 = 0.f;
+  s2 = 0.f;
+  if (c < C)
+    for (int t = tl; t < n_tiles; t += 8) {
+      s1 += part[((size_t)t * 2 + 0) * C + c];
+      s2 += part[((size_t)t * 2 + 1) * C + c];
+    }
+  s1 = lane_sum8(s1, sh, tl, lane);
+  s2 = lane_sum8(s2, sh, tl, lane);
+}
+
+__global__ void __launch_bounds__(256)
+bn_stats2_kernel(const float* __restrict__ part, int n_tiles, int C, float count, float eps, float momentum, float* __restrict__ mean,
+                 float* __restrict__ rstd, float* __restrict__ running_mean, float* __restrict__ running_var) {
+  __shared__ float sh[8][32];
+  const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
+  const int c = blockIdx.x * 32 + lane;
+  float s1, s2;
+  pair_sums(part, n_tiles, C, c, sh, tl, lane, s1, s2);
+  if (tl == 0 && c < C) {
+    const double m = (double)s1 / count;
+    double var = (double)s2 / count - m * m;
+    if (var < 0.0) var = 0.0;
+    mean[c] = (float)m;
+    rstd[c] = rsqrtf((float)var + eps);
+    if (running_mean) {
+      running_mean[c] += momentum * ((float)m - running_mean[c]);
+      running_var[c] += momentum * ((float)var - running_var[c]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+bn_bwd_reduce2_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh,
+                      float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc) {
+  __shared__ float sh[8][32];
+  const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
+  const int c = blockIdx.x * 32 + lane;
+  float s1, s2;
+  pair_sums(part, n_tiles, C, c, sh, tl, lane, s1, s2);
+  if (tl == 0 && c < C) {
+    sum_ds[c] = s1;
+    sum_ds_yh[c] = s2;
+    if (dgamma_acc) dgamma_acc[c] += s2;
+    if (dbeta_acc) dbeta_acc[c] += s1;
+  }
+}
+
 __global__ void dwconv_bwd_reduce_kernel(const float* __restrict__ part, int n_tiles, int C, int K, float* __restrict__ dfilt,
                                          float* __restrict__ dbias, int accumulate = 0) {
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -351,6 +642,11 @@ RB_EXPORT int rb200_glu_dwconv_fwd(const void* x, const float* filt, const float
     rb_set_error("glu_dwconv: C=%d must be a multiple of %d and K=%d <= %d", C, CC, K, KMAX);
     return RB_ERR_ARG;
   }
+  if (K <= KM2) {
+    dim3 grid((n_rows + TT2 - 1) / TT2, C / CC);
+    glu_dwconv_fwd2_kernel<<<grid, kFwd2Threads, 0, stream>>>((const __nv_bfloat16*)x, filt, bias, row_batch, (__nv_bfloat16*)y, part, n_rows, C, K);
+    return rb_check_launch("glu_dwconv_fwd2");
+  }
   dim3 grid((n_rows + TT - 1) / TT, C / CC);
   glu_dwconv_fwd_kernel<<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, filt, bias, row_batch, row_pos, lens, (__nv_bfloat16*)y, part, n_rows, C, K);
   return rb_check_launch("glu_dwconv_fwd");
@@ -358,7 +654,7 @@ RB_EXPORT int rb200_glu_dwconv_fwd(const void* x, const float* filt, const float
 
 RB_EXPORT int rb200_bn_stats(const float* part, int n_tiles, int C, float count, float eps, float momentum, float* mean, float* rstd,
                              float* running_mean, float* running_var, cudaStream_t stream) {
-  bn_stats_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, count, eps, momentum, mean, rstd, running_mean, running_var);
+  bn_stats2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, n_tiles, C, count, eps, momentum, mean, rstd, running_mean, running_var);
   return rb_check_launch("bn_stats");
 }
 
@@ -389,7 +685,7 @@ RB_EXPORT int rb200_bn_silu_bwd_ex(const void* y, const void* dz, const float* m
                                                        (__nv_bfloat16*)ds, part, (int)n_rows, C, rows_per_cta);
   int st = rb_check_launch("bn_silu_bwd_a");
   if (st) return st;
-  bn_bwd_reduce_kernel<<<(C + 127) / 128, 128, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh, dgamma_acc, dbeta_acc);
+  bn_bwd_reduce2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh, dgamma_acc, dbeta_acc);
   st = rb_check_launch("bn_bwd_reduce");
   if (st) return st;
   if (training) {
@@ -418,9 +714,24 @@ RB_EXPORT int rb200_glu_dwconv_bwd_ex(const void* x, const void* dy, const float
   int row_ctas = (4 * 148 + C / CC - 1) / (C / CC);
   if (row_ctas > n_tiles) row_ctas = n_tiles;
   dim3 grid(row_ctas, C / CC);
-  if (K <= 32) {
-    glu_dwconv_bwd_kernel<32><<<grid, kThreads, 0, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch, row_pos, lens,
-                                                             (__nv_bfloat16*)dx, part, n_rows, C, K);
+  if (K <= KM2) {
+    static bool attr2 = false;
+    if (!attr2) {
+      cudaFuncSetAttribute(glu_dwconv_bwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kBwd2Smem);
+      attr2 = true;
+    }
+    // one 512-thread CTA per SM; every CTA leaves one partial (the scratch holds ceil(N/32) of them, more than enough)
+    const int n_tiles2 = (n_rows + TT2 - 1) / TT2;
+    row_ctas = 148 / (C / CC);
+    if (row_ctas < 1) row_ctas = 1;
+    if (row_ctas > n_tiles2) row_ctas = n_tiles2;
+    grid = dim3(row_ctas, C / CC);
+    glu_dwconv_bwd2_kernel<<<grid, kBwd2Threads, kBwd2Smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch,
+                                                                     (__nv_bfloat16*)dx, part, n_rows, C, K);
+    int st2 = rb_check_launch("glu_dwconv_bwd2");
+    if (st2) return st2;
+    dwconv_bwd_reduce2_kernel<<<(C * (K + 1) + 31) / 32, 256, 0, stream>>>(part, row_ctas, C, K, dfilt, dbias, accumulate);
+    return rb_check_launch("dwconv_bwd_reduce2");
   } else {
     static bool attr = false;
     if (!attr) {

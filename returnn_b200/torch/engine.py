@@ -295,10 +295,11 @@ class Engine(EngineBase):
                 last_seq_idx = int(extern_data_raw["seq_idx"].max()) if "seq_idx" in extern_data_raw else -1
                 if step_idx == 0 and self._do_save() and "epoch" in extern_data_raw:
                     assert int(extern_data_raw["epoch"]) == self.epoch, "data loader epoch %i != engine epoch %i" % (int(extern_data_raw["epoch"]), self.epoch)
-                if zero_grad_next_step:
+                if zero_grad_next_step and self._graph_step is None:
                     self._updater.get_optimizer().zero_grad()
                     cur_count_grad_accum = 0
                 if self._graph_step is not None:
+                    # the captured step zeroes its static gradient buffers itself
                     losses_dict, inv_norm = self._graph_step.run_train_step(extern_data_raw)
                     step_idx += 1
                     self.global_train_step += 1
