@@ -242,6 +242,20 @@ def run_ours(args):
     barrier()
     e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3 if False else e0.elapsed_time(e1))
     clocks = sampler.stop() if rank == 0 else None
+    if getattr(args, "profile_ops", False) and rank == 0:
+        # outside every timed region: per-op times of the native encoder calls (warm caches, events between the ops)
+        from returnn_b200.models import conformer_native
+
+        conformer_native.profile_ops(True)
+        for i in range(K):
+            engine.run_train_step(raws[base + i], read_losses=False)
+        torch.cuda.synchronize()
+        rep = conformer_native.profile_report()
+        conformer_native.profile_ops(False)
+        total = sum(ms for _, ms in rep.values()) or 1.0
+        print("op profile over %i steps (encoder executor only): %.3f ms/step" % (K, total / K), file=sys.stderr)
+        for tag, (cnt, ms) in sorted(rep.items(), key=lambda kv: -kv[1][1]):
+            print("  %-22s %6i calls  %9.3f ms/step  %7.1f us/call  %5.1f %%" % (tag, cnt // K, ms / K, 1e3 * ms / max(cnt, 1), 100.0 * ms / total), file=sys.stderr)
     frames_dev = sum(frames_per_step[W: W + K])
     frames_e2e = sum(frames_per_step[base + min(W, 3): base + min(W, 3) + K])
     # max time over ranks, total frames over ranks
@@ -473,6 +487,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=4)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--profile-ops", action="store_true", help="after the measurement, print per-op times of the native encoder to stderr")
     ap.add_argument("--tiny", action="store_true", help="small model and batches on any device: a functional smoke test, not a benchmark")
     args = ap.parse_args()
     if args.tiny:

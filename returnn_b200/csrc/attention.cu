@@ -69,8 +69,19 @@ att_softmax_fwd_kernel(const TS* __restrict__ s_ac, const TS* __restrict__ g, __
   const int z = blockIdx.y;
   const int b = z / heads, h = z % heads;
   const int len = lens[b];
-  if (i >= len) return;
+  // the GEMMs that consume w / wd contract over rows or columns up to the next multiple of 64: that margin is zeroed here,
+  // nothing beyond it is ever read, so the buffers need no memset
+  const int len64 = min(lp, (len + 63) & ~63);
+  if (i >= len64) return;
   const long long srow = ((long long)z * lp + i) * lp;
+  if (i >= len) {
+    const __nv_bfloat16 zero = __float2bfloat16(0.f);
+    for (int j = lane; j < len64; j += 32) {
+      w[srow + j] = zero;
+      if (p_drop > 0.f) wd[srow + j] = zero;
+    }
+    return;
+  }
   const long long grow = (((long long)h * batch + b) * lp + i) * rp;
   float x[kMaxPerLane];
   float mx = -INFINITY;
@@ -101,7 +112,7 @@ att_softmax_fwd_kernel(const TS* __restrict__ s_ac, const TS* __restrict__ g, __
 #pragma unroll
   for (int t = 0; t < kMaxPerLane; ++t) {
     const int j = lane + 32 * t;
-    if (j < lp) {
+    if (j < len64) {
       const float pr = j < len ? x[t] * inv : 0.f;
       w[srow + j] = __float2bfloat16(pr);
       if (drop) {
@@ -122,8 +133,13 @@ att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const TS* __restrict
   const int z = blockIdx.y;
   const int b = z / heads, h = z % heads;
   const int len = lens[b];
-  if (i >= len) return;
+  const int len64 = min(lp, (len + 63) & ~63);  // see the forward kernel
+  if (i >= len64) return;
   const long long srow = ((long long)z * lp + i) * lp;
+  if (i >= len) {
+    for (int j = lane; j < len64; j += 32) ds[srow + j] = __float2bfloat16(0.f);
+    return;
+  }
   const long long grow = (((long long)h * batch + b) * lp + i) * rp;
   const bool drop = p_drop > 0.f;
   const uint64_t sd = drop ? (uint64_t)seed[0] : 0;
@@ -154,6 +170,8 @@ att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const TS* __restrict
       const __nv_bfloat16 o = __float2bfloat16(pw[t] * (dw[t] - delta));
       ds[srow + j] = o;
       dg[grow + (j - i + center)] = o;
+    } else if (j < len64) {
+      ds[srow + j] = __float2bfloat16(0.f);
     }
   }
 }

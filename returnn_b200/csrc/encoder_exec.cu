@@ -13,6 +13,9 @@
 //   x4 = x3 + 0.5 drop(FF2(LN(x3)));  out = LN(x4)
 #include "common.cuh"
 #include "gemm.h"
+#include <map>
+#include <mutex>
+#include <string>
 #include <vector>
 
 // entry points of the other translation units used here
@@ -70,36 +73,37 @@ namespace {
 // ---- small kernels ------------------------------------------------------------------------------------------------
 
 // out[c] += sum_r y[r][c] with y = x, or y = dropout_mask * scale * x (then y is also written).
-// grid (row CTAs, column chunks of 2048); block = groups * rows_per_iter threads, one thread per 8 columns.
-__global__ void __launch_bounds__(256)
-colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ out, int rows, int C, int groups,
-              int rows_per_iter, float scale, float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset,
-              unsigned long long site) {
-  __shared__ float red[256 * 8];
-  const int g = threadIdx.x % groups, rs = threadIdx.x / groups;
-  const int col = blockIdx.y * 2048 + g * 8;
+// A CTA owns 64 columns (8 threads x 8 columns: one 128-byte line per row) and a slice of the rows; 32 row lanes walk the
+// slice with two independent 16-byte loads in flight each (three CTAs per SM). The 32 lane sums meet in shared memory and leave as ONE atomic per
+// column and CTA (a CTA per full row made rows/8 atomics per column, which serialise in L2).
+__global__ void __launch_bounds__(256, 3)
+colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ out, int rows, int C, int rows_per_cta,
+              float scale, float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset, unsigned long long site) {
+  __shared__ float red[32][65];
+  const int cg = threadIdx.x & 7, rl = threadIdx.x >> 3;
+  const int col = blockIdx.y * 64 + cg * 8;
+  const int r_begin = blockIdx.x * rows_per_cta;
+  const int r_end = min(rows, r_begin + rows_per_cta);
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const bool drop = p_drop > 0.f;
   const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] + site : 0;
   const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
   const float keep = drop ? scale / (1.f - p_drop) : scale;
   if (col < C) {
-    const int stride = gridDim.x * rows_per_iter;
     const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
-    // four rows per iteration so that four independent loads are in flight per thread
-    for (int rbase = blockIdx.x * rows_per_iter + rs; rbase < rows; rbase += 4 * stride) {
-      F8 v[4];
-      int64_t idx[4];
+    for (int rbase = r_begin + rl; rbase < r_end; rbase += 2 * 32) {
+      F8 v[2];
+      int64_t idx[2];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = rbase + u * stride;
+      for (int u = 0; u < 2; ++u) {
+        const int r = rbase + u * 32;
         idx[u] = (int64_t)r * C + col;
-        if (r < rows) v[u] = load8(x, idx[u], 1);
+        if (r < r_end) v[u] = load8(x, idx[u], 1);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int r = rbase + u * stride;
-        if (r >= rows) break;
+      for (int u = 0; u < 2; ++u) {
+        const int r = rbase + u * 32;
+        if (r >= r_end) break;
         if (y) {
           if (drop) {
             const uint64_t c = off + (uint64_t)idx[u];
@@ -122,16 +126,15 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
       }
     }
   }
+  if (!out) return;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) red[threadIdx.x * 8 + i] = acc[i];
+  for (int i = 0; i < 8; ++i) red[rl][cg * 8 + i] = acc[i];
   __syncthreads();
-  if (rs == 0 && col < C && out) {
-    for (int k = 1; k < rows_per_iter; ++k) {
+  if (threadIdx.x < 64 && blockIdx.y * 64 + threadIdx.x < C) {
+    float sum = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] += red[(k * groups + g) * 8 + i];
-    }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) atomicAdd(out + col + i, acc[i]);
+    for (int k = 0; k < 32; ++k) sum += red[k][threadIdx.x];
+    atomicAdd(out + blockIdx.y * 64 + threadIdx.x, sum);
   }
 }
 
@@ -142,16 +145,16 @@ int colsum(const void* x, void* y, float* out, int rows, int C, float scale, flo
     rb_set_error("colsum: C=%d must be a multiple of 8", C);
     return RB_ERR_ARG;
   }
-  const int G = C / 8;
-  const int chunks = (G + 255) / 256;
-  const int groups = G < 256 ? G : 256;  // a partial last chunk is masked by col < C
-  const int rpi = 256 / groups > 0 ? 256 / groups : 1;
-  int ctas = (rows + rpi * 8 - 1) / (rpi * 8);
-  const int cap = (592 + chunks - 1) / chunks;
-  if (ctas > cap) ctas = cap;
-  if (ctas < 1) ctas = 1;
-  colsum_kernel<<<dim3(ctas, chunks), groups * rpi, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, out, rows, C, groups, rpi, scale, p_drop,
-                                                            seed, offset, site);
+  const int chunks = (C + 63) / 64;
+  // three resident CTAs per SM; at least 32 rows (one per lane) per CTA
+  int splits = (3 * 148 + chunks - 1) / chunks;
+  const int max_splits = (rows + 31) / 32;
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  const int rows_per_cta = (rows + splits - 1) / splits;
+  splits = (rows + rows_per_cta - 1) / rows_per_cta;
+  colsum_kernel<<<dim3(splits, chunks), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, out, rows, C, rows_per_cta, scale, p_drop, seed,
+                                                     offset, site);
   return rb_check_launch("colsum");
 }
 
@@ -181,11 +184,13 @@ typedef __nv_bfloat16 bf16;
 
 struct Geometry {
   int n, B, D, F, H, Dh, HD, K, Lp, Rp, R, center, L;
+  bool keep_wd;  // attention dropout active: dropout(w) is saved next to w
   size_t pad_rows;     // B * Lp
   size_t score_elems;  // B * H * Lp * Lp
   size_t band_elems;   // H * B * Lp * Rp
   unsigned long long site_ff_act, site_ff_out, site_att, site_att_out, site_conv_out, site_ff2_act, site_ff2_out, per_layer;
   explicit Geometry(const RbEncDims& d) {
+    keep_wd = d.training && d.p_att > 0.f;
     n = d.n_rows; B = d.batch; D = d.D; F = d.F; H = d.H; Dh = d.Dh; HD = H * Dh; K = d.conv_k; L = d.n_layers;
     Lp = (d.max_len + 63) / 64 * 64;
     Rp = 2 * Lp;
@@ -209,7 +214,7 @@ struct Geometry {
 
 // activations kept from forward to backward, per layer
 struct Saved {
-  bf16 *ln1, *z1, *a1, *x1, *ln2, *qu, *qv, *kk, *vv, *w, *posp, *att, *x2, *ln3, *g, *y, *zc, *x3, *ln4, *z2, *a2, *x4, *out;
+  bf16 *ln1, *z1, *a1, *x1, *ln2, *qu, *qv, *kk, *vv, *w, *wd, *posp, *att, *x2, *ln3, *g, *y, *zc, *x3, *ln4, *z2, *a2, *x4, *out;
   float *st1, *st2, *st3, *st4, *st5, *bn_ms;
 };
 
@@ -230,6 +235,8 @@ struct SavedLayout {
     s.kk = s.qu ? s.qu + 2 * g.pad_rows * HD : nullptr;
     s.vv = s.qu ? s.qu + 3 * g.pad_rows * HD : nullptr;
     s.w = bump.take<bf16>(g.score_elems);
+    // the dropped probabilities are kept too (recomputing them in the backward pass costs a full pass over the scores)
+    s.wd = g.keep_wd ? bump.take<bf16>(g.score_elems) : s.w;
     s.posp = bump.take<bf16>((size_t)g.R * HD);
     s.att = bump.take<bf16>(n * HD); s.x2 = bump.take<bf16>(n * D);
     s.ln3 = bump.take<bf16>(n * D); s.st3 = bump.take<float>(2 * n);
@@ -256,6 +263,32 @@ inline int bn_tiles_a(int n) {
   return t;
 }
 
+// ---- per-op timing (off by default) ---------------------------------------------------------------------------------
+// When enabled, every op of a forward/backward call is followed by an event on the stream; at the end of the call the stream
+// is synchronised and the time between consecutive events is added to a table keyed by the op's tag. The numbers are
+// in-pipeline times (warm L2, no gaps between launches), which is what a step is made of; a profiler that serialises and
+// flushes caches reports other numbers.
+struct OpProfile {
+  std::mutex mu;
+  bool enabled = false;
+  std::map<std::string, std::pair<long long, double>> table;  // tag -> (count, ms)
+  std::vector<cudaEvent_t> pool;
+  cudaEvent_t get() {
+    if (!pool.empty()) {
+      cudaEvent_t e = pool.back();
+      pool.pop_back();
+      return e;
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreate(&e);
+    return e;
+  }
+};
+OpProfile& op_profile() {
+  static OpProfile p;
+  return p;
+}
+
 struct Exec {
   const RbEncDims& d;
   Geometry g;
@@ -266,10 +299,50 @@ struct Exec {
   cudaStream_t s;
   int st = RB_OK;
   int launches = 0;
+  bool prof = false;
+  std::vector<std::pair<std::string, cudaEvent_t>> marks;
 
   Exec(const RbEncDims& dims, const long long* t, const int* l, const int* rb, const int* rp, const long long* sd, const long long* of,
        int* stat, cudaStream_t stream)
-      : d(dims), g(dims), tab(t), lens(l), row_batch(rb), row_pos(rp), seed(sd), offset(of), status(stat), s(stream) {}
+      : d(dims), g(dims), tab(t), lens(l), row_batch(rb), row_pos(rp), seed(sd), offset(of), status(stat), s(stream) {
+    OpProfile& p = op_profile();
+    {
+      std::lock_guard<std::mutex> lk(p.mu);
+      prof = p.enabled;
+    }
+    if (prof) mark("(start)");  // takes the lock itself
+  }
+  void mark(const char* tag) {
+    // caller holds no lock; the pool is only touched under the lock
+    OpProfile& p = op_profile();
+    cudaEvent_t ev;
+    {
+      std::lock_guard<std::mutex> lk(p.mu);
+      ev = p.get();
+    }
+    cudaEventRecord(ev, s);
+    std::string t(tag ? tag : "?");
+    const size_t par = t.find('(', 1);
+    if (par != std::string::npos) t.resize(par);
+    marks.emplace_back(t, ev);
+  }
+  // end of a call: with timing on, wait for the stream and book the intervals
+  void finish() {
+    if (!prof || marks.size() < 2) return;
+    cudaStreamSynchronize(s);
+    OpProfile& p = op_profile();
+    std::lock_guard<std::mutex> lk(p.mu);
+    for (size_t i = 1; i < marks.size(); ++i) {
+      float ms = 0.f;
+      if (cudaEventElapsedTime(&ms, marks[i - 1].second, marks[i].second) == cudaSuccess) {
+        auto& slot = p.table[marks[i].first];
+        slot.first += 1;
+        slot.second += ms;
+      }
+    }
+    for (auto& m : marks) p.pool.push_back(m.second);
+    marks.clear();
+  }
 
   const float* p32(int l, int i) const { return reinterpret_cast<const float*>(tab[((size_t)l * P_COUNT + i) * 3 + 0]); }
   float* g32(int l, int i) const { return reinterpret_cast<float*>(tab[((size_t)l * P_COUNT + i) * 3 + 1]); }
@@ -277,10 +350,12 @@ struct Exec {
   unsigned long long site(int l, unsigned long long s_) const { return (unsigned long long)l * g.per_layer + s_; }
   float pdrop(float p) const { return d.training ? p : 0.f; }
 
-  void run(int code) {
+  void run(int code, const char* tag = nullptr) {
     ++launches;
     if (st == RB_OK && code != RB_OK) st = code;
+    if (prof) mark(tag);
   }
+  void run_tagged(const char* tag, int code) { run(code, tag); }
   bool ok() const { return st == RB_OK; }
 
   // y = [resid + res_scale *] drop(act(x·W + b)); z (optional) receives the pre-activation
@@ -295,7 +370,7 @@ struct Exec {
     if (z) { q.c = z; q.c2 = y; } else { q.c = y; }
     q.drop_p = p_drop; q.seed = seed; q.offset = offset; q.drop_site = site_;
     q.resid = resid; q.res_scale = res_scale; q.status = status;
-    run(rb_gemm(q, s));
+    run(rb_gemm(q, s), "gemm_fwd");
   }
   // dx = (dy·W^T) [* act'(z)] [* dropout mask]
   void linear_dgrad(const void* dy, int l, int wi, int m, int in, int out, void* dx, const void* z, int act, float p_drop,
@@ -306,7 +381,7 @@ struct Exec {
     q.a_mn_major = 0; q.b_mn_major = 0;
     q.dact_z = z; q.act = z ? act : 0;
     q.drop_p = p_drop; q.seed = seed; q.offset = offset; q.drop_site = site_; q.status = status;
-    run(rb_gemm(q, s));
+    run(rb_gemm(q, s), "gemm_dgrad");
   }
   // dW += x^T·dy (fp32, atomics, contraction split over CTAs); db += column sums of dy
   void linear_wgrad(const void* x, const void* dy, int l, int wi, int bi, int m, int in, int out, bool bias_sum) {
@@ -315,18 +390,18 @@ struct Exec {
       RbGemm q;
       q.a = x; q.b = dy; q.c = g32(l, wi); q.m = in; q.n = out; q.k = m; q.lda = in; q.ldb = out; q.ldc = out;
       q.a_mn_major = 1; q.b_mn_major = 1; q.out_fp32 = 1; q.accumulate = 2; q.status = status;
-      run(rb_gemm(q, s));
+      run(rb_gemm(q, s), "gemm_wgrad");
     }
-    if (bias_sum && bi >= 0 && g32(l, bi)) run(colsum(dy, nullptr, g32(l, bi), m, out, 1.f, 0.f, nullptr, nullptr, 0, s));
+    if (bias_sum && bi >= 0 && g32(l, bi)) run(colsum(dy, nullptr, g32(l, bi), m, out, 1.f, 0.f, nullptr, nullptr, 0, s), "colsum_bias");
   }
   void layer_norm(const void* x, int l, int gi, void* y, float* stats) {
     if (!ok()) return;
-    run(rb200_layer_norm_fwd(x, p32(l, gi), p32(l, gi + 1), y, stats, stats + g.n, g.n, g.D, d.ln_eps, 1, 0, 0, s));
+    run(rb200_layer_norm_fwd(x, p32(l, gi), p32(l, gi + 1), y, stats, stats + g.n, g.n, g.D, d.ln_eps, 1, 0, 0, s), "layer_norm_fwd");
   }
   void layer_norm_bwd(const void* x, const void* dy, int l, int gi, const float* stats, void* dx, const void* dres, float* part) {
     if (!ok()) return;
     run(rb200_layer_norm_bwd_ex(x, dy, p32(l, gi), stats, stats + g.n, dx, part, g32(l, gi), g32(l, gi + 1), g.n, g.D, ln_parts(g.n), 1, 0, 0,
-                                dres, 1, s));
+                                dres, 1, s), "layer_norm_bwd");
     ++launches;
   }
   void bgemm(const void* a, const void* b, void* c, int m, int n, int k, int a_mn, int b_mn, int lda, int ldb, int ldc, long long a_rows,
@@ -334,7 +409,7 @@ struct Exec {
              int n_l, int k_l, float alpha, int out_fp32) {
     if (!ok()) return;
     run(rb200_gemm_bf16_batched(a, b, c, nullptr, a_rows, a_cols, b_rows, b_cols, lda, ldb, ldc, m, n, k, a_mn, b_mn, 0, 0, out_fp32, 0, alpha,
-                                batch, heads, offs, lens_, m_l, n_l, k_l, status, s));
+                                batch, heads, offs, lens_, m_l, n_l, k_l, status, s), "gemm_batched");
   }
   void memset0(void* p, size_t bytes) {
     if (!ok()) return;
@@ -349,14 +424,13 @@ struct Exec {
 
 // scratch of the forward pass
 struct TmpFwd {
-  bf16 *qkv, *wd, *o_pad;
+  bf16 *qkv, *o_pad;
   float *s_ac, *band, *conv_part;
   TmpFwd(void* base, const Geometry& g, size_t* total) {
     Bump b(base);
     qkv = b.take<bf16>((size_t)g.n * 3 * g.HD);
     s_ac = b.take<float>(g.score_elems);
     band = b.take<float>(g.band_elems);
-    wd = b.take<bf16>(g.score_elems);
     o_pad = b.take<bf16>(g.pad_rows * g.HD);
     conv_part = b.take<float>((size_t)((g.n + 31) / 32) * 2 * g.D);
     if (total) *total = b.off + 256;
@@ -365,7 +439,7 @@ struct TmpFwd {
 
 // scratch of the backward pass
 struct TmpBwd {
-  bf16 *dA, *dB, *tD, *tD2, *tD3, *tW, *datt, *do_pad, *wd, *ds, *dband, *dqu, *dqv, *dk, *dv, *dpos;
+  bf16 *dA, *dB, *tD, *tD2, *tD3, *tW, *datt, *do_pad, *ds, *dband, *dqu, *dqv, *dk, *dv, *dpos;
   float *dwd, *ln_part, *bn_part, *conv_part, *sum_ds, *sum_ds_yh;
   TmpBwd(void* base, const Geometry& g, size_t* total) {
     Bump b(base);
@@ -378,7 +452,6 @@ struct TmpBwd {
     tW = b.take<bf16>(n * wide);
     datt = b.take<bf16>(n * HD);
     do_pad = b.take<bf16>(g.pad_rows * HD);
-    wd = b.take<bf16>(g.score_elems);
     ds = b.take<bf16>(g.score_elems);
     dband = b.take<bf16>(g.band_elems);
     dqu = b.take<bf16>(4 * g.pad_rows * HD);
@@ -452,7 +525,7 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
   const float p_res = e.pdrop(d.p_res), p_ff = e.pdrop(d.p_ff), p_att = e.pdrop(d.p_att);
   if (p_att > 0.f) {
     offsets_kernel<<<1, 64, 0, stream>>>(offset, lay.att_off, g.L, g.site_att, g.per_layer);
-    e.run(rb_check_launch("enc_offsets"));
+    e.run_tagged("rb_check_launch", rb_check_launch("enc_offsets"));
   }
   const void* x0 = x_in;
   const int n = g.n, D = g.D, F = g.F, HD = g.HD, Lp = g.Lp, Rp = g.Rp, B = g.B, H = g.H, Dh = g.Dh;
@@ -467,7 +540,7 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
     e.linear_fwd(sv.ln2, l, P_QKV_W, P_QKV_B, n, D, 3 * HD, t.qkv, nullptr, 0, 0.f, 0, nullptr, 1.f);
     e.linear_fwd(sinus, l, P_POS_W, -1, g.R, D, HD, sv.posp, nullptr, 0, 0.f, 0, nullptr, 1.f);
     e.memset0(sv.qu, 4 * g.pad_rows * HD * sizeof(bf16));
-    if (e.ok()) e.run(rb200_att_prepare(t.qkv, e.p32(l, P_POS_U), e.p32(l, P_POS_V), row_batch, row_pos, sv.qu, sv.qv, sv.kk, sv.vv, n, H, Dh, Lp, stream));
+    if (e.ok()) e.run_tagged("att_prepare", rb200_att_prepare(t.qkv, e.p32(l, P_POS_U), e.p32(l, P_POS_V), row_batch, row_pos, sv.qu, sv.qv, sv.kk, sv.vv, n, H, Dh, Lp, stream));
     {
       const long long o1[10] = {Lp, 0, 0, Dh, Lp, 0, 0, Dh, (long long)H * Lp * Lp, (long long)Lp * Lp};
       // scores and bias band in bf16, like the matmul outputs of the reference under autocast: halves the traffic of this stage
@@ -476,34 +549,30 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
       const long long o2[10] = {Lp, 0, 0, Dh, 0, 0, 0, Dh, (long long)Lp * Rp, (long long)B * Lp * Rp};
       e.bgemm(sv.qv, sv.posp, t.band, Lp, g.R, Dh, 0, 0, HD, HD, Rp, (long long)B * Lp, HD, g.R, HD, o2, B * H, H, lens, 1, 0, 0, d.att_scale, 0);
     }
-    e.memset0(sv.w, g.score_elems * sizeof(bf16));
-    bf16* wd = sv.w;
-    if (p_att > 0.f) {
-      e.memset0(t.wd, g.score_elems * sizeof(bf16));
-      wd = t.wd;
-    }
-    if (e.ok()) e.run(rb200_att_softmax_fwd_ex(t.s_ac, t.band, 1, sv.w, wd, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
+    // w and wd need no memset: the softmax kernel zeroes the margin that the GEMMs read beyond each sequence's length
+    bf16* wd = p_att > 0.f ? sv.wd : sv.w;
+    if (e.ok()) e.run_tagged("att_softmax_fwd_ex", rb200_att_softmax_fwd_ex(t.s_ac, t.band, 1, sv.w, wd, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
     {
       const long long o3[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};
       e.bgemm(wd, sv.vv, t.o_pad, Lp, Dh, Lp, 0, 1, Lp, HD, HD, (long long)B * H * Lp, Lp, (long long)B * Lp, HD, o3, B * H, H, lens, 1, 0, 1, 1.f, 0);
     }
-    if (e.ok()) e.run(rb200_att_rows_gather(t.o_pad, sv.att, row_batch, row_pos, n, HD, Lp, 0, stream));
+    if (e.ok()) e.run_tagged("att_rows_gather", rb200_att_rows_gather(t.o_pad, sv.att, row_batch, row_pos, n, HD, Lp, 0, stream));
     e.linear_fwd(sv.att, l, P_PROJ_W, P_PROJ_B, n, HD, D, sv.x2, nullptr, 0, p_res, e.site(l, g.site_att_out), sv.x1, 1.f);
     // ---- convolution module
     e.layer_norm(sv.x2, l, P_CONV_LN_G, sv.ln3, sv.st3);
     e.linear_fwd(sv.ln3, l, P_PW1_W, P_PW1_B, n, D, 2 * D, sv.g, nullptr, 0, 0.f, 0, nullptr, 1.f);
-    if (e.ok()) e.run(rb200_glu_dwconv_fwd(sv.g, e.p32(l, P_DW_F), e.p32(l, P_DW_B), row_batch, row_pos, lens, sv.y, t.conv_part, n, D, g.K, stream));
+    if (e.ok()) e.run_tagged("glu_dwconv_fwd", rb200_glu_dwconv_fwd(sv.g, e.p32(l, P_DW_F), e.p32(l, P_DW_B), row_batch, row_pos, lens, sv.y, t.conv_part, n, D, g.K, stream));
     if (e.ok()) {
       const bool upd = d.training != 0;
       if (d.training) {
-        e.run(rb200_bn_stats(t.conv_part, (n + 31) / 32, D, (float)n, d.bn_eps, d.bn_momentum, sv.bn_ms, sv.bn_ms + D,
+        e.run_tagged("bn_stats", rb200_bn_stats(t.conv_part, (n + 31) / 32, D, (float)n, d.bn_eps, d.bn_momentum, sv.bn_ms, sv.bn_ms + D,
                              upd ? const_cast<float*>(e.p32(l, P_BN_RM)) : nullptr, upd ? const_cast<float*>(e.p32(l, P_BN_RV)) : nullptr, stream));
       } else {
         rb_set_error("encoder: the native executor runs the training graph only");
         e.st = RB_ERR_UNSUPPORTED;
       }
     }
-    if (e.ok()) e.run(rb200_bn_silu_fwd(sv.y, sv.bn_ms, sv.bn_ms + D, e.p32(l, P_BN_G), e.p32(l, P_BN_B), sv.zc, n, D, stream));
+    if (e.ok()) e.run_tagged("bn_silu_fwd", rb200_bn_silu_fwd(sv.y, sv.bn_ms, sv.bn_ms + D, e.p32(l, P_BN_G), e.p32(l, P_BN_B), sv.zc, n, D, stream));
     e.linear_fwd(sv.zc, l, P_PW2_W, P_PW2_B, n, D, D, sv.x3, nullptr, 0, p_res, e.site(l, g.site_conv_out), sv.x2, 1.f);
     // ---- feed-forward 2
     e.layer_norm(sv.x3, l, P_FF2_LN_G, sv.ln4, sv.st4);
@@ -513,6 +582,7 @@ RB_EXPORT int rb200_enc_forward(const RbEncDims* dims, const long long* tab, con
     e.layer_norm(sv.x4, l, P_FIN_LN_G, sv.out, sv.st5);
     x0 = sv.out;
   }
+  e.finish();
   if (n_launch) *n_launch = e.launches;
   return e.st;
 }
@@ -541,7 +611,7 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
   // dropout(residual-branch) backward + bias gradient:  dy = mask * scale * dx_total;  db += colsum(dy)
   auto branch_in = [&](const void* dxt, void* dy, int l, int bi, float scale, float p, unsigned long long site_) {
     if (!e.ok()) return;
-    e.run(colsum(dxt, dy, bi >= 0 ? e.g32(l, bi) : nullptr, n, D, scale, p, seed, offset, site_, stream));
+    e.run_tagged("colsum_dropout", colsum(dxt, dy, bi >= 0 ? e.g32(l, bi) : nullptr, n, D, scale, p, seed, offset, site_, stream));
   };
 
   for (int l = layer_hi - 1; l >= layer_lo && e.ok(); --l) {
@@ -561,12 +631,12 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
     e.linear_wgrad(sv.zc, t.tD, l, P_PW2_W, P_PW2_B, n, D, D, false);
     e.linear_dgrad(t.tD, l, P_PW2_W, n, D, D, t.tD2, nullptr, 0, 0.f, 0);
     if (e.ok()) {
-      e.run(rb200_bn_silu_bwd_ex(sv.y, t.tD2, sv.bn_ms, sv.bn_ms + D, e.p32(l, P_BN_G), e.p32(l, P_BN_B), t.tD3, t.bn_part, bn_tiles_a(n), t.sum_ds,
+      e.run_tagged("bn_silu_bwd_ex", rb200_bn_silu_bwd_ex(sv.y, t.tD2, sv.bn_ms, sv.bn_ms + D, e.p32(l, P_BN_G), e.p32(l, P_BN_B), t.tD3, t.bn_part, bn_tiles_a(n), t.sum_ds,
                                  t.sum_ds_yh, n, D, 1, e.g32(l, P_BN_G), e.g32(l, P_BN_B), stream));
       e.launches += 2;
     }
     if (e.ok()) {
-      e.run(rb200_glu_dwconv_bwd_ex(sv.g, t.tD3, e.p32(l, P_DW_F), row_batch, row_pos, lens, t.tW, t.conv_part, e.g32(l, P_DW_F), e.g32(l, P_DW_B), n, D,
+      e.run_tagged("glu_dwconv_bwd_ex", rb200_glu_dwconv_bwd_ex(sv.g, t.tD3, e.p32(l, P_DW_F), row_batch, row_pos, lens, t.tW, t.conv_part, e.g32(l, P_DW_F), e.g32(l, P_DW_B), n, D,
                                     g.K, 1, stream));
       e.launches += 1;
     }
@@ -578,22 +648,16 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
     e.linear_wgrad(sv.att, t.tD, l, P_PROJ_W, P_PROJ_B, n, HD, D, false);
     e.linear_dgrad(t.tD, l, P_PROJ_W, n, HD, D, t.datt, nullptr, 0, 0.f, 0);
     e.memset0(t.do_pad, g.pad_rows * HD * sizeof(bf16));
-    if (e.ok()) e.run(rb200_att_rows_gather(t.datt, t.do_pad, row_batch, row_pos, n, HD, Lp, 1, stream));
-    const bf16* wd = sv.w;
-    if (p_att > 0.f) {
-      e.memset0(t.wd, g.score_elems * sizeof(bf16));
-      if (e.ok()) e.run(rb200_att_redrop(sv.w, t.wd, lens, B, H, Lp, p_att, seed, lay.att_off + l, stream));
-      wd = t.wd;
-    }
+    if (e.ok()) e.run_tagged("att_rows_gather", rb200_att_rows_gather(t.datt, t.do_pad, row_batch, row_pos, n, HD, Lp, 1, stream));
+    const bf16* wd = p_att > 0.f ? sv.wd : sv.w;
     {
       const long long o4[10] = {Lp, 0, 0, Dh, Lp, 0, 0, Dh, (long long)H * Lp * Lp, (long long)Lp * Lp};
       e.bgemm(t.do_pad, sv.vv, t.dwd, Lp, Lp, Dh, 0, 0, HD, HD, Lp, (long long)B * Lp, HD, (long long)B * Lp, HD, o4, B * H, H, lens, 1, 1, 0, 1.f, 0);
       const long long o5[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};
       e.bgemm(wd, t.do_pad, t.dv, Lp, Dh, Lp, 1, 1, Lp, HD, HD, (long long)B * H * Lp, Lp, (long long)B * Lp, HD, o5, B * H, H, lens, 1, 0, 1, 1.f, 0);
     }
-    e.memset0(t.ds, g.score_elems * sizeof(bf16));
     e.memset0(t.dband, g.band_elems * sizeof(bf16));
-    if (e.ok()) e.run(rb200_att_softmax_bwd_ex(sv.w, t.dwd, 1, t.ds, t.dband, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
+    if (e.ok()) e.run_tagged("att_softmax_bwd_ex", rb200_att_softmax_bwd_ex(sv.w, t.dwd, 1, t.ds, t.dband, lens, B, H, Lp, Rp, g.center, p_att, seed, lay.att_off + l, stream));
     e.memset0(t.dqu, 2 * g.pad_rows * HD * sizeof(bf16));  // dqu, dqv: their column sums run over all padded rows
     {
       const long long o6[10] = {(long long)H * Lp, Lp, 0, 0, Lp, 0, 0, Dh, (long long)Lp * HD, Dh};
@@ -605,9 +669,9 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
       e.bgemm(t.dband, sv.qv, t.dpos, g.R, Dh, B * Lp, 1, 1, Rp, HD, HD, (long long)H * B * Lp, Rp, (long long)B * Lp, HD, o9, H, H, nullptr, 0, 0, 0,
               d.att_scale, 0);
     }
-    if (e.ok()) e.run(rb200_att_pack_dqkv(t.dqu, t.dqv, t.dk, t.dv, row_batch, row_pos, t.tW, n, H, Dh, Lp, stream));
-    if (e.ok() && e.g32(l, P_POS_U)) e.run(colsum(t.dqu, nullptr, e.g32(l, P_POS_U), (int)g.pad_rows, HD, 1.f, 0.f, nullptr, nullptr, 0, stream));
-    if (e.ok() && e.g32(l, P_POS_V)) e.run(colsum(t.dqv, nullptr, e.g32(l, P_POS_V), (int)g.pad_rows, HD, 1.f, 0.f, nullptr, nullptr, 0, stream));
+    if (e.ok()) e.run_tagged("att_pack_dqkv", rb200_att_pack_dqkv(t.dqu, t.dqv, t.dk, t.dv, row_batch, row_pos, t.tW, n, H, Dh, Lp, stream));
+    if (e.ok() && e.g32(l, P_POS_U)) e.run_tagged("colsum", colsum(t.dqu, nullptr, e.g32(l, P_POS_U), (int)g.pad_rows, HD, 1.f, 0.f, nullptr, nullptr, 0, stream));
+    if (e.ok() && e.g32(l, P_POS_V)) e.run_tagged("colsum", colsum(t.dqv, nullptr, e.g32(l, P_POS_V), (int)g.pad_rows, HD, 1.f, 0.f, nullptr, nullptr, 0, stream));
     e.linear_wgrad(sinus, t.dpos, l, P_POS_W, -1, g.R, D, HD, false);
     e.linear_wgrad(sv.ln2, t.tW, l, P_QKV_W, P_QKV_B, n, D, 3 * HD, true);
     e.linear_dgrad(t.tW, l, P_QKV_W, n, D, 3 * HD, t.tD2, nullptr, 0, 0.f, 0);
@@ -620,6 +684,7 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
     e.linear_dgrad(t.tW, l, P_FF1_W1, n, D, F, t.tD2, nullptr, 0, 0.f, 0);
     e.layer_norm_bwd(x0, t.tD2, l, P_FF1_LN_G, sv.st1, dx, t.dB, t.ln_part);
   }
+  e.finish();
   if (n_launch) *n_launch = e.launches;
   return e.st;
 }
@@ -627,4 +692,30 @@ RB_EXPORT int rb200_enc_backward(const RbEncDims* dims, const long long* tab, co
 // out[c] += sum over rows of x[r][c] (bf16 [rows, C] contiguous, fp32 out, atomics): bias gradient of a linear layer
 RB_EXPORT int rb200_colsum_bf16(const void* x, float* out, int rows, int C, cudaStream_t stream) {
   return colsum(x, nullptr, out, rows, C, 1.f, 0.f, nullptr, nullptr, 0, stream);
+}
+
+// per-op timing of the executor calls: enable/disable (clears the table), and a text report "tag count total_ms" per line
+RB_EXPORT int rb200_enc_profile_enable(int on) {
+  OpProfile& p = op_profile();
+  std::lock_guard<std::mutex> lk(p.mu);
+  p.enabled = on != 0;
+  p.table.clear();
+  return RB_OK;
+}
+
+RB_EXPORT int rb200_enc_profile_report(char* buf, int len) {
+  OpProfile& p = op_profile();
+  std::lock_guard<std::mutex> lk(p.mu);
+  std::string out;
+  for (const auto& kv : p.table) {
+    char line[256];
+    snprintf(line, sizeof(line), "%s %lld %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    out += line;
+  }
+  if (buf && len > 0) {
+    const size_t n = out.size() < (size_t)len - 1 ? out.size() : (size_t)len - 1;
+    memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return (int)out.size() + 1;
 }

@@ -232,3 +232,31 @@ def encoder_stack(x0: torch.Tensor, sinus: torch.Tensor, plan: NativeEncoderPlan
                 for li in range(lo, hi):
                     _gr.notify_grads_written(plan.layer_params[li])
     return _EncoderStackFn.apply(x0, sinus, plan, pack, grad_ready_cb)
+
+
+def profile_ops(enable: bool):
+    """
+    Per-op timing of the executor calls (events between the ops of every forward/backward call; each call then ends with a
+    stream synchronisation, so leave it off for throughput measurements). Enabling clears the table.
+    """
+    import ctypes
+    from ..ops import _lib
+
+    fn = _lib.bind("rb200_enc_profile_enable", [ctypes.c_int])
+    _lib.check(fn(1 if enable else 0), "enc_profile_enable")
+
+
+def profile_report() -> dict:
+    """:return: ``{op tag: (calls, total milliseconds)}`` collected since :func:`profile_ops` was enabled"""
+    import ctypes
+    from ..ops import _lib
+
+    fn = _lib.bind("rb200_enc_profile_report", [ctypes.c_char_p, ctypes.c_int])
+    size = fn(None, 0)
+    buf = ctypes.create_string_buffer(size + 16)
+    fn(buf, size + 16)
+    res = {}
+    for line in buf.value.decode("utf8").splitlines():
+        tag, count, ms = line.rsplit(" ", 2)
+        res[tag] = (int(count), float(ms))
+    return res
