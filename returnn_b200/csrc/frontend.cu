@@ -205,6 +205,65 @@ im2col_transposed_kernel(const bf16* __restrict__ dy, const int* __restrict__ le
   }
 }
 
+// ---- patch-gradient gather (backward data, output side): dcol [out frames * F, 9 * Ci] = dy . W holds, for every output position,
+// the gradient of its 3x3xCi input patch; the input gradient is the sum over the (at most ceil(3/stride) x 3) patches that contain
+// the input position:  dx[(b, t, f), :] = sum_{kt, kf} dcol[(b, to, f + 1 - kf), (kt, kf, :)]  with to = (t + pad_t - kt) / stride_t
+// where exact and to < lens_out[b]; zero for t >= lens_in[b]; optionally times relu'(z). A gather: no atomics, and the matrix
+// product has out-frames rows (the transposed-patch form above has stride_t times more, most of them zeros).
+__global__ void __launch_bounds__(256)
+col2im_kernel(const bf16* __restrict__ dcol, const int* __restrict__ lens_out, const int* __restrict__ lens_in, const int* __restrict__ cu, int B,
+              int T, int F, int Ci, int stride_t, int pad_t, int To, const bf16* __restrict__ relu_z, bf16* __restrict__ dx) {
+  const int G = Ci / 8;
+  const long long total = (long long)B * T * F * G;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int g = (int)(i % G);
+    long long r = i / G;  // (b, t, f)
+    const int f = (int)(r % F);
+    const long long bt = r / F;
+    const int b = (int)(bt / T), t = (int)(bt % T);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (t < lens_in[b]) {
+      const int lo = lens_out[b];
+#pragma unroll
+      for (int kt = 0; kt < 3; ++kt) {
+        const int num = t + pad_t - kt;
+        if (num < 0 || num % stride_t) continue;
+        const int to = num / stride_t;
+        if (to >= lo || to >= To) continue;
+        const long long frame = cu ? (long long)cu[b] + to : (long long)b * To + to;
+#pragma unroll
+        for (int kf = 0; kf < 3; ++kf) {
+          const int fo = f + 1 - kf;
+          if (fo < 0 || fo >= F) continue;
+          const uint4 v = *reinterpret_cast<const uint4*>(dcol + ((frame * F + fo) * 9 + kt * 3 + kf) * Ci + g * 8);
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const float2 p2 = __bfloat1622float2(h[q]);
+            acc[2 * q] += p2.x;
+            acc[2 * q + 1] += p2.y;
+          }
+        }
+      }
+      if (relu_z) {
+        const uint4 z = *reinterpret_cast<const uint4*>(relu_z + r * Ci + g * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&z);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 p2 = __bfloat1622float2(h[q]);
+          if (!(p2.x > 0.f)) acc[2 * q] = 0.f;
+          if (!(p2.y > 0.f)) acc[2 * q + 1] = 0.f;
+        }
+      }
+    }
+    uint4 o;
+    __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) oh[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+    *reinterpret_cast<uint4*>(dx + r * Ci + g * 8) = o;
+  }
+}
+
 int grid_for(long long total) {
   long long g = (total + 255) / 256;
   if (g > 148 * 32) g = 148 * 32;
@@ -251,4 +310,14 @@ RB_EXPORT int rb200_im2col_3x3_transposed(const void* dy, const int* lens_out, c
   im2col_transposed_kernel<<<grid_for((long long)B * T * F * 9 * (Co / 8)), 256, 0, stream>>>((const bf16*)dy, lens_out, lens_in, cu, B, T, F, Co,
                                                                                               stride_t, pad_t, To, (bf16*)col);
   return rb_check_launch("im2col_3x3_transposed");
+}
+
+// dx [B, T, F, Ci] from the patch gradients dcol [out frames * F, 9 * Ci] (see col2im_kernel); relu_z (optional) [B, T, F, Ci]
+RB_EXPORT int rb200_col2im_3x3(const void* dcol, const int* lens_out, const int* lens_in, const int* cu, int B, int T, int F, int Ci, int stride_t,
+                               int pad_t, int To, const void* relu_z, void* dx, cudaStream_t stream) {
+  if (B <= 0 || T <= 0) return RB_OK;
+  if (Ci % 8) return RB_ERR_UNSUPPORTED;
+  col2im_kernel<<<grid_for((long long)B * T * F * (Ci / 8)), 256, 0, stream>>>((const bf16*)dcol, lens_out, lens_in, cu, B, T, F, Ci, stride_t, pad_t,
+                                                                                To, (const bf16*)relu_z, (bf16*)dx);
+  return rb_check_launch("col2im_3x3");
 }

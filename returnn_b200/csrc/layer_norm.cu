@@ -202,6 +202,120 @@ ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const voi
   }
 }
 
+// Backward for bf16 activations with accumulation into fp32 dgamma / dbeta (the form the training step uses). One CTA of
+// 16 warps per SM; a warp walks its rows with the NEXT row's x and dy already in flight while it computes the current one
+// (the loads are the whole cost of a row); the 16 warps' column sums meet in shared memory and leave as one atomic per
+// column and CTA: no partials buffer and no second kernel.
+constexpr int kBwdAccWarps = 16;
+
+template <int CHUNKS>
+__global__ void __launch_bounds__(kBwdAccWarps * 32, 1)
+ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const void* __restrict__ gamma,
+                  const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
+                  float* __restrict__ dgamma, float* __restrict__ dbeta, int64_t rows, int n, int w_bf16, int rms,
+                  const __nv_bfloat16* __restrict__ dres) {
+  extern __shared__ float smem[];  // [2][n]
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  F8 g[CHUNKS], acc_g[CHUNKS], acc_b[CHUNKS];
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < n) g[c] = load8(gamma, col, w_bf16);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc_g[c].v[i] = acc_b[c].v[i] = 0.f;
+  }
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) smem[i] = 0.f;
+  __syncthreads();
+  const int64_t stride = (int64_t)gridDim.x * kBwdAccWarps;
+  int64_t row = (int64_t)blockIdx.x * kBwdAccWarps + warp;
+  uint4 nx[CHUNKS], nd[CHUNKS];
+  auto fetch = [&](int64_t r) {
+    const int64_t base = r * (int64_t)n;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < n) {
+        nx[c] = *reinterpret_cast<const uint4*>(x + base + col);
+        nd[c] = *reinterpret_cast<const uint4*>(dy + base + col);
+      }
+    }
+  };
+  auto unpack = [](const uint4& u, F8& f) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 p = __bfloat1622float2(h[i]);
+      f.v[2 * i] = p.x;
+      f.v[2 * i + 1] = p.y;
+    }
+  };
+  if (row < rows) fetch(row);
+  while (row < rows) {
+    const float mean = mean_in[row], rstd = rstd_in[row];
+    const int64_t base = row * (int64_t)n;
+    F8 xh[CHUNKS], d[CHUNKS];
+    uint4 rr[CHUNKS];
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      unpack(nx[c], xh[c]);
+      unpack(nd[c], d[c]);
+      if (dres && (c * 32 + lane) * 8 < n) rr[c] = *reinterpret_cast<const uint4*>(dres + base + (c * 32 + lane) * 8);
+    }
+    const int64_t next = row + stride;
+    if (next < rows) fetch(next);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < n) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[c].v[i] = (xh[c].v[i] - mean) * rstd;
+          const float gd = g[c].v[i] * d[c].v[i];
+          s1 += gd;
+          s2 += gd * xh[c].v[i];
+          acc_g[c].v[i] += d[c].v[i] * xh[c].v[i];
+          acc_b[c].v[i] += d[c].v[i];
+        }
+      }
+    }
+    s1 = rms ? 0.f : warp_sum(s1) / (float)n;
+    s2 = warp_sum(s2) / (float)n;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = (c * 32 + lane) * 8;
+      if (col < n) {
+        F8 o, res;
+        if (dres) unpack(rr[c], res);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          o.v[i] = rstd * (g[c].v[i] * d[c].v[i] - s1 - xh[c].v[i] * s2);
+          if (dres) o.v[i] += res.v[i];
+        }
+        store8(dx, base + col, o, 1);
+      }
+    }
+    row = next;
+  }
+#pragma unroll
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int col = (c * 32 + lane) * 8;
+    if (col < n) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        atomicAdd(&smem[col + i], acc_g[c].v[i]);
+        atomicAdd(&smem[n + col + i], acc_b[c].v[i]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int col = threadIdx.x; col < n; col += blockDim.x) {
+    if (dgamma) atomicAdd(dgamma + col, smem[col]);
+    if (dbeta) atomicAdd(dbeta + col, smem[n + col]);
+  }
+}
+
 // partial sums -> dgamma / dbeta. Block = 32 columns x 8 slices of the partials; grid = ceil(n / 32).
 __global__ void __launch_bounds__(256)
 ln_bwd_reduce_kernel(const float* __restrict__ part, float* __restrict__ dgamma, float* __restrict__ dbeta, int n, int n_part,
@@ -265,6 +379,20 @@ RB_EXPORT int rb200_layer_norm_bwd_ex(const void* x, const void* dy, const void*
     return RB_ERR_ARG;
   }
   if (n_part <= 0) return RB_ERR_ARG;
+  if (accumulate && x_bf16 && n <= 512 && rows > 0 && (dgamma || dbeta)) {
+    int ctas = (int)((rows + kBwdAccWarps - 1) / kBwdAccWarps);
+    if (ctas > 148) ctas = 148;
+    const size_t sm = (size_t)2 * n * sizeof(float);
+    const int ch = (n + 255) / 256;
+#define LN_ACC(C)                                                                                                                       \
+  ln_bwd_acc_kernel<C><<<ctas, kBwdAccWarps * 32, sm, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, gamma, mean, rstd, \
+                                                                 (__nv_bfloat16*)dx, dgamma, dbeta, rows, n, w_bf16, rms,              \
+                                                                 (const __nv_bfloat16*)dres)
+    if (ch <= 1) LN_ACC(1);
+    else LN_ACC(2);
+#undef LN_ACC
+    return rb_check_launch("layer_norm_bwd_acc");
+  }
   dim3 grid(n_part), block(kWarpsPerCta * 32);
   size_t smem = (size_t)kWarpsPerCta * 2 * n * sizeof(float);
   int chunks = (n + 255) / 256;

@@ -11,6 +11,7 @@ from typing import Optional, Sequence, Union, Callable
 import math as _math
 import numpy
 import torch
+from . import _numpy_backend as _np
 import torch.nn.functional as F
 from ..tensor import Tensor, Dim
 from ._utils import wrap, merge_dims_for_broadcast, convert_to_tensor, torch_dtype, dtype_name
@@ -97,6 +98,8 @@ def compare(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
     :param kind: "==", "!=", "<", "<=", ">", ">=" or the word forms
     :return: bool tensor, dims = union of the operand dims
     """
+    if _np.is_numpy(a) or _np.is_numpy(b):
+        return _np.NumpyBackend.compare(a, kind, b)
     a, b, ra, rb, out_dims = _prep_bin(a, b, allow_broadcast_all_sources, dim_order)
     fn = _CMP.get(kind)
     if fn is None:
@@ -114,6 +117,8 @@ def combine(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
     :param kind: "+", "-", "*", "/", "//", "%", "**", "max", "min", "logical_and", "logical_or", "squared_difference"
     :return: dims = union of the operand dims
     """
+    if _np.is_numpy(a) or _np.is_numpy(b):
+        return _np.NumpyBackend.combine(a, kind, b)
     a, b, ra, rb, out_dims = _prep_bin(a, b, allow_broadcast_all_sources, dim_order)
     fn = _BIN.get(kind)
     if fn is None:

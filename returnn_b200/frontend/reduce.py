@@ -36,6 +36,10 @@ def reduce(source: Tensor, *, mode: str, axis: Union[Dim, Sequence[Dim]], use_ma
     :param use_mask: ignore padded frames of dynamic axes
     :param distributed: additionally reduce over all ranks (sum/max/min/mean)
     """
+    from . import _numpy_backend as _np
+
+    if _np.is_numpy(source):
+        return _np.NumpyBackend.reduce(source, mode=mode, axis=axis, use_mask=use_mask)
     axes = [axis] if isinstance(axis, Dim) else list(axis)
     raw = source._raw_tensor
     idxs = [axis_of(source, d) for d in axes]

@@ -80,6 +80,14 @@ class ConformerCtcModel(rf.Module):
         w = self.logits.weight.raw_tensor
         b = self.logits.bias.raw_tensor
         ar = _arena.find_arena(w) if (training and torch.is_grad_enabled()) else None
+        if ar is not None and w.shape[1] % 8:
+            # vocabulary + blank is odd-sized: computed 8-aligned, the extra classes have probability 0 (the CTC loss takes
+            # the number of classes from the logits)
+            from ..ops import gemm as _gemm
+
+            logits = _gemm.linear_arena_padded_out(rows, w, b, ar)
+            if logits is not None:
+                return logits, pack
         logits = conformer_fused.arena_linear(rows, w, b, None, ar, conformer_fused._Weights(rows.dtype))
         return logits, pack
 

@@ -63,6 +63,14 @@ def _im2col_t(dy, lens_out, lens_in, cu, B, T, F, Co, stride, pad, To):
     return col
 
 
+def _col2im(dcol, lens_out, lens_in, cu, B, T, F, Ci, stride, pad, To, relu_z):
+    dx = torch.empty(B, T, F, Ci, dtype=torch.bfloat16, device=dcol.device)
+    _call("rb200_col2im_3x3", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp], dcol.data_ptr(), lens_out.data_ptr(),
+          lens_in.data_ptr(), cu.data_ptr() if cu is not None else None, B, T, F, Ci, stride, pad, To,
+          relu_z.data_ptr() if relu_z is not None else None, dx.data_ptr(), _lib.stream_ptr())
+    return dx
+
+
 class _FrontendFn(torch.autograd.Function):
     """feats [B,T,F] bf16 -> packed rows [n, (F/2)*C3] bf16"""
 
@@ -111,19 +119,19 @@ class _FrontendFn(torch.autograd.Function):
         dw3p = torch.zeros(C3, 9 * C2, dtype=torch.float32, device=dev)
         _gemm.gemm(dz3, col3, m=C3, n=9 * C2, k=dz3.shape[0], a_mn_major=True, b_mn_major=True, out=dw3p, atomic=True)
         db3 = dz3.float().sum(0) if has_b3 else None
-        colT3 = _im2col_t(dz3, lens_dev[2], lens_dev[1], cu, B, T2, Fp, C3, s3, pad3, T3)
-        w3t = w3.permute(2, 3, 0, 1).reshape(9 * C3, C2).to(bf).contiguous()
-        # data gradient of layer 3, times relu'(out2)
-        dz2 = _gemm.gemm(colT3, w3t, m=colT3.shape[0], n=C2, k=9 * C3, a_mn_major=False, b_mn_major=True, act="relu", dact_z=out2.view(-1, C2))
-        del colT3
+        # data gradient of layer 3: patch gradients on the output side, gathered back (times relu'(out2))
+        w3p = w3.permute(0, 2, 3, 1).reshape(C3, 9 * C2).to(bf).contiguous()
+        dcol3 = _gemm.gemm(dz3, w3p, m=dz3.shape[0], n=9 * C2, k=C3, a_mn_major=False, b_mn_major=True)
+        dz2 = _col2im(dcol3, lens_dev[2], lens_dev[1], cu, B, T2, Fp, C2, s3, pad3, T3, out2).view(-1, C2)
+        del dcol3
         # ---- layer 2
         dw2p = torch.zeros(C2, 9 * C1, dtype=torch.float32, device=dev)
         _gemm.gemm(dz2, col2, m=C2, n=9 * C1, k=dz2.shape[0], a_mn_major=True, b_mn_major=True, out=dw2p, atomic=True)
         db2 = dz2.float().sum(0) if has_b2 else None
-        colT2 = _im2col_t(dz2, lens_dev[1], lens_dev[0], None, B, T, Fp, C2, s2, pad2, T2)
-        w2t = w2.permute(2, 3, 0, 1).reshape(9 * C2, C1).to(bf).contiguous()
-        d_out1 = _gemm.gemm(colT2, w2t, m=colT2.shape[0], n=C1, k=9 * C2, a_mn_major=False, b_mn_major=True)
-        del colT2
+        w2p = w2.permute(0, 2, 3, 1).reshape(C2, 9 * C1).to(bf).contiguous()
+        dcol2 = _gemm.gemm(dz2, w2p, m=dz2.shape[0], n=9 * C1, k=C2, a_mn_major=False, b_mn_major=True)
+        d_out1 = _col2im(dcol2, lens_dev[1], lens_dev[0], None, B, T, Fp, C1, s2, pad2, T2, None)
+        del dcol2
         # ---- layer 1: filter / bias gradient by direct reduction (pool routing and ReLU recomputed)
         dw1 = torch.zeros(C1, 9, dtype=torch.float32, device=dev)
         db1 = torch.zeros(C1, dtype=torch.float32, device=dev) if has_b1 else None

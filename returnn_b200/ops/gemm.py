@@ -248,6 +248,92 @@ def linear_arena(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     return y.reshape(*x.shape[:-1], w16.shape[1])
 
 
+class _PaddedOutLinearFn(torch.autograd.Function):
+    """see :func:`linear_arena_padded_out`"""
+
+    @staticmethod
+    def forward(ctx, x2, w_pad, bias_pad, gw32, gb32, n):
+        m, k = x2.shape
+        n_pad = w_pad.shape[1]
+        y = gemm(x2, w_pad, m=m, n=n_pad, k=k, a_mn_major=False, b_mn_major=True, bias=bias_pad)
+        ctx.save_for_backward(x2, w_pad)
+        ctx.gw32, ctx.gb32, ctx.n = gw32, gb32, n
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_pad = ctx.saved_tensors
+        m, k = x2.shape
+        n_pad, n = w_pad.shape[1], ctx.n
+        dy = dy.contiguous()
+        dx = gemm(dy, w_pad, m=m, n=k, k=n_pad, a_mn_major=False, b_mn_major=False) if ctx.needs_input_grad[0] else None
+        if ctx.gw32 is not None:
+            # only the first n columns of dy reach the parameter gradient [k, n] (its pitch n is not a multiple of 8: scalar atomics)
+            gemm(x2, dy, m=k, n=n, k=m, a_mn_major=True, b_mn_major=True, out=ctx.gw32, atomic=True)
+        if ctx.gb32 is not None:
+            tmp = torch.zeros(n_pad, dtype=torch.float32, device=dy.device)
+            fn = _lib.bind("rb200_colsum_bf16", [_vp, _vp, _i32, _i32, _vp])
+            _lib.check(fn(dy.data_ptr(), tmp.data_ptr(), m, n_pad, _lib.stream_ptr()), "colsum")
+            _lib.count_launch()
+            ctx.gb32.add_(tmp[:n])
+        from ..parallel import grad_reducer as _gr
+
+        _gr.notify_grads_written([ctx.gw32, ctx.gb32])
+        return dx, None, None, None, None, None
+
+
+_padded_cache = {}
+
+
+def linear_arena_padded_out(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], arena, *, pad_bias: float = -1e30) -> Optional[torch.Tensor]:
+    """
+    Output layer whose width ``n`` is not a multiple of 8 (e.g. a vocabulary of 10000 + blank): TMA needs row pitches of 16
+    bytes, so the layer is computed ``n_pad = ceil8(n)`` wide. The extra columns have zero weights and bias ``pad_bias``: with
+    the default they are classes of probability exactly 0 under a following (log-)softmax, receive gradient 0 and change
+    nothing; the caller treats the result as ``n_pad`` classes.
+
+    :return: ``[..., n_pad]`` bf16, or None when the arena path does not apply (see :func:`linear_arena`)
+    """
+    if arena is None or not x.requires_grad or weight.dtype != torch.float32 or arena.grad_dtype != torch.float32 or weight.dim() != 2:
+        return None
+    k, n = weight.shape
+    if not available(x) or not weight.is_contiguous() or k % 8 or n % 8 == 0:
+        return None
+    off = (weight.data_ptr() - arena.flat_param.data_ptr()) // 4
+    if not (0 <= off < arena.total):
+        return None
+    n_pad = (n + 7) // 8 * 8
+    arena.sync_shadow()
+    w16 = arena.shadow_bf16()[off: off + weight.numel()].view(k, n)
+    gw = arena.flat_grad[off: off + weight.numel()].view(k, n) if weight.requires_grad else None
+    gb = None
+    key = (weight.data_ptr(), n_pad, str(x.device))
+    bufs = _padded_cache.get(key)
+    if bufs is None:
+        bufs = (torch.zeros(k, n_pad, dtype=torch.bfloat16, device=x.device), torch.full((n_pad,), pad_bias, dtype=torch.float32, device=x.device))
+        _padded_cache[key] = bufs
+    w_pad, bias_pad = bufs
+    w_pad[:, :n].copy_(w16)
+    if bias is not None:
+        if bias.dtype != torch.float32:
+            return None
+        boff = (bias.data_ptr() - arena.flat_param.data_ptr()) // 4
+        if bias.requires_grad:
+            if not (0 <= boff < arena.total):
+                return None
+            gb = arena.flat_grad[boff: boff + n]
+        bias_pad[:n].copy_(bias.detach())
+    else:
+        bias_pad[:n].zero_()
+    if x.dtype != torch.bfloat16:
+        x = x.to(torch.bfloat16)
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = _PaddedOutLinearFn.apply(x2, w_pad, bias_pad, gw, gb, n)
+    return y.reshape(*x.shape[:-1], n_pad)
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], activation: Optional[str]) -> torch.Tensor:
     """``x[..., in] @ weight[in, out] (+ bias) (activation)`` with bf16 operands"""
     if x.dtype != torch.bfloat16:

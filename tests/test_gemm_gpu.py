@@ -127,3 +127,41 @@ def test_gemm_split_k_atomic(m, n, k):
     gemm.check_status()
     ref = 2.0 + 2.0 * (x.float().t() @ dy.float())
     torch.testing.assert_close(acc, ref, atol=0.05 * k ** 0.5, rtol=2e-2)
+
+
+@pytest.mark.gpu
+def test_linear_arena_padded_out():
+    """output layer of width 1001 (not a multiple of 8) through the 8-aligned computation: loss and gradients as torch in fp32"""
+    from returnn_b200.ops import gemm as G
+    from returnn_b200.parallel.arena import ParamArena
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    m, k, n = 700, 256, 1001
+    lin = torch.nn.Module()
+    lin.weight = torch.nn.Parameter(torch.randn(k, n, device=dev) * 0.05)
+    lin.bias = torch.nn.Parameter(torch.randn(n, device=dev) * 0.1)
+    arena = ParamArena(list(lin.named_parameters()))
+    arena.zero_grad()
+    x = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16).requires_grad_(True)
+    tgt = torch.randint(0, n, (m,), device=dev)
+    y = G.linear_arena_padded_out(x, lin.weight, lin.bias, arena)
+    assert y is not None and y.shape == (m, 1008)
+    logp = torch.log_softmax(y.float(), dim=-1)
+    assert float(logp[:, n:].exp().max()) == 0.0
+    loss = -logp.gather(1, tgt[:, None]).sum()
+    loss.backward()
+    # fp32 reference on the bf16-rounded operands
+    xr = x.detach().float().requires_grad_(True)
+    wr = lin.weight.detach().to(torch.bfloat16).float().requires_grad_(True)
+    br = lin.bias.detach().clone().requires_grad_(True)
+    yr = xr @ wr + br
+    loss_r = -torch.log_softmax(yr, dim=-1).gather(1, tgt[:, None]).sum()
+    loss_r.backward()
+    assert abs(float(loss) - float(loss_r)) / abs(float(loss_r)) < 2e-3
+    torch.testing.assert_close(x.grad.float(), xr.grad, atol=2e-2, rtol=5e-2)
+    by_name = {s.name: s for s in arena.slots}
+    for name, ref in (("weight", wr.grad), ("bias", br.grad)):
+        s = by_name[name]
+        got = arena.flat_grad[s.offset: s.offset + s.numel].view(ref.shape)
+        torch.testing.assert_close(got, ref, atol=3e-2, rtol=5e-2)
