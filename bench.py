@@ -246,16 +246,28 @@ def run_ours(args):
         # outside every timed region: per-op times of the native encoder calls (warm caches, events between the ops)
         from returnn_b200.models import conformer_native
 
+        # host issue time: how long the host needs to enqueue K steps (no synchronisation inside); close to the device time
+        # means the step is bound by the launching thread, not by the kernels
+        torch.cuda.synchronize()
+        th0 = time.perf_counter()
+        for i in range(K):
+            engine.run_train_step(raws[base + i], read_losses=False)
+        th1 = time.perf_counter()
+        torch.cuda.synchronize()
+        th2 = time.perf_counter()
+        print("host issue %.3f ms/step, until the device is done %.3f ms/step" % ((th1 - th0) * 1e3 / K, (th2 - th0) * 1e3 / K), file=sys.stderr)
         conformer_native.profile_ops(True)
         for i in range(K):
             engine.run_train_step(raws[base + i], read_losses=False)
         torch.cuda.synchronize()
         rep = conformer_native.profile_report()
         conformer_native.profile_ops(False)
-        total = sum(ms for _, ms in rep.values()) or 1.0
-        print("op profile over %i steps (encoder executor only): %.3f ms/step" % (K, total / K), file=sys.stderr)
-        for tag, (cnt, ms) in sorted(rep.items(), key=lambda kv: -kv[1][1]):
-            print("  %-22s %6i calls  %9.3f ms/step  %7.1f us/call  %5.1f %%" % (tag, cnt // K, ms / K, 1e3 * ms / max(cnt, 1), 100.0 * ms / total), file=sys.stderr)
+        total = sum(v[1] for v in rep.values()) or 1.0
+        host_total = sum(v[2] for v in rep.values())
+        print("op profile over %i steps (encoder executor only): device %.3f ms/step, host issue %.3f ms/step" % (K, total / K, host_total / K), file=sys.stderr)
+        for tag, (cnt, ms, host) in sorted(rep.items(), key=lambda kv: -kv[1][1]):
+            print("  %-22s %6i calls  %9.3f ms/step  %7.1f us/call  %5.1f %%   host %6.1f us/call" % (
+                tag, cnt // K, ms / K, 1e3 * ms / max(cnt, 1), 100.0 * ms / total, 1e3 * host / max(cnt, 1)), file=sys.stderr)
     frames_dev = sum(frames_per_step[W: W + K])
     frames_e2e = sum(frames_per_step[base + min(W, 3): base + min(W, 3) + K])
     # max time over ranks, total frames over ranks

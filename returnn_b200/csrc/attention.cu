@@ -22,6 +22,8 @@ att_prepare_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restric
                    const int* __restrict__ row_batch, const int* __restrict__ row_pos, __nv_bfloat16* __restrict__ qu,
                    __nv_bfloat16* __restrict__ qv, __nv_bfloat16* __restrict__ kk, __nv_bfloat16* __restrict__ vv,
                    int n_rows, int heads, int dim, int lp) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   // one thread per 8 consecutive elements of one of q/k/v of one head of one row
   const int groups_per_part = dim / 8;
   const int groups_per_row = heads * 3 * groups_per_part;
@@ -64,6 +66,8 @@ __global__ void __launch_bounds__(128)
 att_softmax_fwd_kernel(const TS* __restrict__ s_ac, const TS* __restrict__ g, __nv_bfloat16* __restrict__ w,
                        __nv_bfloat16* __restrict__ wd, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int z = blockIdx.y;
@@ -128,6 +132,8 @@ __global__ void __launch_bounds__(128)
 att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const TS* __restrict__ dwd, __nv_bfloat16* __restrict__ ds,
                        __nv_bfloat16* __restrict__ dg, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const int lane = threadIdx.x & 31;
   const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int z = blockIdx.y;
@@ -199,6 +205,8 @@ __global__ void __launch_bounds__(256)
 att_pack_dqkv_kernel(const __nv_bfloat16* __restrict__ dqu, const __nv_bfloat16* __restrict__ dqv, const __nv_bfloat16* __restrict__ dk,
                      const __nv_bfloat16* __restrict__ dv, const int* __restrict__ row_batch, const int* __restrict__ row_pos,
                      __nv_bfloat16* __restrict__ dqkv, int n_rows, int heads, int dim, int lp) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const int groups_per_part = dim / 8;
   const int groups_per_row = heads * 3 * groups_per_part;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -228,6 +236,8 @@ att_pack_dqkv_kernel(const __nv_bfloat16* __restrict__ dqu, const __nv_bfloat16*
 __global__ void __launch_bounds__(256)
 att_rows_gather_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, const int* __restrict__ row_batch,
                        const int* __restrict__ row_pos, int n_rows, int width, int lp, int to_padded) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const int groups = width / 8;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (gid >= (long long)n_rows * groups) return;
@@ -249,7 +259,7 @@ RB_EXPORT int rb200_att_prepare(const void* qkv, const float* u, const float* v,
     return RB_ERR_ARG;
   }
   long long total = (long long)n_rows * heads * 3 * (dim / 8);
-  att_prepare_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+  rb_launch_pdl(att_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 
       (const __nv_bfloat16*)qkv, u, v, row_batch, row_pos, (__nv_bfloat16*)qu, (__nv_bfloat16*)qv, (__nv_bfloat16*)k, (__nv_bfloat16*)vv,
       n_rows, heads, dim, lp);
   return rb_check_launch("att_prepare");
@@ -264,10 +274,10 @@ RB_EXPORT int rb200_att_softmax_fwd_ex(const void* s_ac, const void* g, int scor
   }
   dim3 grid((lp + 3) / 4, batch * heads);
   if (scores_bf16)
-    att_softmax_fwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)s_ac, (const __nv_bfloat16*)g, (__nv_bfloat16*)w,
+    rb_launch_pdl(att_softmax_fwd_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, stream, (const __nv_bfloat16*)s_ac, (const __nv_bfloat16*)g, (__nv_bfloat16*)w,
                                                                     (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
   else
-  att_softmax_fwd_kernel<float><<<grid, 128, 0, stream>>>((const float*)s_ac, (const float*)g, (__nv_bfloat16*)w, (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop,
+  rb_launch_pdl(att_softmax_fwd_kernel<float>, dim3(grid), dim3(128), 0, stream, (const float*)s_ac, (const float*)g, (__nv_bfloat16*)w, (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop,
                                                    seed, offset);
   return rb_check_launch("att_softmax_fwd");
 }
@@ -277,10 +287,10 @@ RB_EXPORT int rb200_att_softmax_bwd_ex(const void* w, const void* dwd, int dwd_b
   if (lp > 32 * kMaxPerLane) return RB_ERR_UNSUPPORTED;
   dim3 grid((lp + 3) / 4, batch * heads);
   if (dwd_bf16)
-    att_softmax_bwd_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)w, (const __nv_bfloat16*)dwd, (__nv_bfloat16*)ds,
+    rb_launch_pdl(att_softmax_bwd_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dwd, (__nv_bfloat16*)ds,
                                                                     (__nv_bfloat16*)dg, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
   else
-    att_softmax_bwd_kernel<float><<<grid, 128, 0, stream>>>((const __nv_bfloat16*)w, (const float*)dwd, (__nv_bfloat16*)ds, (__nv_bfloat16*)dg, lens,
+    rb_launch_pdl(att_softmax_bwd_kernel<float>, dim3(grid), dim3(128), 0, stream, (const __nv_bfloat16*)w, (const float*)dwd, (__nv_bfloat16*)ds, (__nv_bfloat16*)dg, lens,
                                                             batch, heads, lp, rp, center, p_drop, seed, offset);
   return rb_check_launch("att_softmax_bwd");
 }
@@ -306,7 +316,7 @@ RB_EXPORT int rb200_att_pack_dqkv(const void* dqu, const void* dqv, const void* 
                                   void* dqkv, int n_rows, int heads, int dim, int lp, cudaStream_t stream) {
   if (n_rows <= 0) return RB_OK;
   long long total = (long long)n_rows * heads * 3 * (dim / 8);
-  att_pack_dqkv_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
+  rb_launch_pdl(att_pack_dqkv_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, 
       (const __nv_bfloat16*)dqu, (const __nv_bfloat16*)dqv, (const __nv_bfloat16*)dk, (const __nv_bfloat16*)dv, row_batch, row_pos,
       (__nv_bfloat16*)dqkv, n_rows, heads, dim, lp);
   return rb_check_launch("att_pack_dqkv");
@@ -317,7 +327,7 @@ RB_EXPORT int rb200_att_rows_gather(const void* src, void* dst, const int* row_b
   if (n_rows <= 0) return RB_OK;
   if (width % 8) return RB_ERR_ARG;
   long long total = (long long)n_rows * (width / 8);
-  att_rows_gather_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, row_batch, row_pos,
+  rb_launch_pdl(att_rows_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, row_batch, row_pos,
                                                                               n_rows, width, lp, to_padded);
   return rb_check_launch("att_rows_gather");
 }

@@ -20,6 +20,33 @@ static inline int rb_check_launch(const char* what) {
   return RB_OK;
 }
 
+// ---- programmatic dependent launch -----------------------------------------------------------------------------------
+// Kernels that follow each other on a stream leave the GPU idle for a few microseconds at every boundary (the last CTAs of
+// one drain, then the next is launched). A kernel launched through rb_launch_pdl may be scheduled while its predecessor
+// still runs: it does the part of its prologue that touches no global memory, then calls rb_pdl_wait(), which returns once
+// the predecessor grid has completed and its writes are visible. Every kernel launched this way MUST call rb_pdl_wait()
+// before its first global-memory access; rb_pdl_launch() (right after it) lets the successor start being scheduled in turn.
+// Launched the ordinary way, both calls do nothing. RETURNN_B200_PDL=0 turns the attribute off.
+__device__ __forceinline__ void rb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void rb_pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool rb_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t rb_launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = rb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

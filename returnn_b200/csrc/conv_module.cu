@@ -94,6 +94,8 @@ glu_dwconv_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restri
 __global__ void __launch_bounds__(256)
 bn_silu_fwd_kernel(const __nv_bfloat16* __restrict__ y, const float* __restrict__ mean, const float* __restrict__ rstd,
                    const float* __restrict__ gamma, const float* __restrict__ beta, __nv_bfloat16* __restrict__ z, long long total, int C) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 >= total) return;
   const int c = (int)(i8 % C);
@@ -113,6 +115,8 @@ __global__ void __launch_bounds__(256)
 bn_silu_bwd_a_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* __restrict__ dz, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ beta,
                      __nv_bfloat16* __restrict__ ds_out, float* __restrict__ part, int n_rows, int C, int rows_per_cta) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   // threads: C/8 column groups x (256 / (C/8)) row lanes; requires C/8 <= 256 and 256 % (C/8) == 0
   extern __shared__ float shm[];  // [row_lanes][2][C]
   const int groups = C / 8;
@@ -165,6 +169,8 @@ __global__ void __launch_bounds__(256)
 bn_silu_bwd_b_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ ds, const float* __restrict__ mean,
                      const float* __restrict__ rstd, const float* __restrict__ gamma, const float* __restrict__ sum_ds,
                      const float* __restrict__ sum_ds_yh, float inv_count, long long total, int C) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const long long i8 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8;
   if (i8 >= total) return;
   const int c = (int)(i8 % C);
@@ -346,6 +352,8 @@ constexpr int kFwd2Rpt = 16;
 __global__ void __launch_bounds__(kFwd2Threads, 2)
 glu_dwconv_fwd2_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ filt, const float* __restrict__ bias,
                        const int* __restrict__ row_batch, __nv_bfloat16* __restrict__ y, float* __restrict__ part, int n_rows, int C, int K) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   __shared__ float sh[NST2 * CC];
   __shared__ int ids[NID2];
   __shared__ float red[2][4][CC];
@@ -431,6 +439,8 @@ constexpr size_t kBwd2Smem = (size_t)2 * NST2 * CC * sizeof(float) + NID2 * size
 __global__ void __launch_bounds__(kBwd2Threads, 1)
 glu_dwconv_bwd2_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ dy, const float* __restrict__ filt,
                        const int* __restrict__ row_batch, __nv_bfloat16* __restrict__ dx, float* __restrict__ part, int n_rows, int C, int K) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   extern __shared__ __align__(16) unsigned char smem2[];
   float* sh_dy = reinterpret_cast<float*>(smem2);  // rows r0 - right ..
   float* sh_h = sh_dy + NST2 * CC;                 // rows r0 - left ..
@@ -550,6 +560,8 @@ __device__ __forceinline__ float lane_sum8(float s, float (*sh)[32], int tl, int
 __global__ void __launch_bounds__(256)
 dwconv_bwd_reduce2_kernel(const float* __restrict__ part, int n_tiles, int C, int K, float* __restrict__ dfilt, float* __restrict__ dbias,
                           int accumulate) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   __shared__ float sh[8][32];
   const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
   const int idx = blockIdx.x * 32 + lane;
@@ -582,6 +594,8 @@ __device__ __forceinline__ void pair_sums(const float* __restrict__ part, int n_
 __global__ void __launch_bounds__(256)
 bn_stats2_kernel(const float* __restrict__ part, int n_tiles, int C, float count, float eps, float momentum, float* __restrict__ mean,
                  float* __restrict__ rstd, float* __restrict__ running_mean, float* __restrict__ running_var) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   __shared__ float sh[8][32];
   const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
   const int c = blockIdx.x * 32 + lane;
@@ -603,6 +617,8 @@ bn_stats2_kernel(const float* __restrict__ part, int n_tiles, int C, float count
 __global__ void __launch_bounds__(256)
 bn_bwd_reduce2_kernel(const float* __restrict__ part, int n_tiles, int C, float* __restrict__ sum_ds, float* __restrict__ sum_ds_yh,
                       float* __restrict__ dgamma_acc, float* __restrict__ dbeta_acc) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   __shared__ float sh[8][32];
   const int lane = threadIdx.x % 32, tl = threadIdx.x / 32;
   const int c = blockIdx.x * 32 + lane;
@@ -644,7 +660,7 @@ RB_EXPORT int rb200_glu_dwconv_fwd(const void* x, const float* filt, const float
   }
   if (K <= KM2) {
     dim3 grid((n_rows + TT2 - 1) / TT2, C / CC);
-    glu_dwconv_fwd2_kernel<<<grid, kFwd2Threads, 0, stream>>>((const __nv_bfloat16*)x, filt, bias, row_batch, (__nv_bfloat16*)y, part, n_rows, C, K);
+    rb_launch_pdl(glu_dwconv_fwd2_kernel, dim3(grid), dim3(kFwd2Threads), 0, stream, (const __nv_bfloat16*)x, filt, bias, row_batch, (__nv_bfloat16*)y, part, n_rows, C, K);
     return rb_check_launch("glu_dwconv_fwd2");
   }
   dim3 grid((n_rows + TT - 1) / TT, C / CC);
@@ -654,7 +670,7 @@ RB_EXPORT int rb200_glu_dwconv_fwd(const void* x, const float* filt, const float
 
 RB_EXPORT int rb200_bn_stats(const float* part, int n_tiles, int C, float count, float eps, float momentum, float* mean, float* rstd,
                              float* running_mean, float* running_var, cudaStream_t stream) {
-  bn_stats2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, n_tiles, C, count, eps, momentum, mean, rstd, running_mean, running_var);
+  rb_launch_pdl(bn_stats2_kernel, dim3((C + 31) / 32), dim3(256), 0, stream, part, n_tiles, C, count, eps, momentum, mean, rstd, running_mean, running_var);
   return rb_check_launch("bn_stats");
 }
 
@@ -663,7 +679,7 @@ RB_EXPORT int rb200_bn_silu_fwd(const void* y, const float* mean, const float* r
   if (n_rows <= 0) return RB_OK;
   if (C % 8) return RB_ERR_ARG;
   long long total = n_rows * C;
-  bn_silu_fwd_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)y, mean, rstd, gamma, beta, (__nv_bfloat16*)z, total, C);
+  rb_launch_pdl(bn_silu_fwd_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)y, mean, rstd, gamma, beta, (__nv_bfloat16*)z, total, C);
   return rb_check_launch("bn_silu_fwd");
 }
 
@@ -681,16 +697,16 @@ RB_EXPORT int rb200_bn_silu_bwd_ex(const void* y, const void* dz, const float* m
   const int row_lanes = 256 / groups;
   const int rows_per_cta = (int)((n_rows + n_tiles - 1) / n_tiles);
   size_t smem = (size_t)row_lanes * 2 * C * sizeof(float);
-  bn_silu_bwd_a_kernel<<<n_tiles, 256, smem, stream>>>((const __nv_bfloat16*)y, (const __nv_bfloat16*)dz, mean, rstd, gamma, beta,
+  rb_launch_pdl(bn_silu_bwd_a_kernel, dim3(n_tiles), dim3(256), smem, stream, (const __nv_bfloat16*)y, (const __nv_bfloat16*)dz, mean, rstd, gamma, beta,
                                                        (__nv_bfloat16*)ds, part, (int)n_rows, C, rows_per_cta);
   int st = rb_check_launch("bn_silu_bwd_a");
   if (st) return st;
-  bn_bwd_reduce2_kernel<<<(C + 31) / 32, 256, 0, stream>>>(part, n_tiles, C, sum_ds, sum_ds_yh, dgamma_acc, dbeta_acc);
+  rb_launch_pdl(bn_bwd_reduce2_kernel, dim3((C + 31) / 32), dim3(256), 0, stream, part, n_tiles, C, sum_ds, sum_ds_yh, dgamma_acc, dbeta_acc);
   st = rb_check_launch("bn_bwd_reduce");
   if (st) return st;
   if (training) {
     long long total = n_rows * C;
-    bn_silu_bwd_b_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)ds, mean, rstd, gamma,
+    rb_launch_pdl(bn_silu_bwd_b_kernel, dim3((unsigned)((total / 8 + 255) / 256)), dim3(256), 0, stream, (const __nv_bfloat16*)y, (__nv_bfloat16*)ds, mean, rstd, gamma,
                                                                                  sum_ds, sum_ds_yh, 1.f / (float)n_rows, total, C);
     st = rb_check_launch("bn_silu_bwd_b");
   }
@@ -726,11 +742,11 @@ RB_EXPORT int rb200_glu_dwconv_bwd_ex(const void* x, const void* dy, const float
     if (row_ctas < 1) row_ctas = 1;
     if (row_ctas > n_tiles2) row_ctas = n_tiles2;
     grid = dim3(row_ctas, C / CC);
-    glu_dwconv_bwd2_kernel<<<grid, kBwd2Threads, kBwd2Smem, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch,
+    rb_launch_pdl(glu_dwconv_bwd2_kernel, dim3(grid), dim3(kBwd2Threads), kBwd2Smem, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, filt, row_batch,
                                                                      (__nv_bfloat16*)dx, part, n_rows, C, K);
     int st2 = rb_check_launch("glu_dwconv_bwd2");
     if (st2) return st2;
-    dwconv_bwd_reduce2_kernel<<<(C * (K + 1) + 31) / 32, 256, 0, stream>>>(part, row_ctas, C, K, dfilt, dbias, accumulate);
+    rb_launch_pdl(dwconv_bwd_reduce2_kernel, dim3((C * (K + 1) + 31) / 32), dim3(256), 0, stream, part, row_ctas, C, K, dfilt, dbias, accumulate);
     return rb_check_launch("dwconv_bwd_reduce2");
   } else {
     static bool attr = false;

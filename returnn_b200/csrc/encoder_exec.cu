@@ -13,6 +13,7 @@
 //   x4 = x3 + 0.5 drop(FF2(LN(x3)));  out = LN(x4)
 #include "common.cuh"
 #include "gemm.h"
+#include <chrono>
 #include <map>
 #include <mutex>
 #include <string>
@@ -79,6 +80,8 @@ namespace {
 __global__ void __launch_bounds__(256, 3)
 colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, float* __restrict__ out, int rows, int C, int rows_per_cta,
               float scale, float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset, unsigned long long site) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   __shared__ float red[32][65];
   const int cg = threadIdx.x & 7, rl = threadIdx.x >> 3;
   const int col = blockIdx.y * 64 + cg * 8;
@@ -153,7 +156,7 @@ int colsum(const void* x, void* y, float* out, int rows, int C, float scale, flo
   if (splits < 1) splits = 1;
   const int rows_per_cta = (rows + splits - 1) / splits;
   splits = (rows + rows_per_cta - 1) / rows_per_cta;
-  colsum_kernel<<<dim3(splits, chunks), 256, 0, s>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, out, rows, C, rows_per_cta, scale, p_drop, seed,
+  rb_launch_pdl(colsum_kernel, dim3(splits, chunks), dim3(256), 0, s, (const __nv_bfloat16*)x, (__nv_bfloat16*)y, out, rows, C, rows_per_cta, scale, p_drop, seed,
                                                      offset, site);
   return rb_check_launch("colsum");
 }
@@ -272,6 +275,7 @@ struct OpProfile {
   std::mutex mu;
   bool enabled = false;
   std::map<std::string, std::pair<long long, double>> table;  // tag -> (count, ms)
+  std::map<std::string, double> host_ms;                       // tag -> host time spent issuing the op
   std::vector<cudaEvent_t> pool;
   cudaEvent_t get() {
     if (!pool.empty()) {
@@ -301,6 +305,8 @@ struct Exec {
   int launches = 0;
   bool prof = false;
   std::vector<std::pair<std::string, cudaEvent_t>> marks;
+  std::vector<double> mark_host_ms;
+  std::chrono::steady_clock::time_point last_host;
 
   Exec(const RbEncDims& dims, const long long* t, const int* l, const int* rb, const int* rp, const long long* sd, const long long* of,
        int* stat, cudaStream_t stream)
@@ -320,7 +326,10 @@ struct Exec {
       std::lock_guard<std::mutex> lk(p.mu);
       ev = p.get();
     }
+    const auto now = std::chrono::steady_clock::now();
+    mark_host_ms.push_back(marks.empty() ? 0.0 : std::chrono::duration<double, std::milli>(now - last_host).count());
     cudaEventRecord(ev, s);
+    last_host = std::chrono::steady_clock::now();  // the event record itself is not the op's cost
     std::string t(tag ? tag : "?");
     const size_t par = t.find('(', 1);
     if (par != std::string::npos) t.resize(par);
@@ -339,9 +348,11 @@ struct Exec {
         slot.first += 1;
         slot.second += ms;
       }
+      p.host_ms[marks[i].first] += mark_host_ms[i];
     }
     for (auto& m : marks) p.pool.push_back(m.second);
     marks.clear();
+    mark_host_ms.clear();
   }
 
   const float* p32(int l, int i) const { return reinterpret_cast<const float*>(tab[((size_t)l * P_COUNT + i) * 3 + 0]); }
@@ -694,12 +705,13 @@ RB_EXPORT int rb200_colsum_bf16(const void* x, float* out, int rows, int C, cuda
   return colsum(x, nullptr, out, rows, C, 1.f, 0.f, nullptr, nullptr, 0, stream);
 }
 
-// per-op timing of the executor calls: enable/disable (clears the table), and a text report "tag count total_ms" per line
+// per-op timing of the executor calls: enable/disable (clears the table), and a text report "tag count device_ms host_ms" per line
 RB_EXPORT int rb200_enc_profile_enable(int on) {
   OpProfile& p = op_profile();
   std::lock_guard<std::mutex> lk(p.mu);
   p.enabled = on != 0;
   p.table.clear();
+  p.host_ms.clear();
   return RB_OK;
 }
 
@@ -709,7 +721,8 @@ RB_EXPORT int rb200_enc_profile_report(char* buf, int len) {
   std::string out;
   for (const auto& kv : p.table) {
     char line[256];
-    snprintf(line, sizeof(line), "%s %lld %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second);
+    const auto h = p.host_ms.find(kv.first);
+    snprintf(line, sizeof(line), "%s %lld %.6f %.6f\n", kv.first.c_str(), kv.second.first, kv.second.second, h == p.host_ms.end() ? 0.0 : h->second);
     out += line;
   }
   if (buf && len > 0) {

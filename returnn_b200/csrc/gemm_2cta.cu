@@ -110,6 +110,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   cluster_sync();  // barriers of both CTAs are initialised before anyone signals across
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: it may overlap the tail of the preceding kernel
+  rb_pdl_wait();
+  rb_pdl_launch();
 
   if (warp == 0) {
     if (lane == 0) {
@@ -294,7 +297,7 @@ int rb_gemm_pair(const RbGemm& g, cudaStream_t stream) {
   st = g.b_mn_major ? make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, 64, BK) : make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, BK, BN / 2);
   if (st) return st;
   int pairs = p.units < pairs_max ? p.units : pairs_max;
-  if (full) gemm_pair_kernel<true><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
-  else gemm_pair_kernel<false><<<2 * pairs, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
+  if (full) rb_launch_pdl(gemm_pair_kernel<true>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
+  else rb_launch_pdl(gemm_pair_kernel<false>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
   return rb_check_launch("gemm_pair");
 }

@@ -77,6 +77,9 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
+  // everything above touched no global memory: it may overlap the tail of the preceding kernel
+  rb_pdl_wait();
+  rb_pdl_launch();
   if (warp == 0) {
     if (lane == 0) {
       // ---------------- TMA producer ----------------
@@ -266,8 +269,8 @@ int launch(const RbGemm& g, cudaStream_t stream) {
     }
     if (cap > 0 && grid > cap) grid = cap;
   }
-  if (full) gemm_persist_kernel<BN, true><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
-  else gemm_persist_kernel<BN, false><<<grid, kThreads, kSmemBytes, stream>>>(tm_a, tm_b, p);
+  if (full) rb_launch_pdl(gemm_persist_kernel<BN, true>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
+  else rb_launch_pdl(gemm_persist_kernel<BN, false>, dim3(grid), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
   return rb_check_launch("gemm_persist");
 }
 

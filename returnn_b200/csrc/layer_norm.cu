@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32)
 ln_fwd_kernel(const void* __restrict__ x, const void* __restrict__ gamma, const void* __restrict__ beta,
               void* __restrict__ y, float* __restrict__ mean_out, float* __restrict__ rstd_out,
               int64_t rows, int n, float eps, int x_bf16, int w_bf16, int rms) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
   if (row >= rows) return;
@@ -214,6 +216,8 @@ ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
                   const float* __restrict__ mean_in, const float* __restrict__ rstd_in, __nv_bfloat16* __restrict__ dx,
                   float* __restrict__ dgamma, float* __restrict__ dbeta, int64_t rows, int n, int w_bf16, int rms,
                   const __nv_bfloat16* __restrict__ dres) {
+  rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
+  rb_pdl_launch();
   extern __shared__ float smem[];  // [2][n]
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -360,7 +364,7 @@ RB_EXPORT int rb200_layer_norm_fwd(const void* x, const void* gamma, const void*
   }
   dim3 grid((unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta)), block(kWarpsPerCta * 32);
   int chunks = (n + 255) / 256;
-#define LN_FWD(C) ln_fwd_kernel<C><<<grid, block, 0, stream>>>(x, gamma, beta, y, mean, rstd, rows, n, eps, x_bf16, w_bf16, rms)
+#define LN_FWD(C) rb_launch_pdl(ln_fwd_kernel<C>, dim3(grid), dim3(block), 0, stream, x, gamma, beta, y, mean, rstd, rows, n, eps, x_bf16, w_bf16, rms)
   if (chunks <= 1) LN_FWD(1);
   else if (chunks <= 2) LN_FWD(2);
   else if (chunks <= 4) LN_FWD(4);
@@ -385,7 +389,7 @@ RB_EXPORT int rb200_layer_norm_bwd_ex(const void* x, const void* dy, const void*
     const size_t sm = (size_t)2 * n * sizeof(float);
     const int ch = (n + 255) / 256;
 #define LN_ACC(C)                                                                                                                       \
-  ln_bwd_acc_kernel<C><<<ctas, kBwdAccWarps * 32, sm, stream>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, gamma, mean, rstd, \
+  rb_launch_pdl(ln_bwd_acc_kernel<C>, dim3(ctas), dim3(kBwdAccWarps * 32), sm, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, gamma, mean, rstd, \
                                                                  (__nv_bfloat16*)dx, dgamma, dbeta, rows, n, w_bf16, rms,              \
                                                                  (const __nv_bfloat16*)dres)
     if (ch <= 1) LN_ACC(1);

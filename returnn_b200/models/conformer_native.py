@@ -247,7 +247,7 @@ def profile_ops(enable: bool):
 
 
 def profile_report() -> dict:
-    """:return: ``{op tag: (calls, total milliseconds)}`` collected since :func:`profile_ops` was enabled"""
+    """:return: ``{op tag: (calls, device milliseconds, host milliseconds spent issuing)}`` collected since :func:`profile_ops` was enabled"""
     import ctypes
     from ..ops import _lib
 
@@ -257,6 +257,6 @@ def profile_report() -> dict:
     fn(buf, size + 16)
     res = {}
     for line in buf.value.decode("utf8").splitlines():
-        tag, count, ms = line.rsplit(" ", 2)
-        res[tag] = (int(count), float(ms))
+        tag, count, ms, host = line.rsplit(" ", 3)
+        res[tag] = (int(count), float(ms), float(host))
     return res
