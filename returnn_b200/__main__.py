@@ -119,7 +119,7 @@ def init_data():
     seq_ordering = config.value("batching", "default")
     dev_data = load_data(config, dev_cache, "dev", seq_ordering="sorted", **({} ))
     eval_data = load_data(config, eval_cache, "eval", seq_ordering="sorted")
-    if task in ("train", "nop_init_net_train") or config.bool("need_data", False):
+    if task in ("train", "nop_init_net_train", "compute_priors") or config.bool("need_data", False):
         train_data = load_data(config, train_cache, "train", seq_ordering=seq_ordering)
     else:
         train_data = None

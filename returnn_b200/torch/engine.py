@@ -134,6 +134,7 @@ class Engine(EngineBase):
         self._tensorboard_writer = None
         self._tensorboard_opts = config.typed_value("tensorboard_opts", {}) or {}
         self._graph_step = None
+        self._epoch_mp_pending = 0
         self._nvtx = config.bool("torch_nvtx_ranges", False) and self._device.startswith("cuda")
 
     # -- setup -------------------------------------------------------------------------------------------------------
@@ -225,6 +226,8 @@ class Engine(EngineBase):
             os.kill(os.getpid(), signal.SIGINT)
 
     def _epoch_mp_shared_set(self, epoch: int):
+        """the epoch that dataset workers (or the in-process data pipe) pick up at their next reset"""
+        self._epoch_mp_pending = epoch  # a value created later (first data loader) starts from it
         if self._epoch_mp_shared is not None:
             self._epoch_mp_shared.value = epoch
 
@@ -562,9 +565,9 @@ class Engine(EngineBase):
             from ..utils.multi_proc_manager_with_watchdog import create_manager
 
             self._mp_manager = create_manager()
-            self._epoch_mp_shared = self._mp_manager.Value("i", 0)
+            self._epoch_mp_shared = self._mp_manager.Value("i", self._epoch_mp_pending)
         if self._epoch_mp_shared is None:
-            self._epoch_mp_shared = _LocalValue(0)
+            self._epoch_mp_shared = _LocalValue(self._epoch_mp_pending)
         if not dataset_init_epoch:
             reset_cb = returnn_dataset_wrapper.ReturnnDatasetResetNoOpCallback()
         else:

@@ -1,0 +1,212 @@
+"""CPU tests of the utility modules: bpe, fsa builders, lru cache, math helpers, pretty printer, numpy backend, pretrain schedules,
+hot reload, torch array helpers, inf/nan tracer, native code compiler."""
+
+import io
+import itertools
+import os
+import sys
+import time
+
+import numpy
+import pytest
+import torch
+
+
+def test_bpe_standard_and_sampling(tmp_path):
+    from returnn_b200.utils.bpe import StandardBytePairEncoder, SamplingBytePairEncoder, PrefixTree, BpeOpts, CharSyncSearch
+
+    codes = tmp_path / "codes.txt"
+    codes.write_text("#version: 0.2\nl o\nlo w</w>\ne r</w>\nn e\nne w\nnew er</w>\n")
+    bpe = StandardBytePairEncoder(str(codes))
+    assert bpe.segment_sentence("low newer lower") == ["low", "newer", "lo@@", "w@@", "er"]
+    bpe2 = StandardBytePairEncoder(str(codes), labels=["low", "n@@", "e@@", "w@@", "er", "l@@", "o@@", "ne@@"])
+    assert bpe2.segment_sentence("newer") == ["ne@@", "w@@", "er"]
+    labels = ["a", "b", "ab", "a@@", "b@@", "ab@@", "c"]
+    tree = PrefixTree(opts=BpeOpts(label_postfix_merge_symbol="@@"))
+    for lab in labels:
+        tree.add(lab)
+    segs = sorted(CharSyncSearch(tree, "abab").search())
+    assert segs == [["a@@", "b@@", "a@@", "b"], ["a@@", "b@@", "ab"], ["ab@@", "a@@", "b"], ["ab@@", "ab"]]
+    greedy = SamplingBytePairEncoder(labels=labels, breadth_prob=0.0, rnd=numpy.random.RandomState(1), unknown_label="<unk>")
+    assert greedy.segment_sentence("abab abc x") == ["ab@@", "ab", "ab@@", "c", "<unk>"]
+    fine = SamplingBytePairEncoder(labels=labels, breadth_prob=1.0, rnd=numpy.random.RandomState(1), unknown_label="<unk>")
+    assert fine.segment_sentence("abab") == ["a@@", "b@@", "a@@", "b"]
+    for seg in (greedy, fine):
+        assert "".join(s.replace("@@", "") for s in seg.segment_sentence("abab")) == "abab"
+
+
+def test_fsa_ctc_unique_paths_and_builders():
+    from returnn_b200.utils import fsa as F
+
+    batch = F.get_ctc_fsa_fast_bw(targets=numpy.array([[1, 2, 2], [3, 0, 0]]), seq_lens=numpy.array([3, 1]), blank_idx=0)
+    assert batch.edges.shape[0] == 4 and batch.start_end_states.shape == (2, 2)
+
+    def count_paths(b, string):
+        e = batch.edges
+        states = {int(batch.start_end_states[0, b]): 1}
+        for ch in string:
+            nxt = {}
+            for i in range(e.shape[1]):
+                if e[3, i] == b and e[2, i] == ch and int(e[0, i]) in states:
+                    nxt[int(e[1, i])] = nxt.get(int(e[1, i]), 0) + states[int(e[0, i])]
+            states = nxt
+        return states.get(int(batch.start_end_states[1, b]), 0)
+
+    def collapse(s):
+        return [x for x in (k for k, _ in itertools.groupby(s)) if x != 0]
+
+    for s in itertools.product([0, 1, 2], repeat=5):
+        assert count_paths(0, s) == (1 if collapse(s) == [1, 2, 2] else 0), s
+    g = F.Graph("ab ba")
+    F.Ctc(g).run()
+    assert g.num_states_ctc == 2 * 5 + 1
+    F.Asg(F.Graph("aab")).run()
+    hmm = F.Hmm(F.Graph("hi yo"))
+    hmm.load_lexicon({"hi": [["h", "i"]], "yo": [["y", "o"], ["j", "o"]]})
+    assert hmm.run().num_states_hmm == 3 + 5 + 2 * 5
+    stairs = F.fast_bw_fsa_staircase([3, 2], with_loop=True, max_skip=1)
+    assert stairs.edges.shape[1] == 13
+    shared = F.FastBwFsaShared()
+    shared.add_inf_loop(0, 4)
+    assert shared.get_fast_bw_fsa(2).edges.shape == (4, 8)
+
+
+def test_lru_cache_and_math():
+    from returnn_b200.utils.lru_cache import lru_cache
+    from returnn_b200.utils.math import PiecewiseLinear, StepFunction, next_power_of_two, ceil_div, merge_random_seeds, simplify_and_format_number
+
+    calls = []
+
+    @lru_cache(maxsize=2)
+    def f(x):
+        calls.append(x)
+        return 2 * x
+
+    f(1), f(2), f(3)
+    assert f.cache_len() == 2 and f.cache_peek(1) is None and f.cache_peek(3) == 6
+    f.cache_set(7, 99)
+    assert f(7) == 99 and 7 not in calls
+    assert f.cache_pop(7) == 99 and f.cache_peek(7, fallback="no") == "no"
+    f.cache_set_maxsize(1)
+    assert f.cache_len() == 1
+    f.cache_clear()
+    assert f.cache_info().currsize == 0
+    assert abs(PiecewiseLinear({0: 0.0, 10: 1.0})(5) - 0.5) < 1e-9 and PiecewiseLinear({1: 3.0})(100) == 3.0
+    step = StepFunction({0: 1, 5: 2})
+    assert step(4) == 1 and step(5) == 2 and step(-3) == 1
+    assert next_power_of_two(17) == 32 and next_power_of_two(1) == 1 and ceil_div(7, 2) == 4
+    assert merge_random_seeds([1, 2]) != merge_random_seeds([2, 1]) and simplify_and_format_number(3.0) == "3"
+
+
+def test_pprint_and_collect_outputs():
+    from returnn_b200.utils.pprint import pformat
+    from returnn_b200.utils.collect_outputs_dict import CollectOutputsDict, is_key_allowed_in_collect_outputs_dict
+
+    obj = {"a": 1, "net": {"x": [1, 2, 3], "y": {"class": "linear", "n_out": 5}}, "t": (1,), "arr": numpy.arange(3)}
+    text = pformat(obj)
+    back = eval(text, {"numpy": numpy})
+    assert back["net"] == obj["net"] and back["t"] == (1,) and list(back["arr"]) == [0, 1, 2]
+    d = CollectOutputsDict(allowed_key_patterns=["enc_*", "out"])
+    d["enc_3"] = 1
+    d["dec_1"] = 2
+    d.update({"out": 3, "other": 4})
+    assert dict(d) == {"enc_3": 1, "out": 3} and not is_key_allowed_in_collect_outputs_dict(d, "x") and is_key_allowed_in_collect_outputs_dict({}, "x")
+
+
+def test_numpy_backend():
+    from returnn_b200.tensor import Tensor, Dim, batch_dim
+    import returnn_b200.frontend as rf
+
+    t = Dim(None, name="t")
+    t.dyn_size_ext = Tensor("l", dims=[batch_dim], dtype="int32", raw_tensor=numpy.array([3, 2], dtype="int32"))
+    x = Tensor("x", dims=[batch_dim, t], dtype="float32", raw_tensor=numpy.arange(6, dtype="float32").reshape(2, 3))
+    y = x * 2.0 + 1.0
+    assert isinstance(y.raw_tensor, numpy.ndarray) and y.raw_tensor.tolist() == [[1.0, 3.0, 5.0], [7.0, 9.0, 11.0]]
+    assert (x > 2.0).raw_tensor.tolist() == [[False, False, False], [True, True, True]]
+    assert rf.reduce_sum(x, axis=t).raw_tensor.tolist() == [3.0, 7.0]  # the padded frame of the second sequence is ignored
+    assert rf.reduce_mean(x, axis=t).raw_tensor.tolist() == [1.0, 3.5]
+    assert rf.reduce_max(x, axis=t).raw_tensor.tolist() == [2.0, 4.0]
+    # torch tensors are untouched by the dispatch
+    a = Tensor("a", dims=[batch_dim], dtype="float32", raw_tensor=torch.ones(2))
+    assert isinstance((a + 1).raw_tensor, torch.Tensor)
+
+
+def test_pretrain_schedule():
+    from returnn_b200.pretrain import Pretrain
+
+    net = {"l1": {"class": "linear", "from": "data"}, "l2": {"class": "linear", "from": "l1"}, "l3": {"class": "linear", "from": "l2"},
+           "output": {"class": "softmax", "from": "l3"}}
+    p = Pretrain(net, repetitions={"default": 2, "final": 1})
+    assert p.get_train_num_epochs() == 5
+    assert sorted(p.get_network_json_for_epoch(1)) == ["l3", "output"] and p.get_network_json_for_epoch(1)["l3"]["from"] == ["data"]
+    assert p.get_network_json_for_epoch(5) == net and p.get_network_json_for_epoch(99) == net
+    p2 = Pretrain(net, construction_algo="from_input")
+    assert sorted(p2.get_network_json_for_epoch(1)) == ["l1", "output"] and p2.get_network_json_for_epoch(1)["output"]["from"] == ["l1"]
+    p3 = Pretrain(net, construction_algo=lambda idx, d: None if idx >= 1 else {"output": dict(d["output"], **{"from": "data"})})
+    assert p3.get_train_num_epochs() == 2
+
+
+def test_hot_reload(tmp_path):
+    from returnn_b200.utils.hot_reload import ConfigHotReloader
+
+    mod = tmp_path / "usermod_hot_reload_test.py"
+    mod.write_text("def f():\n    return 1\n")
+    sys.path.insert(0, str(tmp_path))
+    try:
+        import usermod_hot_reload_test as m
+
+        cfg = {"train_step": m.f, "nested": {"fns": [m.f]}, "n": 3}
+        reloader = ConfigHotReloader(cfg)
+        assert reloader.modules == ["usermod_hot_reload_test"] and not reloader.any_module_changed()
+        mod.write_text("def f():\n    return 2\n")
+        future = time.time() + 5
+        os.utime(str(mod), (future, future))
+        assert reloader.any_module_changed()
+        reloader.reload_changed_modules()
+        assert cfg["train_step"]() == 2 and cfg["nested"]["fns"][0]() == 2 and cfg["n"] == 3
+    finally:
+        sys.path.remove(str(tmp_path))
+        sys.modules.pop("usermod_hot_reload_test", None)
+
+
+def test_torch_array_helpers_and_tracer():
+    from returnn_b200.torch.util import array_, scaled_gradient, rope, module as module_util
+    from returnn_b200.torch.util.debug_inf_nan import debug_inf_nan
+
+    x = torch.arange(24.0).reshape(2, 3, 4).requires_grad_(True)
+    m = torch.tensor([[1, 0, 1], [0, 1, 1]], dtype=torch.bool)
+    out, n = array_.masked_select_bound(x, m, bound=5)
+    assert out.shape == (5, 4) and int(n) == 4 and torch.equal(out[:4], x[m]) and float(out[4].abs().sum()) == 0.0
+    out.sum().backward()
+    assert torch.equal(x.grad[:, :, 0], m.float())
+    assert torch.equal(array_.masked_select(x, m), x[m]) and array_.nonzero(m.flatten(), out_len=4).tolist() == [0, 2, 4, 5]
+    assert array_.sequence_mask(torch.tensor([1, 3])).tolist() == [[True, False, False], [True, True, True]]
+    assert array_.sequence_mask_time_major(torch.tensor([1, 3])).shape == (3, 2)
+    y = torch.ones(3, requires_grad=True)
+    scaled_gradient.scaled_gradient(y, -2.0).sum().backward()
+    assert y.grad.tolist() == [-2.0, -2.0, -2.0]
+    ang = torch.rand(5, 4)
+    v = torch.randn(5, 8)
+    r = rope.apply_rope(v, torch.cat([ang.sin(), ang.cos()], -1))
+    torch.testing.assert_close(r.norm(dim=-1), v.norm(dim=-1))  # a rotation
+    lin = torch.nn.Linear(2, 2)
+    module_util.convert_parameters_to_buffers(lin, ["bias"], persistent=False)
+    assert "bias" not in dict(lin.named_parameters()) and "bias" not in lin.state_dict() and lin(torch.zeros(1, 2)).shape == (1, 2)
+    buf = io.StringIO()
+    debug_inf_nan(lambda: torch.log(torch.zeros(3)) * 0, file=buf, report_every_op_call=False)
+    assert "aten::log" in buf.getvalue() and "3 inf" in buf.getvalue()
+
+
+def test_native_code_compiler(tmp_path, monkeypatch):
+    from returnn_b200.utils import basic
+    from returnn_b200.utils.native_code_compiler import NativeCodeCompiler
+
+    monkeypatch.setattr(basic, "get_cache_dir", lambda: str(tmp_path))
+    src = 'extern "C" int add(int a, int b) { return a + b; }'
+    c = NativeCodeCompiler("t_add", code=src)
+    assert c.load_lib_ctypes().add(2, 3) == 5
+    mtime = os.path.getmtime(c.get_lib_filename())
+    c2 = NativeCodeCompiler("t_add", code=src)
+    assert c2.get_lib_filename() == c.get_lib_filename() and os.path.getmtime(c2.get_lib_filename()) == mtime  # cached
+    with pytest.raises(RuntimeError):
+        NativeCodeCompiler("t_bad", code="this is not C++")
