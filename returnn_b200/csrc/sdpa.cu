@@ -1,0 +1,129 @@
+// Scaled-dot-product attention for self, causal and cross attention (decoder layers, Transformer encoders): the softmax stage
+// between the tcgen05 batched GEMMs  S = scale * Q K^T,  O = dropout(P) V  and, backward,  dP = dO V^T,  dQ = scale * dS K,
+// dK = scale * dS^T Q,  dV = dropout(P)^T dO.
+//
+// Score buffers are [B*H, Tqp, Tkp] with Tqp, Tkp = the lengths rounded up to 64: the GEMMs contract over key positions
+// (O, dQ) or query positions (dK, dV) in blocks of 64, so the margins [Tk, Tkp) and [Tq, Tqp) are written as zeros here and
+// the buffers need no memset. A key j of batch entry b is visible to query i iff j < k_lens[b] (k_lens may be null: all Tk) and,
+// for causal attention, j <= i + causal_shift (causal_shift = Tk - Tq: the last query sees all keys; 0 for self attention).
+// One warp per query row; rows are walked in three passes (max, sum, write), the row stays in L1/L2.
+//
+// Reference semantics: returnn/frontend/_backend.py:1575-1647 (scaled_dot_product_attention: matmul, mask, softmax, dropout,
+// matmul; causal via a mask on the upper triangle).
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ uint32_t rng_u32(uint64_t seed, uint64_t idx) {
+  uint4 r = philox4x32(make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)), make_uint4((uint32_t)(idx >> 2), (uint32_t)(idx >> 34), 0x51u, 0u));
+  const uint32_t sel = (uint32_t)(idx & 3);
+  return sel == 0 ? r.x : sel == 1 ? r.y : sel == 2 ? r.z : r.w;
+}
+
+__device__ __forceinline__ int visible_keys(int i, int tk, int klen, int causal, int causal_shift) {
+  int n = klen < tk ? klen : tk;
+  if (causal) {
+    const int c = i + causal_shift + 1;
+    n = c < n ? c : n;
+  }
+  return n < 0 ? 0 : n;
+}
+
+// s [BH, Tqp, Tkp] fp32 (rows < Tq, columns < Tk valid) -> p, pd [BH, Tqp, Tkp] bf16 (pd only with dropout)
+__global__ void __launch_bounds__(128)
+sdpa_softmax_fwd_kernel(const float* __restrict__ s, __nv_bfloat16* __restrict__ p, __nv_bfloat16* __restrict__ pd,
+                        const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
+                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  if (i >= tqp) return;
+  const long long row = ((long long)z * tqp + i) * tkp;
+  const bool drop = p_drop > 0.f;
+  const __nv_bfloat16 zero = __float2bfloat16(0.f);
+  const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
+  float mx = -INFINITY;
+  for (int j = lane; j < n; j += 32) mx = fmaxf(mx, s[row + j]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int j = lane; j < n; j += 32) sum += __expf(s[row + j] - mx);
+  sum = warp_sum(sum);
+  const float inv = n > 0 ? 1.f / sum : 0.f;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+  for (int j = lane; j < tkp; j += 32) {
+    if (j < n) {
+      const float pr = __expf(s[row + j] - mx) * inv;
+      p[row + j] = __float2bfloat16(pr);
+      if (drop) pd[row + j] = __float2bfloat16(rng_u32(sd, off + (uint64_t)(row + j)) >= thresh ? pr * keep_scale : 0.f);
+    } else {
+      p[row + j] = zero;
+      if (drop) pd[row + j] = zero;
+    }
+  }
+}
+
+// p [BH, Tqp, Tkp] bf16, dpd fp32 (gradient w.r.t. the dropped probabilities) -> ds bf16 = p * (dp - sum_j p dp), dp = mask * dpd / (1-p)
+__global__ void __launch_bounds__(128)
+sdpa_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, const float* __restrict__ dpd, __nv_bfloat16* __restrict__ ds,
+                        const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
+                        float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  if (i >= tqp) return;
+  const long long row = ((long long)z * tqp + i) * tkp;
+  const bool drop = p_drop > 0.f;
+  const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+  auto dp_at = [&](int j) {
+    float d = dpd[row + j];
+    if (drop) d = rng_u32(sd, off + (uint64_t)(row + j)) >= thresh ? d * keep_scale : 0.f;
+    return d;
+  };
+  float delta = 0.f;
+  for (int j = lane; j < n; j += 32) delta += __bfloat162float(p[row + j]) * dp_at(j);
+  delta = warp_sum(delta);
+  for (int j = lane; j < tkp; j += 32) {
+    float v = 0.f;
+    if (j < n) v = __bfloat162float(p[row + j]) * (dp_at(j) - delta);
+    ds[row + j] = __float2bfloat16(v);
+  }
+}
+
+}  // namespace
+
+RB_EXPORT int rb200_sdpa_softmax_fwd(const float* s, void* p, void* pd, const int* k_lens, int batch, int heads, int tq, int tk, int tqp, int tkp,
+                                     int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
+                                     cudaStream_t stream) {
+  if (batch <= 0 || tqp <= 0) return RB_OK;
+  if (tqp % 64 || tkp % 64 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !pd || !(p_drop < 1.f)))) {
+    rb_set_error("sdpa_softmax_fwd: padded extents must be multiples of 64 (tq %d/%d tk %d/%d); dropout needs seed, offset and pd", tq, tqp, tk, tkp);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((tqp + 3) / 4, batch * heads);
+  rb_launch_pdl(sdpa_softmax_fwd_kernel, grid, dim3(128), 0, stream, s, (__nv_bfloat16*)p, (__nv_bfloat16*)pd, k_lens, heads, tq, tk, tqp, tkp, causal,
+                causal_shift, p_drop, seed, offset);
+  return rb_check_launch("sdpa_softmax_fwd");
+}
+
+RB_EXPORT int rb200_sdpa_softmax_bwd(const void* p, const float* dpd, void* ds, const int* k_lens, int batch, int heads, int tq, int tk, int tqp,
+                                     int tkp, int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
+                                     cudaStream_t stream) {
+  if (batch <= 0 || tqp <= 0) return RB_OK;
+  if (tqp % 64 || tkp % 64 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !(p_drop < 1.f)))) {
+    rb_set_error("sdpa_softmax_bwd: padded extents must be multiples of 64 (tq %d/%d tk %d/%d)", tq, tqp, tk, tkp);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((tqp + 3) / 4, batch * heads);
+  rb_launch_pdl(sdpa_softmax_bwd_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)p, dpd, (__nv_bfloat16*)ds, k_lens, heads, tq, tk, tqp, tkp,
+                causal, causal_shift, p_drop, seed, offset);
+  return rb_check_launch("sdpa_softmax_bwd");
+}

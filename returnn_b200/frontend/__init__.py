@@ -58,3 +58,8 @@ from .control_flow import control_flow_ctx, get_current_control_flow_ctx
 from .backend_select import select_backend_torch, select_backend_returnn_layers_tf, is_executing_eagerly, get_backend_name
 
 set_random_seed(42)
+
+# native dimension bookkeeping when the extension is built (RETURNN_B200_RF_NATIVE=0 keeps the Python versions)
+from . import _native as _native_opt  # noqa: E402
+
+_native_opt.setup()

@@ -32,8 +32,13 @@ def available(*tensors) -> bool:
 
 
 def supports_sdpa(q, k, v, causal: bool) -> bool:
-    """padded sdpa kernel: not built, the torch math is used"""
-    return False
+    """``[B, H, T, D]`` operands (bf16 or under bf16 autocast) with a head dim that fills the 64-wide contraction blocks"""
+    if q.dim() != 4 or k.dim() != 4 or v.shape != k.shape or q.shape[:2] != k.shape[:2] or q.shape[-1] != k.shape[-1]:
+        return False
+    if q.dtype != torch.bfloat16 and not (q.dtype == torch.float32 and torch.is_autocast_enabled() and torch.get_autocast_gpu_dtype() == torch.bfloat16):
+        return False
+    d = q.shape[-1]
+    return d % 64 == 0 and d <= 256 and q.shape[2] > 0 and k.shape[2] > 0
 
 
 def supports_rel_pos(q, k, v, pos) -> bool:
@@ -198,8 +203,21 @@ def rel_pos_attention_packed(qkv, pos, u, v, pack, *, num_heads: int, head_dim: 
 
 
 def sdpa(q, k, v, *, kv_lens, scale, causal, dropout_p):
-    """not built"""
-    raise NotImplementedError
+    """``[B, H, T, D]`` layout of the RF attention functions -> the ``[B, T, H*D]`` kernels of :mod:`returnn_b200.ops.sdpa`"""
+    from . import sdpa as _sdpa
+
+    B, H, Tq, D = q.shape
+    Tk = k.shape[2]
+    q3 = q.transpose(1, 2).reshape(B, Tq, H * D)
+    k3 = k.transpose(1, 2).reshape(B, Tk, H * D)
+    v3 = v.transpose(1, 2).reshape(B, Tk, H * D)
+    lens = None
+    if kv_lens is not None:
+        lens = kv_lens
+        while lens.dim() > 1:  # given per (batch, head): the heads share the lengths
+            lens = lens[..., 0]
+    o = _sdpa.sdpa(q3, k3, v3, num_heads=H, k_lens=lens, causal=causal, scale=scale, dropout_p=dropout_p)
+    return o.view(B, Tq, H, D).transpose(1, 2)
 
 
 def rel_pos_attention(q, k, v, pos, u, vb, lens, *, scale, dropout_p):

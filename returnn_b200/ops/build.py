@@ -94,6 +94,17 @@ def build_host(force: bool = False, verbose: bool = False) -> List[str]:
         if force or _newer(lib, main_srcs):
             _run([gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-o", lib] + main_srcs + ["-ldl", "-lpthread"], verbose)
         res.append(lib)
+    # CPython extension with the frontend's dimension bookkeeping (needs the Python headers)
+    pyext = os.path.join(_CSRC, "pyext", "rf_native.cpp")
+    if os.path.exists(pyext):
+        import sysconfig
+
+        inc = sysconfig.get_paths().get("include")
+        if inc and os.path.exists(os.path.join(inc, "Python.h")):
+            lib = os.path.join(_BUILD, "_rf_native.so")
+            if force or _newer(lib, [pyext]):
+                _run([gxx, "-O2", "-std=c++17", "-shared", "-fPIC", "-I", inc, "-o", lib, pyext], verbose)
+            res.append(lib)
     atfork = os.path.join(host_dir, "atfork_patch.cpp")
     if os.path.exists(atfork):
         lib = os.path.join(_BUILD, "librb200_atfork.so")

@@ -182,6 +182,84 @@ def try_create_param_averager(arena: ParamArena, *, rank: int, world: int, requi
         return None
 
 
+class SmallVectorAllReduce:
+    """
+    Sum of a small fp32 vector over the ranks through symmetric memory (one CTA per rank: flags, peer loads, peer stores):
+    the cross-rank exchange of batch-norm statistics (``[C]`` sums, ``[C]`` sums of squares, a count). Latency of one kernel
+    instead of a library collective; the same kernel as the gradient all-reduce on a buffer of its own.
+    """
+
+    def __init__(self, *, device, rank: int, world: int, capacity: int = 8192, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.rank, self.world, self.capacity = rank, world, capacity
+        group = group or dist.group.WORLD
+        self._buf = symm_mem.empty(capacity, dtype=torch.float32, device=device)
+        self._buf.zero_()
+        self._hdl = symm_mem.rendezvous(self._buf, group)
+        lib = _lib.get_lib(required=True)
+        lib.rb200_fused_allreduce_flag_words.restype = ctypes.c_int
+        words = int(lib.rb200_fused_allreduce_flag_words())
+        self._flags = symm_mem.empty(words, dtype=torch.int32, device=device)
+        self._flags.zero_()
+        self._hdl_flags = symm_mem.rendezvous(self._flags, group)
+        self._norm = symm_mem.empty(8, dtype=torch.float32, device=device)
+        self._norm.zero_()
+        self._hdl_norm = symm_mem.rendezvous(self._norm, group)
+        self._bufs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl.buffer_ptrs])
+        self._flag_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_flags.buffer_ptrs])
+        self._norm_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_norm.buffer_ptrs])
+        self._epoch = 1
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._fn = _lib.bind("rb200_fused_allreduce", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _f32, _u32, _i32, _i32, _vp, _vp])
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def supports(self, x: torch.Tensor) -> bool:
+        """fp32 CUDA tensor that fits"""
+        return x.is_cuda and x.dtype == torch.float32 and 0 < x.numel() <= self.capacity
+
+    def all_reduce_sum(self, x: torch.Tensor) -> torch.Tensor:
+        """:return: new tensor = sum of x over all ranks; every rank must call this in the same order"""
+        n = x.numel()
+        n4 = (n + 3) // 4 * 4
+        self._buf[:n].copy_(x.reshape(-1))
+        if n4 > n:
+            self._buf[n:n4].zero_()
+        # plain peer loads: a few hundred bytes gain nothing from the multicast mapping
+        _lib.check(self._fn(ctypes.addressof(self._bufs), ctypes.addressof(self._flag_ptrs), ctypes.addressof(self._norm_ptrs), None, self.world,
+                            self.rank, 0, n4, 1.0, self._epoch, 0, 1, self._status.data_ptr(), _lib.stream_ptr()), "small_vector_allreduce")
+        _lib.count_launch()
+        self._epoch += 2
+        return self._buf[:n].clone().reshape(x.shape)
+
+
+_small_reducer: Optional[SmallVectorAllReduce] = None
+
+
+def get_small_reducer() -> Optional[SmallVectorAllReduce]:
+    """the process-wide small-vector reducer, if :func:`try_create_small_reducer` made one"""
+    return _small_reducer
+
+
+def try_create_small_reducer(*, device, rank: int, world: int, group=None) -> Optional[SmallVectorAllReduce]:
+    """create the process-wide reducer for statistics; None (and NCCL is used) where symmetric memory is not available"""
+    global _small_reducer
+    try:
+        lib = _lib.get_lib()
+        if torch.device(device).type != "cuda" or lib is None or not hasattr(lib, "rb200_fused_allreduce"):
+            raise RuntimeError("needs CUDA and the kernel library")
+        if os.environ.get("RETURNN_B200_FUSED_ALLREDUCE", "1") != "1":
+            raise RuntimeError("disabled by RETURNN_B200_FUSED_ALLREDUCE")
+        _small_reducer = SmallVectorAllReduce(device=device, rank=rank, world=world, group=group)
+    except Exception as exc:
+        from ..log import log
+
+        print("Small-vector NVLink all-reduce not available (%s: %s), using torch.distributed." % (type(exc).__name__, exc), file=log.v4)
+        _small_reducer = None
+    return _small_reducer
+
+
 def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedAllReduce]:
     """the fused reducer, or None if it cannot be used here"""
     try:

@@ -90,9 +90,20 @@ def main():
     t_fused = timed(run_fused)
     t_nccl = timed(run_nccl)
     red.check_status()
+    # small-vector exchange (batch-norm statistics): value check and latency against NCCL
+    small = fused_allreduce.SmallVectorAllReduce(device=dev, rank=rank, world=world)
+    vec = torch.arange(1025, device=dev, dtype=torch.float32) * (rank + 1)
+    got = small.all_reduce_sum(vec)
+    want = torch.arange(1025, device=dev, dtype=torch.float32) * sum(r + 1 for r in range(world))
+    small_ok = bool(torch.equal(got, want))
+    ok = ok and small_ok
+    t_small = timed(lambda: small.all_reduce_sum(vec))
+    tmp = vec.clone()
+    t_small_nccl = timed(lambda: dist.all_reduce(tmp))
     okt = torch.tensor(1 if ok else 0, device=dev)
     dist.all_reduce(okt, op=dist.ReduceOp.MIN)
     if rank == 0:
+        print(json.dumps({"small_vector_floats": 1025, "ok": small_ok, "fused_us": round(t_small * 1e3, 1), "nccl_us": round(t_small_nccl * 1e3, 1)}), flush=True)
         nbytes = arena.total * 4
         bus = lambda ms: 2 * (world - 1) / world * nbytes / (ms * 1e-3) / 1e9
         print(json.dumps({"world": world, "elems": arena.total, "multimem": bool(red.multicast_ptr), "max_abs_err": err, "norm_rel_err": norm_err,

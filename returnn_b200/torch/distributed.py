@@ -165,6 +165,12 @@ class DistributedContext:
             from ..parallel import fused_allreduce
 
             self._fused = fused_allreduce.try_create(self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt))
+            from ..config import get_global_config
+
+            cfg = get_global_config(raise_exception=False)
+            if self._fused is not None and cfg is not None and cfg.bool("rf_batch_norm_distributed", False):
+                # cross-rank batch-norm statistics: a one-kernel exchange of the [C] sums instead of a library collective
+                fused_allreduce.try_create_small_reducer(device=device, rank=self._rank, world=self._size)
         if self._reduce_type == "grad":
             self._reducer = BucketedGradReducer(self._arena, fused=self._fused)
 

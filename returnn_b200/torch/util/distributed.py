@@ -12,18 +12,27 @@ import torch.distributed as dist
 _OPS = {"sum": dist.ReduceOp.SUM, "max": dist.ReduceOp.MAX, "min": dist.ReduceOp.MIN, "avg": dist.ReduceOp.SUM}
 
 
+def _sum_over_ranks(x: torch.Tensor) -> torch.Tensor:
+    """small fp32 CUDA vectors (batch-norm statistics) go through the one-kernel NVLink exchange, everything else through NCCL / gloo"""
+    if x.is_cuda:
+        from ...parallel import fused_allreduce as _far
+
+        red = _far.get_small_reducer()
+        if red is not None and red.supports(x):
+            return red.all_reduce_sum(x.contiguous())
+    out = x.clone()
+    dist.all_reduce(out, op=dist.ReduceOp.SUM)
+    return out
+
+
 class _AllReduceSum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x):
-        out = x.clone()
-        dist.all_reduce(out, op=dist.ReduceOp.SUM)
-        return out
+        return _sum_over_ranks(x)
 
     @staticmethod
     def backward(ctx, g):
-        g = g.clone()
-        dist.all_reduce(g, op=dist.ReduceOp.SUM)
-        return g
+        return _sum_over_ranks(g)
 
 
 def all_reduce_differentiable(x: torch.Tensor, op: str = "sum") -> torch.Tensor:

@@ -1,0 +1,64 @@
+"""scaled-dot-product attention kernels against plain PyTorch fp32"""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _case(B, H, D, Tq, Tk, causal, with_lens, seed=0):
+    from returnn_b200.ops import sdpa as S
+
+    torch.manual_seed(seed)
+    dev = torch.device("cuda")
+    bf = torch.bfloat16
+    q = (torch.randn(B, Tq, H * D, device=dev) * 0.7).to(bf).requires_grad_(True)
+    k = (torch.randn(B, Tk, H * D, device=dev) * 0.7).to(bf).requires_grad_(True)
+    v = (torch.randn(B, Tk, H * D, device=dev) * 0.7).to(bf).requires_grad_(True)
+    lens = torch.randint(max(1, Tk // 2), Tk + 1, (B,), device=dev, dtype=torch.int32) if with_lens else None
+    assert S.supports(q, k, H)
+    out = S.sdpa(q, k, v, num_heads=H, k_lens=lens, causal=causal)
+    w = torch.randn_like(out, dtype=torch.float32)
+    (out.float() * w).sum().backward()
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+    ref = S.sdpa_reference(qr, kr, vr, num_heads=H, k_lens=lens, causal=causal)
+    (ref * w).sum().backward()
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    for got, want, name in ((q.grad, qr.grad, "dq"), (k.grad, kr.grad, "dk"), (v.grad, vr.grad, "dv")):
+        err = (got.float() - want).abs().max().item()
+        scale = want.abs().max().item() + 1e-6
+        assert err / scale < 3e-2, (name, err, scale)
+
+
+@pytest.mark.parametrize("B,H,D,Tq,Tk,causal,with_lens", [
+    (3, 2, 64, 70, 70, False, True),     # encoder self attention with padding
+    (2, 4, 64, 33, 33, True, False),     # causal decoder self attention
+    (2, 2, 64, 17, 130, False, True),    # cross attention: short queries, long padded keys
+    (1, 1, 128, 1, 65, True, False),     # one decoding step against a cache (the query is the last position)
+    (2, 8, 64, 128, 192, False, False),  # sizes on tile boundaries
+])
+def test_sdpa_matches_reference(B, H, D, Tq, Tk, causal, with_lens):
+    _case(B, H, D, Tq, Tk, causal, with_lens)
+
+
+def test_sdpa_dropout_statistics_and_4d_entry():
+    from returnn_b200.ops import sdpa as S, attention as A
+
+    torch.manual_seed(1)
+    dev = torch.device("cuda")
+    B, H, D, T = 2, 2, 64, 96
+    q = torch.randn(B, T, H * D, device=dev).to(torch.bfloat16)
+    k = torch.randn(B, T, H * D, device=dev).to(torch.bfloat16)
+    v = torch.ones(B, T, H * D, device=dev).to(torch.bfloat16)
+    # with constant values the output is the kept probability mass / (1-p): mean 1, and not identically 1
+    out = S.sdpa(q, k, v, num_heads=H, dropout_p=0.5).float()
+    assert abs(out.mean().item() - 1.0) < 0.05 and out.std().item() > 0.01
+    # the [B, H, T, D] entry used by rf.dot_attention
+    q4 = q.view(B, T, H, D).transpose(1, 2)
+    k4 = k.view(B, T, H, D).transpose(1, 2)
+    vv = torch.randn(B, T, H * D, device=dev).to(torch.bfloat16)
+    v4 = vv.view(B, T, H, D).transpose(1, 2)
+    lens = torch.tensor([96, 50], device=dev, dtype=torch.int32)
+    got = A.sdpa(q4, k4, v4, kv_lens=lens, scale=D ** -0.5, causal=False)
+    want = A.sdpa_reference(q4.float(), k4.float(), v4.float(), kv_lens=lens, scale=D ** -0.5, causal=False)
+    torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)

@@ -210,3 +210,25 @@ def test_native_code_compiler(tmp_path, monkeypatch):
     assert c2.get_lib_filename() == c.get_lib_filename() and os.path.getmtime(c2.get_lib_filename()) == mtime  # cached
     with pytest.raises(RuntimeError):
         NativeCodeCompiler("t_bad", code="this is not C++")
+
+
+def test_rf_native_dim_helpers():
+    """the CPython extension gives the same answers as the Python specification"""
+    from returnn_b200.frontend import _native
+    from returnn_b200.tensor import Dim, Tensor, batch_dim
+
+    mod = _native.get_module()
+    if mod is None:
+        pytest.skip("extension not built")
+    a, b, c = Dim(3, name="a"), Dim(4, name="b"), Dim(None, name="c")
+    assert mod.match_dims((a, b, c), (c, a, b)) == [2, 0, 1] and mod.match_dims((a, b), (c, a)) == [-1, 0]
+    assert mod.match_dims((a, a), (a, a)) == [0, 1]  # a repeated dim is matched once per occurrence
+    assert mod.same_dims((a, b), (a, b)) and not mod.same_dims((a, b), (b, a)) and not mod.same_dims((a,), (a, b))
+    assert mod.merge_dims((a, b), (b,)) == (a, b) and mod.merge_dims((b,), (a, b)) == (a, b)
+    assert mod.merge_dims((a,), (b,)) == (a, b) and mod.merge_dims((), (b,)) == (b,) and mod.merge_dims((a, c), (c, b)) == (a, c, b)
+    x = Tensor("x", dims=[batch_dim, a, b], dtype="float32", raw_tensor=torch.zeros(2, 3, 4))
+    assert x.get_out_permutation_to_dims([b, batch_dim, a]) == [2, 0, 1]
+    with pytest.raises(ValueError):
+        x.get_out_permutation_to_dims([b, batch_dim, c])
+    y = Tensor("y", dims=[b], dtype="float32", raw_tensor=torch.ones(4))
+    assert (x + y).dims == (batch_dim, a, b) and (y + x).dims == (batch_dim, a, b)
