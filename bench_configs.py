@@ -1,0 +1,380 @@
+#!/usr/bin/env python3
+"""
+Training throughput of the other baseline configurations (the flagship Conformer-CTC has its own ``bench.py``), through the
+public engine API on synthetic data of the named shapes with random-init weights:
+
+    python bench_configs.py --config blstm_ctc       # 6 x BLSTM(1024) + CTC, 20k frames per batch, AdamW
+    python bench_configs.py --config conformer_aed   # 12-layer Conformer + 6-layer Transformer decoder, CE + aux CTC
+    python bench_configs.py --config transformer_mt  # Transformer base, shared 32k vocabulary, 25k tokens per batch
+    python bench_configs.py --config 12ax            # 2 x BLSTM(100) on the 12AX task, CPU fp32, 2 epochs x 1000 seqs (wall time)
+
+One JSON line per run: device-timed (CUDA events around K steps after W warm-up steps), a distinct batch every step, inputs
+staged on the device for ``value`` and copied from pinned host memory inside the timed region for ``e2e``. Multi-GPU:
+launch with ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 bench_configs.py --config ... --gpus N``.
+"""
+
+from __future__ import annotations
+import argparse
+import json
+import os
+import sys
+import time
+
+_ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, _ROOT)
+import bench as _bench  # noqa: E402  (batch synthesis, collate, clock sampler)
+
+FRAME_SEC = 0.01
+
+
+def _asr_batches(seed, n_steps, frames_budget, min_len, max_len, label_ratio):
+    """80-dim features ~N(0,1), labels uniform over 1..9999 with length ratio * frames (a pair: uniform in the range)"""
+    import numpy
+
+    rng = numpy.random.RandomState(seed)
+    batches, cur, cur_max = [], [], 0
+    while len(batches) < n_steps:
+        t = int(rng.randint(min_len, max_len + 1))
+        r = rng.uniform(*label_ratio) if isinstance(label_ratio, tuple) else label_ratio
+        s = max(1, int(round(t * r)))
+        seq = {"data": rng.standard_normal((t, 80)).astype("float32"), "classes": rng.randint(1, 10000, size=(s,)).astype("int32")}
+        new_max = max(cur_max, t)
+        if cur and new_max * (len(cur) + 1) > frames_budget:
+            batches.append(cur)
+            cur, cur_max = [seq], t
+        else:
+            cur.append(seq)
+            cur_max = new_max
+    return batches
+
+
+def _mt_batches(seed, n_steps, tokens_budget, vocab=32000):
+    """token ids Zipf(1.1) over the vocabulary, source length 10..100, target length = source * U(0.8, 1.2)"""
+    import numpy
+
+    rng = numpy.random.RandomState(seed)
+    ranks = numpy.arange(1, vocab, dtype="float64")
+    probs = ranks ** -1.1
+    probs /= probs.sum()
+    cdf = numpy.cumsum(probs)
+
+    def draw(n):
+        return (numpy.searchsorted(cdf, rng.random_sample(n)) + 1).clip(1, vocab - 1).astype("int32")
+
+    batches, cur, cur_max = [], [], 0
+    while len(batches) < n_steps:
+        s = int(rng.randint(10, 101))
+        t = max(1, int(round(s * rng.uniform(0.8, 1.2))))
+        seq = {"data": draw(s), "classes": draw(t)}
+        new_max = max(cur_max, s, t)
+        if cur and new_max * (len(cur) + 1) > tokens_budget:
+            batches.append(cur)
+            cur, cur_max = [seq], max(s, t)
+        else:
+            cur.append(seq)
+            cur_max = new_max
+    return batches
+
+
+def _configs():
+    from returnn_b200.models import blstm_ctc, conformer_aed, transformer_mt
+
+    return {
+        "blstm_ctc": dict(
+            mod=blstm_ctc, model_opts={}, name="blstm-ctc 6x1024 (2x time reduction after layers 1 and 2) vocab10k",
+            batches=lambda seed, n: _asr_batches(seed, n, 20000, 500, 1600, (0.1, 0.25)), budget=20000, unit="audio-s/s",
+            metric="train seconds-of-audio per second", output_dim={"data": (80, 2), "classes": (10000, 1)}, count=lambda b: sum(s["data"].shape[0] for s in b) * FRAME_SEC,
+            extra={"optimizer": {"class": "adamw", "weight_decay": 0.01}}),
+        "conformer_aed": dict(
+            mod=conformer_aed, model_opts={}, name="conformer-aed 12x512 + 6-layer decoder, CE(ls 0.1) + 0.3 CTC, vocab10k",
+            batches=lambda seed, n: _asr_batches(seed, n, 40000, 300, 2000, 1.0 / 30.0), budget=40000, unit="audio-s/s",
+            metric="train seconds-of-audio per second", output_dim={"data": (80, 2), "classes": (10000, 1)}, count=lambda b: sum(s["data"].shape[0] for s in b) * FRAME_SEC,
+            extra={"optimizer": {"class": "adamw", "weight_decay": 0.01}, "gradient_clip_global_norm": 5.0}),
+        "transformer_mt": dict(
+            mod=transformer_mt, model_opts={}, name="transformer-base 6+6x512 h8 ff2048 shared vocab 32k",
+            batches=lambda seed, n: _mt_batches(seed, n, 25000), budget=25000, unit="tokens/s", metric="train tokens per second (source + target)",
+            output_dim={"data": (32000, 1), "classes": (32000, 1)}, count=lambda b: sum(s["data"].shape[0] + s["classes"].shape[0] for s in b),
+            extra={"optimizer": {"class": "adam", "betas": (0.9, 0.98), "eps": 1e-9}}),
+    }
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from returnn_b200.config import Config, set_global_config
+    from returnn_b200.log import log
+    from returnn_b200.utils.basic import BehaviorVersion
+    from returnn_b200.torch.engine import Engine
+    from returnn_b200.datasets.generating import StaticDataset
+    from returnn_b200.ops import _lib
+
+    spec = _configs()[args.config]
+    rank, world, local_rank = _bench._dist_env()
+    assert world == args.gpus
+    torch.cuda.set_device(local_rank)
+    W, K = args.warmup, args.steps
+    batches = spec["batches"](4321 + rank, 2 * (W + K) + 3)
+    mod = spec["mod"]
+    cfg = Config(dict({
+        "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": mod.make_extern_data(spec["model_opts"]),
+        "model_opts": dict(spec["model_opts"]), "get_model": mod.get_model, "train_step": mod.train_step, "batch_size": spec["budget"],
+        "max_seqs": 2000, "learning_rate": 1e-4, "torch_amp": "bfloat16", "num_epochs": 1, "log_verbosity": 2 if rank == 0 else 1,
+        "device": "cuda"}, **spec["extra"]))
+    if world > 1:
+        cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else {"reduce_type": "grad"})
+    set_global_config(cfg)
+    BehaviorVersion._reset(21)
+    log.init_by_config(cfg)
+    train_data = StaticDataset(data=[s for b in batches[:2] for s in b], output_dim=spec["output_dim"])
+    train_data.initialize()
+    engine = Engine(cfg)
+    engine.init_train_from_config(cfg, train_data, None, None)
+    engine.epoch = 1
+    engine._pt_model.train()
+    dev = torch.device("cuda", local_rank)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    raws = [_bench._collate(b, pin=True) for b in batches]
+    counts = [spec["count"](b) for b in batches]
+
+    def to_dev(raw):
+        out = dict(raw)
+        for k in ("data", "classes"):
+            out[k] = raw[k].to(dev, non_blocking=True)
+        return out
+
+    for i in range(W):
+        engine.run_train_step(to_dev(raws[i]), read_losses=False)
+    staged = [to_dev(raws[W + i]) for i in range(K)]
+    barrier()
+    sampler = _bench.ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = _lib.launch_count()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for i in range(K):
+        engine.run_train_step(staged[i], read_losses=False)
+    ev1.record()
+    barrier()
+    dev_ms = ev0.elapsed_time(ev1)
+    launches = _lib.launch_count() - launches0
+    del staged
+    base = W + K
+    for i in range(3):
+        engine.run_train_step(raws[base + i], read_losses=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    h2d = 0
+    last = None
+    for i in range(K):
+        raw = raws[base + 3 + i]
+        h2d += raw["data"].numel() * raw["data"].element_size() + raw["classes"].numel() * raw["classes"].element_size()
+        last = engine.run_train_step(raw, read_losses=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
+    f = torch.tensor([sum(counts[W: W + K]), sum(counts[base + 3: base + 3 + K])], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(f, op=dist.ReduceOp.SUM)
+    dev_ms, e2e_ms = t.tolist()
+    n_dev, n_e2e = f.tolist()
+    if rank == 0:
+        print(json.dumps({
+            "metric": spec["metric"], "value": n_dev / (dev_ms / 1e3), "unit": spec["unit"], "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "impl": "returnn_b200", "config": {"model": spec["name"], "global_batch": "%i per GPU x %i" % (spec["budget"], world)},
+            "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
+                                      "d2h_bytes_per_step": 4 * max(len(last or {}), 1), "last_loss": last},
+            "gpu_launches": launches}))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_12ax(args):
+    """config 1: CPU, fp32, 2 epochs x 1000 sequences, wall time and final dev frame error"""
+    import torch
+    from returnn_b200.config import Config, set_global_config
+    from returnn_b200.log import log
+    from returnn_b200.datasets.basic import init_dataset
+    from returnn_b200.torch.engine import Engine
+    from returnn_b200.tensor import Dim, batch_dim
+    import returnn_b200.frontend as rf
+
+    torch.set_num_threads(int(os.environ.get("OMP_NUM_THREADS", "8")))
+    time_dim, in_dim, out_dim = Dim(None, name="time"), Dim(9, name="in"), Dim(2, name="out")
+
+    class Model(rf.Module):
+        def __init__(self):
+            super().__init__()
+            h = Dim(100, name="lstm")
+            h2 = 2 * h
+            self.fw1, self.bw1 = rf.LSTM(in_dim, h), rf.LSTM(in_dim, h)
+            self.fw2, self.bw2 = rf.LSTM(h2, h), rf.LSTM(h2, h)
+            self.out = rf.Linear(h2, out_dim)
+            self.h2 = h2
+
+        def _bi(self, fw, bw, x, out_feat):
+            y1, _ = fw(x, state=fw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=time_dim)
+            xr = rf.reverse_sequence(x, axis=time_dim)
+            y2, _ = bw(xr, state=bw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=time_dim)
+            y2 = rf.reverse_sequence(y2, axis=time_dim)
+            y, _ = rf.concat((y1, y1.feature_dim), (y2, y2.feature_dim), out_dim=out_feat)
+            return y
+
+        def __call__(self, x):
+            y = self._bi(self.fw1, self.bw1, x, self.h2)
+            y = self._bi(self.fw2, self.bw2, y, self.h2)
+            return self.out(y)
+
+    def train_step(*, model, extern_data, **_):
+        logits = model(extern_data["data"])
+        targets = extern_data["classes"]
+        rf.cross_entropy(estimated=logits, estimated_type="logits", target=targets, axis=out_dim).mark_as_loss("ce")
+        rf.cast(rf.reduce_argmax(logits, axis=out_dim) != targets, "float32").mark_as_loss("fer", as_error=True)
+
+    config = Config({
+        "backend": "torch", "task": "train", "num_epochs": 2, "batch_size": 5000, "max_seqs": 1000, "optimizer": {"class": "adam"},
+        "learning_rate": 1e-3, "device": "cpu", "log_verbosity": 2,
+        "extern_data": {"data": {"dims": (batch_dim, time_dim, in_dim), "dtype": "float32"},
+                        "classes": {"dims": (batch_dim, time_dim), "sparse_dim": out_dim, "dtype": "int32"}},
+        "get_model": lambda **_: Model(), "train_step": train_step})
+    set_global_config(config)
+    log.init_by_config(config)
+    train = init_dataset({"class": "Task12AXDataset", "num_seqs": 1000})
+    dev = init_dataset({"class": "Task12AXDataset", "num_seqs": 100, "fixed_random_seed": 1})
+    engine = Engine(config)
+    engine.init_train_from_config(config, train, dev, None)
+    t0 = time.perf_counter()
+    engine.train()
+    wall = time.perf_counter() - t0
+    scores = engine.learning_rate_control.epoch_data[engine.epoch].error
+    print(json.dumps({"metric": "12AX 2xBLSTM(100) CPU fp32: wall seconds for 2 epochs x 1000 seqs", "value": wall, "unit": "s", "higher_is_better": False,
+                      "impl": "returnn_b200", "dtype": "fp32", "data": "synthetic (Task12AXDataset)", "final_scores": scores,
+                      "threads": torch.get_num_threads()}))
+
+
+_REF_12AX_CONFIG = r'''#!rnn.py
+import time
+from returnn.tensor import Tensor, Dim, batch_dim, TensorDict
+import returnn.frontend as rf
+
+backend = "torch"
+task = "train"
+device = "cpu"
+train = {"class": "Task12AXDataset", "num_seqs": 1000}
+dev = {"class": "Task12AXDataset", "num_seqs": 100, "fixed_random_seed": 1}
+time_dim = Dim(None, name="time")
+in_dim = Dim(9, name="in")
+out_dim = Dim(2, name="out")
+extern_data = {
+    "data": {"dims": (batch_dim, time_dim, in_dim), "dtype": "float32"},
+    "classes": {"dims": (batch_dim, time_dim), "sparse_dim": out_dim, "dtype": "int32", "available_for_inference": False},
+}
+batch_size = 5000
+max_seqs = 1000
+optimizer = {"class": "adam"}
+learning_rate = 1e-3
+num_epochs = 2
+log_verbosity = 3
+torch_dataloader_opts = {"num_workers": 0}
+
+
+class Model(rf.Module):
+    def __init__(self):
+        super().__init__()
+        h = Dim(100, name="lstm")
+        self.h2 = 2 * h
+        self.fw1, self.bw1 = rf.LSTM(in_dim, h), rf.LSTM(in_dim, h)
+        self.fw2, self.bw2 = rf.LSTM(self.h2, h), rf.LSTM(self.h2, h)
+        self.out = rf.Linear(self.h2, out_dim)
+
+    def _bi(self, fw, bw, x):
+        y1, _ = fw(x, state=fw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=time_dim)
+        xr = rf.reverse_sequence(x, axis=time_dim)
+        y2, _ = bw(xr, state=bw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=time_dim)
+        y2 = rf.reverse_sequence(y2, axis=time_dim)
+        y, _ = rf.concat((y1, y1.feature_dim), (y2, y2.feature_dim), out_dim=self.h2)
+        return y
+
+    def __call__(self, x):
+        return self.out(self._bi(self.fw2, self.bw2, self._bi(self.fw1, self.bw1, x)))
+
+
+def get_model(**_kwargs):
+    return Model()
+
+
+def train_step(*, model, extern_data, **_kwargs):
+    logits = model(extern_data["data"]).copy_transpose((batch_dim, time_dim, out_dim))
+    targets = extern_data["classes"]
+    rf.cross_entropy(estimated=logits, estimated_type="logits", target=targets, axis=out_dim).mark_as_loss("ce")
+    rf.cast(rf.reduce_argmax(logits, axis=out_dim) != targets, "float32").mark_as_loss("fer", as_error=True)
+'''
+
+
+def run_12ax_reference(args):
+    """the same task through the unmodified reference (its own engine, datasets and rf backend), when it is installed"""
+    import tempfile
+
+    ref_dir = os.path.join(_ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "returnn")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/returnn not installed"}))
+        return
+    import torch
+
+    torch.set_num_threads(int(os.environ.get("OMP_NUM_THREADS", "8")))
+    tmpdir = tempfile.mkdtemp(prefix="bench_ref_12ax_")
+    cfg_path = os.path.join(tmpdir, "12ax.ref.config")
+    with open(cfg_path, "w") as f:
+        f.write(_REF_12AX_CONFIG)
+    sys.path.insert(0, ref_dir)
+    try:
+        import tree  # noqa: F401
+    except ImportError:
+        sys.path.append(os.path.join(_ROOT, "baseline", "deps"))
+    from returnn.__main__ import main as ref_main
+
+    old_stdout = sys.stdout
+    t0 = time.perf_counter()
+    try:
+        sys.stdout = sys.stderr
+        ref_main(["rnn.py", cfg_path])
+    except SystemExit:
+        pass
+    finally:
+        sys.stdout = old_stdout
+    wall = time.perf_counter() - t0
+    print(json.dumps({"metric": "12AX 2xBLSTM(100) CPU fp32: wall seconds for 2 epochs x 1000 seqs (incl. start-up)", "value": wall, "unit": "s",
+                      "higher_is_better": False, "impl": "reference", "dtype": "fp32", "threads": torch.get_num_threads()}))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--config", required=True, choices=["blstm_ctc", "conformer_aed", "transformer_mt", "12ax"])
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: only for --config 12ax")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        assert args.config == "12ax", "the reference arm of the GPU configs is bench.py --impl reference (Conformer-CTC)"
+        run_12ax_reference(args)
+    elif args.config == "12ax":
+        run_12ax(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
