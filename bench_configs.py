@@ -323,6 +323,142 @@ def train_step(*, model, extern_data, **_kwargs):
 '''
 
 
+_REF_BLSTM_CONFIG = r'''#!rnn.py
+import os, sys, time, json
+import numpy, torch
+from returnn.tensor import Tensor, Dim, batch_dim, TensorDict
+import returnn.frontend as rf
+
+_opts = __OPTS__
+sys.path.insert(0, _opts["root"])
+import bench_configs as _bc
+
+backend = "torch"
+task = "train"
+behavior_version = 21
+_W, _K = _opts["warmup"], _opts["steps"]
+_batches = _bc._asr_batches(4321, _W + _K + 1, 20000, 500, 1600, (0.1, 0.25))
+_frames = [sum(s["data"].shape[0] for s in b) for b in _batches]
+train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (80, 2), "classes": (10000, 1)}}
+time_dim = Dim(None, name="time", kind=Dim.Types.Spatial)
+feat_dim = Dim(80, name="feature", kind=Dim.Types.Feature)
+targets_time = Dim(None, name="targets-time", kind=Dim.Types.Spatial)
+vocab_dim = Dim(10000, name="vocab", kind=Dim.Types.Feature)
+extern_data = {
+    "data": {"dims": (batch_dim, time_dim, feat_dim), "dtype": "float32"},
+    "classes": {"dims": (batch_dim, targets_time), "sparse_dim": vocab_dim, "dtype": "int32", "available_for_inference": False},
+}
+batch_size = 20000
+max_seqs = 2000
+batching = "default"
+optimizer = {"class": "adamw", "weight_decay": 0.01}
+learning_rate = 1e-4
+torch_amp = "bfloat16"
+num_epochs = 1
+log_verbosity = 3
+torch_dataloader_opts = {"num_workers": 0}
+
+
+class Blstm(rf.Module):
+    def __init__(self, in_dim, hidden):
+        super().__init__()
+        self.fw = rf.LSTM(in_dim, hidden)
+        self.bw = rf.LSTM(in_dim, hidden)
+        self.out_dim = hidden + hidden
+
+    def __call__(self, x, *, spatial_dim):
+        yf, _ = self.fw(x, state=self.fw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=spatial_dim)
+        xr = rf.reverse_sequence(x, axis=spatial_dim)
+        yb, _ = self.bw(xr, state=self.bw.default_initial_state(batch_dims=[batch_dim]), spatial_dim=spatial_dim)
+        yb = rf.reverse_sequence(yb, axis=spatial_dim)
+        out, _ = rf.concat((yf, self.fw.out_dim), (yb, self.bw.out_dim), out_dim=self.out_dim)
+        return out
+
+
+class Model(rf.Module):
+    def __init__(self):
+        super().__init__()
+        layers, cur = [], feat_dim
+        for i in range(6):
+            layer = Blstm(cur, Dim(1024, name="lstm%i" % i))
+            layers.append(layer)
+            cur = layer.out_dim
+        self.layers = rf.ModuleList(*layers)
+        self.wb = vocab_dim + 1
+        self.output = rf.Linear(cur, self.wb)
+
+    def __call__(self, x, *, in_spatial_dim):
+        spatial = in_spatial_dim
+        for i, layer in enumerate(self.layers):
+            x = layer(x, spatial_dim=spatial)
+            if i in (0, 1):
+                x, spatial = rf.max_pool1d(x, pool_size=2, padding="same", in_spatial_dim=spatial)
+        return self.output(x), spatial
+
+
+def get_model(**_kwargs):
+    return Model()
+
+
+_state = {"n": 0, "ev0": None}
+
+
+def train_step(*, model, extern_data, **_kwargs):
+    n = _state["n"]
+    if n == _W or n == _W + _K:
+        torch.cuda.synchronize()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        if n == _W:
+            _state["ev0"] = ev
+        else:
+            torch.cuda.synchronize()
+            ms = _state["ev0"].elapsed_time(ev)
+            frames = sum(_frames[_W:_W + _K])
+            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train seconds-of-audio per second", "value": frames * 0.01 / (ms / 1e3),
+                                             "unit": "audio-s/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
+                                             "data": "synthetic", "config": {"model": "blstm-ctc 6x1024 (reference rf.LSTM -> torch.lstm / cuDNN)"}}) + "\n")
+            sys.__stdout__.flush()
+    _state["n"] = n + 1
+    logits, enc_spatial = model(extern_data["data"], in_spatial_dim=time_dim)
+    loss = rf.ctc_loss(logits=logits, targets=extern_data["classes"], input_spatial_dim=enc_spatial, targets_spatial_dim=targets_time, blank_index=10000)
+    loss.mark_as_loss("ctc", custom_inv_norm_factor=targets_time.get_size_tensor(), use_normalized_loss=False)
+'''
+
+
+def run_blstm_reference(args):
+    """BLSTM-CTC through the unmodified reference on one GPU (its LSTM is torch.lstm, i.e. cuDNN)"""
+    import tempfile
+
+    ref_dir = os.path.join(_ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "returnn")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/returnn not installed"}))
+        return
+    opts = {"root": _ROOT, "warmup": args.warmup, "steps": args.steps}
+    tmpdir = tempfile.mkdtemp(prefix="bench_ref_blstm_")
+    cfg_path = os.path.join(tmpdir, "blstm.ref.config")
+    with open(cfg_path, "w") as f:
+        f.write(_REF_BLSTM_CONFIG.replace("__OPTS__", repr(opts)))
+    sys.path.insert(0, ref_dir)
+    try:
+        import tree  # noqa: F401
+    except ImportError:
+        sys.path.append(os.path.join(_ROOT, "baseline", "deps"))
+    from returnn.__main__ import main as ref_main
+
+    old_stdout = sys.stdout
+    try:
+        sys.stdout = sys.stderr
+        ref_main(["rnn.py", cfg_path])
+    except SystemExit:
+        pass
+    except Exception as exc:
+        sys.stdout = old_stdout
+        print(json.dumps({"impl": "reference", "unavailable": "the reference run failed: %s: %s" % (type(exc).__name__, str(exc)[:300])}))
+    finally:
+        sys.stdout = old_stdout
+
+
 def run_12ax_reference(args):
     """the same task through the unmodified reference (its own engine, datasets and rf backend), when it is installed"""
     import tempfile
@@ -365,11 +501,14 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: only for --config 12ax")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: for --config 12ax and blstm_ctc")
     args = ap.parse_args()
     if args.impl == "reference":
-        assert args.config == "12ax", "the reference arm of the GPU configs is bench.py --impl reference (Conformer-CTC)"
-        run_12ax_reference(args)
+        assert args.config in ("12ax", "blstm_ctc"), "reference arms: 12ax, blstm_ctc here; Conformer-CTC in bench.py --impl reference"
+        if args.config == "12ax":
+            run_12ax_reference(args)
+        else:
+            run_blstm_reference(args)
     elif args.config == "12ax":
         run_12ax(args)
     else:

@@ -182,6 +182,180 @@ att_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ w, const TS* __restrict
   }
 }
 
+// ---- bf16-score versions with 16-byte accesses: a lane owns 8 consecutive keys per step (two steps cover 512 keys), one
+// philox call serves 4 keys (the scalar kernels above draw one per key and use a quarter of it). Same arithmetic, same dropout
+// counters, so forward and backward (and the scalar kernels) agree on the mask.
+__device__ __forceinline__ void rng8(uint64_t seed, uint64_t idx0, uint32_t (&r)[8]) {
+  const uint2 key = make_uint2((uint32_t)seed, (uint32_t)(seed >> 32));
+  const uint64_t b0 = idx0 >> 2;  // idx0 is a multiple of 8
+  const uint4 a = philox4x32(key, make_uint4((uint32_t)b0, (uint32_t)(b0 >> 32), 0x51u, 0u));
+  const uint4 b = philox4x32(key, make_uint4((uint32_t)(b0 + 1), (uint32_t)((b0 + 1) >> 32), 0x51u, 0u));
+  r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w; r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    const float2 p = __bfloat1622float2(h[q]);
+    f[2 * q] = p.x;
+    f[2 * q + 1] = p.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int q = 0; q < 4; ++q) h[q] = __floats2bfloat162_rn(f[2 * q], f[2 * q + 1]);
+  return u;
+}
+
+constexpr int kVecSteps = 2;  // 2 * 32 lanes * 8 keys = 512
+
+__global__ void __launch_bounds__(128)
+att_softmax_fwd_vec_kernel(const __nv_bfloat16* __restrict__ s_ac, const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ w,
+                           __nv_bfloat16* __restrict__ wd, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
+                           float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  const int b = z / heads, h = z % heads;
+  const int len = lens[b];
+  const int len64 = min(lp, (len + 63) & ~63);
+  if (i >= len64) return;
+  const long long srow = ((long long)z * lp + i) * lp;
+  const bool drop = p_drop > 0.f;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  if (i >= len) {
+    for (int j0 = lane * 8; j0 < len64; j0 += 256) {
+      *reinterpret_cast<uint4*>(w + srow + j0) = zero4;
+      if (drop) *reinterpret_cast<uint4*>(wd + srow + j0) = zero4;
+    }
+    return;
+  }
+  const long long grow = (((long long)h * batch + b) * lp + i) * rp + (center - i);
+  float x[kVecSteps][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int t = 0; t < kVecSteps; ++t) {
+    const int j0 = (t * 32 + lane) * 8;
+    if (j0 < len) {
+      float a[8];
+      unpack8(*reinterpret_cast<const uint4*>(s_ac + srow + j0), a);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int j = j0 + e;
+        x[t][e] = j < len ? a[e] + __bfloat162float(g[grow + j]) : -INFINITY;
+        mx = fmaxf(mx, x[t][e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[t][e] = -INFINITY;
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int t = 0; t < kVecSteps; ++t)
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      x[t][e] = x[t][e] > -INFINITY ? __expf(x[t][e] - mx) : 0.f;
+      sum += x[t][e];
+    }
+  sum = warp_sum(sum);
+  const float inv = 1.f / sum;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0;
+  const uint64_t off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+#pragma unroll
+  for (int t = 0; t < kVecSteps; ++t) {
+    const int j0 = (t * 32 + lane) * 8;
+    if (j0 < len64) {
+      float pr[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) pr[e] = x[t][e] * inv;  // zero beyond len
+      *reinterpret_cast<uint4*>(w + srow + j0) = pack8(pr);
+      if (drop) {
+        uint32_t r[8];
+        rng8(sd, off + (uint64_t)(srow + j0), r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) pr[e] = r[e] >= thresh ? pr[e] * keep_scale : 0.f;
+        *reinterpret_cast<uint4*>(wd + srow + j0) = pack8(pr);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+att_softmax_bwd_vec_kernel(const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ dwd, __nv_bfloat16* __restrict__ ds,
+                           __nv_bfloat16* __restrict__ dg, const int* __restrict__ lens, int batch, int heads, int lp, int rp, int center,
+                           float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  const int b = z / heads, h = z % heads;
+  const int len = lens[b];
+  const int len64 = min(lp, (len + 63) & ~63);
+  if (i >= len64) return;
+  const long long srow = ((long long)z * lp + i) * lp;
+  const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
+  if (i >= len) {
+    for (int j0 = lane * 8; j0 < len64; j0 += 256) *reinterpret_cast<uint4*>(ds + srow + j0) = zero4;
+    return;
+  }
+  const long long grow = (((long long)h * batch + b) * lp + i) * rp + (center - i);
+  const bool drop = p_drop > 0.f;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0;
+  const uint64_t off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+  float pw[kVecSteps][8], dw[kVecSteps][8];
+  float delta = 0.f;
+#pragma unroll
+  for (int t = 0; t < kVecSteps; ++t) {
+    const int j0 = (t * 32 + lane) * 8;
+    if (j0 < len) {
+      unpack8(*reinterpret_cast<const uint4*>(w + srow + j0), pw[t]);
+      unpack8(*reinterpret_cast<const uint4*>(dwd + srow + j0), dw[t]);
+      uint32_t r[8];
+      if (drop) rng8(sd, off + (uint64_t)(srow + j0), r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (j0 + e >= len) {
+          pw[t][e] = 0.f;
+          dw[t][e] = 0.f;
+        } else if (drop) {
+          dw[t][e] = r[e] >= thresh ? dw[t][e] * keep_scale : 0.f;
+        }
+        delta += pw[t][e] * dw[t][e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) pw[t][e] = dw[t][e] = 0.f;
+    }
+  }
+  delta = warp_sum(delta);
+#pragma unroll
+  for (int t = 0; t < kVecSteps; ++t) {
+    const int j0 = (t * 32 + lane) * 8;
+    if (j0 < len64) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = pw[t][e] * (dw[t][e] - delta);  // zero beyond len
+      const uint4 packed = pack8(o);
+      *reinterpret_cast<uint4*>(ds + srow + j0) = packed;
+      const __nv_bfloat16* ob = reinterpret_cast<const __nv_bfloat16*>(&packed);
+#pragma unroll
+      for (int e = 0; e < 8; ++e)
+        if (j0 + e < len) dg[grow + j0 + e] = ob[e];
+    }
+  }
+}
+
 // wd = dropout(w) with the mask of the forward pass (same seed, same offset)
 __global__ void __launch_bounds__(128)
 att_redrop_kernel(const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ wd, const int* __restrict__ lens, int heads, int lp,
@@ -273,7 +447,10 @@ RB_EXPORT int rb200_att_softmax_fwd_ex(const void* s_ac, const void* g, int scor
     return RB_ERR_UNSUPPORTED;
   }
   dim3 grid((lp + 3) / 4, batch * heads);
-  if (scores_bf16)
+  if (scores_bf16 && lp <= 512 && lp % 64 == 0 && rp % 8 == 0)
+    rb_launch_pdl(att_softmax_fwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)s_ac, (const __nv_bfloat16*)g, (__nv_bfloat16*)w,
+                  (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
+  else if (scores_bf16)
     rb_launch_pdl(att_softmax_fwd_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, stream, (const __nv_bfloat16*)s_ac, (const __nv_bfloat16*)g, (__nv_bfloat16*)w,
                                                                     (__nv_bfloat16*)wd, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
   else
@@ -286,7 +463,10 @@ RB_EXPORT int rb200_att_softmax_bwd_ex(const void* w, const void* dwd, int dwd_b
                                        int rp, int center, float p_drop, const long long* seed, const long long* offset, cudaStream_t stream) {
   if (lp > 32 * kMaxPerLane) return RB_ERR_UNSUPPORTED;
   dim3 grid((lp + 3) / 4, batch * heads);
-  if (dwd_bf16)
+  if (dwd_bf16 && lp <= 512 && lp % 64 == 0 && rp % 8 == 0)
+    rb_launch_pdl(att_softmax_bwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dwd, (__nv_bfloat16*)ds,
+                  (__nv_bfloat16*)dg, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
+  else if (dwd_bf16)
     rb_launch_pdl(att_softmax_bwd_kernel<__nv_bfloat16>, dim3(grid), dim3(128), 0, stream, (const __nv_bfloat16*)w, (const __nv_bfloat16*)dwd, (__nv_bfloat16*)ds,
                                                                     (__nv_bfloat16*)dg, lens, batch, heads, lp, rp, center, p_drop, seed, offset);
   else

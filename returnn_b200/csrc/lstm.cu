@@ -11,6 +11,15 @@
 #include "common.cuh"
 #include "gemm.h"
 
+// lstm_persist.cu: the whole recurrence in one cooperative kernel, for the shapes it supports
+bool rb_lstm_persist_supported(int T, int B, int H);
+int rb_lstm_persist_fwd(const void* z_in, const void* w_rec, const int* lens, const float* h0, const float* c0, int T, int B, int H, int reverse,
+                        void* y, float* c_all, void* gates, void* hprev_all, float* h_final, float* c_final, void* hbuf, int* status,
+                        cudaStream_t stream);
+int rb_lstm_persist_bwd(const void* dy, const float* dh_final, const float* dc_final, const void* w_rec, const int* lens, const void* gates,
+                        const float* c_all, const float* c0, int T, int B, int H, int reverse, void* dz, float* dh0, float* dc0, int* status,
+                        cudaStream_t stream);
+
 namespace {
 
 typedef __nv_bfloat16 bf16;
@@ -105,6 +114,11 @@ RB_EXPORT int rb200_lstm_fwd(const void* z_in, const void* w_rec, const int* len
     rb_set_error("lstm: hidden size %d must be a multiple of 8", H);
     return RB_ERR_UNSUPPORTED;
   }
+  if (rb_lstm_persist_supported(T, B, H)) {
+    // z_rec (B*4H floats) is large enough for the two bf16 copies of the hidden state that the CTAs exchange
+    if (n_launch) *n_launch = 2;
+    return rb_lstm_persist_fwd(z_in, w_rec, lens, h0, c0, T, B, H, reverse, y, c_all, gates, hprev_all, h_final, c_final, z_rec, status, stream);
+  }
   const long long bh = (long long)B * H;
   const int grid = (int)((bh + 255) / 256);
   cudaMemcpyAsync(c_final, c0, bh * sizeof(float), cudaMemcpyDeviceToDevice, stream);
@@ -138,6 +152,21 @@ RB_EXPORT int rb200_lstm_bwd(const void* dy, const float* dh_final, const float*
                              const float* c_all, const float* c0, const void* hprev_all, int T, int B, int H, int reverse, void* dz, float* dw_rec,
                              float* dh0, float* dc0, int* status, int* n_launch, cudaStream_t stream) {
   if (T <= 0 || B <= 0) return RB_OK;
+  if (rb_lstm_persist_supported(T, B, H)) {
+    int st = rb_lstm_persist_bwd(dy, dh_final, dc_final, w_rec, lens, gates, c_all, c0, T, B, H, reverse, dz, dh0, dc0, status, stream);
+    if (st) return st;
+    int launches = 2;
+    if (dw_rec) {
+      RbGemm g;
+      g.a = dz; g.b = hprev_all; g.c = dw_rec; g.m = 4 * H; g.n = H; g.k = T * B; g.lda = 4 * H; g.ldb = H; g.ldc = H;
+      g.a_mn_major = 1; g.b_mn_major = 1; g.out_fp32 = 1; g.accumulate = 2; g.status = status;
+      st = rb_gemm(g, stream);
+      if (st) return st;
+      ++launches;
+    }
+    if (n_launch) *n_launch = launches;
+    return rb_check_launch("lstm_bwd_persist");
+  }
   const long long bh = (long long)B * H;
   const int grid = (int)((bh + 255) / 256);
   if (dh_final) cudaMemcpyAsync(dh0, dh_final, bh * sizeof(float), cudaMemcpyDeviceToDevice, stream);

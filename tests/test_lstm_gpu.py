@@ -8,7 +8,7 @@ gpu = pytest.mark.gpu
 
 @gpu
 @pytest.mark.parametrize("reverse", [False, True])
-@pytest.mark.parametrize("T,B,I,H", [(9, 5, 16, 32), (40, 12, 64, 128)])
+@pytest.mark.parametrize("T,B,I,H", [(9, 5, 16, 32), (40, 12, 64, 128), (30, 40, 64, 256), (12, 50, 32, 128)])
 def test_lstm_native_matches_reference(reverse, T, B, I, H):
     from returnn_b200.ops import lstm as L, lstm_native, gemm
 
