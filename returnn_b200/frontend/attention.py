@@ -85,6 +85,8 @@ def dot_attention(query: Tensor, keys: Tensor, values: Tensor, *, key_dim: Dim, 
         values, _ = _replace(values, axis, kv_dim)
         axis = kv_dim
     v_feat = [d for d in values.dims if d not in keys.dims]
+    if not v_feat and key_dim in values.dims:
+        v_feat = [key_dim]  # value and key features are the same dim (equal per-head sizes derived from one model dim)
     common = [d for d in keys.dims if d in query.dims and d not in (key_dim,)]
     q_only = [d for d in query.dims if d not in keys.dims]
     # fast path for the [batch.., T_q, D] x [batch.., T_kv, D] layout
