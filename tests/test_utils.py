@@ -232,3 +232,35 @@ def test_rf_native_dim_helpers():
         x.get_out_permutation_to_dims([b, batch_dim, c])
     y = Tensor("y", dims=[b], dtype="float32", raw_tensor=torch.ones(4))
     assert (x + y).dims == (batch_dim, a, b) and (y + x).dims == (batch_dim, a, b)
+
+
+def test_tools_on_small_inputs(tmp_path):
+    """command line tools that need no trained model: Bliss readers, word/symbol collection, pickle dump, file cache"""
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    corpus = tmp_path / "corpus.xml"
+    corpus.write_text('<?xml version="1.0" encoding="utf8"?>\n<corpus name="c"><recording name="r1" audio="/nonexistent/r1.wav">'
+                      '<segment name="s1" start="0.0" end="1.5"><orth> hello world </orth></segment>'
+                      '<segment name="s2" start="1.5" end="4.0"><orth>foo bar hello</orth></segment></recording></corpus>\n')
+
+    def run(tool, *args):
+        proc = subprocess.run([sys.executable, os.path.join(root, "tools", tool)] + [str(a) for a in args], stdout=subprocess.PIPE, stderr=subprocess.PIPE, timeout=120)
+        assert proc.returncode == 0, proc.stderr.decode()[-2000:]
+        return proc.stdout.decode()
+
+    assert eval(run("bliss-collect-seq-lens.py", corpus)) == {"c/r1/s1": 150, "c/r1/s2": 250}
+    assert run("bliss-dump-text.py", corpus, "--with-names").splitlines() == ["c/r1/s1 hello world", "c/r1/s2 foo bar hello"]
+    assert run("bliss-get-segment-names.py", corpus).split() == ["c/r1/s1", "c/r1/s2"]
+    assert run("collect-words.py", corpus).splitlines()[0] == "hello 2"
+    assert "'h' 2" in run("collect-orth-symbols.py", corpus)
+    run("bliss-to-ogg-zip.py", corpus, "--output", tmp_path / "c.zip", "--no-audio")
+    import zipfile
+
+    with zipfile.ZipFile(str(tmp_path / "c.zip")) as zf:
+        entries = eval(zf.read("c.txt").decode())
+    assert [e["seq_name"] for e in entries] == ["c/r1/s1", "c/r1/s2"] and entries[1]["text"] == "foo bar hello"
+    import pickle
+
+    (tmp_path / "x.pkl").write_bytes(pickle.dumps({"a": [1, 2]}))
+    assert eval(run("dump-pickle.py", tmp_path / "x.pkl")) == {"a": [1, 2]}
