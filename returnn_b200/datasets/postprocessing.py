@@ -6,6 +6,7 @@ re-ordering with :class:`LaplaceOrdering` (reference: returnn/datasets/postproce
 """
 
 from __future__ import annotations
+from ..utils.basic import OptionalNotImplementedError
 from typing import Any, Callable, Dict, Iterator, List, Optional
 import numpy
 from .basic import Dataset, DatasetSeq, init_dataset
@@ -57,6 +58,12 @@ class PostprocessingDataset(CachedDataset2):
                 dims += [Dim(d, name="%s_dim%i" % (key, i)) for i, d in enumerate(shape)]
             td.data[key] = Tensor(key, dims=dims, dtype=ds.get_data_dtype(key), sparse_dim=sparse)
         return td
+
+    def get_current_seq_order(self):
+        """the order of the wrapped dataset (a stream function that changes the number of sequences has no such order)"""
+        if self._map_seq_stream is not None and not self._map_seq_stream_preserves_num_seqs:
+            raise OptionalNotImplementedError("%s: map_seq_stream may change the sequences" % self)
+        return self._dataset.get_current_seq_order()
 
     def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
         super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)

@@ -182,3 +182,20 @@ def hot_reload_config(config: Dict[str, Any]):
         importlib.reload(sys.modules[m])
     for k in keys:
         _walk(config[k], visit=_rebind, update=lambda v, k=k: config.__setitem__(k, v))
+
+
+_active: Optional[ConfigHotReloader] = None
+
+
+def enable(config) -> Optional[ConfigHotReloader]:
+    """track the user modules behind ``config`` (a :class:`Config`); the engine asks :func:`get_active` when a step fails"""
+    global _active
+    if not should_use_hot_reloading(config=config):
+        return None
+    _active = ConfigHotReloader(config.typed_dict)
+    return _active
+
+
+def get_active() -> Optional[ConfigHotReloader]:
+    """the reloader installed by :func:`enable`, if any"""
+    return _active
