@@ -61,7 +61,7 @@ class PostprocessingDataset(CachedDataset2):
 
     def get_current_seq_order(self):
         """the order of the wrapped dataset (a stream function that changes the number of sequences has no such order)"""
-        if self._map_seq_stream is not None and not self._map_seq_stream_preserves_num_seqs:
+        if not self._preserves_num_seqs:
             raise OptionalNotImplementedError("%s: map_seq_stream may change the sequences" % self)
         return self._dataset.get_current_seq_order()
 
