@@ -41,14 +41,19 @@ BASELINE_PUBLISHED = None  # the reference publishes no number for this config
 
 
 def make_synth_batches(*, seed: int, n_steps: int, frames_budget: int = BATCH_FRAMES, min_len: int = 300, max_len: int = 2000,
-                       feat_dim: int = 80, vocab: int = 10000):
-    """list of batches; a batch is a list of {"data": [T,F] float32, "classes": [S] int32}"""
+                       feat_dim: int = 80, vocab: int = 10000, shape_seed: int = 1234):
+    """
+    list of batches; a batch is a list of {"data": [T,F] float32, "classes": [S] int32}.
+    The sequence lengths come from ``shape_seed`` (the same on every rank: in a weak-scaling run all ranks then do the same
+    amount of work per step and the step time is not the maximum over differently sized random batches), the values from ``seed``.
+    """
     import numpy
 
     rng = numpy.random.RandomState(seed)
+    rng_len = numpy.random.RandomState(shape_seed)
     batches, cur, cur_max = [], [], 0
     while len(batches) < n_steps:
-        t = int(rng.randint(min_len, max_len + 1))
+        t = int(rng_len.randint(min_len, max_len + 1))
         s = max(1, int(round(t / 30.0)))
         seq = {"data": rng.standard_normal((t, feat_dim)).astype("float32"),
                "classes": rng.randint(1, vocab, size=(s,)).astype("int32")}

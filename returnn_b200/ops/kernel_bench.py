@@ -153,6 +153,77 @@ def main():
         prev = torch.randn(64, 12, device=dev)
         fwd = lambda: seq_ops.beam_topk(logits, prev, eos=0, k=12)
         report("beam_topk (64 x 12 x 10001)", _time(fwd, args.iters), None, 64 * 12 * 10001 * 2 * 2, 0)
+    import ctypes
+    from . import _lib
+
+    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    if want("layer_norm_bwd_acc"):
+        # the form the training step uses: bf16 rows, residual gradient added, dgamma / dbeta accumulated in the kernel
+        x = torch.randn(n, D, device=dev, dtype=bf)
+        dy = torch.randn(n, D, device=dev, dtype=bf)
+        dres = torch.randn(n, D, device=dev, dtype=bf)
+        dx = torch.empty_like(x)
+        gam = torch.ones(D, device=dev)
+        mean = x.float().mean(1).contiguous()
+        rstd = (x.float().var(1, unbiased=False) + 1e-6).rsqrt().contiguous()
+        dg, db = torch.zeros(D, device=dev), torch.zeros(D, device=dev)
+        part = torch.empty(2 * 592 * D, device=dev)
+        fn = _lib.bind("rb200_layer_norm_bwd_ex", [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp, i32, vp])
+        call = lambda: _lib.check(fn(x.data_ptr(), dy.data_ptr(), gam.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), part.data_ptr(),
+                                     dg.data_ptr(), db.data_ptr(), n, D, 416, 1, 0, 0, dres.data_ptr(), 1, _lib.stream_ptr()), "ln_bwd")
+        report("layer_norm_bwd_acc (bf16, + residual gradient)", _time(call, args.iters), None, 4 * n * D * 2, 0)
+    if want("colsum"):
+        for width in (D, F):
+            x = torch.randn(n, width, device=dev, dtype=bf)
+            out = torch.zeros(width, device=dev)
+            fn = _lib.bind("rb200_colsum_bf16", [vp, vp, i32, i32, vp])
+            call = lambda: _lib.check(fn(x.data_ptr(), out.data_ptr(), n, width, _lib.stream_ptr()), "colsum")
+            report("colsum (bias gradient, %i columns)" % width, _time(call, args.iters), None, n * width * 2, 0)
+    if want("att_softmax_bf16"):
+        H = 8
+        L = pack.max_len
+        lp = (L + 63) // 64 * 64
+        rp = 2 * lp
+        B = pack.batch
+        s_ac = (torch.randn(B * H * lp, lp, device=dev) * 2).to(bf)
+        band = (torch.randn(H * B * lp, rp, device=dev) * 2).to(bf)
+        w = torch.empty(B * H * lp, lp, device=dev, dtype=bf)
+        wd = torch.empty_like(w)
+        seed = torch.tensor([1234, 0], device=dev, dtype=torch.int64)
+        off = torch.zeros(1, device=dev, dtype=torch.int64)
+        lens_dev = pack.lens
+        fwd_fn = _lib.bind("rb200_att_softmax_fwd_ex", [vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp])
+        fwd = lambda: _lib.check(fwd_fn(s_ac.data_ptr(), band.data_ptr(), 1, w.data_ptr(), wd.data_ptr(), lens_dev.data_ptr(), B, H, lp, rp, lp - 1, 0.1,
+                                        seed.data_ptr(), off.data_ptr(), _lib.stream_ptr()), "att_softmax_fwd")
+        dwd = torch.randn(B * H * lp, lp, device=dev).to(bf)
+        ds = torch.empty_like(w)
+        dband = torch.zeros(H * B * lp, rp, device=dev, dtype=bf)
+        bwd_fn = _lib.bind("rb200_att_softmax_bwd_ex", [vp, vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, f32, vp, vp, vp])
+        bwd = lambda: _lib.check(bwd_fn(w.data_ptr(), dwd.data_ptr(), 1, ds.data_ptr(), dband.data_ptr(), lens_dev.data_ptr(), B, H, lp, rp, lp - 1, 0.1,
+                                        seed.data_ptr(), off.data_ptr(), _lib.stream_ptr()), "att_softmax_bwd")
+        valid = float((lens.double() ** 2).sum()) * H
+        t_f = _time(fwd, args.iters)
+        fwd()
+        t_b = _time(bwd, args.iters)
+        report("att_softmax fwd (bf16 scores, dropout)", t_f, None, valid * 2 * 4, 0)
+        report("att_softmax bwd (bf16 scores, dropout)", t_b, None, valid * 2 * 4, 0)
+    if want("lstm"):
+        from . import lstm_native
+
+        for (T, Bl) in ((400, 48), (1600, 12)):
+            Hl, I = 1024, 2048
+            x = (torch.randn(T, Bl, I, device=dev) * 0.5).to(bf).requires_grad_(True)
+            w_ff = (torch.randn(4 * Hl, I, device=dev) * 0.02).requires_grad_(True)
+            w_rec = (torch.randn(4 * Hl, Hl, device=dev) * 0.02).requires_grad_(True)
+            bias = torch.zeros(4 * Hl, device=dev, requires_grad=True)
+            h0, c0 = torch.zeros(Bl, Hl, device=dev), torch.zeros(Bl, Hl, device=dev)
+            ll = torch.full((Bl,), T, dtype=torch.int32)
+            fwd = lambda: lstm_native.lstm(x, ll, w_ff, w_rec, bias, h0, c0, reverse=False)[0]
+            def fb():
+                fwd().float().sum().backward()
+            t_f, t_fb = _time(fwd, max(2, args.iters // 10)), _time(fb, max(2, args.iters // 10))
+            report("lstm layer T=%i B=%i H=1024 (input GEMM + persistent recurrence)" % (T, Bl), t_f, t_fb, T * Bl * (I + 5 * Hl) * 2, T * Bl * (I + 5 * Hl) * 2 * 3,
+                   {"fwd_us_per_step": round(t_f * 1e6 / T, 2), "bwd_us_per_step": round((t_fb - t_f) * 1e6 / T, 2)})
     from . import gemm as G
 
     G.check_status()

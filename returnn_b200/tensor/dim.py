@@ -401,6 +401,10 @@ class Dim:
             base._maybe_refresh_derived()
         if base._dim_value_cache is not None:
             return base._dim_value_cache
+        if base.capacity is not None and self.dyn_size_ext is not None and getattr(self.dyn_size_ext.raw_tensor, "is_cuda", False):
+            # static-shape regime (captured CUDA graphs): the tensors have the capacity as their extent and the lengths live on
+            # the device, where reading their maximum would synchronise
+            return base.capacity
         ext = self.dyn_size_ext
         if ext is None or ext.raw_tensor is None:
             raise Exception("%r: dynamic size unknown" % self)

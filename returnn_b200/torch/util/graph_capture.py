@@ -149,6 +149,12 @@ class GraphCapturedTrainStep:
         for p in self._params:
             if p.grad is not None:
                 p.grad.zero_()
+        # masks and derived sizes cached on the dims by an earlier step would be baked into the capture: recompute them from the
+        # static length buffers inside this step (re-assigning the lengths invalidates the caches, also of derived dims)
+        for data in self._extern_data.data.values():
+            for dim in data.dims:
+                if dim.is_dynamic() and not dim.is_batch_dim() and dim.dyn_size_ext is not None:
+                    dim.dyn_size_ext = dim.dyn_size_ext
         eng._run_step(self._extern_data, train_flag=True, train_func=True)
         ctx = rf.get_run_ctx()
         names = list(ctx.losses.keys())
