@@ -82,7 +82,9 @@ def num_elements_of_shape(dims: Union[Dim, Sequence[Dim]], *, use_mask: bool = T
         if d.is_dynamic() and not d.is_batch_dim() and use_mask and d.dyn_size_ext is not None and d.dyn_size_ext.dims:
             ext = d.dyn_size_ext
             assert all(dd in dims for dd in ext.dims), "num_elements_of_shape: %r sizes depend on dims outside %r" % (d, dims)
-            n = n * int(ext.raw_tensor.sum())
+            total = ext.raw_tensor.sum()
+            # lengths on the device (static-shape / CUDA-graph regime): stay on the device, the count becomes a scalar Tensor
+            n = n * (total if getattr(total, "is_cuda", False) else int(total))
             done.add(d)
             for dd in ext.dims:
                 done.add(dd)
@@ -90,6 +92,8 @@ def num_elements_of_shape(dims: Union[Dim, Sequence[Dim]], *, use_mask: bool = T
         if d not in done:
             n = n * d.get_dim_value()
             done.add(d)
+    if isinstance(n, torch.Tensor):
+        return Tensor("num_elements", dims=[], dtype=dtype_name(n.dtype), raw_tensor=n)
     return n
 
 

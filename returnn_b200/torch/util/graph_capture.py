@@ -202,8 +202,19 @@ class GraphCapturedTrainStep:
                     if p.grad is None:
                         p.grad = torch.zeros_like(p)
             torch.cuda.current_stream().wait_stream(self._stream)
-            with torch.cuda.graph(graph, stream=self._stream):
-                self._fwd_bwd()
+            first_error: List[BaseException] = []
+            try:
+                with torch.cuda.graph(graph, stream=self._stream):
+                    try:
+                        self._fwd_bwd()
+                    except BaseException as exc:  # the end of the capture raises its own error on top: keep the cause
+                        first_error.append(exc)
+            except Exception as exc:
+                cause = first_error[0] if first_error else exc
+                raise RuntimeError("torch_cuda_graph: the train step cannot be captured (an operation in it synchronises or copies from "
+                                   "pageable host memory): %s: %s" % (type(cause).__name__, cause)) from cause
+            if first_error:
+                raise first_error[0]
             self._graph = graph
             _graphs.append(graph)
             graph.replay()
