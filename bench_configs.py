@@ -94,7 +94,7 @@ def _configs():
             mod=transformer_mt, model_opts={}, name="transformer-base 6+6x512 h8 ff2048 shared vocab 32k",
             batches=lambda seed, n: _mt_batches(seed, n, 25000), budget=25000, unit="tokens/s", metric="train tokens per second (source + target)",
             output_dim={"data": (32000, 1), "classes": (32000, 1)}, count=lambda b: sum(s["data"].shape[0] + s["classes"].shape[0] for s in b),
-            extra={"optimizer": {"class": "adam", "betas": (0.9, 0.98), "eps": 1e-9}}),
+            extra={"optimizer": {"class": "adamw", "betas": (0.9, 0.98), "eps": 1e-9, "weight_decay": 0.0}}),
     }
 
 

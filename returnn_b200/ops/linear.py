@@ -22,6 +22,16 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         from . import gemm as _gemm
 
         if _gemm.available(x) and _gemm.ENABLED and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 == 0:
+            if x.requires_grad and torch.is_grad_enabled() and weight.requires_grad:
+                # parameters of a flat arena (fused AdamW): read the bf16 copy the optimizer maintains instead of casting the fp32
+                # weight in every step, and add the weight / bias gradients straight into the arena
+                from ..parallel import arena as _arena
+
+                ar = _arena.find_arena(weight)
+                if ar is not None:
+                    y = _gemm.linear_arena(x, weight, bias, activation, ar)
+                    if y is not None:
+                        return y
             return _gemm.linear_bf16(x, weight, bias, activation)
     w = weight
     if not torch.is_autocast_enabled() and w.dtype != x.dtype:
