@@ -12,7 +12,7 @@ import torch.nn.functional as F
 from ..tensor import Tensor, Dim, batch_dim
 from ._utils import wrap, axis_of
 
-__all__ = ["cross_entropy", "ctc_loss", "ctc_best_path", "ctc_durations_from_path", "ctc_no_label_loop_blank_durations_from_path",
+__all__ = ["cross_entropy", "softmax_cross_entropy_smoothed_grad", "ctc_loss", "ctc_best_path", "ctc_durations_from_path", "ctc_no_label_loop_blank_durations_from_path",
            "ctc_greedy_decode", "edit_distance", "mse_loss", "binary_cross_entropy"]
 
 
@@ -56,6 +56,43 @@ def cross_entropy(*, estimated: Tensor, target: Tensor, axis: Dim, estimated_typ
     if target.sparse_dim is not None:
         return -gather(log_prob, indices=target, axis=axis)
     return -matmul(target, log_prob, reduce=axis)
+
+
+def softmax_cross_entropy_smoothed_grad(*, logits: Tensor, target: Tensor, axis: Dim, smoothing: float = 0.0,
+                                        with_argmax: bool = False) -> Union[Tensor, Tuple[Tensor, Tensor]]:
+    """
+    The usual teacher-forced training criterion in one pass over the logits::
+
+        log_prob = rf.log_softmax(logits, axis=axis)
+        log_prob = rf.label_smoothed_log_prob_gradient(log_prob, smoothing, axis=axis)
+        loss = rf.cross_entropy(target=target, estimated=log_prob, estimated_type="log-probs", axis=axis)
+        best = rf.reduce_argmax(logits, axis=axis)          # with_argmax
+
+    On the GPU one kernel reads the logits once in forward (online softmax, target logit, arg max) and once in backward (writes
+    ``softmax - (1-s) one_hot - s/V``); the [.., V] log-probabilities, their smoothed gradient and the fp32 copies of the composed
+    form are never materialised. Elsewhere the composed form runs.
+
+    :param logits: [..., axis]
+    :param target: sparse, sparse_dim == axis
+    :param smoothing: label smoothing applied to the gradient only (the loss value is the plain negative log likelihood)
+    :param with_argmax: also return the arg max over axis (sparse tensor like target)
+    :return: loss with the dims of logits without axis (, arg max)
+    """
+    from ..ops import softmax_ce as _ce
+
+    rest = [d for d in logits._dims if d != axis]
+    raw = logits.copy_compatible_to_dims_raw(rest + [axis])
+    tgt = target.copy_compatible_to_dims_raw(rest)
+    shape = list(raw.shape[:-1])
+    if list(tgt.shape) != shape:
+        tgt = tgt.expand(*shape)
+    res = _ce.softmax_cross_entropy(raw.reshape(-1, raw.shape[-1]), tgt.reshape(-1), float(smoothing), grad_only_smoothing=True,
+                                    with_argmax=with_argmax)
+    if not with_argmax:
+        return wrap(res.reshape(shape), rest)
+    loss, best = res
+    best_t = Tensor("argmax", dims=rest, dtype=target.dtype, sparse_dim=axis, raw_tensor=best.reshape(shape).to(tgt.dtype))
+    return wrap(loss.reshape(shape), rest), best_t
 
 
 def mse_loss(estimated: Tensor, target: Tensor) -> Tensor:

@@ -94,11 +94,10 @@ def train_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
     out_t, _ = rf.pad(targets, axes=[tgt_spatial], padding=[(0, 1)], value=model.eos, out_dims=[tgt_ext], handle_dynamic_dims=True)
     enc_state = model.decoder.transform_encoder(enc, axis=enc_spatial)
     logits, _ = model.decoder(inp, spatial_dim=tgt_ext, encoder=enc_state, state=model.decoder.default_initial_state(batch_dims=[batch_dim]))
-    log_prob = rf.log_softmax(logits, axis=model.vocab_dim)
-    log_prob = rf.label_smoothed_log_prob_gradient(log_prob, model.label_smoothing, axis=model.vocab_dim)
-    ce = rf.cross_entropy(target=out_t, estimated=log_prob, estimated_type="log-probs", axis=model.vocab_dim)
+    ce, best = rf.softmax_cross_entropy_smoothed_grad(logits=logits, target=out_t, axis=model.vocab_dim, smoothing=model.label_smoothing,
+                                                      with_argmax=True)
     ce.mark_as_loss("ce", use_normalized_loss=True)
-    err = rf.reduce_argmax(logits, axis=model.vocab_dim) != out_t
+    err = best != out_t
     err.mark_as_loss("fer", as_error=True)
 
 

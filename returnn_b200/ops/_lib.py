@@ -62,7 +62,7 @@ def use_native(*tensors) -> bool:
 
     if not tensors or not all(isinstance(t, torch.Tensor) and t.is_cuda for t in tensors if t is not None):
         return False
-    if os.environ.get("RETURNN_B200_DISABLE_NATIVE", "0") == "1":
+    if _env_data.get(b"RETURNN_B200_DISABLE_NATIVE", b"0") == b"1":  # read on every call (tests toggle it), without the str encode
         return False
     lib = get_lib()
     if lib is None:
@@ -74,11 +74,25 @@ def use_native(*tensors) -> bool:
     return True
 
 
+_env_data = getattr(os.environ, "_data", None)
+if not isinstance(_env_data, dict) or (_env_data and not isinstance(next(iter(_env_data)), bytes)):
+
+    class _EnvBytes:
+        """fallback where os.environ has no bytes-keyed dict behind it"""
+
+        @staticmethod
+        def get(key: bytes, default: bytes) -> bytes:
+            return os.environ.get(key.decode(), default.decode()).encode()
+
+    _env_data = _EnvBytes()
+
+
 def stream_ptr() -> int:
     """current torch CUDA stream as integer handle"""
     import torch
 
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle without the Stream object (current_stream() costs ~15 us of Python per call; a step makes hundreds)
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 _launch_count = 0

@@ -31,18 +31,17 @@ def available(x: torch.Tensor) -> bool:
 
 def status_tensor(device) -> torch.Tensor:
     """device word written by a kernel that gave up waiting (0 = fine)"""
-    key = str(device)
-    t = _status.get(key)
+    t = _status.get(device)
     if t is None:
         t = torch.zeros(1, dtype=torch.int32, device=device)
-        _status[key] = t
+        _status[device] = t
     return t
 
 
 def check_status(device=None):
     """raise if any GEMM launch since the last check reported a timeout (synchronises)"""
     for key, t in _status.items():
-        if device is not None and key != str(device):
+        if device is not None and str(key) != str(device):
             continue
         v = int(t.item())
         if v != 0:

@@ -134,6 +134,9 @@ class Engine(EngineBase):
         self._tensorboard_writer = None
         self._tensorboard_opts = config.typed_value("tensorboard_opts", {}) or {}
         self._graph_step = None
+        self._copy_stream = None  # side stream of stage_batch
+        self._pending_losses = None  # (names, pinned host buffer, event) of the last step with a deferred loss read
+        self._loss_slots = None
         self._epoch_mp_pending = 0
         self._nvtx = config.bool("torch_nvtx_ranges", False) and self._device.startswith("cuda")
 
@@ -424,17 +427,66 @@ class Engine(EngineBase):
         if self._epoch_end_func:
             self._epoch_end_func(epoch=self.epoch, step=self.global_train_step, model=self._orig_model, **get_fwd_compat_kwargs())
 
-    def run_train_step(self, extern_data_raw: Dict[str, Any], *, read_losses: bool = True) -> Dict[str, Any]:
+    def stage_batch(self, extern_data_raw: Dict[str, Any]) -> Dict[str, Any]:
+        """
+        Start the host-to-device copy of a collated batch on the engine's copy stream, so that it runs while the kernels of the
+        step before are still executing. The result is passed to ``run_train_step`` in place of the host batch; that call makes
+        the compute stream wait for the copy. Sequence lengths and other metadata stay on the host.
+
+        :param extern_data_raw: output of the data loader / ``collate_batch`` (pinned host tensors make the copy asynchronous)
+        :return: the same dict with the data tensors on the device
+        """
+        if not str(self._device).startswith("cuda"):
+            return extern_data_raw
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self._device)
+        out = dict(extern_data_raw)
+        with torch.cuda.stream(self._copy_stream):
+            for k, data in self.extern_data.data.items():
+                v = extern_data_raw.get(k)
+                if isinstance(v, torch.Tensor) and not v.is_cuda and data.dtype != "string":
+                    out[k] = v.to(self._device, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(self._copy_stream)
+        out["_staged_event"] = ev
+        return out
+
+    def flush_losses(self) -> Dict[str, Any]:
+        """
+        :return: the losses of the last step run with ``read_losses="deferred"`` that were not handed out yet ({} if none)
+        """
+        pending, self._pending_losses = self._pending_losses, None
+        if pending is None:
+            return {}
+        names, host, ev = pending
+        if ev is not None:
+            ev.synchronize()
+        return dict(zip(names, host[: len(names)].tolist()))
+
+    def run_train_step(self, extern_data_raw: Dict[str, Any], *, read_losses: Union[bool, str] = True) -> Dict[str, Any]:
         """
         One complete training step on one collated batch: host-to-device copy of the inputs, ``train_step`` under
         autocast, backward with the gradient reduction, optimizer update, and (``read_losses``) one device-to-host read of
         the summed losses. This is the unit that ``train_epoch`` repeats; it is public so that benchmarks and custom
         loops can drive the engine batch by batch.
 
-        :param extern_data_raw: output of the data loader / ``collate_batch`` (host tensors; pinned memory makes the copy async)
+        ``read_losses="deferred"`` pipelines the read: the losses of this step are copied to pinned host memory asynchronously
+        and the call returns the losses of the step BEFORE (read after this step's kernels were issued, so the device never
+        runs dry while the host waits); ``flush_losses()`` returns the last ones.
+
+        :param extern_data_raw: output of the data loader / ``collate_batch`` (host tensors; pinned memory makes the copy async),
+            or of ``stage_batch`` (copy already under way on the copy stream)
+        :param read_losses: True, False or "deferred"
         :return: loss name -> float (``read_losses``) or device scalar tensor
         """
         dist = self._torch_distributed_ctx
+        staged_ev = extern_data_raw.get("_staged_event")
+        if staged_ev is not None:
+            cur = torch.cuda.current_stream()
+            cur.wait_event(staged_ev)
+            for v in extern_data_raw.values():
+                if isinstance(v, torch.Tensor) and v.is_cuda:
+                    v.record_stream(cur)
         self._updater.get_optimizer().zero_grad()
         extern_data = extern_data_util.raw_dict_to_extern_data(
             extern_data_raw, extern_data_template=self.extern_data, device=self._device,
@@ -464,6 +516,21 @@ class Engine(EngineBase):
         self._updater.set_current_train_step(global_train_step=self.global_train_step, epoch=self.epoch or 1, epoch_continuous=None)
         if not summed:
             return {}
+        if read_losses == "deferred" and not summed[0].is_cuda:
+            prev = self.flush_losses()
+            self._pending_losses = (names, torch.stack(summed).clone(), None)
+            return prev
+        if read_losses == "deferred":
+            slot = self._loss_slots[self.global_train_step % 2] if self._loss_slots else None
+            if slot is None or slot[0].numel() < len(names):
+                self._loss_slots = [(torch.empty(max(16, len(names)), dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+                slot = self._loss_slots[self.global_train_step % 2]
+            host, ev = slot
+            host[: len(names)].copy_(torch.stack(summed), non_blocking=True)
+            ev.record()
+            prev = self.flush_losses()  # waits for the step before this one; this step's kernels are queued already
+            self._pending_losses = (names, host, ev)
+            return prev
         if read_losses:
             vals = torch.stack(summed).cpu().tolist()
             return dict(zip(names, vals))

@@ -111,3 +111,80 @@ def test_fused_arena_adamw_matches_torch_adamw_on_cpu():
         torch.testing.assert_close(pa, pb, atol=1e-6, rtol=1e-5)
     sd = oa.state_dict()
     assert set(sd["state"][0].keys()) >= {"exp_avg", "exp_avg_sq", "step"}
+
+
+def test_run_train_step_deferred_losses_match_immediate():
+    """``read_losses="deferred"`` hands out the loss of the step before; ``flush_losses`` the last one; same values as reading at once"""
+    _deferred_losses_case("cpu")
+
+
+@pytest.mark.gpu
+def test_run_train_step_staged_batches_and_deferred_losses_gpu():
+    """the same with the batch copied on the copy stream from pinned memory and the loss read through the pinned ring"""
+    _deferred_losses_case("cuda")
+
+
+def _deferred_losses_case(device):
+    import returnn_b200.frontend as rf
+    from returnn_b200.tensor import Tensor, Dim, batch_dim
+    from returnn_b200.config import Config, set_global_config
+    from returnn_b200.torch.engine import Engine
+    from returnn_b200.datasets.generating import StaticDataset
+    from returnn_b200.utils.basic import BehaviorVersion
+
+    time_dim = Dim(None, name="time")
+    in_dim, out_dim = Dim(5, name="in"), Dim(3, name="out")
+
+    class Model(rf.Module):
+        def __init__(self):
+            super().__init__()
+            self.lin = rf.Linear(in_dim, out_dim)
+
+    def get_model(**_kw):
+        return Model()
+
+    def train_step(*, model, extern_data, **_kw):
+        x, y = extern_data["data"], extern_data["classes"]
+        logits = model.lin(x)
+        loss = rf.cross_entropy(estimated=logits, estimated_type="logits", target=y, axis=out_dim)
+        loss.mark_as_loss("ce")
+
+    rng = numpy.random.RandomState(1)
+    seqs = [{"data": rng.randn(7, 5).astype("float32"), "classes": rng.randint(0, 3, (7,)).astype("int32")} for _ in range(4)]
+
+    def make_engine():
+        cfg = Config({"task": "train", "backend": "torch", "behavior_version": 21, "device": device, "get_model": get_model, "train_step": train_step,
+                      "extern_data": {"data": {"dims": (batch_dim, time_dim, in_dim), "dtype": "float32"},
+                                      "classes": {"dims": (batch_dim, time_dim), "sparse_dim": out_dim, "dtype": "int32"}},
+                      "batch_size": 100, "learning_rate": 0.1, "optimizer": {"class": "sgd"}, "num_epochs": 1, "log_verbosity": 1, "random_seed": 3})
+        set_global_config(cfg)
+        BehaviorVersion._reset(21)
+        data = StaticDataset(data=seqs, output_dim={"data": (5, 2), "classes": (3, 1)})
+        data.initialize()
+        eng = Engine(cfg)
+        eng.init_train_from_config(cfg, data, None, None)
+        eng.epoch = 1
+        eng._pt_model.train()
+        return eng
+
+    def batch(i):
+        s = seqs[i]
+        res = {"data": torch.from_numpy(s["data"])[None], "classes": torch.from_numpy(s["classes"])[None],
+               "data:seq_len": torch.tensor([7], dtype=torch.int32), "classes:seq_len": torch.tensor([7], dtype=torch.int32)}
+        if device == "cuda":
+            res = {k: (v.pin_memory() if not k.endswith(":seq_len") else v) for k, v in res.items()}
+        return res
+
+    eng = make_engine()
+    immediate = [eng.run_train_step(batch(i), read_losses=True)["ce"] for i in range(4)]
+    eng = make_engine()
+    got = []
+    for i in range(4):
+        res = eng.run_train_step(eng.stage_batch(batch(i)), read_losses="deferred")
+        assert (res == {}) == (i == 0)
+        if res:
+            got.append(res["ce"])
+    got.append(eng.flush_losses()["ce"])
+    assert eng.flush_losses() == {}
+    numpy.testing.assert_allclose(got, immediate, rtol=1e-6 if device == "cpu" else 1e-3)
+    assert immediate[-1] < immediate[0] or len(set(immediate)) > 1

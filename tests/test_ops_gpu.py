@@ -148,6 +148,29 @@ def test_softmax_ce(rows, v, dtype, smoothing):
 
 
 @gpu
+@pytest.mark.parametrize("rows,v", [(9, 10001), (32, 32000)])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_softmax_ce_smoothed_gradient_and_argmax(rows, v, dtype):
+    """loss = NLL, gradient smoothed uniformly over V; arg max per row from the same pass"""
+    _need_lib()
+    from returnn_b200.ops import softmax_ce as ce
+
+    torch.manual_seed(5)
+    logits = (torch.randn(rows, v, device="cuda") * 3).to(dtype).requires_grad_(True)
+    tgt = torch.randint(0, v, (rows,), device="cuda", dtype=torch.int32)
+    w = torch.rand(rows, device="cuda")
+    loss, best = ce.softmax_cross_entropy(logits, tgt, 0.1, grad_only_smoothing=True, with_argmax=True)
+    (loss * w).sum().backward()
+    l32 = logits.detach().float().requires_grad_(True)
+    ref = ce.softmax_cross_entropy_reference(l32, tgt, 0.1, grad_only_smoothing=True)
+    (ref * w).sum().backward()
+    torch.testing.assert_close(loss, ref, atol=2e-3, rtol=1e-4)
+    tol = 1e-2 if dtype == torch.bfloat16 else 1e-5
+    torch.testing.assert_close(logits.grad.float(), l32.grad, atol=tol, rtol=tol)
+    assert torch.equal(best.long(), logits.detach().float().argmax(dim=-1))
+
+
+@gpu
 def test_log_mel_kernel_matches_stft_path():
     """fused log-mel kernel against the RF path (torch.fft) on the same audio"""
     from returnn_b200.tensor import Tensor, Dim, batch_dim

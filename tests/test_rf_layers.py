@@ -121,3 +121,27 @@ def test_ctc_loss_against_torch():
     lp = torch.log_softmax(x.raw_tensor, -1).transpose(0, 1)
     ref = torch.nn.functional.ctc_loss(lp, tg.raw_tensor.long(), torch.tensor([9, 6]), torch.tensor([3, 2]), blank=5, reduction="none")
     torch.testing.assert_close(loss.raw_tensor, ref, atol=1e-4, rtol=1e-4)
+
+
+def test_softmax_cross_entropy_smoothed_grad_equals_composition():
+    """the one-call criterion equals log_softmax -> label_smoothed_log_prob_gradient -> cross_entropy (value and gradient)"""
+    torch.manual_seed(0)
+    time_dim = Dim(None, name="time")
+    time_dim.dyn_size_ext = Tensor("l", dims=[batch_dim], dtype="int32", raw_tensor=torch.tensor([5, 3], dtype=torch.int32))
+    vocab = Dim(11, name="vocab")
+    raw = torch.randn(2, 5, 11, requires_grad=True)
+    raw2 = raw.detach().clone().requires_grad_(True)
+    tgt = Tensor("t", dims=[batch_dim, time_dim], dtype="int64", sparse_dim=vocab, raw_tensor=torch.randint(0, 11, (2, 5)))
+    logits = Tensor("x", dims=[batch_dim, time_dim, vocab], dtype="float32", raw_tensor=raw)
+    loss, best = rf.softmax_cross_entropy_smoothed_grad(logits=logits, target=tgt, axis=vocab, smoothing=0.1, with_argmax=True)
+    logits2 = Tensor("x", dims=[batch_dim, time_dim, vocab], dtype="float32", raw_tensor=raw2)
+    lp = rf.log_softmax(logits2, axis=vocab)
+    lp = rf.label_smoothed_log_prob_gradient(lp, 0.1, axis=vocab)
+    ref = rf.cross_entropy(target=tgt, estimated=lp, estimated_type="log-probs", axis=vocab)
+    torch.testing.assert_close(loss.raw_tensor, ref.copy_compatible_to_dims_raw(loss.dims))
+    w = torch.rand(2, 5)
+    (loss.raw_tensor * w).sum().backward()
+    (ref.copy_compatible_to_dims_raw(loss.dims) * w).sum().backward()
+    torch.testing.assert_close(raw.grad, raw2.grad, atol=1e-6, rtol=1e-5)
+    assert torch.equal(best.raw_tensor, rf.reduce_argmax(logits2, axis=vocab).copy_compatible_to_dims_raw(best.dims))
+    assert best.sparse_dim == vocab
