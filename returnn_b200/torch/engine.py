@@ -281,6 +281,64 @@ class Engine(EngineBase):
         zero_grad_next_step = True
         cur_count_grad_accum = 0
         extern_data = None
+        # per-step bookkeeping (loss values on the host, progress line, tensorboard, non-finite check). With the pipelined read
+        # (default on CUDA, ``torch_deferred_loss_read``) it runs one step late, after the following step was issued.
+        deferred_read = self.config.bool("torch_deferred_loss_read", str(self._device).startswith("cuda"))
+        loss_ring = None
+        pending_step = None
+
+        def finish_step(rec):
+            """losses of one step reach the host here"""
+            nonlocal elapsed_computation_time, accumulated_losses_dict, accumulated_inv_norm_factors_dict
+            if "vals" in rec:
+                host_vals = rec["vals"]
+            else:
+                rec["event"].synchronize()
+                host_vals = rec["host"][: rec["n"]].tolist()
+            names_ = rec["names"]
+            losses_dict = NumbersDict({n: host_vals[i] for i, n in enumerate(names_)})
+            inv_norm_factors_dict = NumbersDict()
+            j = len(names_)
+            for i, n in enumerate(names_):
+                if rec["inv_list"][i] is not None:
+                    inv_norm_factors_dict[n] = host_vals[j]
+                    j += 1
+                else:
+                    inv_norm_factors_dict[n] = rec["static_inv"][i]
+            if self._updater._log_grad_norm and rec["grad_norm"] is not None:
+                losses_dict["grad_norm:p2"] = float(rec["grad_norm"])
+                inv_norm_factors_dict["grad_norm:p2"] = 1.0
+            step_end_time = time.monotonic()
+            step_duration = step_end_time - rec["step_begin_time"]
+            if "vals" not in rec:
+                # the wait above belongs to the step that was issued meanwhile: count each interval once
+                step_duration = step_end_time - max(rec["step_begin_time"], finish_step.last_end)
+            finish_step.last_end = step_end_time
+            elapsed_computation_time += step_duration
+            accumulated_losses_dict += losses_dict
+            accumulated_inv_norm_factors_dict += inv_norm_factors_dict
+            info = losses_dict / inv_norm_factors_dict
+            if self._calculate_exp_loss and info.has_values():
+                extended = {}
+                for key, value in info.items():
+                    extended[key] = value
+                    if key in rec["score_keys"]:
+                        try:
+                            extended[key + ":exp"] = math.exp(value)
+                        except OverflowError:
+                            extended[key + ":exp"] = float("inf")
+                info = NumbersDict(extended)
+            _print_process("ep %i train" % self.epoch, step=rec["step_idx"], eval_info=dict(info.items()), step_duration=step_duration,
+                           start_elapsed=step_end_time - epoch_start_time, complete_frac=rec["complete_frac"], num_seqs=rec["num_seqs"],
+                           seq_idx=rec["last_seq_idx"], log_memory_usage_device=self._device if self._log_memory_usage else None)
+            if self._use_tensorboard:
+                self._tb_log("train", dict(info.items()), self.global_train_step)
+            if self._stop_on_nonfinite_train_score:
+                if any(math.isinf(v) or math.isnan(v) for v in accumulated_losses_dict.values()):
+                    self._handle_run_exception(None, extern_data=rec["extern_data"], always_direct_print=True)
+                    raise Exception("Inf/nan score in step %i." % rec["step_idx"])
+
+        finish_step.last_end = 0.0
         try:
             while True:
                 with _record("data_loading", self._nvtx):
@@ -290,6 +348,9 @@ class Engine(EngineBase):
                 if dist and (step_idx == 0 or extern_data_raw is None or dist.should_sync_now(epoch_step_idx=step_idx) or dist.reduce_type != "param"):
                     torch.distributed.all_reduce(_has_data, op=torch.distributed.ReduceOp.MIN)
                 if not _has_data[0]:
+                    if pending_step is not None:
+                        finish_step(pending_step)
+                        pending_step = None
                     break
                 for k, v in extern_data_raw.items():
                     if k.endswith(":seq_len"):
@@ -357,34 +418,25 @@ class Engine(EngineBase):
                         dist.step_after_param_update(module=self._pt_model, epoch_step_idx=step_idx)
                 else:
                     zero_grad_next_step = False
-                host_vals = stacked.cpu().tolist() if stacked is not None else []
-                losses_dict = NumbersDict({n: host_vals[i] for i, n in enumerate(names)})
-                inv_norm_factors_dict = NumbersDict()
-                j = len(names)
-                for i, n in enumerate(names):
-                    if inv_list[i] is not None:
-                        inv_norm_factors_dict[n] = host_vals[j]
-                        j += 1
-                    else:
-                        inv_norm_factors_dict[n] = float(train_ctx.losses[n].get_inv_norm_factor())
-                if self._updater._log_grad_norm and grad_norm is not None:
-                    losses_dict["grad_norm:p2"] = float(grad_norm)
-                    inv_norm_factors_dict["grad_norm:p2"] = 1.0
-                step_end_time = time.monotonic()
-                step_duration = step_end_time - step_begin_time
-                elapsed_computation_time += step_duration
-                accumulated_losses_dict += losses_dict
-                accumulated_inv_norm_factors_dict += inv_norm_factors_dict
-                eval_info = self._maybe_extend_losses_info(losses_dict / inv_norm_factors_dict)
-                _print_process("ep %i train" % self.epoch, step=step_idx, eval_info=dict(eval_info.items()), step_duration=step_duration,
-                               start_elapsed=step_end_time - epoch_start_time, complete_frac=complete_frac, num_seqs=num_seqs_,
-                               seq_idx=last_seq_idx, log_memory_usage_device=self._device if self._log_memory_usage else None)
-                if self._use_tensorboard:
-                    self._tb_log("train", dict(eval_info.items()), self.global_train_step)
-                if self._stop_on_nonfinite_train_score:
-                    if any(math.isinf(v) or math.isnan(v) for v in accumulated_losses_dict.values()):
-                        self._handle_run_exception(None, extern_data=extern_data, always_direct_print=True)
-                        raise Exception("Inf/nan score in step %i." % step_idx)
+                rec = dict(names=names, inv_list=inv_list, static_inv=[None if inv_list[i] is not None else float(train_ctx.losses[n].get_inv_norm_factor())
+                                                                      for i, n in enumerate(names)],
+                           score_keys=set(k for k, v in train_ctx.losses.items() if not v.as_error), grad_norm=grad_norm, step_idx=step_idx,
+                           step_begin_time=step_begin_time, complete_frac=complete_frac, num_seqs=num_seqs_, last_seq_idx=last_seq_idx,
+                           extern_data=extern_data)
+                if deferred_read and stacked is not None and stacked.is_cuda:
+                    # pipelined read: async copy into a pinned ring; the host waits for it after the NEXT step was issued
+                    if loss_ring is None or loss_ring[0][0].numel() < stacked.numel():
+                        loss_ring = [(torch.empty(max(32, stacked.numel()), dtype=torch.float32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+                    host, ev = loss_ring[step_idx % 2]
+                    host[: stacked.numel()].copy_(stacked, non_blocking=True)
+                    ev.record()
+                    rec.update(host=host, event=ev, n=stacked.numel())
+                    if pending_step is not None:
+                        finish_step(pending_step)
+                    pending_step = rec
+                else:
+                    rec["vals"] = stacked.cpu().tolist() if stacked is not None else []
+                    finish_step(rec)
                 step_idx += 1
                 self.global_train_step += 1
                 ec = (self.epoch - 1 + complete_frac) if complete_frac >= 0 else ((self.epoch - 1 + (last_seq_idx + 1) / num_seqs_) if num_seqs_ > 0 else None)
@@ -393,6 +445,9 @@ class Engine(EngineBase):
                     profiler.step()
                     if profiler.done:
                         break
+            if pending_step is not None:
+                finish_step(pending_step)
+                pending_step = None
         except Exception as exc:
             self._handle_run_exception(exc, extern_data=extern_data)
             raise
