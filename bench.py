@@ -309,6 +309,7 @@ def run_ours(args):
             "config": {"model": "conformer-ctc 12x512 h8 ff2048 conv32 sub6 vocab10k", "global_batch": "%i padded frames per GPU x %i" % (BATCH_FRAMES, world),
                        "seq_len": "300-2000 frames (10 ms)", "parallelism": "dp%i" % world, "optimizer": "adamw clip5",
                        "l2": "working set per step (fp32 params, grads, Adam moments ~1.5 GB) exceeds L2; a distinct batch every step",
+                       "batches": "sequence lengths drawn from one seed on every rank (equal work per rank), feature and label values per rank",
                        "native_lib": os.path.exists(_lib.lib_path())},
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "audio-s/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,
