@@ -16,6 +16,7 @@
 // Semantics, gate order (i, f, g, o), masking and the tensors saved for backward are those of lstm.cu
 // (reference: returnn/native_op.py:1029-1179 NativeLstm2, returnn/torch/frontend/_backend.py:2796-2810).
 #include "common.cuh"
+#include "gemm.h"
 #include <cooperative_groups.h>
 
 namespace {
@@ -69,7 +70,7 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 
 // red[row][n] += sum_k A[row][k] * Bs[n][k] for rows < n_rows; A in global (written by other CTAs: read through L2), Bs resident
 // in shared memory with row pitch K + kPad. The warp w takes k in [w*K/8, (w+1)*K/8).
-template <int NOUT>
+template <int NOUT, int kPrefetch>
 __device__ __forceinline__ void step_matmul(const bf16* __restrict__ A, int n_rows, int K, const bf16* __restrict__ Bs, float* __restrict__ red) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
@@ -96,8 +97,8 @@ __device__ __forceinline__ void step_matmul(const bf16* __restrict__ A, int n_ro
     }
   };
   // chunks of kPrefetch k-steps: all fragment loads of a chunk are issued before its first multiply, so a chunk costs one
-  // L2 round trip (the forward contraction of H = 1024 is a single chunk per warp)
-  constexpr int kPrefetch = 8;
+  // L2 round trip (with kPrefetch = 8 the forward contraction of H = 1024 is a single chunk per warp; the two-direction kernels
+  // use 4 to stay within 128 registers, so that two CTAs share an SM and cover each other's round trips)
   const int k_begin = warp * kw, k_end = (warp + 1) * kw;
   for (int kc = k_begin; kc < k_end; kc += 16 * kPrefetch) {
     uint32_t a[kPrefetch][3][4];
@@ -150,7 +151,8 @@ struct FwdArgs {
   int* status;          // receives (5 << 24) | cta when a barrier wait ran out
 };
 
-__global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p) {
+template <int kPrefetch>
+__device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const uint32_t n_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.H, B = p.B;
   const int pitch = H + kPad;
@@ -158,8 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p
   float* red = reinterpret_cast<float*>(Ws + (size_t)4 * kUnits * pitch);       // [48][4*kUnits]
   float* cst = red + kMaxRows * 4 * kUnits;                                     // [48][kUnits] cell state
   float* hst = cst + kMaxRows * kUnits;                                         // [48][kUnits] own slice of h (fp32)
-  const int j0 = blockIdx.x * kUnits;
-  const uint32_t n_cta = gridDim.x;
+  const int j0 = cta * kUnits;
   // resident slice: 4*kUnits rows of H elements, 16-byte copies
   for (int idx = threadIdx.x; idx < 4 * kUnits * (H / 8); idx += kThreads) {
     const int r = idx / (H / 8), v = idx % (H / 8);
@@ -202,7 +203,7 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p
     bf16* h_nxt = p.hbuf + (size_t)((s + 1) & 1) * B * H;
     for (int idx = threadIdx.x; idx < kMaxRows * 4 * kUnits; idx += kThreads) red[idx] = 0.f;
     __syncthreads();
-    step_matmul<4 * kUnits>(h_cur, B, H, Ws, red);
+    step_matmul<4 * kUnits, kPrefetch>(h_cur, B, H, Ws, red);
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < kSlots; ++i) {
@@ -248,6 +249,21 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p
   }
 }
 
+__global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p) { fwd_body<8>(p, blockIdx.x, gridDim.x); }
+
+// Both directions of a bidirectional layer in one launch: the first half of the grid runs d[0], the second half d[1], each with
+// its own barrier words. Two CTAs share an SM (128 registers per thread), so the two recurrences, each bound by the latency of
+// its grid barrier and L2 round trip per step, overlap instead of running one after the other.
+struct FwdPair {
+  FwdArgs d[2];
+};
+
+__global__ void __launch_bounds__(kThreads, 2) lstm_persist_fwd_pair_kernel(const __grid_constant__ FwdPair pp) {
+  const int half = gridDim.x / 2;
+  if ((int)blockIdx.x < half) fwd_body<4>(pp.d[0], blockIdx.x, half);
+  else fwd_body<4>(pp.d[1], blockIdx.x - half, half);
+}
+
 struct BwdArgs {
   const bf16* dy;        // [T,B,H] or null
   const float *dh_final, *dc_final;  // [B,H] or null
@@ -263,7 +279,8 @@ struct BwdArgs {
   int* status;
 };
 
-__global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p) {
+template <int kPrefetch>
+__device__ __forceinline__ void bwd_body(const BwdArgs& p, const int cta, const uint32_t n_cta) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.H, B = p.B, K = 4 * p.H;
   const int pitch = K + kPad;
@@ -271,8 +288,7 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p
   float* red = reinterpret_cast<float*>(Wt + (size_t)kUnits * pitch);  // [48][16]
   float* dhs = red + kMaxRows * kUnits;                              // [48][16] gradient arriving at h_t
   float* dcs = dhs + kMaxRows * kUnits;                              // [48][16] gradient arriving at c_t
-  const int j0 = blockIdx.x * kUnits;
-  const uint32_t n_cta = gridDim.x;
+  const int j0 = cta * kUnits;
   for (int idx = threadIdx.x; idx < K * (kUnits / 8); idx += kThreads) {
     // row n of W_rec, units j0 .. j0 + kUnits - 1, in 16-byte pieces
     const int n = idx / (kUnits / 8), piece = idx % (kUnits / 8);
@@ -318,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p
     for (int idx = threadIdx.x; idx < kMaxRows * kUnits; idx += kThreads) red[idx] = 0.f;
     ok = grid_barrier(p.counter, (++n_bar) * n_cta, p.abort_word, p.status);  // all slices of dz_t are written (and red is zero)
     if (!ok) break;
-    step_matmul<kUnits>(dz_t, B, K, Wt, red);
+    step_matmul<kUnits, kPrefetch>(dz_t, B, K, Wt, red);
     __syncthreads();
     for (int idx = threadIdx.x; idx < B * kUnits; idx += kThreads) dhs[idx] += red[idx];
     __syncthreads();
@@ -328,6 +344,18 @@ __global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p
     p.dh0[(size_t)b * H + j0 + u] = dhs[idx];
     p.dc0[(size_t)b * H + j0 + u] = dcs[idx];
   }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p) { bwd_body<8>(p, blockIdx.x, gridDim.x); }
+
+struct BwdPair {
+  BwdArgs d[2];
+};
+
+__global__ void __launch_bounds__(kThreads, 2) lstm_persist_bwd_pair_kernel(const __grid_constant__ BwdPair pp) {
+  const int half = gridDim.x / 2;
+  if ((int)blockIdx.x < half) bwd_body<4>(pp.d[0], blockIdx.x, half);
+  else bwd_body<4>(pp.d[1], blockIdx.x - half, half);
 }
 
 // barrier words of the calls in flight: 64 slots of (counter, abort word), handed out round robin
@@ -416,4 +444,111 @@ int rb_lstm_persist_bwd(const void* dy, const float* dh_final, const float* dc_f
     return RB_ERR_LAUNCH;
   }
   return RB_OK;
+}
+
+// ---- both directions of a bidirectional layer in one cooperative launch -------------------------------------------------
+
+// whether the two-direction kernels take this problem: the single-direction conditions, and both grids co-resident (two CTAs
+// per SM: checked through the occupancy of the pair kernels on the current device)
+RB_EXPORT int rb200_blstm_supported(int T, int B, int H) {
+  if (!rb_lstm_persist_supported(T, B, H)) return 0;
+  static int sm_count = 0, occ_fwd[2] = {-1, 0}, occ_bwd[2] = {-1, 0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  if (!sm_count && cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+  if (occ_fwd[0] != H) {
+    const size_t sf = fwd_smem(H), sb = bwd_smem(H);
+    if (cudaFuncSetAttribute(lstm_persist_fwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sf) != cudaSuccess ||
+        cudaFuncSetAttribute(lstm_persist_bwd_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sb) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_fwd[1], lstm_persist_fwd_pair_kernel, kThreads, sf) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ_bwd[1], lstm_persist_bwd_pair_kernel, kThreads, sb) != cudaSuccess) {
+      cudaGetLastError();
+      return 0;
+    }
+    occ_fwd[0] = occ_bwd[0] = H;
+  }
+  const int need = 2 * (H / kUnits);
+  return occ_fwd[1] * sm_count >= need && occ_bwd[1] * sm_count >= need;
+}
+
+// ptrs[d * 11 + i] for direction d (0: forward in time, 1: reversed):
+//   0 z_in [T,B,4H] bf16, 1 w_rec [4H,H] bf16, 2 h0, 3 c0 [B,H] fp32, 4 y [T,B,H] bf16, 5 c_all [T,B,H] fp32, 6 gates [T,B,4H] bf16,
+//   7 hprev_all [T,B,H] bf16, 8 h_final, 9 c_final [B,H] fp32, 10 hbuf (scratch, 2*B*H bf16)
+RB_EXPORT int rb200_blstm_fwd(void* const* ptrs, const int* lens, int T, int B, int H, int* status, cudaStream_t stream) {
+  if (T <= 0 || B <= 0) return RB_OK;
+  if (!rb200_blstm_supported(T, B, H)) {
+    rb_set_error("blstm_fwd: shape T=%d B=%d H=%d is not supported by the two-direction kernel", T, B, H);
+    return RB_ERR_UNSUPPORTED;
+  }
+  FwdPair pp;
+  for (int d = 0; d < 2; ++d) {
+    unsigned int* sync_words = sync_slot();
+    if (!sync_words) {
+      rb_set_error("blstm_fwd: no barrier words");
+      return RB_ERR_LAUNCH;
+    }
+    void* const* q = ptrs + d * 11;
+    FwdArgs& a = pp.d[d];
+    a.z_in = (const bf16*)q[0]; a.w_rec = (const bf16*)q[1]; a.lens = lens; a.h0 = (const float*)q[2]; a.c0 = (const float*)q[3];
+    a.T = T; a.B = B; a.H = H; a.reverse = d;
+    a.y = (bf16*)q[4]; a.c_all = (float*)q[5]; a.gates = (bf16*)q[6]; a.hprev_all = (bf16*)q[7]; a.h_final = (float*)q[8]; a.c_final = (float*)q[9];
+    a.hbuf = (bf16*)q[10]; a.counter = sync_words; a.abort_word = reinterpret_cast<int*>(sync_words + 1); a.status = status;
+    cudaMemsetAsync(sync_words, 0, 2 * sizeof(unsigned int), stream);
+  }
+  const size_t smem = fwd_smem(H);
+  void* args[] = {&pp};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)lstm_persist_fwd_pair_kernel, dim3(2 * (H / kUnits)), dim3(kThreads), args, smem, stream);
+  if (e != cudaSuccess) {
+    rb_set_error("blstm_fwd: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return RB_ERR_LAUNCH;
+  }
+  return RB_OK;
+}
+
+// ptrs[d * 12 + i]: 0 dy [T,B,H] bf16 or null, 1 dh_final, 2 dc_final [B,H] fp32 or null, 3 w_rec bf16, 4 gates, 5 c_all, 6 c0, 7 hprev_all,
+//   8 dz [T,B,4H] bf16 (out), 9 dw_rec [4H,H] fp32 (accumulated into; may be null), 10 dh0, 11 dc0 [B,H] fp32 (out)
+RB_EXPORT int rb200_blstm_bwd(void* const* ptrs, const int* lens, int T, int B, int H, int* status, int* n_launch, cudaStream_t stream) {
+  if (T <= 0 || B <= 0) return RB_OK;
+  if (!rb200_blstm_supported(T, B, H)) {
+    rb_set_error("blstm_bwd: shape T=%d B=%d H=%d is not supported by the two-direction kernel", T, B, H);
+    return RB_ERR_UNSUPPORTED;
+  }
+  BwdPair pp;
+  for (int d = 0; d < 2; ++d) {
+    unsigned int* sync_words = sync_slot();
+    if (!sync_words) {
+      rb_set_error("blstm_bwd: no barrier words");
+      return RB_ERR_LAUNCH;
+    }
+    void* const* q = ptrs + d * 12;
+    BwdArgs& a = pp.d[d];
+    a.dy = (const bf16*)q[0]; a.dh_final = (const float*)q[1]; a.dc_final = (const float*)q[2]; a.w_rec = (const bf16*)q[3]; a.lens = lens;
+    a.gates = (const bf16*)q[4]; a.c_all = (const float*)q[5]; a.c0 = (const float*)q[6]; a.T = T; a.B = B; a.H = H; a.reverse = d;
+    a.dz = (bf16*)q[8]; a.dh0 = (float*)q[10]; a.dc0 = (float*)q[11];
+    a.counter = sync_words; a.abort_word = reinterpret_cast<int*>(sync_words + 1); a.status = status;
+    cudaMemsetAsync(sync_words, 0, 2 * sizeof(unsigned int), stream);
+  }
+  const size_t smem = bwd_smem(H);
+  void* args[] = {&pp};
+  cudaError_t e = cudaLaunchCooperativeKernel((const void*)lstm_persist_bwd_pair_kernel, dim3(2 * (H / kUnits)), dim3(kThreads), args, smem, stream);
+  if (e != cudaSuccess) {
+    rb_set_error("blstm_bwd: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    return RB_ERR_LAUNCH;
+  }
+  int launches = 3;
+  for (int d = 0; d < 2; ++d) {
+    void* const* q = ptrs + d * 12;
+    if (!q[9]) continue;
+    // dW_rec[4H,H] += dz^T [4H, T*B] . h_prev [T*B, H]
+    RbGemm g;
+    g.a = q[8]; g.b = q[7]; g.c = q[9]; g.m = 4 * H; g.n = H; g.k = T * B; g.lda = 4 * H; g.ldb = H; g.ldc = H;
+    g.a_mn_major = 1; g.b_mn_major = 1; g.out_fp32 = 1; g.accumulate = 2; g.status = status;
+    int st = rb_gemm(g, stream);
+    if (st) return st;
+    ++launches;
+  }
+  if (n_launch) *n_launch = launches;
+  return rb_check_launch("blstm_bwd");
 }

@@ -22,7 +22,7 @@ from .state import State
 from . import init as _init
 from ._utils import wrap
 
-__all__ = ["LSTM", "LstmState", "ZoneoutLSTM"]
+__all__ = ["LSTM", "LstmState", "ZoneoutLSTM", "bidirectional_lstm"]
 
 
 class LstmState(State):
@@ -97,6 +97,52 @@ class LSTM(Module):
 
         return LstmState(h=zeros(list(batch_dims) + [self.out_dim], feature_dim=self.out_dim),
                          c=zeros(list(batch_dims) + [self.out_dim], feature_dim=self.out_dim))
+
+
+def bidirectional_lstm(fw: LSTM, bw: LSTM, source: Tensor, *, spatial_dim: Dim, state_fw: Optional[LstmState] = None,
+                       state_bw: Optional[LstmState] = None) -> Tuple[Tensor, Tensor, LstmState, LstmState]:
+    """
+    ``fw(source, direction=1)`` and ``bw(source, direction=-1)`` over the same input. Same results as the two calls; on the GPU
+    both time loops run in one persistent kernel when the sizes agree (see ``ops.lstm.blstm``).
+
+    :return: output of fw, output of bw ({spatial_dim, batch.., out_dim} each), final states of fw and bw
+    """
+    from ..ops import lstm as _lstm
+
+    bdims = [d for d in source.dims if d not in (spatial_dim, fw.in_dim)]
+    if state_fw is None:
+        state_fw = fw.default_initial_state(batch_dims=bdims)
+    if state_bw is None:
+        state_bw = bw.default_initial_state(batch_dims=bdims)
+    fusable = (type(fw) is LSTM and type(bw) is LSTM and fw.in_dim == bw.in_dim and fw.out_dim.dimension == bw.out_dim.dimension
+               and spatial_dim != single_step_dim and source.raw_tensor.is_cuda and (fw.bias is None) == (bw.bias is None))
+    if not fusable:
+        yf, sf = fw(source, state=state_fw, spatial_dim=spatial_dim, direction=1)
+        yb, sb = bw(source, state=state_bw, spatial_dim=spatial_dim, direction=-1)
+        return yf, yb, sf, sb
+    x = source.copy_compatible_to_dims_raw([spatial_dim] + bdims + [fw.in_dim])
+    T = x.shape[0]
+    bshape = list(x.shape[1:-1])
+    x = x.reshape(T, -1, x.shape[-1])
+    B = x.shape[1]
+
+    def flat(t: Tensor, out_dim: Dim):
+        return t.copy_compatible_to_dims_raw(bdims + [out_dim]).expand(*bshape, -1).reshape(B, -1)
+
+    lens = None
+    if spatial_dim.is_dynamic() and spatial_dim.dyn_size_ext is not None and spatial_dim.dyn_size_ext.dims:
+        sz = spatial_dim.dyn_size_ext
+        if all(d in bdims for d in sz.dims):
+            lens = sz.copy_compatible_to_dims_raw(bdims).expand(*bshape).reshape(B).to(torch.int32)
+    params = [(m.ff_weight.raw_tensor, m.rec_weight.raw_tensor, m.bias.raw_tensor if m.bias is not None else None) for m in (fw, bw)]
+    (yf, hf, cf), (yb, hb, cb) = _lstm.blstm(x, lens, params[0], params[1], flat(state_fw.h, fw.out_dim), flat(state_fw.c, fw.out_dim),
+                                             flat(state_bw.h, bw.out_dim), flat(state_bw.c, bw.out_dim))
+    res = []
+    for m, y, h, c in ((fw, yf, hf, cf), (bw, yb, hb, cb)):
+        st = LstmState(h=wrap(h.reshape(bshape + [-1]), bdims + [m.out_dim], feature_dim=m.out_dim),
+                       c=wrap(c.reshape(bshape + [-1]), bdims + [m.out_dim], feature_dim=m.out_dim))
+        res.append((wrap(y.reshape([T] + bshape + [-1]), [spatial_dim] + bdims + [m.out_dim], feature_dim=m.out_dim), st))
+    return res[0][0], res[1][0], res[0][1], res[1][1]
 
 
 class ZoneoutLSTM(LSTM):

@@ -44,9 +44,7 @@ class BlstmLayer(rf.Module):
         self.out_dim = hidden + hidden
 
     def __call__(self, x: Tensor, *, spatial_dim: Dim) -> Tensor:
-        bdims = [d for d in x.dims if d not in (spatial_dim, x.feature_dim)]
-        yf, _ = self.fw(x, state=self.fw.default_initial_state(batch_dims=bdims), spatial_dim=spatial_dim, direction=1)
-        yb, _ = self.bw(x, state=self.bw.default_initial_state(batch_dims=bdims), spatial_dim=spatial_dim, direction=-1)
+        yf, yb, _, _ = rf.bidirectional_lstm(self.fw, self.bw, x, spatial_dim=spatial_dim)
         out, _ = rf.concat((yf, self.fw.out_dim), (yb, self.bw.out_dim), out_dim=self.out_dim)
         return out
 

@@ -224,6 +224,31 @@ def main():
             t_f, t_fb = _time(fwd, max(2, args.iters // 10)), _time(fb, max(2, args.iters // 10))
             report("lstm layer T=%i B=%i H=1024 (input GEMM + persistent recurrence)" % (T, Bl), t_f, t_fb, T * Bl * (I + 5 * Hl) * 2, T * Bl * (I + 5 * Hl) * 2 * 3,
                    {"fwd_us_per_step": round(t_f * 1e6 / T, 2), "bwd_us_per_step": round((t_fb - t_f) * 1e6 / T, 2)})
+            # both directions of a bidirectional layer: one launch for the two time loops against two launches in a row
+            w2 = [(torch.randn(4 * Hl, I, device=dev) * 0.02).requires_grad_(True), (torch.randn(4 * Hl, Hl, device=dev) * 0.02).requires_grad_(True),
+                  torch.zeros(4 * Hl, device=dev, requires_grad=True)]
+            if lstm_native.blstm_supported(x, w_rec, w2[1]):
+                from . import lstm as lstm_ops
+
+                def pair():
+                    (yf, _, _), (yb, _, _) = lstm_ops.blstm(x, ll, (w_ff, w_rec, bias), tuple(w2), h0, c0, h0, c0)
+                    return yf, yb
+
+                def seq():
+                    return (lstm_native.lstm(x, ll, w_ff, w_rec, bias, h0, c0, reverse=False)[0], lstm_native.lstm(x, ll, *w2, h0, c0, reverse=True)[0])
+
+                def fb_of(f):
+                    def run():
+                        a, b = f()
+                        (a.float().sum() + b.float().sum()).backward()
+                    return run
+
+                n_it = max(2, args.iters // 10)
+                tp_f, tp_fb = _time(pair, n_it), _time(fb_of(pair), n_it)
+                ts_f, ts_fb = _time(seq, n_it), _time(fb_of(seq), n_it)
+                report("blstm layer T=%i B=%i H=1024, both directions in one kernel" % (T, Bl), tp_f, tp_fb, 2 * T * Bl * (I + 5 * Hl) * 2,
+                       2 * T * Bl * (I + 5 * Hl) * 2 * 3, {"two_launches_fwd_ms": round(ts_f * 1e3, 3), "two_launches_fwd_bwd_ms": round(ts_fb * 1e3, 3),
+                                                            "speedup_fwd": round(ts_f / tp_f, 2), "speedup_fwd_bwd": round(ts_fb / tp_fb, 2)})
     from . import gemm as G
 
     G.check_status()

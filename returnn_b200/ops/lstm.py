@@ -90,3 +90,24 @@ def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_re
     if reverse:
         y = _reverse_padded(y, lens)
     return y, hT[0], cT[0]
+
+
+def blstm(x: torch.Tensor, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h0_bw, c0_bw):
+    """
+    Both directions of a bidirectional layer over the same input.
+
+    On the GPU the two recurrences run in ONE persistent kernel (half of the CTAs per direction, two CTAs per SM) when the
+    shape allows it: a recurrence is bound by the latency of its per-step grid barrier, not by throughput, so two of them
+    side by side take little more than one. Otherwise two calls of :func:`lstm`.
+
+    :param x: [T, B, in]
+    :param fw: (w_ff, w_rec, bias) of the direction that runs forward in time; ``bw``: of the reversed one
+    :return: (y_fw, h_T, c_T), (y_bw, h_T, c_T)
+    """
+    if x.is_cuda:
+        from . import lstm_native as _n
+
+        if _n.blstm_supported(x, fw[1], bw[1]):
+            return _n.blstm(x, lens, fw, bw, h0_fw, c0_fw, h0_bw, c0_bw)
+    return (lstm(x, lens, fw[0], fw[1], fw[2], h0_fw, c0_fw, reverse=False),
+            lstm(x, lens, bw[0], bw[1], bw[2], h0_bw, c0_bw, reverse=True))

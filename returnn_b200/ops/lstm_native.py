@@ -94,3 +94,105 @@ def lstm(x, lens: Optional[torch.Tensor], w_ff, w_rec, bias, h0, c0, reverse: bo
     l32 = lens.to(x.device, torch.int32).contiguous() if lens is not None else None
     y, h, c = _LstmRecFn.apply(z_in, w_rec, l32, h0, c0, bool(reverse))
     return y.to(x.dtype), h, c
+
+
+def blstm_supported(x, w_rec_fw, w_rec_bw) -> bool:
+    """both directions of one layer can run in ONE cooperative launch (two CTAs per SM): same sizes, persistent-kernel shapes"""
+    lib = _lib.get_lib()
+    if lib is None or not hasattr(lib, "rb200_blstm_fwd") or not available(x):
+        return False
+    if w_rec_fw.shape != w_rec_bw.shape or not supports(x, w_rec_fw):
+        return False
+    T, B, _ = x.shape
+    fn = _lib.bind("rb200_blstm_supported", [_i32, _i32, _i32])
+    return bool(fn(int(T), int(B), int(w_rec_fw.shape[1])))
+
+
+class _BlstmRecFn(torch.autograd.Function):
+    """the recurrences of both directions on pre-projected inputs z [T,B,4H], one kernel for the two time loops"""
+
+    @staticmethod
+    def forward(ctx, z_fw, z_bw, w_fw, w_bw, lens, h0_fw, c0_fw, h0_bw, c0_bw):
+        T, B, H4 = z_fw.shape
+        H = H4 // 4
+        dev = z_fw.device
+        bf = torch.bfloat16
+        per_dir = []
+        ptrs = (ctypes.c_void_p * 22)()
+        keep = []
+        for d, (z, w, h0, c0) in enumerate(((z_fw, w_fw, h0_fw, c0_fw), (z_bw, w_bw, h0_bw, c0_bw))):
+            z16 = z.to(bf).contiguous()
+            w16 = w.to(bf).contiguous()
+            y = torch.empty(T, B, H, dtype=bf, device=dev)
+            c_all = torch.empty(T, B, H, dtype=torch.float32, device=dev)
+            gates = torch.empty(T, B, H4, dtype=bf, device=dev)
+            hprev = torch.empty(T, B, H, dtype=bf, device=dev)
+            h_fin = torch.empty(B, H, dtype=torch.float32, device=dev)
+            c_fin = torch.empty(B, H, dtype=torch.float32, device=dev)
+            hbuf = torch.empty(2, B, H, dtype=bf, device=dev)
+            h0f, c0f = h0.float().contiguous(), c0.float().contiguous()
+            for i, t in enumerate((z16, w16, h0f, c0f, y, c_all, gates, hprev, h_fin, c_fin, hbuf)):
+                ptrs[d * 11 + i] = t.data_ptr()
+            keep.append((z16, hbuf))
+            per_dir.append((w16, gates, c_all, c0f, hprev, y, h_fin, c_fin))
+        st = _gemm.status_tensor(dev)
+        fn = _lib.bind("rb200_blstm_fwd", [_vp, _vp, _i32, _i32, _i32, _vp, _vp])
+        _lib.check(fn(ctypes.cast(ptrs, _vp), lens.data_ptr() if lens is not None else None, T, B, H, st.data_ptr(), _lib.stream_ptr()), "blstm_fwd")
+        _lib.count_launch(3)
+        (w16f, gf, caf, c0ff, hpf, yf, hff, cff), (w16b, gb, cab, c0fb, hpb, yb, hfb, cfb) = per_dir
+        ctx.save_for_backward(lens, w16f, gf, caf, c0ff, hpf, w16b, gb, cab, c0fb, hpb)
+        ctx.meta = (T, B, H, z_fw.dtype, w_fw.dtype, h0_fw.dtype, c0_fw.dtype)
+        zd = z_fw.dtype
+        return (yf.to(zd) if zd != bf else yf, yb.to(zd) if zd != bf else yb, hff.to(h0_fw.dtype), cff.to(c0_fw.dtype),
+                hfb.to(h0_bw.dtype), cfb.to(c0_bw.dtype))
+
+    @staticmethod
+    def backward(ctx, dy_fw, dy_bw, dh_fw, dc_fw, dh_bw, dc_bw):
+        lens, *rest = ctx.saved_tensors
+        T, B, H, z_dtype, w_dtype, h_dtype, c_dtype = ctx.meta
+        dev = rest[1].device
+        bf = torch.bfloat16
+        ptrs = (ctypes.c_void_p * 24)()
+        outs, keep = [], []
+        for d, (dy, dhf, dcf) in enumerate(((dy_fw, dh_fw, dc_fw), (dy_bw, dh_bw, dc_bw))):
+            w16, gates, c_all, c0f, hprev = rest[d * 5: d * 5 + 5]
+            dy16 = dy.to(bf).contiguous() if dy is not None else None
+            dhf32 = dhf.float().contiguous() if dhf is not None else None
+            dcf32 = dcf.float().contiguous() if dcf is not None else None
+            dz = torch.empty(T, B, 4 * H, dtype=bf, device=dev)
+            dw = torch.zeros(4 * H, H, dtype=torch.float32, device=dev)
+            dh0 = torch.empty(B, H, dtype=torch.float32, device=dev)
+            dc0 = torch.empty(B, H, dtype=torch.float32, device=dev)
+            for i, t in enumerate((dy16, dhf32, dcf32, w16, gates, c_all, c0f, hprev, dz, dw, dh0, dc0)):
+                ptrs[d * 12 + i] = t.data_ptr() if t is not None else None
+            keep.append((dy16, dhf32, dcf32))
+            outs.append((dz, dw, dh0, dc0))
+        st = _gemm.status_tensor(dev)
+        nl = ctypes.c_int(0)
+        fn = _lib.bind("rb200_blstm_bwd", [_vp, _vp, _i32, _i32, _i32, _vp, _vp, _vp])
+        _lib.check(fn(ctypes.cast(ptrs, _vp), lens.data_ptr() if lens is not None else None, T, B, H, st.data_ptr(), ctypes.addressof(nl),
+                      _lib.stream_ptr()), "blstm_bwd")
+        _lib.count_launch(nl.value)
+        (dzf, dwf, dh0f, dc0f), (dzb, dwb, dh0b, dc0b) = outs
+        return (dzf.to(z_dtype), dzb.to(z_dtype), dwf.to(w_dtype), dwb.to(w_dtype), None, dh0f.to(h_dtype), dc0f.to(c_dtype),
+                dh0b.to(h_dtype), dc0b.to(c_dtype))
+
+
+def blstm(x, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h0_bw, c0_bw):
+    """
+    Forward-in-time and reversed LSTM over the same input, both recurrences in one kernel.
+
+    :param x: [T, B, in]
+    :param fw: (w_ff [4H, in], w_rec [4H, H], bias [4H] or None) of the forward direction; ``bw`` likewise for the reversed one
+    :return: (y_fw [T,B,H], h_T, c_T), (y_bw [T,B,H], h_T, c_T)
+    """
+    from . import linear as _lin
+
+    bf = torch.bfloat16
+    x16 = x.to(bf)
+    zs = []
+    for w_ff, _w_rec, bias in (fw, bw):
+        zs.append(_lin.linear(x16, w_ff.t().to(bf), bias.to(bf) if bias is not None else None))
+    l32 = lens.to(x.device, torch.int32).contiguous() if lens is not None else None
+    yf, yb, hf, cf, hb, cb = _BlstmRecFn.apply(zs[0], zs[1], fw[1], bw[1], l32, h0_fw, c0_fw, h0_bw, c0_bw)
+    return (yf.to(x.dtype), hf, cf), (yb.to(x.dtype), hb, cb)

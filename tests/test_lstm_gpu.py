@@ -41,3 +41,44 @@ def test_lstm_native_matches_reference(reverse, T, B, I, H):
         scale = float(t.grad.abs().max()) + 1e-6
         err = float((g.float() - t.grad).abs().max()) / scale
         assert err < 0.06, "gradient of %s: rel. max err %.4f" % (name, err)
+
+
+@gpu
+@pytest.mark.parametrize("T,B,I,H", [(40, 12, 64, 128), (30, 40, 64, 256), (21, 16, 128, 1024)])
+def test_blstm_one_kernel_for_both_directions_matches_reference(T, B, I, H):
+    """the two-direction persistent kernel: outputs, final states and all gradients of both directions against the fp32 step loop"""
+    from returnn_b200.ops import lstm as L, lstm_native, gemm
+
+    torch.manual_seed(1)
+    dev = "cuda"
+    x = (torch.randn(T, B, I, device=dev) * 0.5).requires_grad_(True)
+
+    def params():
+        return [(torch.randn(4 * H, I, device=dev) * 0.2).requires_grad_(True), (torch.randn(4 * H, H, device=dev) * (0.2 if H < 1024 else 0.05)).requires_grad_(True),
+                (torch.randn(4 * H, device=dev) * 0.1).requires_grad_(True)]
+
+    fw, bw = params(), params()
+    states = [(torch.randn(B, H, device=dev) * 0.3).requires_grad_(True) for _ in range(4)]
+    lens = torch.randint(1, T + 1, (B,))
+    lens[0] = T
+    wts = [torch.randn(T, B, H, device=dev) for _ in range(2)] + [torch.randn(B, H, device=dev) for _ in range(4)]
+    leaves = [x] + fw + bw + states
+    assert lstm_native.blstm_supported(x, fw[1], bw[1])
+    (yf, hf, cf), (yb, hb, cb) = L.blstm(x, lens, tuple(fw), tuple(bw), *states)
+    outs = (yf, yb, hf, cf, hb, cb)
+    sum((o.float() * w).sum() for o, w in zip(outs, wts)).backward()
+    gemm.check_status()
+    got = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    yfr, hfr, cfr = L.lstm_reference(x, lens, *fw, states[0], states[1], reverse=False)
+    ybr, hbr, cbr = L.lstm_reference(x, lens, *bw, states[2], states[3], reverse=True)
+    refs = (yfr, ybr, hfr, cfr, hbr, cbr)
+    sum((o * w).sum() for o, w in zip(refs, wts)).backward()
+    for o, r in zip(outs, refs):
+        torch.testing.assert_close(o.float(), r, atol=0.05, rtol=0.03)
+    names = ["x", "fw.w_ff", "fw.w_rec", "fw.bias", "bw.w_ff", "bw.w_rec", "bw.bias", "h0_fw", "c0_fw", "h0_bw", "c0_bw"]
+    for name, g, t in zip(names, got, leaves):
+        scale = float(t.grad.abs().max()) + 1e-6
+        err = float((g.float() - t.grad).abs().max()) / scale
+        assert err < 0.06, "gradient of %s: rel. max err %.4f" % (name, err)
