@@ -323,6 +323,185 @@ def train_step(*, model, extern_data, **_kwargs):
 '''
 
 
+_REF_MT_CONFIG = r'''#!rnn.py
+import os, sys, time, json
+import numpy, torch
+from returnn.tensor import Tensor, Dim, batch_dim, TensorDict
+import returnn.frontend as rf
+from returnn.frontend.encoder.transformer import TransformerEncoder
+from returnn.frontend.decoder.transformer import TransformerDecoder
+
+_opts = __OPTS__
+sys.path.insert(0, _opts["root"])
+import bench_configs as _bc
+
+backend = "torch"
+task = "train"
+behavior_version = 21
+_W, _K = _opts["warmup"], _opts["steps"]
+_batches = _bc._mt_batches(4321, _W + _K + 1, 25000)
+_tokens = [sum(s["data"].shape[0] + s["classes"].shape[0] for s in b) for b in _batches]
+train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (32000, 1), "classes": (32000, 1)}}
+src_time = Dim(None, name="src-time", kind=Dim.Types.Spatial)
+tgt_time = Dim(None, name="tgt-time", kind=Dim.Types.Spatial)
+vocab_dim = Dim(32000, name="vocab", kind=Dim.Types.Feature)
+extern_data = {
+    "data": {"dims": (batch_dim, src_time), "sparse_dim": vocab_dim, "dtype": "int32"},
+    "classes": {"dims": (batch_dim, tgt_time), "sparse_dim": vocab_dim, "dtype": "int32", "available_for_inference": False},
+}
+batch_size = 25000
+max_seqs = 2000
+batching = "default"
+optimizer = {"class": "adamw", "betas": (0.9, 0.98), "epsilon": 1e-9, "weight_decay": 0.0}
+learning_rate = 1e-4
+torch_amp = "bfloat16"
+num_epochs = 1
+log_verbosity = 3
+torch_dataloader_opts = {"num_workers": 0}
+
+
+class Model(rf.Module):
+    def __init__(self):
+        super().__init__()
+        md = Dim(512, name="model")
+        self.encoder = TransformerEncoder(vocab_dim, md, num_layers=6, num_heads=8, dropout=0.1, att_dropout=0.1)
+        self.decoder = TransformerDecoder(md, vocab_dim, Dim(512, name="dec-model"), num_layers=6, num_heads=8, ff_dim=Dim(2048, name="dec-ff"),
+                                          dropout=0.1, att_dropout=0.1, share_embedding=True)
+
+
+def get_model(**_kwargs):
+    return Model()
+
+
+_state = {"n": 0, "ev0": None}
+
+
+def train_step(*, model, extern_data, **_kwargs):
+    n = _state["n"]
+    if n == _W or n == _W + _K:
+        torch.cuda.synchronize()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        if n == _W:
+            _state["ev0"] = ev
+        else:
+            torch.cuda.synchronize()
+            ms = _state["ev0"].elapsed_time(ev)
+            tokens = sum(_tokens[_W:_W + _K])
+            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train tokens per second (source + target)", "value": tokens / (ms / 1e3),
+                                             "unit": "tokens/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
+                                             "data": "synthetic", "config": {"model": "transformer-base 6+6x512 h8 ff2048 shared vocab 32k (reference rf modules)"}}) + "\n")
+            sys.__stdout__.flush()
+    _state["n"] = n + 1
+    src, tgt = extern_data["data"], extern_data["classes"]
+    enc = model.encoder(src, spatial_dim=src_time)
+    inp, (tgt_ext,) = rf.pad(tgt, axes=[tgt_time], padding=[(1, 0)], value=0)
+    out_t, _ = rf.pad(tgt, axes=[tgt_time], padding=[(0, 1)], value=0, out_dims=[tgt_ext], handle_dynamic_dims=True)
+    enc_state = model.decoder.transform_encoder(enc, axis=src_time)
+    logits, _ = model.decoder(inp, spatial_dim=tgt_ext, encoder=enc_state, state=model.decoder.default_initial_state(batch_dims=[batch_dim]))
+    log_prob = rf.log_softmax(logits, axis=vocab_dim)
+    log_prob = rf.label_smoothed_log_prob_gradient(log_prob, 0.1, axis=vocab_dim)
+    ce = rf.cross_entropy(target=out_t, estimated=log_prob, estimated_type="log-probs", axis=vocab_dim)
+    ce.mark_as_loss("ce", use_normalized_loss=True)
+    err = rf.reduce_argmax(logits, axis=vocab_dim) != out_t
+    err.mark_as_loss("fer", as_error=True)
+'''
+
+
+_REF_AED_CONFIG = r'''#!rnn.py
+import os, sys, time, json
+import numpy, torch
+from returnn.tensor import Tensor, Dim, batch_dim, TensorDict
+import returnn.frontend as rf
+from returnn.frontend.encoder.conformer import ConformerEncoder, ConformerConvSubsample
+from returnn.frontend.decoder.transformer import TransformerDecoder
+
+_opts = __OPTS__
+sys.path.insert(0, _opts["root"])
+import bench_configs as _bc
+
+backend = "torch"
+task = "train"
+behavior_version = 21
+_W, _K = _opts["warmup"], _opts["steps"]
+_batches = _bc._asr_batches(4321, _W + _K + 1, 40000, 300, 2000, 1.0 / 30.0)
+_frames = [sum(s["data"].shape[0] for s in b) for b in _batches]
+train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (80, 2), "classes": (10000, 1)}}
+time_dim = Dim(None, name="time", kind=Dim.Types.Spatial)
+feat_dim = Dim(80, name="feature", kind=Dim.Types.Feature)
+targets_time = Dim(None, name="targets-time", kind=Dim.Types.Spatial)
+vocab_dim = Dim(10000, name="vocab", kind=Dim.Types.Feature)
+extern_data = {
+    "data": {"dims": (batch_dim, time_dim, feat_dim), "dtype": "float32"},
+    "classes": {"dims": (batch_dim, targets_time), "sparse_dim": vocab_dim, "dtype": "int32", "available_for_inference": False},
+}
+batch_size = 40000
+max_seqs = 2000
+batching = "default"
+optimizer = {"class": "adamw", "weight_decay": 0.01}
+learning_rate = 1e-4
+gradient_clip_global_norm = 5.0
+torch_amp = "bfloat16"
+num_epochs = 1
+log_verbosity = 3
+torch_dataloader_opts = {"num_workers": 0}
+
+
+class Model(rf.Module):
+    def __init__(self):
+        super().__init__()
+        self.model_dim = Dim(512, name="enc-model")
+        self.encoder = ConformerEncoder(
+            feat_dim, self.model_dim, num_layers=12, num_heads=8, ff_dim=Dim(2048, name="enc-ff"), conv_kernel_size=32, dropout=0.1, att_dropout=0.1,
+            input_layer=ConformerConvSubsample(feat_dim, out_dims=[Dim(32, name="conv1"), Dim(64, name="conv2"), Dim(64, name="conv3")],
+                                               filter_sizes=[(3, 3), (3, 3), (3, 3)], pool_sizes=[(1, 2)], strides=[(1, 1), (3, 1), (2, 1)]))
+        self.decoder = TransformerDecoder(encoder_dim=self.model_dim, vocab_dim=vocab_dim, model_dim=Dim(512, name="dec-model"), num_layers=6,
+                                          num_heads=8, ff_dim=Dim(2048, name="dec-ff"), dropout=0.1, att_dropout=0.1)
+        self.wb_vocab_dim = vocab_dim + 1
+        self.aux_ctc = rf.Linear(self.model_dim, self.wb_vocab_dim)
+
+
+def get_model(**_kwargs):
+    return Model()
+
+
+_state = {"n": 0, "ev0": None}
+
+
+def train_step(*, model, extern_data, **_kwargs):
+    n = _state["n"]
+    if n == _W or n == _W + _K:
+        torch.cuda.synchronize()
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        if n == _W:
+            _state["ev0"] = ev
+        else:
+            torch.cuda.synchronize()
+            ms = _state["ev0"].elapsed_time(ev)
+            frames = sum(_frames[_W:_W + _K])
+            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train seconds-of-audio per second", "value": frames * 0.01 / (ms / 1e3),
+                                             "unit": "audio-s/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
+                                             "data": "synthetic", "config": {"model": "conformer-aed 12x512 + 6-layer decoder, CE(ls 0.1) + 0.3 CTC (reference rf modules)"}}) + "\n")
+            sys.__stdout__.flush()
+    _state["n"] = n + 1
+    data, targets = extern_data["data"], extern_data["classes"]
+    enc, enc_spatial = model.encoder(data, in_spatial_dim=time_dim)
+    ctc = rf.ctc_loss(logits=model.aux_ctc(enc), targets=targets, input_spatial_dim=enc_spatial, targets_spatial_dim=targets_time, blank_index=10000)
+    ctc.mark_as_loss("ctc", scale=0.3, custom_inv_norm_factor=targets_time.get_size_tensor(), use_normalized_loss=False)
+    inp, (tgt_ext,) = rf.pad(targets, axes=[targets_time], padding=[(1, 0)], value=0)
+    out_t, _ = rf.pad(targets, axes=[targets_time], padding=[(0, 1)], value=0, out_dims=[tgt_ext], handle_dynamic_dims=True)
+    enc_state = model.decoder.transform_encoder(enc, axis=enc_spatial)
+    logits, _ = model.decoder(inp, spatial_dim=tgt_ext, encoder=enc_state, state=model.decoder.default_initial_state(batch_dims=[batch_dim]))
+    log_prob = rf.log_softmax(logits, axis=vocab_dim)
+    log_prob = rf.label_smoothed_log_prob_gradient(log_prob, 0.1, axis=vocab_dim)
+    ce = rf.cross_entropy(target=out_t, estimated=log_prob, estimated_type="log-probs", axis=vocab_dim)
+    ce.mark_as_loss("ce", use_normalized_loss=True)
+    err = rf.reduce_argmax(logits, axis=vocab_dim) != out_t
+    err.mark_as_loss("fer", as_error=True)
+'''
+
+
 _REF_BLSTM_CONFIG = r'''#!rnn.py
 import os, sys, time, json
 import numpy, torch
@@ -426,8 +605,8 @@ def train_step(*, model, extern_data, **_kwargs):
 '''
 
 
-def run_blstm_reference(args):
-    """BLSTM-CTC through the unmodified reference on one GPU (its LSTM is torch.lstm, i.e. cuDNN)"""
+def run_blstm_reference(args, config_text: str = None, tag: str = "blstm"):
+    """BLSTM-CTC (or ``config_text``) through the unmodified reference on one GPU (its LSTM is torch.lstm, i.e. cuDNN)"""
     import tempfile
 
     ref_dir = os.path.join(_ROOT, "baseline", "_ref")
@@ -435,10 +614,10 @@ def run_blstm_reference(args):
         print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/returnn not installed"}))
         return
     opts = {"root": _ROOT, "warmup": args.warmup, "steps": args.steps}
-    tmpdir = tempfile.mkdtemp(prefix="bench_ref_blstm_")
-    cfg_path = os.path.join(tmpdir, "blstm.ref.config")
+    tmpdir = tempfile.mkdtemp(prefix="bench_ref_%s_" % tag)
+    cfg_path = os.path.join(tmpdir, "%s.ref.config" % tag)
     with open(cfg_path, "w") as f:
-        f.write(_REF_BLSTM_CONFIG.replace("__OPTS__", repr(opts)))
+        f.write((config_text or _REF_BLSTM_CONFIG).replace("__OPTS__", repr(opts)))
     sys.path.insert(0, ref_dir)
     try:
         import tree  # noqa: F401
@@ -501,12 +680,15 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: for --config 12ax and blstm_ctc")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: every --config here has a reference arm")
     args = ap.parse_args()
     if args.impl == "reference":
-        assert args.config in ("12ax", "blstm_ctc"), "reference arms: 12ax, blstm_ctc here; Conformer-CTC in bench.py --impl reference"
         if args.config == "12ax":
             run_12ax_reference(args)
+        elif args.config == "transformer_mt":
+            run_blstm_reference(args, config_text=_REF_MT_CONFIG, tag="mt")
+        elif args.config == "conformer_aed":
+            run_blstm_reference(args, config_text=_REF_AED_CONFIG, tag="aed")
         else:
             run_blstm_reference(args)
     elif args.config == "12ax":
