@@ -26,7 +26,7 @@ typedef __nv_bfloat16 bf16;
 constexpr int kUnits = 8;      // hidden units per CTA (H = 1024 -> 128 CTAs)
 constexpr int kMaxRows = 48;   // batch rows (three m16 tiles)
 constexpr int kThreads = 256;  // eight warps: each takes one eighth of the contraction
-constexpr int kPad = 8;        // row padding of the resident slice (bank-conflict-free fragment loads)
+constexpr int kPad = 32;       // row padding of the resident slice: pitch = 64 bytes mod 128 (conflict-free 16-byte fragment loads)
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -69,12 +69,18 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // red[row][n] += sum_k A[row][k] * Bs[n][k] for rows < n_rows; A in global (written by other CTAs: read through L2), Bs resident
-// in shared memory with row pitch K + kPad. The warp w takes k in [w*K/8, (w+1)*K/8).
+// in shared memory with row pitch K + kPad. The contraction is cut into blocks of 32 k; the warp w takes the blocks
+// [w*nblk/8, (w+1)*nblk/8).
+//
+// Operand fetch: all CTAs read the same small A matrix at the same time, so the number of L2 requests, not the bytes, sets the
+// step time. A lane therefore fetches 16 contiguous bytes (8 k) per row and block instead of four 4-byte fragment words: the
+// order of the k inside a block is free as long as A and B agree, so the lane t of a quad owns k [8t, 8t+8) of the block, its
+// words 0/1 feed the first m16n8k16 (as the fragment halves "k 2t.." and "k 2t+8..") and its words 2/3 the second one. The B
+// fragments come from shared memory with the same 16-byte pattern (row pitch = 64 bytes mod 128: conflict-free quarter warps).
 template <int NOUT, int kPrefetch>
 __device__ __forceinline__ void step_matmul(const bf16* __restrict__ A, int n_rows, int K, const bf16* __restrict__ Bs, float* __restrict__ red) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int kw = K / 8;
   const int pitch = K + kPad;
   float acc[3][NOUT / 8][4];
 #pragma unroll
@@ -84,38 +90,39 @@ __device__ __forceinline__ void step_matmul(const bf16* __restrict__ A, int n_ro
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[m][n][e] = 0.f;
   const int m_tiles = (n_rows + 15) / 16;
-  auto load_a = [&](int k0, uint32_t (&a)[3][4]) {
+  auto load_a = [&](int k0, uint4 (&a)[3][2]) {
 #pragma unroll
     for (int m = 0; m < 3; ++m) {
       const int r0 = m * 16 + g, r1 = r0 + 8;
-      const uint32_t* p0 = reinterpret_cast<const uint32_t*>(A + (size_t)r0 * K + k0 + 2 * t);
-      const uint32_t* p1 = reinterpret_cast<const uint32_t*>(A + (size_t)r1 * K + k0 + 2 * t);
-      a[m][0] = r0 < n_rows ? __ldcg(p0) : 0u;
-      a[m][1] = r1 < n_rows ? __ldcg(p1) : 0u;
-      a[m][2] = r0 < n_rows ? __ldcg(p0 + 4) : 0u;
-      a[m][3] = r1 < n_rows ? __ldcg(p1 + 4) : 0u;
+      a[m][0] = r0 < n_rows ? __ldcg(reinterpret_cast<const uint4*>(A + (size_t)r0 * K + k0 + 8 * t)) : make_uint4(0u, 0u, 0u, 0u);
+      a[m][1] = r1 < n_rows ? __ldcg(reinterpret_cast<const uint4*>(A + (size_t)r1 * K + k0 + 8 * t)) : make_uint4(0u, 0u, 0u, 0u);
     }
   };
-  // chunks of kPrefetch k-steps: all fragment loads of a chunk are issued before its first multiply, so a chunk costs one
-  // L2 round trip (with kPrefetch = 8 the forward contraction of H = 1024 is a single chunk per warp; the two-direction kernels
-  // use 4 to stay within 128 registers, so that two CTAs share an SM and cover each other's round trips)
-  const int k_begin = warp * kw, k_end = (warp + 1) * kw;
-  for (int kc = k_begin; kc < k_end; kc += 16 * kPrefetch) {
-    uint32_t a[kPrefetch][3][4];
+  // chunks of kPrefetch blocks: all operand loads of a chunk are issued before its first multiply, so a chunk costs one L2 round
+  // trip (kPrefetch = 4: the forward contraction of H = 1024 is a single chunk per warp; the two-direction kernels use 2 to stay
+  // within 128 registers, so that two CTAs share an SM and cover each other's round trips)
+  const int nblk = K >> 5;
+  const int b_begin = warp * nblk / 8, b_end = (warp + 1) * nblk / 8;
+  for (int bc = b_begin; bc < b_end; bc += kPrefetch) {
+    uint4 a[kPrefetch][3][2];
 #pragma unroll
     for (int i = 0; i < kPrefetch; ++i)
-      if (kc + 16 * i < k_end) load_a(kc + 16 * i, a[i]);
+      if (bc + i < b_end) load_a((bc + i) << 5, a[i]);
 #pragma unroll
     for (int i = 0; i < kPrefetch; ++i) {
-      const int k0 = kc + 16 * i;
-      if (k0 >= k_end) break;
+      if (bc + i >= b_end) break;
+      const int k0 = (bc + i) << 5;
 #pragma unroll
       for (int n = 0; n < NOUT / 8; ++n) {
-        const uint32_t* bp = reinterpret_cast<const uint32_t*>(Bs + (size_t)(n * 8 + g) * pitch + k0 + 2 * t);
-        const uint32_t b0 = bp[0], b1 = bp[4];
+        const uint4 b = *reinterpret_cast<const uint4*>(Bs + (size_t)(n * 8 + g) * pitch + k0 + 8 * t);
 #pragma unroll
-        for (int m = 0; m < 3; ++m)
-          if (m < m_tiles) mma16816(acc[m][n], a[i][m], b0, b1);
+        for (int m = 0; m < 3; ++m) {
+          if (m >= m_tiles) continue;
+          const uint32_t f0[4] = {a[i][m][0].x, a[i][m][1].x, a[i][m][0].y, a[i][m][1].y};
+          mma16816(acc[m][n], f0, b.x, b.y);
+          const uint32_t f1[4] = {a[i][m][0].z, a[i][m][1].z, a[i][m][0].w, a[i][m][1].w};
+          mma16816(acc[m][n], f1, b.z, b.w);
+        }
       }
     }
   }
@@ -156,7 +163,7 @@ __device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.H, B = p.B;
   const int pitch = H + kPad;
-  bf16* Ws = reinterpret_cast<bf16*>(smem_raw);                                 // [4*kUnits][H+8]: row q*kUnits+u = W_rec[q*H + j0 + u]
+  bf16* Ws = reinterpret_cast<bf16*>(smem_raw);                                 // [4*kUnits][H+kPad]: row q*kUnits+u = W_rec[q*H + j0 + u]
   float* red = reinterpret_cast<float*>(Ws + (size_t)4 * kUnits * pitch);       // [48][4*kUnits]
   float* cst = red + kMaxRows * 4 * kUnits;                                     // [48][kUnits] cell state
   float* hst = cst + kMaxRows * kUnits;                                         // [48][kUnits] own slice of h (fp32)
@@ -249,7 +256,7 @@ __device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const 
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p) { fwd_body<8>(p, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(kThreads, 1) lstm_persist_fwd_kernel(FwdArgs p) { fwd_body<4>(p, blockIdx.x, gridDim.x); }
 
 // Both directions of a bidirectional layer in one launch: the first half of the grid runs d[0], the second half d[1], each with
 // its own barrier words. Two CTAs share an SM (128 registers per thread), so the two recurrences, each bound by the latency of
@@ -260,8 +267,8 @@ struct FwdPair {
 
 __global__ void __launch_bounds__(kThreads, 2) lstm_persist_fwd_pair_kernel(const __grid_constant__ FwdPair pp) {
   const int half = gridDim.x / 2;
-  if ((int)blockIdx.x < half) fwd_body<4>(pp.d[0], blockIdx.x, half);
-  else fwd_body<4>(pp.d[1], blockIdx.x - half, half);
+  if ((int)blockIdx.x < half) fwd_body<2>(pp.d[0], blockIdx.x, half);
+  else fwd_body<2>(pp.d[1], blockIdx.x - half, half);
 }
 
 struct BwdArgs {
@@ -284,7 +291,7 @@ __device__ __forceinline__ void bwd_body(const BwdArgs& p, const int cta, const 
   extern __shared__ __align__(16) unsigned char smem_raw[];
   const int H = p.H, B = p.B, K = 4 * p.H;
   const int pitch = K + kPad;
-  bf16* Wt = reinterpret_cast<bf16*>(smem_raw);                      // [kUnits][4H+8]: Wt[u][n] = W_rec[n][j0+u]
+  bf16* Wt = reinterpret_cast<bf16*>(smem_raw);                      // [kUnits][4H+kPad]: Wt[u][n] = W_rec[n][j0+u]
   float* red = reinterpret_cast<float*>(Wt + (size_t)kUnits * pitch);  // [48][16]
   float* dhs = red + kMaxRows * kUnits;                              // [48][16] gradient arriving at h_t
   float* dcs = dhs + kMaxRows * kUnits;                              // [48][16] gradient arriving at c_t
@@ -346,7 +353,7 @@ __device__ __forceinline__ void bwd_body(const BwdArgs& p, const int cta, const 
   }
 }
 
-__global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p) { bwd_body<8>(p, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(kThreads, 1) lstm_persist_bwd_kernel(BwdArgs p) { bwd_body<4>(p, blockIdx.x, gridDim.x); }
 
 struct BwdPair {
   BwdArgs d[2];
@@ -354,8 +361,8 @@ struct BwdPair {
 
 __global__ void __launch_bounds__(kThreads, 2) lstm_persist_bwd_pair_kernel(const __grid_constant__ BwdPair pp) {
   const int half = gridDim.x / 2;
-  if ((int)blockIdx.x < half) bwd_body<4>(pp.d[0], blockIdx.x, half);
-  else bwd_body<4>(pp.d[1], blockIdx.x - half, half);
+  if ((int)blockIdx.x < half) bwd_body<2>(pp.d[0], blockIdx.x, half);
+  else bwd_body<2>(pp.d[1], blockIdx.x - half, half);
 }
 
 // barrier words of the calls in flight: 64 slots of (counter, abort word), handed out round robin
