@@ -122,7 +122,9 @@ def convert_to_tensor(value, *, dims: Sequence[Dim] = (), dtype: Optional[str] =
         if dtype is not None and _TORCH_DTYPE_NAMES[raw.dtype] != dtype:
             raw = raw.to(torch_dtype(dtype))
         if device is not None and str(raw.device) != str(device):
-            raw = raw.to(device)
+            from ..tensor.utils import host_to_device
+
+            raw = host_to_device(raw, device)
     else:
         if dtype is None:
             if isinstance(value, bool):

@@ -146,7 +146,9 @@ def ctc_loss(*, logits: Tensor, logits_normalized: bool = False, targets: Tensor
         from ..ops import ctc as _ctc
 
         if _ctc.available() and _ctc.supports(lraw, traw):
-            loss = _ctc.ctc_loss(lraw, traw, in_lens.to(lraw.device), tgt_lens.to(lraw.device), blank_index=blank_index,
+            from ..tensor.utils import host_to_device
+
+            loss = _ctc.ctc_loss(lraw, traw, host_to_device(in_lens, lraw.device), host_to_device(tgt_lens, lraw.device), blank_index=blank_index,
                                  logits_normalized=logits_normalized)
             return wrap(loss, [bd])
     log_probs = lraw.float() if logits_normalized else F.log_softmax(lraw.float(), dim=-1)

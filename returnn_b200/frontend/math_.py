@@ -14,6 +14,7 @@ import torch
 from . import _numpy_backend as _np
 import torch.nn.functional as F
 from ..tensor import Tensor, Dim
+from ..tensor.utils import host_to_device
 from ._utils import wrap, merge_dims_for_broadcast, convert_to_tensor, torch_dtype, dtype_name
 from ..utils.basic import NotSpecified
 
@@ -106,9 +107,9 @@ def compare(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
         raise ValueError("compare: invalid kind %r" % kind)
     if ra.device != rb.device:
         if not rb.ndim:
-            rb = rb.to(ra.device)
+            rb = host_to_device(rb, ra.device)
         elif not ra.ndim:
-            ra = ra.to(rb.device)
+            ra = host_to_device(ra, rb.device)
     return wrap(fn(ra, rb), out_dims, name="compare")
 
 
@@ -125,9 +126,9 @@ def combine(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
         raise ValueError("combine: invalid kind %r" % kind)
     if ra.device != rb.device:
         if not rb.ndim:
-            rb = rb.to(ra.device)
+            rb = host_to_device(rb, ra.device)
         elif not ra.ndim:
-            ra = ra.to(rb.device)
+            ra = host_to_device(ra, rb.device)
     res = fn(ra, rb)
     src = a if a._dims == out_dims or not b._dims else b
     return wrap(res, out_dims, name="combine", like=src)

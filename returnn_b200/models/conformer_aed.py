@@ -49,6 +49,27 @@ class ConformerAedModel(rf.Module):
         self.label_smoothing, self.aux_ctc_scale = label_smoothing, aux_ctc_scale
         self.beam_size, self.max_len_factor, self.bos, self.eos = beam_size, max_len_factor, bos, eos
 
+    def aux_logits(self, enc: Tensor) -> Tensor:
+        """
+        logits of the auxiliary CTC output. The width (vocabulary + blank) is odd: in training on the GPU the layer is computed
+        8-aligned on the tcgen05 GEMM with extra classes of probability 0 (the CTC loss takes the number of classes from the
+        logits it gets); elsewhere the plain linear layer.
+        """
+        raw = enc.raw_tensor
+        w = self.aux_ctc.weight.raw_tensor
+        if raw.is_cuda and w.shape[1] % 8 and torch.is_grad_enabled() and raw.requires_grad:
+            from ..ops import gemm as _gemm
+            from ..parallel import arena as _arena
+
+            ar = _arena.find_arena(w)
+            if ar is not None and enc.dims[-1] == self.model_dim:
+                out = _gemm.linear_arena_padded_out(raw.reshape(-1, raw.shape[-1]), w, self.aux_ctc.bias.raw_tensor, ar)
+                if out is not None:
+                    pad_dim = Dim(int(out.shape[-1]), name="vocab+blank:padded")
+                    return Tensor("aux_logits", dims=list(enc.dims[:-1]) + [pad_dim], dtype=str(out.dtype).split(".")[-1],
+                                  raw_tensor=out.reshape(*raw.shape[:-1], out.shape[-1]), feature_dim=pad_dim)
+        return self.aux_ctc(enc)
+
     def encode(self, source: Tensor, *, in_spatial_dim: Dim) -> Tuple[Tensor, Dim]:
         """encoder output [B, T', D]; on B200 in training the packed native path, unpacked again for the decoder"""
         raw = source.raw_tensor
@@ -86,7 +107,7 @@ def train_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
     tgt_spatial = targets.dims[1]
     enc, enc_spatial = model.encode(data, in_spatial_dim=data.dims[1])
     if model.aux_ctc is not None:
-        ctc = rf.ctc_loss(logits=model.aux_ctc(enc), targets=targets, input_spatial_dim=enc_spatial, targets_spatial_dim=tgt_spatial,
+        ctc = rf.ctc_loss(logits=model.aux_logits(enc), targets=targets, input_spatial_dim=enc_spatial, targets_spatial_dim=tgt_spatial,
                           blank_index=model.blank_idx)
         ctc.mark_as_loss("ctc", scale=model.aux_ctc_scale, custom_inv_norm_factor=tgt_spatial.get_size_tensor(), use_normalized_loss=False)
     # teacher forcing: decoder input = BOS + targets[:-1], target = targets + EOS

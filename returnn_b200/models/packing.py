@@ -8,14 +8,7 @@ from typing import List, Optional, Tuple
 import torch
 
 
-def host_to_device(t: torch.Tensor, device) -> torch.Tensor:
-    """copy of a host tensor on ``device``; through pinned memory and asynchronous on CUDA (no stream synchronisation)"""
-    device = torch.device(device)
-    if device.type == "cuda" and not t.is_cuda:
-        if not t.is_pinned():
-            t = t.pin_memory()
-        return t.to(device, non_blocking=True)
-    return t.to(device)
+from ..tensor.utils import host_to_device  # noqa: F401  (re-exported: used by the fused model paths)
 
 
 class PackInfo:

@@ -11,6 +11,7 @@ from typing import Optional
 import torch
 from . import _lib
 from . import gemm as _gemm
+from ..tensor.utils import host_to_device
 
 _vp, _i32 = ctypes.c_void_p, ctypes.c_int
 
@@ -91,7 +92,7 @@ def lstm(x, lens: Optional[torch.Tensor], w_ff, w_rec, bias, h0, c0, reverse: bo
 
     T, B, _ = x.shape
     z_in = _lin.linear(x.to(torch.bfloat16), w_ff.t().to(torch.bfloat16), bias.to(torch.bfloat16) if bias is not None else None)
-    l32 = lens.to(x.device, torch.int32).contiguous() if lens is not None else None
+    l32 = host_to_device(lens.to(torch.int32), x.device).contiguous() if lens is not None else None
     y, h, c = _LstmRecFn.apply(z_in, w_rec, l32, h0, c0, bool(reverse))
     return y.to(x.dtype), h, c
 
@@ -193,6 +194,6 @@ def blstm(x, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h0_bw, c0_bw):
     zs = []
     for w_ff, _w_rec, bias in (fw, bw):
         zs.append(_lin.linear(x16, w_ff.t().to(bf), bias.to(bf) if bias is not None else None))
-    l32 = lens.to(x.device, torch.int32).contiguous() if lens is not None else None
+    l32 = host_to_device(lens.to(torch.int32), x.device).contiguous() if lens is not None else None
     yf, yb, hf, cf, hb, cb = _BlstmRecFn.apply(zs[0], zs[1], fw[1], bw[1], l32, h0_fw, c0_fw, h0_bw, c0_bw)
     return (yf.to(x.dtype), hf, cf), (yb.to(x.dtype), hb, cb)

@@ -20,6 +20,7 @@ from . import _lib
 from . import gemm as _gemm
 from .attention_native import _bgemm
 from .elementwise import _seed_tensor
+from ..tensor.utils import host_to_device
 
 _vp, _i32, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 
@@ -139,7 +140,7 @@ def sdpa(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, *, num_heads: int, k
     if scale is None:
         scale = 1.0 / math.sqrt(d)
     if k_lens is not None:
-        k_lens = k_lens.to(device=q.device, dtype=torch.int32).contiguous()
+        k_lens = host_to_device(k_lens.to(torch.int32), q.device).contiguous()
     return _SdpaFn.apply(q, k, v, k_lens, int(num_heads), bool(causal), float(scale), float(dropout_p))
 
 

@@ -436,7 +436,9 @@ class Dim:
         key = str(device)
         base = self.get_same_base()
         if key not in base._size_tensor_cache:
-            base._size_tensor_cache[key] = ext.copy_with_raw(ext.raw_tensor.to(device))
+            from .utils import host_to_device
+
+            base._size_tensor_cache[key] = ext.copy_with_raw(host_to_device(ext.raw_tensor, device))
         return base._size_tensor_cache[key]
 
     def get_dyn_size_ext_for_device(self, device=None) -> "Tensor":
@@ -462,7 +464,9 @@ class Dim:
             sizes = torch.as_tensor(numpy.asarray(sizes))
         max_len = self.get_dim_value()
         if device is not None:
-            sizes = sizes.to(device)
+            from .utils import host_to_device
+
+            sizes = host_to_device(sizes, device)
         rng = torch.arange(max_len, device=sizes.device, dtype=sizes.dtype)
         mask_raw = rng.reshape([1] * sizes.ndim + [max_len]) < sizes.unsqueeze(-1)
         mask = Tensor("%s:mask" % (self.name or "dim"), dims=list(ext.dims) + [self], dtype="bool", raw_tensor=mask_raw)

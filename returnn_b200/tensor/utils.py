@@ -68,3 +68,19 @@ def tensor_fill_random_numpy_(x: Tensor, *, min_val: int = 0, max_val: Optional[
         t = t.to(torch.bfloat16)
     x.raw_tensor = t
     return True
+
+
+def host_to_device(t, device):
+    """
+    Copy of a host tensor on ``device``. On CUDA it goes through pinned memory and is asynchronous: a plain ``t.to("cuda")`` of a
+    pageable tensor synchronises the stream, which drains the queue of kernels the host has issued ahead of the device
+    (sequence lengths are moved like this several times per step).
+    """
+    import torch
+
+    device = torch.device(device)
+    if device.type == "cuda" and not t.is_cuda:
+        if not t.is_pinned():
+            t = t.pin_memory()
+        return t.to(device, non_blocking=True)
+    return t.to(device)
