@@ -146,9 +146,8 @@ def ctc_loss(*, logits: Tensor, logits_normalized: bool = False, targets: Tensor
         from ..ops import ctc as _ctc
 
         if _ctc.available() and _ctc.supports(lraw, traw):
-            from ..tensor.utils import host_to_device
-
-            loss = _ctc.ctc_loss(lraw, traw, host_to_device(in_lens, lraw.device), host_to_device(tgt_lens, lraw.device), blank_index=blank_index,
+            # the kernel wrapper packs the valid frames and needs the lengths on the host: hand them over as they are
+            loss = _ctc.ctc_loss(lraw, traw, in_lens, tgt_lens, blank_index=blank_index,
                                  logits_normalized=logits_normalized)
             return wrap(loss, [bd])
     log_probs = lraw.float() if logits_normalized else F.log_softmax(lraw.float(), dim=-1)

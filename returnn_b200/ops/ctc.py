@@ -90,6 +90,8 @@ def ctc_loss(logits: torch.Tensor, targets: torch.Tensor, in_lens: torch.Tensor,
     """padded variant: packs the valid frames and calls the packed kernel"""
     from ..models.packing import PackInfo
 
+    # lengths are wanted on the host (layout of the packed rows): pass host tensors where they exist, a device tensor costs a
+    # synchronising read here
     pack = PackInfo(in_lens.cpu(), logits.device, padded_len=logits.shape[1])
     rows = pack.pack(logits)
     return ctc_loss_packed(rows, pack, targets, tgt_lens.cpu(), blank_index=blank_index)

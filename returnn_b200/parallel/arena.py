@@ -170,13 +170,22 @@ class ParamArena:
         """make sure every ``param.grad`` is the arena view (autograd may have replaced it when it was None)"""
         if self.grad_dtype != self.dtype:
             return
-        for s in self.slots:
+        base = self.flat_grad.data_ptr()
+        views = getattr(self, "_grad_views", None)
+        if views is None or self._grad_views_base != base:
+            # one view object per parameter, kept: the common case below is then an identity check per parameter
+            views = [self.flat_grad[s.offset: s.offset + s.numel].view(s.shape) for s in self.slots]
+            self._grad_views, self._grad_views_base = views, base
+        for s, view in zip(self.slots, views):
             g = s.param.grad
-            view = self.flat_grad[s.offset: s.offset + s.numel].view(s.shape)
+            if g is view:
+                continue
             if g is None:
                 s.param.grad = view
             elif g.data_ptr() != view.data_ptr():
                 view.copy_(g)
+                s.param.grad = view
+            else:
                 s.param.grad = view
 
     def bucket_grad(self, b: int) -> torch.Tensor:

@@ -163,13 +163,16 @@ class Updater:
         """
         if grad_scaler is not None:
             grad_scaler.unscale_(self.optimizer)
-        params = [p for p in self.network.parameters() if p.grad is not None]
+        fused_opt = getattr(self.optimizer, "is_fused_arena", False)
+        if fused_opt and not self._grad_noise and not self._grad_clip:
+            params = None  # the arena optimizer works on the flat buffers: no per-parameter list needed in the step
+        else:
+            params = [p for p in self.network.parameters() if p.grad is not None]
         if self._grad_noise:
             gradient_noise_(params, self._grad_noise, generator=self._get_noise_generator())
         if self._grad_clip:
             torch.nn.utils.clip_grad_value_(params, self._grad_clip)
         grad_norm = None
-        fused_opt = getattr(self.optimizer, "is_fused_arena", False)
         need_norm = self._grad_clip_global_norm or self._log_grad_norm or self._num_allowed_consec_invalid_gradient_steps is not None
         if need_norm:
             if self._precomputed_grad_norm_sq is not None:
