@@ -66,7 +66,12 @@ class DistributedContext:
         self._custom_class_opts = self._opts.get("options", None)
         self._fused_opt = self._opts.get("fused", None)
         self._bucket_cap_mb = self._opts.get("bucket_cap_mb", 32)
+        peer_watch_opts = self._opts.get("peer_watch", None)
         self._opts.assert_all_read()
+        from ..parallel import peer_watch as _peer_watch
+
+        # host-side liveness of the peers (heartbeats in the process group's store), checked before every step
+        self.peer_watch = _peer_watch.create_from_process_group(peer_watch_opts, rank=self._rank, world=self._size)
         self._reducer = None
         self._arena = None
         self._fused = None
@@ -74,6 +79,21 @@ class DistributedContext:
         self._step_after_param_update_module = None
         print("Torch distributed initialized. Hostname %s, pid %i, rank %i / size %i, local rank %s / local size %s, reduce_type %s." % (
             socket.gethostname(), os.getpid(), self._rank, self._size, self._local_rank, self._local_size, self._reduce_type), file=log.v3)
+
+    def check_peers(self, step: Optional[int] = None):
+        """raises ``parallel.peer_watch.PeerFailure`` when a peer left or went silent; call before issuing a step"""
+        if self.peer_watch is not None:
+            self.peer_watch.check(step)
+
+    def leave_job(self, reason: str = "left"):
+        """
+        this rank leaves on purpose: only between steps. Waits for the device (nothing of this rank may be in flight), then
+        tells the peers through the store.
+        """
+        if torch.cuda.is_available() and torch.cuda.is_initialized():
+            torch.cuda.synchronize()
+        if self.peer_watch is not None:
+            self.peer_watch.leave(reason)
 
     def local_rank(self) -> int:
         """rank on this node"""

@@ -345,6 +345,8 @@ class Engine(EngineBase):
                     extern_data_raw = next(data_iter, None)
                 step_begin_time = time.monotonic()
                 _has_data = torch.tensor([extern_data_raw is not None], dtype=torch.int8)
+                if dist:
+                    dist.check_peers(self.global_train_step)  # before any collective of this step
                 if dist and (step_idx == 0 or extern_data_raw is None or dist.should_sync_now(epoch_step_idx=step_idx) or dist.reduce_type != "param"):
                     torch.distributed.all_reduce(_has_data, op=torch.distributed.ReduceOp.MIN)
                 if not _has_data[0]:
@@ -535,6 +537,8 @@ class Engine(EngineBase):
         :return: loss name -> float (``read_losses``) or device scalar tensor
         """
         dist = self._torch_distributed_ctx
+        if dist:
+            dist.check_peers(self.global_train_step)
         staged_ev = extern_data_raw.get("_staged_event")
         if staged_ev is not None:
             cur = torch.cuda.current_stream()

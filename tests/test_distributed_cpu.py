@@ -155,3 +155,94 @@ except Exception as exc:
     rc0, out0 = outs[0]
     assert "DETECTED" in out0 and "NO ERROR" not in out0, out0
     assert outs[1][0] == 3
+
+
+def test_peer_watch_states_with_fake_store_and_clock():
+    """alive -> stale -> PeerFailure; a rank that leaves on purpose is reported at once"""
+    from returnn_b200.parallel.peer_watch import PeerWatch, PeerFailure
+
+    class Store(dict):
+        def set(self, k, v):
+            self[k] = v.encode()
+
+        def get(self, k):
+            return self[k]
+
+        def check(self, keys):
+            return all(k in self for k in keys)
+
+    now = [100.0]
+    store = Store()
+    w0 = PeerWatch(store, rank=0, world=2, max_age_sec=5.0, clock=lambda: now[0], start_thread=False)
+    assert w0.failed_ranks() == {1: "no heartbeat entry"}
+    w1 = PeerWatch(store, rank=1, world=2, max_age_sec=5.0, clock=lambda: now[0], start_thread=False)
+    w0.check(step=1)
+    now[0] += 3.0
+    w1.beat(step=7)
+    now[0] += 4.0
+    w0.check(step=2)  # 4 s old: fine
+    assert w0.status()[1]["step"] == 7
+    now[0] += 2.0
+    with pytest.raises(PeerFailure) as exc:
+        w0.check(step=3)
+    assert exc.value.ranks == [1] and "step 7" in exc.value.reasons[1]
+    w1.beat()
+    w0.check()
+    w1.leave("node drained")
+    with pytest.raises(PeerFailure) as exc:
+        w0.check()
+    assert "node drained" in exc.value.reasons[1]
+
+
+def test_peer_that_leaves_is_detected_on_the_host_before_the_next_collective(tmp_path):
+    """rank 1 leaves between two steps; rank 0 learns of it from the store and never enters the collective (no timeout wait)"""
+    outs = _launch(_COMMON + """
+import time
+rank = int(os.environ["RANK"])
+ctx = make_ctx({"reduce_type": "grad", "timeout_sec": 600, "peer_watch": {"interval_sec": 0.1, "max_age_sec": 3.0}})
+from returnn_b200.parallel.peer_watch import PeerFailure
+t = torch.ones(4)
+ctx.check_peers(0)
+dist.all_reduce(t)
+if rank == 1:
+    ctx.leave_job("test: leaving between steps")
+    print("rank 1 left")
+    os._exit(0)
+t0 = time.time()
+try:
+    for step in range(1, 200):
+        ctx.check_peers(step)      # what the engine does before every step
+        time.sleep(0.05)
+    print("NOT DETECTED")
+except PeerFailure as exc:
+    print("DETECTED_ON_HOST ranks=%s after %.1f s: %s" % (exc.ranks, time.time() - t0, exc))
+os._exit(0)
+""", tmp_path, expect_ok=False, timeout=120)
+    rc0, out0 = outs[0]
+    assert "DETECTED_ON_HOST ranks=[1]" in out0 and "leaving between steps" in out0, out0
+    assert outs[1][0] == 0 and "rank 1 left" in outs[1][1]
+
+
+def test_peer_that_dies_silently_is_detected_by_stale_heartbeat(tmp_path):
+    """rank 1 exits without a word (its heartbeat thread dies with it): rank 0 sees the heartbeat age out"""
+    outs = _launch(_COMMON + """
+import time
+rank = int(os.environ["RANK"])
+ctx = make_ctx({"reduce_type": "grad", "timeout_sec": 600, "peer_watch": {"interval_sec": 0.1, "max_age_sec": 1.5}})
+from returnn_b200.parallel.peer_watch import PeerFailure
+t = torch.ones(4)
+dist.all_reduce(t)
+if rank == 1:
+    os._exit(7)
+try:
+    for step in range(1, 400):
+        ctx.check_peers(step)
+        time.sleep(0.05)
+    print("NOT DETECTED")
+except PeerFailure as exc:
+    print("DETECTED_ON_HOST", exc)
+os._exit(0)
+""", tmp_path, expect_ok=False, timeout=120)
+    rc0, out0 = outs[0]
+    assert "DETECTED_ON_HOST" in out0 and "last heartbeat" in out0, out0
+    assert outs[1][0] == 7
