@@ -119,7 +119,7 @@ def run_gpu(args):
         "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": mod.make_extern_data(spec["model_opts"]),
         "model_opts": dict(spec["model_opts"]), "get_model": mod.get_model, "train_step": mod.train_step, "batch_size": spec["budget"],
         "max_seqs": 2000, "learning_rate": 1e-4, "torch_amp": "bfloat16", "num_epochs": 1, "log_verbosity": 2 if rank == 0 else 1,
-        "device": "cuda"}, **spec["extra"]))
+        "device": "cuda", "forward_step": getattr(mod, "forward_step", None)}, **spec["extra"]))
     if world > 1:
         cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else {"reduce_type": "grad"})
     set_global_config(cfg)
@@ -147,6 +147,56 @@ def run_gpu(args):
             out[k] = raw[k].to(dev, non_blocking=True)
         return out
 
+    if args.task == "search":
+        # beam search through forward_step (beam size and length limit from the model options), end to end per batch: pinned host
+        # batch -> device, decode, best hypotheses and their lengths back on the host
+        from returnn_b200.torch.data import extern_data as extern_data_util
+        import returnn_b200.frontend as rf
+
+        engine._pt_model.eval()
+        n_hyp_tokens = 0
+
+        def decode(raw):
+            extern = extern_data_util.raw_dict_to_extern_data(raw, extern_data_template=engine.extern_data, device=engine._device,
+                                                              float_dtype=engine._default_float_dtype, with_eval_targets=False)
+            engine._run_step(extern, train_func=False)
+            out = rf.get_run_ctx().outputs["output"]
+            hyp = out.raw_tensor.cpu()
+            lens = out.dims[1].dyn_size_ext.raw_tensor.cpu()
+            return hyp, lens
+
+        with torch.no_grad():
+            for i in range(W):
+                decode(raws[i])
+            barrier()
+            sampler = _bench.ClockSampler(local_rank)
+            if rank == 0:
+                sampler.start()
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+            for i in range(K):
+                hyp, lens = decode(raws[W + i])
+                n_hyp_tokens += int(lens.sum())
+            ev1.record()
+            barrier()
+        ms = ev0.elapsed_time(ev1)
+        clocks = sampler.stop() if rank == 0 else None
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        f = torch.tensor([sum(counts[W: W + K])], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dist.all_reduce(f, op=dist.ReduceOp.SUM)
+        if rank == 0:
+            print(json.dumps({"metric": "beam search " + spec["metric"].replace("train ", ""), "value": f.item() / (t.item() / 1e3), "unit": spec["unit"],
+                              "n_gpus": world, "steps": K, "warmup": W, "ms_per_batch": t.item() / K, "higher_is_better": True, "dtype": "bf16",
+                              "data": "synthetic", "impl": "returnn_b200", "config": {"model": spec["name"], "batch": "%i per GPU" % spec["budget"],
+                                                                                          "beam_size": getattr(engine._orig_model, "beam_size", None),
+                                                                                          "hyp_tokens_per_batch": n_hyp_tokens / K},
+                              "clocks": clocks}))
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
     for i in range(W):
         engine.run_train_step(to_dev(raws[i]), read_losses=False)
     staged = [to_dev(raws[W + i]) for i in range(K)]
@@ -680,6 +730,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--task", default="train", choices=["train", "search"], help="search: beam search decoding (conformer_aed, transformer_mt)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: every --config here has a reference arm")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -27,6 +27,7 @@ constexpr int kUnits = 8;      // hidden units per CTA (H = 1024 -> 128 CTAs)
 constexpr int kMaxRows = 48;   // batch rows (three m16 tiles)
 constexpr int kThreads = 256;  // eight warps: each takes one eighth of the contraction
 constexpr int kPad = 32;       // row padding of the resident slice: pitch = 64 bytes mod 128 (conflict-free 16-byte fragment loads)
+constexpr int kRedPad = 8;      // row padding of the partial-sum slots
 constexpr uint32_t kSpinLimit = 1u << 22;
 
 __device__ __forceinline__ float sigm(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -126,19 +127,50 @@ __device__ __forceinline__ void step_matmul(const bf16* __restrict__ A, int n_ro
       }
     }
   }
+  // The partial sums of the eight warps meet in shared memory without atomics (eight warps adding 48 values per lane onto the
+  // same words was the largest batch-dependent part of a forward step): warps 4..7 store theirs into slot (warp - 4), warps
+  // 0..3 add their own onto that slot, the caller sums the four slots (red_sum). Row pitch NOUT + 8 floats: the 8-byte accesses
+  // of a half warp fall on distinct banks.
+  constexpr int RP = NOUT + kRedPad;
+  float* slot = red + (warp & 3) * (kMaxRows * RP);
+  if (warp >= 4) {
 #pragma unroll
-  for (int m = 0; m < 3; ++m) {
-    if (m >= m_tiles) continue;
-    const int r0 = m * 16 + g, r1 = r0 + 8;
+    for (int m = 0; m < 3; ++m) {
+      if (m >= m_tiles) continue;
+      const int r0 = m * 16 + g, r1 = r0 + 8;
 #pragma unroll
-    for (int n = 0; n < NOUT / 8; ++n) {
-      const int c = n * 8 + 2 * t;
-      atomicAdd(&red[r0 * NOUT + c], acc[m][n][0]);
-      atomicAdd(&red[r0 * NOUT + c + 1], acc[m][n][1]);
-      atomicAdd(&red[r1 * NOUT + c], acc[m][n][2]);
-      atomicAdd(&red[r1 * NOUT + c + 1], acc[m][n][3]);
+      for (int n = 0; n < NOUT / 8; ++n) {
+        const int c = n * 8 + 2 * t;
+        *reinterpret_cast<float2*>(&slot[r0 * RP + c]) = make_float2(acc[m][n][0], acc[m][n][1]);
+        *reinterpret_cast<float2*>(&slot[r1 * RP + c]) = make_float2(acc[m][n][2], acc[m][n][3]);
+      }
     }
   }
+  __syncthreads();
+  if (warp < 4) {
+#pragma unroll
+    for (int m = 0; m < 3; ++m) {
+      if (m >= m_tiles) continue;
+      const int r0 = m * 16 + g, r1 = r0 + 8;
+#pragma unroll
+      for (int n = 0; n < NOUT / 8; ++n) {
+        const int c = n * 8 + 2 * t;
+        float2* q0 = reinterpret_cast<float2*>(&slot[r0 * RP + c]);
+        float2* q1 = reinterpret_cast<float2*>(&slot[r1 * RP + c]);
+        const float2 v0 = *q0, v1 = *q1;
+        *q0 = make_float2(v0.x + acc[m][n][0], v0.y + acc[m][n][1]);
+        *q1 = make_float2(v1.x + acc[m][n][2], v1.y + acc[m][n][3]);
+      }
+    }
+  }
+}
+
+// sum over the four slots that step_matmul leaves (after a __syncthreads)
+template <int NOUT>
+__device__ __forceinline__ float red_sum(const float* __restrict__ red, int row, int col) {
+  constexpr int RP = NOUT + kRedPad;
+  const float* q = red + row * RP + col;
+  return (q[0] + q[kMaxRows * RP]) + (q[2 * kMaxRows * RP] + q[3 * kMaxRows * RP]);
 }
 
 struct FwdArgs {
@@ -164,8 +196,8 @@ __device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const 
   const int H = p.H, B = p.B;
   const int pitch = H + kPad;
   bf16* Ws = reinterpret_cast<bf16*>(smem_raw);                                 // [4*kUnits][H+kPad]: row q*kUnits+u = W_rec[q*H + j0 + u]
-  float* red = reinterpret_cast<float*>(Ws + (size_t)4 * kUnits * pitch);       // [48][4*kUnits]
-  float* cst = red + kMaxRows * 4 * kUnits;                                     // [48][kUnits] cell state
+  float* red = reinterpret_cast<float*>(Ws + (size_t)4 * kUnits * pitch);       // [4 slots][48][4*kUnits + kRedPad]
+  float* cst = red + 4 * kMaxRows * (4 * kUnits + kRedPad);                                     // [48][kUnits] cell state
   float* hst = cst + kMaxRows * kUnits;                                         // [48][kUnits] own slice of h (fp32)
   const int j0 = cta * kUnits;
   // resident slice: 4*kUnits rows of H elements, 16-byte copies
@@ -208,8 +240,6 @@ __device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const 
     const int t = p.reverse ? p.T - 1 - s : s;
     const bf16* h_cur = p.hbuf + (size_t)(s & 1) * B * H;
     bf16* h_nxt = p.hbuf + (size_t)((s + 1) & 1) * B * H;
-    for (int idx = threadIdx.x; idx < kMaxRows * 4 * kUnits; idx += kThreads) red[idx] = 0.f;
-    __syncthreads();
     step_matmul<4 * kUnits, kPrefetch>(h_cur, B, H, Ws, red);
     __syncthreads();
 #pragma unroll
@@ -229,11 +259,10 @@ __device__ __forceinline__ void fwd_body(const FwdArgs& p, const int cta, const 
         h_nxt[(size_t)b * H + j0 + u] = __float2bfloat16(hp);
         continue;
       }
-      const float* r = red + b * 4 * kUnits;
-      const float gi = sigm(r[u] + zin[i][0]);
-      const float gf = sigm(r[kUnits + u] + zin[i][1]);
-      const float gg = tanhf(r[2 * kUnits + u] + zin[i][2]);
-      const float go = sigm(r[3 * kUnits + u] + zin[i][3]);
+      const float gi = sigm(red_sum<4 * kUnits>(red, b, u) + zin[i][0]);
+      const float gf = sigm(red_sum<4 * kUnits>(red, b, kUnits + u) + zin[i][1]);
+      const float gg = tanhf(red_sum<4 * kUnits>(red, b, 2 * kUnits + u) + zin[i][2]);
+      const float go = sigm(red_sum<4 * kUnits>(red, b, 3 * kUnits + u) + zin[i][3]);
       const float c = gf * cp + gi * gg;
       const bf16 hb = __float2bfloat16(go * tanhf(c));
       cst[idx] = c;
@@ -292,8 +321,8 @@ __device__ __forceinline__ void bwd_body(const BwdArgs& p, const int cta, const 
   const int H = p.H, B = p.B, K = 4 * p.H;
   const int pitch = K + kPad;
   bf16* Wt = reinterpret_cast<bf16*>(smem_raw);                      // [kUnits][4H+kPad]: Wt[u][n] = W_rec[n][j0+u]
-  float* red = reinterpret_cast<float*>(Wt + (size_t)kUnits * pitch);  // [48][16]
-  float* dhs = red + kMaxRows * kUnits;                              // [48][16] gradient arriving at h_t
+  float* red = reinterpret_cast<float*>(Wt + (size_t)kUnits * pitch);  // [4 slots][48][kUnits + kRedPad]
+  float* dhs = red + 4 * kMaxRows * (kUnits + kRedPad);                              // [48][16] gradient arriving at h_t
   float* dcs = dhs + kMaxRows * kUnits;                              // [48][16] gradient arriving at c_t
   const int j0 = cta * kUnits;
   for (int idx = threadIdx.x; idx < K * (kUnits / 8); idx += kThreads) {
@@ -338,12 +367,11 @@ __device__ __forceinline__ void bwd_body(const BwdArgs& p, const int cta, const 
       dcs[idx] = dc * gf;
       dhs[idx] = 0.f;
     }
-    for (int idx = threadIdx.x; idx < kMaxRows * kUnits; idx += kThreads) red[idx] = 0.f;
-    ok = grid_barrier(p.counter, (++n_bar) * n_cta, p.abort_word, p.status);  // all slices of dz_t are written (and red is zero)
+    ok = grid_barrier(p.counter, (++n_bar) * n_cta, p.abort_word, p.status);  // all slices of dz_t are written
     if (!ok) break;
     step_matmul<kUnits, kPrefetch>(dz_t, B, K, Wt, red);
     __syncthreads();
-    for (int idx = threadIdx.x; idx < B * kUnits; idx += kThreads) dhs[idx] += red[idx];
+    for (int idx = threadIdx.x; idx < B * kUnits; idx += kThreads) dhs[idx] += red_sum<kUnits>(red, idx / kUnits, idx % kUnits);
     __syncthreads();
   }
   for (int idx = threadIdx.x; idx < B * kUnits; idx += kThreads) {
@@ -382,8 +410,12 @@ unsigned int* sync_slot() {
   return base[dev] + 2 * (next++ % kSyncSlots);
 }
 
-size_t fwd_smem(int H) { return (size_t)4 * kUnits * (H + kPad) * sizeof(bf16) + (size_t)kMaxRows * (4 * kUnits + 2 * kUnits) * sizeof(float); }
-size_t bwd_smem(int H) { return (size_t)kUnits * (4 * H + kPad) * sizeof(bf16) + (size_t)kMaxRows * 3 * kUnits * sizeof(float); }
+size_t fwd_smem(int H) {
+  return (size_t)4 * kUnits * (H + kPad) * sizeof(bf16) + (size_t)kMaxRows * (4 * (4 * kUnits + kRedPad) + 2 * kUnits) * sizeof(float);
+}
+size_t bwd_smem(int H) {
+  return (size_t)kUnits * (4 * H + kPad) * sizeof(bf16) + (size_t)kMaxRows * (4 * (kUnits + kRedPad) + 2 * kUnits) * sizeof(float);
+}
 
 bool enabled() {
   static const bool on = [] {

@@ -632,6 +632,10 @@ def sinusoidal_positional_encoding(*, spatial_dim: Dim, feat_dim: Dim, offset=No
     if spatial_dim == single_step_dim:
         assert offset is not None
         indices = convert_to_tensor(offset, device=device) if not isinstance(offset, Tensor) else offset
+        if device is not None and isinstance(indices.raw_tensor, torch.Tensor) and str(indices.raw_tensor.device).split(":")[0] != str(device).split(":")[0]:
+            from ..tensor.utils import host_to_device
+
+            indices = indices.copy_with_raw(host_to_device(indices.raw_tensor, device))
     else:
         indices = range_over_dim(spatial_dim, device=device)
         if offset is not None:

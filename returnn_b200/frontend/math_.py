@@ -106,9 +106,10 @@ def compare(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
     if fn is None:
         raise ValueError("compare: invalid kind %r" % kind)
     if ra.device != rb.device:
-        if not rb.ndim:
+        # a host operand (scalar, sizes, a step counter of a decoder state) follows the device operand
+        if not rb.ndim or (rb.device.type == "cpu" and ra.device.type != "cpu"):
             rb = host_to_device(rb, ra.device)
-        elif not ra.ndim:
+        elif not ra.ndim or ra.device.type == "cpu":
             ra = host_to_device(ra, rb.device)
     return wrap(fn(ra, rb), out_dims, name="compare")
 
@@ -125,9 +126,10 @@ def combine(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
     if fn is None:
         raise ValueError("combine: invalid kind %r" % kind)
     if ra.device != rb.device:
-        if not rb.ndim:
+        # a host operand (scalar, sizes, a step counter of a decoder state) follows the device operand
+        if not rb.ndim or (rb.device.type == "cpu" and ra.device.type != "cpu"):
             rb = host_to_device(rb, ra.device)
-        elif not ra.ndim:
+        elif not ra.ndim or ra.device.type == "cpu":
             ra = host_to_device(ra, rb.device)
     res = fn(ra, rb)
     src = a if a._dims == out_dims or not b._dims else b

@@ -278,6 +278,9 @@ class Engine(EngineBase):
         total_frames = NumbersDict(0)
         total_padded = NumbersDict(0)
         data_iter = iter(self._train_dataloader)
+        if str(self._device).startswith("cuda") and self.config.bool("torch_stage_batches", True):
+            # the copy of batch i+1 runs on the copy stream during step i
+            data_iter = self._staged_iter(data_iter)
         zero_grad_next_step = True
         cur_count_grad_accum = 0
         extern_data = None
@@ -364,6 +367,7 @@ class Engine(EngineBase):
                 last_seq_idx = int(extern_data_raw["seq_idx"].max()) if "seq_idx" in extern_data_raw else -1
                 if step_idx == 0 and self._do_save() and "epoch" in extern_data_raw:
                     assert int(extern_data_raw["epoch"]) == self.epoch, "data loader epoch %i != engine epoch %i" % (int(extern_data_raw["epoch"]), self.epoch)
+                self._consume_staged(extern_data_raw)
                 if zero_grad_next_step and self._graph_step is None:
                     self._updater.get_optimizer().zero_grad()
                     cur_count_grad_accum = 0
@@ -502,11 +506,35 @@ class Engine(EngineBase):
             for k, data in self.extern_data.data.items():
                 v = extern_data_raw.get(k)
                 if isinstance(v, torch.Tensor) and not v.is_cuda and data.dtype != "string":
+                    if not v.is_pinned():
+                        v = v.pin_memory()  # a copy from pageable memory would block the host until it is done
                     out[k] = v.to(self._device, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(self._copy_stream)
         out["_staged_event"] = ev
         return out
+
+    @staticmethod
+    def _consume_staged(extern_data_raw: Dict[str, Any]):
+        """a batch from ``stage_batch``: the compute stream waits for its copy and takes over the device tensors"""
+        staged_ev = extern_data_raw.get("_staged_event")
+        if staged_ev is not None:
+            cur = torch.cuda.current_stream()
+            cur.wait_event(staged_ev)
+            for v in extern_data_raw.values():
+                if isinstance(v, torch.Tensor) and v.is_cuda:
+                    v.record_stream(cur)
+
+    def _staged_iter(self, data_iter):
+        """the batches of ``data_iter``, each already on its way to the device while the step before it runs"""
+        prev = None
+        for raw in data_iter:
+            staged = self.stage_batch(raw)
+            if prev is not None:
+                yield prev
+            prev = staged
+        if prev is not None:
+            yield prev
 
     def flush_losses(self) -> Dict[str, Any]:
         """
@@ -539,13 +567,7 @@ class Engine(EngineBase):
         dist = self._torch_distributed_ctx
         if dist:
             dist.check_peers(self.global_train_step)
-        staged_ev = extern_data_raw.get("_staged_event")
-        if staged_ev is not None:
-            cur = torch.cuda.current_stream()
-            cur.wait_event(staged_ev)
-            for v in extern_data_raw.values():
-                if isinstance(v, torch.Tensor) and v.is_cuda:
-                    v.record_stream(cur)
+        self._consume_staged(extern_data_raw)
         self._updater.get_optimizer().zero_grad()
         extern_data = extern_data_util.raw_dict_to_extern_data(
             extern_data_raw, extern_data_template=self.extern_data, device=self._device,
