@@ -96,3 +96,20 @@ def test_native_encoder_dropout_reproducible():
     from returnn_b200.ops import gemm
 
     gemm.check_status()
+
+
+@gpu
+def test_native_encoder_stays_inside_its_workspace():
+    """forward + backward of the executor with canary regions around its workspace and every tensor of the fused path"""
+    from returnn_b200.ops import guard, gemm
+
+    model, pt, arena = _make(dropout=0.1)
+    torch.manual_seed(3)
+    for lens in (torch.tensor([600, 431, 577, 90], dtype=torch.int32), torch.tensor([61], dtype=torch.int32), torch.tensor([333, 1999, 64], dtype=torch.int32)):
+        feats = torch.randn(len(lens), int(lens.max()), 80, device="cuda")
+        wgt = torch.randn(int((lens // 6 + 2).sum()), model.model_dim.dimension, device="cuda")
+        with guard.CanaryAllocations() as g:
+            out, _, grads = _run(model, arena, feats, lens, wgt, native=True)
+        g.check()
+        gemm.check_status()
+        assert g.num_guarded() > 0 and bool(torch.isfinite(out).all()) and bool(torch.isfinite(grads).all())
