@@ -100,7 +100,91 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, cons
     }
     return;
   }
-  // ---- alpha
+  if (se <= (int)blockDim.x) {
+    // The usual case (at most 127 labels): one state per thread. A frame of the recursion is then a short dependent chain
+    // (two shared-memory reads, two log-adds, a barrier); the log-probability of the next frame (and, in the beta pass, the
+    // stored alpha) is fetched one frame ahead so that no global load sits on that chain.
+    const int s = threadIdx.x;
+    const bool act = s < se;
+    const bool skip_a = act && s >= 2 && (s & 1) && cls[s] != cls[s - 2];
+    const bool skip_b = act && s + 2 < se && (s & 1) && cls[s] != cls[s + 2];
+    float* prev = buf0;
+    float* cur = buf1;
+    if (act) {
+      const float a = (s < 2) ? lp[(size_t)r0 * SE + s] : kNegInf;
+      prev[s] = a;
+      ab[(size_t)r0 * SE + s] = a;
+    }
+    float l_next = (act && T > 1) ? lp[(size_t)(r0 + 1) * SE + s] : 0.f;
+    __syncthreads();
+    for (int t = 1; t < T; ++t) {
+      const size_t row = (size_t)(r0 + t) * SE;
+      const float l = l_next;
+      if (act && t + 1 < T) l_next = lp[row + SE + s];
+      if (act) {
+        float a = prev[s];
+        if (s >= 1) a = log_add(a, prev[s - 1]);
+        if (skip_a) a = log_add(a, prev[s - 2]);
+        a = (a == kNegInf) ? kNegInf : a + l;
+        cur[s] = a;
+        ab[row + s] = a;
+      }
+      __syncthreads();
+      float* tmp = prev;
+      prev = cur;
+      cur = tmp;
+    }
+    __shared__ float logp_fast;
+    if (threadIdx.x == 0) {
+      float lpz = prev[se - 1];
+      if (se >= 2) lpz = log_add(lpz, prev[se - 2]);
+      logp_fast = lpz;
+      logp_out[b] = lpz;
+      loss[b] = (lpz == kNegInf) ? 0.f : -lpz;
+    }
+    __syncthreads();
+    const float logp = logp_fast;
+    if (logp == kNegInf) return;  // infeasible: the gradient kernel writes zeros
+    {
+      const size_t row = (size_t)(r0 + T - 1) * SE;
+      if (act) {
+        const float lt = lp[row + s];
+        const float bt = (s >= se - 2) ? lt : kNegInf;
+        prev[s] = bt;
+        const float a = ab[row + s];  // written by this thread in the alpha pass
+        ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lt - logp);
+      }
+    }
+    float a_next = 0.f;
+    l_next = 0.f;
+    if (act && T > 1) {
+      l_next = lp[(size_t)(r0 + T - 2) * SE + s];
+      a_next = ab[(size_t)(r0 + T - 2) * SE + s];
+    }
+    __syncthreads();
+    for (int t = T - 2; t >= 0; --t) {
+      const size_t row = (size_t)(r0 + t) * SE;
+      const float l = l_next, a = a_next;
+      if (act && t > 0) {
+        l_next = lp[row - SE + s];
+        a_next = ab[row - SE + s];
+      }
+      if (act) {
+        float bt = prev[s];
+        if (s + 1 < se) bt = log_add(bt, prev[s + 1]);
+        if (skip_b) bt = log_add(bt, prev[s + 2]);
+        bt = (bt == kNegInf) ? kNegInf : bt + l;
+        cur[s] = bt;
+        ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - l - logp);
+      }
+      __syncthreads();
+      float* tmp = prev;
+      prev = cur;
+      cur = tmp;
+    }
+    return;
+  }
+  // ---- general case (more states than threads): alpha
   float* prev = buf0;
   float* cur = buf1;
   for (int s = threadIdx.x; s < se; s += blockDim.x) {
