@@ -62,6 +62,15 @@ class _CtcFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dloss):
         grad, row_batch = ctx.saved_tensors
+        lib = _lib.get_lib()
+        if grad.is_cuda and lib is not None and hasattr(lib, "rb200_ctc_scale_rows") and grad.dtype in (torch.bfloat16, torch.float32):
+            dl = dloss.to(torch.float32).contiguous()
+            out = torch.empty_like(grad)
+            fn = _lib.bind("rb200_ctc_scale_rows", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _vp])
+            _lib.check(fn(grad.data_ptr(), row_batch.data_ptr(), dl.data_ptr(), out.data_ptr(), grad.shape[0], grad.shape[1],
+                          1 if grad.dtype == torch.bfloat16 else 0, _lib.stream_ptr()), "ctc_scale_rows")
+            _lib.count_launch()
+            return out, None, None, None, None, None, None, None
         scale = dloss.to(torch.float32)[row_batch.long()].unsqueeze(-1)
         return (grad.float() * scale).to(grad.dtype), None, None, None, None, None, None, None
 
