@@ -71,6 +71,16 @@ def _col2im(dcol, lens_out, lens_in, cu, B, T, F, Ci, stride, pad, To, relu_z):
     return dx
 
 
+def _colsum(x: torch.Tensor) -> torch.Tensor:
+    """column sums of a bf16 [rows, C] matrix in fp32 (bias gradient), one pass on the native kernel"""
+    lib = _lib.get_lib()
+    if x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and lib is not None and hasattr(lib, "rb200_colsum_bf16") and x.shape[1] % 8 == 0:
+        out = torch.zeros(x.shape[1], dtype=torch.float32, device=x.device)
+        _call("rb200_colsum_bf16", [_vp, _vp, _i32, _i32, _vp], x.data_ptr(), out.data_ptr(), x.shape[0], x.shape[1], _lib.stream_ptr())
+        return out
+    return x.float().sum(0)
+
+
 class _FrontendFn(torch.autograd.Function):
     """feats [B,T,F] bf16 -> packed rows [n, (F/2)*C3] bf16"""
 
@@ -118,7 +128,7 @@ class _FrontendFn(torch.autograd.Function):
         dz3 = torch.where(out3 > 0, d_out.reshape(n * Fp, C3).to(bf), torch.zeros((), dtype=bf, device=dev)).contiguous()
         dw3p = torch.zeros(C3, 9 * C2, dtype=torch.float32, device=dev)
         _gemm.gemm(dz3, col3, m=C3, n=9 * C2, k=dz3.shape[0], a_mn_major=True, b_mn_major=True, out=dw3p, atomic=True)
-        db3 = dz3.float().sum(0) if has_b3 else None
+        db3 = _colsum(dz3) if has_b3 else None
         # data gradient of layer 3: patch gradients on the output side, gathered back (times relu'(out2))
         w3p = w3.permute(0, 2, 3, 1).reshape(C3, 9 * C2).to(bf).contiguous()
         dcol3 = _gemm.gemm(dz3, w3p, m=dz3.shape[0], n=9 * C2, k=C3, a_mn_major=False, b_mn_major=True)
@@ -127,7 +137,7 @@ class _FrontendFn(torch.autograd.Function):
         # ---- layer 2
         dw2p = torch.zeros(C2, 9 * C1, dtype=torch.float32, device=dev)
         _gemm.gemm(dz2, col2, m=C2, n=9 * C1, k=dz2.shape[0], a_mn_major=True, b_mn_major=True, out=dw2p, atomic=True)
-        db2 = dz2.float().sum(0) if has_b2 else None
+        db2 = _colsum(dz2) if has_b2 else None
         w2p = w2.permute(0, 2, 3, 1).reshape(C2, 9 * C1).to(bf).contiguous()
         dcol2 = _gemm.gemm(dz2, w2p, m=dz2.shape[0], n=9 * C1, k=C2, a_mn_major=False, b_mn_major=True)
         d_out1 = _col2im(dcol2, lens_dev[1], lens_dev[0], None, B, T, Fp, C1, s2, pad2, T2, None)
