@@ -192,6 +192,34 @@ class Engine(EngineBase):
             from .util.graph_capture import GraphCapturedTrainStep
 
             self._graph_step = GraphCapturedTrainStep(engine=self, opts=graph_opts if isinstance(graph_opts, dict) else {})
+        self._reserve_device_memory()
+
+    def _reserve_device_memory(self):
+        """
+        Batches of a length-bucketed epoch all have different shapes, and every new size class makes the caching allocator go to
+        the driver (``cudaMalloc`` synchronises the device) for dozens of steps. One large block is therefore taken and returned
+        to the allocator's cache up front: later requests are carved out of it without a driver call. Config
+        ``torch_reserve_memory_gb``: number of GB, 0 to disable; default: a fifth of the free device memory, at most 32 GB,
+        nothing on devices with less than 64 GB free.
+        """
+        if not str(self._device).startswith("cuda"):
+            return
+        want = self.config.typed_value("torch_reserve_memory_gb", None)
+        try:
+            free, _total = torch.cuda.mem_get_info(torch.device(self._device))
+        except Exception:
+            return
+        if want is None:
+            want = min(32.0, free / 5 / 2 ** 30) if free >= 64 * 2 ** 30 else 0.0
+        nbytes = int(float(want) * 2 ** 30)
+        if nbytes <= 0 or nbytes > free * 0.8:
+            return
+        try:
+            block = torch.empty(nbytes, dtype=torch.uint8, device=self._device)
+            del block
+            print("Reserved %.1f GB of device memory for the allocator cache." % (nbytes / 2 ** 30), file=log.v4)
+        except RuntimeError:
+            pass
 
     # -- train -------------------------------------------------------------------------------------------------------
     def train(self):
@@ -502,13 +530,25 @@ class Engine(EngineBase):
         if self._copy_stream is None:
             self._copy_stream = torch.cuda.Stream(device=self._device)
         out = dict(extern_data_raw)
+        # The device tensors come from the compute stream's pool of the caching allocator (a tensor allocated under the copy
+        # stream would live in that stream's own pool, which has to grow by driver calls for every new batch shape); the copy
+        # stream first waits for the compute stream as of now, so the memory's previous tenant is done with it. The step before
+        # the one this batch belongs to is still executing at that point: the copy overlaps it.
+        cur = torch.cuda.current_stream()
+        todo = []
+        for k, data in self.extern_data.data.items():
+            v = extern_data_raw.get(k)
+            if isinstance(v, torch.Tensor) and not v.is_cuda and data.dtype != "string":
+                if not v.is_pinned():
+                    v = v.pin_memory()  # a copy from pageable memory would block the host until it is done
+                out[k] = torch.empty(v.shape, dtype=v.dtype, device=self._device)
+                todo.append((out[k], v))
+        allocated = torch.cuda.Event()
+        allocated.record(cur)
         with torch.cuda.stream(self._copy_stream):
-            for k, data in self.extern_data.data.items():
-                v = extern_data_raw.get(k)
-                if isinstance(v, torch.Tensor) and not v.is_cuda and data.dtype != "string":
-                    if not v.is_pinned():
-                        v = v.pin_memory()  # a copy from pageable memory would block the host until it is done
-                    out[k] = v.to(self._device, non_blocking=True)
+            self._copy_stream.wait_event(allocated)
+            for dst, src in todo:
+                dst.copy_(src, non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(self._copy_stream)
         out["_staged_event"] = ev
@@ -519,11 +559,7 @@ class Engine(EngineBase):
         """a batch from ``stage_batch``: the compute stream waits for its copy and takes over the device tensors"""
         staged_ev = extern_data_raw.get("_staged_event")
         if staged_ev is not None:
-            cur = torch.cuda.current_stream()
-            cur.wait_event(staged_ev)
-            for v in extern_data_raw.values():
-                if isinstance(v, torch.Tensor) and v.is_cuda:
-                    v.record_stream(cur)
+            torch.cuda.current_stream().wait_event(staged_ev)
 
     def _staged_iter(self, data_iter):
         """the batches of ``data_iter``, each already on its way to the device while the step before it runs"""
