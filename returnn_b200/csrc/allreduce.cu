@@ -12,8 +12,16 @@
 //      last bucket every rank holds the squared global gradient norm without another pass or collective
 //   4. exit barrier: all pushes have landed before any rank's next kernel reads its buffer
 //
-// Every wait is bounded (kSpinLimit polls with nanosleep, about two seconds): a CTA that gives up writes a status word and
-// skips its data phase; the context stays usable and the host raises an error.
+// Every wait is bounded twice over: by a time limit read from the GPU's global timer (rb200_collective_set_wait_ms, default 20 s:
+// long enough for a peer that is late because of a lazy initialisation or a data stall, short enough that a dead peer does not
+// hold the GPU) and by a poll count that follows from it. A CTA that gives up writes a status word and skips its data phase;
+// the context stays usable and the host raises an error when it reads the word (once per training step, with the losses).
+//
+// Parameter-averaging mode (AdamW update, then average): the slices are interleaved instead of contiguous. With G = grid size
+// x 512 threads, float4 number i is updated on every rank by CTA (i mod G) / 512, and it is reduced by rank (i / G) mod world,
+// again in CTA (i mod G) / 512. So everything a CTA reads in the averaging phase, locally and on the peers, was written by
+// the same-numbered CTA of that rank before that CTA signalled the entry barrier: the barrier between same-numbered CTAs is
+// all the synchronisation the two phases need.
 #include "common.cuh"
 #include "adamw.cuh"
 #include <cstring>
@@ -23,7 +31,9 @@ namespace {
 constexpr int kMaxWorld = 8;
 constexpr int kMaxBlocks = 256;
 constexpr int kThreads = 512;
-constexpr uint32_t kSpinLimit = 1u << 21;
+
+// wait limit of the cross-rank barriers in nanoseconds (process-wide; set through rb200_collective_set_wait_ms)
+unsigned long long g_wait_ns = 20ull * 1000 * 1000 * 1000;
 
 struct ArParams {
   float* bufs[kMaxWorld];       // the gradient arena of every rank (bufs[rank] is local)
@@ -35,8 +45,16 @@ struct ArParams {
   float scale;
   uint32_t epoch;               // barrier values epoch (entry) and epoch + 1 (exit); grows by 2 per call on all ranks alike
   int norm_slot;
+  int interleaved;              // 1: rank r owns float4 i with (i / G) % world == r (parameter-averaging mode), 0: contiguous slices
+  unsigned long long wait_ns;   // time limit of a barrier wait
   int* status;
 };
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -56,11 +74,15 @@ __device__ bool cta_barrier(const ArParams& p, uint32_t val, int* sh_fail, int c
     st_release_sys(p.flags[peer] + (size_t)p.rank * kMaxBlocks + blockIdx.x, val);
     const uint32_t* mine = p.flags[p.rank] + (size_t)peer * kMaxBlocks + blockIdx.x;
     bool ok = false;
-    for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    const unsigned long long t0 = global_timer_ns();
+    // every poll after the first 64 sleeps about a microsecond: the poll count bounds the wait even if the timer stood still
+    const unsigned long long max_polls = 64 + p.wait_ns / 500;
+    for (unsigned long long i = 0; i < max_polls; ++i) {
       if ((int32_t)(ld_acquire_sys(mine) - val) >= 0) {
         ok = true;
         break;
       }
+      if (i >= 64 && global_timer_ns() - t0 > p.wait_ns) break;
       __nanosleep(i < 64 ? 32 : 1000);
     }
     if (!ok) {
@@ -100,10 +122,13 @@ fused_allreduce_kernel(const ArParams p, const AdamwArgs adam) {
   // slices of whole float4s; the tail (n % 4 elements) belongs to the last rank
   const long long n4 = p.n / 4;
   const long long per = (n4 + p.world - 1) / p.world;
-  const long long s0 = per * p.rank < n4 ? per * p.rank : n4;
-  const long long s1 = s0 + per < n4 ? s0 + per : n4;
+  const long long grid_threads = (long long)gridDim.x * kThreads;
+  // contiguous mode: this rank's slice [s0, s1), consecutive iterations one grid apart
+  // interleaved mode: grid-sized chunks dealt out to the ranks in turn, consecutive iterations `world` grids apart
+  const long long s0 = p.interleaved ? (long long)p.rank * grid_threads : (per * p.rank < n4 ? per * p.rank : n4);
+  const long long s1 = p.interleaved ? n4 : (s0 + per < n4 ? s0 + per : n4);
   float ssq = 0.f;
-  const long long stride = (long long)gridDim.x * kThreads;
+  const long long stride = p.interleaved ? grid_threads * p.world : grid_threads;
   // four float4 per thread and iteration: all loads of an iteration are issued before the first use, which keeps enough bytes
   // in flight to cover the NVLink round trip
   constexpr int U = 4;
@@ -204,6 +229,8 @@ RB_EXPORT int rb200_fused_allreduce(const long long* bufs, const long long* flag
   p.scale = scale;
   p.epoch = epoch;
   p.norm_slot = norm_slot;
+  p.interleaved = 0;
+  p.wait_ns = g_wait_ns;
   p.status = status;
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
@@ -219,8 +246,8 @@ RB_EXPORT int rb200_fused_adamw_param_avg(const long long* bufs, const long long
                                           long long n, unsigned int epoch, int blocks, int* status, const void* g, float* m, float* v,
                                           const uint8_t* wd_flags, int g_bf16, float lr, float b1, float b2, float eps, float wd, float bc1,
                                           float bc2, int decoupled, float clip, const float* grad_norm, int do_update, cudaStream_t stream) {
-  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0) {
-    rb_set_error("fused_adamw_param_avg: world %d rank %d n %lld", world, rank, n);
+  if (world < 2 || world > kMaxWorld || rank < 0 || rank >= world || n <= 0 || n % 4 != 0) {
+    rb_set_error("fused_adamw_param_avg: world %d rank %d n %lld (n must be a positive multiple of 4)", world, rank, n);
     return RB_ERR_ARG;
   }
   ArParams p;
@@ -237,6 +264,8 @@ RB_EXPORT int rb200_fused_adamw_param_avg(const long long* bufs, const long long
   p.scale = 1.f / (float)world;
   p.epoch = epoch;
   p.norm_slot = 7;  // unused accumulator slot
+  p.interleaved = 1;
+  p.wait_ns = g_wait_ns;
   p.status = status;
   AdamwArgs a;
   memset(&a, 0, sizeof(a));
@@ -250,3 +279,13 @@ RB_EXPORT int rb200_fused_adamw_param_avg(const long long* bufs, const long long
 }
 
 RB_EXPORT int rb200_fused_allreduce_flag_words() { return kMaxWorld * kMaxBlocks; }
+
+// Time limit of every cross-rank barrier wait of the kernels in this file, for launches made after this call (1 ms .. 10 min).
+RB_EXPORT int rb200_collective_set_wait_ms(int ms) {
+  if (ms < 1 || ms > 600000) {
+    rb_set_error("collective_set_wait_ms: %d is outside 1..600000", ms);
+    return RB_ERR_ARG;
+  }
+  g_wait_ns = (unsigned long long)ms * 1000000ull;
+  return RB_OK;
+}

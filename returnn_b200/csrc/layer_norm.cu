@@ -3,7 +3,10 @@
 // Forward: one warp per row, the row is held in registers (n <= 2048) or re-read from L2 (larger n);
 // statistics in fp32; saves mean and rstd. Backward: one warp per row for dx; every CTA accumulates its
 // rows' contributions to dgamma/dbeta in registers and writes one partial per CTA into scratch memory,
-// which a second kernel reduces. No atomics, so results are deterministic.
+// which a second kernel reduces: that pair (ln_bwd_kernel + ln_bwd_reduce_kernel, also behind the allocation-free entry
+// point) uses no atomics and is deterministic. The accumulating variant used by the native encoder executor
+// (ln_bwd_acc_kernel) adds its per-CTA sums into dgamma/dbeta with fp32 atomics instead: no scratch and no second launch,
+// but the summation order, and so the last bits of dgamma/dbeta, can differ from run to run.
 #include "common.cuh"
 
 namespace {

@@ -13,6 +13,7 @@ import ctypes
 import os
 import torch
 from . import _lib
+from . import status as _status_board
 
 _vp, _i32, _f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 ENABLED = os.environ.get("RETURNN_B200_GEMM", "1") == "1"
@@ -30,23 +31,20 @@ def available(x: torch.Tensor) -> bool:
 
 
 def status_tensor(device) -> torch.Tensor:
-    """device word written by a kernel that gave up waiting (0 = fine)"""
+    """
+    Device word written by a kernel that gave up waiting (0 = fine): the GEMM slot of the device's status board
+    (:mod:`returnn_b200.ops.status`), which the training loop reads once per step.
+    """
     t = _status.get(device)
     if t is None:
-        t = torch.zeros(1, dtype=torch.int32, device=device)
+        t = _status_board.word(device, _status_board.SLOT_GEMM)
         _status[device] = t
     return t
 
 
 def check_status(device=None):
-    """raise if any GEMM launch since the last check reported a timeout (synchronises)"""
-    for key, t in _status.items():
-        if device is not None and str(key) != str(device):
-            continue
-        v = int(t.item())
-        if v != 0:
-            t.zero_()
-            raise RuntimeError("tcgen05 GEMM reported a bounded-wait timeout: role %i, k-block %i" % (v >> 24, v & 0xFFFFFF))
+    """raise ``KernelWaitTimeout`` if any kernel since the last check reported a timeout (synchronises)"""
+    _status_board.check_now(device)
 
 
 KERNEL = os.environ.get("RETURNN_B200_GEMM_KERNEL", "persistent")  # "persistent" | "legacy" (one tile per CTA, plain epilogue)

@@ -166,6 +166,10 @@ class ParamArena:
         """one memset for all gradients"""
         self.flat_grad.zero_()
 
+    def grad_view(self, slot: "ArenaSlot") -> torch.Tensor:
+        """the view of the gradient arena that belongs to one parameter"""
+        return self.flat_grad[slot.offset: slot.offset + slot.numel].view(slot.shape)
+
     def relink_grads(self):
         """make sure every ``param.grad`` is the arena view (autograd may have replaced it when it was None)"""
         if self.grad_dtype != self.dtype:

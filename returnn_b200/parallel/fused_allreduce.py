@@ -16,15 +16,32 @@ import os
 import torch
 import torch.distributed as dist
 from ..ops import _lib
+from ..ops import status as _status_board
 from .arena import ParamArena
 
 _vp, _i32, _i64, _f32, _u32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_uint
+
+DEFAULT_WAIT_MS = 20000
+
+
+def set_wait_ms(ms: Optional[int] = None):
+    """
+    Time limit of the cross-rank barrier waits inside the NVLink kernels, for launches made from now on. A peer that has not
+    arrived within the limit makes the waiting kernel give up: it writes the status word and skips its data phase, and the
+    training loop raises ``KernelWaitTimeout`` when it reads the word. Default: ``RETURNN_B200_COLLECTIVE_WAIT_MS`` or 20 s
+    (config: ``torch_distributed["fused_wait_ms"]``).
+    """
+    if ms is None:
+        ms = int(os.environ.get("RETURNN_B200_COLLECTIVE_WAIT_MS", DEFAULT_WAIT_MS))
+    fn = _lib.bind("rb200_collective_set_wait_ms", [_i32])
+    _lib.check(fn(int(ms)), "collective_set_wait_ms")
+
 
 
 class FusedAllReduce:
     """bucket reductions on the arena's gradient buffer"""
 
-    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128):
+    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128, wait_ms: Optional[int] = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         assert arena.grad_dtype == torch.float32
@@ -58,14 +75,25 @@ class FusedAllReduce:
         self.multicast_ptr = mc
         self._epoch = 1
         self._slot = 0
-        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._status = _status_board.word(dev, _status_board.SLOT_ALLREDUCE)
         self._fn = _lib.bind("rb200_fused_allreduce", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _f32, _u32, _i32, _i32, _vp, _vp])
+        self.skip_launches = 0  # failure-detection tests: this many following launches are left out (the peers' waits then run out)
+        set_wait_ms(wait_ms)
         # all ranks have zeroed their flags and accumulators before anyone's first kernel signals
         torch.cuda.synchronize(dev)
         dist.barrier(group)
 
+    @property
+    def mode(self) -> str:
+        """"fused-multimem" (reduction inside the NVSwitch) or "fused-peer" (peer loads and stores)"""
+        return "fused-multimem" if self.multicast_ptr else "fused-peer"
+
     def reduce_bucket(self, b: int, lo: int, hi: int):
         """average ``flat_grad[lo:hi]`` over the ranks, on the current stream; all ranks must call this in the same order"""
+        if self.skip_launches > 0:
+            self.skip_launches -= 1
+            self._epoch += 2
+            return
         _lib.check(self._fn(ctypes.addressof(self._bufs), ctypes.addressof(self._flag_ptrs), ctypes.addressof(self._norm_ptrs),
                             self.multicast_ptr or None, self.world, self.rank, lo, hi - lo, 1.0 / self.world, self._epoch, self._slot,
                             self.blocks, self._status.data_ptr(), _lib.stream_ptr()), "fused_allreduce")
@@ -84,12 +112,13 @@ class FusedAllReduce:
         return norm_sq
 
     def check_status(self):
-        """raise if a barrier of an earlier call timed out (synchronises)"""
+        """raise ``KernelWaitTimeout`` if a barrier of an earlier call timed out (synchronises; the training loop reads the
+        same word asynchronously once per step through the status board)"""
         v = int(self._status.item())
         if v:
             self._status.zero_()
-            raise RuntimeError("fused all-reduce: rank %i did not see peer %i at the %s barrier of CTA %i within the time limit" % (
-                self.rank, (v >> 16) & 0xFF, "entry" if (v >> 24) == 1 else "exit", v & 0xFFFF))
+            raise _status_board.KernelWaitTimeout("rank %i: %s" % (self.rank, _status_board.describe(_status_board.SLOT_ALLREDUCE, v)),
+                                                  {_status_board.SLOT_ALLREDUCE: v})
 
 
 class FusedParamAverager:
@@ -99,7 +128,7 @@ class FusedParamAverager:
     The parameter arena moves into symmetric memory.
     """
 
-    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128):
+    def __init__(self, arena: ParamArena, *, rank: int, world: int, group=None, blocks: int = 128, wait_ms: Optional[int] = None):
         import torch.distributed._symmetric_memory as symm_mem
 
         assert arena.dtype == torch.float32
@@ -126,11 +155,12 @@ class FusedParamAverager:
         use_mc = os.environ.get("RETURNN_B200_ALLREDUCE_MULTIMEM", default_mc) == "1"
         self.multicast_ptr = int(getattr(self._hdl, "multicast_ptr", 0) or 0) if use_mc else 0
         self._epoch = 1
-        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._status = _status_board.word(dev, _status_board.SLOT_PARAM_AVG)
         self.pending = False  # set by the distributed context on sync steps; the optimizer then fuses its update with the average
         _u8p = ctypes.c_void_p
         self._fn = _lib.bind("rb200_fused_adamw_param_avg", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _u32, _i32, _vp, _vp, _vp, _vp, _u8p, _i32,
                                                               _f32, _f32, _f32, _f32, _f32, _f32, _f32, _i32, _f32, _vp, _i32, _vp])
+        set_wait_ms(wait_ms)
         torch.cuda.synchronize(dev)
         dist.barrier(group)
 
@@ -154,15 +184,22 @@ class FusedParamAverager:
         self.pending = False
         self.arena.invalidate_shadow()
 
+    @property
+    def mode(self) -> str:
+        """"fused-multimem" or "fused-peer""""
+        return "fused-multimem" if self.multicast_ptr else "fused-peer"
+
     def check_status(self):
-        """raise if a barrier timed out (synchronises)"""
+        """raise ``KernelWaitTimeout`` if a barrier timed out (synchronises)"""
         v = int(self._status.item())
         if v:
             self._status.zero_()
-            raise RuntimeError("fused parameter averaging: rank %i did not see peer %i in time" % (self.rank, (v >> 16) & 0xFF))
+            raise _status_board.KernelWaitTimeout("rank %i: %s" % (self.rank, _status_board.describe(_status_board.SLOT_PARAM_AVG, v)),
+                                                  {_status_board.SLOT_PARAM_AVG: v})
 
 
-def try_create_param_averager(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedParamAverager]:
+def try_create_param_averager(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None,
+                              wait_ms: Optional[int] = None) -> Optional[FusedParamAverager]:
     """the fused averager, or None if it cannot be used here"""
     try:
         if arena.device.type != "cuda" or arena.dtype != torch.float32:
@@ -172,7 +209,7 @@ def try_create_param_averager(arena: ParamArena, *, rank: int, world: int, requi
             raise RuntimeError("kernel library without the entry point")
         if os.environ.get("RETURNN_B200_FUSED_ALLREDUCE", "1") != "1":
             raise RuntimeError("disabled by RETURNN_B200_FUSED_ALLREDUCE")
-        return FusedParamAverager(arena, rank=rank, world=world, group=group)
+        return FusedParamAverager(arena, rank=rank, world=world, group=group, wait_ms=wait_ms)
     except Exception as exc:
         if required:
             raise
@@ -210,7 +247,7 @@ class SmallVectorAllReduce:
         self._flag_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_flags.buffer_ptrs])
         self._norm_ptrs = (ctypes.c_longlong * world)(*[int(p) for p in self._hdl_norm.buffer_ptrs])
         self._epoch = 1
-        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._status = _status_board.word(device, _status_board.SLOT_SMALL_REDUCE)
         self._fn = _lib.bind("rb200_fused_allreduce", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _f32, _u32, _i32, _i32, _vp, _vp])
         torch.cuda.synchronize(device)
         dist.barrier(group)
@@ -260,7 +297,8 @@ def try_create_small_reducer(*, device, rank: int, world: int, group=None) -> Op
     return _small_reducer
 
 
-def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None) -> Optional[FusedAllReduce]:
+def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = False, group=None,
+               wait_ms: Optional[int] = None) -> Optional[FusedAllReduce]:
     """the fused reducer, or None if it cannot be used here"""
     try:
         if arena.device.type != "cuda" or arena.grad_dtype != torch.float32:
@@ -270,7 +308,7 @@ def try_create(arena: ParamArena, *, rank: int, world: int, required: bool = Fal
             raise RuntimeError("kernel library without the all-reduce entry point")
         if os.environ.get("RETURNN_B200_FUSED_ALLREDUCE", "1") != "1":
             raise RuntimeError("disabled by RETURNN_B200_FUSED_ALLREDUCE")
-        return FusedAllReduce(arena, rank=rank, world=world, group=group)
+        return FusedAllReduce(arena, rank=rank, world=world, group=group, wait_ms=wait_ms)
     except Exception as exc:
         if required:
             raise

@@ -50,7 +50,7 @@ class BucketedGradReducer:
         self._handles = []
         self._launched = [False] * len(arena.buckets)
         for s in arena.slots:
-            self._handles.append(s.param.register_post_accumulate_grad_hook(self._make_hook(s.bucket)))
+            self._handles.append(s.param.register_post_accumulate_grad_hook(self._make_hook(s)))
         self._counted = set()
         global _active
         _active = self
@@ -82,10 +82,23 @@ class BucketedGradReducer:
             if self._pending[s.bucket] == 0 and not self._launched[s.bucket]:
                 self._launch(s.bucket)
 
-    def _make_hook(self, b: int):
+    def _make_hook(self, slot):
+        b = slot.bucket
+        arena = self.arena
+
         def hook(param):
             if not self._enabled or self.world == 1:
                 return
+            # The bucket reduction reads the arena slice. If this gradient was accumulated into a tensor of its own (the
+            # gradient was None when backward started, e.g. after a zero_grad(set_to_none=True)), move it into the arena and
+            # re-point param.grad BEFORE the bucket counts down: otherwise the reduction would run on stale arena contents.
+            if arena.grad_dtype == arena.dtype:
+                g = param.grad
+                if g is not None:
+                    view = arena.grad_view(slot)
+                    if g.data_ptr() != view.data_ptr():
+                        view.copy_(g)
+                        param.grad = view
             self._pending[b] -= 1
             if self._pending[b] == 0:
                 self._launch(b)

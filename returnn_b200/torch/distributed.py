@@ -14,6 +14,9 @@ Distributed (data-parallel) context for the torch engine. Config key ``torch_dis
   the reduction kernel, fused with scaling and grad-norm partial sums; parameter averaging fused with AdamW) when every
   rank is a B200 on one node. ``False`` keeps the NCCL baseline.
 - ``bucket_cap_mb``: bucket size for ``"grad"`` (default 32)
+- ``fused_wait_ms``: time limit of the cross-rank waits inside the fused kernels (default 20000, or the environment variable
+  ``RETURNN_B200_COLLECTIVE_WAIT_MS``). A kernel whose peer does not arrive in time gives up and reports through the status
+  board; the engine raises ``KernelWaitTimeout`` one step later.
 
 One process per GPU, started by ``torchrun`` (RANK, LOCAL_RANK, WORLD_SIZE, MASTER_ADDR/PORT from the environment).
 
@@ -66,6 +69,7 @@ class DistributedContext:
         self._custom_class_opts = self._opts.get("options", None)
         self._fused_opt = self._opts.get("fused", None)
         self._bucket_cap_mb = self._opts.get("bucket_cap_mb", 32)
+        self._fused_wait_ms = self._opts.get("fused_wait_ms", None)
         peer_watch_opts = self._opts.get("peer_watch", None)
         self._opts.assert_all_read()
         from ..parallel import peer_watch as _peer_watch
@@ -171,7 +175,8 @@ class DistributedContext:
                 from ..parallel import fused_allreduce
 
                 self._arena = ParamArena(named, bucket_bytes=int(self._bucket_cap_mb) << 20)
-                self._param_averager = fused_allreduce.try_create_param_averager(self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt))
+                self._param_averager = fused_allreduce.try_create_param_averager(
+                    self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt), wait_ms=self._fused_wait_ms)
             return
         if self._reduce_type not in ("grad", "grad_explicit") or self._custom_class is not None:
             return
@@ -184,7 +189,8 @@ class DistributedContext:
         if self.want_fused(device):
             from ..parallel import fused_allreduce
 
-            self._fused = fused_allreduce.try_create(self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt))
+            self._fused = fused_allreduce.try_create(self._arena, rank=self._rank, world=self._size, required=bool(self._fused_opt),
+                                                     wait_ms=self._fused_wait_ms)
             from ..config import get_global_config
 
             cfg = get_global_config(raise_exception=False)
@@ -206,6 +212,19 @@ class DistributedContext:
     def fused(self):
         """the fused NVLink reducer, if active"""
         return self._fused
+
+    @property
+    def grad_reduce_mode(self) -> str:
+        """
+        how gradients (or parameters, for ``reduce_type="param"``) cross the GPUs: ``"fused-multimem"`` (own kernel, reduction inside
+        the NVSwitch), ``"fused-peer"`` (own kernel, peer loads and stores), ``"nccl"`` / ``"gloo"`` (library collective), ``"none"``
+        """
+        if self._size == 1:
+            return "none"
+        f = self._fused if self._fused is not None else self._param_averager
+        if f is not None:
+            return f.mode
+        return "nccl" if (self._arena is not None and self._arena.device.type == "cuda") or torch.cuda.is_available() else "gloo"
 
     def prepare_backward(self, *, sync: bool = True):
         """before ``loss.backward()``; ``sync=False`` for gradient accumulation micro-steps"""
@@ -327,9 +346,6 @@ def _sync_params_avg(*, module: torch.nn.Module, sync_on_cpu: bool = False, ctx:
     with torch.no_grad():
         if ctx is not None and ctx.arena is not None and not sync_on_cpu and len(ctx.arena.slots) == len([p for p in params if p.requires_grad]):
             flat = ctx.arena.flat_param
-            if ctx.fused is not None:
-                ctx.fused.average_params()
-                return
             dist.all_reduce(flat)
             flat.div_(size)
             return

@@ -315,6 +315,11 @@ class Engine(EngineBase):
         # per-step bookkeeping (loss values on the host, progress line, tensorboard, non-finite check). With the pipelined read
         # (default on CUDA, ``torch_deferred_loss_read``) it runs one step late, after the following step was issued.
         deferred_read = self.config.bool("torch_deferred_loss_read", str(self._device).startswith("cuda"))
+        # kernels with bounded waits report through the device's status board; it is copied to pinned memory once per step and looked
+        # at one step late, like the losses: no extra synchronisation, and a timed-out collective cannot go unnoticed
+        from ..ops.status import StatusPoller
+
+        status_poller = StatusPoller(self._device)
         loss_ring = None
         pending_step = None
 
@@ -397,15 +402,26 @@ class Engine(EngineBase):
                     assert int(extern_data_raw["epoch"]) == self.epoch, "data loader epoch %i != engine epoch %i" % (int(extern_data_raw["epoch"]), self.epoch)
                 self._consume_staged(extern_data_raw)
                 if zero_grad_next_step and self._graph_step is None:
-                    self._updater.get_optimizer().zero_grad()
+                    self._updater.zero_grad()
                     cur_count_grad_accum = 0
                 if self._graph_step is not None:
-                    # the captured step zeroes its static gradient buffers itself
-                    losses_dict, inv_norm = self._graph_step.run_train_step(extern_data_raw)
+                    # the captured step zeroes its static gradient buffers itself; everything after the replay (gradient reduction,
+                    # update, parameter sync) and the per-step bookkeeping below are the same as on the eager path
+                    res = self._graph_step.run_train_step_ex(extern_data_raw, dist=dist, epoch_step_idx=step_idx)
+                    n_l = len(res["names"])
+                    finish_step(dict(names=res["names"], inv_list=[True] * n_l, static_inv=[None] * n_l, score_keys=res["score_keys"],
+                                     grad_norm=res["grad_norm"], step_idx=step_idx, step_begin_time=step_begin_time,
+                                     complete_frac=complete_frac, num_seqs=num_seqs_, last_seq_idx=last_seq_idx, extern_data=None,
+                                     vals=res["vals"]))
+                    status_poller.step(where="train step %i" % self.global_train_step)
                     step_idx += 1
                     self.global_train_step += 1
-                    accumulated_losses_dict += losses_dict
-                    accumulated_inv_norm_factors_dict += inv_norm
+                    ec = (self.epoch - 1 + complete_frac) if complete_frac >= 0 else ((self.epoch - 1 + (last_seq_idx + 1) / num_seqs_) if num_seqs_ > 0 else None)
+                    self._updater.set_current_train_step(global_train_step=self.global_train_step, epoch=self.epoch, epoch_continuous=ec)
+                    if profiler is not None:
+                        profiler.step()
+                        if profiler.done:
+                            break
                     continue
                 extern_data = extern_data_util.raw_dict_to_extern_data(
                     extern_data_raw, extern_data_template=self.extern_data, device=self._device,
@@ -471,6 +487,7 @@ class Engine(EngineBase):
                 else:
                     rec["vals"] = stacked.cpu().tolist() if stacked is not None else []
                     finish_step(rec)
+                status_poller.step(where="train step %i" % self.global_train_step)
                 step_idx += 1
                 self.global_train_step += 1
                 ec = (self.epoch - 1 + complete_frac) if complete_frac >= 0 else ((self.epoch - 1 + (last_seq_idx + 1) / num_seqs_) if num_seqs_ > 0 else None)
@@ -482,6 +499,7 @@ class Engine(EngineBase):
             if pending_step is not None:
                 finish_step(pending_step)
                 pending_step = None
+            status_poller.flush(where="end of epoch %i" % self.epoch)
         except Exception as exc:
             self._handle_run_exception(exc, extern_data=extern_data)
             raise
@@ -572,11 +590,15 @@ class Engine(EngineBase):
         if prev is not None:
             yield prev
 
-    def flush_losses(self) -> Dict[str, Any]:
+    def flush_losses(self, *, _final: bool = True) -> Dict[str, Any]:
         """
+        Also looks at the kernel status words of the steps issued so far (raises ``KernelWaitTimeout`` if a bounded wait ran out).
+
         :return: the losses of the last step run with ``read_losses="deferred"`` that were not handed out yet ({} if none)
         """
         pending, self._pending_losses = self._pending_losses, None
+        if _final and getattr(self, "_status_poller", None) is not None:
+            self._status_poller.flush(where="train step %i" % (self.global_train_step - 1))
         if pending is None:
             return {}
         names, host, ev = pending
@@ -604,7 +626,7 @@ class Engine(EngineBase):
         if dist:
             dist.check_peers(self.global_train_step)
         self._consume_staged(extern_data_raw)
-        self._updater.get_optimizer().zero_grad()
+        self._updater.zero_grad()
         extern_data = extern_data_util.raw_dict_to_extern_data(
             extern_data_raw, extern_data_template=self.extern_data, device=self._device,
             float_dtype=self._default_float_dtype, with_eval_targets=True)
@@ -631,10 +653,17 @@ class Engine(EngineBase):
             dist.step_after_param_update(module=self._pt_model, epoch_step_idx=self.global_train_step)
         self.global_train_step += 1
         self._updater.set_current_train_step(global_train_step=self.global_train_step, epoch=self.epoch or 1, epoch_continuous=None)
+        if str(self._device).startswith("cuda"):
+            # status words of the kernels with bounded waits: copied now, looked at after the next step was issued
+            if getattr(self, "_status_poller", None) is None:
+                from ..ops.status import StatusPoller
+
+                self._status_poller = StatusPoller(self._device)
+            self._status_poller.step(where="train step %i" % (self.global_train_step - 1))
         if not summed:
             return {}
         if read_losses == "deferred" and not summed[0].is_cuda:
-            prev = self.flush_losses()
+            prev = self.flush_losses(_final=False)
             self._pending_losses = (names, torch.stack(summed).clone(), None)
             return prev
         if read_losses == "deferred":
@@ -645,7 +674,7 @@ class Engine(EngineBase):
             host, ev = slot
             host[: len(names)].copy_(torch.stack(summed), non_blocking=True)
             ev.record()
-            prev = self.flush_losses()  # waits for the step before this one; this step's kernels are queued already
+            prev = self.flush_losses(_final=False)  # waits for the step before this one; this step's kernels are queued already
             self._pending_losses = (names, host, ev)
             return prev
         if read_losses:

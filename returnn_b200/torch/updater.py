@@ -152,6 +152,20 @@ class Updater:
         """flat arena of the distributed context (so that optimizer and reducer share one)"""
         self._arena = arena
 
+    def zero_grad(self):
+        """
+        Clear the gradients before a step. While a flat arena is active (distributed reduction or the arena optimizer), the
+        gradients must stay views of the arena for EVERY optimizer class: the bucket reductions work on arena slices, so a
+        ``zero_grad(set_to_none=True)`` of a torch optimizer, after which autograd allocates fresh gradient tensors, would
+        detach them from what is being reduced. One memset of the arena, then every ``param.grad`` is re-pointed to its view.
+        """
+        arena = self._arena if self._arena is not None else getattr(self.optimizer, "arena", None)
+        if arena is not None:
+            arena.zero_grad()
+            arena.relink_grads()
+            return
+        self.optimizer.zero_grad()
+
     def set_precomputed_grad_norm_sq(self, value: Optional[torch.Tensor]):
         """squared global grad norm delivered by the fused gradient reduction (saves the extra pass)"""
         self._precomputed_grad_norm_sq = value
@@ -196,7 +210,7 @@ class Updater:
                     float(grad_norm), self._current_train_step, self._num_consec_invalid_gradient_steps), file=log.v2)
                 if self._num_consec_invalid_gradient_steps > self._num_allowed_consec_invalid_gradient_steps:
                     raise RuntimeError("Got %i invalid gradients in succession, abort training" % self._num_consec_invalid_gradient_steps)
-                self.optimizer.zero_grad()
+                self.zero_grad()
                 return grad_norm
             self._num_consec_invalid_gradient_steps = 0
         if grad_scaler is not None:

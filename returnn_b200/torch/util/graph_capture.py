@@ -17,6 +17,11 @@ Options (``torch_cuda_graph`` dict): ``batch_size_bound`` (max. sequences per ba
 length}``), ``warmup_steps`` (default 2), ``capture_optimizer`` (default False: the optimizer runs eagerly on the static
 gradients after the replay; True needs a capturable optimizer, e.g. the arena AdamW whose step counter is a device tensor).
 
+With ``torch_distributed`` the captured part is forward + backward; the gradient reduction runs between the replay and the
+eager optimizer step, which needs ``reduce_type="grad_explicit"`` (one flat reduction after backward) or ``"param"``:
+the bucket hooks of ``"grad"`` cannot fire from a replayed graph, and ``capture_optimizer`` would put the update before the
+reduction. Both combinations are rejected when the engine is set up.
+
 The flagship models do not need this: their step is issued by the native encoder executor (one C call per
 forward / backward range), which removes the Python between the kernels without the static-shape restriction.
 
@@ -70,6 +75,13 @@ class GraphCapturedTrainStep:
         self.warmup_steps = int(opts.get("warmup_steps", 2))
         self.capture_optimizer = bool(opts.get("capture_optimizer", False))
         opts.assert_all_read()
+        dist = getattr(engine, "_torch_distributed_ctx", None)
+        if dist is not None and dist.size() > 1:
+            if dist.reduce_type == "grad":
+                raise ValueError('torch_cuda_graph with torch_distributed needs reduce_type "grad_explicit" or "param": the bucket '
+                                 'hooks of "grad" do not fire from a replayed graph')
+            if self.capture_optimizer and dist.reduce_type != "param":
+                raise ValueError("torch_cuda_graph: capture_optimizer=True would run the update before the gradient reduction")
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
         self._len_bufs: Dict[str, torch.Tensor] = {}
@@ -77,6 +89,7 @@ class GraphCapturedTrainStep:
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._n_eager = 0
         self._loss_names: List[str] = []
+        self._score_keys: set = set()
         self._loss_buf: Optional[torch.Tensor] = None  # [2 * n_losses]: summed losses, then inverse norm factors
         self._host_buf: Optional[torch.Tensor] = None
         self._stream = torch.cuda.Stream(device=device)
@@ -160,6 +173,7 @@ class GraphCapturedTrainStep:
         names = list(ctx.losses.keys())
         if not self._loss_names:
             self._loss_names = names
+            self._score_keys = set(k for k, v in ctx.losses.items() if not v.as_error)
             self._loss_buf = torch.zeros(2 * len(names), dtype=torch.float32, device=self.device)
             self._host_buf = torch.zeros(2 * len(names), dtype=torch.float32).pin_memory()
         assert names == self._loss_names, "torch_cuda_graph: the set of losses changed between steps"
@@ -180,6 +194,25 @@ class GraphCapturedTrainStep:
         """
         :param extern_data_raw: the collated batch (host tensors)
         :return: summed losses, inverse norm factors (host numbers), as the eager step of the engine collects them
+        """
+        res = self.run_train_step_ex(extern_data_raw)
+        n = len(res["names"])
+        losses = NumbersDict({name: res["vals"][i] for i, name in enumerate(res["names"])})
+        inv = NumbersDict({name: res["vals"][n + i] for i, name in enumerate(res["names"])})
+        if self.engine._updater._log_grad_norm and res["grad_norm"] is not None:
+            losses["grad_norm:p2"] = float(res["grad_norm"])
+            inv["grad_norm:p2"] = 1.0
+        return losses, inv
+
+    def run_train_step_ex(self, extern_data_raw: Dict[str, Any], *, dist=None, epoch_step_idx: int = 0) -> Dict[str, Any]:
+        """
+        One step: copy in, replay (or warm-up / capture), gradient reduction of the distributed context, optimizer, loss read.
+
+        :param extern_data_raw: the collated batch (host tensors)
+        :param dist: the engine's distributed context or None
+        :param epoch_step_idx: step within the epoch (for the parameter-averaging schedule)
+        :return: ``names`` (loss names), ``vals`` (host floats: the summed losses, then the inverse norm factors),
+            ``score_keys`` (names that are scores, not errors), ``grad_norm`` (device scalar or None)
         """
         eng = self.engine
         if self._extern_data is None:
@@ -219,16 +252,16 @@ class GraphCapturedTrainStep:
             _graphs.append(graph)
             graph.replay()
         if not self.capture_optimizer:
+            if dist is not None:
+                norm_sq = dist.maybe_reduce_grads(eng._pt_model)
+                if norm_sq is not None:
+                    eng._updater.set_precomputed_grad_norm_sq(norm_sq)
+                dist.before_param_update(epoch_step_idx=epoch_step_idx)
             grad_norm = eng._updater.step()
         else:
             grad_norm = None
+        if dist is not None:
+            dist.step_after_param_update(module=eng._pt_model, epoch_step_idx=epoch_step_idx)
         self._host_buf.copy_(self._loss_buf, non_blocking=True)
         torch.cuda.current_stream().synchronize()
-        vals = self._host_buf.tolist()
-        n = len(self._loss_names)
-        losses = NumbersDict({name: vals[i] for i, name in enumerate(self._loss_names)})
-        inv = NumbersDict({name: vals[n + i] for i, name in enumerate(self._loss_names)})
-        if eng._updater._log_grad_norm and grad_norm is not None:
-            losses["grad_norm:p2"] = float(grad_norm)
-            inv["grad_norm:p2"] = 1.0
-        return losses, inv
+        return dict(names=list(self._loss_names), vals=self._host_buf.tolist(), score_keys=set(self._score_keys), grad_norm=grad_norm)

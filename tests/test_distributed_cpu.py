@@ -89,6 +89,56 @@ dist.destroy_process_group()
     assert all("OK" in o for _, o in outs)
 
 
+@pytest.mark.parametrize("zero_mode", ["updater", "set_to_none"])
+def test_grad_reduction_with_torch_sgd_over_several_steps(tmp_path, zero_mode):
+    """
+    A plain torch optimizer (no arena optimizer): after every step the gradients each rank applies must be the average over the
+    ranks, also when the gradients were set to None before backward, so that autograd allocates tensors outside the arena.
+    """
+    outs = _launch(_COMMON + """
+from returnn_b200.torch.updater import Updater
+zero_mode = %r
+ctx = make_ctx({"reduce_type": "grad", "bucket_cap_mb": 0})
+rank, world = ctx.rank(), ctx.size()
+net = model()
+ctx.setup_grad_reduction(net)
+cfg = Config({"optimizer": {"class": "sgd"}, "learning_rate": 0.1})
+upd = Updater(config=cfg, network=net, device=torch.device("cpu"), initial_learning_rate=0.1)
+upd.set_arena(ctx.arena)
+upd.create_optimizer()
+assert not getattr(upd.get_optimizer(), "is_fused_arena", False)
+# the same training done by hand: every rank's data on one model, gradient = average over the ranks
+ref = model()
+for step in range(3):
+    if zero_mode == "updater":
+        upd.zero_grad()
+    else:
+        upd.get_optimizer().zero_grad(set_to_none=True)
+    torch.manual_seed(1000 * step + rank)
+    x = torch.randn(5, 8)
+    ctx.prepare_backward(sync=True)
+    net(x).square().sum().backward()
+    ctx.maybe_reduce_grads(net)
+    mine = torch.cat([p.grad.reshape(-1) for p in net.parameters()]).clone()
+    upd.step()
+    for p in ref.parameters():
+        p.grad = None
+    for r in range(world):
+        torch.manual_seed(1000 * step + r)
+        (ref(torch.randn(5, 8)).square().sum() / world).backward()
+    want = torch.cat([p.grad.reshape(-1) for p in ref.parameters()])
+    assert torch.allclose(mine, want, atol=1e-5), (step, float((mine - want).abs().max()))
+    with torch.no_grad():
+        for p in ref.parameters():
+            p.sub_(0.1 * p.grad)
+    for p, q in zip(net.parameters(), ref.parameters()):
+        assert torch.allclose(p, q, atol=1e-5), (step, float((p - q).abs().max()))
+print("OK", rank)
+dist.destroy_process_group()
+""" % zero_mode, tmp_path)
+    assert all("OK" in o for _, o in outs)
+
+
 def test_param_averaging(tmp_path):
     outs = _launch(_COMMON + """
 ctx = make_ctx({"reduce_type": "param", "param_sync_step": 2})

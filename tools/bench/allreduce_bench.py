@@ -1,8 +1,8 @@
 """
-Self-test and timing of the fused NVLink all-reduce on the GPUs of one node:
+Value check and timing of the fused NVLink all-reduce on the GPUs of one node:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29511 \\
-        -m returnn_b200.parallel.selftest_allreduce [--elems 100000000] [--no-multimem]
+        tools/bench/allreduce_bench.py [--elems 100000000] [--no-multimem]
 
 Every rank fills a gradient arena with values that depend on its rank, reduces it bucket by bucket with the fused
 kernel, and checks the averaged values and the squared global norm against the closed form; then it times the fused
@@ -11,6 +11,10 @@ Rank 0 prints one JSON line.
 """
 
 from __future__ import annotations
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 import argparse
 import json
 import os

@@ -2,7 +2,7 @@
 Micro-benchmark of the tcgen05 GEMM on the linear-layer shapes of the flagship Conformer (forward, data gradient,
 weight gradient), against ``torch.matmul`` (cuBLAS) on the same operands.
 
-``python -m returnn_b200.ops.gemm_bench [--rows N] [--iters K] [--only NAME]``
+``python tools/bench/gemm_bench.py [--rows N] [--iters K] [--only NAME]``
 
 Timing: CUDA events on the launching stream, 5 warm-up calls, then ``iters`` calls over a ring of operand sets that
 together exceed the L2 capacity, so no call finds its operands cached by the previous one. A spin kernel ahead of the
@@ -10,6 +10,10 @@ first event keeps the device busy until the host has queued every launch, so the
 """
 
 from __future__ import annotations
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 import argparse
 import json
 import torch
@@ -31,7 +35,7 @@ def _time(fn, n_sets: int, iters: int) -> float:
 
 
 def main():
-    from . import gemm as G
+    from returnn_b200.ops import gemm as G
 
     ap = argparse.ArgumentParser()
     ap.add_argument("--rows", type=int, default=6656)

@@ -1,7 +1,7 @@
 """
 Micro-benchmarks of the non-GEMM kernels at the shapes of the flagship Conformer step (packed rows n ~ 6.7k, D = 512):
 
-    python -m returnn_b200.ops.kernel_bench [--only NAME] [--iters K] [--rows N]
+    python tools/bench/kernel_bench.py [--only NAME] [--iters K] [--rows N]
 
 For every op: device time of forward and of forward+backward (CUDA events around ``iters`` calls, a spin kernel in front so
 that the host has queued everything before the first event), the algorithmic bytes it has to move, and the achieved
@@ -11,6 +11,10 @@ for ``ncu`` captures: ``--only NAME --iters 2``).
 """
 
 from __future__ import annotations
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 import argparse
 import json
 import os
@@ -49,8 +53,8 @@ def main():
     n, D, F = args.rows, 512, 2048
     peak = _peak_gbs()
     bf = torch.bfloat16
-    from . import layer_norm as ln, elementwise as ew, conv_module as cm, ctc as ctc_op, attention_packed as att, softmax_ce as ce, logmel, seq_ops
-    from ..models.packing import PackInfo
+    from returnn_b200.ops import layer_norm as ln, elementwise as ew, conv_module as cm, ctc as ctc_op, attention_packed as att, softmax_ce as ce, logmel, seq_ops
+    from returnn_b200.models.packing import PackInfo
 
     torch.manual_seed(0)
     lens = torch.randint(60, 334, (64,))
@@ -89,8 +93,8 @@ def main():
         x = torch.randn(n, F, device=dev, dtype=bf)
         report("dropout", _time(lambda: ew.dropout(x, 0.1), args.iters), None, 2 * n * F * 2, 0)
     if want("conv_module"):
-        from ..tensor import Dim
-        from .. import frontend as rf
+        from returnn_b200.tensor import Dim
+        from returnn_b200 import frontend as rf
 
         bn = rf.BatchNorm(Dim(D, name="c"), use_mask=True)
         for p in bn.parameters():
@@ -154,7 +158,7 @@ def main():
         fwd = lambda: seq_ops.beam_topk(logits, prev, eos=0, k=12)
         report("beam_topk (64 x 12 x 10001)", _time(fwd, args.iters), None, 64 * 12 * 10001 * 2 * 2, 0)
     import ctypes
-    from . import _lib
+    from returnn_b200.ops import _lib
 
     vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
     if want("layer_norm_bwd_acc"):
@@ -208,7 +212,7 @@ def main():
         report("att_softmax fwd (bf16 scores, dropout)", t_f, None, valid * 2 * 4, 0)
         report("att_softmax bwd (bf16 scores, dropout)", t_b, None, valid * 2 * 4, 0)
     if want("lstm"):
-        from . import lstm_native
+        from returnn_b200.ops import lstm_native
 
         for (T, Bl) in ((400, 48), (1600, 12)):
             Hl, I = 1024, 2048
@@ -228,7 +232,7 @@ def main():
             w2 = [(torch.randn(4 * Hl, I, device=dev) * 0.02).requires_grad_(True), (torch.randn(4 * Hl, Hl, device=dev) * 0.02).requires_grad_(True),
                   torch.zeros(4 * Hl, device=dev, requires_grad=True)]
             if lstm_native.blstm_supported(x, w_rec, w2[1]):
-                from . import lstm as lstm_ops
+                from returnn_b200.ops import lstm as lstm_ops
 
                 def pair():
                     (yf, _, _), (yb, _, _) = lstm_ops.blstm(x, ll, (w_ff, w_rec, bias), tuple(w2), h0, c0, h0, c0)
@@ -249,7 +253,7 @@ def main():
                 report("blstm layer T=%i B=%i H=1024, both directions in one kernel" % (T, Bl), tp_f, tp_fb, 2 * T * Bl * (I + 5 * Hl) * 2,
                        2 * T * Bl * (I + 5 * Hl) * 2 * 3, {"two_launches_fwd_ms": round(ts_f * 1e3, 3), "two_launches_fwd_bwd_ms": round(ts_fb * 1e3, 3),
                                                             "speedup_fwd": round(ts_f / tp_f, 2), "speedup_fwd_bwd": round(ts_fb / tp_fb, 2)})
-    from . import gemm as G
+    from returnn_b200.ops import gemm as G
 
     G.check_status()
 

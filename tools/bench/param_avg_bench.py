@@ -1,8 +1,8 @@
 """
-Self-test of the fused AdamW + parameter-averaging kernel on the GPUs of one node:
+Value check and timing of the fused AdamW + parameter-averaging kernel on the GPUs of one node:
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port 29521 \\
-        -m returnn_b200.parallel.selftest_param_avg [--elems 50000000]
+        tools/bench/param_avg_bench.py [--elems 50000000]
 
 Every rank starts from the same weights, takes one AdamW step on its own (rank-dependent) gradients inside the fused kernel
 and receives the average. The result is compared with the same computation done with torch ops + ``dist.all_reduce``;
@@ -10,6 +10,10 @@ both are timed (CUDA events, max over ranks). Rank 0 prints one JSON line.
 """
 
 from __future__ import annotations
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
 import argparse
 import json
 import os
