@@ -6,12 +6,16 @@
 //
 // Roles per CTA: warp 0 = TMA producer (loads with .cta_group::2 and no multicast; they complete on the *leader's* full barrier,
 // which is armed for the bytes of both CTAs), warp 1 = TMEM allocation, and in the leader CTA (cluster rank 0) the MMA issuer,
-// warps 2-5 = epilogue of the CTA's own 128 accumulator rows (tensor memory is per SM). tcgen05.commit with a cluster
+// warps 2-17 = epilogue of the CTA's own 128 accumulator rows (tensor memory is per SM): every lane owns one row, reads 64 columns of
+// it from tensor memory, and the results leave through a swizzled box in shared memory and one bulk tensor store per warp (bulk
+// reduce-add for the accumulating fp32 outputs of the weight gradients); see epilogue_rows_tma. Outputs that a tensor map cannot
+// describe (unaligned pitch or base) take the per-lane st.global path. tcgen05.commit with a cluster
 // multicast mask releases a ring stage / publishes an accumulator in both CTAs at once; the epilogue warps of both CTAs arrive on
 // the leader's "accumulator free" barrier. All waits are bounded; a CTA never exits before its peer (cluster barrier at the end),
 // because the leader's MMAs read the peer's shared memory.
 #include "gemm_epilogue.cuh"
 #include <cstdlib>
+#include <cstring>
 
 using namespace rbt;
 using namespace rbg;
@@ -24,9 +28,10 @@ constexpr int kThreads = kGemmThreads;
 constexpr int kTileBytesA = 128 * BK * 2;        // 16 KB: this CTA's rows of A
 constexpr int kTileBytesB = (BN / 2) * BK * 2;   // 16 KB: this CTA's half of B
 constexpr int kStageBytes = kTileBytesA + kTileBytesB;
-constexpr int kStages = 6;
-constexpr int kRingBytes = kStages * kStageBytes;  // 192 KB
-constexpr int kStagingBytes = kEpilogueWarps * kStagingBytesPerWarp;
+constexpr int kStages = 5;
+constexpr int kRingBytes = kStages * kStageBytes;  // 160 KB
+constexpr int kStagingBytes = kEpilogueWarps * kStoreBoxBytesPerWarp;  // 64 KB: one 4 KB store box per epilogue warp (1024-byte aligned)
+static_assert(kStoreBoxBytesPerWarp >= kStagingBytesPerWarp, "the st.global path stages in the same area");
 constexpr int kSmemBytes = kRingBytes + kStagingBytes + 256 + 1024;
 constexpr uint32_t kTmemCols = 2 * BN;
 
@@ -70,7 +75,8 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 
 template <bool FULL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
-gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const Params p) {
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_c,
+                 const __grid_constant__ CUtensorMap tm_c2, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   float* staging = reinterpret_cast<float*>(smem + kRingBytes);
@@ -198,7 +204,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else {
     // ---------------- epilogue: this CTA's 128 rows ----------------
     const int q = warp & 3;
-    float* stg = staging + (warp - 2) * (kStagingBytesPerWarp / 4);
+    uint8_t* box = reinterpret_cast<uint8_t*>(staging) + (warp - 2) * kStoreBoxBytesPerWarp;
+    float* stg = reinterpret_cast<float*>(box);
     uint32_t t_local = 0;
     for (int u = pair; u < p.units; u += n_pairs) {
       const Unit w = decode_unit<BM, BN>(p, u);
@@ -215,9 +222,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
       const int part = (warp - 2) >> 2;  // four warps per lane quarter, each with a quarter of the columns
-      epilogue_columns<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), (part + 1) * (BN / 4), stg, lane, q, [&]() { mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0)); });
+      auto release = [&]() { mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0)); };
+      if (p.tma_store) epilogue_rows_tma<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), box, &tm_c, &tm_c2, lane, q, release);
+      else epilogue_columns<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), (part + 1) * (BN / 4), stg, lane, q, release);
       ++t_local;
     }
+    // the bulk stores read this CTA's shared memory: they must have completed before the CTA exits
+    if (p.tma_store && lane == 0) tma_store_wait_all();
   }
 
   // ---------------- teardown ----------------
@@ -288,8 +299,28 @@ int rb_gemm_pair(const RbGemm& g, cudaStream_t stream) {
   p.vec_ok = (g.ldc % 8 == 0) && al16(g.c) && al16(g.c2) && al16(g.resid) && al16(g.dact_z);
   p.bias_vec = g.bias != nullptr && !g.bias_bf16 && al16(g.bias);
   const bool full = g.dact_z != nullptr || g.drop_p > 0.f || g.resid != nullptr;
-  CUtensorMap tm_a, tm_b;
+  static int tma_store_enabled = -1;
+  if (tma_store_enabled < 0) {
+    const char* e = getenv("RETURNN_B200_GEMM_TMA_STORE");
+    tma_store_enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  // bulk tensor stores need what a tensor map needs: 16-byte aligned base, row pitch a multiple of 16 bytes
+  p.tma_store = tma_store_enabled && p.vec_ok && g.c != nullptr && (g.out_fp32 ? true : (g.ldc % 8 == 0));
+  CUtensorMap tm_a, tm_b, tm_c, tm_c2;
+  memset(&tm_c, 0, sizeof(tm_c));
+  memset(&tm_c2, 0, sizeof(tm_c2));
   int st;
+  if (p.tma_store) {
+    // boxes of 32 rows x 128 bytes: 64 bf16 or 32 fp32 columns; with a second output, 32 rows x 64 bytes (32 bf16 columns) each
+    if (g.c2) {
+      st = make_map(&tm_c, g.c, g.n, g.m, g.ldc, 32, 32, false, true);
+      if (st) return st;
+      st = make_map(&tm_c2, g.c2, g.n, g.m, g.ldc, 32, 32, false, true);
+    } else {
+      st = make_map(&tm_c, g.c, g.n, g.m, g.ldc, g.out_fp32 ? 32 : 64, 32, g.out_fp32 != 0);
+    }
+    if (st) return st;
+  }
   const long long a_rows = g.a_mn_major ? g.k : g.m, a_cols = g.a_mn_major ? g.m : g.k;
   const long long b_rows = g.b_mn_major ? g.k : g.n, b_cols = g.b_mn_major ? g.n : g.k;
   st = g.a_mn_major ? make_map(&tm_a, g.a, a_cols, a_rows, g.lda, 64, BK) : make_map(&tm_a, g.a, a_cols, a_rows, g.lda, BK, 128);
@@ -297,7 +328,7 @@ int rb_gemm_pair(const RbGemm& g, cudaStream_t stream) {
   st = g.b_mn_major ? make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, 64, BK) : make_map(&tm_b, g.b, b_cols, b_rows, g.ldb, BK, BN / 2);
   if (st) return st;
   int pairs = p.units < pairs_max ? p.units : pairs_max;
-  if (full) rb_launch_pdl(gemm_pair_kernel<true>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
-  else rb_launch_pdl(gemm_pair_kernel<false>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, p);
+  if (full) rb_launch_pdl(gemm_pair_kernel<true>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, tm_c, tm_c2, p);
+  else rb_launch_pdl(gemm_pair_kernel<false>, dim3(2 * pairs), dim3(kThreads), kSmemBytes, stream, tm_a, tm_b, tm_c, tm_c2, p);
   return rb_check_launch("gemm_pair");
 }

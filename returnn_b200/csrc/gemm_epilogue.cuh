@@ -14,6 +14,7 @@ struct Params {
   int tiles_m, tiles_n, split, kb_per_split, num_kb, units;
   int vec_ok;    // all epilogue pointers 16-byte aligned and ldc % 8 == 0
   int bias_vec;  // fp32 bias, 16-byte aligned: read as two float4
+  int tma_store; // the output leaves through shared memory and bulk tensor stores (tensor maps of c / c2 passed to the kernel)
 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -244,8 +245,210 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, const Unit& w,
   }
 }
 
+// ---- row-owner epilogue with bulk tensor stores ---------------------------------------------------------------------------------
+// Every lane owns ONE accumulator row (TMEM lane = row) and reads W consecutive columns of it with one or two tcgen05.ld.x32, so
+// the accumulator buffer is handed back to the MMA issuer as soon as the values are in registers. Bias, activation, activation
+// gradient, dropout and residual are computed on groups of 8 consecutive columns (the same grouping and dropout counters as
+// epilogue_group). The results go to this warp's 4 KB box in shared memory in the swizzled layout of the output tensor map (rows
+// of 128 bytes: 64 bf16 or 32 fp32 columns; 16-byte chunk j of row r sits at chunk position j ^ (r & 7), which also keeps the
+// 32 lanes' 16-byte writes on distinct banks), and ONE bulk tensor store (or bulk reduce-add for accumulate != 0) per box moves
+// them to global memory: full-line writes, no st.global from the warps, rows and columns outside the matrix clipped by the TMA
+// unit. The next box is written only after the previous store has finished reading shared memory (wait_group.read).
+
+__device__ __forceinline__ float silu_fast(float x) { return x * (0.5f + 0.5f * tanh_approx(0.5f * x)); }
+
+// v[8] (accumulator values of columns col .. col+7 of `row`) -> final values in v, pre-activation in pre. Loads of dact_z / resid
+// only for valid elements. Same order of operations as epilogue_group.
+template <bool FULL>
+__device__ __forceinline__ void epilogue_math8(const Params& p, int row, int col, bool row_ok, int n_extent, float* v, float* pre) {
+  const RbGemm& g = p.g;
+  const int nvalid = row_ok ? max(0, min(8, n_extent - col)) : 0;
+  const size_t off = (size_t)row * g.ldc + col;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] *= g.alpha;
+  if (g.bias && nvalid == 8) {
+    if (p.bias_vec) {
+      const float4 b0 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.bias) + col));
+      const float4 b1 = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.bias) + col) + 1);
+      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        v[i] += g.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g.bias)[col + i])
+                            : __ldg(reinterpret_cast<const float*>(g.bias) + col + i);
+      }
+    }
+  } else if (g.bias) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (i < nvalid) {
+        v[i] += g.bias_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(g.bias)[col + i])
+                            : __ldg(reinterpret_cast<const float*>(g.bias) + col + i);
+      }
+    }
+  }
+  if (FULL && g.dact_z) {
+    float z[8];
+    load8_bf16(g.dact_z, off, nvalid == 8, nvalid, z);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], g.act);
+  } else if (g.act) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      pre[i] = v[i];
+      v[i] = g.act == 2 ? silu_fast(v[i]) : apply_act(v[i], g.act);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) pre[i] = v[i];
+  }
+  if (FULL && g.drop_p > 0.f) {
+    const uint64_t sd = (uint64_t)g.seed[0];
+    const uint64_t c = (uint64_t)g.offset[0] + g.drop_site + (uint64_t)off;
+    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
+    uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
+    uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
+    const uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    const float scale = 1.f / (1.f - g.drop_p);
+    const uint32_t thresh = (uint32_t)(g.drop_p * 4294967296.0);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = r[i] >= thresh ? v[i] * scale : 0.f;
+  }
+  if (FULL && g.resid) {
+    float rs[8];
+    load8_bf16(g.resid, off, nvalid == 8, nvalid, rs);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = rs[i] + g.res_scale * v[i];
+  }
+}
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* v) {
+  uint4 u;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+  return u;
+}
+
+// One warp's share of a tile: rows m0 + q*32 .. +31 (lane = row), accumulator columns [c_begin, c_begin + 64) at TMEM address
+// t_addr (lane quarter already applied). box: this warp's 4 KB of shared memory, 1024-byte aligned. tm_c / tm_c2: tensor maps of the
+// outputs with boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns; with a second output c2: 32 rows x 64 bytes, 64-byte swizzle). `arrive` hands the accumulator buffer back (lane 0).
+template <bool FULL, typename Arrive>
+__device__ __forceinline__ void epilogue_rows_tma(const Params& p, const Unit& w, int m0, int n0, uint32_t t_addr, int c_begin, uint8_t* box,
+                                                  const CUtensorMap* tm_c, const CUtensorMap* tm_c2, int lane, int q, Arrive arrive) {
+  const RbGemm& g = p.g;
+  const int row0 = m0 + q * 32;
+  const int row = row0 + lane;
+  const bool row_ok = row < w.M;
+  const int col0 = n0 + c_begin;
+  auto release = [&]() {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) arrive();
+  };
+  if (row0 >= w.M || col0 >= w.N) {  // nothing of this warp's box lies inside the matrix (warp-uniform): nothing to read
+    release();
+    return;
+  }
+  // Plain epilogue: all 64 columns are fetched at once and the accumulator is released before the arithmetic starts.
+  // Full epilogue (activation gradient, dropout, residual: more live values per group): the second half is fetched after the
+  // first half has been processed, which keeps the kernel free of register spills at 96 registers per thread.
+  uint32_t r[64];
+  tmem_ld32(t_addr + (uint32_t)c_begin, r);
+  if (!FULL) tmem_ld32(t_addr + (uint32_t)c_begin + 32u, r + 32);
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+  if (!FULL) release();
+  auto second_half = [&]() {
+    if (FULL) {
+      tmem_ld32(t_addr + (uint32_t)c_begin + 32u, r + 32);
+      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+      release();
+    }
+  };
+  uint8_t* my_row = box + lane * 128;
+  const int sw = lane & 7;
+  if (g.out_fp32) {
+    // two boxes of 32 fp32 columns
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h == 1) second_half();
+      if (col0 + 32 * h >= w.N) continue;
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        float v[8], pre[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[32 * h + 8 * gi + i]);
+        epilogue_math8<FULL>(p, row, col0 + 32 * h + 8 * gi, row_ok, w.N, v, pre);
+        *reinterpret_cast<float4*>(my_row + (((2 * gi) ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(my_row + (((2 * gi + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if (g.accumulate) tma_reduce_add_2d(tm_c, col0 + 32 * h, row0, box);
+        else tma_store_2d(tm_c, col0 + 32 * h, row0, box);
+        tma_store_commit();
+      }
+    }
+    return;
+  }
+  if (g.c2) {
+    // The pre-activation goes to c, the final value to c2. The warp's buffer is split into two boxes of 32 rows x 64 bytes (32 bf16
+    // columns, 64-byte swizzle: chunk j of row r at position j ^ ((r >> 1) & 3)); both stores of a round are in flight together.
+    uint8_t* row_pre = box + lane * 64;
+    uint8_t* row_fin = box + 2048 + lane * 64;
+    const int sw64 = (lane >> 1) & 3;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      if (h == 1) second_half();
+      if (col0 + 32 * h >= w.N) continue;
+      if (lane == 0) tma_store_wait_read();
+      __syncwarp();
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        float v[8], pre[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[32 * h + 8 * gi + i]);
+        epilogue_math8<FULL>(p, row, col0 + 32 * h + 8 * gi, row_ok, w.N, v, pre);
+        *reinterpret_cast<uint4*>(row_pre + ((gi ^ sw64) << 4)) = pack8_bf16(pre);
+        *reinterpret_cast<uint4*>(row_fin + ((gi ^ sw64) << 4)) = pack8_bf16(v);
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        tma_store_2d(tm_c, col0 + 32 * h, row0, box);
+        tma_store_2d(tm_c2, col0 + 32 * h, row0, box + 2048);
+        tma_store_commit();
+      }
+    }
+    return;
+  }
+  // the store of the previous tile has long finished reading the box by the time the next accumulator is ready
+  if (lane == 0) tma_store_wait_read();
+  __syncwarp();
+#pragma unroll
+  for (int gi = 0; gi < 8; ++gi) {
+    if (gi == 4) second_half();
+    float v[8], pre[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * gi + i]);
+    epilogue_math8<FULL>(p, row, col0 + 8 * gi, row_ok, w.N, v, pre);
+    *reinterpret_cast<uint4*>(my_row + ((gi ^ sw) << 4)) = pack8_bf16(v);
+  }
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(tm_c, col0, row0, box);
+    tma_store_commit();
+  }
+}
+
 constexpr int kEpilogueWarps = 16;                        // four per TMEM lane quarter: each takes a quarter of the tile's columns
 constexpr int kGemmThreads = 64 + kEpilogueWarps * 32;    // + TMA producer warp + MMA warp
 constexpr int kStagingBytesPerWarp = 32 * 16 * 4;
+constexpr int kStoreBoxBytesPerWarp = 32 * 128;           // row-owner epilogue: one box of 32 rows x 128 bytes per warp
 
 }  // namespace rbg

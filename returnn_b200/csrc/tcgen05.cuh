@@ -89,6 +89,34 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 
+// ---- bulk tensor stores (shared memory -> global memory through a tensor map) ----------------------------------------------------
+// The box in shared memory has the layout that the map's swizzle mode prescribes. x (the inner coordinate) times the element size
+// must be a multiple of 16 bytes and neither coordinate may be negative; parts of the box outside the tensor are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+// element-wise add of the box into global memory (performed at the L2, so concurrent adds to the same element are safe)
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int x, int y, const void* smem_src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// the bulk stores of this thread committed so far have finished READING shared memory (the buffer may be overwritten)
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// ... have completed entirely
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// make this thread's shared-memory writes visible to the asynchronous proxy (the TMA engine) before a bulk store is issued
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 __device__ __forceinline__ float apply_act(float x, int act) {
   if (act == 1) return fmaxf(x, 0.f);
   if (act == 2) return x / (1.f + __expf(-x));
@@ -116,19 +144,21 @@ inline EncodeTiledFn get_encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch in elements
-inline int make_map(CUtensorMap* map, const void* base, long long inner, long long outer, long long pitch_elems, int box_inner, int box_outer) {
+// 2-D tensor map: inner (contiguous) extent `inner`, outer extent `outer`, row pitch in elements; bf16 elements with the 128-byte
+// swizzle unless said otherwise (fp32 = true: 4-byte elements; swizzle64 = true: boxes whose rows are 64 bytes long)
+inline int make_map(CUtensorMap* map, const void* base, long long inner, long long outer, long long pitch_elems, int box_inner, int box_outer,
+                    bool fp32 = false, bool swizzle64 = false) {
   EncodeTiledFn fn = get_encode_fn();
   if (!fn) {
     rb_set_error("gemm: cuTensorMapEncodeTiled not available");
     return RB_ERR_UNSUPPORTED;
   }
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 2};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     rb_set_error("gemm: cuTensorMapEncodeTiled failed (%d): base %p inner %lld outer %lld pitch %lld", (int)r, base, inner, outer, pitch_elems);

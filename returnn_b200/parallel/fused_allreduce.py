@@ -85,7 +85,7 @@ class FusedAllReduce:
 
     @property
     def mode(self) -> str:
-        """"fused-multimem" (reduction inside the NVSwitch) or "fused-peer" (peer loads and stores)"""
+        """``"fused-multimem"`` (reduction inside the NVSwitch) or ``"fused-peer"`` (peer loads and stores)"""
         return "fused-multimem" if self.multicast_ptr else "fused-peer"
 
     def reduce_bucket(self, b: int, lo: int, hi: int):
@@ -186,7 +186,7 @@ class FusedParamAverager:
 
     @property
     def mode(self) -> str:
-        """"fused-multimem" or "fused-peer""""
+        """``"fused-multimem"`` or ``"fused-peer"``"""
         return "fused-multimem" if self.multicast_ptr else "fused-peer"
 
     def check_status(self):

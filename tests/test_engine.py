@@ -188,3 +188,22 @@ def _deferred_losses_case(device):
     assert eng.flush_losses() == {}
     numpy.testing.assert_allclose(got, immediate, rtol=1e-6 if device == "cpu" else 1e-3)
     assert immediate[-1] < immediate[0] or len(set(immediate)) > 1
+
+
+def test_prefetch_thread_gives_the_same_training(tmp_path):
+    """the background prefetch of batches (default on CUDA) does not change what is trained: same final scores as without it"""
+    cfg = os.path.join(_ROOT, "demos", "demo-rf.config")
+    scores = []
+    for flag in ("False", "True"):
+        lr_file = str(tmp_path / ("lr_%s.txt" % flag))
+        _run([cfg, "++model", str(tmp_path / ("model_%s" % flag)), "++learning_rate_file", lr_file, "++device", "cpu", "++log_verbosity", "3",
+              "++num_epochs", "1", "++torch_dataloader_prefetch_thread", flag, "++train", "{'class': 'Task12AXDataset', 'num_seqs': 120}",
+              "++dev", "{'class': 'Task12AXDataset', 'num_seqs': 30, 'fixed_random_seed': 1}"], str(tmp_path))
+        from returnn_b200.learning_rate_control import load_learning_rate_control_from_config
+        from returnn_b200.config import Config
+
+        lrc = load_learning_rate_control_from_config(Config({"learning_rate_file": lr_file, "learning_rate": 0.01}))
+        scores.append(dict(lrc.epoch_data[1].error))
+    assert scores[0].keys() == scores[1].keys() and scores[0]
+    for k in scores[0]:
+        assert abs(scores[0][k] - scores[1][k]) < 1e-6, (k, scores)
