@@ -146,6 +146,35 @@ def _collate(batch, pin: bool):
     return raw
 
 
+CONFIG_MODEL = "conformer-ctc 12x512 h8 ff2048 conv32 sub6 vocab10k"
+
+
+def common_config(world: int):
+    """the ``config`` entry of the JSON line: identical in both arms (what is specific to an arm goes to ``notes``)"""
+    return {
+        "model": CONFIG_MODEL, "global_batch": "%i padded frames per GPU x %i" % (BATCH_FRAMES, world),
+        "seq_len": "300-2000 frames (10 ms)", "parallelism": "dp%i" % world, "optimizer": "adamw clip5",
+        "l2": "no flush needed: the working set of a step (fp32 parameters, gradients and Adam moments 1.3 GB, saved activations 2.3 GB) is "
+              "far larger than the 126 MB L2, and every step gets a distinct batch",
+        "batches": "sequence lengths drawn from one seed on every rank (equal work per rank), feature and label values per rank"}
+
+
+def balanced_rank_batches(*, rank: int, world: int, n_steps: int, frames_budget: int = BATCH_FRAMES):
+    """
+    Batches of a data-parallel job whose ranks all read the SAME sequence stream: every group of ``world`` consecutive greedy
+    batches is re-divided so that the ranks get near-equal real frame totals (``returnn_b200.torch.data.pipeline.balance_batches``,
+    what ``torch_batching = {"type": "rank_balanced"}`` does in training); this rank keeps part ``rank`` of every group.
+    """
+    from returnn_b200.torch.data.pipeline import balance_batches
+
+    stream = make_synth_batches(seed=999, n_steps=n_steps * world, frames_budget=frames_budget, shape_seed=777)
+    out = []
+    for step in range(n_steps):
+        group = stream[step * world: (step + 1) * world]
+        out.append(balance_batches(group, length_key="data", max_seqs=200)[rank])
+    return out
+
+
 def run_ours(args):
     import numpy
     import torch
@@ -157,6 +186,7 @@ def run_ours(args):
     from returnn_b200.torch.engine import Engine
     from returnn_b200.datasets.generating import StaticDataset
     from returnn_b200.ops import _lib
+    from returnn_b200.ops import status as status_board
 
     rank, world, local_rank = _dist_env()
     assert world == args.gpus, "WORLD_SIZE %i != --gpus %i (launch with torchrun for N>1)" % (world, args.gpus)
@@ -167,13 +197,29 @@ def run_ours(args):
     if use_cuda:
         torch.cuda.set_device(local_rank)
     W, K = args.warmup, args.steps
-    n_steps = W + K
-    # weak scaling: every rank gets its own 40k-frame batches
-    batches = make_synth_batches(seed=1234 + rank, n_steps=2 * n_steps, frames_budget=BATCH_FRAMES)
+    # weak scaling: every rank gets its own 40k-frame batches; W warm-up batches, K timed ones, one more so that step W+K starts
+    batches = make_synth_batches(seed=1234 + rank, n_steps=W + K + 1, frames_budget=BATCH_FRAMES)
     extern_data = conformer_ctc.make_extern_data(MODEL_OPTS)
+    hook = {"armed": False, "n": 0, "ev0": None, "ev1": None}
+
+    def train_step(*, model, extern_data, **kwargs):
+        """the model's train_step; while armed (the Engine.train() measurement) it takes the timestamps at the start of steps W and W+K"""
+        if hook["armed"]:
+            n = hook["n"]
+            if n in (W, W + K) and use_cuda:
+                torch.cuda.synchronize()
+                if world > 1:
+                    dist.barrier()
+                    torch.cuda.synchronize()
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                hook["ev0" if n == W else "ev1"] = ev
+            hook["n"] = n + 1
+        return conformer_ctc.train_step(model=model, extern_data=extern_data, **kwargs)
+
     cfg = Config({
         "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": extern_data, "model_opts": dict(MODEL_OPTS),
-        "get_model": conformer_ctc.get_model, "train_step": conformer_ctc.train_step,
+        "get_model": conformer_ctc.get_model, "train_step": train_step,
         "batch_size": BATCH_FRAMES, "max_seqs": 200, "optimizer": {"class": "adamw", "weight_decay": 0.01, "eps": 1e-8},
         "learning_rate": 1e-4, "gradient_clip_global_norm": 5.0, "torch_amp": "bfloat16", "num_epochs": 1,
         "log_verbosity": 2 if rank == 0 else 1, "device": "cuda" if use_cuda else "cpu",
@@ -183,8 +229,9 @@ def run_ours(args):
     set_global_config(cfg)
     BehaviorVersion._reset(21)
     log.init_by_config(cfg)
-    flat = [s for b in batches[:2] for s in b]
-    train_data = StaticDataset(data=flat, output_dim={"data": (80, 2), "classes": (10000, 1)})
+    # the dataset of the Engine.train() measurement: the sequences of all batches in order; the engine's greedy batching under the same
+    # budget re-creates exactly these batches (the reference arm feeds its engine the same way)
+    train_data = StaticDataset(data=[s for b in batches for s in b], output_dim={"data": (80, 2), "classes": (10000, 1)})
     train_data.initialize()
     engine = Engine(cfg)
     engine.init_train_from_config(cfg, train_data, None, None)
@@ -193,7 +240,7 @@ def run_ours(args):
     dev = torch.device("cuda", local_rank) if use_cuda else torch.device("cpu")
     if not use_cuda:
         _cpu_smoke(engine, batches, W, K)
-        return
+        return None
 
     def barrier():
         if world > 1:
@@ -228,14 +275,15 @@ def run_ours(args):
     dev_ms = ev0.elapsed_time(ev1)
     launches = _lib.launch_count() - launches0
     del staged
-    # ---- end to end: pinned host -> device every step, loss read back every step.
+    status_board.check_now(dev)
+    # ---- end to end through run_train_step on the SAME K batches: pinned host -> device every step, loss read back every step.
     # The engine's pipelined form: the copy of batch i+1 is started on the copy stream while step i runs, and the loss of step
     # i is read on the host after step i+1 was issued (the last one by flush_losses), so every step's inputs cross the bus
     # and every step's loss reaches the host inside the timed region, without draining the device queue in between.
-    base = n_steps
-    staged = engine.stage_batch(raws[base])
-    for i in range(min(W, 3)):  # warm-up through the same pipelined path (copy stream, pinned loss ring)
-        nxt = engine.stage_batch(raws[base + i + 1]) if i + 1 < min(W, 3) else None
+    n_warm = min(W, 3)
+    staged = engine.stage_batch(raws[0])
+    for i in range(n_warm):  # warm-up through the same pipelined path (copy stream, pinned loss ring)
+        nxt = engine.stage_batch(raws[i + 1]) if i + 1 < n_warm else None
         engine.run_train_step(staged, read_losses="deferred")
         staged = nxt
     engine.flush_losses()
@@ -245,85 +293,143 @@ def run_ours(args):
     h2d = d2h = 0
     last_loss = None
     n_read = 0
-    first = base + min(W, 3)
-    staged = engine.stage_batch(raws[first])
+    staged = engine.stage_batch(raws[W])
     for i in range(K):
-        raw = raws[first + i]
+        raw = raws[W + i]
         h2d += raw["data"].numel() * raw["data"].element_size() + raw["classes"].numel() * raw["classes"].element_size()
-        nxt = engine.stage_batch(raws[first + i + 1]) if i + 1 < K else None
+        nxt = engine.stage_batch(raws[W + i + 1]) if i + 1 < K else None
         losses = engine.run_train_step(staged, read_losses="deferred")
         staged = nxt
         if losses:
             n_read += 1
-            d2h += 4 * len(losses)
             last_loss = losses
     losses = engine.flush_losses()
     n_read += 1
-    d2h += 4 * max(len(losses), 1)
-    last_loss = losses
+    last_loss = losses or last_loss
     e1.record()
     barrier()
     assert n_read == K, "every step's loss must have been read on the host (%i of %i)" % (n_read, K)
-    e2e_ms = e0.elapsed_time(e1)
+    d2h = K * (4 * max(len(last_loss or {}), 1) + 4 * status_board.NUM_SLOTS)  # the losses and the kernel status board, every step
+    rts_ms = e0.elapsed_time(e1)
+    # ---- end to end through Engine.train(): dataset -> batching -> collation -> pinned memory -> device -> step -> loss on the host,
+    # the loop a user runs. Timestamps at the start of steps W and W+K inside train_step (device synchronised, ranks aligned), as in
+    # the reference arm.
+    train_ms = None
+    train_err = None
+    try:
+        hook.update(armed=True, n=0, ev0=None, ev1=None)
+        engine.train()
+        hook["armed"] = False
+        if hook["ev0"] is not None and hook["ev1"] is not None:
+            torch.cuda.synchronize()
+            train_ms = hook["ev0"].elapsed_time(hook["ev1"])
+        else:
+            train_err = "the engine ran %i steps, fewer than warm-up + timed steps" % hook["n"]
+    except Exception as exc:  # the device-timed number stands on its own; say what happened
+        hook["armed"] = False
+        train_err = "%s: %s" % (type(exc).__name__, str(exc)[:200])
     clocks = sampler.stop() if rank == 0 else None
+    engine._pt_model.train()
+    # ---- data parallel only: batches whose shapes differ between the ranks (what real training has), device-timed
+    distinct = None
+    if world > 1:
+        distinct = {}
+        n_d = min(K, 20)
+        for name, bs in (("independent", make_synth_batches(seed=4321 + rank, n_steps=2 + n_d, shape_seed=5000 + rank)),
+                         ("rank_balanced", balanced_rank_batches(rank=rank, world=world, n_steps=2 + n_d))):
+            rs = [_collate(b, pin=True) for b in bs]
+            for i in range(2):
+                engine.run_train_step(to_dev(rs[i]), read_losses=False)
+            st = [to_dev(rs[2 + i]) for i in range(n_d)]
+            barrier()
+            a, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for i in range(n_d):
+                engine.run_train_step(st[i], read_losses=False)
+            b_.record()
+            barrier()
+            tt = torch.tensor([a.elapsed_time(b_)], device=dev, dtype=torch.float64)
+            ff = torch.tensor([float(sum(int(r["data:seq_len"].sum()) for r in rs[2:]))], device=dev, dtype=torch.float64)
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+            dist.all_reduce(ff, op=dist.ReduceOp.SUM)
+            distinct[name] = {"ms_per_step": tt.item() / n_d, "value": ff.item() * FRAME_SEC / (tt.item() / 1e3), "steps": n_d}
+            del st, rs
+    status_board.check_now(dev)
     if getattr(args, "profile_ops", False) and rank == 0:
-        # outside every timed region: per-op times of the native encoder calls (warm caches, events between the ops)
-        from returnn_b200.models import conformer_native
-
-        # host issue time: how long the host needs to enqueue K steps (no synchronisation inside); close to the device time
-        # means the step is bound by the launching thread, not by the kernels
-        torch.cuda.synchronize()
-        th0 = time.perf_counter()
-        for i in range(K):
-            engine.run_train_step(raws[base + i], read_losses=False)
-        th1 = time.perf_counter()
-        torch.cuda.synchronize()
-        th2 = time.perf_counter()
-        print("host issue %.3f ms/step, until the device is done %.3f ms/step" % ((th1 - th0) * 1e3 / K, (th2 - th0) * 1e3 / K), file=sys.stderr)
-        conformer_native.profile_ops(True)
-        for i in range(K):
-            engine.run_train_step(raws[base + i], read_losses=False)
-        torch.cuda.synchronize()
-        rep = conformer_native.profile_report()
-        conformer_native.profile_ops(False)
-        total = sum(v[1] for v in rep.values()) or 1.0
-        host_total = sum(v[2] for v in rep.values())
-        print("op profile over %i steps (encoder executor only): device %.3f ms/step, host issue %.3f ms/step" % (K, total / K, host_total / K), file=sys.stderr)
-        for tag, (cnt, ms, host) in sorted(rep.items(), key=lambda kv: -kv[1][1]):
-            print("  %-22s %6i calls  %9.3f ms/step  %7.1f us/call  %5.1f %%   host %6.1f us/call" % (
-                tag, cnt // K, ms / K, 1e3 * ms / max(cnt, 1), 100.0 * ms / total, 1e3 * host / max(cnt, 1)), file=sys.stderr)
-    frames_dev = sum(frames_per_step[W: W + K])
-    frames_e2e = sum(frames_per_step[base + min(W, 3): base + min(W, 3) + K])
+        _profile_ops(engine, raws, W, K)
+    frames = sum(frames_per_step[W: W + K])
+    # parameters after the same number of steps on every rank: max - min over the ranks of sum |p| (0 = the ranks hold the same model)
+    checksum = torch.stack([p.detach().double().abs().sum() for p in engine._pt_model.parameters()]).sum().reshape(1)
+    spread = 0.0
+    if world > 1:
+        allc = [torch.zeros_like(checksum) for _ in range(world)]
+        dist.all_gather(allc, checksum)
+        allc = torch.cat(allc)
+        spread = float(allc.max() - allc.min())
     # max time over ranks, total frames over ranks
-    t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-    f = torch.tensor([frames_dev, frames_e2e], device=dev, dtype=torch.float64)
+    t = torch.tensor([dev_ms, rts_ms, train_ms if train_ms is not None else -1.0], device=dev, dtype=torch.float64)
+    f = torch.tensor([frames], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(f, op=dist.ReduceOp.SUM)
-    dev_ms, e2e_ms = t.tolist()
-    frames_dev, frames_e2e = f.tolist()
+    dev_ms, rts_ms, train_ms_all = t.tolist()
+    frames = f.item()
+    dist_ctx = engine._torch_distributed_ctx
+    out = None
     if rank == 0:
-        value = frames_dev * FRAME_SEC / (dev_ms / 1e3)
-        e2e_value = frames_e2e * FRAME_SEC / (e2e_ms / 1e3)
+        value = frames * FRAME_SEC / (dev_ms / 1e3)
+        rts = {"value": frames * FRAME_SEC / (rts_ms / 1e3), "ms_per_step": rts_ms / K,
+               "api": "Engine.stage_batch + Engine.run_train_step(read_losses='deferred') on pre-collated pinned batches"}
+        if train_ms is not None and train_ms_all > 0:
+            e2e = {"value": frames * FRAME_SEC / (train_ms_all / 1e3), "unit": "audio-s/s", "ms_per_step": train_ms_all / K,
+                   "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,
+                   "api": "Engine.train(): StaticDataset -> greedy batching -> collation -> pinned memory -> device -> step -> loss on the host, every step",
+                   "run_train_step": rts, "last_loss": last_loss}
+        else:
+            e2e = dict(rts, unit="audio-s/s", h2d_bytes_per_step=h2d // K, d2h_bytes_per_step=d2h // K, last_loss=last_loss,
+                       engine_train_error=train_err)
         out = {
             "metric": "train seconds-of-audio per second", "value": value, "unit": "audio-s/s", "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_PUBLISHED) if BASELINE_PUBLISHED else None, "dtype": "bf16", "data": "synthetic",
-            "impl": "returnn_b200",
-            "config": {"model": "conformer-ctc 12x512 h8 ff2048 conv32 sub6 vocab10k", "global_batch": "%i padded frames per GPU x %i" % (BATCH_FRAMES, world),
-                       "seq_len": "300-2000 frames (10 ms)", "parallelism": "dp%i" % world, "optimizer": "adamw clip5",
-                       "l2": "working set per step (fp32 params, grads, Adam moments ~1.5 GB) exceeds L2; a distinct batch every step",
-                       "batches": "sequence lengths drawn from one seed on every rank (equal work per rank), feature and label values per rank",
-                       "native_lib": os.path.exists(_lib.lib_path())},
-            "clocks": clocks,
-            "e2e": {"value": e2e_value, "unit": "audio-s/s", "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K,
-                    "last_loss": last_loss},
-            "gpu_launches": launches,
+            "impl": "returnn_b200", "config": common_config(world), "clocks": clocks, "e2e": e2e, "gpu_launches": launches,
+            "grad_reduce": dist_ctx.grad_reduce_mode if dist_ctx else "none", "param_checksum_spread": spread,
+            "notes": {"native_lib": os.path.exists(_lib.lib_path()), "value_and_e2e": "the same K batches in all three measurements",
+                      "distinct_shapes": distinct},
         }
-        print(json.dumps(out))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    return out
+
+
+def _profile_ops(engine, raws, W, K):
+    """outside every timed region: per-op times of the native encoder calls (warm caches, events between the ops), to stderr"""
+    import torch
+    from returnn_b200.models import conformer_native
+
+    # host issue time: how long the host needs to enqueue K steps (no synchronisation inside); close to the device time
+    # means the step is bound by the launching thread, not by the kernels
+    torch.cuda.synchronize()
+    th0 = time.perf_counter()
+    for i in range(K):
+        engine.run_train_step(raws[W + i], read_losses=False)
+    th1 = time.perf_counter()
+    torch.cuda.synchronize()
+    th2 = time.perf_counter()
+    print("host issue %.3f ms/step, until the device is done %.3f ms/step" % ((th1 - th0) * 1e3 / K, (th2 - th0) * 1e3 / K), file=sys.stderr)
+    conformer_native.profile_ops(True)
+    for i in range(K):
+        engine.run_train_step(raws[W + i], read_losses=False)
+    torch.cuda.synchronize()
+    rep = conformer_native.profile_report()
+    conformer_native.profile_ops(False)
+    total = sum(v[1] for v in rep.values()) or 1.0
+    host_total = sum(v[2] for v in rep.values())
+    print("op profile over %i steps (encoder executor only): device %.3f ms/step, host issue %.3f ms/step" % (K, total / K, host_total / K), file=sys.stderr)
+    for tag, (cnt, ms, host) in sorted(rep.items(), key=lambda kv: -kv[1][1]):
+        print("  %-22s %6i calls  %9.3f ms/step  %7.1f us/call  %5.1f %%   host %6.1f us/call" % (
+            tag, cnt // K, ms / K, 1e3 * ms / max(cnt, 1), 100.0 * ms / total, 1e3 * host / max(cnt, 1)), file=sys.stderr)
 
 
 def _cpu_smoke(engine, batches, W, K):
@@ -435,6 +541,7 @@ def train_step(*, model, extern_data, **_kwargs):
 '''
 
 _ref_sampler = None
+_ref_result = None
 
 
 def _ref_timed_region_start(rank: int):
@@ -457,34 +564,35 @@ def _ref_timed_region_end(rank: int, world: int, ms: float, frames: int, W: int,
         clocks = _ref_sampler.stop() if _ref_sampler else None
         ms_, frames_ = t.item(), f.item()
         value = frames_ * FRAME_SEC / (ms_ / 1e3)
-        out = {"impl": "reference", "metric": "train seconds-of-audio per second", "value": value, "unit": "audio-s/s", "n_gpus": world,
-               "steps": K, "warmup": W, "ms_per_step": ms_ / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-               "dtype": "bf16", "data": "synthetic",
-               "config": {"model": "conformer-ctc 12x512 h8 ff2048 conv32 sub6 vocab10k", "global_batch": "%i padded frames per GPU x %i" % (BATCH_FRAMES, world),
-                          "seq_len": "300-2000 frames (10 ms)", "parallelism": "dp%i" % world, "optimizer": "adamw clip5",
-                          "timing": "engine train() loop, timestamps in train_step at steps W and W+K (end to end incl. data loading, H2D, loss .item())"},
-               "clocks": clocks, "e2e": {"value": value, "unit": "audio-s/s", "note": "the reference number is end to end by construction"}}
-        sys.__stdout__.write(json.dumps(out) + "\n")
-        sys.__stdout__.flush()
+        global _ref_result
+        _ref_result = {"impl": "reference", "metric": "train seconds-of-audio per second", "value": value, "unit": "audio-s/s", "n_gpus": world,
+                       "steps": K, "warmup": W, "ms_per_step": ms_ / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                       "dtype": "bf16", "data": "synthetic", "config": common_config(world), "clocks": clocks,
+                       "e2e": {"value": value, "unit": "audio-s/s", "ms_per_step": ms_ / K,
+                               "note": "the reference number is end to end by construction: its engine's train() loop"},
+                       "notes": {"timing": "engine train() loop, timestamps in train_step at steps W and W+K (end to end incl. data loading, "
+                                           "H2D, loss .item())"}}
 
 
 def run_reference(args):
+    """:return: the JSON dict of the reference arm (rank 0; ``{"impl": "reference", "unavailable": ...}`` if it cannot run), None on other ranks"""
     ref_dir = os.path.join(_ROOT, "baseline", "_ref")
+    rank, world, local_rank = _dist_env()
+
+    def unavailable(why):
+        return {"impl": "reference", "unavailable": why}  # on every rank: all of them then skip the secondary runs alike
+
     if not os.path.isdir(os.path.join(ref_dir, "returnn")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/returnn not installed"}))
-        return
+        return unavailable("baseline/_ref/returnn not installed")
     try:
         import torch
 
         if not torch.cuda.is_available() and os.environ.get("BENCH_TINY") != "1":
-            print(json.dumps({"impl": "reference", "unavailable": "no GPU visible"}))
-            return
+            return unavailable("no GPU visible")
     except Exception as exc:
-        print(json.dumps({"impl": "reference", "unavailable": "torch import failed: %s" % exc}))
-        return
+        return unavailable("torch import failed: %s" % exc)
     import tempfile
 
-    rank, world, local_rank = _dist_env()
     opts = {"root": _ROOT, "warmup": args.warmup, "steps": args.steps, "model": dict(MODEL_OPTS), "batch_frames": BATCH_FRAMES}
     cfg_text = "#!rnn.py\n" + _REF_CONFIG.replace("__BENCH_OPTS__", repr(opts))
     tmpdir = tempfile.mkdtemp(prefix="bench_ref_%i_" % rank)
@@ -500,8 +608,7 @@ def run_reference(args):
     try:
         from returnn.__main__ import main as ref_main
     except Exception as exc:
-        print(json.dumps({"impl": "reference", "unavailable": "import of the reference failed: %s: %s" % (type(exc).__name__, str(exc)[:200])}))
-        return
+        return unavailable("import of the reference failed: %s: %s" % (type(exc).__name__, str(exc)[:200]))
     old_stdout = sys.stdout
     try:
         # the reference logs to stdout; the JSON line goes to the real stdout, its log to stderr
@@ -510,22 +617,69 @@ def run_reference(args):
     except SystemExit:
         pass
     except Exception as exc:
-        sys.stdout = old_stdout
-        if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": "the reference run failed: %s: %s" % (type(exc).__name__, str(exc)[:300])}))
-        return
+        return unavailable("the reference run failed: %s: %s" % (type(exc).__name__, str(exc)[:300]))
     finally:
         sys.stdout = old_stdout
+    # the config imports this file as module "bench" (this script itself runs as __main__): the result was stored there
+    mod = sys.modules.get("bench")
+    res = getattr(mod, "_ref_result", None) if mod is not None else None
+    if res is None and rank == 0:
+        return unavailable("the reference engine finished without reaching step warm-up + steps")
+    return res if rank == 0 else {}
+
+
+SECONDARY = ("blstm_ctc", "conformer_aed")
+
+
+def run_secondary(args, impl: str):
+    """
+    The other headline configurations, each as a short run of ``bench_configs.py`` in a child process per rank (its own process
+    group on another port): BLSTM-CTC (6 x 1024, 20k frames per GPU) and Conformer-AED with parameter averaging
+    (``reduce_type="param"``, ``param_sync_step=100``; on more than one GPU the timed region holds 100 steps, so that exactly one
+    parameter synchronisation falls into it). A failure or a timeout of a child is reported in its entry; the flagship line stands.
+
+    :return: {name: JSON dict of the child} on rank 0, None on other ranks
+    """
+    rank, world, local_rank = _dist_env()
+    base_port = int(os.environ.get("MASTER_PORT", "29500"))
+    results = {}
+    for idx, name in enumerate(SECONDARY):
+        steps = min(args.steps, 10)
+        if name == "conformer_aed" and world > 1:
+            steps = 100
+        cmd = [sys.executable, os.path.join(_ROOT, "bench_configs.py"), "--config", name, "--gpus", str(world), "--steps", str(steps), "--warmup", "3",
+               "--impl", impl]
+        env = dict(os.environ, MASTER_PORT=str(base_port + 1 + idx), MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"))
+        # torchrun's own bookkeeping variables must not reach the child: it forms a process group of its own
+        for k in list(env):
+            if k.startswith("TORCHELASTIC_") or k in ("GROUP_RANK", "ROLE_RANK", "ROLE_NAME", "GROUP_WORLD_SIZE", "ROLE_WORLD_SIZE"):
+                env.pop(k)
+        try:
+            p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+            line = None
+            for ln in p.stdout.splitlines():
+                if ln.startswith("{"):
+                    line = ln
+            if line is not None:
+                results[name] = json.loads(line)
+            elif rank == 0:
+                results[name] = {"error": "exit code %i, no result line: %s" % (p.returncode, (p.stderr or "")[-300:])}
+        except subprocess.TimeoutExpired:
+            results[name] = {"error": "timed out after 900 s"}
+        except Exception as exc:
+            results[name] = {"error": "%s: %s" % (type(exc).__name__, str(exc)[:200])}
+    return results if rank == 0 else None
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=4)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--profile-ops", action="store_true", help="after the measurement, print per-op times of the native encoder to stderr")
     ap.add_argument("--tiny", action="store_true", help="small model and batches on any device: a functional smoke test, not a benchmark")
+    ap.add_argument("--no-secondary", action="store_true", help="only the flagship configuration (no BLSTM-CTC / Conformer-AED runs afterwards)")
     args = ap.parse_args()
     if args.tiny:
         global BATCH_FRAMES
@@ -534,10 +688,26 @@ def main():
         os.environ["BENCH_TINY"] = "1"
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
-        run_reference(args)
-    else:
-        run_ours(args)
+    rank = _dist_env()[0]
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    have_gpu = False
+    try:
+        import torch
+
+        have_gpu = torch.cuda.is_available()
+        if have_gpu:
+            torch.cuda.empty_cache()  # the children of the secondary runs get the device memory
+    except Exception:
+        pass
+    if out is None:
+        out = {}  # ranks other than 0 (they take part in the children's process groups below), or the CPU smoke run
+    if "unavailable" not in out and have_gpu and not args.tiny and not args.no_secondary:
+        sec = run_secondary(args, args.impl)
+        if sec is not None:
+            out["secondary"] = sec
+    if rank == 0 and out:
+        sys.__stdout__.write(json.dumps(out) + "\n")
+        sys.__stdout__.flush()
 
 
 if __name__ == "__main__":

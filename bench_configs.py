@@ -76,6 +76,46 @@ def _mt_batches(seed, n_steps, tokens_budget, vocab=32000):
     return batches
 
 
+def _ref_hook(state, W, K, counts, meta):
+    """
+    Timing hook of the reference-arm configs, called at the start of their ``train_step``: at steps W and W+K the device is
+    synchronised, the ranks are aligned and a CUDA event is recorded; after the second one rank 0 prints the JSON line (time =
+    max over ranks, counts summed over ranks).
+    """
+    import torch
+
+    n = state["n"]
+    state["n"] = n + 1
+    if n != W and n != W + K:
+        return
+    torch.cuda.synchronize()
+    dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
+    if dist_on:
+        torch.distributed.barrier()
+        torch.cuda.synchronize()
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    if n == W:
+        state["ev0"] = ev
+        return
+    torch.cuda.synchronize()
+    ms = state["ev0"].elapsed_time(ev)
+    t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    f = torch.tensor([float(sum(counts[W:W + K]))], device="cuda", dtype=torch.float64)
+    world = 1
+    if dist_on:
+        world = torch.distributed.get_world_size()
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(f, op=torch.distributed.ReduceOp.SUM)
+    if int(os.environ.get("RANK", "0")) == 0:
+        out = {"impl": "reference", "metric": meta["metric"], "value": f.item() * meta.get("count_scale", 1.0) / (t.item() / 1e3), "unit": meta["unit"],
+               "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": t.item() / K, "higher_is_better": True, "scaling": "weak", "dtype": "bf16",
+               "data": "synthetic", "config": {"model": meta["model"], "parallelism": meta.get("parallelism", "dp%i" % world)}}
+        sys.__stdout__.write(json.dumps(out) + "\n")
+        sys.__stdout__.flush()
+
+
+
 def _configs():
     from returnn_b200.models import blstm_ctc, conformer_aed, transformer_mt
 
@@ -113,7 +153,10 @@ def run_gpu(args):
     assert world == args.gpus
     torch.cuda.set_device(local_rank)
     W, K = args.warmup, args.steps
-    batches = spec["batches"](4321 + rank, 2 * (W + K) + 3)
+    # a pool of distinct batches that is walked round and round: consecutive steps never see the same batch and the pool (> 200 MB
+    # of inputs) exceeds the L2, while a 100-step run does not pin gigabytes of host memory
+    n_pool = 2 * (W + K) + 3 if args.task == "search" else min(2 * (W + K) + 3, 24)
+    batches = spec["batches"](4321 + rank, n_pool)
     mod = spec["mod"]
     cfg = Config(dict({
         "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": mod.make_extern_data(spec["model_opts"]),
@@ -198,8 +241,8 @@ def run_gpu(args):
             dist.destroy_process_group()
         return
     for i in range(W):
-        engine.run_train_step(to_dev(raws[i]), read_losses=False)
-    staged = [to_dev(raws[W + i]) for i in range(K)]
+        engine.run_train_step(to_dev(raws[i % n_pool]), read_losses=False)
+    staged = [to_dev(raws[(W + i) % n_pool]) for i in range(min(K, n_pool))]
     barrier()
     sampler = _bench.ClockSampler(local_rank)
     if rank == 0:
@@ -209,7 +252,7 @@ def run_gpu(args):
     barrier()
     ev0.record()
     for i in range(K):
-        engine.run_train_step(staged[i], read_losses=False)
+        engine.run_train_step(staged[i % len(staged)], read_losses=False)
     ev1.record()
     barrier()
     dev_ms = ev0.elapsed_time(ev1)
@@ -217,14 +260,14 @@ def run_gpu(args):
     del staged
     base = W + K
     for i in range(3):
-        engine.run_train_step(raws[base + i], read_losses=True)
+        engine.run_train_step(raws[(base + i) % n_pool], read_losses=True)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     h2d = 0
     last = None
     for i in range(K):
-        raw = raws[base + 3 + i]
+        raw = raws[(base + 3 + i) % n_pool]
         h2d += raw["data"].numel() * raw["data"].element_size() + raw["classes"].numel() * raw["classes"].element_size()
         last = engine.run_train_step(raw, read_losses=True)
     e1.record()
@@ -232,7 +275,7 @@ def run_gpu(args):
     e2e_ms = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([dev_ms, e2e_ms], device=dev, dtype=torch.float64)
-    f = torch.tensor([sum(counts[W: W + K]), sum(counts[base + 3: base + 3 + K])], device=dev, dtype=torch.float64)
+    f = torch.tensor([sum(counts[(W + i) % n_pool] for i in range(K)), sum(counts[(base + 3 + i) % n_pool] for i in range(K))], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(f, op=dist.ReduceOp.SUM)
@@ -242,7 +285,9 @@ def run_gpu(args):
         print(json.dumps({
             "metric": spec["metric"], "value": n_dev / (dev_ms / 1e3), "unit": spec["unit"], "n_gpus": world, "steps": K, "warmup": W,
             "ms_per_step": dev_ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "returnn_b200", "config": {"model": spec["name"], "global_batch": "%i per GPU x %i" % (spec["budget"], world)},
+            "impl": "returnn_b200", "config": {"model": spec["name"], "global_batch": "%i per GPU x %i" % (spec["budget"], world),
+                                                "parallelism": ("dp%i param averaging every 100 steps" % world) if args.config == "conformer_aed" else "dp%i" % world},
+            "grad_reduce": engine._torch_distributed_ctx.grad_reduce_mode if engine._torch_distributed_ctx else "none",
             "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
                                       "d2h_bytes_per_step": 4 * max(len(last or {}), 1), "last_loss": last},
             "gpu_launches": launches}))
@@ -389,7 +434,11 @@ backend = "torch"
 task = "train"
 behavior_version = 21
 _W, _K = _opts["warmup"], _opts["steps"]
-_batches = _bc._mt_batches(4321, _W + _K + 1, 25000)
+_rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+_batches = _bc._mt_batches(4321 + _rank, _W + _K + 1, 25000)
+_parallelism = "dp%i" % _world
+if _world > 1:
+    torch_distributed = {"reduce_type": "grad"}
 _tokens = [sum(s["data"].shape[0] + s["classes"].shape[0] for s in b) for b in _batches]
 train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (32000, 1), "classes": (32000, 1)}}
 src_time = Dim(None, name="src-time", kind=Dim.Types.Spatial)
@@ -427,22 +476,7 @@ _state = {"n": 0, "ev0": None}
 
 
 def train_step(*, model, extern_data, **_kwargs):
-    n = _state["n"]
-    if n == _W or n == _W + _K:
-        torch.cuda.synchronize()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        if n == _W:
-            _state["ev0"] = ev
-        else:
-            torch.cuda.synchronize()
-            ms = _state["ev0"].elapsed_time(ev)
-            tokens = sum(_tokens[_W:_W + _K])
-            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train tokens per second (source + target)", "value": tokens / (ms / 1e3),
-                                             "unit": "tokens/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
-                                             "data": "synthetic", "config": {"model": "transformer-base 6+6x512 h8 ff2048 shared vocab 32k (reference rf modules)"}}) + "\n")
-            sys.__stdout__.flush()
-    _state["n"] = n + 1
+    _bc._ref_hook(_state, _W, _K, _tokens, {"metric": "train tokens per second (source + target)", "unit": "tokens/s", "model": "transformer-base 6+6x512 h8 ff2048 shared vocab 32k (reference rf modules)", "count_scale": 1.0, "parallelism": _parallelism})
     src, tgt = extern_data["data"], extern_data["classes"]
     enc = model.encoder(src, spatial_dim=src_time)
     inp, (tgt_ext,) = rf.pad(tgt, axes=[tgt_time], padding=[(1, 0)], value=0)
@@ -474,7 +508,11 @@ backend = "torch"
 task = "train"
 behavior_version = 21
 _W, _K = _opts["warmup"], _opts["steps"]
-_batches = _bc._asr_batches(4321, _W + _K + 1, 40000, 300, 2000, 1.0 / 30.0)
+_rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+_batches = _bc._asr_batches(4321 + _rank, _W + _K + 1, 40000, 300, 2000, 1.0 / 30.0)
+_parallelism = "dp%i param averaging every 100 steps" % _world
+if _world > 1:
+    torch_distributed = {"reduce_type": "param", "param_sync_step": 100}
 _frames = [sum(s["data"].shape[0] for s in b) for b in _batches]
 train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (80, 2), "classes": (10000, 1)}}
 time_dim = Dim(None, name="time", kind=Dim.Types.Spatial)
@@ -519,22 +557,7 @@ _state = {"n": 0, "ev0": None}
 
 
 def train_step(*, model, extern_data, **_kwargs):
-    n = _state["n"]
-    if n == _W or n == _W + _K:
-        torch.cuda.synchronize()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        if n == _W:
-            _state["ev0"] = ev
-        else:
-            torch.cuda.synchronize()
-            ms = _state["ev0"].elapsed_time(ev)
-            frames = sum(_frames[_W:_W + _K])
-            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train seconds-of-audio per second", "value": frames * 0.01 / (ms / 1e3),
-                                             "unit": "audio-s/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
-                                             "data": "synthetic", "config": {"model": "conformer-aed 12x512 + 6-layer decoder, CE(ls 0.1) + 0.3 CTC (reference rf modules)"}}) + "\n")
-            sys.__stdout__.flush()
-    _state["n"] = n + 1
+    _bc._ref_hook(_state, _W, _K, _frames, {"metric": "train seconds-of-audio per second", "unit": "audio-s/s", "model": "conformer-aed 12x512 + 6-layer decoder, CE(ls 0.1) + 0.3 CTC (reference rf modules)", "count_scale": 0.01, "parallelism": _parallelism})
     data, targets = extern_data["data"], extern_data["classes"]
     enc, enc_spatial = model.encoder(data, in_spatial_dim=time_dim)
     ctc = rf.ctc_loss(logits=model.aux_ctc(enc), targets=targets, input_spatial_dim=enc_spatial, targets_spatial_dim=targets_time, blank_index=10000)
@@ -566,7 +589,11 @@ backend = "torch"
 task = "train"
 behavior_version = 21
 _W, _K = _opts["warmup"], _opts["steps"]
-_batches = _bc._asr_batches(4321, _W + _K + 1, 20000, 500, 1600, (0.1, 0.25))
+_rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+_batches = _bc._asr_batches(4321 + _rank, _W + _K + 1, 20000, 500, 1600, (0.1, 0.25))
+_parallelism = "dp%i" % _world
+if _world > 1:
+    torch_distributed = {"reduce_type": "grad"}
 _frames = [sum(s["data"].shape[0] for s in b) for b in _batches]
 train = {"class": "StaticDataset", "data": [s for b in _batches for s in b], "output_dim": {"data": (80, 2), "classes": (10000, 1)}}
 time_dim = Dim(None, name="time", kind=Dim.Types.Spatial)
@@ -633,22 +660,7 @@ _state = {"n": 0, "ev0": None}
 
 
 def train_step(*, model, extern_data, **_kwargs):
-    n = _state["n"]
-    if n == _W or n == _W + _K:
-        torch.cuda.synchronize()
-        ev = torch.cuda.Event(enable_timing=True)
-        ev.record()
-        if n == _W:
-            _state["ev0"] = ev
-        else:
-            torch.cuda.synchronize()
-            ms = _state["ev0"].elapsed_time(ev)
-            frames = sum(_frames[_W:_W + _K])
-            sys.__stdout__.write(json.dumps({"impl": "reference", "metric": "train seconds-of-audio per second", "value": frames * 0.01 / (ms / 1e3),
-                                             "unit": "audio-s/s", "n_gpus": 1, "steps": _K, "warmup": _W, "ms_per_step": ms / _K, "dtype": "bf16",
-                                             "data": "synthetic", "config": {"model": "blstm-ctc 6x1024 (reference rf.LSTM -> torch.lstm / cuDNN)"}}) + "\n")
-            sys.__stdout__.flush()
-    _state["n"] = n + 1
+    _bc._ref_hook(_state, _W, _K, _frames, {"metric": "train seconds-of-audio per second", "unit": "audio-s/s", "model": "blstm-ctc 6x1024 (reference rf.LSTM -> torch.lstm / cuDNN)", "count_scale": 0.01, "parallelism": _parallelism})
     logits, enc_spatial = model(extern_data["data"], in_spatial_dim=time_dim)
     loss = rf.ctc_loss(logits=logits, targets=extern_data["classes"], input_spatial_dim=enc_spatial, targets_spatial_dim=targets_time, blank_index=10000)
     loss.mark_as_loss("ctc", custom_inv_norm_factor=targets_time.get_size_tensor(), use_normalized_loss=False)

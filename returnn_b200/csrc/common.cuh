@@ -95,11 +95,12 @@ __device__ __forceinline__ void store8(void* base, int64_t idx, const F8& r, int
   }
 }
 
-// counter-based RNG: philox4x32-10 keyed on (seed, offset+index/4)
-__device__ __forceinline__ uint4 philox4x32(uint2 key, uint4 ctr) {
+// counter-based RNG: philox4x32 with ROUNDS rounds, keyed on (seed, counter)
+template <int ROUNDS>
+__device__ __forceinline__ uint4 philox4x32_rounds(uint2 key, uint4 ctr) {
   const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
 #pragma unroll
-  for (int i = 0; i < 10; ++i) {
+  for (int i = 0; i < ROUNDS; ++i) {
     uint32_t hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
     uint32_t hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
     ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
@@ -107,4 +108,26 @@ __device__ __forceinline__ uint4 philox4x32(uint2 key, uint4 ctr) {
     key.y += W1;
   }
   return ctr;
+}
+__device__ __forceinline__ uint4 philox4x32(uint2 key, uint4 ctr) { return philox4x32_rounds<10>(key, ctr); }
+
+// Dropout mask of 8 consecutive elements (a 16-byte group of bf16 values), used alike by every kernel that applies or replays
+// the mask of a linear layer's output (GEMM epilogues, the dropout kernels, the column-sum kernel of the backward pass):
+// ONE philox4x32-7 call (7 rounds pass the statistical test batteries; the mask needs no more) keyed on the seed, with the
+// element offset of the group's first element as counter, gives 128 bits = 16 bits per element. Element i is kept when its 16
+// bits are >= thresh16 = floor(p * 65536): the drop probability is p to within 1/65536.
+// Returns the 8 random 16-bit values packed as {e0 | e1 << 16, e2 | e3 << 16, ...}.
+__device__ __forceinline__ uint4 rb_dropout_bits8(uint2 key, uint64_t counter) {
+  return philox4x32_rounds<7>(key, make_uint4((uint32_t)counter, (uint32_t)(counter >> 32), 0xD0u, 0u));
+}
+__device__ __forceinline__ uint32_t rb_dropout_thresh16(float p) { return (uint32_t)(p * 65536.0f); }
+// v[0..7] -> kept values times `scale`, dropped values 0
+__device__ __forceinline__ void rb_dropout_apply8(uint2 key, uint64_t counter, uint32_t thresh16, float scale, float* v) {
+  const uint4 r = rb_dropout_bits8(key, counter);
+  const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = (w[i] & 0xFFFFu) >= thresh16 ? v[2 * i] * scale : 0.f;
+    v[2 * i + 1] = (w[i] >> 16) >= thresh16 ? v[2 * i + 1] * scale : 0.f;
+  }
 }

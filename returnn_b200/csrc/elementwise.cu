@@ -11,26 +11,22 @@ dropout_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ 
   const uint64_t sd = (uint64_t)seed[0];
   const uint64_t off = (uint64_t)offset[0];
   const float scale = 1.f / (1.f - p);
-  const uint32_t thresh = (uint32_t)(p * 4294967296.0);
+  const uint32_t thresh = rb_dropout_thresh16(p);
+  const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
   const int64_t n8 = n & ~(int64_t)7;
   for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n8; i += (int64_t)gridDim.x * blockDim.x * 8) {
-    uint64_t c = off + (uint64_t)i;
-    uint4 r0 = philox4x32(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-    uint4 r1 = philox4x32(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-    uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
     F8 a = load8(x, i, 1);
-#pragma unroll
-    for (int k = 0; k < 8; ++k) a.v[k] = r[k] >= thresh ? a.v[k] * scale : 0.f;
+    rb_dropout_apply8(key, off + (uint64_t)i, thresh, scale, a.v);
     store8(y, i, a, 1);
   }
   if (blockIdx.x == 0 && threadIdx.x < (n - n8)) {
+    // the last, incomplete group: the same 16-bit values as a complete group starting at n8 would use
     int64_t i = n8 + threadIdx.x;
-    uint64_t c = off + (uint64_t)n8;
-    uint4 r0 = philox4x32(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-    uint4 r1 = philox4x32(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-    uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
+    const uint4 r = rb_dropout_bits8(key, off + (uint64_t)n8);
+    const uint32_t w[4] = {r.x, r.y, r.z, r.w};
+    const uint32_t bits = (threadIdx.x & 1) ? (w[threadIdx.x >> 1] >> 16) : (w[threadIdx.x >> 1] & 0xFFFFu);
     float v = __bfloat162float(x[i]);
-    y[i] = __float2bfloat16(r[threadIdx.x] >= thresh ? v * scale : 0.f);
+    y[i] = __float2bfloat16(bits >= thresh ? v * scale : 0.f);
   }
 }
 

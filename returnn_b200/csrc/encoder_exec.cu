@@ -90,7 +90,7 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   const bool drop = p_drop > 0.f;
   const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] + site : 0;
-  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const uint32_t thresh = drop ? rb_dropout_thresh16(p_drop) : 0u;
   const float keep = drop ? scale / (1.f - p_drop) : scale;
   if (col < C) {
     const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
@@ -109,12 +109,7 @@ colsum_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y
         if (r >= r_end) break;
         if (y) {
           if (drop) {
-            const uint64_t c = off + (uint64_t)idx[u];
-            uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-            uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-            const uint32_t rr[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[u].v[i] = rr[i] >= thresh ? v[u].v[i] * keep : 0.f;
+            rb_dropout_apply8(key, off + (uint64_t)idx[u], thresh, keep, v[u].v);
           } else {
 #pragma unroll
             for (int i = 0; i < 8; ++i) v[u].v[i] *= keep;

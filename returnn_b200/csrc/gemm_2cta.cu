@@ -212,6 +212,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (!w.valid) continue;
       const int m0 = w.m0 + (int)rank * 128, n0 = w.n0;
       const uint32_t buf = t_local & 1u;
+      const int part = (warp - 2) >> 2;  // four warps per lane quarter, each with a quarter of the columns
+      // the epilogue's global input of this lane's row (first 16 columns) is requested before the wait: it arrives while the tile is
+      // still multiplied
+      uint4 in_a = make_uint4(0u, 0u, 0u, 0u), in_b = in_a;
+      const bool prefetched = FULL && p.tma_store && (g.dact_z != nullptr || g.resid != nullptr);
+      if (prefetched) epilogue_prefetch16(p, w.M, w.N, m0 + q * 32 + lane, n0 + part * (BN / 4), in_a, in_b);
       bool ok = mbar_wait(&acc_full[buf], (t_local >> 1) & 1u, abort_flag);
       if (!ok && lane == 0) {
         *abort_flag = 1;
@@ -221,14 +227,14 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const uint32_t t_addr = tmem_base + buf * BN + ((uint32_t)(q * 32) << 16);
-      const int part = (warp - 2) >> 2;  // four warps per lane quarter, each with a quarter of the columns
       auto release = [&]() { mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[buf]), 0)); };
-      if (p.tma_store) epilogue_rows_tma<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), box, &tm_c, &tm_c2, lane, q, release);
+      if (p.tma_store) epilogue_rows_tma<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), box, &tm_c, &tm_c2, lane, q, release, in_a, in_b, prefetched);
       else epilogue_columns<FULL>(p, w, m0, n0, t_addr, part * (BN / 4), (part + 1) * (BN / 4), stg, lane, q, release);
       ++t_local;
     }
-    // the bulk stores read this CTA's shared memory: they must have completed before the CTA exits
-    if (p.tma_store && lane == 0) tma_store_wait_all();
+    // the bulk stores read this CTA's shared memory: the reads must have finished before the CTA exits and its shared memory is
+    // handed to another CTA (the writes themselves complete like any other store of the grid)
+    if (p.tma_store && lane == 0) tma_store_wait_read();
   }
 
   // ---------------- teardown ----------------

@@ -24,7 +24,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ float act_grad(float z, int act) {
   if (act == 1) return z > 0.f ? 1.f : 0.f;
   if (act == 2) {
-    float s = 1.f / (1.f + __expf(-z));
+    float s = __fdividef(1.f, 1.f + __expf(-z));
     return s * (1.f + z * (1.f - s));
   }
   if (act == 3) {
@@ -33,6 +33,43 @@ __device__ __forceinline__ float act_grad(float z, int act) {
     return cdf + z * pdf;
   }
   return 1.f;
+}
+
+// The activation (or its derivative) on 8 values. The kind is uniform over the kernel: it is tested ONCE per group, outside the
+// element loops, so that the cheap kinds do not carry the instructions of the expensive one (erf) as predicated code.
+__device__ __forceinline__ float silu_tanh(float x) {
+  float t;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
+  return x * (0.5f + 0.5f * t);  // x * sigmoid(x), sigmoid(x) = (1 + tanh(x / 2)) / 2: one special-function instruction
+}
+__device__ __forceinline__ void act8(float* v, int act) {
+  if (act == 2) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = silu_tanh(v[i]);
+  } else if (act == 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fmaxf(v[i], 0.f);
+  } else if (act == 3) {
+#pragma unroll  // no rolled loop here: a dynamically indexed v[] would move the array, for every kind, from registers to local memory
+    for (int i = 0; i < 8; ++i) v[i] = 0.5f * v[i] * (1.f + erff(v[i] * 0.70710678118654752f));
+  }
+}
+__device__ __forceinline__ void act_grad8(float* v, const float* z, int act) {
+  if (act == 2) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float t;
+      asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * z[i]));
+      const float s = 0.5f + 0.5f * t;
+      v[i] *= s * (1.f + z[i] * (1.f - s));
+    }
+  } else if (act == 1) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = z[i] > 0.f ? v[i] : 0.f;
+  } else if (act == 3) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], 3);
+  }
 }
 
 __device__ __forceinline__ void load8_bf16(const void* base, size_t off, bool vec, int nvalid, float* out) {
@@ -96,14 +133,11 @@ __device__ __forceinline__ void epilogue_group(const Params& p, int row, int col
   if (FULL && g.dact_z) {
     float z[8];
     load8_bf16(g.dact_z, off, vec, nvalid, z);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], g.act);
+    act_grad8(v, z, g.act);
   } else if (g.act) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      pre[i] = v[i];
-      v[i] = apply_act(v[i], g.act);
-    }
+    for (int i = 0; i < 8; ++i) pre[i] = v[i];
+    act8(v, g.act);
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) pre[i] = v[i];
@@ -111,14 +145,7 @@ __device__ __forceinline__ void epilogue_group(const Params& p, int row, int col
   if (FULL && g.drop_p > 0.f) {
     const uint64_t sd = (uint64_t)g.seed[0];
     const uint64_t c = (uint64_t)g.offset[0] + g.drop_site + (uint64_t)off;
-    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
-    uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-    uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-    const uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    const float scale = 1.f / (1.f - g.drop_p);
-    const uint32_t thresh = (uint32_t)(g.drop_p * 4294967296.0);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = r[i] >= thresh ? v[i] * scale : 0.f;
+    rb_dropout_apply8(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), c, rb_dropout_thresh16(g.drop_p), 1.f / (1.f - g.drop_p), v);
   }
   if (FULL && g.resid) {
     float rs[8];
@@ -255,14 +282,40 @@ __device__ __forceinline__ void epilogue_columns(const Params& p, const Unit& w,
 // them to global memory: full-line writes, no st.global from the warps, rows and columns outside the matrix clipped by the TMA
 // unit. The next box is written only after the previous store has finished reading shared memory (wait_group.read).
 
-__device__ __forceinline__ float silu_fast(float x) { return x * (0.5f + 0.5f * tanh_approx(0.5f * x)); }
-
 // v[8] (accumulator values of columns col .. col+7 of `row`) -> final values in v, pre-activation in pre. Loads of dact_z / resid
 // only for valid elements. Same order of operations as epilogue_group.
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float* out) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __bfloat1622float2(h[i]);
+    out[2 * i] = f.x;
+    out[2 * i + 1] = f.y;
+  }
+}
+
+// The epilogue's global input (dact_z if there is one, else resid) for the 16 columns col0 .. col0+15 of `row`, fetched into
+// registers one phase ahead of its use: the first phase BEFORE the warp waits for the accumulator (the loads are in flight while
+// the MMAs of the tile still run), every later phase before the arithmetic of the phase before it. Groups that are not completely
+// inside the matrix are left to the in-line path of epilogue_math8 (their slot stays zero and is not used).
+__device__ __forceinline__ void epilogue_prefetch16(const Params& p, int M, int N, int row, int col0, uint4& a, uint4& b) {
+  const RbGemm& g = p.g;
+  const void* src = g.dact_z ? g.dact_z : g.resid;
+  a = make_uint4(0u, 0u, 0u, 0u);
+  b = a;
+  if (src == nullptr || row >= M) return;
+  const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(src) + (size_t)row * g.ldc + col0;
+  if (col0 + 8 <= N) a = *reinterpret_cast<const uint4*>(base);
+  if (col0 + 16 <= N) b = *reinterpret_cast<const uint4*>(base + 8);
+}
+
+// in8 / in_valid: the group's prefetched input (see epilogue_prefetch_half), passed by value so that it stays in registers
 template <bool FULL>
-__device__ __forceinline__ void epilogue_math8(const Params& p, int row, int col, bool row_ok, int n_extent, float* v, float* pre) {
+__device__ __forceinline__ void epilogue_math8(const Params& p, int row, int col, bool row_ok, int n_extent, float* v, float* pre,
+                                               const uint4 in8 = make_uint4(0u, 0u, 0u, 0u), bool in_valid = false) {
   const RbGemm& g = p.g;
   const int nvalid = row_ok ? max(0, min(8, n_extent - col)) : 0;
+  const bool have_in = FULL && in_valid && nvalid == 8;
   const size_t off = (size_t)row * g.ldc + col;
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] *= g.alpha;
@@ -290,15 +343,13 @@ __device__ __forceinline__ void epilogue_math8(const Params& p, int row, int col
   }
   if (FULL && g.dact_z) {
     float z[8];
-    load8_bf16(g.dact_z, off, nvalid == 8, nvalid, z);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] *= act_grad(z[i], g.act);
+    if (have_in) unpack8_bf16(in8, z);
+    else load8_bf16(g.dact_z, off, nvalid == 8, nvalid, z);
+    act_grad8(v, z, g.act);
   } else if (g.act) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      pre[i] = v[i];
-      v[i] = g.act == 2 ? silu_fast(v[i]) : apply_act(v[i], g.act);
-    }
+    for (int i = 0; i < 8; ++i) pre[i] = v[i];
+    act8(v, g.act);
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) pre[i] = v[i];
@@ -306,18 +357,12 @@ __device__ __forceinline__ void epilogue_math8(const Params& p, int row, int col
   if (FULL && g.drop_p > 0.f) {
     const uint64_t sd = (uint64_t)g.seed[0];
     const uint64_t c = (uint64_t)g.offset[0] + g.drop_site + (uint64_t)off;
-    const uint2 key = make_uint2((uint32_t)sd, (uint32_t)(sd >> 32));
-    uint4 r0 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0u, 0u));
-    uint4 r1 = philox4x32(key, make_uint4((uint32_t)c, (uint32_t)(c >> 32), 1u, 0u));
-    const uint32_t r[8] = {r0.x, r0.y, r0.z, r0.w, r1.x, r1.y, r1.z, r1.w};
-    const float scale = 1.f / (1.f - g.drop_p);
-    const uint32_t thresh = (uint32_t)(g.drop_p * 4294967296.0);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = r[i] >= thresh ? v[i] * scale : 0.f;
+    rb_dropout_apply8(make_uint2((uint32_t)sd, (uint32_t)(sd >> 32)), c, rb_dropout_thresh16(g.drop_p), 1.f / (1.f - g.drop_p), v);
   }
   if (FULL && g.resid) {
     float rs[8];
-    load8_bf16(g.resid, off, nvalid == 8, nvalid, rs);
+    if (have_in && g.dact_z == nullptr) unpack8_bf16(in8, rs);
+    else load8_bf16(g.resid, off, nvalid == 8, nvalid, rs);
 #pragma unroll
     for (int i = 0; i < 8; ++i) v[i] = rs[i] + g.res_scale * v[i];
   }
@@ -334,9 +379,18 @@ __device__ __forceinline__ uint4 pack8_bf16(const float* v) {
 // One warp's share of a tile: rows m0 + q*32 .. +31 (lane = row), accumulator columns [c_begin, c_begin + 64) at TMEM address
 // t_addr (lane quarter already applied). box: this warp's 4 KB of shared memory, 1024-byte aligned. tm_c / tm_c2: tensor maps of the
 // outputs with boxes of 32 rows x 128 bytes (64 bf16 or 32 fp32 columns; with a second output c2: 32 rows x 64 bytes, 64-byte swizzle). `arrive` hands the accumulator buffer back (lane 0).
+// One warp's share of a tile in four phases of 16 columns (a rolled loop: the body is small enough to stay in the instruction
+// cache, which an unrolled 64-column body is not; with 16 warps walking through it once per tile, instruction fetch was the
+// largest stall reason of the unrolled form). A phase: tcgen05.ld of 16 accumulator values, request of the NEXT phase's global
+// input (full epilogue), arithmetic on two groups of 8 columns, 16-byte writes into the box. The accumulator buffer is released
+// after the last phase's tcgen05.ld. A box is handed to the TMA unit when it is complete: after 64 bf16 columns (one output),
+// after 32 columns for fp32 outputs and for two outputs (then a pair of boxes with 64-byte rows, 64-byte swizzle: chunk j of row r
+// at position j ^ ((r >> 1) & 3)), and it is written again only after that store has finished reading it.
+// in_a / in_b: the prefetched input of phase 0 (valid if have_in).
 template <bool FULL, typename Arrive>
 __device__ __forceinline__ void epilogue_rows_tma(const Params& p, const Unit& w, int m0, int n0, uint32_t t_addr, int c_begin, uint8_t* box,
-                                                  const CUtensorMap* tm_c, const CUtensorMap* tm_c2, int lane, int q, Arrive arrive) {
+                                                  const CUtensorMap* tm_c, const CUtensorMap* tm_c2, int lane, int q, Arrive arrive,
+                                                  uint4 in_a, uint4 in_b, bool have_in) {
   const RbGemm& g = p.g;
   const int row0 = m0 + q * 32;
   const int row = row0 + lane;
@@ -351,98 +405,60 @@ __device__ __forceinline__ void epilogue_rows_tma(const Params& p, const Unit& w
     release();
     return;
   }
-  // Plain epilogue: all 64 columns are fetched at once and the accumulator is released before the arithmetic starts.
-  // Full epilogue (activation gradient, dropout, residual: more live values per group): the second half is fetched after the
-  // first half has been processed, which keeps the kernel free of register spills at 96 registers per thread.
-  uint32_t r[64];
-  tmem_ld32(t_addr + (uint32_t)c_begin, r);
-  if (!FULL) tmem_ld32(t_addr + (uint32_t)c_begin + 32u, r + 32);
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-  if (!FULL) release();
-  auto second_half = [&]() {
-    if (FULL) {
-      tmem_ld32(t_addr + (uint32_t)c_begin + 32u, r + 32);
-      asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-      release();
-    }
-  };
+  const bool two_out = g.c2 != nullptr;
+  const bool fp32 = g.out_fp32 != 0;
+  const bool half_boxes = two_out || fp32;  // a box (or pair of boxes) is complete after 32 columns
   uint8_t* my_row = box + lane * 128;
-  const int sw = lane & 7;
-  if (g.out_fp32) {
-    // two boxes of 32 fp32 columns
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 1) second_half();
-      if (col0 + 32 * h >= w.N) continue;
+  uint8_t* row_pre = box + lane * 64;
+  uint8_t* row_fin = box + 2048 + lane * 64;
+  const int sw = lane & 7, sw64 = (lane >> 1) & 3;
+#pragma unroll 1
+  for (int ph = 0; ph < 4; ++ph) {
+    uint32_t r[16];
+    tmem_ld16(t_addr + (uint32_t)(c_begin + 16 * ph), r);
+    uint4 nx_a = make_uint4(0u, 0u, 0u, 0u), nx_b = nx_a;
+    if (FULL && ph < 3 && have_in) epilogue_prefetch16(p, w.M, w.N, row, col0 + 16 * (ph + 1), nx_a, nx_b);
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (ph == 3) release();
+    if (ph == 0 || (half_boxes && ph == 2)) {
       if (lane == 0) tma_store_wait_read();
       __syncwarp();
+    }
+    const bool cols_in = col0 + 16 * ph < w.N;
 #pragma unroll
-      for (int gi = 0; gi < 4; ++gi) {
-        float v[8], pre[8];
+    for (int gi = 0; gi < 2; ++gi) {
+      float v[8], pre[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[32 * h + 8 * gi + i]);
-        epilogue_math8<FULL>(p, row, col0 + 32 * h + 8 * gi, row_ok, w.N, v, pre);
-        *reinterpret_cast<float4*>(my_row + (((2 * gi) ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
-        *reinterpret_cast<float4*>(my_row + (((2 * gi + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+      for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * gi + i]);
+      epilogue_math8<FULL>(p, row, col0 + 16 * ph + 8 * gi, row_ok && cols_in, w.N, v, pre, gi == 0 ? in_a : in_b, have_in);
+      if (fp32) {
+        const int c8 = 4 * (ph & 1) + 2 * gi;  // 16-byte chunk within the 32-column box
+        *reinterpret_cast<float4*>(my_row + ((c8 ^ sw) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<float4*>(my_row + (((c8 + 1) ^ sw) << 4)) = make_float4(v[4], v[5], v[6], v[7]);
+      } else if (two_out) {
+        const int c4 = 2 * (ph & 1) + gi;
+        *reinterpret_cast<uint4*>(row_pre + ((c4 ^ sw64) << 4)) = pack8_bf16(pre);
+        *reinterpret_cast<uint4*>(row_fin + ((c4 ^ sw64) << 4)) = pack8_bf16(v);
+      } else {
+        *reinterpret_cast<uint4*>(my_row + (((2 * ph + gi) ^ sw) << 4)) = pack8_bf16(v);
       }
+    }
+    in_a = nx_a;
+    in_b = nx_b;
+    if (ph == 3 || (half_boxes && ph == 1)) {
+      const int cbox = half_boxes ? col0 + 32 * (ph >> 1) : col0;
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        if (g.accumulate) tma_reduce_add_2d(tm_c, col0 + 32 * h, row0, box);
-        else tma_store_2d(tm_c, col0 + 32 * h, row0, box);
+      if (lane == 0 && cbox < w.N) {
+        if (fp32 && g.accumulate) {
+          tma_reduce_add_2d(tm_c, cbox, row0, box);
+        } else {
+          tma_store_2d(tm_c, cbox, row0, box);
+          if (two_out) tma_store_2d(tm_c2, cbox, row0, box + 2048);
+        }
         tma_store_commit();
       }
     }
-    return;
-  }
-  if (g.c2) {
-    // The pre-activation goes to c, the final value to c2. The warp's buffer is split into two boxes of 32 rows x 64 bytes (32 bf16
-    // columns, 64-byte swizzle: chunk j of row r at position j ^ ((r >> 1) & 3)); both stores of a round are in flight together.
-    uint8_t* row_pre = box + lane * 64;
-    uint8_t* row_fin = box + 2048 + lane * 64;
-    const int sw64 = (lane >> 1) & 3;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 1) second_half();
-      if (col0 + 32 * h >= w.N) continue;
-      if (lane == 0) tma_store_wait_read();
-      __syncwarp();
-#pragma unroll
-      for (int gi = 0; gi < 4; ++gi) {
-        float v[8], pre[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[32 * h + 8 * gi + i]);
-        epilogue_math8<FULL>(p, row, col0 + 32 * h + 8 * gi, row_ok, w.N, v, pre);
-        *reinterpret_cast<uint4*>(row_pre + ((gi ^ sw64) << 4)) = pack8_bf16(pre);
-        *reinterpret_cast<uint4*>(row_fin + ((gi ^ sw64) << 4)) = pack8_bf16(v);
-      }
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_store_2d(tm_c, col0 + 32 * h, row0, box);
-        tma_store_2d(tm_c2, col0 + 32 * h, row0, box + 2048);
-        tma_store_commit();
-      }
-    }
-    return;
-  }
-  // the store of the previous tile has long finished reading the box by the time the next accumulator is ready
-  if (lane == 0) tma_store_wait_read();
-  __syncwarp();
-#pragma unroll
-  for (int gi = 0; gi < 8; ++gi) {
-    if (gi == 4) second_half();
-    float v[8], pre[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * gi + i]);
-    epilogue_math8<FULL>(p, row, col0 + 8 * gi, row_ok, w.N, v, pre);
-    *reinterpret_cast<uint4*>(my_row + ((gi ^ sw) << 4)) = pack8_bf16(v);
-  }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_2d(tm_c, col0, row0, box);
-    tma_store_commit();
   }
 }
 

@@ -111,15 +111,9 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // make this thread's shared-memory writes visible to the asynchronous proxy (the TMA engine) before a bulk store is issued
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-__device__ __forceinline__ float tanh_approx(float x) {
-  float y;
-  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-  return y;
-}
-
 __device__ __forceinline__ float apply_act(float x, int act) {
   if (act == 1) return fmaxf(x, 0.f);
-  if (act == 2) return x / (1.f + __expf(-x));
+  if (act == 2) return __fdividef(x, 1.f + __expf(-x));
   if (act == 3) return 0.5f * x * (1.f + erff(x * 0.70710678118654752f));
   return x;
 }

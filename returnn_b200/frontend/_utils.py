@@ -98,12 +98,18 @@ def merge_dims_for_broadcast(a: Tensor, b: Tensor) -> Tuple[Dim, ...]:
     return tuple(out)
 
 
-def convert_to_tensor(value, *, dims: Sequence[Dim] = (), dtype: Optional[str] = None, sparse_dim: Optional[Dim] = None,
+def convert_to_tensor(value, *, dims: Optional[Sequence[Dim]] = None, dtype: Optional[str] = None, sparse_dim: Optional[Dim] = None,
                       feature_dim: Optional[Dim] = None, device: Optional[str] = None, name: Optional[str] = None,
                       like: Optional[Tensor] = None) -> Tensor:
-    """python scalar / numpy / torch / Tensor -> Tensor"""
+    """
+    python scalar / numpy / torch / Tensor -> Tensor. Without ``dims``, an array or raw tensor gets new static dims, one per axis,
+    sized by its shape (reference: returnn/frontend/array_.py:120-140); a scalar has no dims.
+    """
     if isinstance(value, Tensor):
         return value
+    if dims is None:
+        shape = tuple(value.shape) if isinstance(value, (torch.Tensor, numpy.ndarray)) else ()
+        dims = [Dim(int(n), name="%s_dim%i" % (name or "const", i)) for i, n in enumerate(shape)]
     if isinstance(value, Dim):
         return value.get_size_tensor() if value.is_dynamic() else convert_to_tensor(value.dimension, dtype=dtype or "int32", device=device)
     if like is not None:

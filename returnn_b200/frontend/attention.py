@@ -651,7 +651,9 @@ def sinusoidal_encoding(indices: Tensor, *, feat_dim: Dim, base: Union[int, floa
     dtype = dtype or get_default_float_dtype()
     F2 = feat_dim.dimension // 2
     raw = indices.raw_tensor
-    div_term = torch.exp(torch.arange(F2, device=raw.device, dtype=torch.float32) * -(2.0 * math.log(base) / feat_dim.dimension))
+    # angle of unit i: position * base ** (-i / (F/2 - 1)), i.e. the last unit has the wavelength 2 pi base exactly
+    # (reference: returnn/frontend/attention.py:1281-1283; not the F/2 in the denominator of the original Transformer paper)
+    div_term = torch.exp(torch.arange(F2, device=raw.device, dtype=torch.float32) * -(math.log(base) / max(F2 - 1, 1)))
     arg = raw.to(torch.float32).unsqueeze(-1) * div_term
     emb = torch.cat([torch.sin(arg), torch.sin(arg + math.pi / 2.0)], dim=-1).to(torch_dtype(dtype))
     return wrap(emb, list(indices.dims) + [feat_dim], feature_dim=feat_dim)

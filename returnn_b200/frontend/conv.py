@@ -76,10 +76,38 @@ def _mask_input(source: Tensor, in_spatial_dims: Sequence[Dim], use_mask: Option
     return source
 
 
+def _use_consistent_same_padding() -> bool:
+    """
+    Whether ``padding="same"`` with a stride pads by ``(filter_size - 1) / 2`` on both sides whatever the length (behaviour
+    version >= 24, or the config option ``rf_use_consistent_same_padding``), instead of the TensorFlow rule whose padding depends on
+    the padded length of the batch: with that rule a sequence's frames see a different alignment of the windows depending on the
+    longest sequence it happens to be batched with. Reference: returnn/frontend/conv.py:1019-1048.
+    """
+    from ..config import get_global_config
+    from ..utils.basic import BehaviorVersion
+
+    config = get_global_config(raise_exception=False)
+    if config is not None:
+        if "rf_use_consistent_same_padding" in config.typed_dict:
+            v = config.typed_dict["rf_use_consistent_same_padding"]
+            if v is not None:
+                return bool(v)
+        elif "rf_use_consistent_same_padding" in config.dict:
+            v = config.bool("rf_use_consistent_same_padding", None)
+            if v is not None:
+                return v
+    return BehaviorVersion.get() >= 24
+
+
 def _same_pads(shape_spatial, fs, st) -> List[int]:
+    """``F.pad`` argument (last axis first) for "same" padding; ``fs``: effective (dilated) filter sizes"""
+    consistent = any(s != 1 for s in st) and _use_consistent_same_padding()
     pads: List[int] = []
     for i in reversed(range(len(fs))):
-        pad = max(fs[i] - 1 - (shape_spatial[i] - 1) % st[i], 0)
+        if consistent:
+            pad = fs[i] - 1
+        else:
+            pad = max(fs[i] - 1 - (shape_spatial[i] - 1) % st[i], 0)
         left = pad // 2
         pads.extend([left, pad - left])
     return pads

@@ -101,7 +101,10 @@ class TransformerDecoder(Module):
         self.logits = Linear(model_dim, vocab_dim, with_bias=logits_with_bias)
         if share_embedding:
             assert self.input_embedding is not None and not (embed_dim and embed_dim != model_dim)
-            self.logits.weight = _TiedTransposed(self.input_embedding.weight, self.logits.weight.dims)
+            assert not logits_with_bias, "logits_with_bias=False expected with share_embedding"
+            # the SAME parameter under both names (dims [vocab, model]; Linear multiplies by it transposed): the state dict then has
+            # "input_embedding.weight" and "logits.weight" over one storage, as in the reference (decoder/transformer.py:192-197)
+            self.logits.weight = self.input_embedding.weight
         self.share_embedding = share_embedding
 
     def default_initial_state(self, *, batch_dims: Sequence[Dim]) -> State:
@@ -151,34 +154,6 @@ class TransformerDecoder(Module):
         decoded = self.final_layer_norm(decoded)
         logits = self.logits(decoded)
         return logits, new_state
-
-
-class _TiedTransposed:
-    """
-    Stand-in for ``logits.weight`` when it is tied to the embedding: presents ``embedding.weight^T`` with dims
-    ``[model, vocab]`` without being a second parameter (so it is not in the state dict twice).
-    """
-
-    def __init__(self, emb_weight, dims):
-        self._emb = emb_weight
-        self._dims = tuple(dims)
-
-    @property
-    def dims(self):
-        """[model, vocab]"""
-        return self._dims
-
-    @property
-    def raw_tensor(self):
-        """transposed view of the embedding"""
-        return self._emb.raw_tensor.t()
-
-    _raw_tensor = raw_tensor
-
-    @property
-    def dtype(self):
-        """dtype of the embedding"""
-        return self._emb.dtype
 
 
 class TransformerDecoderLayer(Module):

@@ -47,7 +47,12 @@ class Linear(Module):
             dims = tuple(d for d in dims if d != self.in_dim) + (self.in_dim,)
         from ..ops import linear as _lin
 
-        out = _lin.linear(raw, self.weight._raw_tensor, self.bias._raw_tensor if self.bias is not None else None)
+        w = self.weight
+        w_raw = w._raw_tensor
+        if w.dims[0] != self.in_dim and w.dims[0] == self.out_dim and w.dims[-1] == self.in_dim:
+            # a weight stored [out, in]: e.g. output logits tied to the [vocab, model] table of an Embedding
+            w_raw = w_raw.t()
+        out = _lin.linear(raw, w_raw, self.bias._raw_tensor if self.bias is not None else None)
         return wrap(out, dims[:-1] + (self.out_dim,), feature_dim=self.out_dim)
 
 

@@ -243,6 +243,89 @@ class BucketOrderingIterDataPipe(torch.utils.data.IterableDataset):
         raise Exception("%s.__getitem__ not supported" % self.__class__.__name__)
 
 
+def balance_batches(batches: List[List[Dict[str, Any]]], *, length_key: str, max_seqs: int = -1,
+                    max_padded: Optional[int] = None) -> List[List[Dict[str, Any]]]:
+    """
+    Redistribute the sequences of ``len(batches)`` consecutive batches so that every batch holds nearly the same number of REAL
+    frames (sum of sequence lengths).
+
+    On packed rows the time of a training step follows the real frames of a batch, while the greedy batching rule bounds the
+    padded frames: a batch of short sequences holds many more real frames than a batch with one long sequence. In a
+    data-parallel job every step then takes as long as the rank with the fullest batch. Longest-first assignment to the currently
+    emptiest batch (the LPT rule) evens this out; it is deterministic, so every rank computes the same partition without
+    communication. The group as a whole holds the same sequences as before.
+
+    Mixing long and short sequences raises the PADDED size of a batch above what the greedy rule produced (the padded budget
+    of a group shrinks when every batch contains a long sequence), so this is for models that compute on packed rows, whose
+    memory follows the real frames. ``max_padded`` (optional) bounds ``n * max_len`` per batch; a sequence that fits nowhere
+    under it stays in the batch it came from.
+    """
+    n_bins = len(batches)
+    if n_bins <= 1:
+        return batches
+    items = []
+    for b_idx, b in enumerate(batches):
+        for s_idx, seq in enumerate(b):
+            items.append((int(seq[length_key].shape[0]), b_idx, s_idx))
+    items.sort(key=lambda t: (-t[0], t[1], t[2]))
+    bins: List[List[Dict[str, Any]]] = [[] for _ in range(n_bins)]
+    real = [0] * n_bins
+    longest = [0] * n_bins
+    leftovers = []
+    for length, b_idx, s_idx in items:
+        placed = False
+        for i in sorted(range(n_bins), key=lambda i: (real[i], i)):
+            mx = max(longest[i], length)
+            if max_padded is not None and (len(bins[i]) + 1) * mx > max_padded:
+                continue
+            if max_seqs > 0 and len(bins[i]) >= max_seqs:
+                continue
+            bins[i].append(batches[b_idx][s_idx])
+            real[i] += length
+            longest[i] = mx
+            placed = True
+            break
+        if not placed:
+            leftovers.append((b_idx, s_idx))
+    for b_idx, s_idx in leftovers:
+        bins[b_idx].append(batches[b_idx][s_idx])
+    return bins
+
+
+class RankBalancedBatchingIterDataPipe(torch.utils.data.IterableDataset):
+    """
+    Data-parallel batching with equal work per rank. Every rank reads the SAME sequence stream (same dataset, same seed: set
+    ``random_seed_offset`` to 0 on all ranks), forms ``world`` consecutive batches with the usual greedy rule, evens out their real
+    frame totals with :func:`balance_batches`, and keeps batch number ``rank`` of every group. A step's batches then differ in
+    content but hold the same amount of work on every rank, and no sequence is trained on by two ranks.
+
+    Config: ``torch_batching = {"type": "rank_balanced", "length_key": "data"}`` (rank and world come from the distributed context;
+    ``max_padded`` optionally bounds the padded size of a rebalanced batch, see :func:`balance_batches`).
+    """
+
+    def __init__(self, dataset: torch.utils.data.IterableDataset, *, batch_size, max_seqs: int = -1, length_key: str = "data",
+                 rank: int = 0, world: int = 1, packed_batch_size=None, max_padded: Optional[int] = None):
+        super().__init__()
+        self._batches = BatchingIterDataPipe(dataset, batch_size=batch_size, max_seqs=max_seqs, packed_batch_size=packed_batch_size)
+        self._max_padded = max_padded
+        self._max_seqs = max_seqs if max_seqs is not None else -1
+        self._length_key = length_key
+        self._rank, self._world = rank, world
+        assert 0 <= rank < world
+
+    def __iter__(self):
+        group: List[List[Dict[str, Any]]] = []
+        for batch in self._batches:
+            group.append(batch)
+            if len(group) == self._world:
+                yield balance_batches(group, length_key=self._length_key, max_seqs=self._max_seqs, max_padded=self._max_padded)[self._rank]
+                group = []
+        # an incomplete last group is dropped on every rank alike: all ranks see the same number of steps
+
+    def __getitem__(self, index):
+        raise Exception("%s.__getitem__ not supported" % self.__class__.__name__)
+
+
 def get_batching_iterable_dataset_from_config(*, dataset: torch.utils.data.IterableDataset, config, train: bool) -> torch.utils.data.IterableDataset:
     """batching by config: ``torch_batching`` custom function / dict, else batch_size + max_seqs (+ packed_batch_size)"""
     batch_size = config.typed_value("batch_size", -1)
@@ -254,9 +337,19 @@ def get_batching_iterable_dataset_from_config(*, dataset: torch.utils.data.Itera
     custom = config.typed_value("torch_batching", None)
     if isinstance(custom, dict):
         opts = dict(custom)
-        if opts.pop("type") != "bucket":
-            raise ValueError("torch_batching: only type 'bucket' is known")
-        batches_dataset = BucketOrderingIterDataPipe(dataset, **opts)
+        kind = opts.pop("type")
+        if kind == "bucket":
+            batches_dataset = BucketOrderingIterDataPipe(dataset, **opts)
+        elif kind == "rank_balanced":
+            if "rank" not in opts:
+                import torch.distributed as _dist
+
+                opts["rank"] = _dist.get_rank() if _dist.is_available() and _dist.is_initialized() else 0
+                opts["world"] = _dist.get_world_size() if _dist.is_available() and _dist.is_initialized() else 1
+            batches_dataset = RankBalancedBatchingIterDataPipe(dataset, batch_size=batch_size, max_seqs=max_seqs,
+                                                               packed_batch_size=packed_batch_size, **opts)
+        else:
+            raise ValueError("torch_batching: type must be 'bucket' or 'rank_balanced', got %r" % (kind,))
     elif custom is not None:
         batches_dataset = custom(dataset=dataset, config=config, train=train, **get_fwd_compat_kwargs())
     if batches_dataset is None:

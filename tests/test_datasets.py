@@ -184,3 +184,32 @@ def test_literal_parser_matches_ast():
 
     txt = "{'a': [1, 2.5, -3, 12345678901234567890, True, None], \"b\\n\": ('x', 'y',), 'c': {'d': 'caf\\u00e9'}, # comment\n 'e': [],}"
     assert literal_eval(txt) == ast.literal_eval(txt)
+
+
+def test_rank_balanced_batching_equalises_real_frames():
+    """the ranks of a step get disjoint batches with near-equal sums of sequence lengths"""
+    import numpy
+    from returnn_b200.torch.data.pipeline import balance_batches, BatchingIterDataPipe, RankBalancedBatchingIterDataPipe
+
+    rng = numpy.random.RandomState(7)
+    seqs = [{"data": numpy.zeros((int(rng.randint(300, 2001)), 2), dtype="float32"), "seq_idx": numpy.array(i)} for i in range(400)]
+    budget, world = 40000, 4
+    plain = list(BatchingIterDataPipe(seqs, batch_size=budget, max_seqs=200))
+    groups = [plain[i: i + world] for i in range(0, len(plain) - world + 1, world)]
+    spread_before, spread_after = [], []
+    for g in groups:
+        bal = balance_batches(g, length_key="data", max_seqs=200)
+        assert sorted(int(s["seq_idx"]) for b in g for s in b) == sorted(int(s["seq_idx"]) for b in bal for s in b)
+        for b in bal:
+            assert b and len(b) <= 200
+        real_before = [sum(s["data"].shape[0] for s in b) for b in g]
+        real_after = [sum(s["data"].shape[0] for s in b) for b in bal]
+        spread_before.append(max(real_before) / (sum(real_before) / world))
+        spread_after.append(max(real_after) / (sum(real_after) / world))
+    assert numpy.mean(spread_after) < 1.03 < numpy.mean(spread_before), (numpy.mean(spread_before), numpy.mean(spread_after))
+    # the data pipe: every rank computes the same partition and keeps its own part
+    per_rank = [list(RankBalancedBatchingIterDataPipe(seqs, batch_size=budget, max_seqs=200, length_key="data", rank=r, world=world)) for r in range(world)]
+    assert len({len(x) for x in per_rank}) == 1 and len(per_rank[0]) == len(groups)
+    for step in range(len(groups)):
+        ids = [int(s["seq_idx"]) for r in range(world) for s in per_rank[r][step]]
+        assert len(ids) == len(set(ids)) == sum(len(b) for b in groups[step])

@@ -20,7 +20,7 @@ def _run(config, tmp_path, *extra):
 
 
 @pytest.mark.parametrize("config", ["demo-lstm.12ax.config", "demo-blstm-ctc.config", "demo-conformer-ctc.config", "demo-enc-dec-copy.config",
-                                    "demo-pretrain.config", "demo-rf.config"])
+                                    "demo-pretrain.config", "demo-rf.config", "demo-torch.config"])
 def test_demo_trains_one_epoch(config, tmp_path):
     out = _run(config, tmp_path)
     assert (tmp_path / "model.001.pt").exists(), out[-2000:]

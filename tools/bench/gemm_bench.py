@@ -43,6 +43,9 @@ def main():
     ap.add_argument("--only", default=None)
     ap.add_argument("--wgrad", default="atomic", choices=["atomic", "store"])
     ap.add_argument("--sets", type=int, default=0, help="operand sets in the ring (0: enough to exceed 160 MB)")
+    ap.add_argument("--epilogues", action="store_true",
+                    help="also time the fused epilogues of the training step on the ff1 / ff2 shapes: bias + SiLU with both outputs + dropout "
+                         "(ff1 forward), bias + dropout + half-step residual (ff2 forward), SiLU gradient + dropout mask (ff1 data gradient)")
     args = ap.parse_args()
     dev = torch.device("cuda")
     n = args.rows
@@ -74,6 +77,30 @@ def main():
                 else:
                     ours = lambda i: G.gemm(xs[i], dys[i], m=din, n=dout, k=n, a_mn_major=True, b_mn_major=True, out=out)
                 ref = lambda i: torch.matmul(xs[i].t(), dys[i], out=out)
+            variants = []
+            if args.epilogues and name in ("ff1", "ff2") and kind in ("fwd", "dgrad"):
+                seed = torch.tensor([1234], dtype=torch.int64, device=dev)
+                offs = torch.tensor([0], dtype=torch.int64, device=dev)
+                if name == "ff1" and kind == "fwd":
+                    bias = torch.randn(dout, device=dev)
+                    z = torch.empty(n, dout, device=dev, dtype=torch.bfloat16)
+                    variants.append(("bias+silu+z+dropout", lambda i: G.gemm(xs[i], ws[i], m=n, n=dout, k=din, a_mn_major=False, b_mn_major=True, out=z, bias=bias,
+                                                                             act="silu", want_act_output=True, out_act=out, dropout_p=0.1, dropout_seed=seed,
+                                                                             dropout_offset=offs)))
+                    variants.append(("bias+silu", lambda i: G.gemm(xs[i], ws[i], m=n, n=dout, k=din, a_mn_major=False, b_mn_major=True, out=out, bias=bias, act="silu")))
+                elif name == "ff2" and kind == "fwd":
+                    bias = torch.randn(dout, device=dev)
+                    resid = torch.randn(n, dout, device=dev, dtype=torch.bfloat16)
+                    variants.append(("bias+dropout+resid", lambda i: G.gemm(xs[i], ws[i], m=n, n=dout, k=din, a_mn_major=False, b_mn_major=True, out=out, bias=bias,
+                                                                            dropout_p=0.1, dropout_seed=seed, dropout_offset=offs, resid=resid, res_scale=0.5)))
+                elif name == "ff2" and kind == "dgrad":
+                    # dX of ff2 is the gradient w.r.t. the activated ff1 output: multiplied by SiLU'(z) and the dropout mask of ff1
+                    zz = torch.randn(n, din, device=dev, dtype=torch.bfloat16)
+                    variants.append(("dsilu+dropout", lambda i: G.gemm(dys[i], ws[i], m=n, n=din, k=dout, a_mn_major=False, b_mn_major=False, out=out, dact_z=zz,
+                                                                       act="silu", dropout_p=0.1, dropout_seed=seed, dropout_offset=offs)))
+            for vname, vfn in variants:
+                t_v = _time(vfn, n_sets, args.iters)
+                print(json.dumps({"shape": tag, "epilogue": vname, "ours_us": round(t_v * 1e6, 2)}), flush=True)
             t_ours = _time(ours, n_sets, args.iters)
             t_ref = _time(ref, n_sets, args.iters)
             flops = 2.0 * n * din * dout
