@@ -33,6 +33,23 @@ class Api:
         self.bridge = bridge
         self.single_step_dim = single_step_dim
 
+    def setup(self):
+        """
+        Per-test state of this package: behaviour version and evaluation mode. Other tests of the suite run engines in this
+        process and leave a global config, a train flag or another behaviour version behind.
+        """
+        import importlib
+
+        basic = importlib.import_module(self.rf.__name__.rsplit(".", 1)[0] + (".utils.basic" if self.name == "ours" else ".util.basic"))
+        if self.name == "ours":
+            basic.BehaviorVersion._reset(BEHAVIOR_VERSION)
+        else:
+            basic.BehaviorVersion._reset()
+            basic.BehaviorVersion.set(BEHAVIOR_VERSION)
+        config_mod = importlib.import_module(self.rf.__name__.rsplit(".", 1)[0] + ".config")
+        config_mod.set_global_config(None)
+        self.rf.init_train_step_run_ctx(train_flag=False, step=0, epoch=1)
+
     def mod(self, path: str):
         """submodule of the frontend package, e.g. ``"encoder.conformer"``"""
         import importlib

@@ -44,6 +44,7 @@ def _make_input(case: Case, lens, seed=3):
 
 def run_case(api: P.Api, case: Case, x_np, lens, *, params_from=None):
     """build, optionally load parameters, call; returns (masked output array [B, T', ...], output lengths, env)"""
+    api.setup()
     torch.manual_seed(0)
     api.rf.set_random_seed(1)
     env = case.make(api)
