@@ -652,7 +652,9 @@ def run_secondary(args, impl: str):
         env = dict(os.environ, MASTER_PORT=str(base_port + 1 + idx), MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"))
         # torchrun's own bookkeeping variables must not reach the child: it forms a process group of its own
         for k in list(env):
-            if k.startswith("TORCHELASTIC_") or k in ("GROUP_RANK", "ROLE_RANK", "ROLE_NAME", "GROUP_WORLD_SIZE", "ROLE_WORLD_SIZE"):
+            # (the reference engine exports its process-group state to child processes through an environment variable of its own)
+            if k.startswith("TORCHELASTIC_") or k.startswith("_RETURNN_") or k in ("GROUP_RANK", "ROLE_RANK", "ROLE_NAME", "GROUP_WORLD_SIZE",
+                                                                                   "ROLE_WORLD_SIZE"):
                 env.pop(k)
         try:
             p = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)

@@ -43,6 +43,12 @@ from .hooks import *
 from .parametrize import *
 from .build_from_dict import *
 from .piecewise_linear import *
+from .amp import *
+from .static_traceable import *
+from .graph import *
+from .assert_ import *
+from .types import GetModelFunc, StepFunc, ItemKeyType, get_raw_tensor_type
+from .backend import select_backend, get_selected_backend, select_backend_numpy, select_backend_tf, is_backend_raw_tensor_dim_tag_independent
 from .packed import pack, unpack, pack_import, is_packed, PackedTensor
 
 from . import init
@@ -53,6 +59,13 @@ from . import decoder
 from . import conversions
 from . import hooks
 from . import packed
+from . import amp
+from . import static_traceable
+from . import graph
+from . import types
+from . import backend
+from . import stepwise_scheduler
+from . import parametrize as parametrizations  # weight dropout / noise live in the parametrize module here
 from . import control_flow as _control_flow
 from .control_flow import control_flow_ctx, get_current_control_flow_ctx
 from .backend_select import select_backend_torch, select_backend_returnn_layers_tf, is_executing_eagerly, get_backend_name

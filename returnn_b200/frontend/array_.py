@@ -20,7 +20,8 @@ __all__ = [
     "masked_scatter", "sequence_mask", "pack_padded", "gather", "scatter", "scatter_mean", "scatter_argmax",
     "scatter_logsumexp", "scatter_logmeanexp", "slice", "shift_right", "shift_left", "reverse_sequence", "where",
     "search_sorted", "sparse_to_dense", "one_hot", "top_k_mask", "top_p_mask", "sort", "repeat", "tile", "cumsum",
-    "transpose", "num_elements_of_shape", "is_true", "nonzero_indices",
+    "transpose", "num_elements_of_shape", "is_true", "nonzero_indices", "unstack", "scatter_count", "pad_packed",
+    "expand_make_non_empty", "real_as_complex", "complex_as_real", "make_complex",
 ]
 
 
@@ -892,3 +893,84 @@ def nonzero_indices(mask: Tensor, *, out_dim: Optional[Dim] = None):
         out_dim = Dim(None, name="nonzero")
     out_dim.dyn_size_ext = Tensor("%s:size" % out_dim.name, dims=[], dtype="int32", raw_tensor=torch.tensor(idx.shape[0], dtype=torch.int32))
     return wrap(idx, [out_dim], sparse_dim=mask._dims[0]), out_dim
+
+
+def unstack(source: Tensor, *, axis: Dim) -> Tuple[Tensor, ...]:
+    """
+    ``axis.dimension`` tensors, each ``source`` without ``axis`` (views, nothing is copied): the inverse of :func:`stack`.
+    Reference: returnn/frontend/array_.py:662-677.
+    """
+    if axis.dimension is None:
+        raise ValueError("unstack: axis %s must be static (known dimension)" % (axis,))
+    ax = source.get_axis_from_description(axis)
+    rest = [d for i, d in enumerate(source.dims) if i != ax]
+    return tuple(wrap(raw, rest, like=source, name="unstack") for raw in torch.unbind(source.raw_tensor, dim=ax))
+
+
+def scatter_count(*, indices: Tensor, indices_dim: Union[Dim, Sequence[Dim]], out_dim: Optional[Union[Dim, Sequence[Dim]]] = None,
+                  fill_value: Optional[int] = None) -> Tensor:
+    """
+    How often every index occurs in ``indices`` (int32 counts over ``out_dim``, default: the sparse dim of the indices); entries
+    that never occur get ``fill_value`` (default 0).  Reference: returnn/frontend/array_.py:997-1022.
+    """
+    from .const import ones
+
+    counts = scatter(ones(dims=indices.dims, dtype="int32", device=indices.device), indices=indices, indices_dim=indices_dim, out_dim=out_dim)
+    if fill_value:
+        counts = where(counts > 0, counts, fill_value)
+    return counts
+
+
+def pad_packed(source: Tensor, *, in_dim: Dim, dims: Sequence[Dim]) -> Tensor:
+    """inverse of :func:`pack_padded`: the packed axis ``in_dim`` back to the padded ``dims`` (zeros behind the sequence ends)"""
+    mask = sequence_mask(dims, device=source.device)
+    return masked_scatter(source, mask=mask, in_dim=in_dim, dims=dims)
+
+
+def expand_make_non_empty(source: Tensor, *, axis: Dim, out_dim: Optional[Dim] = None) -> Tuple[Tensor, Dim]:
+    """
+    ``axis`` made at least one entry long: unchanged if it is not empty, else one zero entry (some kernels cannot take empty
+    tensors).  Reference: returnn/frontend/array_.py:1537-1561.
+    """
+    ax = source.get_axis_from_description(axis)
+    if source.raw_tensor.shape[ax] > 0:
+        return source, axis
+    padded, (new_axis,) = pad(source, axes=[axis], padding=[(0, 1)], mode="constant", value=0)
+    if out_dim is not None:
+        from .dims import replace_dim
+
+        padded, new_axis = replace_dim(padded, in_dim=new_axis, out_dim=out_dim)
+    return padded, new_axis
+
+
+def real_as_complex(x: Tensor, *, pair_dim: Dim) -> Tensor:
+    """
+    A real tensor whose size-2 ``pair_dim`` holds (real, imaginary) -> complex tensor without that dim (float32 -> complex64,
+    float64 -> complex128).  Reference: returnn/frontend/array_.py:1564-1589.
+    """
+    if pair_dim.dimension != 2:
+        raise ValueError("real_as_complex: pair_dim %s must have size 2" % (pair_dim,))
+    ax = x.get_axis_from_description(pair_dim)
+    raw = x.raw_tensor.movedim(ax, -1).contiguous()
+    rest = [d for i, d in enumerate(x.dims) if i != ax]
+    out = torch.view_as_complex(raw)
+    return wrap(out, rest, name="real_as_complex")
+
+
+def complex_as_real(x: Tensor, *, out_dim: Optional[Dim] = None) -> Tuple[Tensor, Dim]:
+    """complex tensor -> real tensor with a new last dim of size 2 (real, imaginary); returns the tensor and that dim"""
+    if out_dim is None:
+        out_dim = Dim(2, name="complex")
+    assert out_dim.dimension == 2
+    return wrap(torch.view_as_real(x.raw_tensor), list(x.dims) + [out_dim], name="complex_as_real"), out_dim
+
+
+def make_complex(real: Tensor, imag: Tensor) -> Tensor:
+    """complex tensor from its parts (dims: union of the operands' dims)"""
+    from .math_ import _prep_bin
+
+    a, b, ra, rb, out_dims = _prep_bin(real, imag, None, None)
+    ra, rb = torch.broadcast_tensors(ra, rb)
+    if ra.dtype != rb.dtype:
+        rb = rb.to(ra.dtype)
+    return wrap(torch.complex(ra.contiguous(), rb.contiguous()), out_dims, name="make_complex")

@@ -19,7 +19,8 @@ from ._utils import wrap, axis_of
 
 __all__ = ["conv", "Conv1d", "Conv2d", "Conv3d", "transposed_conv", "TransposedConv1d", "TransposedConv2d",
            "TransposedConv3d", "pool", "max_pool", "max_pool1d", "pool1d", "pool2d", "pool3d", "make_conv_out_spatial_dims",
-           "calc_conv_out_spatial_length"]
+           "calc_conv_out_spatial_length", "calc_conv_out_length", "calc_transposed_conv_out_length",
+           "make_transposed_conv_out_spatial_dims"]
 
 
 def _tup(v, n) -> Tuple[int, ...]:
@@ -404,3 +405,79 @@ def pool3d(source, *, mode, pool_size, padding="valid", dilation_rate=1, strides
     """3-D pooling"""
     return pool(source, mode=mode, pool_size=pool_size, padding=padding, dilation_rate=dilation_rate, strides=strides,
                 in_spatial_dims=in_spatial_dims, out_spatial_dims=out_spatial_dims)
+
+
+def calc_conv_out_length(in_length, *, filter_size, stride: int, padding: Union[str, int], dilation_rate: int = 1, name: Optional[str] = None):
+    """
+    Output length of a convolution along one axis, for an int, a size tensor or a :class:`Dim` (then a derived Dim whose sequence
+    lengths follow the input's).  "same": ``ceil(n / stride)``; "valid" or an int padding: ``ceil((n + 2p - (k - 1) d) / stride)``.
+    Reference: returnn/frontend/conv.py:783-858.
+    """
+    k = filter_size.dimension if isinstance(filter_size, Dim) else filter_size
+    pad = padding.lower() if isinstance(padding, str) else padding
+    if isinstance(in_length, Dim):
+        out = make_conv_out_spatial_dims([in_length], filter_size=[k], padding=pad, strides=stride, dilation_rate=dilation_rate)[0]
+        if name and out is not in_length:
+            out.name = name
+        return out
+    if (k == stride == 1 and pad in ("valid", "same", 0)) or (stride == 1 and pad == "same"):
+        return in_length
+    if isinstance(in_length, Tensor):
+        raw = calc_conv_out_spatial_length(in_length.raw_tensor, filter_size=k, stride=stride, dilation_rate=dilation_rate, padding=pad)
+        return in_length.copy_with_raw(torch.clamp(raw, min=0) if isinstance(raw, torch.Tensor) else raw)
+    return max(calc_conv_out_spatial_length(in_length, filter_size=k, stride=stride, dilation_rate=dilation_rate, padding=pad), 0)
+
+
+def calc_transposed_conv_out_length(in_length, *, filter_size, padding: Union[int, str], output_padding: Optional[int] = None,
+                                    stride: Optional[int] = None, dilation_rate: int = 1, name: Optional[str] = None):
+    """
+    Output length of a transposed convolution along one axis (int, size tensor or Dim): ``n * stride`` plus, for "valid",
+    ``max(k - stride, 0)``; "same": ``n * stride``; "full": ``n * stride - (stride + k - 2)``; with ``output_padding`` the exact
+    ``n * stride + k - stride - 2 * pad + output_padding``.  Reference: returnn/frontend/conv.py:910-1004.
+    """
+    assert padding in ("same", "valid", "full") or isinstance(padding, int)
+    k = filter_size.dimension if isinstance(filter_size, Dim) else filter_size
+    if dilation_rate != 1 and k != 1:
+        k = k + (k - 1) * (dilation_rate - 1)
+    if stride is None:
+        stride = k
+
+    def calc(n):
+        n = n * stride if stride != 1 else n
+        if output_padding is None:
+            if padding == "valid" or padding == 0:
+                return n if k == stride else n + max(k - stride, 0)
+            if padding == "full":
+                return n - (stride + k - 2)
+            if padding == "same":
+                return n
+            raise ValueError("calc_transposed_conv_out_length: invalid padding %r without output_padding" % (padding,))
+        pad = {"same": k // 2, "valid": 0, "full": k - 1}.get(padding, padding)
+        return n + (k - stride - 2 * pad + output_padding)
+
+    if isinstance(in_length, Dim):
+        if in_length.dimension is not None:
+            out = Dim(calc(in_length.dimension), name=name or ("%s:transposed-conv" % (in_length.name or "dim")))
+        else:
+            out = Dim(None, name=name or ("%s:transposed-conv" % (in_length.name or "dim")))
+            if in_length.dyn_size_ext is not None:
+                out.dyn_size_ext = in_length.dyn_size_ext.copy_with_raw(calc(in_length.dyn_size_ext.raw_tensor))
+        return out
+    if isinstance(in_length, Tensor):
+        return in_length.copy_with_raw(calc(in_length.raw_tensor))
+    return calc(in_length)
+
+
+def make_transposed_conv_out_spatial_dims(in_spatial_dims: Sequence[Dim], *, filter_size, padding, output_padding=None, strides=None,
+                                          dilation_rate=1, description_prefix: Optional[str] = None) -> List[Dim]:
+    """out spatial dims of a transposed convolution, one per in spatial dim (see :func:`calc_transposed_conv_out_length`)"""
+    n = len(in_spatial_dims)
+
+    def seq(v):
+        return list(v) if isinstance(v, (list, tuple)) else [v] * n
+
+    fs = [d.dimension if isinstance(d, Dim) else d for d in seq(filter_size)]
+    st, dl, pd, op = seq(strides), seq(dilation_rate), seq(padding), seq(output_padding)
+    return [calc_transposed_conv_out_length(in_spatial_dims[i], filter_size=fs[i], padding=pd[i].lower() if isinstance(pd[i], str) else pd[i],
+                                            output_padding=op[i], stride=st[i], dilation_rate=dl[i],
+                                            name="%s:spatial%i" % (description_prefix, i) if description_prefix else None) for i in range(n)]

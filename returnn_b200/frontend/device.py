@@ -8,7 +8,7 @@ import contextlib
 from ..tensor import Tensor
 from ._utils import wrap
 
-__all__ = ["copy_to_device", "get_default_device", "set_default_device", "set_default_device_ctx"]
+__all__ = ["copy_to_device", "get_default_device", "set_default_device", "set_default_device_ctx", "get_default_dim_size_device"]
 
 _default_device: Optional[str] = None
 
@@ -43,3 +43,8 @@ def set_default_device_ctx(device: Optional[str]):
         yield
     finally:
         _default_device = old
+
+
+def get_default_dim_size_device() -> Optional[str]:
+    """where the size tensors of dynamic dims (``Dim.dyn_size_ext``) live: on the host, so that shapes are known without a device read"""
+    return "cpu"

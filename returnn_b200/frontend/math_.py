@@ -25,7 +25,7 @@ __all__ = [
     "is_finite", "is_infinite", "is_neg_infinite", "maximum", "minimum", "clip_by_value", "lerp", "identity", "exp",
     "expm1", "log", "safe_log", "log1p", "sqrt", "rsqrt", "square", "abs", "tanh", "sigmoid", "log_sigmoid", "sin",
     "cos", "ceil", "floor", "round", "relu", "relu_square", "elu", "selu", "silu", "swish", "gelu", "softplus", "softmax",
-    "log_softmax", "gating", "glu", "sign", "erf", "leaky_relu", "hardtanh",
+    "log_softmax", "gating", "glu", "sign", "erf", "leaky_relu", "hardtanh", "log_add_exp",
 ]
 
 _CMP = {
@@ -63,6 +63,7 @@ _BIN = {
     "min": torch.minimum, "minimum": torch.minimum,
     "logical_and": torch.logical_and, "logical_or": torch.logical_or,
     "squared_difference": _sqdiff,
+    "logaddexp": torch.logaddexp,
 }
 
 
@@ -138,6 +139,11 @@ def combine(a, kind: str, b, *, allow_broadcast_all_sources: Optional[bool] = No
 
 compare_bc = compare
 combine_bc = combine
+
+
+def log_add_exp(a: Tensor, b: Tensor) -> Tensor:
+    """``log(exp(a) + exp(b))`` computed stably (sums of log probabilities, e.g. in beam search); see also ``reduce_logsumexp``"""
+    return combine(a, "logaddexp", b)
 
 
 def equal(a, b):

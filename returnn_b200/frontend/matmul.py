@@ -10,7 +10,7 @@ import torch
 from ..tensor import Tensor, Dim
 from ._utils import wrap
 
-__all__ = ["matmul"]
+__all__ = ["matmul", "dot"]
 
 
 def matmul(a: Tensor, b: Tensor, *, reduce: Union[Dim, Sequence[Dim]], use_mask: bool = True) -> Tensor:
@@ -65,3 +65,6 @@ def matmul(a: Tensor, b: Tensor, *, reduce: Union[Dim, Sequence[Dim]], use_mask:
     elif a_only and a.feature_dim in a_only:
         fd = a.feature_dim
     return wrap(out, out_dims, feature_dim=fd)
+
+
+dot = matmul  # the general contraction under its other name (reference: returnn/frontend/matmul.py:47)

@@ -16,7 +16,8 @@ from .reduce import reduce_sum as _reduce_sum, reduce_mean as _reduce_mean
 from . import math_ as _m
 from .run_ctx import get_run_ctx
 
-__all__ = ["moments", "LayerNorm", "RMSNorm", "GroupNorm", "GroupNormSpatial", "BatchNorm", "normalize", "Normalize"]
+__all__ = ["moments", "LayerNorm", "RMSNorm", "GroupNorm", "GroupNormSpatial", "BatchNorm", "normalize", "Normalize",
+           "batch_norm_distributed_default"]
 
 
 def moments(x: Tensor, axis: Union[Dim, Sequence[Dim]], *, use_mask: bool = True, correction: Union[int, float] = 0,
@@ -259,3 +260,11 @@ class Normalize(Module):
         if self.bias is not None:
             norm = norm + self.bias
         return norm
+
+
+def batch_norm_distributed_default() -> bool:
+    """config option ``rf_batch_norm_distributed`` (default False): batch-norm statistics summed over all data-parallel ranks"""
+    from ..config import get_global_config
+
+    config = get_global_config(raise_exception=False)
+    return bool(config.bool("rf_batch_norm_distributed", False)) if config else False

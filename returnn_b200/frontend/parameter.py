@@ -11,7 +11,7 @@ import torch
 from ..tensor import Tensor, Dim
 from ._utils import torch_dtype, get_default_float_dtype, dtype_name
 
-__all__ = ["Parameter"]
+__all__ = ["Parameter", "set_parameter_copy_behavior_ctx"]
 
 
 class Parameter(Tensor):
@@ -56,6 +56,8 @@ class Parameter(Tensor):
             self.initial = initial
 
     def __copy__(self):
+        if _copy_behavior == "share":
+            return self
         res = type(self)(dims=self.dims, dtype=self.dtype, trainable=self.trainable, auxiliary=self.auxiliary,
                          non_critical_for_restore=self.non_critical_for_restore, weight_decay=self.weight_decay)
         res.name = self.name
@@ -131,3 +133,26 @@ class Parameter(Tensor):
 
     def __repr__(self):
         return "Parameter{%r, [%s], %s}" % (self.name, ",".join(d.short_repr() for d in self.dims), self.dtype)
+
+
+_copy_behavior = "copy_init"
+
+
+import contextlib as _contextlib
+
+
+@_contextlib.contextmanager
+def set_parameter_copy_behavior_ctx(mode: str):
+    """
+    What ``copy.copy`` / ``copy.deepcopy`` of a parameter gives inside the block: ``"copy_init"`` (default) a new parameter of its
+    own, ``"share"`` the very same parameter (deep copies of a module then share their weights with the original).
+    Reference: returnn/frontend/parameter.py:262-282.
+    """
+    global _copy_behavior
+    assert mode in ("copy_init", "share")
+    old = _copy_behavior
+    try:
+        _copy_behavior = mode
+        yield
+    finally:
+        _copy_behavior = old

@@ -14,7 +14,8 @@ from ..tensor import Tensor, Dim
 from ._utils import wrap, torch_dtype, shape_of, get_default_float_dtype
 
 __all__ = ["set_random_seed", "get_random_state", "set_random_state", "reset_rng_states", "random", "random_uniform",
-           "random_normal", "random_truncated_normal", "random_choice_without_replacement", "random_choice_with_replacement", "random_label"]
+           "random_normal", "random_truncated_normal", "random_choice_without_replacement", "random_choice_with_replacement", "random_label",
+           "reset_step_random_state", "get_static_step_based_seed"]
 
 _seed = 42
 _gens: Dict[str, torch.Generator] = {}
@@ -160,3 +161,19 @@ def random_choice_without_replacement(*, log_probs: Tensor, axis: Dim, k: Union[
 def random_label(dims: Sequence[Dim], sparse_dim: Dim, *, dtype: str = "int32", device=None) -> Tensor:
     """uniform random class indices"""
     return random(dims=dims, dtype=dtype, device=device, sparse_dim=sparse_dim, distribution="uniform", minval=0, maxval=sparse_dim.dimension)
+
+
+# seeds for ``random(..., static=True)``: a host random state that is rewound at the start of every step, so that the n-th static
+# random call of a step gets the same seed in every step (and in the forward and the recomputation of a checkpointed region)
+_step_rnd_seed = 42
+_step_rnd = numpy.random.RandomState(_step_rnd_seed)
+
+
+def reset_step_random_state():
+    """rewind the step-based seed sequence; called at the beginning of every step"""
+    _step_rnd.seed(_step_rnd_seed)
+
+
+def get_static_step_based_seed(*, size=None):
+    """the next seed (or array of seeds) of the step-based sequence"""
+    return _step_rnd.randint(2 ** 31, size=size)

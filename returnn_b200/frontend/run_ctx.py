@@ -16,7 +16,7 @@ from typing import Any, Callable, Dict, Optional, Sequence, Union
 import contextlib
 from ..tensor import Tensor, Dim, TensorDict, batch_dim
 
-__all__ = ["RunCtx", "Loss", "get_run_ctx", "init_train_step_run_ctx", "init_forward_step_run_ctx"]
+__all__ = ["RunCtx", "Loss", "get_run_ctx", "get_run_ctx_step", "init_train_step_run_ctx", "init_forward_step_run_ctx"]
 
 _run_ctx: Optional["RunCtx"] = None
 _init_run_ctx: Optional["RunCtx"] = None
@@ -86,6 +86,22 @@ class RunCtx:
     def epoch(self) -> Union[int, Tensor]:
         """epoch"""
         return self._epoch
+
+    def get_step_tensor(self) -> Tensor:
+        """the global train step as a scalar int64 tensor (on the host)"""
+        if isinstance(self._step, Tensor):
+            return self._step
+        import torch
+
+        return Tensor("global_train_step", dims=(), dtype="int64", raw_tensor=torch.tensor(int(self._step), dtype=torch.int64))
+
+    def get_epoch_tensor(self) -> Tensor:
+        """the epoch as a scalar int64 tensor (on the host)"""
+        if isinstance(self._epoch, Tensor):
+            return self._epoch
+        import torch
+
+        return Tensor("epoch", dims=(), dtype="int64", raw_tensor=torch.tensor(int(self._epoch), dtype=torch.int64))
 
     def is_train_flag_enabled(self, *, func: Optional[Callable] = None) -> Union[bool, Tensor]:
         """train flag, possibly overridden for func"""
@@ -254,3 +270,8 @@ def _to_device_float(x: Tensor, like: Tensor) -> Tensor:
     if not raw.is_floating_point():
         raw = raw.float()
     return wrap(raw, x._dims)
+
+
+def get_run_ctx_step() -> Tensor:
+    """the global train step of the current run context as a scalar tensor (``get_run_ctx().get_step_tensor()``)"""
+    return get_run_ctx().get_step_tensor()

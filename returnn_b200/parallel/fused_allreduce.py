@@ -75,6 +75,13 @@ class FusedAllReduce:
         self.multicast_ptr = mc
         self._epoch = 1
         self._slot = 0
+        # Every rank's accumulator receives the same partial sums, but through atomics whose order differs from rank to rank, so the
+        # last bits of the ranks' totals differ. The norm that scales the update must be bitwise the same everywhere (or the ranks'
+        # parameters drift apart by rounding noise): all ranks read rank 0's accumulator.
+        try:
+            self._norm_rank0 = self._hdl_norm.get_buffer(0, (8,), torch.float32)
+        except Exception:
+            self._norm_rank0 = None
         self._status = _status_board.word(dev, _status_board.SLOT_ALLREDUCE)
         self._fn = _lib.bind("rb200_fused_allreduce", [_vp, _vp, _vp, _vp, _i32, _i32, _i64, _i64, _f32, _u32, _i32, _i32, _vp, _vp])
         self.skip_launches = 0  # failure-detection tests: this many following launches are left out (the peers' waits then run out)
@@ -106,7 +113,9 @@ class FusedAllReduce:
         the averaged gradient as a device scalar. The accumulator alternates between two slots; the one for the next step
         is cleared here, which is safe because no peer adds to it before its next step's entry barrier with this rank.
         """
-        norm_sq = self._norm[self._slot].clone()
+        # complete on every rank once the last bucket's kernel has passed its exit barrier (the kernels ahead of this read in stream order)
+        src = self._norm_rank0 if self._norm_rank0 is not None else self._norm
+        norm_sq = src[self._slot].clone()
         self._slot ^= 1
         self._norm[self._slot].zero_()
         return norm_sq

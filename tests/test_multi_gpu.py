@@ -119,6 +119,11 @@ def test_fused_allreduce_values_ragged(tmp_path, multimem):
         nerr = abs(float(norm_sq) - ref_norm) / ref_norm
         if err > 1e-6 or nerr > 1e-5:
             print("trial", trial, "max abs err", err, "norm rel err", nerr); ok = False
+        # the squared norm is bitwise the same on every rank (it scales the update: a difference in the last bit lets the ranks drift)
+        both = [torch.zeros_like(norm_sq.reshape(1)) for _ in range(world)]
+        dist.all_gather(both, norm_sq.reshape(1).contiguous())
+        if not all(torch.equal(both[0], b) for b in both):
+            print("trial", trial, "norm differs between ranks", [float(b) for b in both]); ok = False
         # the ragged sub-ranges on fresh data (every element of the range must be the average, everything else untouched)
         for (lo, hi) in ranges[len(arena.buckets):]:
             g.copy_(mine)
