@@ -245,152 +245,263 @@ class Task12AXDataset(GeneratingDataset):
         return DatasetSeq(seq_idx=seq_idx, features=features, targets=targets)
 
 
-class TaskEpisodicCopyDataset(GeneratingDataset):
+class _CharTaskDataset(GeneratingDataset):
     """
-    Episodic copy (Arjovsky et al. 2015): memorise a short random prefix, wait through a blank delay, then reproduce
-    it after a marker.
+    Character-level memory tasks: the input is a string over ``_input_classes`` (one-hot), the target a string of the same length
+    over the same alphabet, computed from the input by a small state machine (``make_output_seq``). The alphabets, the order of
+    the random draws and the target rules follow the reference exactly, so that a seed gives the same data in both frameworks
+    (returnn/datasets/generating.py:374-674).
     """
 
-    _input_classes = "ABCDEFGH?."
-    _output_classes = _input_classes
+    _input_classes = ""
+    _output_classes = ""
 
     def __init__(self, **kwargs):
         super().__init__(input_dim=len(self._input_classes), output_dim=len(self._output_classes), **kwargs)
         self.labels = {"classes": list(self._output_classes)}
 
+    def _draw_word(self, alphabet: str, length: int) -> str:
+        """``length`` characters, one ``choice`` draw each"""
+        letters = list(alphabet)
+        return "".join(self.random.choice(letters) for _ in range(length))
+
     def generate_input_seq(self) -> List[int]:
-        """prefix of 10 symbols, delay, marker, blanks"""
-        rnd = self.random
-        seq = "".join(rnd.choice(list(self._input_classes[:-2])) for _ in range(10))
-        seq += "." * rnd.randint(1, 101 + 1)
-        seq += "?"
-        seq += "." * 10
-        return [self._input_classes.index(c) for c in seq]
+        """class indices of a random input string"""
+        raise NotImplementedError
 
     @classmethod
     def make_output_seq(cls, input_seq: Sequence[int]) -> List[int]:
-        """blanks, then the prefix at the end"""
-        blank = cls._input_classes.index(".")
-        out = [blank] * len(input_seq)
-        out[-10:] = list(input_seq[:10])
-        return out
+        """class indices of the target string for an input"""
+        raise NotImplementedError
 
     def generate_seq(self, seq_idx: int) -> DatasetSeq:
         input_seq = self.generate_input_seq()
         features = class_idx_seq_to_1_of_k(input_seq, num_classes=len(self._input_classes))
-        return DatasetSeq(seq_idx=seq_idx, features=features, targets=numpy.array(self.make_output_seq(input_seq), dtype="int32"))
+        return DatasetSeq(seq_idx=seq_idx, features=features, targets=numpy.array(self.make_output_seq(input_seq)))
 
 
-class TaskXmlModelingDataset(GeneratingDataset):
+class TaskEpisodicCopyDataset(_CharTaskDataset):
     """
-    XML modeling (Jozefowicz et al. 2015): random nested tags ``<abc><de></de></abc>``; predict the next character.
+    Episodic copy (Arjovsky et al. 2015, https://arxiv.org/abs/1511.06464) with random lengths: 1-9 digits to remember, 1-99
+    blanks, a delimiter ``.``, then one ``.`` per digit plus one. Target: blank while reading; from the delimiter on the
+    remembered digits one by one, then ``.``.
     """
 
-    _input_classes = " !<>/abcdefghijklmnopqrstuvwxyz"
+    _input_classes = " .01234567"
     _output_classes = _input_classes
 
-    def __init__(self, limit_stack_depth: int = 4, **kwargs):
-        super().__init__(input_dim=len(self._input_classes), output_dim=len(self._output_classes), **kwargs)
-        self.limit_stack_depth = limit_stack_depth
-        self.labels = {"classes": list(self._output_classes)}
-
-    def generate_input_seq(self, seq_len: int) -> List[int]:
-        """well-formed nested tags until seq_len"""
-        rnd = self.random
-        letters = self._input_classes[5:]
-        stack: List[str] = []
-        s = " "
-        while len(s) < seq_len:
-            open_new = len(stack) < self.limit_stack_depth and (not stack or rnd.uniform() < 0.5)
-            if open_new:
-                name = "".join(rnd.choice(list(letters)) for _ in range(rnd.randint(2, 11)))
-                stack.append(name)
-                s += "<%s>" % name
-            else:
-                s += "</%s>" % stack.pop()
-        while stack:
-            s += "</%s>" % stack.pop()
-        s += "!"
-        return [self._input_classes.index(c) for c in s]
+    def generate_input_seq(self) -> List[int]:
+        n_chars = self.random.randint(1, 10)
+        text = self._draw_word(self._input_classes[2:], n_chars)
+        text += " " * self.random.randint(1, 100)
+        text += "." + "." * (n_chars + 1)
+        return [self._input_classes.index(c) for c in text]
 
     @classmethod
     def make_output_seq(cls, input_seq: Sequence[int]) -> List[int]:
-        """next char; the last target is the blank"""
-        return list(input_seq[1:]) + [cls._input_classes.index(" ")]
+        memory: List[str] = []
+        recalling = False
+        out = []
+        for idx in input_seq:
+            c = cls._input_classes[idx]
+            if not recalling:
+                out.append(" ")
+                if c == ".":
+                    recalling = True
+                elif c != " ":
+                    memory.append(c)
+            else:
+                out.append(memory.pop(0) if memory else ".")
+        return [cls._output_classes.index(c) for c in out]
 
-    def generate_seq(self, seq_idx: int) -> DatasetSeq:
-        input_seq = self.generate_input_seq(self.random.randint(10, 100))
-        features = class_idx_seq_to_1_of_k(input_seq, num_classes=len(self._input_classes))
-        return DatasetSeq(seq_idx=seq_idx, features=features, targets=numpy.array(self.make_output_seq(input_seq), dtype="int32"))
 
-
-class TaskVariableAssignmentDataset(GeneratingDataset):
+class TaskXmlModelingDataset(_CharTaskDataset):
     """
-    Variable assignment (Ba et al. 2016, fast weights): ``a1b2c3??b`` -> answer the value last assigned to the queried
-    variable at the final position.
+    XML modelling (Jozefowicz et al. 2015): nested tags with names of 1-9 letters, at most ``limit_stack_depth`` open at once.
+    Target: ``<`` where a tag must start, the letters of the closing tag's name (known from the stack) and its ``>``; blank where the
+    next character cannot be known (inside opening tags).
     """
 
-    _input_classes = " ,.?abcdefghijklmnopqrstuvwxyz0123456789"
+    _input_classes = " <>/abcdefgh"
     _output_classes = _input_classes
 
-    def __init__(self, **kwargs):
-        super().__init__(input_dim=len(self._input_classes), output_dim=len(self._output_classes), **kwargs)
-        self.labels = {"classes": list(self._output_classes)}
+    def __init__(self, limit_stack_depth: int = 4, **kwargs):
+        super().__init__(**kwargs)
+        self.limit_stack_depth = limit_stack_depth
 
-    def generate_input_seq(self) -> Tuple[List[int], int]:
-        rnd = self.random
-        letters = "abcdefghijklmnopqrstuvwxyz"
-        digits = "0123456789"
-        n = rnd.randint(1, 9)
-        names = list(rnd.choice(list(letters), size=n, replace=False))
-        values = {}
-        s = ""
-        for name in names:
-            v = rnd.choice(list(digits))
-            values[name] = v
-            s += name + v
-        q = rnd.choice(names)
-        s += "??" + q
-        return [self._input_classes.index(c) for c in s], self._input_classes.index(values[q])
+    def generate_input_seq(self) -> List[int]:
+        text = " "  # a prediction task: the target at the leading blank is the first character
+        open_tags: List[str] = []
+        while True:
+            if not open_tags or (len(open_tags) < self.limit_stack_depth and self.random.rand() > 0.6):
+                name = self._draw_word(self._input_classes[4:], self.random.randint(1, 10))
+                text += "<%s>" % name
+                open_tags.append(name)
+            else:
+                text += "</%s>" % open_tags.pop()
+            if not open_tags and self.random.rand() > 0.2:
+                break
+        return [self._input_classes.index(c) for c in text]
 
-    def generate_seq(self, seq_idx: int) -> DatasetSeq:
-        input_seq, answer = self.generate_input_seq()
-        blank = self._input_classes.index(" ")
-        out = [blank] * len(input_seq)
-        out[-1] = answer
-        features = class_idx_seq_to_1_of_k(input_seq, num_classes=len(self._input_classes))
-        return DatasetSeq(seq_idx=seq_idx, features=features, targets=numpy.array(out, dtype="int32"))
+    @classmethod
+    def make_output_seq(cls, input_seq: Sequence[int]) -> List[int]:
+        text = "".join(cls._input_classes[i] for i in input_seq)
+        EXPECT_LT, AFTER_LT, IN_OPEN, IN_CLOSE = "expect<", "after<", "open", "close"
+        state = None
+        stack: List[str] = []  # per open tag: what of its name is still to be emitted when it closes
+        out = []
+        for c in text:
+            if c in " >" and state != IN_CLOSE:
+                assert state != EXPECT_LT, repr(text)
+                out.append("<")
+                state = EXPECT_LT
+            elif state == EXPECT_LT:
+                assert c == "<", repr(text)
+                out.append(" ")
+                state = AFTER_LT
+            elif state == AFTER_LT:
+                if c == "/":
+                    assert stack, repr(text)
+                    out.append(stack[-1][0])
+                    stack[-1] = stack[-1][1:]
+                    state = IN_CLOSE
+                else:
+                    assert c not in " <>/", repr(text)
+                    out.append(" ")
+                    stack.append(c)
+                    state = IN_OPEN
+            elif state == IN_OPEN:
+                out.append(" ")
+                stack[-1] += c
+            elif state == IN_CLOSE:
+                assert stack, repr(text)
+                if stack[-1]:
+                    out.append(stack[-1][0])
+                    stack[-1] = stack[-1][1:]
+                else:
+                    out.append(">")
+                    stack.pop()
+                    state = None
+            else:
+                raise AssertionError("unexpected %r in %r" % (c, text))
+        return [cls._output_classes.index(c) for c in out]
+
+
+class TaskVariableAssignmentDataset(_CharTaskDataset):
+    """
+    Variable assignment (key-value retrieval, from the Associative LSTM paper): 1-4 stores ``S(key,value)`` with unique keys of
+    2-4 letters and values of 1 letter, then one query ``Q(key)`` followed by the value and ``.``. Target: blank everywhere except
+    after the query's ``)``, where the value is spelled out, then ``.``.
+    """
+
+    _input_classes = " ,.SQ()abcdefgh"
+    _output_classes = _input_classes
+
+    def generate_input_seq(self) -> List[int]:
+        letters = self._input_classes[7:]
+        store: Dict[str, str] = {}
+        parts = []
+        for _ in range(self.random.randint(1, 5)):
+            key_len = self.random.randint(2, 5)
+            while True:
+                key = self._draw_word(letters, key_len)
+                if key not in store:
+                    break
+            value = self._draw_word(letters, self.random.randint(1, 2))
+            parts.append("S(%s,%s)" % (key, value))
+            store[key] = value
+        key = self.random.choice(list(store.keys()))
+        text = ",".join(parts) + ",Q(%s)%s." % (key, store[key])
+        return [self._input_classes.index(c) for c in text]
+
+    @classmethod
+    def make_output_seq(cls, input_seq: Sequence[int]) -> List[int]:
+        text = "".join(cls._input_classes[i] for i in input_seq)
+        store: Dict[str, str] = {}
+        out = []
+        mode, key, value = "idle", "", ""
+        for c in text:
+            emit = " "
+            if mode == "idle":
+                key = ""
+                if c == "S":
+                    mode = "store("
+                elif c == "Q":
+                    mode = "query("
+                else:
+                    assert c in " ,", repr(text)
+            elif mode in ("store(", "query("):
+                assert c == "(", repr(text)
+                mode = "store-key" if mode == "store(" else "query-key"
+            elif mode == "store-key":
+                if c == ",":
+                    assert key
+                    value, mode = "", "store-value"
+                else:
+                    key += c
+            elif mode == "store-value":
+                if c == ")":
+                    assert value
+                    store[key] = value
+                    mode = "idle"
+                else:
+                    value += c
+            elif mode == "query-key":
+                if c == ")":
+                    value = store[key]
+                    emit, value, mode = value[0], value[1:], "answer"
+                else:
+                    key += c
+            elif mode == "answer":
+                if value:
+                    emit, value = value[0], value[1:]
+                else:
+                    emit, mode = ".", "end"
+            elif mode == "end":
+                assert c == ".", repr(text)
+            out.append(emit)
+        return [cls._output_classes.index(c) for c in out]
 
 
 class TaskNumberBaseConvertDataset(GeneratingDataset):
-    """convert a number from input_base digits to output_base digits (seq-to-seq, different lengths)"""
+    """
+    Convert a number written in ``input_base`` digits into ``output_base`` digits (sequence to sequence, different lengths).
+    Reference: returnn/datasets/generating.py:677-745.
+    """
 
     def __init__(self, input_base: int = 8, output_base: int = 2, min_input_seq_len: int = 1, max_input_seq_len: int = 8, **kwargs):
         super().__init__(input_dim=input_base, output_dim={"data": (input_base, 1), "classes": (output_base, 1)}, **kwargs)
         chars = "0123456789abcdefghijklmnopqrstuvwxyz"
+        assert 2 <= input_base <= len(chars) and 2 <= output_base <= len(chars)
+        assert 0 < min_input_seq_len <= max_input_seq_len
         self.input_base, self.output_base = input_base, output_base
         self._input_classes = chars[:input_base]
         self._output_classes = chars[:output_base]
-        self.labels = {"data": list(self._input_classes), "classes": list(self._output_classes)}
+        self.labels = {"data": self._input_classes, "classes": self._output_classes}
         self.min_input_seq_len, self.max_input_seq_len = min_input_seq_len, max_input_seq_len
 
     def get_random_input_seq_len(self) -> int:
         """uniform in [min, max]"""
         return self.random.randint(self.min_input_seq_len, self.max_input_seq_len + 1)
 
-    def generate_seq(self, seq_idx: int) -> DatasetSeq:
-        n = self.get_random_input_seq_len()
-        digits = [self.random.randint(0, self.input_base) for _ in range(n)]
+    def generate_input_seq(self) -> List[int]:
+        """digits, most significant first"""
+        return [self.random.randint(0, len(self._input_classes)) for _ in range(self.get_random_input_seq_len())]
+
+    def make_output_seq(self, input_seq: Sequence[int]) -> List[int]:
+        """the same number in the output base (``[0]`` for zero)"""
         value = 0
-        for d in digits:
+        for d in input_seq:
             value = value * self.input_base + int(d)
-        out = []
-        while True:
+        out: List[int] = []
+        while value:
             out.insert(0, value % self.output_base)
             value //= self.output_base
-            if value == 0:
-                break
-        return DatasetSeq(seq_idx=seq_idx, features=numpy.array(digits, dtype="int32"), targets={"classes": numpy.array(out, dtype="int32")})
+        return out or [0]
+
+    def generate_seq(self, seq_idx: int) -> DatasetSeq:
+        input_seq = self.generate_input_seq()
+        return DatasetSeq(seq_idx=seq_idx, features=numpy.array(input_seq), targets=numpy.array(self.make_output_seq(input_seq)))
 
 
 class DummyDataset(GeneratingDataset):
@@ -671,19 +782,29 @@ class StaticDataset(CachedDataset2):
 
 
 class CopyTaskDataset(GeneratingDataset):
-    """targets = inputs: random class sequences of length in [minimum_size, maximum_size]"""
+    """
+    Copy task: targets = inputs, random sparse labels. The length is uniform in ``[minlen, maxlen]``; both bounds can grow with the
+    epoch (``*_epoch_factor``). Reference: returnn/datasets/generating.py:1231-1277.
+    """
 
-    def __init__(self, nsymbols: int, minimum_size: int = 1, maximum_size: int = 20, **kwargs):
+    def __init__(self, nsymbols: int, minlen: int = 0, maxlen: int = 0, minlen_epoch_factor: float = 0, maxlen_epoch_factor: float = 0,
+                 minimum_size: Optional[int] = None, maximum_size: Optional[int] = None, **kwargs):
         super().__init__(input_dim=nsymbols, output_dim={"data": (nsymbols, 1), "classes": (nsymbols, 1)}, **kwargs)
         assert nsymbols <= 256
         self.nsymbols = nsymbols
-        self.minimum_size, self.maximum_size = minimum_size, maximum_size
+        # minimum_size / maximum_size: the names this class used before it took over the reference's
+        self.minlen = minlen if minimum_size is None else minimum_size
+        self.maxlen = maxlen if maximum_size is None else maximum_size
+        self.minlen_epoch_factor, self.maxlen_epoch_factor = minlen_epoch_factor, maxlen_epoch_factor
 
     def get_random_seq_len(self) -> int:
-        """uniform [min, max]"""
-        assert isinstance(self.minimum_size, int) and isinstance(self.maximum_size, int)
-        return self.random.randint(self.minimum_size, self.maximum_size + 1)
+        """uniform in the epoch's [min, max]"""
+        epoch = self.epoch or 1
+        lo = int(self.minlen + self.minlen_epoch_factor * epoch)
+        hi = int(self.maxlen + self.maxlen_epoch_factor * epoch)
+        assert 0 < lo <= hi, "CopyTaskDataset: need 0 < minlen <= maxlen, got %i, %i" % (lo, hi)
+        return self.random.randint(lo, hi + 1)
 
     def generate_seq(self, seq_idx: int) -> DatasetSeq:
-        seq = self.random.randint(0, self.nsymbols, size=self.get_random_seq_len()).astype("int32")
-        return DatasetSeq(seq_idx=seq_idx, features={"data": seq, "classes": seq.copy()})
+        seq = numpy.array([self.random.randint(0, self.nsymbols) for _ in range(self.get_random_seq_len())], dtype="int8")
+        return DatasetSeq(seq_idx=seq_idx, features=seq, targets={"classes": seq})
