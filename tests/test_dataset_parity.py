@@ -195,8 +195,7 @@ def test_variable_assignment_targets_follow_the_query():
         assert len(text) == len(target) and text.endswith(".")
         q = text.rindex("Q(")
         key = text[q + 2: text.index(")", q)]
-        stores = dict(p[2:-1].split(",") for p in text[:q].split("),") if p.startswith("S("))
-        stores = {k: v.rstrip(")") for k, v in stores.items()}
+        stores = dict(p[2:].split(",") for p in text[:q].split("),") if p.startswith("S("))
         value = stores[key]
         close = text.index(")", q)
         assert target[:close].strip() == "" and target[close: close + len(value) + 1] == value + "." and target[close + len(value) + 1:].strip() == ""
