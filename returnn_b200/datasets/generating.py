@@ -808,3 +808,10 @@ class CopyTaskDataset(GeneratingDataset):
     def generate_seq(self, seq_idx: int) -> DatasetSeq:
         seq = numpy.array([self.random.randint(0, self.nsymbols) for _ in range(self.get_random_seq_len())], dtype="int8")
         return DatasetSeq(seq_idx=seq_idx, features=seq, targets={"classes": seq})
+
+
+# The corpus readers live in their own module; the reference has them in its generating module
+# (returnn/datasets/generating.py: LibriSpeechCorpus, TimitDataset, BlissDataset, Enwik8Corpus), so configs name them through here.
+from .corpora import LibriSpeechCorpus, TimitDataset, BlissDataset, Enwik8Corpus  # noqa: E402
+
+__all__ += ["LibriSpeechCorpus", "TimitDataset", "BlissDataset", "Enwik8Corpus"]

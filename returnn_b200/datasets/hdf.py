@@ -6,9 +6,13 @@ File layout of :class:`HDFDataset` (written by :class:`SimpleHDFWriter` / :class
 ``seqTags`` ``[num_seqs]``, ``targets/data/<key>``, ``targets/size/<key>`` (attrs: dim, ndim), ``targets/labels/<key>``,
 file attrs ``inputPattSize``, ``numSeqs``, ``numTimesteps``, ``numLabels``.
 
-``h5py`` is an optional dependency: the classes import it on first use and raise an error that names the package when
-it is missing. ``NpzDataset`` / ``NpzWriter`` below keep the same logical layout in a ``.npz`` file for environments
-without HDF5.
+``h5py`` is an optional dependency. Without it the same code runs on the stand-in of :mod:`returnn_b200.utils.h5_shim` (same
+object model; the container is then a numpy archive, not HDF5). ``NpzDataset`` / ``NpzWriter`` below keep the logical layout of
+:class:`HDFDataset` in a plain ``.npz`` file.
+
+:class:`NextGenHDFDataset` / :class:`SiameseHDFDataset` read the stream layout: ``seq_names`` plus one group per stream under
+``streams`` (attr ``parser`` = feature_sequence / sparse / segment_alignment, group ``data`` with one dataset per sequence, and
+``feature_names`` for the sparse kinds); :class:`NextGenHDFWriter` writes it.
 """
 
 from __future__ import annotations
@@ -21,12 +25,10 @@ from ..utils.basic import NumbersDict
 
 
 def _h5py():
-    try:
-        import h5py
-    except ImportError as exc:
-        raise ImportError("HDFDataset / SimpleHDFWriter need the h5py package, which is not installed here: %s "
-                          "(NpzDataset / NpzWriter keep the same layout without HDF5)" % exc)
-    return h5py
+    """h5py, or its stand-in where the package is missing"""
+    from ..utils.h5_shim import get_h5py
+
+    return get_h5py()
 
 
 class _Layout:
@@ -170,12 +172,370 @@ class HDFDataset(CachedDataset2):
         return [] if self.is_data_sparse(key) else [self.num_outputs[key][0]]
 
 
-class NextGenHDFDataset(HDFDataset):
-    """stream-per-group layout of the reference's NextGenHDFDataset is read through the same logical layout"""
+def _decode(x) -> str:
+    return x.decode("utf8") if isinstance(x, bytes) else str(x)
 
 
-class SiameseHDFDataset(HDFDataset):
-    """as HDFDataset; the reference's class additionally samples same/different-class pairs"""
+class StreamParser:
+    """
+    One stream of one stream-layout file: ``get_data(seq_name)``, ``get_seq_length(seq_name)``, and after construction
+    ``num_features``, ``feature_type`` (1 sparse, 2 dense) and ``dtype``. Reference: returnn/datasets/hdf.py:475-628.
+    """
+
+    feature_type = 0
+
+    def __init__(self, seq_names: Sequence[str], stream):
+        self.seq_names = list(seq_names)
+        self.stream = stream
+        self.num_features: Optional[int] = None
+        self.dtype: Optional[str] = None
+        for name in self.seq_names:
+            self._check(self.stream["data"][name])
+
+    def _check(self, seq_data):
+        if self.dtype is None:
+            self.dtype = str(seq_data.dtype)
+        assert str(seq_data.dtype) == self.dtype, "stream with mixed dtypes: %s vs %s" % (seq_data.dtype, self.dtype)
+
+    def get_data(self, seq_name: str) -> numpy.ndarray:
+        """the sequence's array"""
+        return self.stream["data"][seq_name][...]
+
+    def get_seq_length(self, seq_name: str) -> int:
+        """its length"""
+        return int(self.stream["data"][seq_name].shape[0])
+
+    def get_dtype(self) -> str:
+        """numpy dtype name"""
+        assert isinstance(self.dtype, str)
+        return self.dtype
+
+
+class FeatureSequenceStreamParser(StreamParser):
+    """dense ``[time, features]`` per sequence"""
+
+    feature_type = 2
+
+    def _check(self, seq_data):
+        super()._check(seq_data)
+        assert len(seq_data.shape) == 2
+        if self.num_features is None:
+            self.num_features = int(seq_data.shape[1])
+        assert seq_data.shape[1] == self.num_features
+
+
+class SparseStreamParser(StreamParser):
+    """class indices ``[time]`` per sequence; the number of classes is the length of ``feature_names``"""
+
+    feature_type = 1
+
+    def __init__(self, seq_names, stream):
+        super().__init__(seq_names, stream)
+        self.num_features = int(stream["feature_names"].shape[0])
+
+    def _check(self, seq_data):
+        super()._check(seq_data)
+        assert len(seq_data.shape) == 1
+
+
+class SegmentAlignmentStreamParser(StreamParser):
+    """
+    Segments ``[num_segments, 2]`` = (class, length) per sequence, expanded to a frame-wise alignment that is returned flattened as
+    ``[2 * frames]``: (class, 1 at the last frame of a segment else 0) per frame.
+    """
+
+    feature_type = 1
+
+    def __init__(self, seq_names, stream):
+        super().__init__(seq_names, stream)
+        self.num_features = int(stream["feature_names"].shape[0])
+
+    def _check(self, seq_data):
+        super()._check(seq_data)
+        assert len(seq_data.shape) == 2 and seq_data.shape[1] == 2
+
+    def get_seq_length(self, seq_name: str) -> int:
+        return 2 * int(numpy.sum(self.stream["data"][seq_name][:, 1]))
+
+    def get_data(self, seq_name: str) -> numpy.ndarray:
+        segments = self.stream["data"][seq_name][...]
+        frames = int(segments[:, 1].sum())
+        alignment = numpy.zeros((frames, 2), dtype=self.dtype)
+        ends = numpy.cumsum(segments[:, 1])
+        alignment[:, 0] = numpy.repeat(segments[:, 0], segments[:, 1])
+        alignment[ends[segments[:, 1] > 0] - 1, 1] = 1
+        return alignment.reshape(-1)
+
+
+class _StreamHDFBase(CachedDataset2):
+    """what the two stream-layout datasets share: the files, the sequence index over all files, one parser per stream and file"""
+
+    parsers = {"feature_sequence": FeatureSequenceStreamParser, "sparse": SparseStreamParser, "segment_alignment": SegmentAlignmentStreamParser}
+
+    def __init__(self, input_stream_name: str, files: Optional[Sequence[str]] = None, **kwargs):
+        super().__init__(**kwargs)
+        self.input_stream_name = input_stream_name
+        self.files: List[str] = []
+        self.h5_files: List[Any] = []
+        self.all_seq_names: List[str] = []
+        self.seq_name_to_idx: Dict[str, int] = {}
+        self.file_indices: List[int] = []
+        self.seq_order: List[int] = []
+        self.all_parsers: Dict[str, List[StreamParser]] = {}
+        for fn in files or []:
+            self.add_file(fn)
+
+    @staticmethod
+    def _normalize_seq_name(name: str) -> str:
+        """a dataset name cannot contain '/' (it would make sub-groups): stored with a backslash instead"""
+        return name.replace("/", "\\")
+
+    def _required_streams(self) -> List[str]:
+        return [self.input_stream_name]
+
+    def add_file(self, path: str):
+        """register one more file"""
+        f = _h5py().File(path, "r")
+        assert "seq_names" in f and "streams" in f, "%s does not contain all required datasets/groups" % path
+        self.files.append(path)
+        self.h5_files.append(f)
+        seqs = [_decode(x) for x in f["seq_names"][...]]
+        norm = [self._normalize_seq_name(x) for x in seqs]
+        first = len(self.all_seq_names)
+        self.seq_name_to_idx.update({name: first + i for i, name in enumerate(seqs)})
+        self.all_seq_names.extend(seqs)
+        self.file_indices.extend([len(self.files) - 1] * len(seqs))
+        for need in self._required_streams():
+            assert need in f["streams"], "%s does not contain the stream %s" % (path, need)
+        parsers = {}
+        for name in f["streams"].keys():
+            stream = f["streams"][name]
+            kind = _decode(stream.attrs["parser"])
+            parsers[name] = self.parsers[kind](norm, stream)
+        for name, parser in parsers.items():
+            self.all_parsers.setdefault(name, []).append(parser)
+        if len(self.files) == 1:
+            self.num_outputs = {name: [parser.num_features, parser.feature_type] for name, parser in parsers.items()}
+            self.num_inputs = self.num_outputs[self.input_stream_name][0]
+        else:
+            for name, parser in parsers.items():
+                assert self.num_outputs[name][0] == parser.num_features, "number of features of stream %s: %s (first file) vs %s (%s)" % (
+                    name, self.num_outputs[name][0], parser.num_features, path)
+
+    def initialize(self):
+        self._num_seqs = len(self.all_seq_names)
+        self._estimated_num_seqs = self._num_seqs
+        super().initialize()
+
+    def get_total_num_seqs(self, *, fast: bool = False) -> int:
+        return len(self.all_seq_names)
+
+    def get_all_tags(self) -> List[str]:
+        return list(self.all_seq_names)
+
+    def _get_seq_length(self, orig_seq_idx: int) -> int:
+        parser = self.all_parsers[self.input_stream_name][self.file_indices[orig_seq_idx]]
+        return parser.get_seq_length(self._normalize_seq_name(self.all_seq_names[orig_seq_idx]))
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        if seq_order is not None:
+            self.seq_order = list(seq_order)
+        elif seq_list is not None:
+            self.seq_order = [self.seq_name_to_idx[x] for x in seq_list]
+        else:
+            self.seq_order = list(self.get_seq_order_for_epoch(epoch or 1, len(self.all_seq_names), self._get_seq_length))
+        self._num_seqs = len(self.seq_order)
+        return True
+
+    @property
+    def num_seqs(self) -> int:
+        return len(self.seq_order)
+
+    def supports_seq_order_sorting(self) -> bool:
+        return True
+
+    def supports_sharding(self) -> bool:
+        return True
+
+    def get_current_seq_order(self):
+        return list(self.seq_order)
+
+    def _stream_data(self, orig_seq_idx: int) -> Dict[str, numpy.ndarray]:
+        fi = self.file_indices[orig_seq_idx]
+        name = self._normalize_seq_name(self.all_seq_names[orig_seq_idx])
+        return {stream: parsers[fi].get_data(name) for stream, parsers in self.all_parsers.items()}
+
+    def get_data_dtype(self, key: str) -> str:
+        if key == "data":
+            key = self.input_stream_name
+        return self.all_parsers[key][0].get_dtype()
+
+
+class NextGenHDFDataset(_StreamHDFBase):
+    """
+    Stream-layout HDF files: every stream of a file becomes a data key; ``"data"`` is the stream named by ``input_stream_name``.
+    Reference: returnn/datasets/hdf.py:631-788.
+    """
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        if seq_idx >= len(self.seq_order):
+            return None
+        orig = self.seq_order[seq_idx]
+        targets = self._stream_data(orig)
+        return DatasetSeq(seq_idx=seq_idx, seq_tag=self.all_seq_names[orig], features=targets[self.input_stream_name], targets=targets)
+
+
+class SiameseHDFDataset(_StreamHDFBase):
+    """
+    Triplet sampling for weakly supervised training on stream-layout files in which every sequence has ONE label (first entry of
+    its ``seq_label_stream``). Before each epoch every sequence gets a partner with the same label (itself if it is alone in its
+    class) and one with a different label, drawn uniformly over the classes or by ``class_distribution`` (path to an ``.npz`` whose
+    ``arr_0[i]`` holds the probabilities of the other classes for anchor class i). Data keys: ``<stream>_0`` (anchor), ``<stream>_1``
+    (same label), ``<stream>_2`` (different label) for every stream, and ``<label stream>_all`` = the three labels concatenated;
+    ``"data"`` is the anchor's input stream. Reference: returnn/datasets/hdf.py:791-1067.
+    """
+
+    def __init__(self, input_stream_name: str, seq_label_stream: str = "words", class_distribution: Optional[str] = None,
+                 files: Optional[Sequence[str]] = None, **kwargs):
+        self.targets_stream = seq_label_stream
+        self.class_probs = numpy.load(class_distribution)["arr_0"] if class_distribution is not None else None
+        self.seq_to_target: Dict[str, int] = {}
+        self.target_to_seqs: Dict[int, List[str]] = {}
+        self.curr_epoch_triplets: List[tuple] = []
+        self._triplet_rng = numpy.random.RandomState()
+        super().__init__(input_stream_name, files=files, **kwargs)
+
+    def _required_streams(self) -> List[str]:
+        return [self.input_stream_name] + ([self.targets_stream] if self.targets_stream is not None else [])
+
+    def initialize(self):
+        self.target_to_seqs, self.seq_to_target = {}, {}
+        for fi, f in enumerate(self.h5_files):
+            labels = f["streams"][self.targets_stream]["data"]
+            for orig, name in enumerate(self.all_seq_names):
+                if self.file_indices[orig] != fi:
+                    continue
+                target = int(labels[self._normalize_seq_name(name)][0])
+                self.target_to_seqs.setdefault(target, []).append(name)
+                self.seq_to_target[name] = target
+        super().initialize()
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        if not self.seq_to_target:
+            self.initialize()
+        # fresh partners every epoch; with a fixed_random_seed the draws repeat per epoch number
+        seed = (self._get_random_seed_for_epoch(epoch or 1) + (epoch or 1)) % (2 ** 31) if self.fixed_random_seed is not None else None
+        self._triplet_rng = numpy.random.RandomState(seed)
+        self._init_triplets()
+        return True
+
+    def _sample_diff_class(self, anchor_target: int) -> int:
+        classes = list(self.target_to_seqs.keys())
+        if self.class_probs is not None:
+            probs = numpy.array(self.class_probs[anchor_target][classes], dtype="float64")
+            probs /= probs.sum()
+            return int(self._triplet_rng.choice(classes, p=probs))
+        return int(classes[self._triplet_rng.randint(0, len(classes))])
+
+    def _init_triplets(self):
+        assert len(self.target_to_seqs) > 1, "SiameseHDFDataset needs at least two classes"
+        self.curr_epoch_triplets = []
+        rng = self._triplet_rng
+        for orig in self.seq_order:
+            name = self.all_seq_names[orig]
+            target = self.seq_to_target[name]
+            same = self.target_to_seqs[target]
+            pair = orig
+            if len(same) > 1:
+                while True:
+                    cand = same[rng.randint(0, len(same))]
+                    if cand != name:
+                        break
+                pair = self.seq_name_to_idx[cand]
+            other = self._sample_diff_class(target)
+            while other == target:
+                other = self._sample_diff_class(target)
+            third_names = self.target_to_seqs[other]
+            third = self.seq_name_to_idx[third_names[rng.randint(0, len(third_names))]]
+            self.curr_epoch_triplets.append((orig, pair, third))
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        if seq_idx >= len(self.seq_order):
+            return None
+        targets: Dict[str, numpy.ndarray] = {}
+        for pos, orig in enumerate(self.curr_epoch_triplets[seq_idx]):
+            for stream, arr in self._stream_data(orig).items():
+                targets["%s_%d" % (stream, pos)] = arr
+        ts = self.targets_stream
+        targets["%s_all" % ts] = numpy.concatenate([targets["%s_%d" % (ts, i)] for i in range(3)], axis=0)
+        return DatasetSeq(seq_idx=seq_idx, seq_tag=self.all_seq_names[self.seq_order[seq_idx]],
+                          features=targets["%s_0" % self.input_stream_name], targets=targets)
+
+    def get_data_keys(self):
+        keys = ["data"]
+        for stream in self.all_parsers:
+            keys += ["%s_%d" % (stream, i) for i in range(3)]
+        return keys + ["%s_all" % self.targets_stream]
+
+    def is_data_sparse(self, key: str) -> bool:
+        if key == "data":
+            key = self.input_stream_name
+        return "features" not in key
+
+    def get_data_dim(self, key: str) -> int:
+        if key == "data":
+            return self.num_outputs[self.input_stream_name][0]
+        base = "_".join(key.split("_")[:-1]) if "_" in key else key
+        return self.num_outputs[base][0] if base in self.num_outputs else 1
+
+    def get_data_dtype(self, key: str) -> str:
+        if key == "data":
+            key = self.input_stream_name
+        base = "_".join(key.split("_")[:-1]) if key not in self.all_parsers and "_" in key else key
+        return self.all_parsers[base][0].get_dtype()
+
+
+class NextGenHDFWriter:
+    """
+    Writes the stream layout: ``add_stream(name, kind, feature_names=...)`` once per stream, then ``add_seq(seq_name, {stream:
+    array})`` per sequence, then ``close()``.
+    """
+
+    def __init__(self, filename: str):
+        self._h5 = _h5py()
+        self._file = self._h5.File(filename, "w")
+        self._streams = self._file.create_group("streams")
+        self._seq_names: List[str] = []
+
+    def add_stream(self, name: str, kind: str, feature_names: Optional[Sequence[str]] = None):
+        """``kind``: feature_sequence, sparse or segment_alignment (the last two need ``feature_names``)"""
+        assert kind in _StreamHDFBase.parsers
+        grp = self._streams.create_group(name)
+        grp.attrs["parser"] = kind
+        grp.create_group("data")
+        if kind != "feature_sequence":
+            assert feature_names is not None, "stream %r of kind %s needs feature_names" % (name, kind)
+            grp.create_dataset("feature_names", data=numpy.array(list(feature_names), dtype=object), dtype=self._h5.special_dtype(vlen=str))
+
+    def add_seq(self, seq_name: str, data: Dict[str, numpy.ndarray]):
+        """one sequence for every stream"""
+        self._seq_names.append(seq_name)
+        norm = _StreamHDFBase._normalize_seq_name(seq_name)
+        for stream, arr in data.items():
+            self._streams[stream]["data"].create_dataset(norm, data=numpy.asarray(arr))
+
+    def close(self):
+        """write ``seq_names`` and close the file"""
+        self._file.create_dataset("seq_names", data=numpy.array(self._seq_names, dtype=object), dtype=self._h5.special_dtype(vlen=str))
+        self._file.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
 
 
 class SimpleHDFWriter:

@@ -7,6 +7,7 @@ files), :class:`Lexicon` (Bliss XML lexicon) and :class:`PhoneSeqGenerator`.
 from __future__ import annotations
 from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Union
 import gzip
+import re
 import os
 import xml.etree.ElementTree as ElementTree
 import numpy
@@ -363,3 +364,141 @@ class PhoneSeqGenerator:
     def seq_to_class_idxs(self, phones: Sequence[str], dtype: str = "int32") -> numpy.ndarray:
         """phoneme indices"""
         return numpy.array([self.lexicon.phonemes[p]["index"] for p in phones], dtype=dtype)
+
+
+# ---- text post-processing (names as in the reference, returnn/datasets/lm.py:2245-2563) ------------------------------------------
+
+_ABBREVIATIONS = [(re.compile(r"\b%s\." % a, re.IGNORECASE), b) for a, b in [
+    ("mrs", "misess"), ("mr", "mister"), ("dr", "doctor"), ("st", "saint"), ("co", "company"), ("jr", "junior"), ("maj", "major"),
+    ("gen", "general"), ("drs", "doctors"), ("rev", "reverend"), ("lt", "lieutenant"), ("hon", "honorable"), ("sgt", "sergeant"),
+    ("capt", "captain"), ("esq", "esquire"), ("ltd", "limited"), ("col", "colonel"), ("ft", "fort")]]
+_WHITESPACE = re.compile(r"\s+")
+_SMALL = "zero one two three four five six seven eight nine ten eleven twelve thirteen fourteen fifteen sixteen seventeen eighteen nineteen".split()
+_TENS = "zero ten twenty thirty forty fifty sixty seventy eighty ninety".split()
+
+
+def expand_abbreviations(text: str) -> str:
+    """``Mr.`` -> ``mister`` etc."""
+    for rx, full in _ABBREVIATIONS:
+        text = rx.sub(full, text)
+    return text
+
+
+def lowercase(text: str) -> str:
+    """lower case"""
+    return text.lower()
+
+
+def lowercase_keep_special(text: str) -> str:
+    """lower case except for ``[...]`` tokens (noise markers and the like)"""
+    return re.sub(r"(\[[^\]]*\])|([^\[]+)", lambda m: m.group(1) or m.group(2).lower(), text)
+
+
+def collapse_whitespace(text: str) -> str:
+    """runs of whitespace -> one blank, trimmed"""
+    return _WHITESPACE.sub(" ", text).strip()
+
+
+def convert_to_ascii(text: str) -> str:
+    """transliterate to ASCII (``unidecode`` when installed, else drop the accents)"""
+    try:
+        from unidecode import unidecode
+
+        return unidecode(text)
+    except ImportError:
+        import unicodedata
+
+        return unicodedata.normalize("NFKD", text).encode("ascii", "ignore").decode("ascii")
+
+
+def _number_to_words(n: int) -> str:
+    if n < 0:
+        return "minus " + _number_to_words(-n)
+    if n < 20:
+        return _SMALL[n]
+    if n < 100:
+        return _TENS[n // 10] + ("" if n % 10 == 0 else " " + _SMALL[n % 10])
+    if n < 1000:
+        return _SMALL[n // 100] + " hundred" + ("" if n % 100 == 0 else " " + _number_to_words(n % 100))
+    for size, name in ((10 ** 9, "billion"), (10 ** 6, "million"), (1000, "thousand")):
+        if n >= size:
+            return _number_to_words(n // size) + " " + name + ("" if n % size == 0 else " " + _number_to_words(n % size))
+    return str(n)
+
+
+def normalize_numbers(text: str, with_spacing: bool = False) -> str:
+    """digits -> words (integers, ``1,000`` style separators, simple decimals)"""
+    text = re.sub(r"(\d),(\d{3})", r"\1\2", text)
+
+    def repl(m):
+        whole, frac = m.group(1), m.group(3)
+        words = _number_to_words(int(whole))
+        if frac:
+            words += " point " + " ".join(_SMALL[int(d)] for d in frac)
+        return (" %s " % words) if with_spacing else words
+
+    return re.sub(r"(\d+)(\.(\d+))?", repl, text)
+
+
+def basic_cleaners(text: str) -> str:
+    """lower case, whitespace collapsed"""
+    return collapse_whitespace(lowercase(text))
+
+
+def transliteration_cleaners(text: str) -> str:
+    """ASCII, lower case, whitespace collapsed"""
+    return collapse_whitespace(lowercase(convert_to_ascii(text)))
+
+
+def english_cleaners(text: str) -> str:
+    """ASCII, lower case, numbers and abbreviations written out, whitespace collapsed"""
+    return collapse_whitespace(expand_abbreviations(normalize_numbers(lowercase(convert_to_ascii(text)), with_spacing=True)))
+
+
+def english_cleaners_keep_special(text: str) -> str:
+    """as english_cleaners, ``[...]`` tokens untouched"""
+    return collapse_whitespace(expand_abbreviations(normalize_numbers(lowercase_keep_special(convert_to_ascii(text)), with_spacing=True)))
+
+
+def get_remove_chars(chars: str):
+    """function that deletes every character of ``chars``"""
+    table = {ord(c): None for c in chars}
+    return lambda text: text.translate(table)
+
+
+def get_replace(old: str, new: str):
+    """function that replaces ``old`` by ``new``"""
+    return lambda text: text.replace(old, new)
+
+
+def _identity_pp(text: str) -> str:
+    return text
+
+
+def get_post_processor_function(opts):
+    """
+    Text -> text function from a name of a function of this module (``"english_cleaners"``), an expression that builds one
+    (``"get_remove_chars(',/')"``), a callable, or a list of those (applied in order).
+    """
+    if not opts:
+        return _identity_pp
+    if callable(opts):
+        assert isinstance(opts("test"), str), "%r is not a function str -> str" % (opts,)
+        return opts
+    if isinstance(opts, str):
+        f = eval(opts, globals()) if ("(" in opts or "," in opts) else globals()[opts]
+        if isinstance(f, (tuple, list)):
+            f = get_post_processor_function(f)
+        assert callable(f) and isinstance(f("test"), str), "%r is not a function str -> str" % (opts,)
+        return f
+    assert isinstance(opts, (tuple, list))
+    if len(opts) == 1:
+        return get_post_processor_function(opts[0])
+    steps = [get_post_processor_function(o) for o in opts]
+
+    def chained(text: str) -> str:
+        for step in steps:
+            text = step(text)
+        return text
+
+    return chained

@@ -633,6 +633,188 @@ class VariableDataset(_WrapOne):
         return self.dataset.get_all_tags()
 
 
+class ClusteringDataset(_WrapOne):
+    """
+    One sub-dataset plus a cluster index per sequence (data key ``cluster_idx``, one int32), read from a cluster-map file in the
+    Sprint XML format: lines ``<map-item key="<seq tag>" value="<cluster>"/>`` inside ``<coprus-key-map>`` (spelled like that in those
+    files). ``single_cluster``: the legacy batch generator keeps every batch within one cluster.
+    Reference: returnn/datasets/meta.py:642-760.
+    """
+
+    def __init__(self, dataset: Dict[str, Any], cluster_map_file: str, n_clusters: int, single_cluster: bool = False, **kwargs):
+        super().__init__(**kwargs)
+        self._adopt(init_dataset(dataset, parent_dataset=self))
+        self.n_clusters = n_clusters
+        self.single_cluster = single_cluster
+        self.cluster_idx_dtype = "int32"
+        self.cluster_map = self._load_cluster_map(cluster_map_file)
+        self.num_outputs = dict(self.dataset.num_outputs)
+        self.num_outputs["cluster_idx"] = (n_clusters, 1)
+
+    def _load_cluster_map(self, filename: str) -> Dict[str, int]:
+        import re
+
+        with open(filename) as f:
+            lines = f.read().splitlines()
+        assert any("<coprus-key-map>" in ln or "<corpus-key-map>" in ln for ln in lines[:3]), "%s: expected the Sprint XML cluster-map format" % filename
+        item = re.compile(r'\s*<map-item key="(.*)" value="(.*)"/>')
+        out: Dict[str, int] = {}
+        for ln in lines:
+            m = item.match(ln)
+            if m:
+                idx = int(m.group(2))
+                assert 0 <= idx < self.n_clusters, "%s: cluster %i outside 0..%i" % (filename, idx, self.n_clusters - 1)
+                out[m.group(1)] = idx
+        return out
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        self.dataset.init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        return super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+
+    def get_data_keys(self):
+        return list(self.dataset.get_data_keys()) + ["cluster_idx"]
+
+    def get_data_dtype(self, key):
+        return self.cluster_idx_dtype if key == "cluster_idx" else self.dataset.get_data_dtype(key)
+
+    def get_data_dim(self, key):
+        return self.n_clusters if key == "cluster_idx" else self.dataset.get_data_dim(key)
+
+    def get_data_shape(self, key):
+        return [] if key == "cluster_idx" else self.dataset.get_data_shape(key)
+
+    def is_data_sparse(self, key):
+        return True if key == "cluster_idx" else self.dataset.is_data_sparse(key)
+
+    def is_less_than_num_seqs(self, n):
+        return self.dataset.is_less_than_num_seqs(n)
+
+    def get_tag(self, seq_idx):
+        return self.dataset.get_tag(seq_idx)
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        seq = super()._collect_single_seq(seq_idx)
+        if seq is None:
+            return None
+        seq.features["cluster_idx"] = numpy.array([self.cluster_map[seq.seq_tag]], dtype=self.cluster_idx_dtype)
+        return seq
+
+    def _generate_batches(self, recurrent_net, batch_size, max_seqs=-1, seq_drop=0.0, max_seq_length=None, used_data_keys=None, **kwargs):
+        if not self.single_cluster:
+            yield from super()._generate_batches(recurrent_net=recurrent_net, batch_size=batch_size, max_seqs=max_seqs, seq_drop=seq_drop,
+                                                 max_seq_length=max_seq_length if max_seq_length is not None else 2 ** 31,
+                                                 used_data_keys=used_data_keys, **kwargs)
+            return
+        from ..engine.batch import Batch
+
+        budget = NumbersDict(batch_size or 2 ** 31)
+        limit = NumbersDict(max_seq_length if max_seq_length is not None else 2 ** 31)
+        max_seqs_ = float("inf") if max_seqs == -1 else max_seqs
+        batch, batch_cluster = Batch(), None
+        for seq_idx, t_start, t_end in self.iterate_seqs(recurrent_net=recurrent_net, used_data_keys=used_data_keys):
+            length = t_end - t_start
+            if length.any_compare(limit, (lambda a, b: a > b)):
+                continue
+            if self.rnd_seq_drop.random_sample() < seq_drop:
+                continue
+            cluster = self.cluster_map[self.get_tag(seq_idx)]
+            dt, ds = batch.try_sequence_as_slice(length)
+            full = batch.num_slices >= 1 and ((dt * ds).any_compare(budget, (lambda a, b: a > b)) or ds > max_seqs_)
+            if batch.num_slices >= 1 and (full or cluster != batch_cluster):
+                yield batch
+                batch = Batch()
+            batch_cluster = cluster
+            batch.add_sequence_as_slice(seq_idx=seq_idx, seq_start_frame=t_start, length=length)
+        if batch.num_slices:
+            yield batch
+
+
+class ChunkShuffleDataset(CachedDataset2):
+    """
+    Chunks (the batches of the sub-dataset's legacy batch generator, ``batch_gen_max_seqs`` sequences or chunks each) turned into
+    sequences of their own and shuffled within a sliding cache of ``chunk_shuffle_cache`` chunks: a cheap way to decorrelate
+    neighbouring chunks of long recordings without loading everything. Tags: ``<original tag>.<running index>``.
+    Reference: returnn/datasets/meta.py:1873-2010.
+    """
+
+    def __init__(self, dataset: Dict[str, Any], chunk_shuffle_cache: int = 1000, batch_gen_batch_size: int = 5000, batch_gen_max_seqs: int = 1,
+                 batch_gen_recurrent_net: bool = True, **kwargs):
+        super().__init__(**kwargs)
+        import random
+
+        self.dataset = init_dataset(dataset, parent_dataset=self)
+        self.chunk_shuffle_cache = chunk_shuffle_cache
+        self.batch_gen_batch_size = batch_gen_batch_size
+        self.batch_gen_max_seqs = batch_gen_max_seqs
+        self.batch_gen_recurrent_net = batch_gen_recurrent_net
+        self.num_inputs, self.num_outputs, self.labels = self.dataset.num_inputs, self.dataset.num_outputs, self.dataset.labels
+        self.rng = random.Random(0)
+        self._batches = None
+        self._pool: List[DatasetSeq] = []  # chunks read from the sub-dataset and not handed out yet
+        self._made = 0  # chunks read so far
+        self._exhausted = False
+        self._last_loaded_end = 0
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        if seq_list is not None or seq_order is not None:
+            raise NotImplementedError("%s: a predefined order is not supported" % self)
+        if self.seq_ordering != "default":
+            raise NotImplementedError("%s: seq_ordering %r (order the sub-dataset instead)" % (self, self.seq_ordering))
+        super().init_seq_order(epoch=epoch)
+        self.rng.seed(epoch or 1)
+        self.dataset.init_seq_order(epoch=epoch)
+        self._batches = iter(self.dataset._generate_batches(recurrent_net=self.batch_gen_recurrent_net, batch_size=self.batch_gen_batch_size,
+                                                            max_seqs=self.batch_gen_max_seqs))
+        self._pool, self._made, self._exhausted, self._last_loaded_end = [], 0, False, 0
+        self._num_seqs = None
+        return True
+
+    def _read_chunk_batch(self) -> bool:
+        batch = next(self._batches, None)
+        if batch is None:
+            self._exhausted = True
+            return False
+        if batch.end_seq > self._last_loaded_end:
+            self.dataset.load_seqs(batch.start_seq, batch.end_seq)
+            self._last_loaded_end = batch.end_seq
+        keys = self.get_data_keys()
+        for part in batch.seqs:
+            feats = {}
+            for k in keys:
+                data = self.dataset.get_data(part.seq_idx, k)
+                if data is not None:
+                    feats[k] = data[part.seq_start_frame[k]: part.seq_end_frame[k]]
+            self._pool.append(DatasetSeq(seq_idx=-1, seq_tag="%s.%i" % (self.dataset.get_tag(part.seq_idx), self._made), features=feats))
+            self._made += 1
+        return True
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        # keep the cache full, then hand out a random member of it
+        while not self._exhausted and len(self._pool) < self.chunk_shuffle_cache:
+            self._read_chunk_batch()
+        if not self._pool:
+            return None
+        pick = self.rng.randrange(len(self._pool))
+        seq = self._pool.pop(pick)
+        seq.seq_idx = seq_idx
+        return seq
+
+    def get_data_keys(self):
+        return self.dataset.get_data_keys()
+
+    def get_target_list(self):
+        return self.dataset.get_target_list()
+
+    def get_data_dim(self, key):
+        return self.dataset.get_data_dim(key)
+
+    def get_data_dtype(self, key):
+        return self.dataset.get_data_dtype(key)
+
+    def is_data_sparse(self, key):
+        return self.dataset.is_data_sparse(key)
+
+
 class AnythingDataset(Dataset):
     """
     Empty dataset that only declares data keys and dims: for tasks that need ``extern_data`` but never read data

@@ -213,3 +213,347 @@ def test_rank_balanced_batching_equalises_real_frames():
     for step in range(len(groups)):
         ids = [int(s["seq_idx"]) for r in range(world) for s in per_rank[r][step]]
         assert len(ids) == len(set(ids)) == sum(len(b) for b in groups[step])
+
+
+def _write_stream_file(path, rng, n_seqs=7, n_classes=3, first=0):
+    from returnn_b200.datasets.hdf import NextGenHDFWriter
+
+    seqs = {}
+    with NextGenHDFWriter(str(path)) as w:
+        w.add_stream("features", "feature_sequence")
+        w.add_stream("words", "sparse", feature_names=["w%i" % i for i in range(n_classes)])
+        w.add_stream("align", "segment_alignment", feature_names=["a", "b", "c", "d"])
+        for i in range(n_seqs):
+            t = int(rng.randint(3, 9))
+            feat = rng.standard_normal((t, 4)).astype("float32")
+            word = numpy.array([(first + i) % n_classes], dtype="int32")
+            segs = numpy.array([[1, 2], [3, t - 2]], dtype="int32")
+            name = "corpus/rec%i/%i" % (first, i)
+            w.add_seq(name, {"features": feat, "words": word, "align": segs})
+            seqs[name] = (feat, word, segs)
+    return seqs
+
+
+def test_next_gen_hdf_dataset_streams(tmp_path):
+    """stream-layout files: every stream is a data key, several files, sorted order, the segment alignment expanded per frame"""
+    from returnn_b200.datasets.hdf import NextGenHDFDataset
+
+    rng = numpy.random.RandomState(3)
+    seqs = _write_stream_file(tmp_path / "a.hdf", rng)
+    seqs.update(_write_stream_file(tmp_path / "b.hdf", rng, n_seqs=4, first=1))
+    ds = NextGenHDFDataset("features", files=[str(tmp_path / "a.hdf"), str(tmp_path / "b.hdf")], seq_ordering="sorted")
+    ds.initialize()
+    assert ds.num_inputs == 4 and ds.num_outputs["words"] == [3, 1] and ds.num_outputs["align"] == [4, 1] and ds.get_data_dtype("data") == "float32"
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 11
+    lens = []
+    for i in range(ds.num_seqs):
+        ds.load_seqs(i, i + 1)
+        tag = ds.get_tag(i)
+        feat, word, segs = seqs[tag]
+        assert numpy.array_equal(ds.get_data(i, "data"), feat) and numpy.array_equal(ds.get_data(i, "features"), feat)
+        assert numpy.array_equal(ds.get_data(i, "words"), word)
+        al = ds.get_data(i, "align").reshape(-1, 2)
+        t = feat.shape[0]
+        assert al.shape[0] == t and al[:2, 0].tolist() == [1, 1] and set(al[2:, 0].tolist()) == {3}
+        assert al[:, 1].tolist() == [0, 1] + [0] * (t - 3) + [1]
+        lens.append(t)
+    assert lens == sorted(lens)
+
+
+def test_siamese_hdf_dataset_triplets(tmp_path):
+    """anchor / same-label / other-label triplets, re-drawn per epoch"""
+    from returnn_b200.datasets.hdf import SiameseHDFDataset
+
+    rng = numpy.random.RandomState(4)
+    _write_stream_file(tmp_path / "s.hdf", rng, n_seqs=12, n_classes=3)
+    ds = SiameseHDFDataset("features", seq_label_stream="words", files=[str(tmp_path / "s.hdf")], fixed_random_seed=7)
+    ds.initialize()
+    picks = []
+    for epoch in (1, 2):
+        ds.init_seq_order(epoch=epoch)
+        row = []
+        for i in range(ds.num_seqs):
+            ds.load_seqs(i, i + 1)
+            w0, w1, w2 = (int(ds.get_data(i, "words_%i" % k)[0]) for k in range(3))
+            assert w0 == w1 != w2
+            assert ds.get_data(i, "words_all").tolist() == [w0, w1, w2]
+            assert numpy.array_equal(ds.get_data(i, "data"), ds.get_data(i, "features_0"))
+            assert not numpy.array_equal(ds.get_data(i, "features_0"), ds.get_data(i, "features_1"))  # 4 sequences per class: never itself
+            row.append((ds.get_data(i, "features_1").tobytes(), ds.get_data(i, "features_2").tobytes()))
+        picks.append(row)
+    assert picks[0] != picks[1]
+    assert ds.get_data_dim("features_2") == 4 and not ds.is_data_sparse("features_1") and ds.is_data_sparse("words_0")
+
+
+def test_simple_hdf_writer_and_hdf_dataset_roundtrip(tmp_path):
+    """SimpleHDFWriter -> HDFDataset through the HDF container (the stand-in where h5py is missing)"""
+    from returnn_b200.datasets.hdf import SimpleHDFWriter, HDFDataset
+
+    fn = str(tmp_path / "d.hdf")
+    rng = numpy.random.RandomState(1)
+    seqs = []
+    with SimpleHDFWriter(fn, dim=3, ndim=2, extra_type={"classes": (5, 1, "int32")}) as w:
+        for i in range(5):
+            t = 2 + i
+            x = rng.standard_normal((t, 3)).astype("float32")
+            c = rng.randint(0, 5, size=(t,)).astype("int32")
+            w.insert_seq(x, "seq-%i" % i, extra={"classes": c})
+            seqs.append((x, c))
+    ds = HDFDataset(files=[fn])
+    ds.initialize()
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 5 and ds.get_data_dim("classes") == 5 and ds.is_data_sparse("classes")
+    for i in range(5):
+        ds.load_seqs(i, i + 1)
+        assert ds.get_tag(i) == "seq-%i" % i
+        assert numpy.array_equal(ds.get_data(i, "data"), seqs[i][0]) and numpy.array_equal(ds.get_data(i, "classes"), seqs[i][1])
+
+
+def _write_wav(path, samples, rate=16000):
+    import wave
+
+    with wave.open(str(path), "wb") as w:
+        w.setnchannels(1)
+        w.setsampwidth(2)
+        w.setframerate(rate)
+        w.writeframes((numpy.clip(samples, -1, 1) * 32767).astype("<i2").tobytes())
+
+
+def test_clustering_and_chunk_shuffle_datasets(tmp_path):
+    from returnn_b200.datasets.basic import init_dataset
+
+    cmap = tmp_path / "cluster.map"
+    cmap.write_text('<?xml version="1.0"?>\n<coprus-key-map>\n' + "".join('<map-item key="seq-%i" value="%i"/>\n' % (i, i % 3) for i in range(12)) + "</coprus-key-map>\n")
+    ds = init_dataset({"class": "ClusteringDataset", "dataset": {"class": "DummyDataset", "input_dim": 3, "output_dim": 4, "num_seqs": 12, "seq_len": 5},
+                       "cluster_map_file": str(cmap), "n_clusters": 3})
+    ds.init_seq_order(epoch=1)
+    assert "cluster_idx" in ds.get_data_keys() and ds.get_data_dim("cluster_idx") == 3 and ds.is_data_sparse("cluster_idx")
+    for i in range(12):
+        ds.load_seqs(i, i + 1)
+        assert ds.get_data(i, "cluster_idx").tolist() == [i % 3] and ds.get_data(i, "data").shape == (5, 3)
+    sub = {"class": "DummyDataset", "input_dim": 2, "output_dim": 3, "num_seqs": 9, "seq_len": 20, "chunking": "6:6"}
+    cs = init_dataset({"class": "ChunkShuffleDataset", "dataset": sub, "chunk_shuffle_cache": 8, "batch_gen_batch_size": 1000, "batch_gen_max_seqs": 1})
+    orders = []
+    for epoch in (1, 2):
+        cs.init_seq_order(epoch=epoch)
+        tags, frames, i = [], 0, 0
+        while cs.is_less_than_num_seqs(i):
+            cs.load_seqs(i, i + 1)
+            tags.append(cs.get_tag(i))
+            x = cs.get_data(i, "data")
+            assert 0 < x.shape[0] <= 6 and cs.get_data(i, "classes").shape[0] == x.shape[0]
+            frames += x.shape[0]
+            i += 1
+        assert frames == 9 * 20 and len(tags) == 9 * 4 and len(set(tags)) == len(tags)
+        orders.append(tags)
+    running = [int(t.rsplit(".", 1)[1]) for t in orders[0]]
+    assert running != sorted(running) and sorted(running) == list(range(36))  # shuffled, every chunk exactly once
+    assert orders[0] != orders[1]
+
+
+def test_stereo_hdf_dataset_with_bundle_and_normalization(tmp_path):
+    from returnn_b200.utils.h5_shim import get_h5py
+    from returnn_b200.datasets.stereo import StereoHdfDataset, DatasetWithTimeContext
+    from returnn_b200.datasets.normalization_data import NormalizationData
+    from returnn_b200.datasets.bundle_file import BundleFile
+
+    h5py = get_h5py()
+    rng = numpy.random.RandomState(0)
+    ref = {}
+    files = []
+    for fi in range(2):
+        fn = tmp_path / ("part%i.hdf" % fi)
+        with h5py.File(str(fn), "w") as f:
+            gi, go = f.create_group("inputs"), f.create_group("outputs")
+            for j in range(3):
+                t = 4 + j
+                x, y = rng.standard_normal((t, 3)) + 2.0, rng.standard_normal((t, 2)) - 1.0
+                gi.create_dataset(str(j), data=x)
+                go.create_dataset(str(j), data=y)
+                ref[(fi, j)] = (x, y)
+        files.append(str(fn))
+    bundle = tmp_path / "all.bundle"
+    bundle.write_text("\n".join(files) + "\n\n")
+    assert BundleFile(str(bundle)).number_of_dataset_files == 2
+    norm_fn = str(tmp_path / "norm.hdf")
+    NormalizationData.create_normalization_file(str(bundle), norm_fn)
+    norm = NormalizationData(norm_fn)
+    all_x = numpy.concatenate([v[0] for v in ref.values()])
+    assert numpy.allclose(norm.inputMean, all_x.mean(axis=0)) and numpy.allclose(norm.inputVariance, all_x.var(axis=0))
+    ds = StereoHdfDataset(str(bundle), normalizationFile=norm_fn)
+    ds.initialize()
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 6 and ds.num_inputs == 3 and ds.num_outputs["classes"] == (2, 2)
+    got = []
+    for i in range(6):
+        ds.load_seqs(i, i + 1)
+        got.append(ds.get_data(i, "data"))
+    stacked = numpy.concatenate(got)
+    assert abs(stacked.mean()) < 1e-5 and abs(stacked.var(axis=0).mean() - 1.0) < 1e-4
+    ctx = DatasetWithTimeContext(files[0], tau=2)
+    ctx.initialize()
+    ctx.init_seq_order(epoch=1)
+    ctx.load_seqs(0, 1)
+    x = ref[(0, 0)][0].astype("float32")
+    out = ctx.get_data(0, "data")
+    assert out.shape == (4, 15) and numpy.allclose(out[1, 6:9], x[1]) and numpy.allclose(out[0, 0:3], x[0]) and numpy.allclose(out[3, 12:15], x[3])
+    with pytest.raises(ValueError):
+        with h5py.File(str(tmp_path / "in_only.hdf"), "w") as f:
+            f.create_group("inputs").create_dataset("0", data=numpy.zeros((3, 2)))
+        StereoHdfDataset(str(tmp_path / "in_only.hdf"))
+
+
+def test_raw_wav_dataset_frames(tmp_path):
+    from returnn_b200.datasets.raw_wav import RawWavDataset
+
+    sig = numpy.sin(numpy.arange(1000) * 0.05) * 0.5
+    _write_wav(tmp_path / "a.wav", sig)
+    _write_wav(tmp_path / "b.wav", sig[:330])
+    lst = tmp_path / "wavs.lst"
+    lst.write_text("%s\n%s\n" % (tmp_path / "a.wav", tmp_path / "b.wav"))
+    ds = RawWavDataset(str(lst), frameLength=100, frameShift=50, num_outputs=1)
+    ds.init_seq_order(epoch=1)
+    ds.load_seqs(0, 2)
+    a, b = ds.get_data(0, "data"), ds.get_data(1, "data")
+    assert a.shape == (19, 100) and b.shape == (6, 100)
+    assert numpy.allclose(a[1, :50], a[0, 50:]) and numpy.allclose(a[0], sig[:100], atol=1e-4)
+    assert numpy.allclose(b[5, :80], sig[250:330], atol=1e-4) and float(numpy.abs(b[5, 80:]).max()) == 0.0
+    with pytest.raises(ValueError):
+        RawWavDataset(str(lst), frameLength=100, frameShift=50)
+
+
+def test_librispeech_timit_bliss_enwik8_corpora(tmp_path):
+    import zipfile
+    from returnn_b200.datasets.generating import LibriSpeechCorpus, TimitDataset, BlissDataset, Enwik8Corpus
+
+    rng = numpy.random.RandomState(2)
+    # --- LibriSpeech tree (wav instead of flac: no decoder for flac here)
+    root = tmp_path / "libri"
+    for sub, speaker, chapter, n in (("train-clean-100", 19, 198, 3), ("train-other-500", 20, 205, 2), ("dev-clean", 84, 121, 2)):
+        d = root / sub / str(speaker) / str(chapter)
+        d.mkdir(parents=True)
+        lines = []
+        for i in range(n):
+            _write_wav(d / ("%i-%i-%04i.wav" % (speaker, chapter, i)), rng.uniform(-0.3, 0.3, size=4000 + 800 * i))
+            lines.append("%i-%i-%04i HELLO WORLD %s" % (speaker, chapter, i, "A" * i))
+        (d / ("%i-%i.trans.txt" % (speaker, chapter))).write_text("\n".join(lines) + "\n")
+    ds = LibriSpeechCorpus(str(root), prefix="train", audio={"features": "mfcc", "num_feature_filters": 13}, chars={"vocab_file": None, "labels": list(" ABCDEHLORW")}
+                           if False else None, targets={"class": "Utf8ByteTargets"}, orth_post_process="lowercase", seq_ordering="sorted")
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 5 and ds.get_all_tags()[0] == "train-clean-100-19-198-0000"
+    ds.load_seqs(0, 5)
+    assert ds.get_data(0, "data").shape[1] == 13 and ds.get_data(0, "data").shape[0] > 10
+    assert bytes(ds.get_data(4, "orth")).decode() == "hello world aa" and ds.get_data(0, "classes").dtype == numpy.int32
+    # --- TIMIT
+    troot = tmp_path / "timit" / "train" / "dr1" / "fcjf0"
+    troot.mkdir(parents=True)
+    for utt in ("sa1", "si1027", "sx37"):
+        _write_wav(troot / (utt + ".wav"), rng.uniform(-0.3, 0.3, size=8000))
+        (troot / (utt + ".phn")).write_text("0 2000 h#\n2000 5000 aa\n5000 6400 q\n6400 8000 ux\n")
+    td = TimitDataset(str(tmp_path / "timit"), train=True, num_feature_filters=13, num_phones=39)
+    td.init_seq_order(epoch=1)
+    assert td.num_seqs == 2 and len(td.labels["classes"]) == 39
+    td.load_seqs(0, 1)
+    x, c = td.get_data(0, "data"), td.get_data(0, "classes")
+    assert x.shape[0] == c.shape[0] and x.shape[1] == 13
+    lab = td.labels["classes"]
+    assert lab[c[2]] == "sil" and lab[c[20]] == "aa" and lab[c[45]] == "uw"
+    # --- Bliss
+    _write_wav(tmp_path / "rec1.wav", rng.uniform(-0.3, 0.3, size=16000))
+    (tmp_path / "corpus.xml").write_text(
+        '<?xml version="1.0"?><corpus name="demo"><recording name="rec1" audio="rec1.wav">'
+        '<segment name="1" start="0.0" end="0.4"><orth> ab  ba </orth></segment><segment name="2" start="0.4" end="1.0"><orth>b</orth></segment>'
+        "</recording></corpus>")
+    (tmp_path / "vocab.txt").write_text(repr({"ab": 0, "ba": 1, "b": 2}))
+    bd = BlissDataset(str(tmp_path / "corpus.xml"), vocab_file=str(tmp_path / "vocab.txt"), num_feature_filters=13)
+    bd.init_seq_order(epoch=1)
+    bd.load_seqs(0, 2)
+    assert bd.get_tag(0) == "demo/rec1/1" and bd.get_data(0, "classes").tolist() == [0, 1] and bd.get_data(1, "classes").tolist() == [2]
+    assert bd.get_data(1, "data").shape[0] > bd.get_data(0, "data").shape[0]
+    # --- enwik8
+    edir = tmp_path / "enwik8"
+    edir.mkdir()
+    text = bytes(rng.randint(97, 105, size=5000).astype("uint8"))
+    with zipfile.ZipFile(str(edir / "enwik8.zip"), "w") as z:
+        z.writestr("enwik8", text)
+    ed = Enwik8Corpus(str(edir), subset="training", seq_len=50, batch_num_seqs=4)
+    ed.init_seq_order(epoch=1)
+    n = ed.num_seqs
+    assert n % 4 == 0 and n == (4000 // 50 // 4) * 4
+    ed.load_seqs(0, 8)
+    d0, c0 = ed.get_data(0, "data"), ed.get_data(0, "classes")
+    assert d0.shape == (50,) and numpy.array_equal(d0[1:], c0[:-1]) and ed.get_tag(0) == "offset_0_50"
+    # batch entry 0 of the next batch continues where entry 0 of this batch stopped
+    assert ed.get_tag(4) == "offset_50_50" and ed.get_tag(1) == "offset_%i_50" % (50 * (n // 4))
+
+
+def test_huggingface_dataset_wrapper():
+    import datasets
+    from returnn_b200.datasets.huggingface import HuggingFaceDataset
+
+    hf = datasets.Dataset.from_dict({"id": ["u%i" % i for i in range(6)], "text": ["ab", "a", "bba", "abab", "b", "aab"],
+                                     "feat": [numpy.arange(2 * (i + 1), dtype="float32").reshape(i + 1, 2).tolist() for i in range(6)],
+                                     "n": [2, 1, 3, 4, 1, 3]})
+    ds = HuggingFaceDataset(lambda: hf, data_format={"text": {"vocab": {"class": "CharacterTargets", "vocab_file": None, "labels": ["a", "b"], "unknown_label": None}},
+                                                     "feat": {"dim": 2, "ndim": 2}},
+                            sorting_seq_len_column="n", seq_ordering="sorted")
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 6 and ds.get_data_dim("text") == 2 and ds.is_data_sparse("text") and not ds.is_data_sparse("feat")
+    lens = []
+    for i in range(6):
+        ds.load_seqs(i, i + 1)
+        t = ds.get_data(i, "text")
+        lens.append(len(t))
+        corpus_idx = ds.get_corpus_seq_idx(i)
+        assert ds.get_tag(i) == "u%i" % corpus_idx and ds.get_data(i, "feat").shape == (corpus_idx + 1, 2)
+    assert lens == sorted(lens)
+
+
+def _pp_scale(td, *, epoch, seq_idx, rng, **_):
+    td.data["data"].raw_tensor = td.data["data"].raw_tensor * 2.0 + seq_idx
+    return td
+
+
+def _pp_drop_every_third(it, *, epoch, rng, **_):
+    for i, td in enumerate(it):
+        if i % 3 != 2:
+            yield td
+
+
+def test_postprocessing_dataset_worker_processes():
+    """the same sequences, in the same order, with and without worker processes; functions may come from a config (by value)"""
+    from returnn_b200.datasets.basic import init_dataset
+
+    sub = {"class": "DummyDataset", "input_dim": 3, "output_dim": 4, "num_seqs": 11, "seq_len": 6}
+
+    def read(ds, epoch):
+        ds.init_seq_order(epoch=epoch)
+        out, i = [], 0
+        while ds.is_less_than_num_seqs(i):
+            ds.load_seqs(i, i + 1)
+            out.append((ds.get_tag(i), ds.get_data(i, "data").copy(), ds.get_data(i, "classes").copy()))
+            i += 1
+        return out
+
+    plain = init_dataset({"class": "PostprocessingDataset", "dataset": sub, "map_seq": _pp_scale})
+    multi = init_dataset({"class": "PostprocessingDataset", "dataset": sub, "map_seq": _pp_scale, "num_workers": 2, "buf_size": 3})
+    try:
+        for epoch in (1, 2):
+            a, b = read(plain, epoch), read(multi, epoch)
+            assert len(a) == len(b) == 11
+            for (ta, xa, ca), (tb, xb, cb) in zip(a, b):
+                assert ta == tb and numpy.array_equal(xa, xb) and numpy.array_equal(ca, cb)
+    finally:
+        multi.finish_epoch(free_resources=True)
+    # a stream function per worker: every worker drops each third sequence of ITS share; functions defined in an exec'd config
+    cfg = {"__name__": "__returnn_config__"}
+    exec("def drop(it, *, epoch, rng, **_):\n    for i, td in enumerate(it):\n        if i % 3 != 2:\n            yield td\n", cfg)
+    stream = init_dataset({"class": "PostprocessingDataset", "dataset": sub, "map_seq_stream": cfg["drop"], "num_workers": 2})
+    try:
+        tags = [t for t, _, _ in read(stream, 1)]
+        # worker 0 has seqs 0,2,4,6,8,10 and drops its 3rd and 6th (4, 10); worker 1 has 1,3,5,7,9 and drops 5
+        assert tags == ["seq-%i" % i for i in (0, 1, 2, 3, 6, 7, 8, 9)], tags
+        assert stream.num_seqs == 8
+    finally:
+        stream.finish_epoch(free_resources=True)

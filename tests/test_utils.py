@@ -264,3 +264,41 @@ def test_tools_on_small_inputs(tmp_path):
 
     (tmp_path / "x.pkl").write_bytes(pickle.dumps({"a": [1, 2]}))
     assert eval(run("dump-pickle.py", tmp_path / "x.pkl")) == {"a": [1, 2]}
+
+
+def test_task_system_pickler_sends_config_functions_by_value(tmp_path):
+    """functions, classes, closures and recursion from an exec'd module survive a trip into a fresh interpreter; big arrays use shared memory"""
+    import subprocess
+    import sys
+    import os
+    import numpy
+    from returnn_b200.utils import task_system as ts
+
+    src = (
+        "import numpy\nSCALE = 3\n"
+        "def helper(x):\n    return x * SCALE\n"
+        "def fn(x, *, k=2):\n    return helper(x) + k + int(numpy.sum([1, 2]))\n"
+        "def fact(n):\n    return 1 if n <= 1 else n * fact(n - 1)\n"
+        "class Aug:\n    factor = 5\n    def __init__(self, a):\n        self.a = a\n    def __call__(self, x):\n        return helper(x) * self.factor + self.a\n"
+        "def make_closure(c):\n    def inner(x):\n        return x + c\n    return inner\n")
+    g = {"__name__": "__returnn_config__"}
+    exec(compile(src, "cfg", "exec"), g)
+    objs = {"fn": g["fn"], "fact": g["fact"], "aug": g["Aug"](7), "clo": g["make_closure"](11), "lam": (lambda x: x * 2),
+            "arr": numpy.arange(600000, dtype="float32"), "mod": numpy, "meth": g["Aug"](1).__call__}
+    fn = tmp_path / "objs.pkl"
+    fn.write_bytes(ts.dumps(objs, shared_mem=True))
+    assert fn.stat().st_size < 10000  # the 2.4 MB array went through shared memory
+    code = ("import pickle; o = pickle.load(open(%r, 'rb')); "
+            "print(o['fn'](4), o['fact'](5), o['aug'](2), o['clo'](1), o['lam'](21), int(o['arr'][-1]), o['mod'].__name__, o['meth'](1))" % str(fn))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.check_output([sys.executable, "-c", code], cwd=root, env=dict(os.environ, PYTHONPATH=root)).decode().split()
+    assert out == ["17", "120", "37", "12", "42", "599999", "numpy", "16"]
+    # importable functions still go by name
+    assert b"numpy" in ts.dumps(numpy.sum) and len(ts.dumps(numpy.sum)) < 100
+    sh = ts.SharedNumpyArray.from_array(numpy.arange(10))
+    sh2 = ts.loads(ts.dumps(sh))
+    sh2.array[3] = 77
+    assert sh.array[3] == 77
+    sh2.close()
+    sh.close()
+    assert ts.next_power_of_two(5) == 8 and ts.next_power_of_two(8) == 8
