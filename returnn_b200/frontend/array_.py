@@ -74,11 +74,10 @@ def num_elements_of_shape(dims: Union[Dim, Sequence[Dim]], *, use_mask: bool = T
     if isinstance(dims, Dim):
         dims = [dims]
     n: Any = 1
-    done = set()
-    dims = list(dims)
-    # dynamic dims with sizes over other dims in the list: sum of sizes
-    for d in dims:
-        if d in done:
+    remaining = list(dims)  # a static dim may occur more than once (a square weight matrix): every occurrence counts
+    # dynamic dims with sizes over other dims in the list: sum of sizes, which accounts for those other dims too
+    for d in list(remaining):
+        if d not in remaining:
             continue
         if d.is_dynamic() and not d.is_batch_dim() and use_mask and d.dyn_size_ext is not None and d.dyn_size_ext.dims:
             ext = d.dyn_size_ext
@@ -86,13 +85,12 @@ def num_elements_of_shape(dims: Union[Dim, Sequence[Dim]], *, use_mask: bool = T
             total = ext.raw_tensor.sum()
             # lengths on the device (static-shape / CUDA-graph regime): stay on the device, the count becomes a scalar Tensor
             n = n * (total if getattr(total, "is_cuda", False) else int(total))
-            done.add(d)
+            remaining.remove(d)
             for dd in ext.dims:
-                done.add(dd)
-    for d in dims:
-        if d not in done:
-            n = n * d.get_dim_value()
-            done.add(d)
+                if dd in remaining:
+                    remaining.remove(dd)
+    for d in remaining:
+        n = n * d.get_dim_value()
     if isinstance(n, torch.Tensor):
         return Tensor("num_elements", dims=[], dtype=dtype_name(n.dtype), raw_tensor=n)
     return n

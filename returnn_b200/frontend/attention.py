@@ -265,14 +265,28 @@ def _expand_at(x: Tensor, new_dim: Dim, like_accum: Tensor, accum_axis: Dim) -> 
 
 
 def _apply_rope(x: Tensor, pos_enc: Tensor, feat_dim: Dim) -> Tensor:
-    """rotate pairs (x[..., :D/2], x[..., D/2:]) by the angles encoded in pos_enc = [sin | cos]"""
+    """
+    Rotary position embedding: the features are D/2 complex numbers stored interleaved, ``(x[2i], x[2i+1]) = (re, im)``, and
+    number i is multiplied by ``cos_i + j sin_i``, where ``pos_enc = [sin_0..sin_{D/2-1} | cos_0..cos_{D/2-1}]``
+    (the layout of returnn/frontend/attention.py:535; HuggingFace's Llama stores (x[i], x[i + D/2]) instead, which is why
+    its q/k projection columns are permuted on import).
+    """
     half = feat_dim.div_left(2)
-    x1, x2 = _a.split(x, axis=feat_dim, out_dims=[half, half])
     sin, cos = _a.split(pos_enc, axis=feat_dim, out_dims=[half, half])
-    r1 = x1 * cos - x2 * sin
-    r2 = x1 * sin + x2 * cos
-    out, _ = _a.concat((r1, half), (r2, half), out_dim=feat_dim)
+    pair = Dim(2, name="complex")
+    xs = _a.split_dims(x, axis=feat_dim, dims=(half, pair))
+    re, im = _a.unstack(xs, axis=pair)
+    out, _ = _a.stack((re * cos - im * sin, re * sin + im * cos), out_dim=pair)
+    out, _ = _a.merge_dims(out, dims=(half, pair), out_dim=feat_dim)
     return out
+
+
+def _rope_base(head_dim: Dim) -> float:
+    """
+    ``sinusoidal_positional_encoding`` spaces its D/2 frequencies as ``base ** (-i / (D/2 - 1))``; RoPE as commonly defined
+    uses ``10000 ** (-2i / D)``. Both agree for ``base = 10000 ** (1 - 2 / D)`` (returnn/frontend/attention.py:492).
+    """
+    return 10_000 ** (1 - 2 / head_dim.dimension)
 
 
 class RotaryPosSelfAttention(SelfAttention):
@@ -280,7 +294,7 @@ class RotaryPosSelfAttention(SelfAttention):
 
     def __call__(self, source: Tensor, *, axis: Dim) -> Tensor:
         q, k, v = self.forward_qkv(source)
-        pos_enc = sinusoidal_positional_encoding(spatial_dim=axis, feat_dim=self.key_dim_per_head, device=source.device)
+        pos_enc = sinusoidal_positional_encoding(spatial_dim=axis, feat_dim=self.key_dim_per_head, base=_rope_base(self.key_dim_per_head), device=source.device)
         q = _apply_rope(q, pos_enc, self.key_dim_per_head)
         k = _apply_rope(k, pos_enc, self.key_dim_per_head)
         kv_axis = Dim(None, name="%s-kv" % axis.name)
@@ -297,9 +311,10 @@ class RotaryPosCausalSelfAttention(CausalSelfAttention):
         if axis == single_step_dim:
             assert state
             offset = state.accum_axis.get_dim_value() if state.accum_axis.dimension != 0 else 0
-            pos_enc = sinusoidal_positional_encoding(spatial_dim=single_step_dim, offset=offset, feat_dim=self.key_dim_per_head, device=source.device)
+            pos_enc = sinusoidal_positional_encoding(spatial_dim=single_step_dim, offset=offset, feat_dim=self.key_dim_per_head,
+                                                     base=_rope_base(self.key_dim_per_head), device=source.device)
         else:
-            pos_enc = sinusoidal_positional_encoding(spatial_dim=axis, feat_dim=self.key_dim_per_head, device=source.device)
+            pos_enc = sinusoidal_positional_encoding(spatial_dim=axis, feat_dim=self.key_dim_per_head, base=_rope_base(self.key_dim_per_head), device=source.device)
         q = _apply_rope(q, pos_enc, self.key_dim_per_head)
         k = _apply_rope(k, pos_enc, self.key_dim_per_head)
         k, v, hist_dim, new_state, causal_dim = _causal_self_att_step(k, v, axis=axis, state=state, self=self)

@@ -57,5 +57,8 @@ def build_dict(cls: Union[type, Any], **kwargs) -> Dict[str, Any]:
     """inverse: dict which build_from_dict turns into cls(**kwargs)"""
     name = "%s.%s" % (cls.__module__, cls.__qualname__)
     if name.startswith("returnn_b200.frontend."):
-        name = "rf." + cls.__qualname__
+        from .. import frontend as rf
+
+        if getattr(rf, cls.__qualname__, None) is cls:  # the short form only for what the package namespace exports
+            name = "rf." + cls.__qualname__
     return {"class": name, **kwargs}

@@ -249,21 +249,8 @@ class ConformerEncoder(ISeqDownsamplingEncoder):
             raise TypeError("unexpected pos_enc type %r" % (pos_enc,))
         self.pos_enc = pos_enc
         self.input_dropout = input_dropout
-        if not encoder_layer or isinstance(encoder_layer, (dict, type)):
-            opts = dict(out_dim=out_dim, ff_dim=ff_dim, ff_activation=ff_activation, dropout=dropout,
-                        conv_kernel_size=conv_kernel_size, conv_norm=conv_norm, num_heads=num_heads, att_dropout=att_dropout)
-            opts = {k: v for k, v in opts.items() if v is not NotSpecified}
-            if encoder_layer_opts:
-                opts.update(encoder_layer_opts)
-            if not encoder_layer:
-                encoder_layer = ConformerEncoderLayer(**opts)
-            elif isinstance(encoder_layer, type):
-                encoder_layer = encoder_layer(**opts)
-            else:
-                opts = {k: v for k, v in opts.items() if k not in encoder_layer}
-                encoder_layer = build_from_dict(encoder_layer, **opts)
-        elif not callable(encoder_layer):
-            raise TypeError("%s: invalid non-callable encoder_layer %r" % (self, encoder_layer))
+        encoder_layer = make_encoder_layer(encoder_layer, encoder_layer_opts, owner=self, out_dim=out_dim, ff_dim=ff_dim, ff_activation=ff_activation,
+                                           dropout=dropout, conv_kernel_size=conv_kernel_size, conv_norm=conv_norm, num_heads=num_heads, att_dropout=att_dropout)
         self.layers = sequential(_copy.deepcopy(encoder_layer) for _ in range(num_layers))
 
     def __call__(self, source: Tensor, *, in_spatial_dim: Dim, collected_outputs: Optional[Dict[str, Tensor]] = None) -> Tuple[Tensor, Dim]:
@@ -281,6 +268,26 @@ class ConformerEncoder(ISeqDownsamplingEncoder):
         x = dropout(x, self.input_dropout, axis=self.dropout_broadcast and self.out_dim)
         x = self.layers(x, spatial_dim=out_spatial_dim, collected_outputs=collected_outputs)
         return x, out_spatial_dim
+
+
+def make_encoder_layer(encoder_layer, encoder_layer_opts: Optional[Dict[str, Any]], *, owner=None, **common_opts):
+    """
+    The prototype layer of an encoder stack from ``None`` (a :class:`ConformerEncoderLayer`), a class, a dict for
+    ``build_from_dict`` (the common options fill in what the dict does not name) or a ready module / callable.
+    Options that are ``NotSpecified`` are left to the layer's defaults.
+    """
+    if encoder_layer and not isinstance(encoder_layer, (dict, type)):
+        if not callable(encoder_layer):
+            raise TypeError("%s: invalid non-callable encoder_layer %r" % (owner, encoder_layer))
+        return encoder_layer
+    opts = {k: v for k, v in common_opts.items() if v is not NotSpecified}
+    if encoder_layer_opts:
+        opts.update(encoder_layer_opts)
+    if not encoder_layer:
+        return ConformerEncoderLayer(**opts)
+    if isinstance(encoder_layer, type):
+        return encoder_layer(**opts)
+    return build_from_dict(encoder_layer, **{k: v for k, v in opts.items() if k not in encoder_layer})
 
 
 def make_ff(*, out_dim: Dim, ff, ff_dim, ff_activation, dropout: float):

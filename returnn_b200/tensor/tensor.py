@@ -515,6 +515,12 @@ class Tensor:
         """like copy_compatible_to_dims(other.dims)"""
         return self.copy_compatible_to_dims(other.dims, unbroadcast=unbroadcast)
 
+    def num_elements(self):
+        """number of (non-padded) elements: an int, or a scalar Tensor when sequence lengths live on the device"""
+        from .. import frontend as rf
+
+        return rf.num_elements_of_shape(self.dims)
+
     def copy_masked(self, mask_value, *, dims: Optional[Sequence[Dim]] = None, allow_int=NotSpecified) -> "Tensor":
         """padded frames of all dynamic dims (or given dims) set to mask_value"""
         from .. import frontend as rf

@@ -182,6 +182,48 @@ def _fwd_encoder(api, env, x, time):
     return y, out_time
 
 
+def _conformer_v2(api):
+    i = api.Dim(10, name="in")
+    model = api.Dim(8, name="model")
+    C, C2 = api.mod("encoder.conformer"), api.mod("encoder.conformer_v2")
+
+    class Both(api.rf.Module):
+        def __init__(self):
+            super().__init__()
+            self.frontend = C2.ConformerFrontend(
+                i, model, input_embedding_scale=8 ** 0.5, input_dropout=0.1,
+                input_layer=C.ConformerConvSubsample(i, out_dims=[api.Dim(3, name="c1"), api.Dim(4, name="c2")], filter_sizes=[(3, 3), (3, 3)],
+                                                     pool_sizes=[(1, 2)], strides=[(1, 1), (2, 1)]))
+            self.encoder = C2.ConformerEncoderV2(model, num_layers=2, num_heads=2, ff_dim=api.Dim(16, name="ff"), conv_kernel_size=5,
+                                                 encoder_layer_opts={"conv_norm": api.rf.LayerNorm})
+
+        def __call__(self, x, *, in_spatial_dim):
+            x, out_time = self.frontend(x, in_spatial_dim=in_spatial_dim)
+            return self.encoder(x, spatial_dim=out_time), out_time
+
+    return {"module": Both(), "in_dim": i}
+
+
+def _e_branchformer_encoder(api):
+    i = api.Dim(10, name="in")
+    model = api.Dim(8, name="model")
+    C, C2, E = api.mod("encoder.conformer"), api.mod("encoder.conformer_v2"), api.mod("encoder.e_branchformer")
+
+    class Both(api.rf.Module):
+        def __init__(self):
+            super().__init__()
+            self.frontend = C2.ConformerFrontend(i, model, input_layer=C.ConformerConvSubsample(
+                i, out_dims=[api.Dim(3, name="c1"), api.Dim(4, name="c2")], filter_sizes=[(3, 3), (3, 3)], pool_sizes=[(1, 2)], strides=[(1, 1), (2, 1)]))
+            self.encoder = C2.ConformerEncoderV2(model, num_layers=2, encoder_layer=api.rf.build_dict(
+                E.EBranchformerLayer, ff_dim=16, num_heads=2, cgmlp_ff_dim=12, cgmlp_conv_kernel=5, merge_conv_kernel=3))
+
+        def __call__(self, x, *, in_spatial_dim):
+            x, out_time = self.frontend(x, in_spatial_dim=in_spatial_dim)
+            return self.encoder(x, spatial_dim=out_time), out_time
+
+    return {"module": Both(), "in_dim": i}
+
+
 def _transformer_encoder(api):
     v = api.Dim(13, name="vocab")
     m = api.mod("encoder.transformer").TransformerEncoder(
@@ -198,6 +240,22 @@ def _transformer_decoder_lm(api):
     v = api.Dim(13, name="vocab")
     m = api.mod("decoder.transformer").TransformerDecoder(None, v, api.Dim(8, name="model"), num_layers=2, num_heads=2, ff_dim=api.Dim(16, name="ff"),
                                                       dropout=0.1, att_dropout=0.1)
+    return {"module": m, "in_dim": v}
+
+
+def _llama_style_decoder(api):
+    if api.name == "reference":
+        # the reference's default RoPE goes through torch.compile, whose C++ build has no OpenMP spec file on this image; its own
+        # eager restatement of the same op (used by the reference whenever it traces statically) takes its place
+        import returnn.torch.util.rope as ref_rope
+
+        ref_rope.apply_rope = ref_rope.apply_rope_plain
+    v = api.Dim(13, name="vocab")
+    D = api.mod("decoder.transformer")
+    m = D.TransformerDecoder(
+        None, v, api.Dim(8, name="model"), num_layers=2, num_heads=2, pos_enc=None, norm=api.rf.build_dict(api.rf.RMSNorm),
+        ff=api.rf.build_dict(D.FeedForwardGated, ff_dim=12), layer_opts=dict(self_att=api.rf.build_dict(api.rf.RotaryPosCausalSelfAttention, with_bias=False)),
+        share_embedding=False, dropout=0.1, att_dropout=0.1)
     return {"module": m, "in_dim": v}
 
 
@@ -225,8 +283,11 @@ CASES = [
     Case("conformer_conv_subsample", _conformer_subsample, _fwd_subsample, in_feat=10, min_len=7),
     Case("conformer_layer", _conformer_layer, _fwd_spatial, in_feat=8, atol=2e-5),
     Case("conformer_encoder", _conformer_encoder, _fwd_encoder, in_feat=10, atol=5e-5, min_len=7),
+    Case("conformer_frontend_and_encoder_v2", _conformer_v2, _fwd_encoder, in_feat=10, atol=5e-5, min_len=7),
+    Case("e_branchformer_encoder", _e_branchformer_encoder, _fwd_encoder, in_feat=10, atol=5e-5, min_len=7),
     Case("transformer_encoder", _transformer_encoder, _fwd_tr_encoder, sparse_vocab=13, atol=2e-5),
     Case("transformer_decoder_lm", _transformer_decoder_lm, _fwd_decoder_lm, sparse_vocab=13, atol=2e-5),
+    Case("llama_style_decoder_rope_rmsnorm_swiglu", _llama_style_decoder, _fwd_decoder_lm, sparse_vocab=13, atol=2e-5),
 ]
 
 
