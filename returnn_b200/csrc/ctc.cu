@@ -10,6 +10,7 @@
 // The [T, V] log-probabilities are never materialised. Scratch (global memory, given by the caller):
 // lse [N], lp [N, SE], ab [N, SE] floats with SE = 2 * max_target_len + 1, and logp [B].
 // Infeasible alignments (fewer frames than needed) give loss 0 and zero gradient (zero_infinity semantics).
+#include <algorithm>
 #include "common.cuh"
 
 namespace {
@@ -78,14 +79,25 @@ ctc_lse_gather_kernel(const void* __restrict__ logits, int is_bf16, const int* _
   }
 }
 
-// one CTA per sequence; dynamic shared memory: 2 * SE floats (alpha/beta double buffer) + SE ints (classes)
-__global__ void __launch_bounds__(256)
-ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, const int* __restrict__ cu, const int* __restrict__ targets,
-                      const int* __restrict__ tgt_lens, float* __restrict__ logp_out, float* __restrict__ loss, int s_pitch, int SE, int blank) {
+// One CTA per sequence; dynamic shared memory: 4 * SE floats (double buffers of alpha and of beta) + SE ints (classes).
+// The forward and the backward recursion do not depend on each other, so they run at the same time in the two halves of the CTA
+// (threads [0, G) alpha, [G, 2G) beta, one lattice state per thread), each half with its own named barrier. A frame of a recursion
+// is a short dependent chain (two shared-memory reads, two log-adds, a barrier); the log-probabilities it needs are fetched
+// kCtcDepth frames ahead into registers, so that no global-memory latency sits on that chain. alpha goes to `al`, beta (including
+// the frame's own log-probability) to `be`; the gradient kernel forms the occupancies exp(alpha + beta - lp - logP) from them.
+constexpr int kCtcDepth = 8;
+
+__device__ __forceinline__ void bar_sync_named(int id, int count) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+
+__global__ void __launch_bounds__(512)
+ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ al, float* __restrict__ be, const int* __restrict__ cu,
+                      const int* __restrict__ targets, const int* __restrict__ tgt_lens, float* __restrict__ logp_out, float* __restrict__ loss,
+                      int s_pitch, int SE, int blank) {
   extern __shared__ float sm[];
-  float* buf0 = sm;
-  float* buf1 = sm + SE;
-  int* cls = reinterpret_cast<int*>(sm + 2 * SE);
+  int* cls = reinterpret_cast<int*>(sm + 4 * SE);
+  const int G = blockDim.x >> 1;
   const int b = blockIdx.x;
   const int r0 = cu[b];
   const int T = cu[b + 1] - r0;
@@ -100,97 +112,103 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, cons
     }
     return;
   }
-  if (se <= (int)blockDim.x) {
-    // The usual case (at most 127 labels): one state per thread. A frame of the recursion is then a short dependent chain
-    // (two shared-memory reads, two log-adds, a barrier); the log-probability of the next frame (and, in the beta pass, the
-    // stored alpha) is fetched one frame ahead so that no global load sits on that chain.
-    const int s = threadIdx.x;
+  if (se <= G) {
+    const int dir = threadIdx.x >= G ? 1 : 0;
+    const int s = threadIdx.x - dir * G;
+    const int gb = (se + 31) & ~31;  // threads of this direction that take part (whole warps)
+    if (s >= gb) return;
     const bool act = s < se;
-    const bool skip_a = act && s >= 2 && (s & 1) && cls[s] != cls[s - 2];
-    const bool skip_b = act && s + 2 < se && (s & 1) && cls[s] != cls[s + 2];
-    float* prev = buf0;
-    float* cur = buf1;
-    if (act) {
-      const float a = (s < 2) ? lp[(size_t)r0 * SE + s] : kNegInf;
-      prev[s] = a;
-      ab[(size_t)r0 * SE + s] = a;
-    }
-    float l_next = (act && T > 1) ? lp[(size_t)(r0 + 1) * SE + s] : 0.f;
-    __syncthreads();
-    for (int t = 1; t < T; ++t) {
-      const size_t row = (size_t)(r0 + t) * SE;
-      const float l = l_next;
-      if (act && t + 1 < T) l_next = lp[row + SE + s];
+    float* prev = sm + dir * 2 * SE;
+    float* cur = prev + SE;
+    const int bar = 1 + dir;
+    float lq[kCtcDepth];
+    if (dir == 0) {
+      const bool skip = act && s >= 2 && (s & 1) && cls[s] != cls[s - 2];
       if (act) {
-        float a = prev[s];
-        if (s >= 1) a = log_add(a, prev[s - 1]);
-        if (skip_a) a = log_add(a, prev[s - 2]);
-        a = (a == kNegInf) ? kNegInf : a + l;
-        cur[s] = a;
-        ab[row + s] = a;
+        const float a = (s < 2) ? lp[(size_t)r0 * SE + s] : kNegInf;
+        prev[s] = a;
+        al[(size_t)r0 * SE + s] = a;
       }
-      __syncthreads();
-      float* tmp = prev;
-      prev = cur;
-      cur = tmp;
-    }
-    __shared__ float logp_fast;
-    if (threadIdx.x == 0) {
-      float lpz = prev[se - 1];
-      if (se >= 2) lpz = log_add(lpz, prev[se - 2]);
-      logp_fast = lpz;
-      logp_out[b] = lpz;
-      loss[b] = (lpz == kNegInf) ? 0.f : -lpz;
-    }
-    __syncthreads();
-    const float logp = logp_fast;
-    if (logp == kNegInf) return;  // infeasible: the gradient kernel writes zeros
-    {
-      const size_t row = (size_t)(r0 + T - 1) * SE;
+#pragma unroll
+      for (int j = 0; j < kCtcDepth; ++j) lq[j] = (act && 1 + j < T) ? lp[(size_t)(r0 + 1 + j) * SE + s] : 0.f;
+      bar_sync_named(bar, gb);
+      for (int t0 = 1; t0 < T; t0 += kCtcDepth) {
+        float nq[kCtcDepth];
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) nq[j] = (act && t0 + kCtcDepth + j < T) ? lp[(size_t)(r0 + t0 + kCtcDepth + j) * SE + s] : 0.f;
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) {
+          const int t = t0 + j;
+          if (t < T) {  // uniform over the CTA
+            if (act) {
+              float a = prev[s];
+              if (s >= 1) a = log_add(a, prev[s - 1]);
+              if (skip) a = log_add(a, prev[s - 2]);
+              a = (a == kNegInf) ? kNegInf : a + lq[j];
+              cur[s] = a;
+              al[(size_t)(r0 + t) * SE + s] = a;
+            }
+            bar_sync_named(bar, gb);
+            float* tmp = prev;
+            prev = cur;
+            cur = tmp;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) lq[j] = nq[j];
+      }
+      if (s == 0) {
+        float lpz = prev[se - 1];
+        if (se >= 2) lpz = log_add(lpz, prev[se - 2]);
+        logp_out[b] = lpz;
+        loss[b] = (lpz == kNegInf) ? 0.f : -lpz;
+      }
+    } else {
+      const bool skip = act && s + 2 < se && (s & 1) && cls[s] != cls[s + 2];
       if (act) {
-        const float lt = lp[row + s];
-        const float bt = (s >= se - 2) ? lt : kNegInf;
+        const size_t row = (size_t)(r0 + T - 1) * SE;
+        const float bt = (s >= se - 2) ? lp[row + s] : kNegInf;
         prev[s] = bt;
-        const float a = ab[row + s];  // written by this thread in the alpha pass
-        ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lt - logp);
+        be[row + s] = bt;
       }
-    }
-    float a_next = 0.f;
-    l_next = 0.f;
-    if (act && T > 1) {
-      l_next = lp[(size_t)(r0 + T - 2) * SE + s];
-      a_next = ab[(size_t)(r0 + T - 2) * SE + s];
-    }
-    __syncthreads();
-    for (int t = T - 2; t >= 0; --t) {
-      const size_t row = (size_t)(r0 + t) * SE;
-      const float l = l_next, a = a_next;
-      if (act && t > 0) {
-        l_next = lp[row - SE + s];
-        a_next = ab[row - SE + s];
+#pragma unroll
+      for (int j = 0; j < kCtcDepth; ++j) lq[j] = (act && T - 2 - j >= 0) ? lp[(size_t)(r0 + T - 2 - j) * SE + s] : 0.f;
+      bar_sync_named(bar, gb);
+      for (int t0 = T - 2; t0 >= 0; t0 -= kCtcDepth) {
+        float nq[kCtcDepth];
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) nq[j] = (act && t0 - kCtcDepth - j >= 0) ? lp[(size_t)(r0 + t0 - kCtcDepth - j) * SE + s] : 0.f;
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) {
+          const int t = t0 - j;
+          if (t >= 0) {
+            if (act) {
+              float bt = prev[s];
+              if (s + 1 < se) bt = log_add(bt, prev[s + 1]);
+              if (skip) bt = log_add(bt, prev[s + 2]);
+              bt = (bt == kNegInf) ? kNegInf : bt + lq[j];
+              cur[s] = bt;
+              be[(size_t)(r0 + t) * SE + s] = bt;
+            }
+            bar_sync_named(bar, gb);
+            float* tmp = prev;
+            prev = cur;
+            cur = tmp;
+          }
+        }
+#pragma unroll
+        for (int j = 0; j < kCtcDepth; ++j) lq[j] = nq[j];
       }
-      if (act) {
-        float bt = prev[s];
-        if (s + 1 < se) bt = log_add(bt, prev[s + 1]);
-        if (skip_b) bt = log_add(bt, prev[s + 2]);
-        bt = (bt == kNegInf) ? kNegInf : bt + l;
-        cur[s] = bt;
-        ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - l - logp);
-      }
-      __syncthreads();
-      float* tmp = prev;
-      prev = cur;
-      cur = tmp;
     }
     return;
   }
-  // ---- general case (more states than threads): alpha
-  float* prev = buf0;
-  float* cur = buf1;
+  // ---- general case (more states than threads per direction): the whole CTA runs alpha, then beta
+  float* prev = sm;
+  float* cur = sm + SE;
   for (int s = threadIdx.x; s < se; s += blockDim.x) {
     const float a = (s < 2) ? lp[(size_t)r0 * SE + s] : kNegInf;
     prev[s] = a;
-    ab[(size_t)r0 * SE + s] = a;
+    al[(size_t)r0 * SE + s] = a;
   }
   __syncthreads();
   for (int t = 1; t < T; ++t) {
@@ -201,32 +219,26 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, cons
       if (s >= 2 && (s & 1) && cls[s] != cls[s - 2]) a = log_add(a, prev[s - 2]);
       a = (a == kNegInf) ? kNegInf : a + lp[row + s];
       cur[s] = a;
-      ab[row + s] = a;
+      al[row + s] = a;
     }
     __syncthreads();
     float* tmp = prev;
     prev = cur;
     cur = tmp;
   }
-  __shared__ float logp_sh;
   if (threadIdx.x == 0) {
     float lpz = prev[se - 1];
     if (se >= 2) lpz = log_add(lpz, prev[se - 2]);
-    logp_sh = lpz;
     logp_out[b] = lpz;
     loss[b] = (lpz == kNegInf) ? 0.f : -lpz;
   }
   __syncthreads();
-  const float logp = logp_sh;
-  if (logp == kNegInf) return;  // infeasible: the gradient kernel writes zeros
-  // ---- beta, and gamma = exp(alpha + beta - lp - logP) written over ab
   {
     const size_t row = (size_t)(r0 + T - 1) * SE;
     for (int s = threadIdx.x; s < se; s += blockDim.x) {
       const float bt = (s >= se - 2) ? lp[row + s] : kNegInf;
       prev[s] = bt;
-      const float a = ab[row + s];
-      ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lp[row + s] - logp);
+      be[row + s] = bt;
     }
   }
   __syncthreads();
@@ -236,11 +248,9 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, cons
       float bt = prev[s];
       if (s + 1 < se) bt = log_add(bt, prev[s + 1]);
       if (s + 2 < se && (s & 1) && cls[s] != cls[s + 2]) bt = log_add(bt, prev[s + 2]);
-      const float l = lp[row + s];
-      bt = (bt == kNegInf) ? kNegInf : bt + l;
+      bt = (bt == kNegInf) ? kNegInf : bt + lp[row + s];
       cur[s] = bt;
-      const float a = ab[row + s];
-      ab[row + s] = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - l - logp);
+      be[row + s] = bt;
     }
     __syncthreads();
     float* tmp = prev;
@@ -252,9 +262,9 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ ab, cons
 // one CTA handles `frames_per_cta` consecutive frames; dynamic shared memory: V floats (dense class occupancy)
 __global__ void __launch_bounds__(256)
 ctc_grad_kernel(const void* __restrict__ logits, int is_bf16, const int* __restrict__ row_batch, const int* __restrict__ targets,
-                const int* __restrict__ tgt_lens, const float* __restrict__ lse, const float* __restrict__ gamma,
-                const float* __restrict__ logp, void* __restrict__ grad, int n_rows, int V, int s_pitch, int SE, int blank,
-                int frames_per_cta) {
+                const int* __restrict__ tgt_lens, const float* __restrict__ lse, const float* __restrict__ lp, const float* __restrict__ al,
+                const float* __restrict__ be, const float* __restrict__ logp, void* __restrict__ grad, int n_rows, int V, int s_pitch, int SE,
+                int blank, int frames_per_cta) {
   extern __shared__ float post[];
   for (int v = threadIdx.x; v < V; v += blockDim.x) post[v] = 0.f;
   __syncthreads();
@@ -264,11 +274,14 @@ ctc_grad_kernel(const void* __restrict__ logits, int is_bf16, const int* __restr
   const int per16 = 16 / elem;
   for (int r = r_begin; r < r_end; ++r) {
     const int b = row_batch[r];
-    const bool feasible = logp[b] != kNegInf;
+    const float lpz = logp[b];
+    const bool feasible = lpz != kNegInf;
     const int se = 2 * tgt_lens[b] + 1;
     if (feasible) {
       for (int s = threadIdx.x; s < se; s += blockDim.x) {
-        const float g = gamma[(size_t)r * SE + s];
+        // occupancy of state s at this frame; beta already contains the frame's own log-probability
+        const float a = al[(size_t)r * SE + s], bt = be[(size_t)r * SE + s];
+        const float g = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lp[(size_t)r * SE + s] - lpz);
         if (g != 0.f) {
           const int c = (s & 1) ? targets[(size_t)b * s_pitch + (s >> 1)] : blank;
           atomicAdd(&post[c], g);
@@ -308,13 +321,13 @@ ctc_grad_kernel(const void* __restrict__ logits, int is_bf16, const int* __restr
 
 }  // namespace
 
-// scratch: at least n_rows * (1 + 2 * SE) + batch floats, SE = 2 * max_s + 1
+// scratch: at least n_rows * (1 + 3 * SE) + batch floats, SE = 2 * max_s + 1
 RB_EXPORT int rb200_ctc_loss(const void* logits, int is_bf16, const int* cu, const int* row_batch, const int* targets, const int* tgt_lens,
                              float* loss, void* grad, float* scratch, int batch, int n_rows, int V, int s_pitch, int max_s, int blank,
                              long long scratch_floats, cudaStream_t stream) {
   if (batch <= 0) return RB_OK;
   const int SE = 2 * max_s + 1;
-  const long long need = (long long)n_rows * (1 + 2 * SE) + batch;
+  const long long need = (long long)n_rows * (1 + 3 * SE) + batch;
   if (scratch_floats < need) {
     rb_set_error("ctc_loss: scratch of %lld floats given, %lld needed", scratch_floats, need);
     return RB_ERR_ARG;
@@ -323,7 +336,7 @@ RB_EXPORT int rb200_ctc_loss(const void* logits, int is_bf16, const int* cu, con
     rb_set_error("ctc_loss: blank index %d outside [0, %d)", blank, V);
     return RB_ERR_ARG;
   }
-  const size_t smem_ab = (size_t)(3 * SE) * sizeof(float);
+  const size_t smem_ab = (size_t)(5 * SE) * sizeof(float);
   const size_t smem_grad = (size_t)V * sizeof(float);
   if (smem_ab > 200 * 1024 || smem_grad > 200 * 1024) {
     rb_set_error("ctc_loss: target length %d or vocabulary %d too large for the shared-memory buffers", max_s, V);
@@ -331,22 +344,24 @@ RB_EXPORT int rb200_ctc_loss(const void* logits, int is_bf16, const int* cu, con
   }
   float* lse = scratch;
   float* lp = lse + n_rows;
-  float* ab = lp + (size_t)n_rows * SE;
-  float* logp = ab + (size_t)n_rows * SE;
+  float* al = lp + (size_t)n_rows * SE;
+  float* be = al + (size_t)n_rows * SE;
+  float* logp = be + (size_t)n_rows * SE;
   if (n_rows > 0) {
     ctc_lse_gather_kernel<<<(n_rows + 7) / 8, 256, 0, stream>>>(logits, is_bf16, row_batch, targets, tgt_lens, lse, lp, n_rows, V, s_pitch, SE, blank);
     int st = rb_check_launch("ctc_lse_gather");
     if (st) return st;
   }
   if (smem_ab > 48 * 1024) cudaFuncSetAttribute(ctc_alpha_beta_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_ab);
-  ctc_alpha_beta_kernel<<<batch, 256, smem_ab, stream>>>(lp, ab, cu, targets, tgt_lens, logp, loss, s_pitch, SE, blank);
+  const int per_dir = std::min(256, (SE + 31) / 32 * 32);  // threads per direction; longer label sequences take the sequential path
+  ctc_alpha_beta_kernel<<<batch, 2 * per_dir, smem_ab, stream>>>(lp, al, be, cu, targets, tgt_lens, logp, loss, s_pitch, SE, blank);
   int st = rb_check_launch("ctc_alpha_beta");
   if (st) return st;
   if (n_rows > 0 && grad != nullptr) {
     if (smem_grad > 48 * 1024) cudaFuncSetAttribute(ctc_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_grad);
     const int frames_per_cta = 8;
     ctc_grad_kernel<<<(n_rows + frames_per_cta - 1) / frames_per_cta, 256, smem_grad, stream>>>(
-        logits, is_bf16, row_batch, targets, tgt_lens, lse, ab, logp, grad, n_rows, V, s_pitch, SE, blank, frames_per_cta);
+        logits, is_bf16, row_batch, targets, tgt_lens, lse, lp, al, be, logp, grad, n_rows, V, s_pitch, SE, blank, frames_per_cta);
     st = rb_check_launch("ctc_grad");
   }
   return st;

@@ -12,6 +12,7 @@ struct RbGemm {
   int bias_bf16 = 0;
   int m = 0, n = 0, k = 0, lda = 0, ldb = 0, ldc = 0;
   int a_mn_major = 0, b_mn_major = 0;
+  int ab_fp16 = 0;           // A and B hold IEEE fp16 instead of bf16 (same size, so the copies and layouts are the same; only the MMA reads them differently)
   int act = 0;               // 0 none, 1 relu, 2 silu, 3 gelu(erf)
   int out_fp32 = 0;
   int accumulate = 0;        // fp32 output only: 0 store, 1 c += value, 2 atomic c += value (needed with split_k > 1)

@@ -162,7 +162,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0 && leader) {
       // ---------------- MMA issuer (leader CTA only) ----------------
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.a_mn_major ? 1 : 0) << 15) |
+      const uint32_t ab_fmt = g.ab_fp16 ? 0u : 1u;  // operand format field: 0 = fp16, 1 = bf16 (accumulator fp32 either way)
+      const uint32_t idesc = (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(g.a_mn_major ? 1 : 0) << 15) |
                              ((uint32_t)(g.b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t it = 0, t_local = 0;
       bool ok = true;

@@ -120,7 +120,8 @@ gemm_persist_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   } else if (warp == 1) {
     if (lane == 0) {
       // ---------------- MMA issuer ----------------
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(g.a_mn_major ? 1 : 0) << 15) |
+      const uint32_t ab_fmt = g.ab_fp16 ? 0u : 1u;  // operand format field: 0 = fp16, 1 = bf16 (accumulator fp32 either way)
+      const uint32_t idesc = (1u << 4) | (ab_fmt << 7) | (ab_fmt << 10) | ((uint32_t)(g.a_mn_major ? 1 : 0) << 15) |
                              ((uint32_t)(g.b_mn_major ? 1 : 0) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       uint32_t it = 0, t_local = 0;
       bool ok = true;
@@ -311,18 +312,35 @@ int rb_gemm(const RbGemm& g, cudaStream_t stream) {
   return launch<128>(g, stream);
 }
 
-// C entry point with the full epilogue (see gemm.h for the meaning of the arguments)
+// C entry points with the full epilogue (see gemm.h for the meaning of the arguments); the second reads A and B as fp16
+static int gemm_ex(const void* a, const void* b, void* c, void* c2, const void* bias, int m, int n, int k, int lda, int ldb, int ldc, int a_mn_major,
+                   int b_mn_major, int bias_bf16, int act, int out_fp32, int accumulate, float alpha, const void* dact_z, float drop_p,
+                   const long long* seed, const long long* offset, unsigned long long drop_site, const void* resid, float res_scale, int split_k,
+                   int* status, int ab_fp16, cudaStream_t stream) {
+  RbGemm g;
+  g.a = a; g.b = b; g.c = c; g.c2 = c2; g.bias = bias; g.bias_bf16 = bias_bf16;
+  g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
+  g.a_mn_major = a_mn_major; g.b_mn_major = b_mn_major; g.ab_fp16 = ab_fp16;
+  g.act = act; g.out_fp32 = out_fp32; g.accumulate = accumulate; g.alpha = alpha;
+  g.dact_z = dact_z; g.drop_p = drop_p; g.seed = seed; g.offset = offset; g.drop_site = drop_site;
+  g.resid = resid; g.res_scale = res_scale; g.split_k = split_k; g.status = status;
+  return rb_gemm(g, stream);
+}
+
 RB_EXPORT int rb200_gemm_bf16_ex(const void* a, const void* b, void* c, void* c2, const void* bias, int m, int n, int k, int lda, int ldb,
                                  int ldc, int a_mn_major, int b_mn_major, int bias_bf16, int act, int out_fp32, int accumulate, float alpha,
                                  const void* dact_z, float drop_p, const long long* seed, const long long* offset,
                                  unsigned long long drop_site, const void* resid, float res_scale, int split_k, int* status,
                                  cudaStream_t stream) {
-  RbGemm g;
-  g.a = a; g.b = b; g.c = c; g.c2 = c2; g.bias = bias; g.bias_bf16 = bias_bf16;
-  g.m = m; g.n = n; g.k = k; g.lda = lda; g.ldb = ldb; g.ldc = ldc;
-  g.a_mn_major = a_mn_major; g.b_mn_major = b_mn_major;
-  g.act = act; g.out_fp32 = out_fp32; g.accumulate = accumulate; g.alpha = alpha;
-  g.dact_z = dact_z; g.drop_p = drop_p; g.seed = seed; g.offset = offset; g.drop_site = drop_site;
-  g.resid = resid; g.res_scale = res_scale; g.split_k = split_k; g.status = status;
-  return rb_gemm(g, stream);
+  return gemm_ex(a, b, c, c2, bias, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, bias_bf16, act, out_fp32, accumulate, alpha, dact_z, drop_p, seed,
+                 offset, drop_site, resid, res_scale, split_k, status, 0, stream);
+}
+
+RB_EXPORT int rb200_gemm_fp16_ex(const void* a, const void* b, void* c, void* c2, const void* bias, int m, int n, int k, int lda, int ldb,
+                                 int ldc, int a_mn_major, int b_mn_major, int bias_bf16, int act, int out_fp32, int accumulate, float alpha,
+                                 const void* dact_z, float drop_p, const long long* seed, const long long* offset,
+                                 unsigned long long drop_site, const void* resid, float res_scale, int split_k, int* status,
+                                 cudaStream_t stream) {
+  return gemm_ex(a, b, c, c2, bias, m, n, k, lda, ldb, ldc, a_mn_major, b_mn_major, bias_bf16, act, out_fp32, accumulate, alpha, dact_z, drop_p, seed,
+                 offset, drop_site, resid, res_scale, split_k, status, 1, stream);
 }

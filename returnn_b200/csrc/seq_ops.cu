@@ -83,81 +83,119 @@ struct Cand {
   int idx;
 };
 
-__device__ __forceinline__ void insert_topk(Cand* best, int k, float s, int idx) {
-  if (s <= best[k - 1].s) return;
-  int pos = k - 1;
-  while (pos > 0 && best[pos - 1].s < s) {
-    best[pos] = best[pos - 1];
-    --pos;
+// sorted insert with static indices only, so that the list stays in registers: the new entry replaces the last one and bubbles up
+template <int K>
+__device__ __forceinline__ void insert_topk(Cand (&best)[K], float s, int idx) {
+  if (s <= best[K - 1].s) return;
+  best[K - 1].s = s;
+  best[K - 1].idx = idx;
+#pragma unroll
+  for (int i = K - 1; i > 0; --i) {
+    if (best[i].s > best[i - 1].s) {
+      const Cand t = best[i];
+      best[i] = best[i - 1];
+      best[i - 1] = t;
+    }
   }
-  best[pos].s = s;
-  best[pos].idx = idx;
 }
 
+// Two kernels. (1) One CTA per hypothesis row [V]: ONE pass over the row with 16-byte loads computes the row's log-sum-exp (online
+// max / sum per thread) and the row's K best logits (a sorted list per thread, merged per warp by K rounds of "take the warp-wide
+// best head", then over the 8 warps); the candidates leave as (prev + logit - lse, h * V + v). B * beam CTAs fill the machine where
+// one CTA per batch entry left most SMs idle and read the row three times. (2) One warp per batch entry merges the beam sorted lists.
 template <int K>
 __global__ void __launch_bounds__(kTopkThreads)
-beam_topk_kernel(const void* __restrict__ logits, int is_bf16, int normalized, const float* __restrict__ prev_scores,
-                 const uint8_t* __restrict__ finished, int beam, int V, int eos, float* __restrict__ out_scores,
-                 int* __restrict__ out_backref, int* __restrict__ out_label, int k_out) {
-  __shared__ float sh_lse[64];
-  __shared__ float sh_red[kTopkThreads / 32];
+beam_topk_row_kernel(const void* __restrict__ logits, int is_bf16, int normalized, const float* __restrict__ prev_scores,
+                     const uint8_t* __restrict__ finished, int beam, int V, int eos, Cand* __restrict__ cands) {
+  __shared__ float sh_m[kTopkThreads / 32], sh_s[kTopkThreads / 32];
   __shared__ Cand sh_c[kTopkThreads / 32][K];
-  const int b = blockIdx.x;
+  const int row = blockIdx.x;  // b * beam + h
+  const int h = row % beam;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const size_t base = (size_t)b * beam * V;
-  auto ld = [&](size_t i) -> float {
-    return is_bf16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[i]) : reinterpret_cast<const float*>(logits)[i];
-  };
-  // log-sum-exp per hypothesis
-  for (int h = 0; h < beam; ++h) {
-    float lse = 0.f;
-    if (!normalized) {
-      float mx = -INFINITY;
-      for (int v = threadIdx.x; v < V; v += kTopkThreads) mx = fmaxf(mx, ld(base + (size_t)h * V + v));
-      mx = warp_max(mx);
-      if (lane == 0) sh_red[warp] = mx;
-      __syncthreads();
-      mx = sh_red[0];
-      for (int w = 1; w < kTopkThreads / 32; ++w) mx = fmaxf(mx, sh_red[w]);
-      __syncthreads();
-      float sum = 0.f;
-      for (int v = threadIdx.x; v < V; v += kTopkThreads) sum += __expf(ld(base + (size_t)h * V + v) - mx);
-      sum = warp_sum(sum);
-      if (lane == 0) sh_red[warp] = sum;
-      __syncthreads();
-      sum = 0.f;
-      for (int w = 0; w < kTopkThreads / 32; ++w) sum += sh_red[w];
-      __syncthreads();
-      lse = mx + __logf(sum);
+  Cand* out = cands + (size_t)row * K;
+  const float prev = prev_scores[row];
+  if (finished && finished[row]) {  // only continuation: eos at unchanged score
+    if (threadIdx.x < K) {
+      out[threadIdx.x].s = threadIdx.x == 0 ? prev : -INFINITY;
+      out[threadIdx.x].idx = threadIdx.x == 0 ? h * V + eos : -1;
     }
-    if (threadIdx.x == 0) sh_lse[h] = lse;
+    return;
   }
-  __syncthreads();
   Cand best[K];
 #pragma unroll
   for (int i = 0; i < K; ++i) {
     best[i].s = -INFINITY;
     best[i].idx = -1;
   }
-  const int total = beam * V;
-  for (int i = threadIdx.x; i < total; i += kTopkThreads) {
-    const int h = i / V, v = i - h * V;
-    float s;
-    if (finished && finished[(size_t)b * beam + h]) {
-      s = v == eos ? prev_scores[(size_t)b * beam + h] : -INFINITY;
+  float mx = -INFINITY, sum = 0.f;
+  auto visit = [&](float x, int v) {
+    if (x > mx) {
+      sum = sum * __expf(mx - x) + 1.f;
+      mx = x;
     } else {
-      s = prev_scores[(size_t)b * beam + h] + ld(base + i) - sh_lse[h];
+      sum += __expf(x - mx);
     }
-    insert_topk(best, K, s, i);
+    insert_topk<K>(best, x, v);
+  };
+  if (is_bf16) {
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(logits) + (size_t)row * V;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 1);
+    const int head = min(V, (8 - mis) & 7);  // elements before the first 16-byte boundary
+    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
+    const int n_vec = (V - head) >> 3;
+    const uint4* pv = reinterpret_cast<const uint4*>(p + head);
+    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
+      const uint4 u = pv[q];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        visit(__uint_as_float(w[e] << 16), head + q * 8 + 2 * e);
+        visit(__uint_as_float(w[e] & 0xffff0000u), head + q * 8 + 2 * e + 1);
+      }
+    }
+    for (int v = head + n_vec * 8 + threadIdx.x; v < V; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
+  } else {
+    const float* p = reinterpret_cast<const float*>(logits) + (size_t)row * V;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 2);
+    const int head = min(V, (4 - mis) & 3);
+    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(p[v], v);
+    const int n_vec = (V - head) >> 2;
+    const float4* pv = reinterpret_cast<const float4*>(p + head);
+    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
+      const float4 u = pv[q];
+      visit(u.x, head + q * 4);
+      visit(u.y, head + q * 4 + 1);
+      visit(u.z, head + q * 4 + 2);
+      visit(u.w, head + q * 4 + 3);
+    }
+    for (int v = head + n_vec * 4 + threadIdx.x; v < V; v += kTopkThreads) visit(p[v], v);
   }
-  // merge inside each warp: K rounds of "take the warp-wide best head"
-  Cand merged[K];
-  int head = 0;
+  // log-sum-exp over the CTA
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, mx, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
+    const float nm = fmaxf(mx, om);
+    sum = (mx == -INFINITY ? 0.f : sum * __expf(mx - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+    mx = nm;
+  }
+  if (lane == 0) {
+    sh_m[warp] = mx;
+    sh_s[warp] = sum;
+  }
+  // the warp's K best: K rounds over the heads of the lanes' sorted lists
+  int head_i = 0;
 #pragma unroll 1
   for (int r = 0; r < K; ++r) {
-    float s = head < K ? best[head].s : -INFINITY;
-    int idx = head < K ? best[head].idx : -1;
-    float ms = s;
+    float cs = -INFINITY;
+    int cidx = -1;
+#pragma unroll
+    for (int i = 0; i < K; ++i) {  // best[head_i] without dynamic indexing (keeps the list in registers)
+      if (i == head_i) {
+        cs = best[i].s;
+        cidx = best[i].idx;
+      }
+    }
+    float ms = cs;
     int ml = lane;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -168,37 +206,112 @@ beam_topk_kernel(const void* __restrict__ logits, int is_bf16, int normalized, c
         ml = ol;
       }
     }
-    const int midx = __shfl_sync(0xffffffffu, idx, ml);
-    if (lane == ml) ++head;
-    merged[r].s = ms;
-    merged[r].idx = midx;
-  }
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < K; ++r) sh_c[warp][r] = merged[r];
+    const int midx = __shfl_sync(0xffffffffu, cidx, ml);
+    if (lane == ml) ++head_i;
+    if (lane == 0) {
+      sh_c[warp][r].s = ms;
+      sh_c[warp][r].idx = midx;
+    }
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    // final merge of the per-warp sorted lists
-    int heads[kTopkThreads / 32];
-    for (int w = 0; w < kTopkThreads / 32; ++w) heads[w] = 0;
-    for (int r = 0; r < k_out; ++r) {
-      int bw = -1;
-      float bs = -INFINITY;
-      for (int w = 0; w < kTopkThreads / 32; ++w) {
-        if (heads[w] < K && sh_c[w][heads[w]].idx >= 0 && (bw < 0 || sh_c[w][heads[w]].s > bs)) {
-          bs = sh_c[w][heads[w]].s;
-          bw = w;
+  if (warp == 0) {
+    // lanes 0..7 each walk one warp's list; K rounds of an 8-wide argmax
+    constexpr int kW = kTopkThreads / 32;
+    float lse = 0.f;
+    if (!normalized) {
+      float m = lane < kW ? sh_m[lane] : -INFINITY, sm = lane < kW ? sh_s[lane] : 0.f;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, sm, o);
+        const float nm = fmaxf(m, om);
+        sm = (m == -INFINITY ? 0.f : sm * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+        m = nm;
+      }
+      m = __shfl_sync(0xffffffffu, m, 0);
+      sm = __shfl_sync(0xffffffffu, sm, 0);
+      lse = m + __logf(sm);
+    }
+    int hd = 0;
+#pragma unroll 1
+    for (int r = 0; r < K; ++r) {
+      const bool have = lane < kW && hd < K && sh_c[lane][hd].idx >= 0;
+      float ms = have ? sh_c[lane][hd].s : -INFINITY;
+      int ml = have ? lane : 64;
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) {
+        const float os = __shfl_xor_sync(0xffffffffu, ms, o);
+        const int ol = __shfl_xor_sync(0xffffffffu, ml, o);
+        if (os > ms || (os == ms && ol < ml)) {
+          ms = os;
+          ml = ol;
         }
       }
-      int idx = -1;
-      if (bw >= 0) {
-        idx = sh_c[bw][heads[bw]].idx;
-        ++heads[bw];
+      ms = __shfl_sync(0xffffffffu, ms, 0);
+      ml = __shfl_sync(0xffffffffu, ml, 0);
+      if (ml < kW) {
+        const int idx = sh_c[ml][__shfl_sync(0xffffffffu, hd, ml)].idx;
+        if (lane == ml) ++hd;
+        if (lane == 0) {
+          out[r].s = prev + ms - lse;
+          out[r].idx = h * V + idx;
+        }
+      } else if (lane == 0) {
+        out[r].s = -INFINITY;
+        out[r].idx = -1;
       }
-      out_scores[(size_t)b * k_out + r] = bw >= 0 ? bs : -INFINITY;
-      out_backref[(size_t)b * k_out + r] = idx >= 0 ? idx / V : 0;
-      out_label[(size_t)b * k_out + r] = idx >= 0 ? idx % V : 0;
+    }
+  }
+}
+
+// one warp per batch entry: lane l owns the sorted lists of hypotheses l and l + 32; k_out rounds of a warp-wide argmax over the heads
+__global__ void __launch_bounds__(32)
+beam_topk_merge_kernel(const Cand* __restrict__ cands, int beam, int K, int V, float* __restrict__ out_scores, int* __restrict__ out_backref,
+                       int* __restrict__ out_label, int k_out) {
+  const int b = blockIdx.x, lane = threadIdx.x;
+  const Cand* base = cands + (size_t)b * beam * K;
+  int hd0 = 0, hd1 = 0;
+  for (int r = 0; r < k_out; ++r) {
+    float s0 = -INFINITY, s1 = -INFINITY;
+    int i0 = -1, i1 = -1;
+    if (lane < beam && hd0 < K) {
+      const Cand c = base[(size_t)lane * K + hd0];
+      s0 = c.s;
+      i0 = c.idx;
+    }
+    if (lane + 32 < beam && hd1 < K) {
+      const Cand c = base[(size_t)(lane + 32) * K + hd1];
+      s1 = c.s;
+      i1 = c.idx;
+    }
+    const bool second = i1 >= 0 && (i0 < 0 || s1 > s0);
+    float ms = second ? s1 : s0;
+    int mi = second ? i1 : i0;
+    if (mi < 0) ms = -INFINITY;
+    int ml = mi >= 0 ? lane : 64;
+    float bs = ms;
+    int bl = ml;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+      const int ol = __shfl_xor_sync(0xffffffffu, bl, o);
+      if (ol < 64 && (bl >= 64 || os > bs || (os == bs && ol < bl))) {
+        bs = os;
+        bl = ol;
+      }
+    }
+    bs = __shfl_sync(0xffffffffu, bs, 0);
+    bl = __shfl_sync(0xffffffffu, bl, 0);
+    int widx = -1;
+    if (bl < 64) {
+      widx = __shfl_sync(0xffffffffu, mi, bl);
+      if (lane == bl) {
+        if (second) ++hd1; else ++hd0;
+      }
+    }
+    if (lane == 0) {
+      out_scores[(size_t)b * k_out + r] = widx >= 0 ? bs : -INFINITY;
+      out_backref[(size_t)b * k_out + r] = widx >= 0 ? widx / V : 0;
+      out_label[(size_t)b * k_out + r] = widx >= 0 ? widx % V : 0;
     }
   }
 }
@@ -308,24 +421,36 @@ RB_EXPORT int rb200_edit_distance(const int* a, const int* a_len, int lda, const
   return rb_check_launch("edit_distance");
 }
 
+// scratch: room for batch * beam * Kt candidates of 8 bytes, Kt = 8 / 16 / 32 for k <= 8 / 16 / 32 (rb200_beam_topk_scratch_bytes)
+RB_EXPORT long long rb200_beam_topk_scratch_bytes(int batch, int beam, int k) {
+  const int kt = k <= 8 ? 8 : (k <= 16 ? 16 : 32);
+  return (long long)batch * beam * kt * (long long)sizeof(Cand);
+}
+
 RB_EXPORT int rb200_beam_topk(const void* logits, int is_bf16, int normalized, const float* prev_scores, const void* finished, int batch, int beam, int V,
-                              int eos, int k, float* out_scores, int* out_backref, int* out_label, cudaStream_t stream) {
+                              int eos, int k, float* out_scores, int* out_backref, int* out_label, void* scratch, cudaStream_t stream) {
   if (batch <= 0) return RB_OK;
-  if (k < 1 || k > kTopkMaxK || beam < 1 || beam > 64 || (long long)beam * V > 0x7fffffffLL) {
-    rb_set_error("beam_topk: k=%d (<= %d), beam=%d (<= 64)", k, kTopkMaxK, beam);
+  if (k < 1 || k > kTopkMaxK || beam < 1 || beam > 64 || (long long)beam * V > 0x7fffffffLL || !scratch) {
+    rb_set_error("beam_topk: k=%d (<= %d), beam=%d (<= 64), scratch %p", k, kTopkMaxK, beam, scratch);
     return RB_ERR_UNSUPPORTED;
   }
+  Cand* cands = reinterpret_cast<Cand*>(scratch);
+  const int rows = batch * beam;
+  int kt;
   if (k <= 8) {
-    beam_topk_kernel<8><<<batch, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, out_scores,
-                                                           out_backref, out_label, k);
+    kt = 8;
+    beam_topk_row_kernel<8><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
   } else if (k <= 16) {
-    beam_topk_kernel<16><<<batch, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, out_scores,
-                                                            out_backref, out_label, k);
+    kt = 16;
+    beam_topk_row_kernel<16><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
   } else {
-    beam_topk_kernel<32><<<batch, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, out_scores,
-                                                            out_backref, out_label, k);
+    kt = 32;
+    beam_topk_row_kernel<32><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
   }
-  return rb_check_launch("beam_topk");
+  int rc = rb_check_launch("beam_topk rows");
+  if (rc != RB_OK) return rc;
+  beam_topk_merge_kernel<<<batch, 32, 0, stream>>>(cands, beam, kt, V, out_scores, out_backref, out_label, k);
+  return rb_check_launch("beam_topk merge");
 }
 
 RB_EXPORT int rb200_rnnt_loss(const float* lp_blank, const float* lp_label, const int* t_lens, const int* u_lens, int batch, int T, int U1, float* alpha,

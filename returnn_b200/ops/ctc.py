@@ -30,7 +30,7 @@ def supports(logits, targets) -> bool:
 
 
 def max_target_len() -> int:
-    """longest label sequence the kernel handles (3 * (2S+1) floats of shared memory per sequence)"""
+    """longest label sequence the kernel handles (5 * (2S+1) floats of shared memory per sequence)"""
     return 4000
 
 
@@ -49,7 +49,7 @@ class _CtcFn(torch.autograd.Function):
         need_grad = logits_rows.requires_grad
         grad = torch.empty_like(logits_rows) if need_grad else None
         s_ext = 2 * max_s + 1
-        scratch = torch.empty(n * (1 + 2 * s_ext) + b, dtype=torch.float32, device=logits_rows.device)
+        scratch = torch.empty(n * (1 + 3 * s_ext) + b, dtype=torch.float32, device=logits_rows.device)
         fn = _lib.bind("rb200_ctc_loss", [_vp, _i32, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i64, _vp])
         _lib.check(fn(logits_rows.data_ptr(), 1 if logits_rows.dtype == torch.bfloat16 else 0, cu.data_ptr(), row_batch.data_ptr(),
                       targets.data_ptr(), tgt_lens.data_ptr(), loss.data_ptr(), grad.data_ptr() if grad is not None else None,

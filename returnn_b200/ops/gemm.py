@@ -70,7 +70,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, m: int, n: int, k: int, a_mn_major
     :param resid: bf16 ``[m, n]``: ``resid + res_scale * value``
     :param atomic: fp32 out only: add into ``out`` with atomics; the contraction may then be split over CTAs (``split_k``, 0 = auto)
     """
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16 and a.dim() == 2 and b.dim() == 2
+    assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16) and a.dim() == 2 and b.dim() == 2
+    fp16 = a.dtype == torch.float16  # fp16 operands (3 more mantissa bits, smaller range): same kernels, other MMA operand format
     assert a.stride(1) == 1 and b.stride(1) == 1
     lda, ldb = a.stride(0), b.stride(0)
     if a.shape[0] == 1:
@@ -84,7 +85,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, m: int, n: int, k: int, a_mn_major
     if want_act_output:
         c2 = out_act if out_act is not None else torch.empty(m, n, dtype=torch.bfloat16, device=a.device)
     st = status_tensor(a.device)
-    extended = dact_z is not None or dropout_p > 0.0 or resid is not None or atomic
+    extended = dact_z is not None or dropout_p > 0.0 or resid is not None or atomic or fp16
     bias_bf16 = 1 if (bias is not None and bias.dtype == torch.bfloat16) else 0
     if KERNEL == "legacy" and not extended:
         fn = _lib.bind("rb200_gemm_bf16", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp])
@@ -95,7 +96,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, m: int, n: int, k: int, a_mn_major
     else:
         for t in (dact_z, resid):
             assert t is None or (t.dtype == torch.bfloat16 and t.stride(-1) == 1 and t.stride(0) == out.stride(0))
-        fn = _lib.bind("rb200_gemm_bf16_ex", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
+        fn = _lib.bind("rb200_gemm_fp16_ex" if fp16 else "rb200_gemm_bf16_ex", [_vp, _vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32,
                                               _vp, _f32, _vp, _vp, _u64, _vp, _f32, _i32, _vp, _vp])
         _lib.check(fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), c2.data_ptr() if c2 is not None else None,
                       bias.data_ptr() if bias is not None else None, m, n, k, lda, ldb, out.stride(0), 1 if a_mn_major else 0,

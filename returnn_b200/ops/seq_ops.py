@@ -122,11 +122,13 @@ def beam_topk(logits: torch.Tensor, prev_scores: torch.Tensor, *, finished: Opti
         out_s = torch.empty(B, k, dtype=torch.float32, device=dev)
         out_b = torch.empty(B, k, dtype=torch.int32, device=dev)
         out_l = torch.empty(B, k, dtype=torch.int32, device=dev)
-        fn = _lib.bind("rb200_beam_topk", [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp])
+        kt = 8 if k <= 8 else (16 if k <= 16 else 32)
+        scratch = torch.empty(B * beam * kt * 2, dtype=torch.int32, device=dev)  # (score, index) per candidate of the per-row stage
+        fn = _lib.bind("rb200_beam_topk", [_vp, _i32, _i32, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp, _vp, _vp])
         _lib.check(fn(lg.data_ptr(), 1 if lg.dtype == torch.bfloat16 else 0, 1 if normalized else 0, ps.data_ptr(),
                       fin.data_ptr() if fin is not None else None, B, beam, V, int(eos), int(k), out_s.data_ptr(), out_b.data_ptr(), out_l.data_ptr(),
-                      _lib.stream_ptr()), "beam_topk")
-        _lib.count_launch()
+                      scratch.data_ptr(), _lib.stream_ptr()), "beam_topk")
+        _lib.count_launch(2)
         return out_s, out_b, out_l
     return beam_topk_reference(logits, prev_scores, finished, eos, k, normalized)
 

@@ -194,3 +194,70 @@ def test_log_mel_kernel_matches_stft_path():
         del os.environ["RETURNN_B200_DISABLE_NATIVE"]
     assert tuple(got.raw_tensor.shape) == tuple(ref.raw_tensor.shape) == (3, 98, 80)
     torch.testing.assert_close(got.raw_tensor.cpu(), ref.raw_tensor, atol=2e-3, rtol=2e-3)
+
+
+def _log_mel_fp64(audio, lens, *, window, step, n_fft, n_mel, sampling_rate=16000):
+    """float64 restatement: frames -> Hann window -> rfft -> power -> mel -> log10"""
+    from returnn_b200.frontend.audio.mel import _fbank_matrix
+
+    win = torch.hann_window(window, periodic=True, dtype=torch.float64)
+    fb = torch.from_numpy(_fbank_matrix(sampling_rate, n_fft, 0.0, sampling_rate / 2.0, n_mel)).double()
+    rows, T = audio.shape
+    n_frames = (T - window) // step + 1
+    frames = audio.double().unfold(1, window, step)[:, :n_frames] * win
+    power = torch.fft.rfft(frames, n=n_fft).abs() ** 2
+    out = torch.log10(torch.clamp(power @ fb, min=1e-10))
+    for r, n in enumerate(lens):
+        out[r, max((int(n) - window) // step + 1, 0):] = 0
+    return out.float()
+
+
+def test_log_mel_dft_table_layout_cpu():
+    """the packed DFT table (X_0 and X_{N/2} share the first column pair) and the mel filter ranges, checked in float64 on the CPU"""
+    from returnn_b200.ops import logmel
+    from returnn_b200.frontend.audio.mel import _fbank_matrix
+
+    window, n_fft, n_mel = 400, 512, 80
+    win = torch.hann_window(window, periodic=True, dtype=torch.float32)
+    fb = torch.from_numpy(_fbank_matrix(16000, n_fft, 0.0, 8000.0, n_mel))
+    t_hi, t_lo, start, length = logmel._dft_tables(torch.device("cpu"), window, n_fft, win, fb)
+    table = t_hi.double() + t_lo.double()
+    x = torch.randn(5, window, dtype=torch.float64)
+    spec = x @ table
+    ref = torch.fft.rfft(x * win.double(), n=n_fft)
+    assert torch.allclose(spec[:, 0], ref[:, 0].real, atol=2e-3) and torch.allclose(spec[:, 1], ref[:, n_fft // 2].real, atol=2e-3)
+    assert torch.allclose(spec[:, 2::2], ref[:, 1:n_fft // 2].real, atol=2e-3) and torch.allclose(spec[:, 3::2], ref[:, 1:n_fft // 2].imag, atol=2e-3)
+    for m in range(n_mel):
+        nz = torch.nonzero(fb[:, m]).flatten()
+        assert int(start[m]) == int(nz[0]) and int(start[m] + length[m]) == int(nz[-1]) + 1
+
+
+@gpu
+def test_log_mel_gemm_form_matches_float64():
+    """tensor-core DFT (fp16 hi/lo split, three products) against float64, on a signal with about 80 dB between its strongest and weakest band"""
+    import os
+    from returnn_b200.ops import logmel
+
+    torch.manual_seed(0)
+    rows, T = 24, 16000 * 2 + 37
+    tt = torch.arange(T, device="cuda")
+    audio = torch.sin(tt * 0.05)[None] * 0.8 + torch.randn(rows, T, device="cuda") * 3e-5
+    lens = torch.tensor([T] * (rows - 2) + [T // 2, 300], dtype=torch.int32)
+    ref = _log_mel_fp64(audio.cpu(), lens, window=400, step=160, n_fft=512, n_mel=80)
+    kw = dict(sampling_rate=16000, window=400, step=160, n_fft=512, n_mel=80, f_min=0.0, f_max=8000.0, lens=lens)
+    old = os.environ.get("RETURNN_B200_LOGMEL")
+    try:
+        os.environ["RETURNN_B200_LOGMEL"] = "gemm"
+        got = logmel.log_mel(audio, **kw).cpu()
+        os.environ["RETURNN_B200_LOGMEL"] = "direct"
+        direct = logmel.log_mel(audio, **kw).cpu()
+    finally:
+        if old is None:
+            del os.environ["RETURNN_B200_LOGMEL"]
+        else:
+            os.environ["RETURNN_B200_LOGMEL"] = old
+    assert got.shape == ref.shape == direct.shape
+    assert float(ref.max() - ref[:rows - 2].min()) > 7.0  # the test signal really spans > 70 dB in the mel domain
+    torch.testing.assert_close(direct, ref, atol=5e-3, rtol=0)
+    torch.testing.assert_close(got, ref, atol=5e-3, rtol=0)
+    assert float(got[-1].abs().max()) == 0.0 and float(got[-2, (T // 2 - 400) // 160 + 1:].abs().max()) == 0.0

@@ -71,7 +71,7 @@ def test_edit_distance_kernel():
 
 @gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("k,beam,V", [(12, 12, 10001), (4, 1, 57), (32, 8, 1000)])
+@pytest.mark.parametrize("k,beam,V", [(12, 12, 10001), (4, 1, 57), (32, 8, 1000), (8, 40, 501), (16, 64, 33)])
 def test_beam_topk_kernel(dtype, k, beam, V):
     from returnn_b200.ops import seq_ops
 
