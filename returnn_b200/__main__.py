@@ -331,8 +331,16 @@ def execute_main_task():
         from .torch.util.compute_priors import compute_priors
 
         compute_priors(engine=engine, dataset=train_data, config=config)
+    elif task == "analyze":
+        data = eval_data or dev_data
+        assert data is not None, "task analyze: no 'eval' or 'dev' data"
+        engine.init_network_from_config(config)
+        engine.analyze(data=data, statistics=config.list("statistics", None))
     elif task == "analyze_data":
         analyze_data(config)
+    elif task == "search_server":
+        engine.init_network_from_config(config)
+        engine.web_server(port=config.int("web_server_port", 12380))
     elif task == "cleanup_old_models":
         engine.cleanup_old_models(ask_for_confirmation=True)
     elif task == "initialize_model":

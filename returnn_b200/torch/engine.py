@@ -1082,6 +1082,21 @@ class Engine(EngineBase):
         print("Forward %i steps, %s elapsed" % (step_idx, hms(time.monotonic() - epoch_start_time)), file=log.v3)
         self._maybe_reset_dev_memory_caches()
 
+    def analyze(self, data: Dataset, statistics: Optional[List[str]] = None) -> Dict[str, Any]:
+        """task ``analyze``: statistics of the model's per-frame class distribution over ``data`` (see :mod:`.serving`)"""
+        from .serving import analyze
+
+        return analyze(self, data, statistics)
+
+    def web_server(self, port: Optional[int] = None):
+        """task ``search_server``: serve ``forward_step`` over HTTP until interrupted (see :mod:`.serving`)"""
+        from .serving import ModelServer
+
+        cfg = self.config
+        server = ModelServer(self, port=port if port is not None else cfg.int("web_server_port", 12380), host=cfg.value("web_server_host", "127.0.0.1"),
+                             max_batch=cfg.int("web_server_max_batch", 16), batch_wait_ms=cfg.float("web_server_batch_wait_ms", 2.0))
+        server.serve_forever()
+
     # -- misc --------------------------------------------------------------------------------------------------------
     def _handle_run_exception(self, exc: Optional[Exception], *, extern_data=None, always_direct_print: bool = False):
         from .util import diagnose_gpu

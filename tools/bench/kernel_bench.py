@@ -211,6 +211,22 @@ def main():
         t_b = _time(bwd, args.iters)
         report("att_softmax fwd (bf16 scores, dropout)", t_f, None, valid * 2 * 4, 0)
         report("att_softmax bwd (bf16 scores, dropout)", t_b, None, valid * 2 * 4, 0)
+    if want("adamw"):
+        # the optimizer step of the flagship model: one kernel over the flat arena of 82.4 M fp32 parameters; per element it reads
+        # parameter, gradient and both moments and writes parameter, both moments and the bf16 copy of the parameter (30 bytes)
+        from returnn_b200.ops import optim_native
+
+        n_par = 82387968
+        p_ = torch.randn(n_par, device=dev) * 0.05
+        g_ = torch.randn(n_par, device=dev) * 0.01
+        m_ = torch.zeros(n_par, device=dev)
+        v_ = torch.zeros(n_par, device=dev)
+        p16 = torch.empty(n_par, device=dev, dtype=bf)
+        flags = torch.ones(n_par // 4, device=dev, dtype=torch.uint8)
+        norm = torch.full((1,), 3.0, device=dev)
+        step = lambda: optim_native.adamw_arena(p_, g_, m_, v_, flags, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, bc1=0.1, bc2=0.001, decoupled=True,
+                                                clip=5.0, norm=norm, p_bf16=p16)
+        report("adamw (82.4 M parameters, clip factor on the fly, bf16 copy)", _time(step, args.iters), None, n_par * 30, 0)
     if want("lstm"):
         from returnn_b200.ops import lstm_native
 
