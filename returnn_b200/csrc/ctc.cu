@@ -87,6 +87,14 @@ ctc_lse_gather_kernel(const void* __restrict__ logits, int is_bf16, const int* _
 // the frame's own log-probability) to `be`; the gradient kernel forms the occupancies exp(alpha + beta - lp - logP) from them.
 constexpr int kCtcDepth = 8;
 
+// log(e^a + e^b + e^c) without branches and with one logarithm: the dependent chain is max -> exp -> add -> log.
+// Inputs may be -inf (e^-inf = 0); all three -inf gives log(0) = -inf.
+__device__ __forceinline__ float log_add3(float a, float b, float c) {
+  const float m = fmaxf(a, fmaxf(b, c));
+  const float mm = (m == kNegInf) ? 0.f : m;
+  return mm + __logf(__expf(a - mm) + __expf(b - mm) + __expf(c - mm));
+}
+
 __device__ __forceinline__ void bar_sync_named(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
@@ -141,9 +149,7 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ al, floa
           const int t = t0 + j;
           if (t < T) {  // uniform over the CTA
             if (act) {
-              float a = prev[s];
-              if (s >= 1) a = log_add(a, prev[s - 1]);
-              if (skip) a = log_add(a, prev[s - 2]);
+              float a = log_add3(prev[s], s >= 1 ? prev[s - 1] : kNegInf, skip ? prev[s - 2] : kNegInf);
               a = (a == kNegInf) ? kNegInf : a + lq[j];
               cur[s] = a;
               al[(size_t)(r0 + t) * SE + s] = a;
@@ -183,9 +189,7 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ al, floa
           const int t = t0 - j;
           if (t >= 0) {
             if (act) {
-              float bt = prev[s];
-              if (s + 1 < se) bt = log_add(bt, prev[s + 1]);
-              if (skip) bt = log_add(bt, prev[s + 2]);
+              float bt = log_add3(prev[s], s + 1 < se ? prev[s + 1] : kNegInf, skip ? prev[s + 2] : kNegInf);
               bt = (bt == kNegInf) ? kNegInf : bt + lq[j];
               cur[s] = bt;
               be[(size_t)(r0 + t) * SE + s] = bt;

@@ -47,14 +47,23 @@ __global__ void __launch_bounds__(256)
 fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const int* __restrict__ e_em, const float* __restrict__ weights,
            const int* __restrict__ edge_start, const float* __restrict__ am, const int* __restrict__ start, const int* __restrict__ end,
            const int* __restrict__ end2, const int* __restrict__ lens, int T, int B, int V, int S, float* __restrict__ fwd,
-           float* __restrict__ bwd, float* __restrict__ out, float* __restrict__ obs) {
+           float* __restrict__ bwd, float* __restrict__ out, float* __restrict__ obs, const int* __restrict__ end_start,
+           const int* __restrict__ end_state, const float* __restrict__ end_weight) {
   const int b = blockIdx.x;
   const int e0 = edge_start[b], e1 = edge_start[b + 1];
   const int Tb = lens[b];
   if (threadIdx.x == 0) {
     fwd[start[b]] = 0.f;
-    bwd[(size_t)Tb * S + end[b]] = 0.f;
-    if (end2 && end2[b] >= 0) bwd[(size_t)Tb * S + end2[b]] = 0.f;
+    if (end_start) {
+      // any number of final states per sequence, each with its own weight (-log): entries end_start[b] .. end_start[b + 1]
+      for (int i = end_start[b]; i < end_start[b + 1]; ++i) {
+        float* slot = bwd + (size_t)Tb * S + end_state[i];
+        *slot = log_add2(*slot, -end_weight[i]);
+      }
+    } else {
+      bwd[(size_t)Tb * S + end[b]] = 0.f;
+      if (end2 && end2[b] >= 0) bwd[(size_t)Tb * S + end2[b]] = 0.f;
+    }
   }
   __syncthreads();
   for (int t = 0; t < Tb; ++t) {
@@ -87,6 +96,63 @@ fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const i
     for (int e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
       const float a = f[e_from[e]], c = bw[e_to[e]];
       if (a > -INFINITY && c > -INFINITY) atomic_log_add(o + e_em[e], a - weights[e] - amt[e_em[e]] + c - total);
+    }
+  }
+}
+
+// Segmental forward-backward: an edge taken at frame t consumes a SEGMENT of l = 1 .. L frames and costs
+//   weights[e] + am_scale * am[row_start[b] + t][l - 1][e_em[e]] + length_models[e_lenmod[e]][l - 1]          (all -log)
+// am holds one row per (sequence, segment start frame): [N, L, V]; out has the same shape and receives the log posterior of
+// (start frame, length, label). State scores fwd / bwd: [T_max + 1, S] pre-filled with -inf; out pre-filled with -inf.
+// One CTA per sequence; the (edge, length) pairs of a frame are spread over the threads.
+// (reference: returnn/native_op.py:4369 SegmentFastBaumWelchOp, kernels next_frame_fwd / next_frame_bwd)
+__global__ void __launch_bounds__(256)
+seg_fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const int* __restrict__ e_em, const int* __restrict__ e_lenmod,
+               const float* __restrict__ weights, const int* __restrict__ edge_start, const float* __restrict__ am,
+               const float* __restrict__ length_models, const int* __restrict__ row_start, const int* __restrict__ start,
+               const int* __restrict__ end, const int* __restrict__ lens, int L, int V, int S, int T_max, float am_scale, float* __restrict__ fwd,
+               float* __restrict__ bwd, float* __restrict__ out, float* __restrict__ obs) {
+  const int b = blockIdx.x;
+  const int e0 = edge_start[b], ne = edge_start[b + 1] - e0;
+  const int Tb = lens[b];
+  const size_t r0 = (size_t)row_start[b];
+  if (threadIdx.x == 0) {
+    fwd[start[b]] = 0.f;
+    bwd[(size_t)Tb * S + end[b]] = 0.f;
+  }
+  __syncthreads();
+  auto cost = [&](int e, int t, int l) -> float {  // l = segment length - 1
+    return weights[e] + am_scale * am[((r0 + t) * L + l) * V + e_em[e]] + length_models[(size_t)e_lenmod[e] * L + l];
+  };
+  for (int t = 0; t < Tb; ++t) {
+    const int lmax = min(L, Tb - t);
+    const float* cur = fwd + (size_t)t * S;
+    for (int i = threadIdx.x; i < ne * lmax; i += blockDim.x) {
+      const int e = e0 + i / lmax, l = i % lmax;
+      const float s = cur[e_from[e]];
+      if (s > -INFINITY) atomic_log_add(fwd + (size_t)(t + l + 1) * S + e_to[e], s - cost(e, t, l));
+    }
+    __syncthreads();
+  }
+  for (int t = Tb - 1; t >= 0; --t) {
+    const int lmax = min(L, Tb - t);
+    float* cur = bwd + (size_t)t * S;
+    for (int i = threadIdx.x; i < ne * lmax; i += blockDim.x) {
+      const int e = e0 + i / lmax, l = i % lmax;
+      const float s = bwd[(size_t)(t + l + 1) * S + e_to[e]];
+      if (s > -INFINITY) atomic_log_add(cur + e_from[e], s - cost(e, t, l));
+    }
+    __syncthreads();
+  }
+  const float total = bwd[start[b]];
+  if (threadIdx.x == 0) obs[b] = total;
+  if (total == -INFINITY) return;
+  for (int t = 0; t < Tb; ++t) {
+    const int lmax = min(L, Tb - t);
+    for (int i = threadIdx.x; i < ne * lmax; i += blockDim.x) {
+      const int e = e0 + i / lmax, l = i % lmax;
+      const float a = fwd[(size_t)t * S + e_from[e]], c = bwd[(size_t)(t + l + 1) * S + e_to[e]];
+      if (a > -INFINITY && c > -INFINITY) atomic_log_add(out + ((r0 + t) * L + l) * V + e_em[e], a - cost(e, t, l) + c - total);
     }
   }
 }
@@ -186,8 +252,30 @@ RB_EXPORT int rb200_fsa_fbw(const int* e_from, const int* e_to, const int* e_em,
                             const int* start, const int* end, const int* end2, const int* lens, int T, int B, int V, int S, float* fwd, float* bwd,
                             float* out, float* obs, cudaStream_t stream) {
   if (B <= 0) return RB_OK;
-  fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, end, end2, lens, T, B, V, S, fwd, bwd, out, obs);
+  fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, end, end2, lens, T, B, V, S, fwd, bwd, out, obs, nullptr, nullptr,
+                                    nullptr);
   return rb_check_launch("fsa_fbw");
+}
+
+// as rb200_fsa_fbw, with a list of weighted final states per sequence: end_start [B+1] into end_state [N] / end_weight [N] (-log)
+RB_EXPORT int rb200_fsa_fbw_multi_end(const int* e_from, const int* e_to, const int* e_em, const float* weights, const int* edge_start, const float* am,
+                                      const int* start, const int* end_start, const int* end_state, const float* end_weight, const int* lens, int T,
+                                      int B, int V, int S, float* fwd, float* bwd, float* out, float* obs, cudaStream_t stream) {
+  if (B <= 0) return RB_OK;
+  fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, nullptr, nullptr, lens, T, B, V, S, fwd, bwd, out, obs, end_start,
+                                    end_state, end_weight);
+  return rb_check_launch("fsa_fbw_multi_end");
+}
+
+// segmental form: see seg_fbw_kernel
+RB_EXPORT int rb200_fsa_seg_fbw(const int* e_from, const int* e_to, const int* e_em, const int* e_lenmod, const float* weights, const int* edge_start,
+                                const float* am, const float* length_models, const int* row_start, const int* start, const int* end, const int* lens,
+                                int B, int L, int V, int S, int T_max, float am_scale, float* fwd, float* bwd, float* out, float* obs,
+                                cudaStream_t stream) {
+  if (B <= 0) return RB_OK;
+  seg_fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, e_lenmod, weights, edge_start, am, length_models, row_start, start, end, lens, L, V, S, T_max,
+                                        am_scale, fwd, bwd, out, obs);
+  return rb_check_launch("fsa_seg_fbw");
 }
 
 RB_EXPORT int rb200_fsa_viterbi(const int* e_from, const int* e_to, const int* e_em, const float* weights, const int* edge_start, const float* am,

@@ -83,32 +83,66 @@ struct Cand {
   int idx;
 };
 
-// sorted insert with static indices only, so that the list stays in registers: the new entry replaces the last one and bubbles up
-template <int K>
-__device__ __forceinline__ void insert_topk(Cand (&best)[K], float s, int idx) {
-  if (s <= best[K - 1].s) return;
-  best[K - 1].s = s;
-  best[K - 1].idx = idx;
+// Two kernels. (1) One CTA per hypothesis row [V] selects the row's K best logits and computes its log-sum-exp; the candidates
+// leave as (prev + logit - lse, h * V + v), sorted. B * beam CTAs fill the machine where one CTA per batch entry left most SMs idle.
+// Selection by threshold instead of by sorting: the 256 threads form K groups, every group finds the maximum of its elements; the
+// smallest of these K maxima is a lower bound of the row's K-th largest element (K distinct elements are >= it), so only elements
+// >= that bound can be among the K best. They are few (a few times K for unstructured data): the threads append them to a list in
+// shared memory and the list is ranked by counting.
+// A row where more than kTopkCap elements pass (many equal values) takes K rounds of a block-wide argmax instead.
+// (2) One warp per batch entry merges the beam sorted lists.
+constexpr int kTopkCap = 1024;
+
+__device__ __forceinline__ bool cand_before(float sa, int ia, float sb, int ib) {  // order: score descending, index ascending
+  return sa > sb || (sa == sb && ia < ib);
+}
+
+template <typename F>
+__device__ __forceinline__ void for_each_in_row(const void* logits, int is_bf16, size_t row, int V, F&& visit) {
+  if (is_bf16) {
+    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(logits) + row * V;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 1);
+    const int head = min(V, (8 - mis) & 7);  // elements before the first 16-byte boundary
+    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
+    const int n_vec = (V - head) >> 3;
+    const uint4* pv = reinterpret_cast<const uint4*>(p + head);
+    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
+      const uint4 u = __ldg(pv + q);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
-  for (int i = K - 1; i > 0; --i) {
-    if (best[i].s > best[i - 1].s) {
-      const Cand t = best[i];
-      best[i] = best[i - 1];
-      best[i - 1] = t;
+      for (int e = 0; e < 4; ++e) {
+        visit(__uint_as_float(w[e] << 16), head + q * 8 + 2 * e);
+        visit(__uint_as_float(w[e] & 0xffff0000u), head + q * 8 + 2 * e + 1);
+      }
     }
+    for (int v = head + n_vec * 8 + threadIdx.x; v < V; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
+  } else {
+    const float* p = reinterpret_cast<const float*>(logits) + row * V;
+    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 2);
+    const int head = min(V, (4 - mis) & 3);
+    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(p[v], v);
+    const int n_vec = (V - head) >> 2;
+    const float4* pv = reinterpret_cast<const float4*>(p + head);
+    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
+      const float4 u = __ldg(pv + q);
+      visit(u.x, head + q * 4);
+      visit(u.y, head + q * 4 + 1);
+      visit(u.z, head + q * 4 + 2);
+      visit(u.w, head + q * 4 + 3);
+    }
+    for (int v = head + n_vec * 4 + threadIdx.x; v < V; v += kTopkThreads) visit(p[v], v);
   }
 }
 
-// Two kernels. (1) One CTA per hypothesis row [V]: ONE pass over the row with 16-byte loads computes the row's log-sum-exp (online
-// max / sum per thread) and the row's K best logits (a sorted list per thread, merged per warp by K rounds of "take the warp-wide
-// best head", then over the 8 warps); the candidates leave as (prev + logit - lse, h * V + v). B * beam CTAs fill the machine where
-// one CTA per batch entry left most SMs idle and read the row three times. (2) One warp per batch entry merges the beam sorted lists.
-template <int K>
 __global__ void __launch_bounds__(kTopkThreads)
 beam_topk_row_kernel(const void* __restrict__ logits, int is_bf16, int normalized, const float* __restrict__ prev_scores,
-                     const uint8_t* __restrict__ finished, int beam, int V, int eos, Cand* __restrict__ cands) {
+                     const uint8_t* __restrict__ finished, int beam, int V, int eos, int K, Cand* __restrict__ cands) {
   __shared__ float sh_m[kTopkThreads / 32], sh_s[kTopkThreads / 32];
-  __shared__ Cand sh_c[kTopkThreads / 32][K];
+  __shared__ float sh_gmax[kTopkMaxK];
+  __shared__ Cand sh_c[kTopkCap];
+  __shared__ float sh_lse;
+  __shared__ int sh_cnt;
+  __shared__ Cand sh_best[kTopkThreads / 32];
   const int row = blockIdx.x;  // b * beam + h
   const int h = row % beam;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -121,145 +155,122 @@ beam_topk_row_kernel(const void* __restrict__ logits, int is_bf16, int normalize
     }
     return;
   }
-  Cand best[K];
-#pragma unroll
-  for (int i = 0; i < K; ++i) {
-    best[i].s = -INFINITY;
-    best[i].idx = -1;
-  }
+  // pass 1: this thread's maximum, and the log-sum-exp
   float mx = -INFINITY, sum = 0.f;
-  auto visit = [&](float x, int v) {
+  for_each_in_row(logits, is_bf16, (size_t)row, V, [&](float x, int) {
     if (x > mx) {
       sum = sum * __expf(mx - x) + 1.f;
       mx = x;
     } else {
       sum += __expf(x - mx);
     }
-    insert_topk<K>(best, x, v);
-  };
-  if (is_bf16) {
-    const __nv_bfloat16* p = reinterpret_cast<const __nv_bfloat16*>(logits) + (size_t)row * V;
-    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 1);
-    const int head = min(V, (8 - mis) & 7);  // elements before the first 16-byte boundary
-    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
-    const int n_vec = (V - head) >> 3;
-    const uint4* pv = reinterpret_cast<const uint4*>(p + head);
-    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
-      const uint4 u = pv[q];
-      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        visit(__uint_as_float(w[e] << 16), head + q * 8 + 2 * e);
-        visit(__uint_as_float(w[e] & 0xffff0000u), head + q * 8 + 2 * e + 1);
-      }
-    }
-    for (int v = head + n_vec * 8 + threadIdx.x; v < V; v += kTopkThreads) visit(__bfloat162float(p[v]), v);
-  } else {
-    const float* p = reinterpret_cast<const float*>(logits) + (size_t)row * V;
-    const int mis = (int)((reinterpret_cast<uintptr_t>(p) & 15) >> 2);
-    const int head = min(V, (4 - mis) & 3);
-    for (int v = threadIdx.x; v < head; v += kTopkThreads) visit(p[v], v);
-    const int n_vec = (V - head) >> 2;
-    const float4* pv = reinterpret_cast<const float4*>(p + head);
-    for (int q = threadIdx.x; q < n_vec; q += kTopkThreads) {
-      const float4 u = pv[q];
-      visit(u.x, head + q * 4);
-      visit(u.y, head + q * 4 + 1);
-      visit(u.z, head + q * 4 + 2);
-      visit(u.w, head + q * 4 + 3);
-    }
-    for (int v = head + n_vec * 4 + threadIdx.x; v < V; v += kTopkThreads) visit(p[v], v);
+  });
+  {
+    const int g = kTopkThreads / K;  // threads per group: 32, 16 or 8 (K is 8, 16 or 32), so a group lies within a warp
+    float gm = mx;
+    for (int o = g >> 1; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+    if ((threadIdx.x & (g - 1)) == 0) sh_gmax[threadIdx.x / g] = gm;
   }
-  // log-sum-exp over the CTA
+  if (threadIdx.x == 0) sh_cnt = 0;
+  float wm = mx, ws = sum;
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
-    const float om = __shfl_xor_sync(0xffffffffu, mx, o), os = __shfl_xor_sync(0xffffffffu, sum, o);
-    const float nm = fmaxf(mx, om);
-    sum = (mx == -INFINITY ? 0.f : sum * __expf(mx - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
-    mx = nm;
+    const float om = __shfl_xor_sync(0xffffffffu, wm, o), os = __shfl_xor_sync(0xffffffffu, ws, o);
+    const float nm = fmaxf(wm, om);
+    ws = (wm == -INFINITY ? 0.f : ws * __expf(wm - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+    wm = nm;
   }
   if (lane == 0) {
-    sh_m[warp] = mx;
-    sh_s[warp] = sum;
-  }
-  // the warp's K best: K rounds over the heads of the lanes' sorted lists
-  int head_i = 0;
-#pragma unroll 1
-  for (int r = 0; r < K; ++r) {
-    float cs = -INFINITY;
-    int cidx = -1;
-#pragma unroll
-    for (int i = 0; i < K; ++i) {  // best[head_i] without dynamic indexing (keeps the list in registers)
-      if (i == head_i) {
-        cs = best[i].s;
-        cidx = best[i].idx;
-      }
-    }
-    float ms = cs;
-    int ml = lane;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float os = __shfl_xor_sync(0xffffffffu, ms, o);
-      const int ol = __shfl_xor_sync(0xffffffffu, ml, o);
-      if (os > ms || (os == ms && ol < ml)) {
-        ms = os;
-        ml = ol;
-      }
-    }
-    const int midx = __shfl_sync(0xffffffffu, cidx, ml);
-    if (lane == ml) ++head_i;
-    if (lane == 0) {
-      sh_c[warp][r].s = ms;
-      sh_c[warp][r].idx = midx;
-    }
+    sh_m[warp] = wm;
+    sh_s[warp] = ws;
   }
   __syncthreads();
-  if (warp == 0) {
-    // lanes 0..7 each walk one warp's list; K rounds of an 8-wide argmax
-    constexpr int kW = kTopkThreads / 32;
-    float lse = 0.f;
-    if (!normalized) {
-      float m = lane < kW ? sh_m[lane] : -INFINITY, sm = lane < kW ? sh_s[lane] : 0.f;
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, m, o), os = __shfl_xor_sync(0xffffffffu, sm, o);
-        const float nm = fmaxf(m, om);
-        sm = (m == -INFINITY ? 0.f : sm * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
-        m = nm;
-      }
-      m = __shfl_sync(0xffffffffu, m, 0);
-      sm = __shfl_sync(0xffffffffu, sm, 0);
-      lse = m + __logf(sm);
+  if (threadIdx.x == 0) {
+    float m = sh_m[0], sm = sh_s[0];
+    for (int w = 1; w < kTopkThreads / 32; ++w) {
+      const float om = sh_m[w], os = sh_s[w];
+      const float nm = fmaxf(m, om);
+      sm = (m == -INFINITY ? 0.f : sm * __expf(m - nm)) + (om == -INFINITY ? 0.f : os * __expf(om - nm));
+      m = nm;
     }
-    int hd = 0;
-#pragma unroll 1
-    for (int r = 0; r < K; ++r) {
-      const bool have = lane < kW && hd < K && sh_c[lane][hd].idx >= 0;
-      float ms = have ? sh_c[lane][hd].s : -INFINITY;
-      int ml = have ? lane : 64;
-#pragma unroll
-      for (int o = 4; o > 0; o >>= 1) {
-        const float os = __shfl_xor_sync(0xffffffffu, ms, o);
-        const int ol = __shfl_xor_sync(0xffffffffu, ml, o);
-        if (os > ms || (os == ms && ol < ml)) {
-          ms = os;
-          ml = ol;
-        }
-      }
-      ms = __shfl_sync(0xffffffffu, ms, 0);
-      ml = __shfl_sync(0xffffffffu, ml, 0);
-      if (ml < kW) {
-        const int idx = sh_c[ml][__shfl_sync(0xffffffffu, hd, ml)].idx;
-        if (lane == ml) ++hd;
-        if (lane == 0) {
-          out[r].s = prev + ms - lse;
-          out[r].idx = h * V + idx;
-        }
-      } else if (lane == 0) {
-        out[r].s = -INFINITY;
-        out[r].idx = -1;
+    sh_lse = normalized ? 0.f : m + __logf(sm);
+  }
+  __syncthreads();
+  float theta = sh_gmax[0];
+  for (int j = 1; j < K; ++j) theta = fminf(theta, sh_gmax[j]);
+  // pass 2 (the row comes from L1 / L2 now): collect everything >= theta
+  for_each_in_row(logits, is_bf16, (size_t)row, V, [&](float x, int v) {
+    if (x >= theta) {
+      const int pos = atomicAdd(&sh_cnt, 1);
+      if (pos < kTopkCap) {
+        sh_c[pos].s = x;
+        sh_c[pos].idx = v;
       }
     }
+  });
+  __syncthreads();
+  const int M = sh_cnt;
+  const float lse = sh_lse;
+  if (M <= kTopkCap) {
+    for (int c = threadIdx.x; c < M; c += kTopkThreads) {
+      const float x = sh_c[c].s;
+      const int v = sh_c[c].idx;
+      int before = 0;
+      for (int j = 0; j < M; ++j) before += cand_before(sh_c[j].s, sh_c[j].idx, x, v) ? 1 : 0;
+      if (before < K) {
+        out[before].s = prev + x - lse;
+        out[before].idx = h * V + v;
+      }
+    }
+    for (int r = M + threadIdx.x; r < K; r += kTopkThreads) {  // fewer than K elements in the row
+      out[r].s = -INFINITY;
+      out[r].idx = -1;
+    }
+    return;
+  }
+  // many equal values: K rounds, each the best element that comes after the previous winner in (score desc, index asc) order
+  float last_s = INFINITY;
+  int last_i = -1;
+  for (int r = 0; r < K; ++r) {
+    float bs = -INFINITY;
+    int bi = 0x7fffffff;
+    for_each_in_row(logits, is_bf16, (size_t)row, V, [&](float x, int v) {
+      const bool after_last = x < last_s || (x == last_s && v > last_i);
+      if (after_last && cand_before(x, v, bs, bi)) {
+        bs = x;
+        bi = v;
+      }
+    });
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (cand_before(os, oi, bs, bi)) {
+        bs = os;
+        bi = oi;
+      }
+    }
+    if (lane == 0) {
+      sh_best[warp].s = bs;
+      sh_best[warp].idx = bi;
+    }
+    __syncthreads();
+    bs = sh_best[0].s;
+    bi = sh_best[0].idx;
+    for (int w = 1; w < kTopkThreads / 32; ++w) {
+      if (cand_before(sh_best[w].s, sh_best[w].idx, bs, bi)) {
+        bs = sh_best[w].s;
+        bi = sh_best[w].idx;
+      }
+    }
+    __syncthreads();
+    const bool found = bi != 0x7fffffff;
+    if (threadIdx.x == 0) {
+      out[r].s = found ? prev + bs - lse : -INFINITY;
+      out[r].idx = found ? h * V + bi : -1;
+    }
+    last_s = found ? bs : -INFINITY;
+    last_i = found ? bi : 0x7fffffff;
   }
 }
 
@@ -436,17 +447,8 @@ RB_EXPORT int rb200_beam_topk(const void* logits, int is_bf16, int normalized, c
   }
   Cand* cands = reinterpret_cast<Cand*>(scratch);
   const int rows = batch * beam;
-  int kt;
-  if (k <= 8) {
-    kt = 8;
-    beam_topk_row_kernel<8><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
-  } else if (k <= 16) {
-    kt = 16;
-    beam_topk_row_kernel<16><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
-  } else {
-    kt = 32;
-    beam_topk_row_kernel<32><<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, cands);
-  }
+  const int kt = k <= 8 ? 8 : (k <= 16 ? 16 : 32);  // candidates kept per row (the scratch is sized for this)
+  beam_topk_row_kernel<<<rows, kTopkThreads, 0, stream>>>(logits, is_bf16, normalized, prev_scores, (const uint8_t*)finished, beam, V, eos, kt, cands);
   int rc = rb_check_launch("beam_topk rows");
   if (rc != RB_OK) return rc;
   beam_topk_merge_kernel<<<batch, 32, 0, stream>>>(cands, beam, kt, V, out_scores, out_backref, out_label, k);

@@ -6,6 +6,10 @@ An FSA batch is a :class:`FsaBatch`: edge arrays ``from, to, emission`` (int32 `
 ``edge_start [B+1]``), ``weights [E]`` (negative log), ``start / end / end2 [B]`` state indices (``end2 = -1``: only one
 final state) and the total number of states. Every edge consumes one frame.
 
+Two generalisations run on the same engine: any number of weighted final states per sequence (``fast_baum_welch_multi_end``;
+MultiEndFastBaumWelchOp, returnn/native_op.py:4064) and edges that consume a whole segment of 1 .. L frames with a length model
+(``segment_fast_baum_welch``; SegmentFastBaumWelchOp, :4369).
+
 Reference ops: FastBaumWelchOp (returnn/native_op.py:3259), FastViterbiOp (:4948), GetCtcFsaFastBwOp (:5320);
 ``ctc_loss_via_fsa`` is the counterpart of the ``use_native_op=True`` path of ``rf.ctc_loss``
 (returnn/torch/frontend/_backend.py:832-843).
@@ -175,6 +179,169 @@ def fast_baum_welch(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor) 
         _lib.count_launch()
         return -out, -obs
     return fast_baum_welch_reference(am_scores.float(), fsa, lens)
+
+
+def fast_baum_welch_multi_end_reference(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor, end_start: torch.Tensor, end_state: torch.Tensor,
+                                        end_weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """torch implementation of :func:`fast_baum_welch_multi_end`"""
+    T, B, V = am_scores.shape
+    dev = am_scores.device
+    S = fsa.num_states
+    seq = fsa.edge_seq()
+    ef, et, ee = fsa.e_from.long(), fsa.e_to.long(), fsa.e_em.long()
+    lens_d = lens.to(dev)
+    ninf = float("-inf")
+    fwd = [torch.full((S,), ninf, device=dev).index_fill(0, fsa.start.long(), 0.0)]
+    for t in range(T):
+        active = (t < lens_d)[seq]
+        sc = torch.where(active, fwd[t][ef] - fsa.weights - am_scores[t, seq, ee], torch.full((ef.shape[0],), ninf, device=dev))
+        fwd.append(_scatter_logsumexp(sc, et, S))
+    bwd_t = torch.full((T + 1, S), ninf, device=dev)
+    es = end_start.tolist()
+    for b in range(B):
+        Tb = int(lens[b])
+        for i in range(es[b], es[b + 1]):
+            st = int(end_state[i])
+            bwd_t[Tb, st] = torch.logaddexp(bwd_t[Tb, st], -end_weight[i].to(dev))
+    for t in range(T - 1, -1, -1):
+        active = (t < lens_d)[seq]
+        sc = torch.where(active, bwd_t[t + 1][et] - fsa.weights - am_scores[t, seq, ee], torch.full((ef.shape[0],), ninf, device=dev))
+        cur = _scatter_logsumexp(sc, ef, S)
+        bwd_t[t] = torch.where(torch.isinf(bwd_t[t]), cur, torch.logaddexp(bwd_t[t], cur))
+    total = bwd_t[0][fsa.start.long()]
+    out = torch.full((T, B, V), ninf, device=dev)
+    for t in range(T):
+        active = (t < lens_d)[seq]
+        sc = fwd[t][ef] - fsa.weights - am_scores[t, seq, ee] + bwd_t[t + 1][et] - total[seq]
+        sc = torch.where(active, sc, torch.full_like(sc, ninf))
+        out[t] = _scatter_logsumexp(sc, seq * V + ee, B * V).reshape(B, V)
+    return -out, -total
+
+
+def fast_baum_welch_multi_end(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor, *, end_states: torch.Tensor,
+                              end_state_weights: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """
+    Full-sum forward-backward where every sequence may end in several states, each with its own weight
+    (``fsa.end`` / ``fsa.end2`` are not used).
+
+    :param am_scores: [T, B, V] negative log scores
+    :param end_states: [N, 2] int: (sequence index, state index), in any order
+    :param end_state_weights: [N] negative log weight of ending in that state
+    :return: (fwdbwd [T, B, V] -log posteriors, obs_scores [B] -log total score incl. the end weights)
+    """
+    T, B, V = am_scores.shape
+    dev = am_scores.device
+    es = end_states.to(dev).long()
+    order = torch.argsort(es[:, 0], stable=True)
+    seq_of = es[order, 0]
+    end_state = es[order, 1].to(torch.int32).contiguous()
+    end_weight = end_state_weights.to(dev, torch.float32)[order].contiguous()
+    counts = torch.bincount(seq_of, minlength=B)
+    end_start = torch.zeros(B + 1, dtype=torch.int32, device=dev)
+    end_start[1:] = torch.cumsum(counts, 0).to(torch.int32)
+    if _native(am_scores, "rb200_fsa_fbw_multi_end"):
+        am = am_scores.float().contiguous()
+        S = fsa.num_states
+        fwd = torch.full((T + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        bwd = torch.full((T + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        out = torch.full((T, B, V), float("-inf"), dtype=torch.float32, device=dev)
+        obs = torch.empty(B, dtype=torch.float32, device=dev)
+        l32 = lens.to(dev, torch.int32).contiguous()
+        fn = _lib.bind("rb200_fsa_fbw_multi_end", [_vp] * 11 + [_i32] * 4 + [_vp] * 5)
+        _lib.check(fn(fsa.e_from.data_ptr(), fsa.e_to.data_ptr(), fsa.e_em.data_ptr(), fsa.weights.data_ptr(), fsa.edge_start.data_ptr(), am.data_ptr(),
+                      fsa.start.data_ptr(), end_start.data_ptr(), end_state.data_ptr(), end_weight.data_ptr(), l32.data_ptr(), T, B, V, S,
+                      fwd.data_ptr(), bwd.data_ptr(), out.data_ptr(), obs.data_ptr(), _lib.stream_ptr()), "fsa_fbw_multi_end")
+        _lib.count_launch()
+        return -out, -obs
+    return fast_baum_welch_multi_end_reference(am_scores.float(), fsa, lens, end_start.cpu(), end_state, end_weight)
+
+
+def segment_fast_baum_welch_reference(am_scores: torch.Tensor, fsa: FsaBatch, e_lenmod: torch.Tensor, length_models: torch.Tensor, row_start: torch.Tensor,
+                                      lens: torch.Tensor, am_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """torch implementation of :func:`segment_fast_baum_welch`: a loop over frames, vectorised over (edge, length)"""
+    N, L, V = am_scores.shape
+    dev = am_scores.device
+    S = fsa.num_states
+    B = fsa.batch
+    seq = fsa.edge_seq()
+    ef, et, ee, lm = fsa.e_from.long(), fsa.e_to.long(), fsa.e_em.long(), e_lenmod.long().to(dev)
+    lens_d = lens.to(dev).long()
+    rows = row_start.to(dev).long()
+    T = int(lens.max()) if B else 0
+    ninf = float("-inf")
+    E = ef.shape[0]
+    ar = torch.arange(L, device=dev)
+
+    def costs(t: int):
+        """[E, L] cost of every edge with every length at start frame t; +inf where the segment leaves the sequence"""
+        row = torch.clamp(rows[seq] + t, max=N - 1)
+        c = fsa.weights[:, None] + am_scale * am_scores[row[:, None], ar[None, :], ee[:, None]] + length_models.to(dev)[lm]
+        ok = (t + ar[None, :] + 1) <= lens_d[seq][:, None]
+        return torch.where(ok, c, torch.full_like(c, float("inf")))
+
+    fwd = torch.full((T + L + 1, S), ninf, device=dev)
+    fwd[0, fsa.start.long()] = 0.0
+    for t in range(T):
+        sc = fwd[t][ef][:, None] - costs(t)  # [E, L]
+        for l in range(L):
+            upd = _scatter_logsumexp(sc[:, l], et, S)
+            fwd[t + l + 1] = torch.logaddexp(fwd[t + l + 1], upd)
+    bwd = torch.full((T + L + 1, S), ninf, device=dev)
+    for b in range(B):
+        bwd[int(lens[b]), int(fsa.end[b])] = 0.0
+    for t in range(T - 1, -1, -1):
+        c = costs(t)
+        nxt = torch.stack([bwd[t + l + 1][et] for l in range(L)], dim=1)  # [E, L]
+        sc = torch.logsumexp(nxt - c, dim=1)
+        cur = _scatter_logsumexp(sc, ef, S)
+        bwd[t] = torch.logaddexp(bwd[t], cur)
+    total = bwd[0][fsa.start.long()]
+    out = torch.full((N * L * V,), ninf, device=dev)
+    for t in range(T):
+        c = costs(t)
+        nxt = torch.stack([bwd[t + l + 1][et] for l in range(L)], dim=1)
+        sc = fwd[t][ef][:, None] - c + nxt - total[seq][:, None]  # [E, L]
+        row = torch.clamp(rows[seq] + t, max=N - 1)
+        idx = (row[:, None] * L + ar[None, :]) * V + ee[:, None]
+        valid = torch.isfinite(sc)
+        upd = _scatter_logsumexp(torch.where(valid, sc, torch.full_like(sc, ninf)).reshape(-1), idx.reshape(-1), N * L * V)
+        out = torch.logaddexp(out, upd)
+    return -out.reshape(N, L, V), -total
+
+
+def segment_fast_baum_welch(am_scores: torch.Tensor, fsa: FsaBatch, *, e_lenmod: torch.Tensor, length_models: torch.Tensor, row_start: torch.Tensor,
+                            lens: torch.Tensor, am_scale: float = 1.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """
+    Segmental full-sum: an edge taken at frame ``t`` consumes ``l`` = 1 .. L frames and costs
+    ``weight + am_scale * am_scores[row_start[b] + t, l - 1, emission] + length_models[e_lenmod[e], l - 1]``.
+
+    :param am_scores: [N, L, V] negative log scores, one row per (sequence, segment start frame); the rows of sequence b are
+        ``row_start[b] .. row_start[b] + lens[b]``
+    :param e_lenmod: [E] int: which length model each edge uses
+    :param length_models: [M, L] negative log probability of every segment length
+    :return: (posteriors [N, L, V] as -log of P(a segment with this start, length and label), obs_scores [B])
+    """
+    N, L, V = am_scores.shape
+    dev = am_scores.device
+    if _native(am_scores, "rb200_fsa_seg_fbw"):
+        am = am_scores.float().contiguous()
+        S, B = fsa.num_states, fsa.batch
+        t_max = int(lens.max()) if B else 0
+        fwd = torch.full((t_max + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        bwd = torch.full((t_max + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        out = torch.full((N, L, V), float("-inf"), dtype=torch.float32, device=dev)
+        obs = torch.empty(B, dtype=torch.float32, device=dev)
+        l32 = lens.to(dev, torch.int32).contiguous()
+        rs = row_start.to(dev, torch.int32).contiguous()
+        lm = e_lenmod.to(dev, torch.int32).contiguous()
+        lmod = length_models.to(dev, torch.float32).contiguous()
+        fn = _lib.bind("rb200_fsa_seg_fbw", [_vp] * 12 + [_i32] * 5 + [ctypes.c_float] + [_vp] * 5)
+        _lib.check(fn(fsa.e_from.data_ptr(), fsa.e_to.data_ptr(), fsa.e_em.data_ptr(), lm.data_ptr(), fsa.weights.data_ptr(), fsa.edge_start.data_ptr(),
+                      am.data_ptr(), lmod.data_ptr(), rs.data_ptr(), fsa.start.data_ptr(), fsa.end.data_ptr(), l32.data_ptr(), B, L, V, S, t_max,
+                      float(am_scale), fwd.data_ptr(), bwd.data_ptr(), out.data_ptr(), obs.data_ptr(), _lib.stream_ptr()), "fsa_seg_fbw")
+        _lib.count_launch()
+        return -out, -obs
+    return segment_fast_baum_welch_reference(am_scores.float(), fsa, e_lenmod, length_models.float(), row_start, lens, am_scale)
 
 
 def fast_viterbi_reference(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
