@@ -2,13 +2,13 @@
 //
 //   ctc_lse_gather   one warp per frame: log-sum-exp over the vocabulary (online softmax, one pass), then the
 //                    log-probabilities of the 2S+1 extended states (blank, l1, blank, l2, ..., blank) of that frame
-//   ctc_alpha_beta   one CTA per sequence: alpha and beta recursions over time in shared memory (double buffered),
-//                    log-likelihood, and the state occupancies gamma[t,s] = exp(alpha + beta - lp - logP)
-//   ctc_grad         CTAs over frames: occupancies scattered per class into a dense shared-memory row (several states
-//                    share a class: all blanks, repeated labels), then grad[t,:] = softmax[t,:] - occupancy in one pass
+//   ctc_alpha_beta   one CTA per sequence: the alpha and the beta recursion run at the same time in the two halves of the CTA
+//                    (shared memory, double buffered), and the log-likelihood
+//   ctc_grad         CTAs over frames: softmax[t,:] streamed to the output, then the entries of the label classes corrected by
+//                    their occupancies exp(alpha + beta - lp - logP) (several states share a class: all blanks, repeated labels)
 //
 // The [T, V] log-probabilities are never materialised. Scratch (global memory, given by the caller):
-// lse [N], lp [N, SE], ab [N, SE] floats with SE = 2 * max_target_len + 1, and logp [B].
+// lse [N], lp [N, SE], alpha [N, SE], beta [N, SE] floats with SE = 2 * max_target_len + 1, and logp [B].
 // Infeasible alignments (fewer frames than needed) give loss 0 and zero gradient (zero_infinity semantics).
 #include <algorithm>
 #include "common.cuh"
@@ -263,63 +263,101 @@ ctc_alpha_beta_kernel(const float* __restrict__ lp, float* __restrict__ al, floa
   }
 }
 
-// one CTA handles `frames_per_cta` consecutive frames; dynamic shared memory: V floats (dense class occupancy)
+// Gradient w.r.t. the logits: softmax(logits) - (occupancy of each class). One CTA handles kGradFrames consecutive frames.
+// Only the classes of the label sequence (at most 2S + 1 states, S + 1 distinct classes) have a non-zero occupancy, so the kernel
+// first streams softmax(logits) for its frames straight to the output (no shared memory on that path), and then corrects the few
+// label entries: state s "owns" its class if no earlier state has the same one; the owner sums the occupancies
+// exp(alpha + beta - lp - logP) of all states with that class and rewrites the one output element.
+// Dynamic shared memory: kGradFrames * SE floats (occupancies) + kGradFrames * SE ints (classes).
+constexpr int kGradFrames = 8;
+
 __global__ void __launch_bounds__(256)
 ctc_grad_kernel(const void* __restrict__ logits, int is_bf16, const int* __restrict__ row_batch, const int* __restrict__ targets,
                 const int* __restrict__ tgt_lens, const float* __restrict__ lse, const float* __restrict__ lp, const float* __restrict__ al,
                 const float* __restrict__ be, const float* __restrict__ logp, void* __restrict__ grad, int n_rows, int V, int s_pitch, int SE,
-                int blank, int frames_per_cta) {
-  extern __shared__ float post[];
-  for (int v = threadIdx.x; v < V; v += blockDim.x) post[v] = 0.f;
-  __syncthreads();
-  const int r_begin = blockIdx.x * frames_per_cta;
-  const int r_end = min(n_rows, r_begin + frames_per_cta);
+                int blank) {
+  extern __shared__ float gsm[];
+  float* gam = gsm;                                                  // [kGradFrames][SE]
+  int* gcls = reinterpret_cast<int*>(gsm + kGradFrames * SE);         // [kGradFrames][SE]
+  const int r_begin = blockIdx.x * kGradFrames;
+  const int r_end = min(n_rows, r_begin + kGradFrames);
   const int elem = is_bf16 ? 2 : 4;
   const int per16 = 16 / elem;
+  // occupancies and classes of the frames' states (independent of the streaming pass below)
   for (int r = r_begin; r < r_end; ++r) {
     const int b = row_batch[r];
     const float lpz = logp[b];
-    const bool feasible = lpz != kNegInf;
     const int se = 2 * tgt_lens[b] + 1;
-    if (feasible) {
-      for (int s = threadIdx.x; s < se; s += blockDim.x) {
-        // occupancy of state s at this frame; beta already contains the frame's own log-probability
-        const float a = al[(size_t)r * SE + s], bt = be[(size_t)r * SE + s];
-        const float g = (a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lp[(size_t)r * SE + s] - lpz);
-        if (g != 0.f) {
-          const int c = (s & 1) ? targets[(size_t)b * s_pitch + (s >> 1)] : blank;
-          atomicAdd(&post[c], g);
-        }
-      }
+    for (int s = threadIdx.x; s < se; s += blockDim.x) {
+      const float a = al[(size_t)r * SE + s], bt = be[(size_t)r * SE + s];
+      // beta already contains the frame's own log-probability
+      gam[(r - r_begin) * SE + s] = (lpz == kNegInf || a == kNegInf || bt == kNegInf) ? 0.f : __expf(a + bt - lp[(size_t)r * SE + s] - lpz);
+      gcls[(r - r_begin) * SE + s] = (s & 1) ? targets[(size_t)b * s_pitch + (s >> 1)] : blank;
     }
-    __syncthreads();
+  }
+  // softmax of every frame, streamed
+  for (int r = r_begin; r < r_end; ++r) {
+    const bool feasible = logp[row_batch[r]] != kNegInf;
     const size_t base = (size_t)r * V;
     const float l = lse[r];
     int head = (int)((per16 - (base % per16)) % per16);
     if (head > V) head = V;
     const int body8 = is_bf16 ? ((V - head) / 8) * 8 : 0;
-    // scalar head and tail around the 16-byte aligned vector body
-    for (int c = threadIdx.x; c < V - body8; c += blockDim.x) {
+    for (int c = threadIdx.x; c < V - body8; c += blockDim.x) {  // scalar head and tail around the 16-byte aligned vector body
       const int cc = c < head ? c : c + body8;
-      const float g = feasible ? __expf(ldf(logits, base + cc, is_bf16) - l) - post[cc] : 0.f;
+      const float g = feasible ? __expf(ldf(logits, base + cc, is_bf16) - l) : 0.f;
       if (is_bf16) reinterpret_cast<__nv_bfloat16*>(grad)[base + cc] = __float2bfloat16(g);
       else reinterpret_cast<float*>(grad)[base + cc] = g;
     }
-    for (int c = head + threadIdx.x * 8; c < head + body8; c += blockDim.x * 8) {
-      F8 a = load8(logits, base + c, 1);
+    // four independent 16-byte loads per thread in flight (a row is about five vectors per thread): the pass is bound by
+    // memory latency times bytes in flight, not by arithmetic
+    constexpr int kU = 4;
+    const int n_vec = body8 >> 3;
+    for (int v0 = threadIdx.x; v0 < n_vec; v0 += blockDim.x * kU) {
+      F8 a[kU];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) a.v[k] = feasible ? __expf(a.v[k] - l) - post[c + k] : 0.f;
-      store8(grad, base + c, a, 1);
-    }
-    __syncthreads();
-    // clear the touched classes for the next frame
-    if (feasible) {
-      for (int s = threadIdx.x; s < se; s += blockDim.x) {
-        const int c = (s & 1) ? targets[(size_t)b * s_pitch + (s >> 1)] : blank;
-        post[c] = 0.f;
+      for (int u = 0; u < kU; ++u) {
+        const int v = v0 + u * blockDim.x;
+        if (v < n_vec) a[u] = load8(logits, base + head + (size_t)v * 8, 1);
+      }
+#pragma unroll
+      for (int u = 0; u < kU; ++u) {
+        const int v = v0 + u * blockDim.x;
+        if (v < n_vec) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) a[u].v[k] = feasible ? __expf(a[u].v[k] - l) : 0.f;
+          store8(grad, base + head + (size_t)v * 8, a[u], 1);
+        }
       }
     }
-    __syncthreads();
+  }
+  __syncthreads();  // the streamed values are in place (and visible to this CTA) before single elements are rewritten
+  for (int r = r_begin; r < r_end; ++r) {
+    const int b = row_batch[r];
+    if (logp[b] == kNegInf) continue;
+    const int se = 2 * tgt_lens[b] + 1;
+    const float* g_r = gam + (r - r_begin) * SE;
+    const int* c_r = gcls + (r - r_begin) * SE;
+    const size_t base = (size_t)r * V;
+    const float l = lse[r];
+    for (int s = threadIdx.x; s < se; s += blockDim.x) {
+      const int c = c_r[s];
+      bool first = true;
+      float total = 0.f;
+      for (int q = 0; q < se; ++q) {
+        if (c_r[q] == c) {
+          if (q < s) {
+            first = false;
+            break;
+          }
+          total += g_r[q];
+        }
+      }
+      if (!first || total == 0.f) continue;
+      const float g = __expf(ldf(logits, base + c, is_bf16) - l) - total;
+      if (is_bf16) reinterpret_cast<__nv_bfloat16*>(grad)[base + c] = __float2bfloat16(g);
+      else reinterpret_cast<float*>(grad)[base + c] = g;
+    }
   }
 }
 
@@ -341,7 +379,7 @@ RB_EXPORT int rb200_ctc_loss(const void* logits, int is_bf16, const int* cu, con
     return RB_ERR_ARG;
   }
   const size_t smem_ab = (size_t)(5 * SE) * sizeof(float);
-  const size_t smem_grad = (size_t)V * sizeof(float);
+  const size_t smem_grad = (size_t)kGradFrames * SE * 2 * sizeof(float);
   if (smem_ab > 200 * 1024 || smem_grad > 200 * 1024) {
     rb_set_error("ctc_loss: target length %d or vocabulary %d too large for the shared-memory buffers", max_s, V);
     return RB_ERR_UNSUPPORTED;
@@ -363,9 +401,8 @@ RB_EXPORT int rb200_ctc_loss(const void* logits, int is_bf16, const int* cu, con
   if (st) return st;
   if (n_rows > 0 && grad != nullptr) {
     if (smem_grad > 48 * 1024) cudaFuncSetAttribute(ctc_grad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_grad);
-    const int frames_per_cta = 8;
-    ctc_grad_kernel<<<(n_rows + frames_per_cta - 1) / frames_per_cta, 256, smem_grad, stream>>>(
-        logits, is_bf16, row_batch, targets, tgt_lens, lse, lp, al, be, logp, grad, n_rows, V, s_pitch, SE, blank, frames_per_cta);
+    ctc_grad_kernel<<<(n_rows + kGradFrames - 1) / kGradFrames, 256, smem_grad, stream>>>(
+        logits, is_bf16, row_batch, targets, tgt_lens, lse, lp, al, be, logp, grad, n_rows, V, s_pitch, SE, blank);
     st = rb_check_launch("ctc_grad");
   }
   return st;

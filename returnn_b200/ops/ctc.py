@@ -30,8 +30,8 @@ def supports(logits, targets) -> bool:
 
 
 def max_target_len() -> int:
-    """longest label sequence the kernel handles (5 * (2S+1) floats of shared memory per sequence)"""
-    return 4000
+    """longest label sequence the kernels handle (the gradient kernel keeps 16 * (2S+1) floats in shared memory)"""
+    return 1500
 
 
 class _CtcFn(torch.autograd.Function):
