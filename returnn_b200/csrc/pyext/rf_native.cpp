@@ -168,10 +168,153 @@ PyObject* merge_dims(PyObject*, PyObject* args) {
   return res;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------------
+// raw-tensor side: the view of a raw tensor whose axes follow another dim order (axes the tensor lacks get size 1), and the
+// preparation of a binary op. The raw tensor is only touched through its own methods (permute, __getitem__), so any array type
+// with these works.
+
+// view of `raw` (axes `own`) with axes in the order of `dims`; new reference, or nullptr with an exception set.
+// `own` and `dims` are fast sequences.
+PyObject* compatible_raw(PyObject* raw, PyObject* own, PyObject* dims) {
+  const Py_ssize_t n_own = PySequence_Fast_GET_SIZE(own), n = PySequence_Fast_GET_SIZE(dims);
+  std::vector<char> used((size_t)n_own, 0);
+  std::vector<long> found((size_t)n, -1);
+  bool identity = n == n_own;
+  Py_ssize_t n_found = 0;
+  for (Py_ssize_t j = 0; j < n; ++j) {
+    PyObject* d = PySequence_Fast_GET_ITEM(dims, j);
+    for (Py_ssize_t i = 0; i < n_own; ++i) {
+      if (used[(size_t)i]) continue;
+      const int eq = dim_equal(PySequence_Fast_GET_ITEM(own, i), d);
+      if (eq < 0) return nullptr;
+      if (eq) {
+        found[(size_t)j] = (long)i;
+        used[(size_t)i] = 1;
+        ++n_found;
+        break;
+      }
+    }
+    if (found[(size_t)j] != (long)j) identity = false;
+  }
+  if (n_found != n_own) {
+    PyErr_Format(PyExc_ValueError, "tensor dims %R are not all in the target dims %R", own, dims);
+    return nullptr;
+  }
+  if (identity) {
+    Py_INCREF(raw);
+    return raw;
+  }
+  PyObject* cur = raw;
+  Py_INCREF(cur);
+  // permute when the existing axes change their relative order
+  bool sorted = true;
+  long last = -1;
+  for (Py_ssize_t j = 0; j < n; ++j) {
+    if (found[(size_t)j] < 0) continue;
+    if (found[(size_t)j] < last) sorted = false;
+    last = found[(size_t)j];
+  }
+  if (!sorted) {
+    PyObject* perm = PyTuple_New(n_own);
+    if (!perm) {
+      Py_DECREF(cur);
+      return nullptr;
+    }
+    Py_ssize_t k = 0;
+    for (Py_ssize_t j = 0; j < n; ++j)
+      if (found[(size_t)j] >= 0) PyTuple_SET_ITEM(perm, k++, PyLong_FromLong(found[(size_t)j]));
+    PyObject* meth = PyObject_GetAttrString(cur, "permute");
+    PyObject* res = meth ? PyObject_CallObject(meth, perm) : nullptr;
+    Py_XDECREF(meth);
+    Py_DECREF(perm);
+    Py_DECREF(cur);
+    if (!res) return nullptr;
+    cur = res;
+  }
+  if (n != n_own) {  // raw[None / slice(None), ...]: size-1 axes where the tensor has no such dim
+    PyObject* key = PyTuple_New(n);
+    PyObject* full = key ? PySlice_New(nullptr, nullptr, nullptr) : nullptr;
+    if (!key || !full) {
+      Py_XDECREF(key);
+      Py_XDECREF(full);
+      Py_DECREF(cur);
+      return nullptr;
+    }
+    for (Py_ssize_t j = 0; j < n; ++j) {
+      PyObject* item = found[(size_t)j] < 0 ? Py_None : full;
+      Py_INCREF(item);
+      PyTuple_SET_ITEM(key, j, item);
+    }
+    Py_DECREF(full);
+    PyObject* res = PyObject_GetItem(cur, key);
+    Py_DECREF(key);
+    Py_DECREF(cur);
+    if (!res) return nullptr;
+    cur = res;
+  }
+  return cur;
+}
+
+// copy_compatible_raw(raw, own_dims, target_dims) -> raw view
+PyObject* copy_compatible_raw(PyObject*, PyObject* args) {
+  PyObject *raw, *own_o, *dims_o;
+  if (!PyArg_ParseTuple(args, "OOO", &raw, &own_o, &dims_o)) return nullptr;
+  PyObject *own, *dims;
+  if (!as_fast_seq(own_o, "own must be a sequence", &own)) return nullptr;
+  if (!as_fast_seq(dims_o, "dims must be a sequence", &dims)) {
+    Py_DECREF(own);
+    return nullptr;
+  }
+  PyObject* res = compatible_raw(raw, own, dims);
+  Py_DECREF(own);
+  Py_DECREF(dims);
+  return res;
+}
+
+// bin_op_prepare(a_raw, a_dims, b_raw, b_dims) -> (a_view, b_view, out_dims): both operands as views over the merged dims of a
+// binary op. Fast paths without any matching work: the very same dims tuple, or one operand without dims (a scalar).
+PyObject* bin_op_prepare(PyObject* self, PyObject* args) {
+  PyObject *a_raw, *a_dims_o, *b_raw, *b_dims_o;
+  if (!PyArg_ParseTuple(args, "OOOO", &a_raw, &a_dims_o, &b_raw, &b_dims_o)) return nullptr;
+  if (a_dims_o == b_dims_o && PyTuple_Check(a_dims_o)) return PyTuple_Pack(3, a_raw, b_raw, a_dims_o);
+  PyObject *ad, *bd;
+  if (!as_fast_seq(a_dims_o, "a dims must be a sequence", &ad)) return nullptr;
+  if (!as_fast_seq(b_dims_o, "b dims must be a sequence", &bd)) {
+    Py_DECREF(ad);
+    return nullptr;
+  }
+  PyObject* res = nullptr;
+  const Py_ssize_t na = PySequence_Fast_GET_SIZE(ad), nb = PySequence_Fast_GET_SIZE(bd);
+  if (nb == 0 || na == 0) {
+    PyObject* out = PySequence_Tuple(nb == 0 ? ad : bd);
+    if (out) {
+      res = PyTuple_Pack(3, a_raw, b_raw, out);
+      Py_DECREF(out);
+    }
+  } else {
+    PyObject* margs = PyTuple_Pack(2, ad, bd);
+    PyObject* out = margs ? merge_dims(self, margs) : nullptr;
+    Py_XDECREF(margs);
+    if (out) {
+      PyObject* av = compatible_raw(a_raw, ad, out);
+      PyObject* bv = av ? compatible_raw(b_raw, bd, out) : nullptr;
+      if (av && bv) res = PyTuple_Pack(3, av, bv, out);
+      Py_XDECREF(av);
+      Py_XDECREF(bv);
+      Py_DECREF(out);
+    }
+  }
+  Py_DECREF(ad);
+  Py_DECREF(bd);
+  return res;
+}
+
 PyMethodDef methods[] = {
     {"match_dims", match_dims, METH_VARARGS, "for every dim of `dims` the index in `own` of the first unused equal dim, or -1"},
     {"same_dims", same_dims, METH_VARARGS, "whether two dim sequences are pairwise equal"},
     {"merge_dims", merge_dims, METH_VARARGS, "dims of the result of a binary op on tensors with these dims"},
+    {"copy_compatible_raw", copy_compatible_raw, METH_VARARGS, "view of a raw tensor with axes in the order of other dims (size 1 where missing)"},
+    {"bin_op_prepare", bin_op_prepare, METH_VARARGS, "(a view, b view, out dims) of a binary op"},
     {nullptr, nullptr, 0, nullptr}};
 
 PyModuleDef module_def = {PyModuleDef_HEAD_INIT, "_rf_native", "native dimension bookkeeping of the frontend", -1, methods};

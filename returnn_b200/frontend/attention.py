@@ -188,6 +188,12 @@ class SelfAttention(SelfAttentionBase):
     """bidirectional self-attention over ``axis``"""
 
     def __call__(self, source: Tensor, *, axis: Dim) -> Tensor:
+        if axis not in source.dims:
+            from . import packed_mode
+
+            pdim = packed_mode.packed_dim_of(source, axis)
+            if pdim is not None:  # packed rows: attention inside every sequence, on the padded form
+                return packed_mode.apply_padded(lambda padded: self(padded, axis=axis), source, pdim)
         q, k, v = self.forward_qkv(source)
         kv_axis = Dim(None, name="%s-kv" % axis.name)
         k, _ = _replace(k, axis, kv_axis)
@@ -375,6 +381,12 @@ class RelPosSelfAttention(SelfAttentionBase):
         return pos_emb, pos_dim
 
     def __call__(self, source: Tensor, *, axis: Dim, **_kwargs) -> Tensor:
+        if axis not in source.dims:
+            from . import packed_mode
+
+            pdim = packed_mode.packed_dim_of(source, axis)
+            if pdim is not None:
+                return self._call_packed(source, axis=axis, pdim=pdim)
         pos_emb, pos_dim = self._pos_emb(axis, source.device)
         q, k, v = self.forward_qkv(source)
         batch_dims = [d for d in q.dims if d not in (axis, self.num_heads, self.key_dim_per_head)]
@@ -409,6 +421,39 @@ class RelPosSelfAttention(SelfAttentionBase):
         if self.proj:
             output = self.proj(output)
         return output
+
+
+def _rel_pos_self_att_call_packed(self: RelPosSelfAttention, source: Tensor, *, axis: Dim, pdim: Dim) -> Tensor:
+    """
+    ``source [rows, in]`` with the valid frames of all sequences back to back. With the standard configuration (sinusoidal positions
+    through ``linear_pos``, both biases, a position table per head, no broadcast dropout) the packed qkv rows go straight to the
+    varlen attention (``ops/attention_packed.py``: own kernels on the GPU); otherwise the padded form runs and the result is packed.
+    """
+    from . import packed_mode
+    from ..ops import attention_packed as _ap
+
+    p_drop = _train_dropout(self.att_dropout)
+    standard = (self.linear_pos is not None and self.pos_bias_u is not None and self.pos_bias_v is not None and self.separate_pos_emb_per_head
+                and self.learned_pos_emb is None and not (p_drop and self.att_dropout_broadcast)
+                and self.key_dim_per_head == self.value_dim_per_head and len(source.dims) == 2)
+    if not standard:
+        return packed_mode.apply_padded(lambda padded: self(padded, axis=axis), source, pdim)
+    info = pdim.packed_info
+    pos_emb, pos_dim = self._pos_emb(axis, source.device)  # [2 T_max - 1, heads * dim] after linear_pos
+    qkv = self.qkv(source)  # [rows, heads * (q | k | v)]
+    H, D = self.num_heads.dimension, self.key_dim_per_head.dimension
+    qkv_raw = qkv.copy_compatible_to_dims_raw([pdim, self.qkv_dim_total])
+    # the kernels want (q | k | v) per head contiguous: [rows, H, 3, D], which is the layout of the fused projection
+    pos_raw = pos_emb.copy_compatible_to_dims_raw([pos_dim, self.num_heads, self.key_dim_per_head]).reshape(-1, H * D).to(qkv_raw.dtype)
+    out_raw = _ap.rel_pos_attention_packed(qkv_raw.contiguous(), pos_raw.contiguous(), self.pos_bias_u.raw_tensor, self.pos_bias_v.raw_tensor, info.pack,
+                                           num_heads=H, head_dim=D, scale=D ** -0.5, dropout_p=p_drop)
+    output = wrap(out_raw, [pdim, self.value_dim_total], feature_dim=self.value_dim_total)
+    if self.proj:
+        output = self.proj(output)
+    return output
+
+
+RelPosSelfAttention._call_packed = _rel_pos_self_att_call_packed
 
 
 def _rel_pos_enc_shift(x: Tensor, axis: Dim, pos_emb_spatial_dim: Dim, hist_dim: Dim) -> Tensor:

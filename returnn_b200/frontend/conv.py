@@ -122,6 +122,15 @@ def conv(source: Tensor, *, in_dim: Dim, out_dim: Dim, in_spatial_dims: Sequence
     N-d convolution (N = 1, 2, 3). filter dims: ``(out_dim, in_dim // groups, *filter_size)``.
     """
     n = len(in_spatial_dims)
+    if n == 1 and in_spatial_dims[0] not in source._dims:
+        from . import packed_mode
+
+        pdim = packed_mode.packed_dim_of(source, in_spatial_dims[0])
+        if pdim is not None:  # packed rows: no padded frames exist, so nothing to mask; run on the padded form and pack the result
+            return packed_mode.apply_padded(
+                lambda padded: conv(padded, in_dim=in_dim, out_dim=out_dim, in_spatial_dims=in_spatial_dims, out_spatial_dims=out_spatial_dims,
+                                    filter=filter, filter_size=filter_size, padding=padding, strides=strides, dilation_rate=dilation_rate, groups=groups,
+                                    bias=bias, use_mask=use_mask), source, pdim)
     source = _mask_input(source, in_spatial_dims, use_mask)
     if not out_spatial_dims:
         out_spatial_dims = make_conv_out_spatial_dims(in_spatial_dims, filter_size=filter_size, strides=strides or 1,
@@ -330,6 +339,14 @@ def pool(source: Tensor, *, mode: str, pool_size: Union[Sequence[int], int], pad
     if isinstance(in_spatial_dims, Dim):
         in_spatial_dims = [in_spatial_dims]
     n = len(in_spatial_dims)
+    if n == 1 and in_spatial_dims[0] not in source._dims:
+        from . import packed_mode
+
+        pdim = packed_mode.packed_dim_of(source, in_spatial_dims[0])
+        if pdim is not None:
+            return packed_mode.apply_padded(
+                lambda padded: pool(padded, mode=mode, pool_size=pool_size, padding=padding, dilation_rate=dilation_rate, strides=strides,
+                                    in_spatial_dims=in_spatial_dims, out_spatial_dims=out_spatial_dims, use_mask=use_mask), source, pdim)
     ps = _tup(pool_size, n)
     st = _tup(strides if strides is not None else ps, n)
     dl = _tup(dilation_rate, n)

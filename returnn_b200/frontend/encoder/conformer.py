@@ -266,6 +266,14 @@ class ConformerEncoder(ISeqDownsamplingEncoder):
         if self.pos_enc is not None:
             x = x + self.pos_enc(spatial_dim=out_spatial_dim)
         x = dropout(x, self.input_dropout, axis=self.dropout_broadcast and self.out_dim)
+        from .. import packed_mode
+
+        batch_dims = [d for d in x.dims if d not in (out_spatial_dim, self.out_dim)]
+        if packed_mode.is_enabled() and len(batch_dims) == 1 and collected_outputs is None:
+            # the layers run on the valid frames only: [rows, model] instead of [batch, time, model]
+            x = packed_mode.pack_padded_tensor(x, dims=(batch_dims[0], out_spatial_dim))
+            x = self.layers(x, spatial_dim=out_spatial_dim)
+            return packed_mode.unpack_to_padded(x), out_spatial_dim
         x = self.layers(x, spatial_dim=out_spatial_dim, collected_outputs=collected_outputs)
         return x, out_spatial_dim
 

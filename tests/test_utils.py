@@ -232,6 +232,32 @@ def test_rf_native_dim_helpers():
         x.get_out_permutation_to_dims([b, batch_dim, c])
     y = Tensor("y", dims=[b], dtype="float32", raw_tensor=torch.ones(4))
     assert (x + y).dims == (batch_dim, a, b) and (y + x).dims == (batch_dim, a, b)
+    # raw views: permutation, size-1 axes for missing dims, the identical tensor when nothing changes
+    raw = torch.arange(24.0).reshape(2, 3, 4)
+    assert mod.copy_compatible_raw(raw, (batch_dim, a, b), (batch_dim, a, b)) is raw
+    v = mod.copy_compatible_raw(raw, (batch_dim, a, b), (b, c, batch_dim, a))
+    assert tuple(v.shape) == (4, 1, 2, 3) and torch.equal(v[:, 0], raw.permute(2, 0, 1)) and v.data_ptr() == raw.data_ptr()
+    with pytest.raises(ValueError):
+        mod.copy_compatible_raw(raw, (batch_dim, a, b), (a, b))
+    # operand preparation of a binary op: same dims tuple, scalar, subset, disjoint dims
+    dims = (batch_dim, a, b)
+    ra, rb, out = mod.bin_op_prepare(raw, dims, raw, dims)
+    assert ra is raw and rb is raw and out is dims
+    ra, rb, out = mod.bin_op_prepare(raw, dims, torch.tensor(2.0), ())
+    assert ra is raw and out == dims and rb.ndim == 0
+    ra, rb, out = mod.bin_op_prepare(torch.ones(4), (b,), raw, dims)
+    assert out == dims and tuple(ra.shape) == (1, 1, 4) and rb is raw
+    ra, rb, out = mod.bin_op_prepare(torch.ones(3), (a,), torch.ones(5), (c,))
+    assert out == (a, c) and tuple(ra.shape) == (3, 1) and tuple(rb.shape) == (1, 5)
+    # through the frontend: the results equal plain torch broadcasting
+    import returnn_b200.frontend as rf
+
+    z = Tensor("z", dims=[b, batch_dim], dtype="float32", raw_tensor=torch.arange(8.0).reshape(4, 2))
+    xr = Tensor("x", dims=[batch_dim, a, b], dtype="float32", raw_tensor=raw)
+    s = xr * z
+    assert s.dims == (batch_dim, a, b) and torch.equal(s.raw_tensor, raw * torch.arange(8.0).reshape(4, 2).t()[:, None, :])
+    assert torch.equal((xr > 11.0).raw_tensor, raw > 11.0) and torch.equal(rf.maximum(xr, 5.0).raw_tensor, raw.clamp_min(5.0))
+    assert torch.equal(xr.copy_compatible_to_dims_raw([a, b, batch_dim]), raw.permute(1, 2, 0))
 
 
 def test_tools_on_small_inputs(tmp_path):
