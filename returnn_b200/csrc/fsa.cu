@@ -48,8 +48,11 @@ fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const i
            const int* __restrict__ edge_start, const float* __restrict__ am, const int* __restrict__ start, const int* __restrict__ end,
            const int* __restrict__ end2, const int* __restrict__ lens, int T, int B, int V, int S, float* __restrict__ fwd,
            float* __restrict__ bwd, float* __restrict__ out, float* __restrict__ obs, const int* __restrict__ end_start,
-           const int* __restrict__ end_state, const float* __restrict__ end_weight) {
+           const int* __restrict__ end_state, const float* __restrict__ end_weight, const int* __restrict__ row_start) {
   const int b = blockIdx.x;
+  // frame t of this sequence: row t * B + b of am / out [T, B, V], or row row_start[b] + t of the packed form [N, V]
+  const size_t r_base = row_start ? (size_t)row_start[b] : (size_t)b;
+  const size_t r_step = row_start ? 1 : (size_t)B;
   const int e0 = edge_start[b], e1 = edge_start[b + 1];
   const int Tb = lens[b];
   if (threadIdx.x == 0) {
@@ -69,7 +72,7 @@ fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const i
   for (int t = 0; t < Tb; ++t) {
     const float* cur = fwd + (size_t)t * S;
     float* nxt = fwd + (size_t)(t + 1) * S;
-    const float* amt = am + ((size_t)t * B + b) * V;
+    const float* amt = am + (r_base + (size_t)t * r_step) * V;
     for (int e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
       const float s = cur[e_from[e]];
       if (s > -INFINITY) atomic_log_add(nxt + e_to[e], s - weights[e] - amt[e_em[e]]);
@@ -79,7 +82,7 @@ fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const i
   for (int t = Tb - 1; t >= 0; --t) {
     const float* nxt = bwd + (size_t)(t + 1) * S;
     float* cur = bwd + (size_t)t * S;
-    const float* amt = am + ((size_t)t * B + b) * V;
+    const float* amt = am + (r_base + (size_t)t * r_step) * V;
     for (int e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
       const float s = nxt[e_to[e]];
       if (s > -INFINITY) atomic_log_add(cur + e_from[e], s - weights[e] - amt[e_em[e]]);
@@ -91,8 +94,8 @@ fbw_kernel(const int* __restrict__ e_from, const int* __restrict__ e_to, const i
   for (int t = 0; t < Tb; ++t) {
     const float* f = fwd + (size_t)t * S;
     const float* bw = bwd + (size_t)(t + 1) * S;
-    const float* amt = am + ((size_t)t * B + b) * V;
-    float* o = out + ((size_t)t * B + b) * V;
+    const float* amt = am + (r_base + (size_t)t * r_step) * V;
+    float* o = out + (r_base + (size_t)t * r_step) * V;
     for (int e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
       const float a = f[e_from[e]], c = bw[e_to[e]];
       if (a > -INFINITY && c > -INFINITY) atomic_log_add(o + e_em[e], a - weights[e] - amt[e_em[e]] + c - total);
@@ -253,7 +256,7 @@ RB_EXPORT int rb200_fsa_fbw(const int* e_from, const int* e_to, const int* e_em,
                             float* out, float* obs, cudaStream_t stream) {
   if (B <= 0) return RB_OK;
   fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, end, end2, lens, T, B, V, S, fwd, bwd, out, obs, nullptr, nullptr,
-                                    nullptr);
+                                    nullptr, nullptr);
   return rb_check_launch("fsa_fbw");
 }
 
@@ -263,8 +266,18 @@ RB_EXPORT int rb200_fsa_fbw_multi_end(const int* e_from, const int* e_to, const 
                                       int B, int V, int S, float* fwd, float* bwd, float* out, float* obs, cudaStream_t stream) {
   if (B <= 0) return RB_OK;
   fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, nullptr, nullptr, lens, T, B, V, S, fwd, bwd, out, obs, end_start,
-                                    end_state, end_weight);
+                                    end_state, end_weight, nullptr);
   return rb_check_launch("fsa_fbw_multi_end");
+}
+
+// as rb200_fsa_fbw on packed scores: am and out are [N, V], the frames of sequence b are rows row_start[b] .. row_start[b] + lens[b]
+RB_EXPORT int rb200_fsa_fbw_packed(const int* e_from, const int* e_to, const int* e_em, const float* weights, const int* edge_start, const float* am,
+                                   const int* start, const int* end, const int* end2, const int* lens, const int* row_start, int T_max, int B, int V,
+                                   int S, float* fwd, float* bwd, float* out, float* obs, cudaStream_t stream) {
+  if (B <= 0) return RB_OK;
+  fbw_kernel<<<B, 256, 0, stream>>>(e_from, e_to, e_em, weights, edge_start, am, start, end, end2, lens, T_max, B, V, S, fwd, bwd, out, obs, nullptr,
+                                    nullptr, nullptr, row_start);
+  return rb_check_launch("fsa_fbw_packed");
 }
 
 // segmental form: see seg_fbw_kernel

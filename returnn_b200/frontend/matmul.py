@@ -34,7 +34,14 @@ def matmul(a: Tensor, b: Tensor, *, reduce: Union[Dim, Sequence[Dim]], use_mask:
             a_raw, b_raw = a_raw.to(common_dtype), b_raw.to(common_dtype)
     # fast path: x[..., in] @ w[in, out]
     if len(red) == 1 and len(bd) == 2 and ad and ad[-1] == red[0] and bd[0] == red[0] and bd[1] not in ad:
-        out = torch.matmul(a_raw, b_raw)
+        if a_raw.is_cuda:
+            # the same route as rf.Linear: the tcgen05 GEMM with its own backward (bf16 operands, i.e. bf16 tensors or autocast),
+            # torch.matmul where that does not apply (fp32 without autocast, pitches that are not multiples of 8)
+            from ..ops import linear as _linear
+
+            out = _linear.linear(a_raw, b_raw)
+        else:
+            out = torch.matmul(a_raw, b_raw)
         res = wrap(out, tuple(ad[:-1]) + (bd[1],), feature_dim=bd[1])
         return res
     common = [d for d in ad if d in bd and d not in red]

@@ -181,6 +181,42 @@ def fast_baum_welch(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor) 
     return fast_baum_welch_reference(am_scores.float(), fsa, lens)
 
 
+def fast_baum_welch_packed(am_scores: torch.Tensor, fsa: FsaBatch, *, row_start: torch.Tensor, lens: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """
+    :func:`fast_baum_welch` on packed scores (FastBaumWelchPackedOp, returnn/native_op.py:3754).
+
+    :param am_scores: [N, V] negative log scores, the frames of sequence b are rows ``row_start[b] .. row_start[b] + lens[b]``
+    :return: (fwdbwd [N, V] -log posteriors, obs_scores [B])
+    """
+    N, V = am_scores.shape
+    B = fsa.batch
+    dev = am_scores.device
+    t_max = int(lens.max()) if B else 0
+    if _native(am_scores, "rb200_fsa_fbw_packed"):
+        am = am_scores.float().contiguous()
+        S = fsa.num_states
+        fwd = torch.full((t_max + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        bwd = torch.full((t_max + 1, S), float("-inf"), dtype=torch.float32, device=dev)
+        out = torch.full((N, V), float("-inf"), dtype=torch.float32, device=dev)
+        obs = torch.empty(B, dtype=torch.float32, device=dev)
+        l32 = lens.to(dev, torch.int32).contiguous()
+        rs = row_start.to(dev, torch.int32).contiguous()
+        fn = _lib.bind("rb200_fsa_fbw_packed", [_vp] * 11 + [_i32] * 4 + [_vp] * 5)
+        _lib.check(fn(fsa.e_from.data_ptr(), fsa.e_to.data_ptr(), fsa.e_em.data_ptr(), fsa.weights.data_ptr(), fsa.edge_start.data_ptr(), am.data_ptr(),
+                      fsa.start.data_ptr(), fsa.end.data_ptr(), fsa.end2.data_ptr(), l32.data_ptr(), rs.data_ptr(), t_max, B, V, S, fwd.data_ptr(),
+                      bwd.data_ptr(), out.data_ptr(), obs.data_ptr(), _lib.stream_ptr()), "fsa_fbw_packed")
+        _lib.count_launch()
+        return -out, -obs
+    padded = torch.zeros(t_max, B, V, dtype=torch.float32, device=dev)
+    for b in range(B):
+        padded[: int(lens[b]), b] = am_scores[int(row_start[b]): int(row_start[b]) + int(lens[b])].float()
+    res, obs = fast_baum_welch(padded, fsa, lens)
+    out = torch.full((N, V), float("inf"), dtype=torch.float32, device=dev)
+    for b in range(B):
+        out[int(row_start[b]): int(row_start[b]) + int(lens[b])] = res[: int(lens[b]), b]
+    return out, obs
+
+
 def fast_baum_welch_multi_end_reference(am_scores: torch.Tensor, fsa: FsaBatch, lens: torch.Tensor, end_start: torch.Tensor, end_state: torch.Tensor,
                                         end_weight: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
     """torch implementation of :func:`fast_baum_welch_multi_end`"""

@@ -205,3 +205,33 @@ def test_segment_baum_welch_cpu():
 @gpu
 def test_segment_baum_welch_kernel():
     _check_segment("cuda")
+
+
+def _check_packed(dev):
+    from returnn_b200.ops import fsa
+
+    logits, targets, in_lens, tgt_lens = _case(dev)
+    V = logits.shape[-1]
+    f = fsa.ctc_fsa(targets, tgt_lens, blank=V - 1)
+    am = -torch.log_softmax(logits.detach().float(), -1).transpose(0, 1).contiguous()  # [T, B, V]
+    out_ref, obs_ref = fsa.fast_baum_welch(am, f, in_lens)
+    rows = [am[: int(in_lens[b]), b] for b in range(am.shape[1])]
+    packed = torch.cat(rows)
+    row_start = torch.tensor([0] + torch.cumsum(in_lens, 0).tolist()[:-1])
+    out, obs = fsa.fast_baum_welch_packed(packed, f, row_start=row_start, lens=in_lens)
+    torch.testing.assert_close(obs.cpu(), obs_ref.cpu(), atol=1e-4, rtol=1e-5)
+    for b in range(am.shape[1]):
+        a = out[int(row_start[b]): int(row_start[b]) + int(in_lens[b])].cpu()
+        r = out_ref[: int(in_lens[b]), b].cpu()
+        fin = torch.isfinite(r)
+        assert bool((torch.isfinite(a) == fin).all())
+        torch.testing.assert_close(a[fin], r[fin], atol=1e-4, rtol=1e-5)
+
+
+def test_packed_baum_welch_cpu():
+    _check_packed("cpu")
+
+
+@gpu
+def test_packed_baum_welch_kernel():
+    _check_packed("cuda")

@@ -119,3 +119,79 @@ def test_device_assert_records_failure_without_trap():
         seq_ops.check_asserts()
     # the context is still usable
     assert int((x + 1).sum()) == 5050
+
+
+def _seq_util_checks(dev):
+    from returnn_b200.ops import seq_util as su
+
+    torch.manual_seed(0)
+    T, B, D = 11, 3, 4
+    x = torch.randn(T, B, D, device=dev)
+    lens = torch.tensor([11, 7, 4])
+    for b in range(B):
+        x[int(lens[b]):, b] = 0
+    y, ym = su.chunk(x, lens, chunk_size=5, chunk_step=3)
+    n = su.num_chunks(T, 5, 3)
+    assert n == 3 and tuple(y.shape) == (5, B * n, D) and tuple(ym.shape) == (5, B * n)
+    for b in range(B):
+        for c in range(n):
+            for ot in range(5):
+                t = c * 3 + ot
+                ok = t < int(lens[b])
+                assert float(ym[ot, b * n + c]) == float(ok)
+                assert torch.equal(y[ot, b * n + c], x[t, b] if ok else torch.zeros(D, device=dev))
+    back, bm, fac = su.unchunk(y, ym, T=T, B=B, chunk_size=5, chunk_step=3)
+    torch.testing.assert_close(back, x, atol=1e-6, rtol=0)  # the mean of equal copies is the value itself
+    assert torch.equal(bm, (torch.arange(T, device=dev)[:, None] < lens.to(dev)[None, :]).float())
+    assert float(fac[3, 0]) == 0.5 and float(fac[0, 0]) == 1.0 and float(fac[5, 0]) == 1.0  # frames 3, 4 lie in windows 0 and 1
+    # windows with different content: overlap is averaged
+    y2 = y.clone()
+    y2[3, 0 * n + 0] += 2.0  # frame 3 of sequence 0 as seen by window 0
+    back2, _, _ = su.unchunk(y2, ym, T=T, B=B, chunk_size=5, chunk_step=3)
+    torch.testing.assert_close(back2[3, 0], x[3, 0] + 1.0, atol=1e-6, rtol=0)
+    # select by index
+    xs = torch.randn(T, B, D, device=dev, requires_grad=True)
+    idx = torch.randint(0, D, (T, B), device=dev)
+    sel = su.select_by_index(xs, idx)
+    torch.testing.assert_close(sel, torch.gather(xs, -1, idx[..., None]).squeeze(-1))
+    gy = torch.randn(T, B, device=dev)
+    sel.backward(gy)
+    ref = torch.zeros(T, B, D, device=dev).scatter_(-1, idx[..., None], gy[..., None])
+    torch.testing.assert_close(xs.grad, ref)
+    # COO targets
+    n_e = 9
+    s0 = torch.randint(0, T, (n_e, B), device=dev)
+    s1 = torch.randint(0, D, (n_e, B), device=dev)
+    w = torch.rand(n_e, B, device=dev)
+    m = (torch.rand(n_e, B, device=dev) > 0.2).float()
+    dense = su.sparse_to_dense(s0, s1, w, m, T=T, D=D)
+    ref = torch.zeros(T, B, D, device=dev)
+    for i in range(n_e):
+        for b in range(B):
+            if m[i, b] > 0:
+                ref[s0[i, b], b, s1[i, b]] += w[i, b]
+    torch.testing.assert_close(dense, ref)
+    mx, am = su.max_and_argmax_sparse(s0, s1, w, m, T=T)
+    for t in range(T):
+        for b in range(B):
+            ent = [(float(w[i, b]), int(s1[i, b])) for i in range(n_e) if m[i, b] > 0 and int(s0[i, b]) == t]
+            if ent:
+                best = max(ent, key=lambda e: (e[0], -e[1]))
+                assert abs(float(mx[t, b]) - best[0]) < 1e-7 and int(am[t, b]) == best[1]
+            else:
+                assert float(mx[t, b]) == float("-inf")
+    z = torch.randn(T, B, D, device=dev)
+    zm = (torch.arange(T, device=dev)[:, None] < lens.to(dev)[None, :]).float()
+    ce, g = su.sparse_ce_softmax_and_grad(z, zm, s0, s1, w, m)
+    logp = torch.log_softmax(z, -1)
+    torch.testing.assert_close(ce, -(ref * logp).sum(-1) * zm, atol=1e-5, rtol=1e-5)
+    torch.testing.assert_close(g, (logp.exp() - ref) * zm[..., None], atol=1e-5, rtol=1e-5)
+
+
+def test_seq_util_references_cpu():
+    _seq_util_checks("cpu")
+
+
+@gpu
+def test_seq_util_kernels():
+    _seq_util_checks("cuda")
