@@ -40,11 +40,11 @@ def _diagonals(T: int, S: int, device) -> List[Tuple[torch.Tensor, torch.Tensor]
 def _cell_fwd(z, c_up, c_left, mask, n: int):
     """z [R, 5n] -> (gates [R, 5n], c [R, n], h [R, n])"""
     if _native(z):
-        z = z.contiguous()
+        z, c_up, c_left = z.contiguous(), c_up.contiguous(), c_left.contiguous()  # local names keep them alive until the launch is queued
         c = torch.empty_like(c_up)
         h = torch.empty_like(c_up)
         fn = _lib.bind("rb200_lstm2d_cell_fwd", [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _vp])
-        _lib.check(fn(z.data_ptr(), c_up.contiguous().data_ptr(), c_left.contiguous().data_ptr(), mask.data_ptr(), c.data_ptr(), h.data_ptr(),
+        _lib.check(fn(z.data_ptr(), c_up.data_ptr(), c_left.data_ptr(), mask.data_ptr(), c.data_ptr(), h.data_ptr(),
                       z.shape[0], n, _lib.stream_ptr()), "lstm2d_cell_fwd")
         _lib.count_launch()
         return z, c, h
@@ -58,12 +58,13 @@ def _cell_fwd(z, c_up, c_left, mask, n: int):
 def _cell_bwd(gates, c, c_up, c_left, mask, dh, dc_in, n: int):
     """-> (dz [R, 5n], dc_up [R, n], dc_left [R, n])"""
     if _native(gates):
+        gates, c, c_up, c_left, dh, dc_in = (t.contiguous() for t in (gates, c, c_up, c_left, dh, dc_in))
         dz = torch.empty_like(gates)
         dc_up = torch.empty_like(c)
         dc_left = torch.empty_like(c)
         fn = _lib.bind("rb200_lstm2d_cell_bwd", [_vp] * 10 + [_i64, _i32, _vp])
-        _lib.check(fn(gates.contiguous().data_ptr(), c.contiguous().data_ptr(), c_up.contiguous().data_ptr(), c_left.contiguous().data_ptr(),
-                      mask.data_ptr(), dh.contiguous().data_ptr(), dc_in.contiguous().data_ptr(), dz.data_ptr(), dc_up.data_ptr(), dc_left.data_ptr(),
+        _lib.check(fn(gates.data_ptr(), c.data_ptr(), c_up.data_ptr(), c_left.data_ptr(),
+                      mask.data_ptr(), dh.data_ptr(), dc_in.data_ptr(), dz.data_ptr(), dc_up.data_ptr(), dc_left.data_ptr(),
                       gates.shape[0], n, _lib.stream_ptr()), "lstm2d_cell_bwd")
         _lib.count_launch()
         return dz, dc_up, dc_left

@@ -41,7 +41,8 @@ def chunk(x: torch.Tensor, lens: torch.Tensor, *, chunk_size: int, chunk_step: i
         y = torch.empty(chunk_size, B * n, D, dtype=torch.float32, device=dev)
         m = torch.empty(chunk_size, B * n, dtype=torch.float32, device=dev)
         fn = _lib.bind("rb200_chunk", [_vp, _vp] + [_i32] * 6 + [_vp, _vp, _vp])
-        _lib.check(fn(x.contiguous().data_ptr(), l32.data_ptr(), T, B, D, chunk_size, chunk_step, n, y.data_ptr(), m.data_ptr(), _lib.stream_ptr()), "chunk")
+        x = x.contiguous()  # (a local name keeps the tensor alive until the launch is queued)
+        _lib.check(fn(x.data_ptr(), l32.data_ptr(), T, B, D, chunk_size, chunk_step, n, y.data_ptr(), m.data_ptr(), _lib.stream_ptr()), "chunk")
         _lib.count_launch()
         return y, m
     ot = torch.arange(chunk_size, device=dev)[:, None, None]
@@ -68,7 +69,8 @@ def unchunk(y: torch.Tensor, y_mask: torch.Tensor, *, T: int, B: int, chunk_size
         xm = torch.empty(T, B, dtype=torch.float32, device=dev)
         fac = torch.empty(T, B, dtype=torch.float32, device=dev)
         fn = _lib.bind("rb200_unchunk", [_vp, _vp] + [_i32] * 6 + [_vp, _vp, _vp, _vp])
-        _lib.check(fn(y.contiguous().data_ptr(), y_mask.contiguous().data_ptr(), T, B, D, chunk_size, chunk_step, n, x.data_ptr(), xm.data_ptr(),
+        y, y_mask = y.contiguous(), y_mask.float().contiguous()
+        _lib.check(fn(y.data_ptr(), y_mask.data_ptr(), T, B, D, chunk_size, chunk_step, n, x.data_ptr(), xm.data_ptr(),
                       fac.data_ptr(), _lib.stream_ptr()), "unchunk")
         _lib.count_launch()
         return x, xm, fac
@@ -103,7 +105,8 @@ class _SelectFn(torch.autograd.Function):
         D = ctx.D
         dx = torch.empty(tuple(dy.shape) + (D,), dtype=torch.float32, device=dy.device)
         fn = _lib.bind("rb200_select_by_index_bwd", [_vp, _vp, _i64, _i32, _vp, _vp])
-        _lib.check(fn(dy.contiguous().float().data_ptr(), idx.data_ptr(), dy.numel(), D, dx.data_ptr(), _lib.stream_ptr()), "select_by_index_bwd")
+        dy = dy.contiguous().float()
+        _lib.check(fn(dy.data_ptr(), idx.data_ptr(), dy.numel(), D, dx.data_ptr(), _lib.stream_ptr()), "select_by_index_bwd")
         _lib.count_launch()
         return dx, None
 
@@ -125,8 +128,8 @@ def sparse_to_dense(s0: torch.Tensor, s1: torch.Tensor, weight: torch.Tensor, ma
     out = initial.clone().float().contiguous() if initial is not None else torch.zeros(T, B, D, dtype=torch.float32, device=dev)
     if _native(weight, "rb200_sparse_to_dense"):
         fn = _lib.bind("rb200_sparse_to_dense", [_vp, _vp, _vp, _vp] + [_i32] * 4 + [_vp, _vp])
-        _lib.check(fn(s0.to(torch.int32).contiguous().data_ptr(), s1.to(torch.int32).contiguous().data_ptr(), weight.float().contiguous().data_ptr(),
-                      mask.float().contiguous().data_ptr(), n, T, B, D, out.data_ptr(), _lib.stream_ptr()), "sparse_to_dense")
+        s0_, s1_, w_, m_ = s0.to(torch.int32).contiguous(), s1.to(torch.int32).contiguous(), weight.float().contiguous(), mask.float().contiguous()
+        _lib.check(fn(s0_.data_ptr(), s1_.data_ptr(), w_.data_ptr(), m_.data_ptr(), n, T, B, D, out.data_ptr(), _lib.stream_ptr()), "sparse_to_dense")
         _lib.count_launch()
         return out
     b = torch.arange(B, device=dev)[None, :].expand(n, B)
@@ -145,8 +148,8 @@ def max_and_argmax_sparse(s0: torch.Tensor, s1: torch.Tensor, weight: torch.Tens
     if _native(weight, "rb200_max_argmax_sparse"):
         best = torch.zeros(T * B, dtype=torch.int64, device=dev)
         fn = _lib.bind("rb200_max_argmax_sparse", [_vp, _vp, _vp, _vp] + [_i32] * 3 + [_vp, _vp, _vp, _vp])
-        _lib.check(fn(s0.to(torch.int32).contiguous().data_ptr(), s1.to(torch.int32).contiguous().data_ptr(), weight.float().contiguous().data_ptr(),
-                      mask.float().contiguous().data_ptr(), n, T, B, best.data_ptr(), out_max.data_ptr(), out_arg.data_ptr(), _lib.stream_ptr()),
+        s0_, s1_, w_, m_ = s0.to(torch.int32).contiguous(), s1.to(torch.int32).contiguous(), weight.float().contiguous(), mask.float().contiguous()
+        _lib.check(fn(s0_.data_ptr(), s1_.data_ptr(), w_.data_ptr(), m_.data_ptr(), n, T, B, best.data_ptr(), out_max.data_ptr(), out_arg.data_ptr(), _lib.stream_ptr()),
                    "max_argmax_sparse")
         _lib.count_launch(2)
         return out_max, out_arg
@@ -174,8 +177,9 @@ def sparse_ce_softmax_and_grad(z: torch.Tensor, z_mask: torch.Tensor, y_t: torch
         grad = torch.empty(T, B, D, dtype=torch.float32, device=dev)
         lse = torch.empty(T, B, dtype=torch.float32, device=dev)
         fn = _lib.bind("rb200_sparse_ce_softmax_grad", [_vp] * 6 + [_i32] * 4 + [_vp] * 4)
-        _lib.check(fn(z.contiguous().data_ptr(), z_mask.float().contiguous().data_ptr(), y_t.to(torch.int32).contiguous().data_ptr(),
-                      y_i.to(torch.int32).contiguous().data_ptr(), y_w.float().contiguous().data_ptr(), y_mask.float().contiguous().data_ptr(), n, T, B, D,
+        z_, zm_, yt_, yi_ = z.contiguous(), z_mask.float().contiguous(), y_t.to(torch.int32).contiguous(), y_i.to(torch.int32).contiguous()
+        yw_, ym_ = y_w.float().contiguous(), y_mask.float().contiguous()
+        _lib.check(fn(z_.data_ptr(), zm_.data_ptr(), yt_.data_ptr(), yi_.data_ptr(), yw_.data_ptr(), ym_.data_ptr(), n, T, B, D,
                       lse.data_ptr(), ce.data_ptr(), grad.data_ptr(), _lib.stream_ptr()), "sparse_ce_softmax_grad")
         _lib.count_launch(2)
         return ce, grad
