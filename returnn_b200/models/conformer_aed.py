@@ -146,6 +146,19 @@ def recognize(model: ConformerAedModel, enc: Tensor, enc_spatial: Dim):
     beam_batch.dyn_size_ext = Tensor("bb", dims=[], dtype="int32", raw_tensor=torch.tensor(B * beam, dtype=torch.int32))
     enc_bt = enc.copy_transpose([batch_dim, enc_spatial, enc.feature_dim])
     enc_raw = enc_bt.raw_tensor.repeat_interleave(beam, dim=0)
+    max_len = torch.clamp((enc_spatial.dyn_size_ext.raw_tensor.float() * model.max_len_factor).ceil().to(torch.int64), min=1)
+    if getattr(model, "static_decode", True) and not torch.is_grad_enabled():
+        # one CUDA-graph replay per label over static caches (models/decode_graph.py); decoders it does not cover use the loop below
+        from .decode_graph import StaticTransformerDecoderStep, beam_search_static
+
+        try:
+            stepper = StaticTransformerDecoderStep(dec, enc=enc_bt.raw_tensor, enc_lens=enc_spatial.dyn_size_ext.raw_tensor,
+                                                   num_hyps=B * beam, max_steps=int(max_len.max()),
+                                                   dtype=torch.bfloat16 if (dev.type == "cuda" and torch.is_autocast_enabled()) else None)
+        except TypeError:
+            stepper = None
+        if stepper is not None:
+            return beam_search_static(stepper, batch=B, beam=beam, bos=model.bos, eos=model.eos, max_len=max_len)
     spatial_b = Dim(None, name="enc-time-beam")
     spatial_b.dyn_size_ext = Tensor("l", dims=[beam_batch], dtype="int32", raw_tensor=enc_spatial.dyn_size_ext.raw_tensor.repeat_interleave(beam))
     enc_b = Tensor("enc", dims=[beam_batch, spatial_b, enc.feature_dim], dtype=enc.dtype, raw_tensor=enc_raw, feature_dim=enc.feature_dim)
@@ -168,6 +181,5 @@ def recognize(model: ConformerAedModel, enc: Tensor, enc_spatial: Dim):
 
         return _nested.tree_map(g, st)
 
-    max_len = torch.clamp((enc_spatial.dyn_size_ext.raw_tensor.float() * model.max_len_factor).ceil().to(torch.int64), min=1)
     return beam_search_raw(step_fn, state, reorder, batch=B, beam=beam, vocab=model.vocab_dim.dimension, bos=model.bos, eos=model.eos,
                            max_len=max_len, device=dev)

@@ -48,6 +48,7 @@ def main():
     ap.add_argument("--rows", type=int, default=6656)
     ap.add_argument("--iters", type=int, default=30)
     ap.add_argument("--only", default=None)
+    ap.add_argument("--variant", default="", help="op-specific switches, comma separated (decode_step: bf16, static_only)")
     args = ap.parse_args()
     dev = torch.device("cuda")
     n, D, F = args.rows, 512, 2048
@@ -227,6 +228,69 @@ def main():
         step = lambda: optim_native.adamw_arena(p_, g_, m_, v_, flags, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, bc1=0.1, bc2=0.001, decoupled=True,
                                                 clip=5.0, norm=norm, p_bf16=p16)
         report("adamw (82.4 M parameters, clip factor on the fly, bf16 copy)", _time(step, args.iters), None, n_par * 30, 0)
+    if want("decode_step"):
+        # one label of beam search with a 6 x 512 Transformer decoder (8 heads, ff 2048, vocabulary 10k), 32 sequences x beam 12:
+        # the RF step interface driven from Python against one CUDA-graph replay per label over static caches
+        import time
+        from returnn_b200.tensor import Tensor, Dim
+        from returnn_b200 import frontend as rf
+        from returnn_b200.frontend.decoder.transformer import TransformerDecoder
+        from returnn_b200.frontend import nested
+        from returnn_b200.models.beam_search import beam_search_raw
+        from returnn_b200.models.decode_graph import StaticTransformerDecoderStep, beam_search_static
+
+        Bq, beam, t_enc, n_lab = 32, 12, 160, 40
+        enc_dim, vocab, model = Dim(512, name="enc"), Dim(10000, name="vocab"), Dim(512, name="model")
+        dec = TransformerDecoder(enc_dim, vocab, model, num_layers=6, num_heads=8, ff_dim=Dim(2048, name="ff"), dropout=0.0, att_dropout=0.0)
+        for p_ in dec.parameters():
+            p_.raw_tensor.data = p_.raw_tensor.data.to(dev)
+        rf.init_train_step_run_ctx(train_flag=False, step=0, epoch=1)
+        enc_raw = torch.randn(Bq * beam, t_enc, 512, device=dev)
+        enc_lens = torch.full((Bq * beam,), t_enc, dtype=torch.int32)
+        max_len = torch.full((Bq,), n_lab, dtype=torch.int64)
+        bb = Dim(None, name="bb")
+        bb.dyn_size_ext = Tensor("bb", dims=[], dtype="int32", raw_tensor=torch.tensor(Bq * beam, dtype=torch.int32))
+        sp = Dim(None, name="enc-time")
+        sp.dyn_size_ext = Tensor("l", dims=[bb], dtype="int32", raw_tensor=enc_lens)
+
+        def rf_search():
+            enc_state = dec.transform_encoder(Tensor("enc", dims=[bb, sp, enc_dim], dtype="float32", raw_tensor=enc_raw), axis=sp)
+
+            def step_fn(prev, st):
+                lab = Tensor("prev", dims=[bb], dtype="int64", sparse_dim=vocab, raw_tensor=prev)
+                logits, st = dec(lab, spatial_dim=rf.single_step_dim, encoder=enc_state, state=st)
+                return logits.copy_transpose([bb, vocab]).raw_tensor, st
+
+            def reorder(st, flat):
+                return nested.tree_map(lambda t: rf._utils.wrap(t.raw_tensor.index_select(list(t.dims).index(bb), flat), t.dims, like=t)
+                                       if isinstance(t, Tensor) and t.raw_tensor is not None and bb in t.dims else t, st)
+
+            # eos = a label the random model practically never prefers, so that all n_lab labels are decoded
+            return beam_search_raw(step_fn, dec.default_initial_state(batch_dims=[bb]), reorder, batch=Bq, beam=beam, vocab=10000, bos=1, eos=0,
+                                   max_len=max_len, device=dev)
+
+        variants = set(v for v in args.variant.split(",") if v)
+        with torch.no_grad(), torch.autocast("cuda", dtype=bf, enabled="bf16" in variants):
+            stepper = StaticTransformerDecoderStep(dec, enc=enc_raw[::beam].contiguous(), enc_lens=enc_lens[::beam].contiguous(), num_hyps=Bq * beam, max_steps=n_lab,
+                                                   dtype=bf if "bf16" in variants else None)
+            res = {}
+            forms = (("rf_loop", rf_search), ("static_graph", lambda: beam_search_static(stepper, batch=Bq, beam=beam, bos=1, eos=0, max_len=max_len)))
+            if "static_only" in variants:
+                forms = forms[1:]
+                res["rf_loop"] = (0.0, 1)
+            for name, fn_ in forms:
+                fn_()
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                out_ = fn_()
+                torch.cuda.synchronize()
+                res[name] = ((time.perf_counter() - t0) * 1e3, int(out_[1].max()))
+        r = {"op": "beam search label step (6x512 decoder, 32 x 12 hypotheses, vocab 10k)",
+             "rf_loop_ms_per_label": round(res["rf_loop"][0] / max(res["rf_loop"][1], 1), 3), "rf_loop_labels": res["rf_loop"][1],
+             "static_graph_ms_per_label": round(res["static_graph"][0] / max(res["static_graph"][1], 1), 3), "static_graph_labels": res["static_graph"][1],
+             "dtype": "bf16" if "bf16" in variants else "fp32",
+             "note": "wall clock of the second search (the static form replays the graph captured by the first) / labels decoded"}
+        print(json.dumps(r), flush=True)
     if want("lstm"):
         from returnn_b200.ops import lstm_native
 
