@@ -178,7 +178,10 @@ def pos_projection(enc, max_len: int, device, dtype, W) -> Optional[torch.Tensor
     """
     D = enc.out_dim.dimension
     idx = torch.arange(-(max_len - 1), max_len, device=device, dtype=torch.float32)
-    div = torch.exp(torch.arange(D // 2, device=device, dtype=torch.float32) * -(2.0 * math.log(1e4) / D))
+    # the frequency spacing of rf.sinusoidal_encoding (base ** (-i / (D/2 - 1)), as in returnn/frontend/attention.py): checkpoints and
+    # outputs then agree with the RF module, which tests/test_native_encoder_gpu.py checks against an fp32 run of that module
+    half = D // 2
+    div = torch.exp(torch.arange(half, device=device, dtype=torch.float32) * -(math.log(1e4) / max(half - 1, 1)))
     arg = idx[:, None] * div[None, :]
     return torch.cat([torch.sin(arg), torch.sin(arg + math.pi / 2.0)], dim=-1).to(dtype)
 

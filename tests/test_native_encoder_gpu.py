@@ -113,3 +113,62 @@ def test_native_encoder_stays_inside_its_workspace():
         g.check()
         gemm.check_status()
         assert g.num_guarded() > 0 and bool(torch.isfinite(out).all()) and bool(torch.isfinite(grads).all())
+
+
+@gpu
+def test_native_encoder_against_fp32_rf_oracle():
+    """
+    The native executor (bf16, own kernels, packed rows) against an independent oracle: the SAME module called through the ordinary
+    RF path (``ConformerEncoder.__call__`` on padded tensors) on the CPU in fp32, where no kernel of this repository runs.
+    Outputs and every parameter gradient, relative to their scale, at bf16 tolerances.
+    """
+    import copy
+    import returnn_b200.frontend as rf
+    from returnn_b200.tensor import Tensor, Dim, batch_dim
+    from returnn_b200.models import conformer_fused, conformer_native
+
+    model, pt, arena = _make()
+    torch.manual_seed(2)
+    lens = torch.tensor([600, 431, 577, 90], dtype=torch.int32)
+    feats = torch.randn(4, 600, 80, device="cuda")
+    for b, n in enumerate(lens.tolist()):
+        feats[b, n:] = 0
+    wgt = torch.randn(600, 128, device="cuda")
+    out_native, _, grads_native = _run(model, arena, feats, lens, wgt, native=True)
+    # the oracle: a CPU fp32 copy of the module tree, RF call on padded [B, T, F]
+    state = {k: v.detach().float().cpu().clone() for k, v in pt.state_dict().items()}
+    cpu_model = copy.deepcopy(model)
+    from returnn_b200.torch.frontend.bridge import rf_module_to_pt_module
+
+    cpu_pt = rf_module_to_pt_module(cpu_model).to("cpu").float()
+    cpu_pt.load_state_dict(state)
+    rf.init_train_step_run_ctx(train_flag=True, step=0, epoch=1)
+    batch_dim.dyn_size_ext = Tensor("batch_size", dims=[], dtype="int32", raw_tensor=torch.tensor(4, dtype=torch.int32))
+    time = Dim(None, name="time")
+    time.dyn_size_ext = Tensor("lens", dims=[batch_dim], dtype="int32", raw_tensor=lens.clone())
+    enc = cpu_model.encoder
+    x = Tensor("x", dims=[batch_dim, time, enc.in_dim], dtype="float32", raw_tensor=feats.cpu())
+    y, out_time = enc(x, in_spatial_dim=time)
+    y_raw = y.copy_transpose([batch_dim, out_time, enc.out_dim]).raw_tensor
+    out_lens = out_time.dyn_size_ext.raw_tensor.tolist()
+    rows = torch.cat([y_raw[b, : int(n)] for b, n in enumerate(out_lens)])  # the packed order of the executor's output
+    assert rows.shape == out_native.shape
+    (rows * wgt.cpu()[: rows.shape[0]]).sum().backward()
+    scale = float(rows.detach().abs().max())
+    err = float((out_native.cpu() - rows.detach()).abs().max()) / scale
+    assert err < 0.05, "outputs: rel. max err %.4f" % err
+    cpu_grads = {n: p.grad for n, p in cpu_pt.named_parameters()}
+    bad = []
+    for s in arena.slots:
+        if s.name.endswith("depthwise_conv.bias"):
+            continue  # in front of BatchNorm: exactly zero gradient, only rounding noise on both sides
+        g_ref = cpu_grads.get(s.name)
+        if g_ref is None:
+            continue
+        a = grads_native[s.offset: s.offset + s.numel].cpu()
+        b_ = g_ref.reshape(-1)
+        sc = float(b_.abs().max()) + 1e-6
+        e = float((a - b_).abs().max()) / sc
+        if e >= 0.1:
+            bad.append("%s: rel. max err %.4f (scale %.3g)" % (s.name, e, sc))
+    assert not bad, "parameter gradients differ from the fp32 oracle:\n" + "\n".join(bad)
