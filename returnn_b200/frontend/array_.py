@@ -406,13 +406,13 @@ def cum_concat_step(source: Tensor, *, prev_accum: Tensor, axis: Dim, out_spatia
 
 
 def stack(sources: Sequence[Tensor], *, out_dim: Optional[Dim] = None) -> Tuple[Tensor, Dim]:
-    """stack along a new last axis"""
+    """stack along a new first axis (the dim order of the reference: returnn/torch/frontend/_backend.py:592)"""
     if out_dim is None:
         out_dim = Dim(len(sources), name="stack")
     dims = sources[0]._dims
     raws = [s.copy_compatible_to_dims_raw(dims) for s in sources]
-    raw = torch.stack(raws, dim=-1)
-    return wrap(raw, list(dims) + [out_dim], like=sources[0]), out_dim
+    raw = torch.stack(raws, dim=0)
+    return wrap(raw, [out_dim] + list(dims), like=sources[0]), out_dim
 
 
 def sequence_mask(dims: Union[Dim, Sequence[Dim]], *, device: Optional[str] = None) -> Tensor:

@@ -76,6 +76,50 @@ FUNCS = {
     "top_k_values": lambda api, d: (api.rf.top_k(d["x"], axis=d["f"], k_dim=api.Dim(2, name="k"))[0], None, True),
     "sort_values": lambda api, d: (api.rf.sort(d["x"], axis=d["f"])[0], None, True),
     "expand_dim_and_sum": lambda api, d: (api.rf.reduce_sum(api.rf.expand_dim(d["z"], d["t"]), axis=d["f2"]), [api.batch_dim, d["t"]], True),
+    # -- second batch -------------------------------------------------------------------------------------------------------------
+    "tanh_sigmoid": lambda api, d: (api.rf.tanh(d["x"]) * api.rf.sigmoid(d["y"]), [api.batch_dim, d["t"], d["f"]], True),
+    "exp_log_abs": lambda api, d: (api.rf.log(api.rf.abs(d["x"]) + 1.0) + api.rf.exp(-api.rf.abs(d["y"])), [api.batch_dim, d["t"], d["f"]], True),
+    "sqrt_square": lambda api, d: (api.rf.sqrt(api.rf.square(d["x"]) + 1e-3), [api.batch_dim, d["t"], d["f"]], True),
+    "minimum_tensor": lambda api, d: (api.rf.minimum(d["x"], d["y"]), [api.batch_dim, d["t"], d["f"]], True),
+    "relu_elu_silu": lambda api, d: (api.rf.relu(d["x"]) + api.rf.elu(d["y"]) + api.rf.silu(d["x"]), [api.batch_dim, d["t"], d["f"]], True),
+    "reduce_min_feat": lambda api, d: (api.rf.reduce_min(d["x"], axis=d["f"]), [api.batch_dim, d["t"]], True),
+    "reduce_argmin_feat": lambda api, d: (api.rf.reduce_argmin(d["x"], axis=d["f"]), [api.batch_dim, d["t"]], True),
+    "reduce_sum_two_axes": lambda api, d: (api.rf.reduce_sum(d["x"], axis=[d["t"], d["f"]]), [api.batch_dim], False),
+    "reduce_mean_batch_time": lambda api, d: (api.rf.reduce_mean(d["x"], axis=[api.batch_dim, d["t"]]), [d["f"]], False),
+    "reduce_max_time_masked": lambda api, d: (api.rf.reduce_max(d["x"], axis=d["t"], use_mask=True), [api.batch_dim, d["f"]], False),
+    "reduce_logsumexp_time": lambda api, d: (api.rf.reduce_logsumexp(d["x"], axis=d["t"]), [api.batch_dim, d["f"]], False),
+    "reduce_any_all": lambda api, d: (api.rf.cast(api.rf.reduce_any(d["x"] > 1.0, axis=d["f"]), "float32") + 2.0 * api.rf.cast(
+        api.rf.reduce_all(d["x"] > -2.0, axis=d["f"]), "float32"), [api.batch_dim, d["t"]], True),
+    "logical_ops": lambda api, d: (api.rf.cast(api.rf.logical_and(d["x"] > 0.0, api.rf.logical_not(d["y"] > 0.0)), "float32"),
+                                   [api.batch_dim, d["t"], d["f"]], True),
+    "compare_eq_idx": lambda api, d: (api.rf.cast(api.rf.compare(d["idx"], "==", 3), "float32"), [api.batch_dim, d["t"]], True),
+    "where_scalar": lambda api, d: (api.rf.where(d["x"] > 0.0, d["x"], 0.5), [api.batch_dim, d["t"], d["f"]], True),
+    "concat_feat": lambda api, d: (api.rf.concat((d["x"], d["f"]), (d["y"], d["f"]))[0], None, True),
+    "split_feat": lambda api, d: (api.rf.split(d["x"], axis=d["f"], out_dims=[api.Dim(2, name="a"), api.Dim(4, name="b")])[1], None, True),
+    "stack_two": lambda api, d: (lambda r: (r[0], list(r[0].dims), False))(api.rf.stack([d["x"], d["y"]], out_dim=api.Dim(2, name="stack"))),
+    "merge_split_dims": lambda api, d: (api.rf.split_dims(d["x"], axis=d["f"], dims=[api.Dim(2, name="a"), api.Dim(3, name="b")]), None, True),
+    "pad_feat": lambda api, d: (api.rf.pad(d["x"], axes=[d["f"]], padding=[(1, 2)], value=0.5)[0], None, True),
+    "slice_feat": lambda api, d: (api.rf.slice(d["x"], axis=d["f"], start=1, end=5)[0], None, True),
+    "shift_right_idx": lambda api, d: (api.rf.shift_right(d["idx"], axis=d["t"], pad_value=0), [api.batch_dim, d["t"]], True),
+    "cumsum_feat": lambda api, d: (api.rf.cumsum(d["x"], spatial_dim=d["f"]), [api.batch_dim, d["t"], d["f"]], True),
+    "gather_time_first": lambda api, d: (api.rf.gather(d["x"], indices=0, axis=d["t"]), [api.batch_dim, d["f"]], False),
+    "masked_fill_via_where": lambda api, d: (api.rf.where(api.rf.sequence_mask([api.batch_dim, d["t"]]), d["x"], -1.0), [api.batch_dim, d["t"], d["f"]], False),
+    "num_elements_mean": lambda api, d: (api.rf.reduce_sum(d["x"], axis=[api.batch_dim, d["t"]]) / float(sum(LENS)), [d["f"]], False),
+    "relative_positional_encoding": lambda api, d: (lambda r: (r[0], [r[1], d["f"]], False))(api.rf.relative_positional_encoding(
+        query_spatial_dim=d["t"], key_value_spatial_dim=d["t"], feat_dim=d["f"])),
+    "one_hot_times_x": lambda api, d: (api.rf.reduce_sum(api.rf.one_hot(d["idx"]) * d["x"], axis=d["f"]), [api.batch_dim, d["t"]], True),
+    "matmul_outer": lambda api, d: (api.rf.matmul(d["x"], d["z"], reduce=[]), None, True),
+    "ctc_greedy_like_argmax_shift": lambda api, d: (api.rf.cast(api.rf.reduce_argmax(d["x"], axis=d["f"]) != api.rf.shift_right(
+        api.rf.reduce_argmax(d["x"], axis=d["f"]), axis=d["t"], pad_value=-1), "float32"), [api.batch_dim, d["t"]], True),
+    "power_and_div": lambda api, d: ((api.rf.abs(d["x"]) + 1.0) ** 1.5 / (api.rf.abs(d["y"]) + 2.0), [api.batch_dim, d["t"], d["f"]], True),
+    "floor_ceil_round": lambda api, d: (api.rf.floor(d["x"]) + 2.0 * api.rf.ceil(d["y"]) + 4.0 * api.rf.round(d["x"] * 3.0), [api.batch_dim, d["t"], d["f"]], True),
+    "clip_by_value_int": lambda api, d: (api.rf.clip_by_value(d["idx"], 1, 4), [api.batch_dim, d["t"]], True),
+    "log_softmax_two_step": lambda api, d: (d["x"] - api.rf.reduce_logsumexp(d["x"], axis=d["f"]), [api.batch_dim, d["t"], d["f"]], True),
+    "cosine_similarity_func": lambda api, d: (api.rf.matmul(d["x"], d["y"], reduce=d["f"]) * api.rf.rsqrt(
+        api.rf.reduce_sum(api.rf.square(d["x"]), axis=d["f"]) * api.rf.reduce_sum(api.rf.square(d["y"]), axis=d["f"]) + 1e-6), [api.batch_dim, d["t"]], True),
+    "kl_div_probs": lambda api, d: (api.rf.reduce_sum(api.rf.softmax(d["x"], axis=d["f"]) * (api.rf.log_softmax(d["x"], axis=d["f"])
+                                                                                              - api.rf.log_softmax(d["y"], axis=d["f"])), axis=d["f"]),
+                                    [api.batch_dim, d["t"]], True),
 }
 
 
