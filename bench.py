@@ -218,7 +218,7 @@ def run_ours(args):
         return conformer_ctc.train_step(model=model, extern_data=extern_data, **kwargs)
 
     cfg = Config({
-        "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": extern_data, "model_opts": dict(MODEL_OPTS),
+        "task": "train", "backend": "torch", "behavior_version": 24, "extern_data": extern_data, "model_opts": dict(MODEL_OPTS),
         "get_model": conformer_ctc.get_model, "train_step": train_step,
         "batch_size": BATCH_FRAMES, "max_seqs": 200, "optimizer": {"class": "adamw", "weight_decay": 0.01, "eps": 1e-8},
         "learning_rate": 1e-4, "gradient_clip_global_norm": 5.0, "torch_amp": "bfloat16", "num_epochs": 1,
@@ -227,7 +227,7 @@ def run_ours(args):
     if world > 1:
         cfg.set("torch_distributed", {"reduce_type": "grad"})
     set_global_config(cfg)
-    BehaviorVersion._reset(21)
+    BehaviorVersion._reset(24)
     log.init_by_config(cfg)
     # the dataset of the Engine.train() measurement: the sequences of all batches in order; the engine's greedy batching under the same
     # budget re-creates exactly these batches (the reference arm feeds its engine the same way)
@@ -454,7 +454,7 @@ import bench as _bench_mod
 
 backend = "torch"
 task = "train"
-behavior_version = 21
+behavior_version = 24
 _rank = int(os.environ.get("RANK", "0"))
 _world = int(os.environ.get("WORLD_SIZE", "1"))
 _W, _K = _bench["warmup"], _bench["steps"]
@@ -493,6 +493,7 @@ class Model(rf.Module):
         self.encoder = ConformerEncoder(
             feat_dim, self.model_dim, num_layers=o["num_layers"], num_heads=o["num_heads"], ff_dim=Dim(o["ff_dim"], name="enc-ff"),
             conv_kernel_size=o["conv_kernel_size"], dropout=o["dropout"], att_dropout=o["att_dropout"],
+            conv_norm=rf.build_dict(rf.BatchNorm, use_mask=True),
             input_layer=ConformerConvSubsample(feat_dim, out_dims=[Dim(c1, name="conv1"), Dim(c2, name="conv2"), Dim(c3, name="conv3")],
                                                filter_sizes=[(3, 3), (3, 3), (3, 3)], pool_sizes=[(1, 2)], strides=[(1, 1), (3, 1), (2, 1)]))
         self.wb_vocab_dim = vocab_dim + 1

@@ -159,14 +159,14 @@ def run_gpu(args):
     batches = spec["batches"](4321 + rank, n_pool)
     mod = spec["mod"]
     cfg = Config(dict({
-        "task": "train", "backend": "torch", "behavior_version": 21, "extern_data": mod.make_extern_data(spec["model_opts"]),
+        "task": "train", "backend": "torch", "behavior_version": 24, "extern_data": mod.make_extern_data(spec["model_opts"]),
         "model_opts": dict(spec["model_opts"]), "get_model": mod.get_model, "train_step": mod.train_step, "batch_size": spec["budget"],
         "max_seqs": 2000, "learning_rate": 1e-4, "torch_amp": "bfloat16", "num_epochs": 1, "log_verbosity": 2 if rank == 0 else 1,
         "device": "cuda", "forward_step": getattr(mod, "forward_step", None)}, **spec["extra"]))
     if world > 1:
         cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else {"reduce_type": "grad"})
     set_global_config(cfg)
-    BehaviorVersion._reset(21)
+    BehaviorVersion._reset(24)
     log.init_by_config(cfg)
     train_data = StaticDataset(data=[s for b in batches[:2] for s in b], output_dim=spec["output_dim"])
     train_data.initialize()
@@ -432,7 +432,7 @@ import bench_configs as _bc
 
 backend = "torch"
 task = "train"
-behavior_version = 21
+behavior_version = 24
 _W, _K = _opts["warmup"], _opts["steps"]
 _rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 _batches = _bc._mt_batches(4321 + _rank, _W + _K + 1, 25000)
@@ -506,7 +506,7 @@ import bench_configs as _bc
 
 backend = "torch"
 task = "train"
-behavior_version = 21
+behavior_version = 24
 _W, _K = _opts["warmup"], _opts["steps"]
 _rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 _batches = _bc._asr_batches(4321 + _rank, _W + _K + 1, 40000, 300, 2000, 1.0 / 30.0)
@@ -541,6 +541,7 @@ class Model(rf.Module):
         self.model_dim = Dim(512, name="enc-model")
         self.encoder = ConformerEncoder(
             feat_dim, self.model_dim, num_layers=12, num_heads=8, ff_dim=Dim(2048, name="enc-ff"), conv_kernel_size=32, dropout=0.1, att_dropout=0.1,
+            conv_norm=rf.build_dict(rf.BatchNorm, use_mask=True),
             input_layer=ConformerConvSubsample(feat_dim, out_dims=[Dim(32, name="conv1"), Dim(64, name="conv2"), Dim(64, name="conv3")],
                                                filter_sizes=[(3, 3), (3, 3), (3, 3)], pool_sizes=[(1, 2)], strides=[(1, 1), (3, 1), (2, 1)]))
         self.decoder = TransformerDecoder(encoder_dim=self.model_dim, vocab_dim=vocab_dim, model_dim=Dim(512, name="dec-model"), num_layers=6,
@@ -587,7 +588,7 @@ import bench_configs as _bc
 
 backend = "torch"
 task = "train"
-behavior_version = 21
+behavior_version = 24
 _W, _K = _opts["warmup"], _opts["steps"]
 _rank, _world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
 _batches = _bc._asr_batches(4321 + _rank, _W + _K + 1, 20000, 500, 1600, (0.1, 0.25))

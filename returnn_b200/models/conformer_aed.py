@@ -40,6 +40,7 @@ class ConformerAedModel(rf.Module):
         self.encoder = ConformerEncoder(
             in_dim, self.model_dim, num_layers=num_layers, num_heads=num_heads, ff_dim=Dim(ff_dim, name="enc-ff"), conv_kernel_size=conv_kernel_size,
             dropout=dropout, att_dropout=att_dropout,
+            conv_norm=rf.build_dict(rf.BatchNorm, use_mask=True),  # statistics over valid frames: the same model on padded and on packed batches
             input_layer=ConformerConvSubsample(in_dim, out_dims=[Dim(c1, name="conv1"), Dim(c2, name="conv2"), Dim(c3, name="conv3")],
                                                filter_sizes=[(3, 3), (3, 3), (3, 3)], pool_sizes=[(1, 2)], strides=[(1, 1), (3, 1), (2, 1)]))
         self.decoder = TransformerDecoder(encoder_dim=self.model_dim, vocab_dim=vocab_dim, model_dim=Dim(model_dim, name="dec-model"),

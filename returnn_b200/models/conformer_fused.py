@@ -178,10 +178,10 @@ def pos_projection(enc, max_len: int, device, dtype, W) -> Optional[torch.Tensor
     """
     D = enc.out_dim.dimension
     idx = torch.arange(-(max_len - 1), max_len, device=device, dtype=torch.float32)
-    # the frequency spacing of rf.sinusoidal_encoding (base ** (-i / (D/2 - 1)), as in returnn/frontend/attention.py): checkpoints and
-    # outputs then agree with the RF module, which tests/test_native_encoder_gpu.py checks against an fp32 run of that module
-    half = D // 2
-    div = torch.exp(torch.arange(half, device=device, dtype=torch.float32) * -(math.log(1e4) / max(half - 1, 1)))
+    # the frequency spacing of rf.relative_positional_encoding, 1e4 ** (-2i / D) (returnn/frontend/attention.py:1189; the absolute
+    # sinusoidal encoding spaces its frequencies differently); tests/test_native_encoder_gpu.py checks the whole encoder against an
+    # fp32 run of the RF module
+    div = torch.exp(torch.arange(D // 2, device=device, dtype=torch.float32) * -(2.0 * math.log(1e4) / D))
     arg = idx[:, None] * div[None, :]
     return torch.cat([torch.sin(arg), torch.sin(arg + math.pi / 2.0)], dim=-1).to(dtype)
 
@@ -212,6 +212,12 @@ def supports_fused(enc) -> bool:
 
     if not isinstance(enc.input_layer, ConformerConvSubsample) or enc.pos_enc is not None or enc.input_projection is None:
         return False
+    # this path works on valid frames only: it computes what the RF modules compute when convolutions mask their padded input
+    # (default from behavior version 23) and the BatchNorm statistics leave the padded frames out (use_mask)
+    from ..frontend.dims import use_mask_default
+
+    if not use_mask_default(default=True, default_false_for_behavior_version_up_to=22):
+        return False
     if enc.input_layer.activation is not _m.relu:
         return False
     for layer in enc.layers:
@@ -223,6 +229,14 @@ def supports_fused(enc) -> bool:
         if sa.pos_emb_dropout or sa.att_dropout_broadcast:
             return False
         if not isinstance(layer.conv_block.norm, BatchNorm) or not isinstance(layer.ffn1_layer_norm, LayerNorm):
+            return False
+        bn_mask = layer.conv_block.norm.use_mask
+        if bn_mask is None:  # BatchNorm's own default: config rf_batch_norm_use_mask, else unmasked
+            from ..config import get_global_config
+
+            cfg = get_global_config(raise_exception=False)
+            bn_mask = cfg.bool("rf_batch_norm_use_mask", False) if cfg else False
+        if not bn_mask:
             return False
         if not isinstance(layer.ffn1, ConformerPositionwiseFeedForward) or layer.ffn1.activation is not _m.swish:
             return False

@@ -153,12 +153,12 @@ def _deferred_losses_case(device):
     seqs = [{"data": rng.randn(7, 5).astype("float32"), "classes": rng.randint(0, 3, (7,)).astype("int32")} for _ in range(4)]
 
     def make_engine():
-        cfg = Config({"task": "train", "backend": "torch", "behavior_version": 21, "device": device, "get_model": get_model, "train_step": train_step,
+        cfg = Config({"task": "train", "backend": "torch", "behavior_version": 24, "device": device, "get_model": get_model, "train_step": train_step,
                       "extern_data": {"data": {"dims": (batch_dim, time_dim, in_dim), "dtype": "float32"},
                                       "classes": {"dims": (batch_dim, time_dim), "sparse_dim": out_dim, "dtype": "int32"}},
                       "batch_size": 100, "learning_rate": 0.1, "optimizer": {"class": "sgd"}, "num_epochs": 1, "log_verbosity": 1, "random_seed": 3})
         set_global_config(cfg)
-        BehaviorVersion._reset(21)
+        BehaviorVersion._reset(24)
         data = StaticDataset(data=seqs, output_dim={"data": (5, 2), "classes": (3, 1)})
         data.initialize()
         eng = Engine(cfg)

@@ -16,7 +16,7 @@ def test_frontend_native_matches_torch_path(lens):
     from returnn_b200.models.packing import PackInfo
     from returnn_b200.utils.basic import BehaviorVersion
 
-    BehaviorVersion._reset(21)
+    BehaviorVersion._reset(24)
     torch.manual_seed(0)
     f = Dim(80, name="feat")
     enc = ConformerEncoder(f, Dim(64, name="model"), num_layers=1, num_heads=1, ff_dim=Dim(64, name="ff"), conv_kernel_size=3, dropout=0.0, att_dropout=0.0,

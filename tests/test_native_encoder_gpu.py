@@ -16,7 +16,7 @@ def _make(num_layers=2, model_dim=128, heads=2, ff=256, conv_k=7, dropout=0.0):
     from returnn_b200.parallel.arena import ParamArena
     from returnn_b200.utils.basic import BehaviorVersion
 
-    BehaviorVersion.set_min_behavior_version(21)
+    BehaviorVersion._reset(24)  # convolutions mask padded input: the semantics of the fused path
     torch.manual_seed(1)
     model = ConformerCtcModel(in_dim=Dim(80, name="feat"), vocab_dim=Dim(55, name="vocab"), num_layers=num_layers, model_dim=model_dim,
                               num_heads=heads, ff_dim=ff, conv_kernel_size=conv_k, dropout=dropout, att_dropout=dropout,
@@ -127,7 +127,11 @@ def test_native_encoder_against_fp32_rf_oracle():
     from returnn_b200.tensor import Tensor, Dim, batch_dim
     from returnn_b200.models import conformer_fused, conformer_native
 
+    from returnn_b200.utils.basic import BehaviorVersion
+
     model, pt, arena = _make()
+    BehaviorVersion._reset(24)  # convolutions mask their padded input (default from 23): what the executor computes on valid frames
+    model.encoder.input_dropout = 0.0  # the RF path draws its dropout from torch's generator, the executor from its counter-based one
     torch.manual_seed(2)
     lens = torch.tensor([600, 431, 577, 90], dtype=torch.int32)
     feats = torch.randn(4, 600, 80, device="cuda")
@@ -138,6 +142,7 @@ def test_native_encoder_against_fp32_rf_oracle():
     # the oracle: a CPU fp32 copy of the module tree, RF call on padded [B, T, F]
     state = {k: v.detach().float().cpu().clone() for k, v in pt.state_dict().items()}
     cpu_model = copy.deepcopy(model)
+    assert all(layer.conv_block.norm.use_mask for layer in cpu_model.encoder.layers)  # BatchNorm statistics over valid frames
     from returnn_b200.torch.frontend.bridge import rf_module_to_pt_module
 
     cpu_pt = rf_module_to_pt_module(cpu_model).to("cpu").float()
