@@ -38,6 +38,12 @@ def supports(in_feat: int, channels: Tuple[int, ...], filter_sizes, strides, poo
 
 
 def _same_pad_left(in_len: int, k: int, stride: int) -> int:
+    """left part of "same" padding, by the rule rf.conv follows at the current behavior version (from 24 on it no longer depends on
+    the padded length of the batch when the convolution has a stride)"""
+    from ..frontend.conv import _use_consistent_same_padding
+
+    if stride != 1 and _use_consistent_same_padding():
+        return (k - 1) // 2
     pad = max(k - 1 - (in_len - 1) % stride, 0)
     return pad // 2
 
