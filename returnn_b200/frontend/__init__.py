@@ -70,6 +70,9 @@ from . import control_flow as _control_flow
 from .control_flow import control_flow_ctx, get_current_control_flow_ctx
 from .backend_select import select_backend_torch, select_backend_returnn_layers_tf, is_executing_eagerly, get_backend_name
 
+from . import checkpoint  # noqa: E402,F401
+from ._random_journal import RandomJournal  # noqa: E402,F401
+
 set_random_seed(42)
 
 # native dimension bookkeeping when the extension is built (RETURNN_B200_RF_NATIVE=0 keeps the Python versions)

@@ -73,6 +73,17 @@ def random(*, dims: Sequence[Dim], dtype: Optional[str] = None, device: Optional
         device = get_default_device()
     shape = shape_of(dims)
     tdt = torch_dtype(dtype)
+    from . import _random_journal
+
+    journal, journal_mode = _random_journal.current_journal()
+    if journal_mode == "replay":  # the draw recorded by another run takes the place of this one
+        entry = journal.get_next(shape=shape, dtype=dtype, distribution=distribution)
+        raw = torch.from_numpy(entry.out).to(device=device, dtype=tdt)
+        res = wrap(raw, dims, sparse_dim=sparse_dim, feature_dim=feature_dim)
+        if out is not None:
+            out.raw_tensor = raw
+            return out
+        return res
     g = _gen(device, bool(static))
     if seed is not None:
         g = torch.Generator(device=torch.device(device or "cpu"))
@@ -100,6 +111,9 @@ def random(*, dims: Sequence[Dim], dtype: Optional[str] = None, device: Optional
         raise ValueError("random: invalid distribution %r" % distribution)
     if raw.dtype != tdt:
         raw = raw.to(tdt)
+    if journal_mode == "record":
+        journal.append(out=(raw.float() if raw.dtype == torch.bfloat16 else raw).detach().cpu().numpy(), dtype=dtype, distribution=distribution,
+                       mean=mean, stddev=stddev, bound=bound, minval=minval, maxval=maxval, seed=seed, static=static)
     res = wrap(raw, dims, sparse_dim=sparse_dim, feature_dim=feature_dim)
     if out is not None:
         out.raw_tensor = raw

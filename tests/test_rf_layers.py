@@ -3,6 +3,7 @@ RF layers and model zoo on CPU: shapes, gradients, and the padding-invariance pr
 (outputs of a sequence do not depend on how much padding the batch carries; reference: tests/rf_utils.py run_model).
 """
 
+import pytest
 import torch
 from returnn_b200.tensor import Tensor, Dim, batch_dim
 import returnn_b200.frontend as rf
@@ -145,3 +146,61 @@ def test_softmax_cross_entropy_smoothed_grad_equals_composition():
     torch.testing.assert_close(raw.grad, raw2.grad, atol=1e-6, rtol=1e-5)
     assert torch.equal(best.raw_tensor, rf.reduce_argmax(logits2, axis=vocab).copy_compatible_to_dims_raw(best.dims))
     assert best.sparse_dim == vocab
+
+
+def test_random_journal_and_npz_checkpoints(tmp_path):
+    """draws recorded in one run come back in another; parameters round-trip through .npz and from an engine-style .pt file"""
+    import numpy
+    import returnn_b200.frontend as rf
+    from returnn_b200.tensor import Dim
+
+    a, b = Dim(3, name="a"), Dim(5, name="b")
+    journal = rf.RandomJournal()
+    with journal.recording():
+        x1 = rf.random_normal([a, b])
+        u1 = rf.random_uniform([b], minval=-2.0, maxval=2.0)
+    assert len(journal) == 2
+    rf.set_random_seed(12345)  # another generator state: without the journal the draws would differ
+    with journal.replaying():
+        x2 = rf.random_normal([a, b])
+        u2 = rf.random_uniform([b], minval=-2.0, maxval=2.0)
+        assert journal.reached_end()
+        with pytest.raises(IndexError):
+            rf.random_normal([a])
+    assert torch.equal(x1.raw_tensor, x2.raw_tensor) and torch.equal(u1.raw_tensor, u2.raw_tensor)
+    with journal.replaying():
+        with pytest.raises(ValueError):
+            rf.random_normal([b, a])  # other shape than recorded
+    # dropout draws through rf.random: the same mask in two runs
+    rf.init_train_step_run_ctx(train_flag=True, step=0, epoch=1)
+    ones = rf.ones([a, b])
+    j2 = rf.RandomJournal()
+    with j2.recording():
+        d1 = rf.dropout(ones, 0.5, axis=b)
+    if len(j2):
+        with j2.replaying():
+            d2 = rf.dropout(ones, 0.5, axis=b)
+        assert torch.equal(d1.raw_tensor, d2.raw_tensor)
+    # checkpoints
+    lin = rf.Linear(a, b)
+    params = rf.checkpoint.get_model_params(lin)
+    fn = str(tmp_path / "ck.npz")
+    rf.checkpoint.save_params(params, fn, step=7, epoch=2)
+    back = rf.checkpoint.load_params(fn)
+    assert sorted(back) == ["bias", "weight"] and int(rf.checkpoint.load_params(fn, with_meta=True)["_step"]) == 7
+    lin2 = rf.Linear(a, b)
+    assert rf.checkpoint.set_model_params(lin2, back) == ["weight", "bias"] or set(rf.checkpoint.set_model_params(lin2, back)) == {"weight", "bias"}
+    assert torch.equal(lin2.weight.raw_tensor, lin.weight.raw_tensor)
+    with pytest.raises(ValueError):
+        rf.checkpoint.check_params_complete(lin2, {"weight": back["weight"]})
+    assert rf.checkpoint.check_params_complete(lin2, {"weight": back["weight"]}, allow_missing=True) == ["weight"]
+    with pytest.raises(ValueError):
+        rf.checkpoint.check_params_complete(lin2, dict(back, extra=numpy.zeros(1)))
+    with pytest.raises(ValueError):
+        rf.checkpoint.check_params_complete(lin2, dict(back, weight=numpy.zeros((5, 3), dtype="float32")))
+    from returnn_b200.torch.frontend.bridge import rf_module_to_pt_module
+
+    pt_fn = str(tmp_path / "model.pt")
+    torch.save({"model": rf_module_to_pt_module(lin).state_dict(), "epoch": 3, "step": 11}, pt_fn)
+    from_pt = rf.checkpoint.load_torch_checkpoint(pt_fn)
+    assert numpy.array_equal(from_pt["weight"], params["weight"]) and numpy.array_equal(from_pt["bias"], params["bias"])
