@@ -228,6 +228,35 @@ def main():
         step = lambda: optim_native.adamw_arena(p_, g_, m_, v_, flags, lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, wd=0.01, bc1=0.1, bc2=0.001, decoupled=True,
                                                 clip=5.0, norm=norm, p_bf16=p16)
         report("adamw (82.4 M parameters, clip factor on the fly, bf16 copy)", _time(step, args.iters), None, n_par * 30, 0)
+    if want("sdpa"):
+        # scaled dot-product attention of the Transformer models: 64 sequences x 256 positions, 8 heads x 64, bf16, causal and with key lengths
+        from returnn_b200.ops import sdpa as sdpa_op
+
+        Bs, Ts, Hs, Ds = 64, 256, 8, 64
+        q_ = (torch.randn(Bs, Ts, Hs * Ds, device=dev) * 0.5).to(bf).requires_grad_(True)
+        k_ = (torch.randn(Bs, Ts, Hs * Ds, device=dev) * 0.5).to(bf).requires_grad_(True)
+        v_ = (torch.randn(Bs, Ts, Hs * Ds, device=dev) * 0.5).to(bf).requires_grad_(True)
+        kl = torch.randint(Ts // 2, Ts + 1, (Bs,), dtype=torch.int32)
+        dy_ = torch.randn(Bs, Ts, Hs * Ds, device=dev).to(bf)
+        for name_, kw in (("sdpa (key lengths)", dict(k_lens=kl)), ("sdpa (causal)", dict(causal=True))):
+            fwd = lambda kw=kw: sdpa_op.sdpa(q_, k_, v_, num_heads=Hs, **kw)
+            def fb(fwd=fwd):
+                fwd().backward(dy_)
+            flops = 4.0 * Bs * Hs * Ts * Ts * Ds
+            report(name_ + " 64 x 256, 8 x 64", _time(fwd, args.iters), _time(fb, args.iters), 4 * Bs * Ts * Hs * Ds * 2, 9 * Bs * Ts * Hs * Ds * 2,
+                   {"fwd_gflop": round(flops / 1e9, 1)})
+    if want("rnnt"):
+        # RNN-T loss over the [T, U+1] lattice of every sequence: 32 sequences, T = 200 frames, U = 50 labels
+        Br, Tr, Ur = 32, 200, 50
+        lp_b = torch.log_softmax(torch.randn(Br, Tr, Ur + 1, 2, device=dev), -1)
+        lpb = lp_b[..., 0].contiguous().requires_grad_(True)
+        lpl = lp_b[..., 1].contiguous().requires_grad_(True)
+        t_l = torch.full((Br,), Tr, dtype=torch.int32)
+        u_l = torch.full((Br,), Ur, dtype=torch.int32)
+        fwd = lambda: seq_ops.rnnt_loss(lpb, lpl, t_l, u_l)
+        def fb():
+            fwd().sum().backward()
+        report("rnnt_loss (32 x 200 x 51 lattice)", _time(fwd, args.iters), _time(fb, args.iters), 2 * Br * Tr * (Ur + 1) * 4, 6 * Br * Tr * (Ur + 1) * 4)
     if want("decode_step"):
         # one label of beam search with a 6 x 512 Transformer decoder (8 heads, ff 2048, vocabulary 10k), 32 sequences x beam 12:
         # the RF step interface driven from Python against one CUDA-graph replay per label over static caches
