@@ -354,38 +354,62 @@ rnnt_kernel(const float* __restrict__ lp_blank, const float* __restrict__ lp_lab
     if (threadIdx.x == 0) loss[b] = 0.f;
     return;
   }
-  // forward
-  for (int d = 0; d < Tb + Ub - 1; ++d) {
-    for (int u = threadIdx.x; u < Ub; u += blockDim.x) {
-      const int t = d - u;
-      if (t < 0 || t >= Tb) continue;
-      float v;
-      if (t == 0 && u == 0) v = 0.f;
-      else {
-        const float from_t = t > 0 ? al[(size_t)(t - 1) * U1 + u] + pb[(size_t)(t - 1) * U1 + u] : -INFINITY;
-        const float from_u = u > 0 ? al[(size_t)t * U1 + u - 1] + pl[(size_t)t * U1 + u - 1] : -INFINITY;
-        v = log_add(from_t, from_u);
+  // The forward and the backward recursion are independent: they run at the same time in the two halves of the CTA, each half
+  // with its own named barrier. A lattice node needs its two predecessors, which both lie on the previous anti-diagonal: that
+  // diagonal is kept in shared memory (indexed by u), so the dependent chain of a step is shared memory -> log-add -> barrier and
+  // global memory is only written inside the loops (and read for the log-probabilities, which do not depend on the chain).
+  extern __shared__ float rsm[];  // [4][U1]: previous / current diagonal of alpha and of beta
+  const int half = blockDim.x >> 1;
+  const int dir = threadIdx.x >= half ? 1 : 0;
+  const int lt = threadIdx.x - dir * half;
+  float* prev = rsm + dir * 2 * U1;
+  float* cur = prev + U1;
+  for (int u = lt; u < U1; u += half) prev[u] = -INFINITY;
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + dir), "r"(half) : "memory");
+  if (dir == 0) {
+    for (int d = 0; d < Tb + Ub - 1; ++d) {
+      for (int u = lt; u < Ub; u += half) {
+        const int t = d - u;
+        float v = -INFINITY;
+        if (t >= 0 && t < Tb) {
+          if (t == 0 && u == 0) v = 0.f;
+          else {
+            const float from_t = t > 0 ? prev[u] + pb[(size_t)(t - 1) * U1 + u] : -INFINITY;
+            const float from_u = u > 0 ? prev[u - 1] + pl[(size_t)t * U1 + u - 1] : -INFINITY;
+            v = log_add(from_t, from_u);
+          }
+          al[(size_t)t * U1 + u] = v;
+        }
+        cur[u] = v;
       }
-      al[(size_t)t * U1 + u] = v;
+      asm volatile("bar.sync 1, %0;" ::"r"(half) : "memory");
+      float* tmp = prev;
+      prev = cur;
+      cur = tmp;
     }
-    __syncthreads();
-  }
-  // backward
-  for (int d = Tb + Ub - 2; d >= 0; --d) {
-    for (int u = threadIdx.x; u < Ub; u += blockDim.x) {
-      const int t = d - u;
-      if (t < 0 || t >= Tb) continue;
-      float v;
-      if (t == Tb - 1 && u == Ub - 1) v = pb[(size_t)t * U1 + u];
-      else {
-        const float to_t = t < Tb - 1 ? be[(size_t)(t + 1) * U1 + u] + pb[(size_t)t * U1 + u] : -INFINITY;
-        const float to_u = u < Ub - 1 ? be[(size_t)t * U1 + u + 1] + pl[(size_t)t * U1 + u] : -INFINITY;
-        v = log_add(to_t, to_u);
+  } else {
+    for (int d = Tb + Ub - 2; d >= 0; --d) {
+      for (int u = lt; u < Ub; u += half) {
+        const int t = d - u;
+        float v = -INFINITY;
+        if (t >= 0 && t < Tb) {
+          if (t == Tb - 1 && u == Ub - 1) v = pb[(size_t)t * U1 + u];
+          else {
+            const float to_t = t < Tb - 1 ? prev[u] + pb[(size_t)t * U1 + u] : -INFINITY;
+            const float to_u = u < Ub - 1 ? prev[u + 1] + pl[(size_t)t * U1 + u] : -INFINITY;
+            v = log_add(to_t, to_u);
+          }
+          be[(size_t)t * U1 + u] = v;
+        }
+        cur[u] = v;
       }
-      be[(size_t)t * U1 + u] = v;
+      asm volatile("bar.sync 2, %0;" ::"r"(half) : "memory");
+      float* tmp = prev;
+      prev = cur;
+      cur = tmp;
     }
-    __syncthreads();
   }
+  __syncthreads();  // both recursions are done and their global writes are visible to the whole CTA
   const float log_z = be[0];
   if (threadIdx.x == 0) loss[b] = -log_z;
   if (d_blank || d_label) {
@@ -458,6 +482,10 @@ RB_EXPORT int rb200_beam_topk(const void* logits, int is_bf16, int normalized, c
 RB_EXPORT int rb200_rnnt_loss(const float* lp_blank, const float* lp_label, const int* t_lens, const int* u_lens, int batch, int T, int U1, float* alpha,
                               float* beta, float* loss, float* d_blank, float* d_label, cudaStream_t stream) {
   if (batch <= 0) return RB_OK;
-  rnnt_kernel<<<batch, 256, 0, stream>>>(lp_blank, lp_label, t_lens, u_lens, T, U1, alpha, beta, loss, d_blank, d_label);
+  if ((size_t)4 * U1 * sizeof(float) > 48 * 1024) {
+    rb_set_error("rnnt_loss: %d label positions exceed the shared-memory diagonals (at most 3071)", U1);
+    return RB_ERR_UNSUPPORTED;
+  }
+  rnnt_kernel<<<batch, 256, (size_t)4 * U1 * sizeof(float), stream>>>(lp_blank, lp_label, t_lens, u_lens, T, U1, alpha, beta, loss, d_blank, d_label);
   return rb_check_launch("rnnt_loss");
 }

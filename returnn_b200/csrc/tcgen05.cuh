@@ -151,9 +151,18 @@ inline int make_map(CUtensorMap* map, const void* base, long long inner, long lo
   cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * (fp32 ? 4 : 2)};
   cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
   cuuint32_t elem[2] = {1, 1};
-  CUresult r = fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                  CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  auto encode = [&]() {
+    return fn(map, fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  };
+  CUresult r = encode();
+  if (r == CUDA_ERROR_INVALID_CONTEXT) {
+    // a thread that has made no runtime call yet (a worker thread of the autograd engine) has no current context for the driver
+    // API: cudaFree(0) binds the device's primary context to this thread
+    cudaFree(0);
+    r = encode();
+  }
   if (r != CUDA_SUCCESS) {
     rb_set_error("gemm: cuTensorMapEncodeTiled failed (%d): base %p inner %lld outer %lld pitch %lld", (int)r, base, inner, outer, pitch_elems);
     return RB_ERR_ARG;
