@@ -6,7 +6,9 @@
 // (O, dQ) or query positions (dK, dV) in blocks of 64, so the margins [Tk, Tkp) and [Tq, Tqp) are written as zeros here and
 // the buffers need no memset. A key j of batch entry b is visible to query i iff j < k_lens[b] (k_lens may be null: all Tk) and,
 // for causal attention, j <= i + causal_shift (causal_shift = Tk - Tq: the last query sees all keys; 0 for self attention).
-// One warp per query row; rows are walked in three passes (max, sum, write), the row stays in L1/L2.
+// One warp per query row. Scores (and, backward, the gradient w.r.t. the dropped probabilities) are bf16 as the GEMMs of an
+// autocast region write them: a row of up to 1024 keys is read ONCE with 16-byte loads and kept in registers for max, sum and
+// write (the *_vec kernels); longer rows and fp32 scores take the scalar three-pass kernels.
 //
 // Reference semantics: returnn/frontend/_backend.py:1575-1647 (scaled_dot_product_attention: matmul, mask, softmax, dropout,
 // matmul; causal via a mask on the upper triangle).
@@ -98,6 +100,159 @@ sdpa_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, const float* __rest
   }
 }
 
+// ---- bf16 rows in registers: lane l holds elements [c * 256 + l * 8, + 8) of the row for chunks c < kChunks (tkp <= kChunks * 256)
+constexpr int kVecChunks = 4;
+
+__device__ __forceinline__ void unpack8_bf16(const uint4& u, float* f) {
+  const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    f[2 * e] = __uint_as_float(w[e] << 16);
+    f[2 * e + 1] = __uint_as_float(w[e] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint4 pack8_bf16(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+    w[e] = *reinterpret_cast<const uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// keep flags of 8 consecutive elements starting at idx (the same element -> random word mapping as rng_u32: counter idx >> 2, word idx & 3)
+__device__ __forceinline__ uint32_t keep_mask8(uint64_t seed, uint64_t idx, uint32_t thresh) {
+  uint32_t mask = 0;
+  uint64_t have = ~0ull;
+  uint4 r = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const uint64_t i = idx + e, c = i >> 2;
+    if (c != have) {
+      r = philox4x32(make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)), make_uint4((uint32_t)c, (uint32_t)(c >> 32), 0x51u, 0u));
+      have = c;
+    }
+    const uint32_t sel = (uint32_t)(i & 3);
+    const uint32_t word = sel == 0 ? r.x : sel == 1 ? r.y : sel == 2 ? r.z : r.w;
+    mask |= (word >= thresh ? 1u : 0u) << e;
+  }
+  return mask;
+}
+
+__global__ void __launch_bounds__(128)
+sdpa_softmax_fwd_vec_kernel(const __nv_bfloat16* __restrict__ s, __nv_bfloat16* __restrict__ p, __nv_bfloat16* __restrict__ pd,
+                            const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
+                            float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  if (i >= tqp) return;
+  const long long row = ((long long)z * tqp + i) * tkp;
+  const bool drop = p_drop > 0.f;
+  const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
+  float v[kVecChunks][8];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int c = 0; c < kVecChunks; ++c) {
+    const int j0 = c * 256 + lane * 8;
+    if (j0 < n) {  // at least one visible key in this vector
+      unpack8_bf16(*reinterpret_cast<const uint4*>(s + row + j0), v[c]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (j0 + e >= n) v[c][e] = -INFINITY;
+        mx = fmaxf(mx, v[c][e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[c][e] = -INFINITY;
+    }
+  }
+  mx = warp_max(mx);
+  float sum = 0.f;
+#pragma unroll
+  for (int c = 0; c < kVecChunks; ++c) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      v[c][e] = (n > 0 && v[c][e] > -INFINITY) ? __expf(v[c][e] - mx) : 0.f;
+      sum += v[c][e];
+    }
+  }
+  sum = warp_sum(sum);
+  const float inv = n > 0 ? 1.f / sum : 0.f;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+#pragma unroll
+  for (int c = 0; c < kVecChunks; ++c) {
+    const int j0 = c * 256 + lane * 8;
+    if (j0 >= tkp) continue;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[c][e] *= inv;
+    *reinterpret_cast<uint4*>(p + row + j0) = pack8_bf16(v[c]);
+    if (drop) {
+      const uint32_t keep = j0 < n ? keep_mask8(sd, off + (uint64_t)(row + j0), thresh) : 0u;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[c][e] = (keep >> e) & 1u ? v[c][e] * keep_scale : 0.f;
+      *reinterpret_cast<uint4*>(pd + row + j0) = pack8_bf16(v[c]);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(128)
+sdpa_softmax_bwd_vec_kernel(const __nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ dpd, __nv_bfloat16* __restrict__ ds,
+                            const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
+                            float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
+  rb_pdl_wait();
+  rb_pdl_launch();
+  const int lane = threadIdx.x & 31;
+  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int z = blockIdx.y;
+  if (i >= tqp) return;
+  const long long row = ((long long)z * tqp + i) * tkp;
+  const bool drop = p_drop > 0.f;
+  const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
+  const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
+  const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
+  const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
+  float pv[kVecChunks][8], dv[kVecChunks][8];
+  float delta = 0.f;
+#pragma unroll
+  for (int c = 0; c < kVecChunks; ++c) {
+    const int j0 = c * 256 + lane * 8;
+    if (j0 < n) {
+      unpack8_bf16(*reinterpret_cast<const uint4*>(p + row + j0), pv[c]);
+      unpack8_bf16(*reinterpret_cast<const uint4*>(dpd + row + j0), dv[c]);
+      const uint32_t keep = drop ? keep_mask8(sd, off + (uint64_t)(row + j0), thresh) : 0xffu;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (j0 + e >= n) {
+          pv[c][e] = 0.f;
+          dv[c][e] = 0.f;
+        } else if (drop) {
+          dv[c][e] = (keep >> e) & 1u ? dv[c][e] * keep_scale : 0.f;
+        }
+        delta += pv[c][e] * dv[c][e];
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) pv[c][e] = dv[c][e] = 0.f;
+    }
+  }
+  delta = warp_sum(delta);
+#pragma unroll
+  for (int c = 0; c < kVecChunks; ++c) {
+    const int j0 = c * 256 + lane * 8;
+    if (j0 >= tkp) continue;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) dv[c][e] = pv[c][e] * (dv[c][e] - delta);
+    *reinterpret_cast<uint4*>(ds + row + j0) = pack8_bf16(dv[c]);
+  }
+}
+
 }  // namespace
 
 RB_EXPORT int rb200_sdpa_softmax_fwd(const float* s, void* p, void* pd, const int* k_lens, int batch, int heads, int tq, int tk, int tqp, int tkp,
@@ -126,4 +281,34 @@ RB_EXPORT int rb200_sdpa_softmax_bwd(const void* p, const float* dpd, void* ds, 
   rb_launch_pdl(sdpa_softmax_bwd_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)p, dpd, (__nv_bfloat16*)ds, k_lens, heads, tq, tk, tqp, tkp,
                 causal, causal_shift, p_drop, seed, offset);
   return rb_check_launch("sdpa_softmax_bwd");
+}
+
+// bf16 scores / gradients; rows of at most 1024 (padded) keys
+RB_EXPORT int rb200_sdpa_softmax_fwd_bf16(const void* s, void* p, void* pd, const int* k_lens, int batch, int heads, int tq, int tk, int tqp, int tkp,
+                                          int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
+                                          cudaStream_t stream) {
+  if (batch <= 0 || tqp <= 0) return RB_OK;
+  if (tqp % 64 || tkp % 64 || tkp > kVecChunks * 256 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !pd || !(p_drop < 1.f)))) {
+    rb_set_error("sdpa_softmax_fwd_bf16: padded extents must be multiples of 64, keys at most %d (tq %d/%d tk %d/%d); dropout needs seed, offset and pd",
+                 kVecChunks * 256, tq, tqp, tk, tkp);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((tqp + 3) / 4, batch * heads);
+  rb_launch_pdl(sdpa_softmax_fwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)s, (__nv_bfloat16*)p, (__nv_bfloat16*)pd, k_lens, heads, tq,
+                tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset);
+  return rb_check_launch("sdpa_softmax_fwd_bf16");
+}
+
+RB_EXPORT int rb200_sdpa_softmax_bwd_bf16(const void* p, const void* dpd, void* ds, const int* k_lens, int batch, int heads, int tq, int tk, int tqp,
+                                          int tkp, int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
+                                          cudaStream_t stream) {
+  if (batch <= 0 || tqp <= 0) return RB_OK;
+  if (tqp % 64 || tkp % 64 || tkp > kVecChunks * 256 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !(p_drop < 1.f)))) {
+    rb_set_error("sdpa_softmax_bwd_bf16: padded extents must be multiples of 64, keys at most %d (tq %d/%d tk %d/%d)", kVecChunks * 256, tq, tqp, tk, tkp);
+    return RB_ERR_ARG;
+  }
+  dim3 grid((tqp + 3) / 4, batch * heads);
+  rb_launch_pdl(sdpa_softmax_bwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)p, (const __nv_bfloat16*)dpd, (__nv_bfloat16*)ds, k_lens, heads,
+                tq, tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset);
+  return rb_check_launch("sdpa_softmax_bwd_bf16");
 }

@@ -51,6 +51,44 @@ def _reverse_padded(x: torch.Tensor, lens: Optional[torch.Tensor]) -> torch.Tens
     return torch.gather(x, 0, idx.reshape(T, -1, *([1] * (x.dim() - 2))).expand_as(x))
 
 
+PERSIST_MAX_ROWS = 48  # batch rows of one launch of the persistent recurrence kernels
+PERSIST_MAX_CHUNKS = 3  # beyond that the per-step executor (whose step time hardly grows with the batch) is the faster one
+
+
+def _batch_chunks(x: torch.Tensor, lens: Optional[torch.Tensor], w_rec: torch.Tensor, w_rec_bw: Optional[torch.Tensor] = None):
+    """
+    The persistent recurrence kernels take at most :data:`PERSIST_MAX_ROWS` sequences. A larger batch is cut into nearly equal
+    groups of consecutive sequences, each running in the persistent kernel over its own longest length (sequences are independent;
+    the gradients of the weights add up through autograd), as long as that beats the per-step executor.
+
+    :return: list of (b0, b1, frames) or None when the batch is not to be cut
+    """
+    from . import lstm_native as _n
+
+    T, B, _ = x.shape
+    n = -(-B // PERSIST_MAX_ROWS)
+    if B <= PERSIST_MAX_ROWS or n > PERSIST_MAX_CHUNKS or T == 0:
+        return None
+    if w_rec_bw is not None and w_rec_bw.shape != w_rec.shape:
+        return None
+    per = -(-B // n)
+    if not _n.persist_supported(x, per, w_rec):
+        return None
+    lens_host = lens.tolist() if (lens is not None and not lens.is_cuda) else None
+    out = []
+    for b0 in range(0, B, per):
+        b1 = min(B, b0 + per)
+        t = max(1, min(T, max(lens_host[b0:b1]))) if lens_host is not None else T
+        out.append((b0, b1, t))
+    return out
+
+
+def _join_chunks(outs, T: int):
+    """(y [t_c, b_c, H], h, c) per chunk -> one (y [T, B, H], h, c); frames beyond a chunk's own length are zero"""
+    ys = [torch.nn.functional.pad(y, (0, 0, 0, 0, 0, T - y.shape[0])) if y.shape[0] < T else y for y, _h, _c in outs]
+    return torch.cat(ys, dim=1), torch.cat([h for _y, h, _c in outs], dim=0), torch.cat([c for _y, _h, c in outs], dim=0)
+
+
 def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_rec: torch.Tensor, bias: Optional[torch.Tensor],
          h0: torch.Tensor, c0: torch.Tensor, reverse: bool = False) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """
@@ -62,6 +100,11 @@ def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_re
         from . import lstm_native as _n
 
         if _n.available(x) and _n.supports(x, w_rec):
+            chunks = _batch_chunks(x, lens, w_rec)
+            if chunks:
+                outs = [_n.lstm(x[:t, b0:b1], lens[b0:b1] if lens is not None else None, w_ff, w_rec, bias, h0[b0:b1], c0[b0:b1], reverse=reverse)
+                        for b0, b1, t in chunks]
+                return _join_chunks(outs, x.shape[0])
             return _n.lstm(x, lens, w_ff, w_rec, bias, h0, c0, reverse=reverse)
     T, B, _ = x.shape
     H = w_rec.shape[1]
@@ -109,5 +152,10 @@ def blstm(x: torch.Tensor, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h
 
         if _n.blstm_supported(x, fw[1], bw[1]):
             return _n.blstm(x, lens, fw, bw, h0_fw, c0_fw, h0_bw, c0_bw)
+        chunks = _batch_chunks(x, lens, fw[1], bw[1])
+        if chunks:
+            outs = [_n.blstm(x[:t, b0:b1], lens[b0:b1] if lens is not None else None, fw, bw, h0_fw[b0:b1], c0_fw[b0:b1], h0_bw[b0:b1], c0_bw[b0:b1])
+                    for b0, b1, t in chunks]
+            return _join_chunks([o[0] for o in outs], x.shape[0]), _join_chunks([o[1] for o in outs], x.shape[0])
     return (lstm(x, lens, fw[0], fw[1], fw[2], h0_fw, c0_fw, reverse=False),
             lstm(x, lens, bw[0], bw[1], bw[2], h0_bw, c0_bw, reverse=True))

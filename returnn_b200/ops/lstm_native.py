@@ -109,6 +109,15 @@ def blstm_supported(x, w_rec_fw, w_rec_bw) -> bool:
     return bool(fn(int(T), int(B), int(w_rec_fw.shape[1])))
 
 
+def persist_supported(x, batch: int, w_rec) -> bool:
+    """whether a batch of ``batch`` sequences of this input runs in the persistent recurrence kernels"""
+    lib = _lib.get_lib()
+    if lib is None or not hasattr(lib, "rb200_blstm_supported") or not available(x) or not supports(x, w_rec):
+        return False
+    fn = _lib.bind("rb200_blstm_supported", [_i32, _i32, _i32])
+    return bool(fn(int(x.shape[0]), int(batch), int(w_rec.shape[1])))
+
+
 class _BlstmRecFn(torch.autograd.Function):
     """the recurrences of both directions on pre-projected inputs z [T,B,4H], one kernel for the two time loops"""
 

@@ -59,11 +59,13 @@ class _SdpaFn(torch.autograd.Function):
         k2 = k.to(bf).contiguous().view(B * Tk, HD)
         v2 = v.to(bf).contiguous().view(B * Tk, HD)
         Tqp, Tkp = _r64(Tq), _r64(Tk)
-        s = torch.empty(B * H * Tqp, Tkp, dtype=torch.float32, device=dev)
+        # bf16 scores (what a matmul under autocast writes) whenever a key row fits the register-resident softmax: half the traffic
+        vec = Tkp <= 1024 and hasattr(_lib.get_lib(), "rb200_sdpa_softmax_fwd_bf16")
+        s = torch.empty(B * H * Tqp, Tkp, dtype=bf if vec else torch.float32, device=dev)
         # 1. S = scale * Q K^T per (batch, head)
         _bgemm(q2, k2, s, m=Tq, n=Tk, k=D, a_mn=False, b_mn=False, lda=HD, ldb=HD, ldc=Tkp, a_shape=(B * Tq, HD), b_shape=(B * Tk, HD),
                offs=(Tq, 0, 0, D, Tk, 0, 0, D, H * Tqp * Tkp, Tqp * Tkp), batch=B * H, heads=H, lens=None, m_l=False, n_l=False, k_l=False,
-               alpha=scale, out_fp32=True)
+               alpha=scale, out_fp32=not vec)
         # 2. P = softmax(mask(S)), Pd = dropout(P); margins up to the padded extents are written as zeros
         drop = p_drop > 0.0
         p = torch.empty(B * H * Tqp, Tkp, dtype=bf, device=dev)
@@ -73,7 +75,7 @@ class _SdpaFn(torch.autograd.Function):
         if drop:
             seed[1] += B * H * Tqp * Tkp
         causal_shift = Tk - Tq
-        fn = _lib.bind("rb200_sdpa_softmax_fwd", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp])
+        fn = _lib.bind("rb200_sdpa_softmax_fwd_bf16" if vec else "rb200_sdpa_softmax_fwd", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp])
         _lib.check(fn(s.data_ptr(), p.data_ptr(), pd.data_ptr() if drop else None, k_lens.data_ptr() if k_lens is not None else None, B, H, Tq, Tk,
                       Tqp, Tkp, 1 if causal else 0, causal_shift, float(p_drop), seed.data_ptr(), off.data_ptr(), _lib.stream_ptr()), "sdpa_softmax_fwd")
         _lib.count_launch()
@@ -84,6 +86,7 @@ class _SdpaFn(torch.autograd.Function):
                offs=(H * Tqp, Tqp, 0, 0, Tk, 0, 0, D, Tq * HD, D), batch=B * H, heads=H, lens=None, m_l=False, n_l=False, k_l=False)
         ctx.save_for_backward(q2, k2, v2, p, pd if drop else None, k_lens, off)
         ctx.geom = (B, H, Tq, Tk, D, Tqp, Tkp, bool(causal), float(scale), float(p_drop), q.dtype)
+        ctx.vec = vec
         return o.view(B, Tq, HD).to(q.dtype)
 
     @staticmethod
@@ -102,13 +105,14 @@ class _SdpaFn(torch.autograd.Function):
         _bgemm(pd, do2, dv, m=Tk, n=D, k=Tq, a_mn=True, b_mn=True, lda=Tkp, ldb=HD, ldc=HD, a_shape=(B * H * Tqp, Tkp), b_shape=(B * Tq, HD),
                offs=(H * Tqp, Tqp, 0, 0, Tq, 0, 0, D, Tk * HD, D), batch=B * H, heads=H, lens=None, m_l=False, n_l=False, k_l=False)
         # dPd = dO V^T
-        dpd = torch.empty(B * H * Tqp, Tkp, dtype=torch.float32, device=dev)
+        vec = ctx.vec
+        dpd = torch.empty(B * H * Tqp, Tkp, dtype=bf if vec else torch.float32, device=dev)
         _bgemm(do2, v2, dpd, m=Tq, n=Tk, k=D, a_mn=False, b_mn=False, lda=HD, ldb=HD, ldc=Tkp, a_shape=(B * Tq, HD), b_shape=(B * Tk, HD),
                offs=(Tq, 0, 0, D, Tk, 0, 0, D, H * Tqp * Tkp, Tqp * Tkp), batch=B * H, heads=H, lens=None, m_l=False, n_l=False, k_l=False,
-               out_fp32=True)
+               out_fp32=not vec)
         ds = torch.empty(B * H * Tqp, Tkp, dtype=bf, device=dev)
         seed = _seed_tensor(dev)
-        fn = _lib.bind("rb200_sdpa_softmax_bwd", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp])
+        fn = _lib.bind("rb200_sdpa_softmax_bwd_bf16" if vec else "rb200_sdpa_softmax_bwd", [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _f32, _vp, _vp, _vp])
         _lib.check(fn(p.data_ptr(), dpd.data_ptr(), ds.data_ptr(), k_lens.data_ptr() if k_lens is not None else None, B, H, Tq, Tk, Tqp, Tkp,
                       1 if causal else 0, Tk - Tq, float(p_drop), seed.data_ptr(), off.data_ptr(), _lib.stream_ptr()), "sdpa_softmax_bwd")
         _lib.count_launch()

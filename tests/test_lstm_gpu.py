@@ -82,3 +82,47 @@ def test_blstm_one_kernel_for_both_directions_matches_reference(T, B, I, H):
         scale = float(t.grad.abs().max()) + 1e-6
         err = float((g.float() - t.grad).abs().max()) / scale
         assert err < 0.06, "gradient of %s: rel. max err %.4f" % (name, err)
+
+
+@gpu
+@pytest.mark.parametrize("T,B,I,H", [(25, 96, 64, 128), (18, 130, 32, 256)])
+def test_blstm_large_batch_runs_in_chunks_of_the_persistent_kernel(T, B, I, H):
+    """more sequences than one launch of the persistent kernels takes: groups of sequences, each over its own longest length"""
+    from returnn_b200.ops import lstm as L, gemm
+
+    torch.manual_seed(2)
+    dev = "cuda"
+    x = (torch.randn(T, B, I, device=dev) * 0.5).requires_grad_(True)
+
+    def params():
+        return [(torch.randn(4 * H, I, device=dev) * 0.2).requires_grad_(True), (torch.randn(4 * H, H, device=dev) * 0.2).requires_grad_(True),
+                (torch.randn(4 * H, device=dev) * 0.1).requires_grad_(True)]
+
+    fw, bw = params(), params()
+    states = [(torch.randn(B, H, device=dev) * 0.3).requires_grad_(True) for _ in range(4)]
+    lens = torch.sort(torch.randint(1, T + 1, (B,)), descending=True).values
+    lens[0] = T
+    chunks = L._batch_chunks(x, lens, fw[1], bw[1])
+    assert chunks is not None and len(chunks) == -(-B // L.PERSIST_MAX_ROWS) and chunks[-1][2] < T
+    wts = [torch.randn(T, B, H, device=dev) for _ in range(2)] + [torch.randn(B, H, device=dev) for _ in range(4)]
+    leaves = [x] + fw + bw + states
+    (yf, hf, cf), (yb, hb, cb) = L.blstm(x, lens, tuple(fw), tuple(bw), *states)
+    outs = (yf, yb, hf, cf, hb, cb)
+    sum((o.float() * w).sum() for o, w in zip(outs, wts)).backward()
+    gemm.check_status()
+    got = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    yfr, hfr, cfr = L.lstm_reference(x, lens, *fw, states[0], states[1], reverse=False)
+    ybr, hbr, cbr = L.lstm_reference(x, lens, *bw, states[2], states[3], reverse=True)
+    sum((o * w).sum() for o, w in zip((yfr, ybr, hfr, cfr, hbr, cbr), wts)).backward()
+    for o, r in zip(outs, (yfr, ybr, hfr, cfr, hbr, cbr)):
+        torch.testing.assert_close(o.float(), r, atol=0.05, rtol=0.03)
+    for g, t in zip(got, leaves):
+        scale = float(t.grad.abs().max()) + 1e-6
+        assert float((g.float() - t.grad).abs().max()) / scale < 0.06
+    # one direction alone takes the same route
+    y, h, c = L.lstm(x, lens, *fw, states[0], states[1], reverse=True)
+    yr, hr, cr = L.lstm_reference(x, lens, *fw, states[0], states[1], reverse=True)
+    torch.testing.assert_close(y.float(), yr, atol=0.05, rtol=0.03)
+    torch.testing.assert_close(c.float(), cr, atol=0.05, rtol=0.03)
