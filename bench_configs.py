@@ -164,7 +164,12 @@ def run_gpu(args):
         "max_seqs": 2000, "learning_rate": 1e-4, "torch_amp": "bfloat16", "num_epochs": 1, "log_verbosity": 2 if rank == 0 else 1,
         "device": "cuda", "forward_step": getattr(mod, "forward_step", None)}, **spec["extra"]))
     if world > 1:
-        cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else {"reduce_type": "grad"})
+        cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else
+                {"reduce_type": "grad_explicit" if args.cuda_graph else "grad"})
+    if args.cuda_graph:
+        # whole-step graph replay over buffers bounded by the largest batch of the pool (sequences, and frames per key rounded up to 8)
+        cap = {k: -(-max(s[k].shape[0] for b in batches for s in b) // 8) * 8 for k in ("data", "classes")}
+        cfg.set("torch_cuda_graph", {"batch_size_bound": max(len(b) for b in batches), "dim_capacity": cap, "warmup_steps": 2})
     set_global_config(cfg)
     BehaviorVersion._reset(24)
     log.init_by_config(cfg)
@@ -288,7 +293,7 @@ def run_gpu(args):
             "impl": "returnn_b200", "config": {"model": spec["name"], "global_batch": "%i per GPU x %i" % (spec["budget"], world),
                                                 "parallelism": ("dp%i param averaging every 100 steps" % world) if args.config == "conformer_aed" else "dp%i" % world},
             "grad_reduce": engine._torch_distributed_ctx.grad_reduce_mode if engine._torch_distributed_ctx else "none",
-            "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
+            "cuda_graph": bool(args.cuda_graph), "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
                                       "d2h_bytes_per_step": 4 * max(len(last or {}), 1), "last_loss": last},
             "gpu_launches": launches}))
     if world > 1:
@@ -744,6 +749,7 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--task", default="train", choices=["train", "search"], help="search: beam search decoding (conformer_aed, transformer_mt)")
+    ap.add_argument("--cuda-graph", action="store_true", help="train through the captured whole-step CUDA graph (config option torch_cuda_graph)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: every --config here has a reference arm")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -208,10 +208,22 @@ ln_bwd_kernel(const void* __restrict__ x, const void* __restrict__ dy, const voi
 }
 
 // Backward for bf16 activations with accumulation into fp32 dgamma / dbeta (the form the training step uses). One CTA of
-// 16 warps per SM; a warp walks its rows with the NEXT row's x and dy already in flight while it computes the current one
-// (the loads are the whole cost of a row); the 16 warps' column sums meet in shared memory and leave as one atomic per
-// column and CTA: no partials buffer and no second kernel.
+// 16 warps per SM. A warp owns only two or three rows of a launch, so the cost of a row is the latency of its loads: every warp
+// keeps a ring of kBwdAccDepth rows (x, dy, residual gradient) in flight through cp.async into shared memory, each lane fetching
+// exactly the 16-byte pieces it reads back itself (no barrier between fetch and use), with the rows' mean / rstd parked in the
+// lanes of the warp. The 16 warps' column sums meet in the same shared memory afterwards and leave as one atomic per column and
+// CTA: no partials buffer and no second kernel.
 constexpr int kBwdAccWarps = 16;
+constexpr int kBwdAccDepth = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
 
 template <int CHUNKS>
 __global__ void __launch_bounds__(kBwdAccWarps * 32, 1)
@@ -221,9 +233,10 @@ ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
                   const __nv_bfloat16* __restrict__ dres) {
   rb_pdl_wait();  // may have been scheduled before the preceding kernel finished
   rb_pdl_launch();
-  extern __shared__ float smem[];  // [2][n]
+  extern __shared__ __align__(16) unsigned char smem_raw[];  // [warps][depth][3][n] bf16, later [warps][2][n] fp32
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(smem_raw) + (size_t)warp * kBwdAccDepth * 3 * n;
   F8 g[CHUNKS], acc_g[CHUNKS], acc_b[CHUNKS];
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
@@ -232,21 +245,28 @@ ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc_g[c].v[i] = acc_b[c].v[i] = 0.f;
   }
-  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) smem[i] = 0.f;
-  __syncthreads();
   const int64_t stride = (int64_t)gridDim.x * kBwdAccWarps;
-  int64_t row = (int64_t)blockIdx.x * kBwdAccWarps + warp;
-  uint4 nx[CHUNKS], nd[CHUNKS];
-  auto fetch = [&](int64_t r) {
-    const int64_t base = r * (int64_t)n;
+  const int64_t row0 = (int64_t)blockIdx.x * kBwdAccWarps + warp;
+  float my_mean = 0.f, my_rstd = 0.f;  // of the row in ring slot `lane` (lanes < depth)
+  auto fetch = [&](int64_t r, int slot) {
+    if (r < rows) {
+      const int64_t base = r * (int64_t)n;
+      __nv_bfloat16* dst = ring + (size_t)slot * 3 * n;
 #pragma unroll
-    for (int c = 0; c < CHUNKS; ++c) {
-      const int col = (c * 32 + lane) * 8;
-      if (col < n) {
-        nx[c] = *reinterpret_cast<const uint4*>(x + base + col);
-        nd[c] = *reinterpret_cast<const uint4*>(dy + base + col);
+      for (int c = 0; c < CHUNKS; ++c) {
+        const int col = (c * 32 + lane) * 8;
+        if (col < n) {
+          cp_async16(dst + col, x + base + col);
+          cp_async16(dst + n + col, dy + base + col);
+          if (dres) cp_async16(dst + 2 * n + col, dres + base + col);
+        }
+      }
+      if (lane == slot) {
+        my_mean = mean_in[r];
+        my_rstd = rstd_in[r];
       }
     }
+    cp_async_commit();  // also when nothing was issued: the group count per iteration stays fixed
   };
   auto unpack = [](const uint4& u, F8& f) {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
@@ -257,20 +277,25 @@ ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       f.v[2 * i + 1] = p.y;
     }
   };
-  if (row < rows) fetch(row);
-  while (row < rows) {
-    const float mean = mean_in[row], rstd = rstd_in[row];
+#pragma unroll
+  for (int k = 0; k < kBwdAccDepth; ++k) fetch(row0 + k * stride, k);
+  int slot = 0;
+  for (int64_t row = row0; row < rows; row += stride) {
+    cp_async_wait<kBwdAccDepth - 1>();  // the oldest group (this row) has landed; own copies only, so no barrier
+    const float mean = __shfl_sync(0xffffffffu, my_mean, slot), rstd = __shfl_sync(0xffffffffu, my_rstd, slot);
     const int64_t base = row * (int64_t)n;
-    F8 xh[CHUNKS], d[CHUNKS];
-    uint4 rr[CHUNKS];
+    const __nv_bfloat16* src = ring + (size_t)slot * 3 * n;
+    F8 xh[CHUNKS], d[CHUNKS], res[CHUNKS];
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
-      unpack(nx[c], xh[c]);
-      unpack(nd[c], d[c]);
-      if (dres && (c * 32 + lane) * 8 < n) rr[c] = *reinterpret_cast<const uint4*>(dres + base + (c * 32 + lane) * 8);
+      const int col = (c * 32 + lane) * 8;
+      if (col < n) {
+        unpack(*reinterpret_cast<const uint4*>(src + col), xh[c]);
+        unpack(*reinterpret_cast<const uint4*>(src + n + col), d[c]);
+        if (dres) unpack(*reinterpret_cast<const uint4*>(src + 2 * n + col), res[c]);
+      }
     }
-    const int64_t next = row + stride;
-    if (next < rows) fetch(next);
+    fetch(row + (int64_t)kBwdAccDepth * stride, slot);  // the slot is in registers now
     float s1 = 0.f, s2 = 0.f;
 #pragma unroll
     for (int c = 0; c < CHUNKS; ++c) {
@@ -293,33 +318,41 @@ ln_bwd_acc_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     for (int c = 0; c < CHUNKS; ++c) {
       const int col = (c * 32 + lane) * 8;
       if (col < n) {
-        F8 o, res;
-        if (dres) unpack(rr[c], res);
+        F8 o;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           o.v[i] = rstd * (g[c].v[i] * d[c].v[i] - s1 - xh[c].v[i] * s2);
-          if (dres) o.v[i] += res.v[i];
+          if (dres) o.v[i] += res[c].v[i];
         }
         store8(dx, base + col, o, 1);
       }
     }
-    row = next;
+    slot = slot + 1 == kBwdAccDepth ? 0 : slot + 1;
   }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its ring: the memory becomes [warps][2][n] fp32
+  float* sums = reinterpret_cast<float*>(smem_raw);
 #pragma unroll
   for (int c = 0; c < CHUNKS; ++c) {
     const int col = (c * 32 + lane) * 8;
     if (col < n) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        atomicAdd(&smem[col + i], acc_g[c].v[i]);
-        atomicAdd(&smem[n + col + i], acc_b[c].v[i]);
-      }
+      float* pg = sums + (size_t)(warp * 2) * n + col;
+      *reinterpret_cast<float4*>(pg) = make_float4(acc_g[c].v[0], acc_g[c].v[1], acc_g[c].v[2], acc_g[c].v[3]);
+      *reinterpret_cast<float4*>(pg + 4) = make_float4(acc_g[c].v[4], acc_g[c].v[5], acc_g[c].v[6], acc_g[c].v[7]);
+      *reinterpret_cast<float4*>(pg + n) = make_float4(acc_b[c].v[0], acc_b[c].v[1], acc_b[c].v[2], acc_b[c].v[3]);
+      *reinterpret_cast<float4*>(pg + n + 4) = make_float4(acc_b[c].v[4], acc_b[c].v[5], acc_b[c].v[6], acc_b[c].v[7]);
     }
   }
   __syncthreads();
-  for (int col = threadIdx.x; col < n; col += blockDim.x) {
-    if (dgamma) atomicAdd(dgamma + col, smem[col]);
-    if (dbeta) atomicAdd(dbeta + col, smem[n + col]);
+  for (int i = threadIdx.x; i < 2 * n; i += blockDim.x) {  // i < n: dgamma column i, else dbeta column i - n
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kBwdAccWarps; ++w) t += sums[(size_t)w * 2 * n + i];
+    if (i < n) {
+      if (dgamma) atomicAdd(dgamma + i, t);
+    } else if (dbeta) {
+      atomicAdd(dbeta + i - n, t);
+    }
   }
 }
 
@@ -389,14 +422,25 @@ RB_EXPORT int rb200_layer_norm_bwd_ex(const void* x, const void* dy, const void*
   if (accumulate && x_bf16 && n <= 512 && rows > 0 && (dgamma || dbeta)) {
     int ctas = (int)((rows + kBwdAccWarps - 1) / kBwdAccWarps);
     if (ctas > 148) ctas = 148;
-    const size_t sm = (size_t)2 * n * sizeof(float);
+    const size_t sm = (size_t)kBwdAccWarps * kBwdAccDepth * 3 * n * sizeof(__nv_bfloat16);  // >= the [warps][2][n] fp32 it becomes at the end
     const int ch = (n + 255) / 256;
+    static bool attr_set[2] = {false, false};
 #define LN_ACC(C)                                                                                                                       \
+  if (!attr_set[C - 1]) {                                                                                                               \
+    if (cudaFuncSetAttribute(ln_bwd_acc_kernel<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)((size_t)kBwdAccWarps * kBwdAccDepth * 3 * 512 * 2)) != cudaSuccess) { \
+      rb_set_error("layer_norm_bwd_acc: cannot reserve shared memory");                                                                 \
+      return RB_ERR_LAUNCH;                                                                                                              \
+    }                                                                                                                                   \
+    attr_set[C - 1] = true;                                                                                                             \
+  }                                                                                                                                     \
   rb_launch_pdl(ln_bwd_acc_kernel<C>, dim3(ctas), dim3(kBwdAccWarps * 32), sm, stream, (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, gamma, mean, rstd, \
                                                                  (__nv_bfloat16*)dx, dgamma, dbeta, rows, n, w_bf16, rms,              \
                                                                  (const __nv_bfloat16*)dres)
-    if (ch <= 1) LN_ACC(1);
-    else LN_ACC(2);
+    if (ch <= 1) {
+      LN_ACC(1);
+    } else {
+      LN_ACC(2);
+    }
 #undef LN_ACC
     return rb_check_launch("layer_norm_bwd_acc");
   }

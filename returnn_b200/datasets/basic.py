@@ -232,6 +232,17 @@ class Dataset:
             start, end = self._get_shuffle_frames_range(start, end)
         self._load_seqs(start, end)
 
+    def _sliding_window(self, xr: numpy.ndarray) -> numpy.ndarray:
+        """
+        :param xr: [time, feature]
+        :return: [time, window * feature]: frame t is the concatenation of frames t - window//2 .. t + window//2, zeros outside
+        """
+        half = int(self.window) // 2
+        t, f = xr.shape
+        padded = numpy.concatenate([numpy.zeros((half, f), dtype=xr.dtype), xr, numpy.zeros((half, f), dtype=xr.dtype)], axis=0)
+        view = numpy.lib.stride_tricks.sliding_window_view(padded, (2 * half + 1, f))[:, 0]  # [time, window, feature]
+        return numpy.ascontiguousarray(view.reshape(t, (2 * half + 1) * f))
+
     def _get_shuffle_frames_range(self, start, end):
         n = self.shuffle_frames_of_nseqs
         return start - start % n, end + (n - end % n) % n

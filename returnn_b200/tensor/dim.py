@@ -532,6 +532,15 @@ class Dim:
             for v in vals[1:]:
                 cap = _apply_int_op(kind, cap, v)
             res.capacity = int(cap)
+        elif dimension is None and caps and caps[0] is not None and kind == "pad":
+            res.capacity = int(caps[0]) + attribs["left"] + attribs["right"]
+        elif dimension is None and caps and caps[0] is not None and kind == "conv":
+            cap = int(caps[0])
+            if attribs["padding"] == "valid":
+                cap -= (attribs["filter_size"] - 1) * attribs["dilation"]
+            elif isinstance(attribs["padding"], int):
+                cap += 2 * attribs["padding"] - (attribs["filter_size"] - 1) * attribs["dilation"]
+            res.capacity = max(-(-cap // attribs["stride"]), 0)
         _derived_cache[key] = res
         return res
 

@@ -634,6 +634,19 @@ class Engine(EngineBase):
         if dist:
             dist.check_peers(self.global_train_step)
         self._consume_staged(extern_data_raw)
+        if self._graph_step is not None:
+            # ``torch_cuda_graph``: the captured step (it zeroes its static gradients itself), then reduction and update as below
+            res = self._graph_step.run_train_step_ex(extern_data_raw, dist=dist, epoch_step_idx=self.global_train_step, read=bool(read_losses))
+            self.global_train_step += 1
+            self._updater.set_current_train_step(global_train_step=self.global_train_step, epoch=self.epoch or 1, epoch_continuous=None)
+            if getattr(self, "_status_poller", None) is None:
+                from ..ops.status import StatusPoller
+
+                self._status_poller = StatusPoller(self._device)
+            self._status_poller.step(where="train step %i" % (self.global_train_step - 1))
+            if res["vals"] is None:
+                return {}
+            return dict(zip(res["names"], res["vals"][: len(res["names"])]))
         self._updater.zero_grad()
         extern_data = extern_data_util.raw_dict_to_extern_data(
             extern_data_raw, extern_data_template=self.extern_data, device=self._device,

@@ -204,13 +204,14 @@ class GraphCapturedTrainStep:
             inv["grad_norm:p2"] = 1.0
         return losses, inv
 
-    def run_train_step_ex(self, extern_data_raw: Dict[str, Any], *, dist=None, epoch_step_idx: int = 0) -> Dict[str, Any]:
+    def run_train_step_ex(self, extern_data_raw: Dict[str, Any], *, dist=None, epoch_step_idx: int = 0, read: bool = True) -> Dict[str, Any]:
         """
         One step: copy in, replay (or warm-up / capture), gradient reduction of the distributed context, optimizer, loss read.
 
         :param extern_data_raw: the collated batch (host tensors)
         :param dist: the engine's distributed context or None
         :param epoch_step_idx: step within the epoch (for the parameter-averaging schedule)
+        :param read: False: the losses stay on the device (``vals`` is None then) and the host does not wait for the step
         :return: ``names`` (loss names), ``vals`` (host floats: the summed losses, then the inverse norm factors),
             ``score_keys`` (names that are scores, not errors), ``grad_norm`` (device scalar or None)
         """
@@ -262,6 +263,8 @@ class GraphCapturedTrainStep:
             grad_norm = None
         if dist is not None:
             dist.step_after_param_update(module=eng._pt_model, epoch_step_idx=epoch_step_idx)
+        if not read:
+            return dict(names=list(self._loss_names), vals=None, score_keys=set(self._score_keys), grad_norm=grad_norm)
         self._host_buf.copy_(self._loss_buf, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return dict(names=list(self._loss_names), vals=self._host_buf.tolist(), score_keys=set(self._score_keys), grad_norm=grad_norm)

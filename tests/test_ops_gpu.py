@@ -261,3 +261,41 @@ def test_log_mel_gemm_form_matches_float64():
     torch.testing.assert_close(direct, ref, atol=5e-3, rtol=0)
     torch.testing.assert_close(got, ref, atol=5e-3, rtol=0)
     assert float(got[-1].abs().max()) == 0.0 and float(got[-2, (T // 2 - 400) // 160 + 1:].abs().max()) == 0.0
+
+
+@gpu
+@pytest.mark.parametrize("rows,n", [(1, 512), (37, 256), (4100, 512), (9475, 384), (2368 * 5 + 3, 512)])
+@pytest.mark.parametrize("with_res", [False, True])
+def test_layer_norm_bwd_accumulating_kernel_matches_fp32(rows, n, with_res):
+    """the backward the native encoder uses (bf16 rows, residual gradient added, dgamma / dbeta added onto fp32 buffers) against torch in fp32"""
+    import ctypes
+    from returnn_b200.ops import _lib
+
+    torch.manual_seed(rows + n)
+    dev = "cuda"
+    bf = torch.bfloat16
+    x = (torch.randn(rows, n, device=dev) * 1.5 + 0.3).to(bf)
+    dy = torch.randn(rows, n, device=dev).to(bf)
+    dres = torch.randn(rows, n, device=dev).to(bf) if with_res else None
+    gam = torch.randn(n, device=dev) * 0.5 + 1.0
+    xf = x.float().requires_grad_(True)
+    gf = gam.clone().requires_grad_(True)
+    bias = torch.zeros(n, device=dev, requires_grad=True)
+    mean = xf.detach().mean(1).contiguous()
+    rstd = (xf.detach().var(1, unbiased=False) + 1e-6).rsqrt().contiguous()
+    y = torch.nn.functional.layer_norm(xf, (n,), gf, bias, eps=1e-6)
+    y.backward(dy.float())
+    dg0, db0 = torch.randn(n, device=dev), torch.randn(n, device=dev)
+    dg, db = dg0.clone(), db0.clone()
+    dx = torch.empty_like(x)
+    part = torch.empty(2 * 592 * n, device=dev)
+    vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    fn = _lib.bind("rb200_layer_norm_bwd_ex", [vp, vp, vp, vp, vp, vp, vp, vp, vp, i64, i32, i32, i32, i32, i32, vp, i32, vp])
+    _lib.check(fn(x.data_ptr(), dy.data_ptr(), gam.data_ptr(), mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(), part.data_ptr(), dg.data_ptr(), db.data_ptr(),
+                  rows, n, 416, 1, 0, 0, dres.data_ptr() if with_res else None, 1, _lib.stream_ptr()), "ln_bwd")
+    torch.cuda.synchronize()
+    want_dx = xf.grad + (dres.float() if with_res else 0.0)
+    torch.testing.assert_close(dx.float(), want_dx, atol=0.03, rtol=0.02)
+    scale = max(1.0, rows ** 0.5)
+    torch.testing.assert_close(dg - dg0, gf.grad, atol=2e-3 * scale, rtol=1e-3)
+    torch.testing.assert_close(db - db0, bias.grad, atol=2e-3 * scale, rtol=1e-3)
