@@ -100,8 +100,22 @@ sdpa_softmax_bwd_kernel(const __nv_bfloat16* __restrict__ p, const float* __rest
   }
 }
 
-// ---- bf16 rows in registers: lane l holds elements [c * 256 + l * 8, + 8) of the row for chunks c < kChunks (tkp <= kChunks * 256)
-constexpr int kVecChunks = 4;
+// ---- bf16 rows in registers. LPR lanes share a row (32 / LPR rows per warp, so that short rows keep every lane busy); lane l of the
+// row holds elements [c * LPR * 8 + l * 8, + 8) for chunks c < CHUNKS (tkp <= CHUNKS * LPR * 8).
+constexpr int kVecMaxKeys = 1024;
+
+template <int LPR>
+__device__ __forceinline__ float row_max(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+template <int LPR>
+__device__ __forceinline__ float row_sum(float v) {
+#pragma unroll
+  for (int o = LPR / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
 
 __device__ __forceinline__ void unpack8_bf16(const uint4& u, float* f) {
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
@@ -141,24 +155,26 @@ __device__ __forceinline__ uint32_t keep_mask8(uint64_t seed, uint64_t idx, uint
   return mask;
 }
 
+template <int LPR, int CHUNKS>
 __global__ void __launch_bounds__(128)
 sdpa_softmax_fwd_vec_kernel(const __nv_bfloat16* __restrict__ s, __nv_bfloat16* __restrict__ p, __nv_bfloat16* __restrict__ pd,
                             const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
                             float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
   rb_pdl_wait();
   rb_pdl_launch();
-  const int lane = threadIdx.x & 31;
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  constexpr int RPW = 32 / LPR;  // rows per warp
+  const int lane = threadIdx.x & (LPR - 1);
+  const int i = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + (threadIdx.x & 31) / LPR;
   const int z = blockIdx.y;
-  if (i >= tqp) return;
+  if (i >= tqp) return;  // whole warps only: tqp is a multiple of 64, a block covers 4 * RPW <= 16 rows
   const long long row = ((long long)z * tqp + i) * tkp;
   const bool drop = p_drop > 0.f;
   const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
-  float v[kVecChunks][8];
+  float v[CHUNKS][8];
   float mx = -INFINITY;
 #pragma unroll
-  for (int c = 0; c < kVecChunks; ++c) {
-    const int j0 = c * 256 + lane * 8;
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int j0 = c * (LPR * 8) + lane * 8;
     if (j0 < n) {  // at least one visible key in this vector
       unpack8_bf16(*reinterpret_cast<const uint4*>(s + row + j0), v[c]);
 #pragma unroll
@@ -171,24 +187,24 @@ sdpa_softmax_fwd_vec_kernel(const __nv_bfloat16* __restrict__ s, __nv_bfloat16* 
       for (int e = 0; e < 8; ++e) v[c][e] = -INFINITY;
     }
   }
-  mx = warp_max(mx);
+  mx = row_max<LPR>(mx);
   float sum = 0.f;
 #pragma unroll
-  for (int c = 0; c < kVecChunks; ++c) {
+  for (int c = 0; c < CHUNKS; ++c) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
       v[c][e] = (n > 0 && v[c][e] > -INFINITY) ? __expf(v[c][e] - mx) : 0.f;
       sum += v[c][e];
     }
   }
-  sum = warp_sum(sum);
+  sum = row_sum<LPR>(sum);
   const float inv = n > 0 ? 1.f / sum : 0.f;
   const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
   const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
   const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
 #pragma unroll
-  for (int c = 0; c < kVecChunks; ++c) {
-    const int j0 = c * 256 + lane * 8;
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int j0 = c * (LPR * 8) + lane * 8;
     if (j0 >= tkp) continue;
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[c][e] *= inv;
@@ -202,27 +218,29 @@ sdpa_softmax_fwd_vec_kernel(const __nv_bfloat16* __restrict__ s, __nv_bfloat16* 
   }
 }
 
+template <int LPR, int CHUNKS>
 __global__ void __launch_bounds__(128)
 sdpa_softmax_bwd_vec_kernel(const __nv_bfloat16* __restrict__ p, const __nv_bfloat16* __restrict__ dpd, __nv_bfloat16* __restrict__ ds,
                             const int* __restrict__ k_lens, int heads, int tq, int tk, int tqp, int tkp, int causal, int causal_shift,
                             float p_drop, const long long* __restrict__ seed, const long long* __restrict__ offset) {
   rb_pdl_wait();
   rb_pdl_launch();
-  const int lane = threadIdx.x & 31;
-  const int i = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  constexpr int RPW = 32 / LPR;  // rows per warp
+  const int lane = threadIdx.x & (LPR - 1);
+  const int i = (blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5)) * RPW + (threadIdx.x & 31) / LPR;
   const int z = blockIdx.y;
-  if (i >= tqp) return;
+  if (i >= tqp) return;  // whole warps only: tqp is a multiple of 64, a block covers 4 * RPW <= 16 rows
   const long long row = ((long long)z * tqp + i) * tkp;
   const bool drop = p_drop > 0.f;
   const int n = i < tq ? visible_keys(i, tk, k_lens ? k_lens[z / heads] : tk, causal, causal_shift) : 0;
   const uint64_t sd = drop ? (uint64_t)seed[0] : 0, off = drop ? (uint64_t)offset[0] : 0;
   const uint32_t thresh = drop ? (uint32_t)(p_drop * 4294967296.0) : 0u;
   const float keep_scale = drop ? 1.f / (1.f - p_drop) : 1.f;
-  float pv[kVecChunks][8], dv[kVecChunks][8];
+  float pv[CHUNKS][8], dv[CHUNKS][8];
   float delta = 0.f;
 #pragma unroll
-  for (int c = 0; c < kVecChunks; ++c) {
-    const int j0 = c * 256 + lane * 8;
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int j0 = c * (LPR * 8) + lane * 8;
     if (j0 < n) {
       unpack8_bf16(*reinterpret_cast<const uint4*>(p + row + j0), pv[c]);
       unpack8_bf16(*reinterpret_cast<const uint4*>(dpd + row + j0), dv[c]);
@@ -242,10 +260,10 @@ sdpa_softmax_bwd_vec_kernel(const __nv_bfloat16* __restrict__ p, const __nv_bflo
       for (int e = 0; e < 8; ++e) pv[c][e] = dv[c][e] = 0.f;
     }
   }
-  delta = warp_sum(delta);
+  delta = row_sum<LPR>(delta);
 #pragma unroll
-  for (int c = 0; c < kVecChunks; ++c) {
-    const int j0 = c * 256 + lane * 8;
+  for (int c = 0; c < CHUNKS; ++c) {
+    const int j0 = c * (LPR * 8) + lane * 8;
     if (j0 >= tkp) continue;
 #pragma unroll
     for (int e = 0; e < 8; ++e) dv[c][e] = pv[c][e] * (dv[c][e] - delta);
@@ -288,14 +306,20 @@ RB_EXPORT int rb200_sdpa_softmax_fwd_bf16(const void* s, void* p, void* pd, cons
                                           int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
                                           cudaStream_t stream) {
   if (batch <= 0 || tqp <= 0) return RB_OK;
-  if (tqp % 64 || tkp % 64 || tkp > kVecChunks * 256 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !pd || !(p_drop < 1.f)))) {
+  if (tqp % 64 || tkp % 64 || tkp > kVecMaxKeys || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !pd || !(p_drop < 1.f)))) {
     rb_set_error("sdpa_softmax_fwd_bf16: padded extents must be multiples of 64, keys at most %d (tq %d/%d tk %d/%d); dropout needs seed, offset and pd",
-                 kVecChunks * 256, tq, tqp, tk, tkp);
+                 kVecMaxKeys, tq, tqp, tk, tkp);
     return RB_ERR_ARG;
   }
-  dim3 grid((tqp + 3) / 4, batch * heads);
-  rb_launch_pdl(sdpa_softmax_fwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)s, (__nv_bfloat16*)p, (__nv_bfloat16*)pd, k_lens, heads, tq,
-                tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset);
+#define SDPA_FWD(LPR, CH)                                                                                                                  \
+  rb_launch_pdl(sdpa_softmax_fwd_vec_kernel<LPR, CH>, dim3(tqp / (4 * (32 / LPR)), batch * heads), dim3(128), 0, stream, (const __nv_bfloat16*)s, \
+                (__nv_bfloat16*)p, (__nv_bfloat16*)pd, k_lens, heads, tq, tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset)
+  if (tkp <= 64) SDPA_FWD(8, 1);
+  else if (tkp <= 128) SDPA_FWD(16, 1);
+  else if (tkp <= 256) SDPA_FWD(32, 1);
+  else if (tkp <= 512) SDPA_FWD(32, 2);
+  else SDPA_FWD(32, 4);
+#undef SDPA_FWD
   return rb_check_launch("sdpa_softmax_fwd_bf16");
 }
 
@@ -303,12 +327,18 @@ RB_EXPORT int rb200_sdpa_softmax_bwd_bf16(const void* p, const void* dpd, void* 
                                           int tkp, int causal, int causal_shift, float p_drop, const long long* seed, const long long* offset,
                                           cudaStream_t stream) {
   if (batch <= 0 || tqp <= 0) return RB_OK;
-  if (tqp % 64 || tkp % 64 || tkp > kVecChunks * 256 || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !(p_drop < 1.f)))) {
-    rb_set_error("sdpa_softmax_bwd_bf16: padded extents must be multiples of 64, keys at most %d (tq %d/%d tk %d/%d)", kVecChunks * 256, tq, tqp, tk, tkp);
+  if (tqp % 64 || tkp % 64 || tkp > kVecMaxKeys || tq > tqp || tk > tkp || (p_drop > 0.f && (!seed || !offset || !(p_drop < 1.f)))) {
+    rb_set_error("sdpa_softmax_bwd_bf16: padded extents must be multiples of 64, keys at most %d (tq %d/%d tk %d/%d)", kVecMaxKeys, tq, tqp, tk, tkp);
     return RB_ERR_ARG;
   }
-  dim3 grid((tqp + 3) / 4, batch * heads);
-  rb_launch_pdl(sdpa_softmax_bwd_vec_kernel, grid, dim3(128), 0, stream, (const __nv_bfloat16*)p, (const __nv_bfloat16*)dpd, (__nv_bfloat16*)ds, k_lens, heads,
-                tq, tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset);
+#define SDPA_BWD(LPR, CH)                                                                                                                  \
+  rb_launch_pdl(sdpa_softmax_bwd_vec_kernel<LPR, CH>, dim3(tqp / (4 * (32 / LPR)), batch * heads), dim3(128), 0, stream, (const __nv_bfloat16*)p, \
+                (const __nv_bfloat16*)dpd, (__nv_bfloat16*)ds, k_lens, heads, tq, tk, tqp, tkp, causal, causal_shift, p_drop, seed, offset)
+  if (tkp <= 64) SDPA_BWD(8, 1);
+  else if (tkp <= 128) SDPA_BWD(16, 1);
+  else if (tkp <= 256) SDPA_BWD(32, 1);
+  else if (tkp <= 512) SDPA_BWD(32, 2);
+  else SDPA_BWD(32, 4);
+#undef SDPA_BWD
   return rb_check_launch("sdpa_softmax_bwd_bf16");
 }

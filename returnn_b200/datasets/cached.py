@@ -110,3 +110,44 @@ class CachedDataset(Dataset):
 
     def get_target_list(self):
         return [k for k in self._keys if k != "data"]
+
+    # -- accessors of the reference class that tools and old configs use ------------------------------------------------
+    def supports_sharding(self) -> bool:
+        return True
+
+    def have_corpus_seq_idx(self) -> bool:
+        return True
+
+    def get_corpus_seq_idx(self, seq_idx: int) -> int:
+        return int(self._order[seq_idx])
+
+    def get_seq_length_nd(self, sorted_seq_idx: int) -> numpy.ndarray:
+        """lengths of all keys as one row (reference: cached.py:593)"""
+        return numpy.asarray(self._seq_lengths[self._order[sorted_seq_idx]])
+
+    def get_seq_start(self, sorted_seq_idx: int) -> numpy.ndarray:
+        """frames of all keys in front of this sequence, in the order of the current epoch (reference: cached.py:616)"""
+        if getattr(self, "_seq_starts_for", None) is not self._order:
+            lens = numpy.asarray(self._seq_lengths)[numpy.asarray(self._order, dtype="int64")] if len(self._order) else numpy.zeros((0, 1), "int64")
+            self._seq_starts = numpy.concatenate([numpy.zeros((1, lens.shape[1]), dtype="int64"), numpy.cumsum(lens, axis=0, dtype="int64")])
+            self._seq_starts_for = self._order
+        return self._seq_starts[sorted_seq_idx]
+
+    def batch_set_generator_cache_whole_epoch(self) -> bool:
+        """whether a batch generator may keep the whole epoch (everything fits into the cache)"""
+        return self.cache_byte_size_total_limit == 0
+
+    def delete(self, nframes: int) -> int:
+        """
+        Frees cached sequences, least recently used first, until at least ``nframes`` frames are gone (reference: cached.py:536).
+
+        :return: frames actually freed
+        """
+        freed = 0
+        while self._lru and freed < nframes:
+            victim = self._lru.pop(0)
+            d = self._cache.pop(victim, None)
+            if d:
+                self._cache_bytes -= sum(a.nbytes for a in d.values())
+                freed += int(self._seq_lengths[victim, 0])
+        return freed

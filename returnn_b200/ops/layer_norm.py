@@ -45,14 +45,24 @@ class _LayerNormFn(torch.autograd.Function):
         dy2 = dy.reshape(rows, n).contiguous()
         dx = torch.empty_like(x2)
         n_part = min(296, max(1, (rows + 31) // 32))
-        part = torch.empty(2, n_part, n, dtype=torch.float32, device=x2.device)
-        dgamma = torch.empty(n, dtype=torch.float32, device=x2.device)
-        dbeta = torch.empty(n, dtype=torch.float32, device=x2.device)
-        fn = _lib.bind("rb200_layer_norm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp])
-        _lib.check(fn(_p(x2), _p(dy2), _p(g), _p(mean), _p(rstd), _p(dx), _p(part), _p(dgamma), _p(dbeta), rows, n, n_part,
-                      1 if x2.dtype == torch.bfloat16 else 0, 1 if g.dtype == torch.bfloat16 else 0, 1 if ctx.rms else 0,
-                      _lib.stream_ptr()), "layer_norm_bwd")
-        _lib.count_launch(2)
+        bf16_x = x2.dtype == torch.bfloat16
+        if bf16_x and n <= 512 and rows > 0 and dy2.dtype == torch.bfloat16:
+            # one kernel: the column sums are added onto zeroed dgamma / dbeta inside the row pass (the form the native encoder uses)
+            sums = torch.zeros(2, n, dtype=torch.float32, device=x2.device)
+            dgamma, dbeta = sums[0], sums[1]
+            fn = _lib.bind("rb200_layer_norm_bwd_ex", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp, _i32, _vp])
+            _lib.check(fn(_p(x2), _p(dy2), _p(g), _p(mean), _p(rstd), _p(dx), None, _p(dgamma), _p(dbeta), rows, n, n_part, 1,
+                          1 if g.dtype == torch.bfloat16 else 0, 1 if ctx.rms else 0, None, 1, _lib.stream_ptr()), "layer_norm_bwd")
+            _lib.count_launch()
+        else:
+            part = torch.empty(2, n_part, n, dtype=torch.float32, device=x2.device)
+            dgamma = torch.empty(n, dtype=torch.float32, device=x2.device)
+            dbeta = torch.empty(n, dtype=torch.float32, device=x2.device)
+            fn = _lib.bind("rb200_layer_norm_bwd", [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i32, _i32, _i32, _i32, _i32, _vp])
+            _lib.check(fn(_p(x2), _p(dy2), _p(g), _p(mean), _p(rstd), _p(dx), _p(part), _p(dgamma), _p(dbeta), rows, n, n_part,
+                          1 if bf16_x else 0, 1 if g.dtype == torch.bfloat16 else 0, 1 if ctx.rms else 0,
+                          _lib.stream_ptr()), "layer_norm_bwd")
+            _lib.count_launch(2)
         return dx.reshape(ctx.shape), dgamma.to(g.dtype), (dbeta.to(g.dtype) if ctx.has_beta else None), None, None
 
 

@@ -557,3 +557,35 @@ def test_postprocessing_dataset_worker_processes():
         assert stream.num_seqs == 8
     finally:
         stream.finish_epoch(free_resources=True)
+
+
+def test_cached_dataset_budget_eviction_and_accessors():
+    from returnn_b200.datasets.cached import CachedDataset
+
+    class Ten(CachedDataset):
+        def __init__(self, **kw):
+            super().__init__(**kw)
+            self._seq_tags = ["s%i" % i for i in range(10)]
+            self._seq_lengths = numpy.array([[3 + i, 1] for i in range(10)])
+            self._keys = ["data", "classes"]
+            self.num_inputs = 2
+            self.num_outputs = {"data": (2, 2), "classes": (5, 1)}
+            self.loads = []
+
+        def _load_seq_data(self, ci):
+            self.loads.append(ci)
+            return {"data": numpy.full((3 + ci, 2), ci, dtype="float32"), "classes": numpy.array([ci % 5], dtype="int32")}
+
+    per_seq = lambda i: (3 + i) * 2 * 4 + 4
+    ds = Ten(cache_byte_size=per_seq(0) + per_seq(1) + per_seq(2) + 8)
+    ds.initialize()
+    ds.init_seq_order(epoch=1)
+    assert ds.num_seqs == 10 and ds.get_seq_start(3).tolist() == [3 + 4 + 5, 3] and ds.get_seq_length_nd(2).tolist() == [5, 1]
+    ds.load_seqs(0, 3)
+    assert ds.is_cached(0, 3) and ds.loads == [0, 1, 2]
+    ds.load_seqs(3, 4)  # needs room: the least recently used sequences leave
+    assert not ds.is_cached(0, 1) and ds.is_cached(3, 4)
+    assert ds.get_data(3, "data").shape == (6, 2) and ds.get_corpus_seq_idx(3) == 3 and ds.get_tag(3) == "s3"
+    freed = ds.delete(1)
+    assert freed >= 1 and ds._cache_bytes >= 0
+    assert not ds.batch_set_generator_cache_whole_epoch()

@@ -36,6 +36,9 @@ def _case(B, H, D, Tq, Tk, causal, with_lens, seed=0):
     (2, 2, 64, 17, 130, False, True),    # cross attention: short queries, long padded keys
     (1, 1, 128, 1, 65, True, False),     # one decoding step against a cache (the query is the last position)
     (2, 8, 64, 128, 192, False, False),  # sizes on tile boundaries
+    (2, 2, 64, 40, 300, False, True),    # key rows of two register chunks per lane
+    (1, 2, 64, 64, 600, False, True),    # ... and of four
+    (2, 2, 64, 200, 200, True, True),    # causal with padding, a whole warp per row
 ])
 def test_sdpa_matches_reference(B, H, D, Tq, Tk, causal, with_lens):
     _case(B, H, D, Tq, Tk, causal, with_lens)
