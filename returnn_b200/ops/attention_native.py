@@ -206,18 +206,14 @@ def sdpa(q, k, v, *, kv_lens, scale, causal, dropout_p):
     """``[B, H, T, D]`` layout of the RF attention functions -> the ``[B, T, H*D]`` kernels of :mod:`returnn_b200.ops.sdpa`"""
     from . import sdpa as _sdpa
 
-    B, H, Tq, D = q.shape
-    Tk = k.shape[2]
-    q3 = q.transpose(1, 2).reshape(B, Tq, H * D)
-    k3 = k.transpose(1, 2).reshape(B, Tk, H * D)
-    v3 = v.transpose(1, 2).reshape(B, Tk, H * D)
     lens = None
     if kv_lens is not None:
         lens = kv_lens
         while lens.dim() > 1:  # given per (batch, head): the heads share the lengths
             lens = lens[..., 0]
-    o = _sdpa.sdpa(q3, k3, v3, num_heads=H, k_lens=lens, causal=causal, scale=scale, dropout_p=dropout_p)
-    return o.view(B, Tq, H, D).transpose(1, 2)
+    # [B, T, H, D] views of the same memory: the kernels take row and head pitches, so the slices of a fused projection are not copied
+    o = _sdpa.sdpa_heads(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), k_lens=lens, causal=causal, scale=scale, dropout_p=dropout_p)
+    return o.transpose(1, 2)
 
 
 def rel_pos_attention(q, k, v, pos, u, vb, lens, *, scale, dropout_p):

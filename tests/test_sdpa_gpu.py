@@ -65,3 +65,36 @@ def test_sdpa_dropout_statistics_and_4d_entry():
     got = A.sdpa(q4, k4, v4, kv_lens=lens, scale=D ** -0.5, causal=False)
     want = A.sdpa_reference(q4.float(), k4.float(), v4.float(), kv_lens=lens, scale=D ** -0.5, causal=False)
     torch.testing.assert_close(got.float(), want, atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("layout", ["per_head_interleaved", "three_blocks"])
+def test_sdpa_heads_reads_slices_of_a_fused_projection_in_place(layout):
+    """q / k / v as strided views of one [B, T, 3 * H * D] tensor (both common column orders): same result and gradients as on copies"""
+    from returnn_b200.ops import sdpa as S
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    B, T, H, D = 3, 75, 4, 64
+    qkv = (torch.randn(B, T, 3 * H * D, device=dev) * 0.7).to(torch.bfloat16).requires_grad_(True)
+    lens = torch.tensor([75, 40, 9], device=dev, dtype=torch.int32)
+
+    def split(x):
+        if layout == "per_head_interleaved":  # [.., H, 3 * D] -> three [.., H, D] slices
+            x4 = x.view(B, T, H, 3 * D)
+            return x4[..., :D], x4[..., D: 2 * D], x4[..., 2 * D:]
+        x4 = x.view(B, T, 3, H, D)
+        return x4[:, :, 0], x4[:, :, 1], x4[:, :, 2]
+
+    q, k, v = split(qkv)
+    assert not q.is_contiguous() and S._rows(q)[0].data_ptr() == q.data_ptr()  # addressed in place
+    w = torch.randn(B, T, H, D, device=dev)
+    out = S.sdpa_heads(q, k, v, k_lens=lens)
+    (out.float() * w).sum().backward()
+    got = qkv.grad.clone()
+    qkv.grad = None
+    qc, kc, vc = (t.contiguous().view(B, T, H * D) for t in split(qkv))
+    ref = S.sdpa_reference(qc, kc, vc, num_heads=H, k_lens=lens).view(B, T, H, D)
+    (ref * w).sum().backward()
+    torch.testing.assert_close(out.float(), ref, atol=2e-2, rtol=2e-2)
+    scale = float(qkv.grad.abs().max())
+    assert float((got.float() - qkv.grad.float()).abs().max()) / scale < 3e-2
