@@ -130,21 +130,44 @@ bn_silu_bwd_a_kernel(const __nv_bfloat16* __restrict__ y, const __nv_bfloat16* _
   const int r_begin = blockIdx.x * rows_per_cta;
   const int r_end = min(n_rows, r_begin + rows_per_cta);
   if (rl < row_lanes) {
-    for (int r = r_begin + rl; r < r_end; r += row_lanes) {
-      F8 yv = load8(y, (long long)r * C + c, 1);
-      F8 dv = load8(dz, (long long)r * C + c, 1);
-      F8 o;
+    // per-channel constants once; then four rows per step with all of their loads issued before the first use (a thread owns few
+    // rows: their load latency is the cost of this kernel)
+    float mu[8], rs[8], ga[8], be[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const float yh = (yv.v[k] - mean[c + k]) * rstd[c + k];
-        const float s = yh * (gamma ? gamma[c + k] : 1.f) + (beta ? beta[c + k] : 0.f);
-        const float sg = sigmoidf_(s);
-        const float d = dv.v[k] * (sg * (1.f + s * (1.f - sg)));
-        o.v[k] = d;
-        a1[k] += d;
-        a2[k] += d * yh;
+    for (int k = 0; k < 8; ++k) {
+      mu[k] = mean[c + k];
+      rs[k] = rstd[c + k];
+      ga[k] = gamma ? gamma[c + k] : 1.f;
+      be[k] = beta ? beta[c + k] : 0.f;
+    }
+    for (int r0 = r_begin + rl; r0 < r_end; r0 += 4 * row_lanes) {
+      F8 yv[4], dv[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = r0 + j * row_lanes;
+        if (r < r_end) {
+          yv[j] = load8(y, (long long)r * C + c, 1);
+          dv[j] = load8(dz, (long long)r * C + c, 1);
+        }
       }
-      store8(ds_out, (long long)r * C + c, o, 1);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = r0 + j * row_lanes;
+        if (r < r_end) {
+          F8 o;
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const float yh = (yv[j].v[k] - mu[k]) * rs[k];
+            const float s = yh * ga[k] + be[k];
+            const float sg = sigmoidf_(s);
+            const float d = dv[j].v[k] * (sg * (1.f + s * (1.f - sg)));
+            o.v[k] = d;
+            a1[k] += d;
+            a2[k] += d * yh;
+          }
+          store8(ds_out, (long long)r * C + c, o, 1);
+        }
+      }
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {

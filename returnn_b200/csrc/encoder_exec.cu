@@ -254,8 +254,8 @@ inline int ln_parts(int n) {
   if (p < 1) p = 1;
   return p;
 }
-inline int bn_tiles_a(int n) {
-  int t = (n + 63) / 64;
+inline int bn_tiles_a(int n) {  // 16 rows per CTA: a few hundred CTAs for the batches of a training step
+  int t = (n + 15) / 16;
   if (t > 592) t = 592;
   if (t < 1) t = 1;
   return t;

@@ -75,7 +75,7 @@ class _ConvModuleFn(torch.autograd.Function):
         dev = dz.device
         dz = dz.contiguous()
         s = _lib.stream_ptr()
-        n_tiles_a = min(592, max(1, (N + 63) // 64))
+        n_tiles_a = min(592, max(1, (N + 15) // 16))
         ds = torch.empty(N, C, dtype=torch.bfloat16, device=dev)
         part_a = torch.empty(n_tiles_a * 2 * C, dtype=torch.float32, device=dev)
         sum_ds = torch.empty(C, dtype=torch.float32, device=dev)
