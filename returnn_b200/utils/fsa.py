@@ -441,3 +441,128 @@ def fast_bw_fsa_staircase(seq_lens, with_loop: bool = False, max_skip=None, star
         state = base + n + 1
     e = numpy.array(edges, dtype="int32").T.reshape(4, -1)
     return FastBaumWelchBatchFsa(e, numpy.zeros(e.shape[1], dtype="float32"), numpy.array(start_end, dtype="int32").T.reshape(2, -1))
+
+
+class Store:
+    """
+    Writes an automaton to disk: Graphviz source (``.dot``, always) and, when the ``dot`` program is installed, the rendering in
+    ``file_format``. Parity: returnn/util/fsa.py:933 (which goes through the ``graphviz`` Python package).
+    """
+
+    def __init__(self, num_states: int, edges: Sequence[Edge], filename: str = "edges", path: str = "./tmp/", file_format: str = "svg"):
+        self.num_states = num_states
+        self.edges = list(edges)
+        self.filename = filename
+        self.path = path
+        self.file_format = file_format
+        self.dot_source: Optional[str] = None
+
+    @staticmethod
+    def label_conversion(edges: Sequence[Edge]) -> List[Edge]:
+        """integer labels back to printable ones where that is unambiguous (characters), everything else as ``str``"""
+        out = []
+        for e in edges:
+            lab = e.label
+            if isinstance(lab, (int, numpy.integer)) and 32 <= int(lab) < 127:
+                lab = "%s(%i)" % (chr(int(lab)), int(lab))
+            out.append(Edge(e.source_state_idx, e.target_state_idx, str(lab), e.weight))
+        return out
+
+    def fsa_to_dot_format(self) -> str:
+        """Graphviz source: left-to-right, state 0 marked as start, the last state as final"""
+        lines = ["digraph fsa {", "  rankdir=LR;", '  node [shape=circle];']
+        for s in range(self.num_states):
+            shape = "doublecircle" if s == self.num_states - 1 else "circle"
+            style = ', style=bold' if s == 0 else ""
+            lines.append('  %i [shape=%s%s];' % (s, shape, style))
+        for e in self.label_conversion(self.edges):
+            label = e.label.replace('"', '\\"')
+            if e.weight:
+                label += " / %g" % e.weight
+            lines.append('  %i -> %i [label="%s"];' % (e.source_state_idx, e.target_state_idx, label))
+        lines.append("}")
+        self.dot_source = "\n".join(lines) + "\n"
+        return self.dot_source
+
+    def save_to_file(self) -> str:
+        """
+        :return: path of the ``.dot`` file (the rendering, if made, lies beside it with the extension ``file_format``)
+        """
+        import os
+        import shutil
+        import subprocess
+
+        if self.dot_source is None:
+            self.fsa_to_dot_format()
+        os.makedirs(self.path, exist_ok=True)
+        dot_path = os.path.join(self.path, self.filename + ".dot")
+        with open(dot_path, "w") as f:
+            f.write(self.dot_source)
+        exe = shutil.which("dot")
+        if exe and self.file_format != "dot":
+            subprocess.run([exe, "-T" + self.file_format, dot_path, "-o", os.path.join(self.path, "%s.%s" % (self.filename, self.file_format))], check=False)
+        return dot_path
+
+
+def main(argv: Optional[Sequence[str]] = None) -> Graph:
+    """
+    ``python -m returnn_b200.utils.fsa --fsa {ctc,asg,hmm} --label_seq "hello world" [--file NAME]``: builds the automaton of one
+    sentence, prints its size and edges, optionally stores it. Parity: returnn/util/fsa.py:1305.
+    """
+    import argparse
+    import time
+
+    ap = argparse.ArgumentParser(description="automaton of one label sequence")
+    ap.add_argument("--fsa", type=str, default="ctc", choices=["ctc", "asg", "hmm"])
+    ap.add_argument("--label_seq", type=str, required=True)
+    ap.add_argument("--file", type=str)
+    ap.add_argument("--path", type=str, default="./tmp/")
+    ap.add_argument("--file_format", type=str, default="svg")
+    ap.add_argument("--asg_repetition", type=int, default=2)
+    ap.add_argument("--num_labels", type=int, default=256)
+    ap.add_argument("--label_conversion", dest="label_conversion", action="store_true")
+    ap.add_argument("--no_label_conversion", dest="label_conversion", action="store_false")
+    ap.set_defaults(label_conversion=False, state_tying_conversion=False, single_state=False, timings=False)
+    ap.add_argument("--depth", type=int, default=6)
+    ap.add_argument("--allo_num_states", type=int, default=3)
+    ap.add_argument("--lexicon", type=str)
+    ap.add_argument("--state_tying", type=str)
+    ap.add_argument("--state_tying_conversion", dest="state_tying_conversion", action="store_true")
+    ap.add_argument("--no_state_tying_conversion", dest="state_tying_conversion", action="store_false")
+    ap.add_argument("--single_state", dest="single_state", action="store_true")
+    ap.add_argument("--no_single_state", dest="single_state", action="store_false")
+    ap.add_argument("--timings", dest="timings", action="store_true")
+    ap.add_argument("--ngram", type=int)
+    args = ap.parse_args(argv)
+    t0 = time.time()
+    fsa = Graph(lemma=args.label_seq)
+    if args.ngram:
+        ngram = Ngram(args.ngram)
+        ngram.run()
+    if args.fsa == "ctc":
+        Ctc(fsa, num_labels=args.num_labels, label_conversion=args.label_conversion).run()
+    elif args.fsa == "asg":
+        Asg(fsa, num_labels=args.num_labels, asg_repetition=args.asg_repetition, label_conversion=args.label_conversion).run()
+    else:
+        assert args.lexicon, "--fsa hmm needs --lexicon (and optionally --state_tying)"
+        hmm = Hmm(fsa, depth=args.depth, allo_num_states=args.allo_num_states, state_tying_conversion=args.state_tying_conversion)
+        hmm.load_lexicon(load_lexicon(args.lexicon))
+        if args.state_tying:
+            hmm.load_state_tying(load_state_tying(args.state_tying))
+        hmm.run()
+    num_states, edges = fsa.num_states, fsa.edges
+    if args.single_state:
+        num_states, edges = Graph.make_single_state_graph(num_states, edges)
+    if args.timings:
+        print("built in %.3f s" % (time.time() - t0))
+    print("%s automaton of %r: %i states, %i edges" % (args.fsa, fsa.lemma, num_states, len(edges)))
+    for e in edges:
+        print(" ", e.as_tuple())
+    if args.file:
+        where = Store(num_states, edges, filename=args.file, path=args.path, file_format=args.file_format).save_to_file()
+        print("stored:", where)
+    return fsa
+
+
+if __name__ == "__main__":
+    main()

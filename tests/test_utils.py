@@ -328,3 +328,58 @@ def test_task_system_pickler_sends_config_functions_by_value(tmp_path):
     sh2.close()
     sh.close()
     assert ts.next_power_of_two(5) == 8 and ts.next_power_of_two(8) == 8
+
+
+def test_fsa_store_and_command_line(tmp_path, capsys):
+    from returnn_b200.utils import fsa as F
+
+    g = F.main(["--fsa", "ctc", "--label_seq", "ab", "--file", "ctc_ab", "--path", str(tmp_path), "--file_format", "dot"])
+    out = capsys.readouterr().out
+    assert "ctc automaton of 'ab': 5 states" in out and g.num_states_ctc == 5
+    dot = (tmp_path / "ctc_ab.dot").read_text()
+    assert dot.startswith("digraph fsa {") and '0 -> 1 [label="a"]' in dot and "4 [shape=doublecircle]" in dot and dot.count("->") == len(g.edges_ctc)
+    g2 = F.main(["--fsa", "asg", "--label_seq", "aab", "--label_conversion", "--single_state"])
+    assert g2.num_states_asg > 0
+    st = F.Store(2, [F.Edge(0, 1, 97, 0.5)])
+    assert 'label="a(97) / 0.5"' in st.fsa_to_dot_format()
+
+
+def test_better_exchook_statement_names_chain_and_threads():
+    import io
+    import sys
+    from returnn_b200.utils import better_exchook as B
+
+    def inner(alpha, table):
+        beta = {"k": [1, 2, 3]}
+        return (alpha +
+                table["missing"] +
+                len(beta))
+
+    def outer():
+        try:
+            inner(41, {"present": 1})
+        except KeyError as exc:
+            raise ValueError("outer failed") from exc
+
+    buf = io.StringIO()
+    try:
+        outer()
+    except ValueError:
+        B.better_exchook(*sys.exc_info(), file=buf, with_color=False, autodebugshell=False)
+    text = buf.getvalue()
+    # both exceptions of the chain, oldest first, joined by the standard sentence
+    assert text.index("KeyError: 'missing'") < text.index("direct cause") < text.index("ValueError: outer failed")
+    # the whole three-line statement and the values of the names in it
+    assert "return (alpha +" in text and 'table["missing"] +' in text and "len(beta))" in text
+    assert "alpha = <local> 41" in text and "table = <local> {'present': 1}" in text and "beta = <local> {'k': [1, 2, 3]}" in text
+    assert "len = " not in text  # builtins are not listed
+    src, first = B.get_source_statement(__file__, inner.__code__.co_firstlineno + 3)
+    assert src.startswith("return (alpha +") and src.endswith("len(beta))") and first == inner.__code__.co_firstlineno + 2
+    assert list(B.iter_names_in_source("f(a.b.c, key=x) + y.z")) == ["f", "a", "a.b", "a.b.c", "x", "y", "y.z"]
+    col = B.Color(True)
+    assert col("x", "red", bold=True) == "\x1b[1;31mx\x1b[0m" and B.Color(False)("x", "red") == "x"
+    out = io.StringIO()
+    B.dump_all_thread_tracebacks(file=out)
+    assert "MainThread" in out.getvalue() and "dump_all_thread_tracebacks" in out.getvalue()
+    lines = B.format_tb(sys._getframe(), limit=1, with_color=False)
+    assert any("test_better_exchook_statement_names_chain_and_threads" in ln for ln in lines)
