@@ -5,7 +5,7 @@ files), :class:`Lexicon` (Bliss XML lexicon) and :class:`PhoneSeqGenerator`.
 """
 
 from __future__ import annotations
-from typing import Any, Callable, Dict, Iterator, List, Optional, Sequence, Union
+from typing import Tuple, Any, Callable, Dict, Iterator, List, Optional, Sequence, Union
 import gzip
 import re
 import os
@@ -303,6 +303,281 @@ class TranslationDataset(CachedDataset2):
 
     def get_data_shape(self, key):
         return []
+
+
+class TranslationFactorsDataset(TranslationDataset):
+    """
+    Parallel text whose words carry extra factors (casing, morphology ...): ``this|u is|l an|l example|u``. Every word of a file has the
+    same number of factors. The first source factor is the key ``data``, the first target factor ``classes``; the further ones get the
+    keys named in ``source_factors`` / ``target_factors`` and need a vocabulary ``<key>.vocab.pkl`` each.
+    Parity: returnn/datasets/lm.py:1895.
+    """
+
+    def __init__(self, source_factors: Union[None, str, Sequence[str]] = None, target_factors: Union[None, str, Sequence[str]] = None,
+                 factor_separator: str = "|", **kwargs):
+        self._source_factors = [source_factors] if isinstance(source_factors, str) else list(source_factors or [])
+        self._target_factors = [target_factors] if isinstance(target_factors, str) else list(target_factors or [])
+        self._factor_separator = factor_separator
+        super().__init__(**kwargs)
+        import pickle
+
+        groups = [("data", self._source_factors)] + ([] if self.source_only else [("classes", self._target_factors)])
+        self._factor_keys: Dict[str, List[str]] = {}
+        for main, extra in groups:
+            self._factor_keys[main] = [main] + extra
+            for k in extra:
+                with open(os.path.join(self.path, "%s.vocab.pkl" % k), "rb") as f:
+                    self._vocabs[k] = pickle.load(f)
+                self._unknown[k] = self._unknown[main]
+                self._add[k] = self._add[main]
+                self.labels[k] = [w for w, _ in sorted(self._vocabs[k].items(), key=lambda kv: kv[1])]
+                self.num_outputs[k] = (max(self._vocabs[k].values()) + 1, 1)
+        self._all_keys = [k for main, _ in groups for k in self._factor_keys[main]]
+
+    def _encode_factors(self, main: str, line: str) -> Dict[str, numpy.ndarray]:
+        keys = self._factor_keys[main]
+        words = line.split()
+        cols: List[List[str]] = [[] for _ in keys]
+        for w in words:
+            parts = w.split(self._factor_separator)
+            assert len(parts) == len(keys), "%s: word %r has %i factors, expected %i (%s)" % (self, w, len(parts), len(keys), ", ".join(keys))
+            for c, part in zip(cols, parts):
+                c.append(part)
+        # the postfix (sentence end etc.) is appended to every factor, as to the main stream
+        return {k: self._encode(k, " ".join(c)) for k, c in zip(keys, cols)}
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        if seq_idx >= len(self._order):
+            return None
+        line = self._order[seq_idx]
+        feats: Dict[str, numpy.ndarray] = {}
+        for main in self._factor_keys:
+            feats.update(self._encode_factors(main, self._lines[main][line]))
+        return DatasetSeq(seq_idx=seq_idx, seq_tag="line-%i" % line, features=feats)
+
+    def get_data_keys(self):
+        return list(self._all_keys)
+
+    def get_target_list(self):
+        return [k for k in self._all_keys if k not in self._factor_keys["data"]]
+
+
+class ConfusionNetworkDataset(TranslationDataset):
+    """
+    Source sentences with weighted alternatives per position (confusion networks):
+    ``__ALT__ we're|0.9997__were|0.0003 a|0.98__EPS|0.02 social|1.0 species|1.0``. Positions are separated by blanks, alternatives by two
+    underscores, a weight follows each word after ``|``; a line without the ``__ALT__`` mark is plain text (one alternative of weight 1
+    per position). Keys: ``sparse_inputs`` (int32 ``[time, max_density]``, unused slots 0), ``sparse_weights`` (float32, unused slots 0)
+    and ``classes``. Parity: returnn/datasets/lm.py:2025.
+    """
+
+    ALT_MARK = "__ALT__"
+
+    def __init__(self, max_density: int = 20, **kwargs):
+        self.density = int(max_density)
+        super().__init__(**kwargs)
+        self._cn_keys = ["sparse_inputs", "sparse_weights"] + ([] if self.source_only else ["classes"])
+        self.num_outputs["sparse_inputs"] = (self.num_outputs["data"][0], 2)
+        self.num_outputs["sparse_weights"] = (self.density, 2)
+        self.labels["sparse_inputs"] = self.labels["data"]
+
+    def _lookup(self, word: str) -> int:
+        v = self._vocabs["data"]
+        if word in v:
+            return v[word]
+        unk = self._unknown["data"]
+        if unk is None:
+            raise KeyError("%s: %r not in the source vocabulary and no unknown_label given" % (self, word))
+        return v[unk]
+
+    def _encode_network(self, line: str):
+        words = line.split()
+        if words and words[0] == self.ALT_MARK:
+            slots = []
+            for pos in words[1:]:
+                arcs = []
+                for arc in pos.split("__"):
+                    w, _, weight = arc.rpartition("|")
+                    assert w, "%s: alternative %r has no weight" % (self, arc)
+                    arcs.append((self._lookup(w), float(weight)))
+                slots.append(arcs)
+        else:
+            slots = [[(self._lookup(w), 1.0)] for w in words]
+        for w in self._add["data"].split():
+            slots.append([(self._lookup(w), 1.0)])
+        ids = numpy.zeros((len(slots), self.density), dtype="int32")
+        weights = numpy.zeros((len(slots), self.density), dtype="float32")
+        for t, arcs in enumerate(slots):
+            assert len(arcs) <= self.density, "%s: %i alternatives at one position, max_density is %i" % (self, len(arcs), self.density)
+            for a, (i, wgt) in enumerate(arcs):
+                ids[t, a] = i
+                weights[t, a] = wgt
+        return ids, weights
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        res = super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        if seq_order is None and seq_list is None:
+            # lengths for the sorted orders: positions, not alternatives
+            n = len(self._lines["data"])
+            self._order = list(self.get_seq_order_for_epoch(epoch=epoch, num_seqs=n, get_seq_len=lambda i: len(self._lines["data"][i].split())))
+            self._num_seqs = len(self._order)
+        return res
+
+    def _collect_single_seq(self, seq_idx: int) -> Optional[DatasetSeq]:
+        if seq_idx >= len(self._order):
+            return None
+        line = self._order[seq_idx]
+        ids, weights = self._encode_network(self._lines["data"][line])
+        feats = {"sparse_inputs": ids, "sparse_weights": weights}
+        if not self.source_only:
+            feats["classes"] = self._encode("classes", self._lines["classes"][line])
+        return DatasetSeq(seq_idx=seq_idx, seq_tag="line-%i" % line, features=feats)
+
+    def get_data_keys(self):
+        return list(self._cn_keys)
+
+    def get_target_list(self):
+        return ["classes"] if not self.source_only else []
+
+    def get_data_dtype(self, key):
+        return "float32" if key == "sparse_weights" else "int32"
+
+    def is_data_sparse(self, key):
+        return key == "classes"
+
+    def get_data_dim(self, key):
+        return self.density if key in ("sparse_inputs", "sparse_weights") else self.num_outputs[key][0]
+
+    def get_data_shape(self, key):
+        return [self.density] if key in ("sparse_inputs", "sparse_weights") else []
+
+
+class AllophoneState:
+    """
+    One HMM state of a context-dependent phone, in RASR's notation ``center{left+right}@i@f.state`` (``@i`` / ``@f``: first / last phone of
+    a word). Hashable; :meth:`index` maps it to a dense integer given the phone inventory. Parity: returnn/datasets/lm.py:882.
+    """
+
+    def __init__(self, id: Optional[str] = None, state: Optional[int] = None):
+        self.id: Optional[str] = id  # centre phone
+        self.context_history: Tuple[str, ...] = ()  # left context, nearest phone last
+        self.context_future: Tuple[str, ...] = ()  # right context, nearest phone first
+        self.boundary = 0  # bit 1: word-initial, bit 2: word-final
+        self.state = state
+        self._attrs = ("id", "context_history", "context_future", "boundary", "state")
+
+    def format(self) -> str:
+        """RASR notation"""
+        s = "%s{%s+%s}" % (self.id, "-".join(self.context_history) or "#", "-".join(self.context_future) or "#")
+        if self.boundary & 1:
+            s += "@i"
+        if self.boundary & 2:
+            s += "@f"
+        if self.state is not None:
+            s += ".%i" % self.state
+        return s
+
+    __repr__ = format
+
+    def copy(self) -> "AllophoneState":
+        """shallow copy"""
+        a = AllophoneState(self.id, self.state)
+        a.context_history, a.context_future, a.boundary = self.context_history, self.context_future, self.boundary
+        return a
+
+    def mark_initial(self):
+        """first phone of a word"""
+        self.boundary |= 1
+
+    def mark_final(self):
+        """last phone of a word"""
+        self.boundary |= 2
+
+    def phone_idx(self, ctx_idx: int, phone_idxs: Dict[str, int]) -> int:
+        """index of the centre phone (``ctx_idx`` 0) or of a context phone (-1, -2 ... left; 1, 2 ... right), 0 meaning "none", phones from 1"""
+        if ctx_idx == 0:
+            p = self.id
+        elif ctx_idx > 0:
+            p = self.context_future[ctx_idx - 1] if ctx_idx - 1 < len(self.context_future) else None
+        else:
+            p = self.context_history[ctx_idx] if -ctx_idx <= len(self.context_history) else None
+        return 0 if p is None else phone_idxs[p] + 1
+
+    def index(self, phone_idxs: Dict[str, int], num_states: int = 3, context_length: int = 1) -> int:
+        """
+        Dense index over (centre, left and right contexts, boundary, state), mixed radix with the phone inventory + 1 ("none") as the
+        base of the phone digits.
+        """
+        assert self.state is not None and 0 <= self.state < num_states
+        base = max(phone_idxs.values()) + 2
+        r = 0
+        for i in range(2 * context_length + 1):
+            ctx = (i + 1) // 2 * (1 if i % 2 else -1)  # 0, 1, -1, 2, -2 ...
+            r = r * base + self.phone_idx(ctx, phone_idxs)
+        r = r * 4 + self.boundary
+        return r * num_states + self.state
+
+    @classmethod
+    def from_index(cls, index: int, phone_ids: Dict[int, str], num_states: int = 3, context_length: int = 1) -> "AllophoneState":
+        """inverse of :meth:`index` (``phone_ids``: index -> phone)"""
+        base = max(phone_ids.keys()) + 2
+        a = cls()
+        a.state = index % num_states
+        index //= num_states
+        a.boundary = index % 4
+        index //= 4
+        digits = []
+        for _ in range(2 * context_length + 1):
+            digits.append(index % base)
+            index //= base
+        digits.reverse()
+        hist: List[Optional[str]] = [None] * context_length
+        fut: List[Optional[str]] = [None] * context_length
+        for i, d in enumerate(digits):
+            ctx = (i + 1) // 2 * (1 if i % 2 else -1)
+            p = phone_ids[d - 1] if d > 0 else None
+            if ctx == 0:
+                a.id = p
+            elif ctx > 0:
+                fut[ctx - 1] = p
+            else:
+                hist[ctx] = p
+        a.context_history = tuple(p for p in hist if p is not None)
+        a.context_future = tuple(p for p in fut if p is not None)
+        return a
+
+    def __hash__(self):
+        return hash(tuple(getattr(self, a) for a in self._attrs))
+
+    def __eq__(self, other):
+        return isinstance(other, AllophoneState) and all(getattr(self, a) == getattr(other, a) for a in self._attrs)
+
+    def __ne__(self, other):
+        return not self == other
+
+
+class StateTying:
+    """
+    RASR state-tying file: one ``<allophone state> <class index>`` per line. Parity: returnn/datasets/lm.py:1197.
+    """
+
+    def __init__(self, state_tying_file: str):
+        self.allo_map: Dict[str, int] = {}  # allophone state notation -> class
+        self.class_map: Dict[int, set] = {}  # class -> allophone states
+        with _open_text(state_tying_file) as f:
+            for line in f:
+                line = line.strip()
+                if not line or line.startswith("#"):
+                    continue
+                allo, cls_idx = line.rsplit(None, 1)
+                idx = int(cls_idx)
+                assert allo not in self.allo_map, "state tying %s: %s listed twice" % (state_tying_file, allo)
+                self.allo_map[allo] = idx
+                self.class_map.setdefault(idx, set()).add(allo)
+        n = max(self.class_map) + 1 if self.class_map else 0
+        missing = [i for i in range(n) if i not in self.class_map]
+        assert not missing, "state tying %s: classes %r have no allophone state" % (state_tying_file, missing[:10])
+        self.num_classes = n
 
 
 class Lexicon:

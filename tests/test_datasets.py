@@ -589,3 +589,76 @@ def test_cached_dataset_budget_eviction_and_accessors():
     freed = ds.delete(1)
     assert freed >= 1 and ds._cache_bytes >= 0
     assert not ds.batch_set_generator_cache_whole_epoch()
+
+
+def _write_translation_fixture(tmp_path, source_lines, target_lines, extra_vocabs=None):
+    import pickle
+
+    def vocab(words):
+        return {w: i for i, w in enumerate(sorted(set(words)))}
+
+    (tmp_path / "source.train").write_text("\n".join(source_lines) + "\n")
+    (tmp_path / "target.train").write_text("\n".join(target_lines) + "\n")
+    for name, v in (extra_vocabs or {}).items():
+        with open(tmp_path / ("%s.vocab.pkl" % name), "wb") as f:
+            pickle.dump(v, f)
+    return vocab
+
+
+def test_translation_factors_dataset(tmp_path):
+    from returnn_b200.datasets.basic import init_dataset
+
+    src = ["this|u is|l an|l example|u", "short|l"]
+    tgt = ["das|u|x ist|l|y", "kurz|l|x"]
+    _write_translation_fixture(tmp_path, src, tgt, extra_vocabs={
+        "source": {"this": 0, "is": 1, "an": 2, "example": 3, "short": 4, "</s>": 5}, "src_case": {"u": 0, "l": 1, "</s>": 2},
+        "target": {"das": 0, "ist": 1, "kurz": 2, "</s>": 3}, "tgt_case": {"u": 0, "l": 1, "</s>": 2}, "tgt_tag": {"x": 0, "y": 1, "</s>": 2}})
+    ds = init_dataset({"class": "TranslationFactorsDataset", "path": str(tmp_path), "file_postfix": "train", "source_factors": "src_case",
+                       "target_factors": ["tgt_case", "tgt_tag"], "source_postfix": " </s>", "target_postfix": " </s>"})
+    ds.init_seq_order(epoch=1)
+    assert ds.get_data_keys() == ["data", "src_case", "classes", "tgt_case", "tgt_tag"] and ds.get_target_list() == ["classes", "tgt_case", "tgt_tag"]
+    ds.load_seqs(0, 2)
+    assert ds.get_data(0, "data").tolist() == [0, 1, 2, 3, 5] and ds.get_data(0, "src_case").tolist() == [0, 1, 1, 0, 2]
+    assert ds.get_data(0, "classes").tolist() == [0, 1, 3] and ds.get_data(0, "tgt_case").tolist() == [0, 1, 2] and ds.get_data(0, "tgt_tag").tolist() == [0, 1, 2]
+    assert ds.get_data(1, "tgt_tag").tolist() == [0, 2] and ds.get_data_dim("tgt_tag") == 3
+
+
+def test_confusion_network_dataset(tmp_path):
+    from returnn_b200.datasets.basic import init_dataset
+
+    src = ["__ALT__ we're|0.75__were|0.25 a|0.9__EPS|0.1 species|1.0", "plain text here"]
+    tgt = ["x y", "z"]
+    _write_translation_fixture(tmp_path, src, tgt, extra_vocabs={
+        "source": {"PAD": 0, "we're": 1, "were": 2, "a": 3, "EPS": 4, "species": 5, "UNK": 6}, "target": {"x": 0, "y": 1, "z": 2}})
+    ds = init_dataset({"class": "ConfusionNetworkDataset", "path": str(tmp_path), "file_postfix": "train", "max_density": 3, "unknown_label": {"data": "UNK"}})
+    ds.init_seq_order(epoch=1)
+    ds.load_seqs(0, 2)
+    assert ds.get_data_keys() == ["sparse_inputs", "sparse_weights", "classes"]
+    ids, w = ds.get_data(0, "sparse_inputs"), ds.get_data(0, "sparse_weights")
+    assert ids.tolist() == [[1, 2, 0], [3, 4, 0], [5, 0, 0]] and w.dtype == numpy.float32
+    numpy.testing.assert_allclose(w, [[0.75, 0.25, 0], [0.9, 0.1, 0], [1, 0, 0]])
+    assert ds.get_data(1, "sparse_inputs")[:, 0].tolist() == [6, 6, 6] and ds.get_data(1, "sparse_weights")[:, 0].tolist() == [1.0, 1.0, 1.0]
+    assert ds.get_data(1, "classes").tolist() == [2] and ds.get_data_shape("sparse_weights") == [3] and not ds.is_data_sparse("sparse_inputs")
+
+
+def test_allophone_state_and_state_tying(tmp_path):
+    from returnn_b200.datasets.lm import AllophoneState, StateTying
+
+    phones = {"a": 0, "b": 1, "sil": 2}
+    a = AllophoneState("a", 1)
+    a.context_history, a.context_future = ("b",), ("sil",)
+    a.mark_initial()
+    assert a.format() == "a{b+sil}@i.1"
+    idx = a.index(phones, num_states=3, context_length=1)
+    back = AllophoneState.from_index(idx, {v: k for k, v in phones.items()}, num_states=3, context_length=1)
+    assert back == a and hash(back) == hash(a) and back.format() == a.format()
+    seen = set()
+    for c in phones:
+        for st in range(3):
+            x = AllophoneState(c, st)
+            seen.add(x.index(phones))
+    assert len(seen) == 9
+    f = tmp_path / "state-tying.txt"
+    f.write_text("a{#+#}@i@f.0 0\na{#+#}@i@f.1 1\nb{a+#}.0 0\n# comment\n")
+    t = StateTying(str(f))
+    assert t.num_classes == 2 and t.allo_map["b{a+#}.0"] == 0 and t.class_map[0] == {"a{#+#}@i@f.0", "b{a+#}.0"}
