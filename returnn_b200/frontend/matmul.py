@@ -64,7 +64,14 @@ def matmul(a: Tensor, b: Tensor, *, reduce: Union[Dim, Sequence[Dim]], use_mask:
 
     a3 = a2.reshape(cshape + [_prod(ao_shape), _prod(r_shape)])
     b3 = b2.reshape(cshape + [_prod(r_shape), _prod(bo_shape)])
-    out = torch.matmul(a3, b3).reshape(cshape + ao_shape + bo_shape)
+    if a3.is_cuda and cshape:
+        # batched products on the own GEMM where its shape rules hold (ops/bmm.py), torch.matmul otherwise
+        from ..ops import bmm as _bmm
+
+        bt = _prod(cshape)
+        out = _bmm.bmm(a3.reshape(bt, a3.shape[-2], a3.shape[-1]), b3.reshape(bt, b3.shape[-2], b3.shape[-1])).reshape(cshape + ao_shape + bo_shape)
+    else:
+        out = torch.matmul(a3, b3).reshape(cshape + ao_shape + bo_shape)
     out_dims = common + a_only + b_only
     fd = None
     if b_only and b.feature_dim in b_only:

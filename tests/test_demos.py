@@ -38,3 +38,19 @@ def test_forward_task_and_priors(tmp_path):
     assert proc.returncode == 0, out[-3000:]
     vals = [float(x) for x in prior_file.read_text().split()]
     assert len(vals) == 2 and abs(sum(2.718281828 ** v for v in vals) - 1.0) < 1e-3
+
+
+@pytest.mark.parametrize("script", ["demo-sprint-interface.py", "demo-push-to-webserver.py"])
+def test_demo_scripts_run(script):
+    """the stand-alone demo scripts (producer-fed dataset through a child process; HTTP client against an in-process server)"""
+    import os
+    import subprocess
+    import sys
+
+    demos = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "demos")
+    res = subprocess.run([sys.executable, script], cwd=demos, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    if "sprint" in script:
+        assert "epoch 2 seq 4" in res.stdout and "data (" in res.stdout
+    else:
+        assert "output 'output': (7, 2)" in res.stdout

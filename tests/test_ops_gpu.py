@@ -299,3 +299,47 @@ def test_layer_norm_bwd_accumulating_kernel_matches_fp32(rows, n, with_res):
     scale = max(1.0, rows ** 0.5)
     torch.testing.assert_close(dg - dg0, gf.grad, atol=2e-3 * scale, rtol=1e-3)
     torch.testing.assert_close(db - db0, bias.grad, atol=2e-3 * scale, rtol=1e-3)
+
+
+@gpu
+@pytest.mark.parametrize("bt,m,k,n", [(6, 128, 64, 72), (3, 64, 192, 256), (1, 37, 40, 24), (5, 70, 64, 64)])
+def test_batched_matmul_on_own_gemm(bt, m, k, n):
+    """ops.bmm (what rf.matmul runs for batched bf16 products): result and both gradients against fp32 torch; shapes outside its rules fall back"""
+    from returnn_b200.ops import bmm as B, gemm
+
+    torch.manual_seed(bt * 1000 + m)
+    a = (torch.randn(bt, m, k, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn(bt, k, n, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    own = B.supported(a, b)
+    assert own == (bt == 1 or (k % 64 == 0 and m % 64 == 0))
+    launches0 = __import__("returnn_b200.ops._lib", fromlist=["x"]).launch_count()
+    c = B.bmm(a, b)
+    w = torch.randn(bt, m, n, device="cuda")
+    (c.float() * w).sum().backward()
+    gemm.check_status()
+    launches = __import__("returnn_b200.ops._lib", fromlist=["x"]).launch_count() - launches0
+    assert launches == (3 if own else 0)
+    ga, gb = a.grad.float().clone(), b.grad.float().clone()
+    af, bf_ = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    ref = torch.matmul(af, bf_)
+    (ref * w).sum().backward()
+    torch.testing.assert_close(c.float(), ref, atol=0.06, rtol=0.02)
+    for g, r in ((ga, af.grad), (gb, bf_.grad)):
+        assert float((g - r).abs().max()) / (float(r.abs().max()) + 1e-6) < 0.02
+
+
+@gpu
+def test_rf_matmul_batched_uses_own_gemm():
+    import returnn_b200.frontend as rf
+    from returnn_b200.tensor import Tensor, Dim
+    from returnn_b200.ops import _lib
+
+    b_, h, t, d = Dim(2, name="b"), Dim(4, name="h"), Dim(128, name="t"), Dim(64, name="d")
+    t2 = Dim(192, name="t2")
+    q = Tensor("q", dims=[b_, h, t, d], dtype="bfloat16", raw_tensor=torch.randn(2, 4, 128, 64, device="cuda").to(torch.bfloat16))
+    k = Tensor("k", dims=[b_, h, t2, d], dtype="bfloat16", raw_tensor=torch.randn(2, 4, 192, 64, device="cuda").to(torch.bfloat16))
+    n0 = _lib.launch_count()
+    e = rf.matmul(q, k, reduce=d)
+    assert _lib.launch_count() == n0 + 1 and e.dims == (b_, h, t, t2)
+    ref = torch.matmul(q.raw_tensor.float(), k.raw_tensor.float().transpose(-1, -2))
+    torch.testing.assert_close(e.raw_tensor.float(), ref, atol=0.1, rtol=0.02)
