@@ -83,6 +83,43 @@ def _batch_chunks(x: torch.Tensor, lens: Optional[torch.Tensor], w_rec: torch.Te
     return out
 
 
+def _padded_hidden(x: torch.Tensor, w_rec: torch.Tensor) -> int:
+    """
+    The persistent recurrence kernels want a hidden size that is a multiple of 128. Other sizes are run zero-padded: units whose weights,
+    bias and initial state are zero stay exactly zero (their candidate is tanh(0) = 0, so the cell never moves and h = o * tanh(0) = 0),
+    so the first H units compute the same function, at the cost of the extra units, and still far below the per-step executor.
+
+    :return: padded size to use, or 0 when the size is fine as it is or the padded problem does not fit the kernels either
+    """
+    from . import lstm_native as _n
+
+    H = w_rec.shape[1]
+    if H % 128 == 0 or x.shape[0] == 0:
+        return 0
+    Hp = -(-H // 128) * 128
+    B = x.shape[1]
+    if B > PERSIST_MAX_ROWS * PERSIST_MAX_CHUNKS:
+        return 0
+    per = -(-B // (-(-B // PERSIST_MAX_ROWS)))
+    lib_ok = _n.available(x) and x.shape[-1] % 8 == 0
+    if not lib_ok:
+        return 0
+    from . import _lib
+    import ctypes
+
+    fn = _lib.bind("rb200_blstm_supported", [ctypes.c_int, ctypes.c_int, ctypes.c_int])
+    return Hp if fn(int(x.shape[0]), int(per), int(Hp)) else 0
+
+
+def _pad_params(w_ff, w_rec, bias, H: int, Hp: int):
+    """gate-wise zero padding: [4H, in] -> [4Hp, in], [4H, H] -> [4Hp, Hp], [4H] -> [4Hp]"""
+    F = torch.nn.functional
+    w_ff_p = F.pad(w_ff.reshape(4, H, -1), (0, 0, 0, Hp - H)).reshape(4 * Hp, -1)
+    w_rec_p = F.pad(w_rec.reshape(4, H, H), (0, Hp - H, 0, Hp - H)).reshape(4 * Hp, Hp)
+    bias_p = F.pad(bias.reshape(4, H), (0, Hp - H)).reshape(4 * Hp) if bias is not None else None
+    return w_ff_p, w_rec_p, bias_p
+
+
 def _join_chunks(outs, T: int):
     """(y [t_c, b_c, H], h, c) per chunk -> one (y [T, B, H], h, c); frames beyond a chunk's own length are zero"""
     ys = [torch.nn.functional.pad(y, (0, 0, 0, 0, 0, T - y.shape[0])) if y.shape[0] < T else y for y, _h, _c in outs]
@@ -99,6 +136,12 @@ def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_re
     if x.is_cuda:
         from . import lstm_native as _n
 
+        Hp = _padded_hidden(x, w_rec)
+        if Hp:
+            H = w_rec.shape[1]
+            pad = (0, Hp - H)
+            y, h, c = lstm(x, lens, *_pad_params(w_ff, w_rec, bias, H, Hp), torch.nn.functional.pad(h0, pad), torch.nn.functional.pad(c0, pad), reverse=reverse)
+            return y[..., :H], h[..., :H], c[..., :H]
         if _n.available(x) and _n.supports(x, w_rec):
             chunks = _batch_chunks(x, lens, w_rec)
             if chunks:
@@ -150,6 +193,14 @@ def blstm(x: torch.Tensor, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h
     if x.is_cuda:
         from . import lstm_native as _n
 
+        Hp = _padded_hidden(x, fw[1]) if fw[1].shape == bw[1].shape else 0
+        if Hp:
+            H = fw[1].shape[1]
+            pad = (0, Hp - H)
+            P = torch.nn.functional.pad
+            (yf, hf, cf), (yb, hb, cb) = blstm(x, lens, _pad_params(*fw, H, Hp), _pad_params(*bw, H, Hp), P(h0_fw, pad), P(c0_fw, pad), P(h0_bw, pad),
+                                               P(c0_bw, pad))
+            return (yf[..., :H], hf[..., :H], cf[..., :H]), (yb[..., :H], hb[..., :H], cb[..., :H])
         if _n.blstm_supported(x, fw[1], bw[1]):
             return _n.blstm(x, lens, fw, bw, h0_fw, c0_fw, h0_bw, c0_bw)
         chunks = _batch_chunks(x, lens, fw[1], bw[1])

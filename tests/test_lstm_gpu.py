@@ -126,3 +126,44 @@ def test_blstm_large_batch_runs_in_chunks_of_the_persistent_kernel(T, B, I, H):
     yr, hr, cr = L.lstm_reference(x, lens, *fw, states[0], states[1], reverse=True)
     torch.testing.assert_close(y.float(), yr, atol=0.05, rtol=0.03)
     torch.testing.assert_close(c.float(), cr, atol=0.05, rtol=0.03)
+
+
+@gpu
+@pytest.mark.parametrize("T,B,I,H", [(20, 10, 32, 100), (15, 60, 64, 320)])
+def test_lstm_hidden_sizes_off_the_kernel_grid_run_zero_padded(T, B, I, H):
+    """hidden sizes that are not multiples of 128 go through the persistent kernels zero-padded: same function and gradients"""
+    from returnn_b200.ops import lstm as L, gemm
+
+    torch.manual_seed(4)
+    dev = "cuda"
+    x = (torch.randn(T, B, I, device=dev) * 0.5).requires_grad_(True)
+
+    def params():
+        return [(torch.randn(4 * H, I, device=dev) * 0.2).requires_grad_(True), (torch.randn(4 * H, H, device=dev) * 0.15).requires_grad_(True),
+                (torch.randn(4 * H, device=dev) * 0.1).requires_grad_(True)]
+
+    fw, bw = params(), params()
+    states = [(torch.randn(B, H, device=dev) * 0.3).requires_grad_(True) for _ in range(4)]
+    lens = torch.sort(torch.randint(1, T + 1, (B,)), descending=True).values
+    lens[0] = T
+    assert L._padded_hidden(x, fw[1]) == -(-H // 128) * 128
+    wts = [torch.randn(T, B, H, device=dev) for _ in range(2)] + [torch.randn(B, H, device=dev) for _ in range(4)]
+    leaves = [x] + fw + bw + states
+    (yf, hf, cf), (yb, hb, cb) = L.blstm(x, lens, tuple(fw), tuple(bw), *states)
+    outs = (yf, yb, hf, cf, hb, cb)
+    assert yf.shape == (T, B, H) and cf.shape == (B, H)
+    sum((o.float() * w).sum() for o, w in zip(outs, wts)).backward()
+    gemm.check_status()
+    got = [t.grad.clone() for t in leaves]
+    for t in leaves:
+        t.grad = None
+    yfr, hfr, cfr = L.lstm_reference(x, lens, *fw, states[0], states[1], reverse=False)
+    ybr, hbr, cbr = L.lstm_reference(x, lens, *bw, states[2], states[3], reverse=True)
+    sum((o * w).sum() for o, w in zip((yfr, ybr, hfr, cfr, hbr, cbr), wts)).backward()
+    for o, r in zip(outs, (yfr, ybr, hfr, cfr, hbr, cbr)):
+        torch.testing.assert_close(o.float(), r, atol=0.05, rtol=0.03)
+    for g, t in zip(got, leaves):
+        scale = float(t.grad.abs().max()) + 1e-6
+        assert float((g.float() - t.grad).abs().max()) / scale < 0.06
+    y, h, c = L.lstm(x, lens, *fw, states[0], states[1])
+    torch.testing.assert_close(y.float(), yfr, atol=0.05, rtol=0.03)
