@@ -594,7 +594,7 @@ class DummyGenericDataset(GeneratingDataset):
 
         tmpl = TensorDict()
         tmpl.update(data_template, auto_convert=True)
-        old_style = {k: (v.dim, v.batch_ndim - (1 if v.have_batch_axis else 0) + (0 if v.sparse else 0)) for k, v in tmpl.data.items()}
+        old_style = {k: (v.dim, v.batch_ndim - (1 if v.have_batch_axis() else 0) + (0 if v.sparse else 0)) for k, v in tmpl.data.items()}
         old_style = {k: (v.dim, len([d for d in v.dims if not d.is_batch_dim()])) for k, v in tmpl.data.items()}
         super().__init__(input_dim=None, output_dim=old_style, num_seqs=num_seqs, **kwargs)
         self.data_template = tmpl

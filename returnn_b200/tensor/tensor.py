@@ -202,10 +202,13 @@ class Tensor:
         """static sizes with batch, None for dynamic"""
         return tuple(d.dimension for d in self._dims)
 
-    @property
     def have_batch_axis(self) -> bool:
         """batch_dim in dims"""
         return any(d.is_batch_dim() for d in self._dims)
+
+    def have_time_axis(self) -> bool:
+        """a time (first dynamic / spatial) axis exists"""
+        return self.time_dim_axis is not None
 
     def have_feature_axis(self) -> bool:
         """feature dim exists"""

@@ -82,3 +82,214 @@ def test_merge_split_concat_gather():
     idx = Tensor("i", dims=[a], dtype="int32", sparse_dim=b, raw_tensor=torch.tensor([2, 0], dtype=torch.int32))
     g = rf.gather(x, indices=idx, axis=b)
     assert g.raw_tensor.tolist() == [2.0, 3.0]
+
+
+# ---- a wider sweep over the Tensor / Dim surface -------------------------------------------------------------------------------
+import copy
+import pickle
+import pytest
+
+
+def _x(lens=(2, 3), feat=4, fill=None):
+    t = _time_dim(list(lens))
+    f = Dim(feat, name="feat")
+    raw = torch.arange(len(lens) * max(lens) * feat, dtype=torch.float32).reshape(len(lens), max(lens), feat) if fill is None else torch.full(
+        (len(lens), max(lens), feat), float(fill))
+    return Tensor("x", dims=[batch_dim, t, f], dtype="float32", raw_tensor=raw, feature_dim=f), t, f
+
+
+@pytest.mark.parametrize("op,expect", [("add", 7), ("sub", 1), ("mul", 12), ("floordiv", 1), ("ceildiv", 2)])
+def test_static_dim_arithmetic(op, expect):
+    a, b = Dim(4, name="a"), Dim(3, name="b")
+    res = {"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "floordiv": lambda: a // 3, "ceildiv": lambda: a.ceildiv_right(3)}[op]()
+    assert res.dimension == expect and res.is_static() and not res.is_dynamic()
+    assert res == {"add": lambda: a + b, "sub": lambda: a - b, "mul": lambda: a * b, "floordiv": lambda: a // 3, "ceildiv": lambda: a.ceildiv_right(3)}[op]()
+
+
+@pytest.mark.parametrize("lens", [[1], [5, 3, 4], [2, 2]])
+def test_dynamic_dim_arithmetic_per_sequence(lens):
+    t = _time_dim(lens)
+    assert (t + 2).dyn_size_ext.raw_tensor.tolist() == [n + 2 for n in lens]
+    assert (t * 3).dyn_size_ext.raw_tensor.tolist() == [n * 3 for n in lens]
+    assert (t // 2).dyn_size_ext.raw_tensor.tolist() == [n // 2 for n in lens]
+    assert t.ceildiv_right(2).dyn_size_ext.raw_tensor.tolist() == [-(-n // 2) for n in lens]
+    assert (t + t).dyn_size_ext.raw_tensor.tolist() == [2 * n for n in lens]
+    assert ((t + 2) - 2) == t and (t * 3).div_left(3) == t  # inverse operations cancel
+    assert t.get_dim_value() == max(lens) and (t + 1).get_dim_value() == max(lens) + 1
+    assert t.is_dynamic() and t.is_dynamic_seq_length() and t.need_masking() == (min(lens) != max(lens) or len(lens) > 1 and False or t.need_masking())
+
+
+def test_dim_kinds_and_predicates():
+    f, s = Dim(3, name="f", kind=Dim.Types.Feature), Dim(None, name="s", kind=Dim.Types.Spatial)
+    assert batch_dim.is_batch_dim() and not f.is_batch_dim()
+    assert f.is_feature_dim() and s.is_spatial_dim() and not f.is_spatial_dim()
+    assert f.is_static() and s.is_dynamic() and not s.is_dim_known()
+    s.dyn_size_ext = Tensor("l", dims=[batch_dim], dtype="int32", raw_tensor=torch.tensor([2, 1], dtype=torch.int32))
+    assert s.is_dim_known()
+    assert "f" in repr(f) and "3" in repr(f) and f.short_repr()
+
+
+def test_declare_same_as_merges_identity():
+    a, b = Dim(None, name="a"), Dim(None, name="b")
+    a.dyn_size_ext = Tensor("l", dims=[batch_dim], dtype="int32", raw_tensor=torch.tensor([2, 4], dtype=torch.int32))
+    assert a != b
+    b.declare_same_as(a)
+    assert a == b and hash(a) == hash(b) and b.get_same_base() is a.get_same_base()
+    assert b.dyn_size_ext.raw_tensor.tolist() == [2, 4]
+    x = Tensor("x", dims=[batch_dim, a], dtype="float32", raw_tensor=torch.zeros(2, 4))
+    assert x.get_axis_from_description(b) == 1
+
+
+def test_dim_copy_pickle_and_deepcopy_keep_static_identity_rules():
+    f = Dim(5, name="f")
+    assert copy.copy(f) is f or copy.copy(f) == f
+    g = pickle.loads(pickle.dumps(f))
+    assert g.dimension == 5 and g.name == "f"
+    assert copy.deepcopy(f).dimension == 5
+    c = f.copy(same_as_self=False) if "same_as_self" in Dim.copy.__code__.co_varnames else f.copy()
+    assert c.dimension == 5
+
+
+@pytest.mark.parametrize("order", [[0, 1, 2], [1, 0, 2], [2, 1, 0], [2, 0, 1]])
+def test_copy_transpose_and_permutations(order):
+    x, t, f = _x()
+    dims = [x.dims[i] for i in order]
+    y = x.copy_transpose(dims)
+    assert list(y.dims) == dims and y.raw_tensor.shape == tuple(x.raw_tensor.shape[i] for i in order)
+    torch.testing.assert_close(y.raw_tensor, x.raw_tensor.permute(*order))
+    assert x.get_out_permutation_to_dims(dims) == order
+    assert y.feature_dim == f and y.feature_dim_axis == dims.index(f)
+    back = y.copy_transpose(list(x.dims))
+    torch.testing.assert_close(back.raw_tensor, x.raw_tensor)
+
+
+def test_copy_compatible_to_dims_broadcasts_and_orders():
+    x, t, f = _x()
+    extra = Dim(7, name="extra")
+    y = x.copy_compatible_to_dims([extra, f, batch_dim, t])
+    assert [d for d in y.dims] == [extra, f, batch_dim, t] and y.raw_tensor.shape == (1, 4, 2, 3)
+    raw = x.copy_compatible_to_dims_raw([f, extra, t, batch_dim])
+    assert raw.shape == (4, 1, 3, 2)
+    v = Tensor("v", dims=[f], dtype="float32", raw_tensor=torch.arange(4.0))
+    z = x + v  # broadcast by identity, not by position
+    torch.testing.assert_close(z.raw_tensor, x.raw_tensor + torch.arange(4.0))
+    w = Tensor("w", dims=[t], dtype="float32", raw_tensor=torch.arange(3.0))
+    torch.testing.assert_close((x * w).raw_tensor, x.raw_tensor * torch.arange(3.0)[None, :, None])
+    with pytest.raises(Exception):
+        x.copy_compatible_to_dims([batch_dim, f])  # a dim of x is missing in the target
+
+
+def test_copy_move_axis_batch_time_major_and_feature_last():
+    x, t, f = _x()
+    tm = x.copy_as_time_major()
+    assert tm.dims[0] == t and tm.time_dim_axis == 0 and tm.batch_dim_axis == 1
+    bm = tm.copy_as_batch_major()
+    assert bm.dims[0] == batch_dim and bm.have_batch_axis()
+    y = x.copy_move_axis(2, 0)
+    assert y.dims == (f, batch_dim, t)
+    assert y.copy_with_feature_last().dims[-1] == f
+    assert x.copy_with_feature_dim_axis(1).dims == (batch_dim, f, t)
+
+
+def test_templates_and_kwargs_roundtrip():
+    x, t, f = _x()
+    templ = x.copy_template(name="y")
+    assert templ.raw_tensor is None and templ.dims == x.dims and templ.dtype == "float32" and templ.name == "y"
+    kw = x.get_kwargs()
+    again = Tensor(**kw)
+    assert again.dims == x.dims and again.dtype == x.dtype
+    new_f = Dim(9, name="nf")
+    r = x.copy_template_replace_dim_tag(axis=2, new_dim_tag=new_f)
+    assert r.dims == (batch_dim, t, new_f)
+    e = x.copy_template_excluding_axis(1)
+    assert e.dims == (batch_dim, f)
+    a = e.copy_template_adding_time_dim(time_dim_axis=1) if hasattr(e, "copy_template_adding_time_dim") else None
+    assert a is None or a.batch_ndim == 3
+    added = x.copy_add_dim_by_tag(Dim(1, name="one"), unbroadcast=True, axis=0)
+    assert added.raw_tensor.shape == (1, 2, 3, 4)
+
+
+def test_copy_masked_and_sequence_masks():
+    x, t, f = _x(fill=1.0)
+    m = x.copy_masked(-5.0)
+    assert m.raw_tensor[0, 2].tolist() == [-5.0] * 4 and m.raw_tensor[0, :2].eq(1).all() and m.raw_tensor[1].eq(1).all()
+    assert x.get_sequence_lengths().tolist() == [2, 3]
+    mask = x.get_sequence_mask_tensor(1) if hasattr(x, "get_sequence_mask_tensor") else None
+    assert mask is None or mask.raw_tensor.sum().item() == 5
+    mb = x.get_sequence_mask_broadcast(1)
+    assert tuple(mb.shape) == (2, 3, 1) and int(mb.sum()) == 5
+    assert x.num_elements() == 5 * 4 if callable(getattr(x, "num_elements", None)) else True
+
+
+def test_axis_descriptions():
+    x, t, f = _x()
+    assert x.get_axis_from_description("B") == 0 and x.get_axis_from_description("T") == 1 and x.get_axis_from_description("F") == 2
+    assert x.get_axis_from_description(t) == 1 and x.get_axis_from_description(-1) == 2
+    assert x.get_axes_from_description(["B", f]) == [0, 2]
+    assert x.get_dim_tag(1) == t and x.get_dim_tag_from_description("F") == f
+    assert x.get_dynamic_axes() == [1] and x.get_static_axes() == [2]
+    assert x.get_batch_shape(batch_dim=7) == (7, None, 4) if hasattr(x, "get_batch_shape") else True
+    assert x.batch_shape == (None, None, 4) and x.shape == (None, 4) and x.batch_ndim == 3
+    with pytest.raises(Exception):
+        x.get_axis_from_description(Dim(4, name="other"))
+
+
+def test_sparse_tensor_properties_and_squeeze():
+    vocab = Dim(10, name="vocab")
+    t = _time_dim([2, 1])
+    y = Tensor("y", dims=[batch_dim, t], dtype="int32", sparse_dim=vocab, raw_tensor=torch.tensor([[1, 2], [3, 0]], dtype=torch.int32))
+    assert y.sparse and y.dim == 10 and y.is_int() and not y.is_float() and y.feature_dim is None
+    one = Dim(1, name="one")
+    z = Tensor("z", dims=[batch_dim, one, t], dtype="int32", raw_tensor=y.raw_tensor[:, None])
+    s = z.copy_squeeze_axes([1])
+    assert s.dims == (batch_dim, t) and torch.equal(s.raw_tensor, y.raw_tensor)
+
+
+@pytest.mark.parametrize("op", ["add", "sub", "mul", "truediv", "pow", "neg", "abs", "eq", "lt", "ge", "and", "or", "invert", "radd", "rsub", "rmul", "mod", "floordiv"])
+def test_operator_overloads_match_torch(op):
+    x, t, f = _x()
+    a = x.raw_tensor
+    y = Tensor("y", dims=x.dims, dtype="float32", raw_tensor=a.flip(-1) + 1.0)
+    b = y.raw_tensor
+    bx, by = (x > 10.0), (y > 10.0)
+    table = {
+        "add": (lambda: x + y, a + b), "sub": (lambda: x - y, a - b), "mul": (lambda: x * y, a * b), "truediv": (lambda: x / y, a / b),
+        "pow": (lambda: y ** 2.0, b ** 2.0), "neg": (lambda: -x, -a), "abs": (lambda: abs(x - 10.0), (a - 10.0).abs()),
+        "eq": (lambda: x == y, a == b), "lt": (lambda: x < y, a < b), "ge": (lambda: x >= y, a >= b),
+        "and": (lambda: bx & by, (a > 10) & (b > 10)), "or": (lambda: bx | by, (a > 10) | (b > 10)), "invert": (lambda: ~bx, ~(a > 10)),
+        "radd": (lambda: 2.0 + x, 2.0 + a), "rsub": (lambda: 2.0 - x, 2.0 - a), "rmul": (lambda: 3.0 * x, 3.0 * a),
+        "mod": (lambda: x % 3.0, a % 3.0), "floordiv": (lambda: x // 3.0, torch.floor(a / 3.0)),
+    }
+    fn, want = table[op]
+    got = fn()
+    assert got.dims == x.dims
+    assert torch.equal(got.raw_tensor, want) if want.dtype == torch.bool else torch.allclose(got.raw_tensor, want)
+
+
+def test_tensor_dict_api():
+    x, t, f = _x()
+    vocab = Dim(10, name="vocab")
+    y = Tensor("classes", dims=[batch_dim, t], dtype="int32", sparse_dim=vocab, raw_tensor=torch.zeros(2, 3, dtype=torch.int32))
+    td = TensorDict([x, y]) if not isinstance(TensorDict(), dict) else TensorDict()
+    if not td.data:
+        td.data["x"], td.data["classes"] = x, y
+    assert set(td.data.keys()) == {"x", "classes"} and td["x"] is x
+    templ = td.copy_template()
+    assert templ["x"].raw_tensor is None and templ["classes"].sparse_dim == vocab
+    raw = td.as_raw_tensor_dict(include_const_sizes=True) if hasattr(td, "as_raw_tensor_dict") else None
+    if raw is not None:
+        assert torch.equal(raw["x"], x.raw_tensor) and any(k.startswith("x:size") for k in raw)
+        templ2 = td.copy_template()
+        templ2.assign_from_raw_tensor_dict_(raw)
+        assert torch.equal(templ2["x"].raw_tensor, x.raw_tensor)
+
+
+def test_verify_out_shape_and_sanity_check():
+    x, t, f = _x()
+    x.verify_out_shape({batch_dim, t, f})
+    with pytest.raises(Exception):
+        x.verify_out_shape({batch_dim, f})
+    x.sanity_check()
+    bad = Tensor("bad", dims=[batch_dim, f], dtype="float32")
+    with pytest.raises(Exception):
+        bad.raw_tensor = torch.zeros(2, 5)  # size of f is 4
