@@ -109,8 +109,13 @@ __device__ __forceinline__ void multimem_st(float* addr, float4 v) {
 // With `adam` set (adam.p != null) the kernel first runs this rank's AdamW update over its whole parameter arena (p.bufs[rank] is
 // then the parameter arena, not the gradient arena), and only then averages: the entry barrier doubles as "every rank has
 // finished its update". This is the parameter-averaging mode (local steps, sync every N): update + average in one launch.
-__global__ void __launch_bounds__(kThreads)
+// T threads per CTA. The 128-thread form is capped at 80 registers: four such warps fit into what a resident GEMM CTA of the
+// backward pass (18 warps x 96 registers, ~200 KB shared memory) leaves free on an SM, so a bucket reduction running next to the
+// backward pass does not keep the CTAs of the next persistent GEMM off its SMs.
+template <int U, int T>
+__global__ void __launch_bounds__(T, T == 128 ? 6 : 1)
 fused_allreduce_kernel(const ArParams p, const AdamwArgs adam) {
+  constexpr int kThreads = T;  // shadows the file-level default inside this kernel
   __shared__ int sh_fail;
   __shared__ float sh_red[kThreads / 32];
   if (threadIdx.x == 0) sh_fail = 0;
@@ -129,9 +134,10 @@ fused_allreduce_kernel(const ArParams p, const AdamwArgs adam) {
   const long long s1 = p.interleaved ? n4 : (s0 + per < n4 ? s0 + per : n4);
   float ssq = 0.f;
   const long long stride = p.interleaved ? grid_threads * p.world : grid_threads;
-  // four float4 per thread and iteration: all loads of an iteration are issued before the first use, which keeps enough bytes
-  // in flight to cover the NVLink round trip
-  constexpr int U = 4;
+  // U float4 per thread and iteration: all loads of an iteration are issued before the first use, which keeps enough bytes in
+  // flight to cover the NVLink round trip. A bucket reduction overlaps the backward pass and takes the SMs of its CTAs away from
+  // it for its whole duration (it is bound by the link, not by the SM), so the deeper unroll with FEWER CTAs is the better
+  // neighbour: the bytes in flight per GPU stay the same, on a quarter of the SMs.
   for (long long i0 = s0 + (long long)blockIdx.x * kThreads + threadIdx.x; i0 < s1; i0 += U * stride) {
     float4 acc[U];
     if (p.mc) {
@@ -236,7 +242,24 @@ RB_EXPORT int rb200_fused_allreduce(const long long* bufs, const long long* flag
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
   AdamwArgs none;
   memset(&none, 0, sizeof(none));
-  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p, none);
+  static int unroll = 0, threads = 0;
+  if (!unroll) {
+    const char* e = getenv("RETURNN_B200_ALLREDUCE_UNROLL");
+    unroll = e ? atoi(e) : 4;
+    if (unroll != 4 && unroll != 8 && unroll != 16) unroll = 4;
+    const char* t = getenv("RETURNN_B200_ALLREDUCE_THREADS");
+    threads = t && atoi(t) == 128 ? 128 : kThreads;
+  }
+  if (threads == 128) {
+    if (unroll == 4) fused_allreduce_kernel<4, 128><<<blocks, 128, 0, stream>>>(p, none);
+    else fused_allreduce_kernel<8, 128><<<blocks, 128, 0, stream>>>(p, none);
+  } else if (unroll == 16) {
+    fused_allreduce_kernel<16, kThreads><<<blocks, kThreads, 0, stream>>>(p, none);
+  } else if (unroll == 8) {
+    fused_allreduce_kernel<8, kThreads><<<blocks, kThreads, 0, stream>>>(p, none);
+  } else {
+    fused_allreduce_kernel<4, kThreads><<<blocks, kThreads, 0, stream>>>(p, none);
+  }
   return rb_check_launch("fused_allreduce");
 }
 
@@ -274,7 +297,7 @@ RB_EXPORT int rb200_fused_adamw_param_avg(const long long* bufs, const long long
   }
   if (blocks < 1) blocks = 1;
   if (blocks > kMaxBlocks) blocks = kMaxBlocks;
-  fused_allreduce_kernel<<<blocks, kThreads, 0, stream>>>(p, a);
+  fused_allreduce_kernel<4, kThreads><<<blocks, kThreads, 0, stream>>>(p, a);
   return rb_check_launch("fused_adamw_param_avg");
 }
 

@@ -47,7 +47,8 @@ class FusedAllReduce:
         assert arena.grad_dtype == torch.float32
         self.arena = arena
         self.rank, self.world = rank, world
-        self.blocks = blocks
+        # CTAs of a bucket reduction: it shares the SMs with the backward pass it overlaps (RETURNN_B200_ALLREDUCE_BLOCKS overrides)
+        self.blocks = int(os.environ.get("RETURNN_B200_ALLREDUCE_BLOCKS", blocks))
         dev = arena.device
         group = group or dist.group.WORLD
         n = (arena.total + 3) // 4 * 4
