@@ -650,6 +650,8 @@ def run_secondary(args, impl: str):
             steps = 100
         cmd = [sys.executable, os.path.join(_ROOT, "bench_configs.py"), "--config", name, "--gpus", str(world), "--steps", str(steps), "--warmup", "3",
                "--impl", impl]
+        if name == "conformer_aed" and impl == "ours":
+            cmd.append("--graph-decoder")  # decoder + loss as a captured graph pair inside the eager step (models/graphed_decoder.py)
         env = dict(os.environ, MASTER_PORT=str(base_port + 1 + idx), MASTER_ADDR=os.environ.get("MASTER_ADDR", "127.0.0.1"))
         # torchrun's own bookkeeping variables must not reach the child: it forms a process group of its own
         for k in list(env):

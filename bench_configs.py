@@ -166,6 +166,13 @@ def run_gpu(args):
     if world > 1:
         cfg.set("torch_distributed", {"reduce_type": "param", "param_sync_step": 100} if args.config == "conformer_aed" else
                 {"reduce_type": "grad_explicit" if args.cuda_graph else "grad"})
+    if args.graph_decoder:
+        # decoder + loss of the encoder-decoder model as a captured forward / backward graph pair, bounded by the largest batch of the pool
+        assert args.config == "conformer_aed"
+        enc_len = lambda t: -(-(-(-t // 3)) // 2)
+        cfg.set("model_opts", dict(spec["model_opts"], graphed_decoder={
+            "batch_size_bound": max(len(b) for b in batches), "enc_capacity": -(-enc_len(max(s["data"].shape[0] for b in batches for s in b)) // 8) * 8,
+            "tgt_capacity": -(-max(s["classes"].shape[0] for b in batches for s in b) // 8) * 8}))
     if args.cuda_graph:
         # whole-step graph replay over buffers bounded by the largest batch of the pool (sequences, and frames per key rounded up to 8)
         cap = {k: -(-max(s[k].shape[0] for b in batches for s in b) // 8) * 8 for k in ("data", "classes")}
@@ -293,7 +300,7 @@ def run_gpu(args):
             "impl": "returnn_b200", "config": {"model": spec["name"], "global_batch": "%i per GPU x %i" % (spec["budget"], world),
                                                 "parallelism": ("dp%i param averaging every 100 steps" % world) if args.config == "conformer_aed" else "dp%i" % world},
             "grad_reduce": engine._torch_distributed_ctx.grad_reduce_mode if engine._torch_distributed_ctx else "none",
-            "cuda_graph": bool(args.cuda_graph), "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
+            "cuda_graph": bool(args.cuda_graph), "graph_decoder": bool(args.graph_decoder), "clocks": clocks, "e2e": {"value": n_e2e / (e2e_ms / 1e3), "unit": spec["unit"], "ms_per_step": e2e_ms / K, "h2d_bytes_per_step": h2d // K,
                                       "d2h_bytes_per_step": 4 * max(len(last or {}), 1), "last_loss": last},
             "gpu_launches": launches}))
     if world > 1:
@@ -749,6 +756,7 @@ def main():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--task", default="train", choices=["train", "search"], help="search: beam search decoding (conformer_aed, transformer_mt)")
+    ap.add_argument("--graph-decoder", action="store_true", help="conformer_aed: decoder and cross entropy as a captured CUDA-graph pair inside the eager step")
     ap.add_argument("--cuda-graph", action="store_true", help="train through the captured whole-step CUDA graph (config option torch_cuda_graph)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"], help="reference: every --config here has a reference arm")
     args = ap.parse_args()

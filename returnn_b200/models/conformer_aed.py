@@ -30,8 +30,15 @@ class ConformerAedModel(rf.Module):
 
     def __init__(self, *, in_dim: Dim, vocab_dim: Dim, num_layers: int = 12, model_dim: int = 512, num_heads: int = 8, ff_dim: int = 2048,
                  conv_kernel_size: int = 32, dropout: float = 0.1, att_dropout: float = 0.1, conv_channels=(32, 64, 64), dec_layers: int = 6,
-                 label_smoothing: float = 0.1, aux_ctc_scale: float = 0.3, beam_size: int = 12, max_len_factor: float = 0.3, bos: int = 0, eos: int = 0):
+                 label_smoothing: float = 0.1, aux_ctc_scale: float = 0.3, beam_size: int = 12, max_len_factor: float = 0.3, bos: int = 0, eos: int = 0,
+                 graphed_decoder: Optional[dict] = None):
+        """
+        :param graphed_decoder: ``{"batch_size_bound", "enc_capacity", "tgt_capacity"}``: in training on the GPU the decoder and its loss run as
+            a captured pair of CUDA graphs over buffers of these bounds (``models/graphed_decoder.py``); batches beyond them run eagerly
+        """
         super().__init__()
+        self.graphed_decoder_opts = dict(graphed_decoder) if graphed_decoder else None
+        self._graphed_decoder = None
         self.in_dim, self.vocab_dim = in_dim, vocab_dim
         self.wb_vocab_dim = vocab_dim + 1
         self.blank_idx = vocab_dim.dimension
@@ -99,7 +106,8 @@ def get_model(*, epoch: int = 1, step: int = 0, **_kwargs) -> ConformerAedModel:
         in_dim, vocab_dim = Dim(opts["in_dim"], name="feature"), Dim(opts["vocab"], name="vocab")
     keys = ("num_layers", "model_dim", "num_heads", "ff_dim", "conv_kernel_size", "dropout", "att_dropout", "dec_layers", "label_smoothing",
             "aux_ctc_scale", "beam_size", "max_len_factor", "bos", "eos")
-    return ConformerAedModel(in_dim=in_dim, vocab_dim=vocab_dim, conv_channels=tuple(opts["conv_channels"]), **{k: opts[k] for k in keys})
+    return ConformerAedModel(in_dim=in_dim, vocab_dim=vocab_dim, conv_channels=tuple(opts["conv_channels"]), graphed_decoder=opts.get("graphed_decoder"),
+                             **{k: opts[k] for k in keys})
 
 
 def train_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
@@ -111,6 +119,8 @@ def train_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
         ctc = rf.ctc_loss(logits=model.aux_logits(enc), targets=targets, input_spatial_dim=enc_spatial, targets_spatial_dim=tgt_spatial,
                           blank_index=model.blank_idx)
         ctc.mark_as_loss("ctc", scale=model.aux_ctc_scale, custom_inv_norm_factor=tgt_spatial.get_size_tensor(), use_normalized_loss=False)
+    if _graphed_decoder_loss(model, enc, enc_spatial, targets, tgt_spatial):
+        return
     # teacher forcing: decoder input = BOS + targets[:-1], target = targets + EOS
     inp, (tgt_ext,) = rf.pad(targets, axes=[tgt_spatial], padding=[(1, 0)], value=model.bos)
     out_t, _ = rf.pad(targets, axes=[tgt_spatial], padding=[(0, 1)], value=model.eos, out_dims=[tgt_ext], handle_dynamic_dims=True)
@@ -121,6 +131,31 @@ def train_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
     ce.mark_as_loss("ce", use_normalized_loss=True)
     err = best != out_t
     err.mark_as_loss("fer", as_error=True)
+
+
+def _graphed_decoder_loss(model: ConformerAedModel, enc: Tensor, enc_spatial: Dim, targets: Tensor, tgt_spatial: Dim) -> bool:
+    """the decoder + cross entropy through the captured graphs when configured and the batch fits; marks "ce" and "fer"; False: not taken"""
+    opts = model.graphed_decoder_opts
+    enc_raw = enc.copy_transpose([batch_dim, enc_spatial, model.model_dim]).raw_tensor
+    if not opts or not enc_raw.is_cuda or not rf.get_run_ctx().train_flag or not torch.is_grad_enabled():
+        return False
+    if model._graphed_decoder is None:
+        from .graphed_decoder import GraphedDecoderLoss
+
+        model._graphed_decoder = GraphedDecoderLoss(
+            model.decoder, vocab_dim=model.vocab_dim, enc_dim=model.model_dim, bos=model.bos, eos=model.eos, label_smoothing=model.label_smoothing,
+            batch_bound=opts["batch_size_bound"], enc_capacity=opts["enc_capacity"], tgt_capacity=opts["tgt_capacity"])
+    gd = model._graphed_decoder
+    tgt_raw = targets.copy_transpose([batch_dim, tgt_spatial]).raw_tensor
+    if not gd.fits(enc_raw.shape[0], enc_raw.shape[1], tgt_raw.shape[1]):
+        return False
+    tgt_lens = tgt_spatial.dyn_size_ext.raw_tensor
+    ce_sum, wrong = gd(enc_raw, enc_spatial.dyn_size_ext.raw_tensor, tgt_raw, tgt_lens)
+    n_frames = int(tgt_lens.sum()) + int(tgt_raw.shape[0])  # every sequence has its labels and the end symbol
+    ctx = rf.get_run_ctx()
+    ctx.mark_as_loss(Tensor("ce", dims=[], dtype="float32", raw_tensor=ce_sum), "ce", use_normalized_loss=True, custom_inv_norm_factor=n_frames)
+    ctx.mark_as_loss(Tensor("fer", dims=[], dtype="float32", raw_tensor=wrong), "fer", as_error=True, custom_inv_norm_factor=n_frames)
+    return True
 
 
 def forward_step(*, model: ConformerAedModel, extern_data: TensorDict, **_kwargs):
