@@ -49,7 +49,7 @@ from .graph import *
 from .assert_ import *
 from .types import GetModelFunc, StepFunc, ItemKeyType, get_raw_tensor_type
 from .backend import select_backend, get_selected_backend, select_backend_numpy, select_backend_tf, is_backend_raw_tensor_dim_tag_independent
-from .packed import pack, unpack, pack_import, is_packed, PackedTensor
+from .packed import pack, unpack, pack_import, is_packed, PackedTensor, packed_regap, packed_flat_content
 
 from . import init
 from . import nested

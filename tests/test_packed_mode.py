@@ -122,3 +122,37 @@ def test_plain_rf_conformer_packed_equals_padded_gpu():
     out_pad, g_pad = _run(enc, in_dim, model, "cuda", packed=False, train=False)
     out_packed, g_packed = _run(enc, in_dim, model, "cuda", packed=True, train=False)
     assert torch.allclose(out_pad, out_packed, atol=2e-2), float((out_pad - out_packed).abs().max())
+
+
+def test_packed_regap_and_flat_content():
+    """re-layout of a packed tensor with gaps and aligned starts, and the dense flat view: same sequences, zeros in between"""
+    import torch
+    import returnn_b200.frontend as rf
+    from returnn_b200.tensor import Tensor, Dim, batch_dim
+
+    lens = [3, 1, 4]
+    t = Dim(None, name="time")
+    batch_dim.dyn_size_ext = Tensor("batch_size", dims=[], dtype="int32", raw_tensor=torch.tensor(3, dtype=torch.int32))
+    t.dyn_size_ext = Tensor("lens", dims=[batch_dim], dtype="int32", raw_tensor=torch.tensor(lens, dtype=torch.int32))
+    f = Dim(2, name="f")
+    raw = torch.arange(3 * 4 * 2, dtype=torch.float32).reshape(3, 4, 2) + 1.0
+    x = Tensor("x", dims=[batch_dim, t, f], dtype="float32", raw_tensor=raw, feature_dim=f)
+    p = rf.pack(x, dims=[batch_dim, t])
+    assert p.gap == 0 and p.align == 1 and p.raw_tensor.shape[0] == 8
+    g = rf.packed_regap(p, 2, align=4)
+    # starts: 0, then 3 + 2 = 5 -> aligned to 8, then 8 + 1 + 2 = 11 -> 12; end 12 + 4 + 2 = 18
+    assert g.seq_starts.tolist() == [0, 8, 12] and g.raw_tensor.shape[0] == 18 and (g.gap, g.align) == (2, 4)
+    for b, (s, n) in enumerate(zip([0, 8, 12], lens)):
+        torch.testing.assert_close(g.raw_tensor[s: s + n], raw[b, :n])
+    holes = torch.ones(18, dtype=torch.bool)
+    for s, n in zip([0, 8, 12], lens):
+        holes[s: s + n] = False
+    assert float(g.raw_tensor[holes].abs().max()) == 0.0
+    assert rf.packed_regap(g, 2, align=4) is g
+    b24 = rf.packed_regap(p, 1, total_bound=24)
+    assert b24.raw_tensor.shape[0] == 24 and b24.packed_dim.capacity == 24 and float(b24.raw_tensor[11:].abs().max()) == 0.0
+    flat, flat_dim = rf.packed_flat_content(g)
+    assert flat.dims == (flat_dim, f) and int(flat_dim.dyn_size_ext.raw_tensor) == 8
+    torch.testing.assert_close(flat.raw_tensor, p.raw_tensor)
+    back = rf.unpack(g)
+    torch.testing.assert_close(back.raw_tensor, x.copy_masked(0.0).raw_tensor)
