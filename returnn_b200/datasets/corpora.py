@@ -287,6 +287,13 @@ class TimitDataset(_AudioTextCorpus):
         self._num_phones = num_phones
         self._phone_map, self.labels["classes"] = self._make_phone_map(num_phones)
         self.num_outputs = {"data": (self.num_inputs, 2), "classes": (len(self.labels["classes"]), 1)}
+        self._collect_entries()
+        assert self._entries, "%s: no utterances" % type(self).__name__
+        self._finish_entries()
+
+    def _collect_entries(self):
+        """fills ``self._entries`` from ``<timit_dir>/{train,test}/<dialect>/<speaker>/<utterance>.{wav,phn}``"""
+        timit_dir, train = self._timit_dir, self._is_train
         sub = "train" if train else "test"
         root = None
         for cand in (os.path.join(timit_dir, sub), os.path.join(timit_dir, sub.upper())):
@@ -303,8 +310,6 @@ class TimitDataset(_AudioTextCorpus):
                 continue
             rel = os.path.relpath(base, root).replace(os.sep, "/").lower()
             self._entries.append({"tag": "%s/%s" % (sub, rel), "phn": phn, "wav": wav, "text": ""})
-        assert self._entries, "TimitDataset: no utterances under %s" % root
-        self._finish_entries()
 
     @classmethod
     def _make_phone_map(cls, num_phones: int) -> Tuple[Dict[str, Optional[str]], List[str]]:
@@ -366,6 +371,49 @@ class TimitDataset(_AudioTextCorpus):
 
     def get_target_list(self):
         return ["classes"]
+
+
+class NltkTimitDataset(TimitDataset):
+    """
+    The TIMIT sample that NLTK distributes (160 training utterances, no test set): ``<nltk data>/corpora/timit/<dialect>-<speaker>/<utterance>.{wav,phn}``.
+    ``nltk_download_dir`` names the NLTK data directory; without it the directories NLTK itself would search are tried (``NLTK_DATA``,
+    ``~/nltk_data``, ``/usr/share/nltk_data`` ...). Nothing is downloaded here. The one set is split 90 / 10 into ``train=True`` / ``train=False``.
+    Parity: returnn/datasets/generating.py:1800.
+    """
+
+    def __init__(self, nltk_download_dir: Optional[str] = None, **kwargs):
+        self._nltk_download_dir = nltk_download_dir
+        super().__init__(timit_dir=self._find_dir(nltk_download_dir), **kwargs)
+
+    @staticmethod
+    def _find_dir(nltk_download_dir: Optional[str]) -> str:
+        cands = [nltk_download_dir] if nltk_download_dir else []
+        if not cands:
+            cands += [p for p in os.environ.get("NLTK_DATA", "").split(os.pathsep) if p]
+            try:
+                import nltk.data  # noqa
+
+                cands += list(nltk.data.path)
+            except ImportError:
+                pass
+            cands += [os.path.expanduser("~/nltk_data"), "/usr/share/nltk_data", "/usr/local/share/nltk_data", "/usr/lib/nltk_data"]
+        for c in cands:
+            d = os.path.join(c, "corpora", "timit")
+            if os.path.isdir(d):
+                return d
+        raise FileNotFoundError("NltkTimitDataset: no corpora/timit under %s (fetch it with nltk.download('timit') and pass nltk_download_dir)" % cands)
+
+    def _collect_entries(self):
+        entries = []
+        for phn in sorted(_glob.glob(self._timit_dir + "/*/*.[pP][hH][nN]")):
+            base = os.path.splitext(phn)[0]
+            wav = next((base + e for e in (".wav", ".WAV") if os.path.exists(base + e)), None)
+            if wav is None:
+                continue
+            rel = os.path.relpath(base, self._timit_dir).replace(os.sep, "/").lower()
+            entries.append({"tag": rel, "phn": phn, "wav": wav, "text": ""})
+        split = int(len(entries) * 0.9)
+        self._entries.extend(entries[:split] if self._is_train else entries[split:])
 
 
 class BlissDataset(_AudioTextCorpus):

@@ -812,6 +812,6 @@ class CopyTaskDataset(GeneratingDataset):
 
 # The corpus readers live in their own module; the reference has them in its generating module
 # (returnn/datasets/generating.py: LibriSpeechCorpus, TimitDataset, BlissDataset, Enwik8Corpus), so configs name them through here.
-from .corpora import LibriSpeechCorpus, TimitDataset, BlissDataset, Enwik8Corpus  # noqa: E402
+from .corpora import LibriSpeechCorpus, TimitDataset, NltkTimitDataset, BlissDataset, Enwik8Corpus  # noqa: E402
 
 __all__ += ["LibriSpeechCorpus", "TimitDataset", "BlissDataset", "Enwik8Corpus"]

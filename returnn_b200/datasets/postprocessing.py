@@ -464,3 +464,24 @@ class LaplaceOrdering:
                 ascending = not ascending
         buf.sort(key=lambda t: t.data[self.length_key].raw_tensor.shape[0], reverse=not ascending)
         yield from buf
+
+
+class Sequential:
+    """
+    Composition of post-processing functions: ``Sequential(f, g)(x) == g(f(x))``. Works for ``map_seq`` functions (one sequence in, one
+    out) and for ``map_seq_stream`` functions (iterator in, iterator out); the two kinds are not to be mixed in one instance.
+    Keyword arguments (``epoch``, ``rng`` ...) are handed to every function. Parity: returnn/datasets/postprocessing.py:975.
+    """
+
+    def __init__(self, *postprocessing_funcs: Callable):
+        self.funcs = postprocessing_funcs
+
+    def __call__(self, arg, **kwargs):
+        for func in self.funcs:
+            arg = func(arg, **kwargs)
+        return arg
+
+    @property
+    def preserves_num_seqs(self) -> bool:
+        """whether every composed function says of itself that it maps sequences one to one"""
+        return all(getattr(f, "preserves_num_seqs", False) for f in self.funcs)

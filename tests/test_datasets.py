@@ -662,3 +662,39 @@ def test_allophone_state_and_state_tying(tmp_path):
     f.write_text("a{#+#}@i@f.0 0\na{#+#}@i@f.1 1\nb{a+#}.0 0\n# comment\n")
     t = StateTying(str(f))
     assert t.num_classes == 2 and t.allo_map["b{a+#}.0"] == 0 and t.class_map[0] == {"a{#+#}@i@f.0", "b{a+#}.0"}
+
+
+def test_nltk_timit_layout_and_sequential_postprocessing(tmp_path):
+    from returnn_b200.datasets.generating import NltkTimitDataset
+    from returnn_b200.datasets.postprocessing import Sequential
+
+    rng = numpy.random.RandomState(3)
+    root = tmp_path / "nltk_data" / "corpora" / "timit"
+    for spk in ("dr1-fvmh0", "dr2-marc0"):
+        d = root / spk
+        d.mkdir(parents=True)
+        for utt in ("sa1", "sa2", "si1466", "sx116", "sx206"):
+            _write_wav(d / (utt + ".wav"), rng.uniform(-0.3, 0.3, size=6000))
+            (d / (utt + ".phn")).write_text("0 1500 h#\n1500 4000 iy\n4000 6000 h#\n")
+    train = NltkTimitDataset(nltk_download_dir=str(tmp_path / "nltk_data"), train=True, num_feature_filters=13)
+    dev = NltkTimitDataset(nltk_download_dir=str(tmp_path / "nltk_data"), train=False, num_feature_filters=13)
+    train.init_seq_order(epoch=1)
+    dev.init_seq_order(epoch=1)
+    assert train.num_seqs == 9 and dev.num_seqs == 1 and dev.get_all_tags() == ["dr2-marc0/sx206"]
+    train.load_seqs(0, 1)
+    c = train.get_data(0, "classes")
+    assert train.labels["classes"][c[len(c) // 2]] == "iy"
+    with pytest.raises(FileNotFoundError):
+        NltkTimitDataset(nltk_download_dir=str(tmp_path / "nowhere"))
+
+    def double(t, **kw):
+        return t * 2
+
+    def add_epoch(t, *, epoch=0, **kw):
+        return t + epoch
+
+    double.preserves_num_seqs = True
+    seq = Sequential(double, add_epoch)
+    assert seq(3, epoch=5) == 11 and not seq.preserves_num_seqs
+    add_epoch.preserves_num_seqs = True
+    assert Sequential(double, add_epoch).preserves_num_seqs
