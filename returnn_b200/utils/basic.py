@@ -980,3 +980,7 @@ def cf(filename: str) -> str:
     if fc is None:
         return filename
     return fc.get_file(filename)
+
+
+from .basic_more import *  # noqa: E402,F401,F403  (the smaller helpers of this module live in basic_more.py)
+from .basic_more import _eq as _eq_generic  # noqa: E402,F401

@@ -383,3 +383,97 @@ def test_better_exchook_statement_names_chain_and_threads():
     assert "MainThread" in out.getvalue() and "dump_all_thread_tracebacks" in out.getvalue()
     lines = B.format_tb(sys._getframe(), limit=1, with_color=False)
     assert any("test_better_exchook_statement_names_chain_and_threads" in ln for ln in lines)
+
+
+def test_basic_helpers(tmp_path, capsys):
+    import io
+    import sys
+    from returnn_b200.utils import basic as U
+
+    assert U.model_epoch_from_filename("net/model.042.pt") == 42 and U.model_epoch_from_filename("m.pretrain.007") == 7
+    assert U.get_checkpoint_filepattern("a/b.010.pt") == "a/b.010" and U.get_checkpoint_filepattern("a/b.010.opt.pt") == "a/b.010" and U.get_model_filename_postfix() == ".pt"
+    assert U.find_ranges([1, 2, 3, 7, 8, 10]) == [(1, 4), (7, 9), (10, 11)]
+    assert U.dict_joined({"a": 1}, {"a": 2, "b": 3}) == {"a": 2, "b": 3} and U.dict_zip(["x", "y"], [1, 2]) == {"x": 1, "y": 2}
+    assert U.sorted_values_from_dict({"b": 2, "a": 1}) == [1, 2]
+    assert U.obj_diff_str({"a": [1, 2]}, {"a": [1, 2]}) == "No diff."
+    diff = U.obj_diff_list({"a": [1, 2], "b": 1}, {"a": [1, 3], "c": 1})
+    assert any("[1]" in d and "2 != other: 3" in d for d in diff) and any("'b' not in other" in d for d in diff) and any("'c' not in self" in d for d in diff)
+    assert U.uniq_generic([[1], [2], [1], numpy.array([1, 2]), numpy.array([1, 2])])[:2] == [[1], [2]] and len(U.uniq_generic([[1], [1]])) == 1
+    fd = U.FrozenDict({"a": [1, 2]}) if False else U.make_hashable({"a": [1, {"b": {3, 4}}], "z": numpy.arange(3)})
+    assert hash(fd) == hash(U.make_hashable({"a": [1, {"b": {4, 3}}], "z": numpy.arange(3)}))
+    with pytest.raises(TypeError):
+        fd["x"] = 1
+    a, b = [1], [1]
+    refs = U.DictRefKeys()
+    refs[a] = "a"
+    assert a in refs and b not in refs and refs[a] == "a" and len(refs) == 1 and U.RefIdEq(a) != U.RefIdEq(b)
+    assert U.ObjAsDict(refs)["_d"] is refs._d and U.DictAsObj({"q": 5}).q == 5
+    assert U.attr_chain(sys, ["version_info", "major"]) == 3 and U.camel_case_to_snake_case("HelloWorldHTTPServer") == "hello_world_http_server"
+    assert U.str_is_number("1e-3") and not U.str_is_number("x1") and U.unicode_to_str(b"ab") == "ab" and U.prod([2, 3, 4]) == 24 and U.prod([]) == 1
+    x = numpy.arange(10).reshape(5, 2)
+    assert U.slice_pad_zeros(x, -2, 2).tolist() == [[0, 0], [0, 0], [0, 1], [2, 3]] and U.slice_pad_zeros(x, 4, 7).tolist() == [[8, 9], [0, 0], [0, 0]]
+    q = U.random_orthogonal((4, 6), seed=1)
+    numpy.testing.assert_allclose(q @ q.T, numpy.eye(4), atol=1e-5)
+    acc = numpy.zeros(3)
+    U.inplace_increment(acc, numpy.array([0, 0, 2]), numpy.array([1.0, 2.0, 5.0]))
+    assert acc.tolist() == [3.0, 0.0, 5.0]
+    numpy.testing.assert_allclose(U.softmax(numpy.array([[0.0, 0.0], [1000.0, 0.0]]), axis=1), [[0.5, 0.5], [1.0, 0.0]], atol=1e-9)
+    assert U.parse_orthography_into_symbols("hi  [laugh] you") == ["h", "i", " ", "[LAUGH]", " ", "y", "o", "u"]
+    assert U.parse_orthography_into_symbols("a b [x]", word_based=True) == ["a", "b", "[X]"]
+    assert U.parse_orthography("(a) b", postfix=["[END]"]) == ["a", " ", "b", "[END]"]
+    assert U.json_remove_comments('{"a": "x//y", // c\n /* block */ "b": 2}') == '{"a": "x//y",\n  "b": 2}'
+
+    class Base:
+        def __init__(self, base_arg, base_opt=1):
+            pass
+
+    class Child(Base):
+        def __init__(self, child_arg, *, child_kw=2, **kwargs):
+            super().__init__(**kwargs)
+
+    assert U.collect_class_init_kwargs(Child) == ["child_arg", "child_kw", "base_arg", "base_opt"]
+    assert U.collect_class_init_kwargs(Child, only_with_default=True) == ["child_kw", "base_opt"]
+    assert U.collect_mandatory_class_init_kwargs(Child) == ["child_arg", "base_arg"]
+    U.help_on_type_error_wrong_args(Child, ["child_arg", "bogus"])
+    err = capsys.readouterr().err
+    assert "bogus" in err and "base_arg" in err
+    assert U.type_attrib_mro_chain(Child, "__init__")[:2] == [Child.__dict__["__init__"], Base.__dict__["__init__"]]
+    assert U.next_type_attrib_in_mro_chain(Child, "__init__", Child.__dict__["__init__"]) is Base.__dict__["__init__"]
+    assert U.getargspec(Base.__init__).args == ["self", "base_arg", "base_opt"]
+    assert U.AsyncThreadRun("t", lambda: 7).get() == 7 and U.wrap_async_func(lambda: 8) == 8
+    with pytest.raises(ZeroDivisionError):
+        U.AsyncThreadRun("t", lambda: 1 / 0).get()
+    with U.guard_infinite_recursion("f", 1):
+        with pytest.raises(U.InfiniteRecursionDetected):
+            with U.guard_infinite_recursion("f", 1):
+                pass
+    assert U.try_get_caller_name(depth=0) == "test_basic_helpers"
+    f = tmp_path / "sub" / "touched"
+    U.maybe_make_dirs(str(tmp_path / "sub"))
+    U.touch_file(str(f))
+    assert f.exists() and U.is_valid_fd(0) and not U.is_valid_fd(9999)
+    (tmp_path / "vec.txt").write_text("1.5\n2\n\n")
+    assert U.load_txt_vector(str(tmp_path / "vec.txt")) == [1.5, 2.0]
+    buf = io.BytesIO()
+    U.write_pickled_object(buf, {"k": [1, 2]})
+    buf.seek(0)
+    import struct
+
+    (n,) = struct.unpack("<i", buf.read(4))
+    assert U.deserialize_object(U.read_bytes_to_new_buffer(buf, n).read()) == {"k": [1, 2]}
+    assert U.eval_shell_str("echo 'a b' $HOME")[:2] == ["echo", "a b"] and U.eval_shell_str(lambda: ["x", "$NOPE_NOT_SET"]) == ["x", ""]
+    assert U.sys_exec_out("echo", "hi").strip() == "hi" and U.sys_exec_ret_code("false") == 1 and U.sys_cmd_out_lines("printf 'a\\nb\\n'") == ["a", "b"]
+    assert U.which("sh") and U.is_64bit_platform() and U.get_number_available_cpus() >= 1 and U.available_physical_memory_in_bytes() > 0
+    assert isinstance(U.describe_returnn_version(), str) and "(" in U.describe_torch_version() and U.make_dll_name("x") == "libx.so"
+    assert U.escape_c_str('a"b\n') == '"a\\"b\\n"' and U.terminal_size(io.StringIO()) == (-1, -1) and not U.is_tty(io.StringIO())
+    assert "cut at 2 items" in U.pretty_print(list(range(10)), limit=2) and U.pretty_print({"a": 1}) == "{'a': 1}"
+    U.log_runtime_info_to_dir(str(tmp_path / "logs"))
+    assert len(list((tmp_path / "logs").iterdir())) == 1
+    from returnn_b200.utils.h5_shim import get_h5py
+
+    with get_h5py().File(str(tmp_path / "t.hdf"), "w") as h:
+        h.attrs["numLabels"] = 7
+        h.create_dataset("inputs", data=numpy.zeros((5, 3)))
+        U.hdf5_strings(h, "labels", ["a", "bcd"])
+    assert U.hdf5_dimension(str(tmp_path / "t.hdf"), "numLabels") == 7 and U.hdf5_dimension(str(tmp_path / "t.hdf"), "inputs") == 5
+    assert U.hdf5_shape(str(tmp_path / "t.hdf"), "inputs") == (5, 3)
