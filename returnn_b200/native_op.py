@@ -74,12 +74,9 @@ def edit_distance(a: torch.Tensor, a_len: torch.Tensor, b: torch.Tensor, b_len: 
 
 def optimal_completion_edit_distance(a: torch.Tensor, a_len: torch.Tensor, b: torch.Tensor, b_len: torch.Tensor) -> torch.Tensor:
     """min over all prefixes of b of the edit distance between a and that prefix (a = hypothesis so far, b = reference)"""
-    best = None
-    for n in range(int(b.shape[1]) + 1):
-        bl = torch.clamp(b_len, max=n)
-        d = _seq.edit_distance(a, a_len, b, bl)
-        best = d if best is None else torch.minimum(best, d)
-    return best
+    from .torch.util.native_op import optimal_completion_edit_distance as _oc
+
+    return _oc(a, a_len, b, b_len)
 
 
 def chunk(x: torch.Tensor, index: torch.Tensor, chunk_size: int, chunk_step: int) -> Tuple[torch.Tensor, torch.Tensor]:

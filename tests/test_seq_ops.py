@@ -195,3 +195,69 @@ def test_seq_util_references_cpu():
 @gpu
 def test_seq_util_kernels():
     _seq_util_checks("cuda")
+
+
+def _levenshtein_row(a, b):
+    """distances of a to every prefix of b"""
+    row = list(range(len(b) + 1))
+    for i, x in enumerate(a):
+        new = [i + 1]
+        for j, y in enumerate(b):
+            new.append(min(row[j + 1] + 1, new[j] + 1, row[j] + (x != y)))
+        row = new
+    return row
+
+
+def test_row_wise_edit_distance_family():
+    """next_edit_distance_row / _reduce and the optimal-completion forms against a plain dynamic program"""
+    import torch
+    from returnn_b200.torch.util import native_op as N
+
+    g = torch.Generator().manual_seed(5)
+    B, t1, t2, V = 6, 7, 9, 4
+    a = torch.randint(0, V, (B, t1), generator=g, dtype=torch.int32)
+    b = torch.randint(0, V, (B, t2), generator=g, dtype=torch.int32)
+    a_len = torch.tensor([7, 3, 0, 5, 7, 1], dtype=torch.int32)
+    b_len = torch.tensor([9, 4, 6, 0, 2, 9], dtype=torch.int32)
+    full = N.edit_distance_via_next_edit_distance_row(a, a_len, b, b_len, full_row_output=True)
+    for i in range(B):
+        want = _levenshtein_row(a[i, : a_len[i]].tolist(), b[i, : b_len[i]].tolist())
+        assert full[i, : b_len[i] + 1].tolist() == want
+        assert full[i, b_len[i]:].tolist() == [want[-1]] * (t2 + 1 - int(b_len[i]))  # the entry at b_len is repeated
+    dist = N.edit_distance_via_next_edit_distance_row(a, a_len, b, b_len)
+    assert dist.tolist() == N.edit_distance(a, a_len, b, b_len).tolist()
+    oc = N.optimal_completion_edit_distance(a, a_len, b, b_len)
+    assert oc.tolist() == [min(_levenshtein_row(a[i, : a_len[i]].tolist(), b[i, : b_len[i]].tolist())) for i in range(B)]
+    per = N.optimal_completion_edit_distance_per_successor(a, a_len, b, b_len, V)
+    assert per.shape == (B, V)
+    for i in range(B):
+        for s in range(V):
+            assert int(per[i, s]) == min(_levenshtein_row(a[i, : a_len[i]].tolist() + [s], b[i, : b_len[i]].tolist()))
+    # the loop form: sequences of full length are extended, shorter ones count as ended (their row is kept)
+    via = N.optimal_completion_edit_distance_per_successor_via_next_edit_distance(a, a_len, b, b_len, V)
+    for i in range(B):
+        for s in range(V):
+            ext = a[i, : a_len[i]].tolist() + ([s] if int(a_len[i]) == t1 else [])
+            assert int(via[i, s]) == min(_levenshtein_row(ext, b[i, : b_len[i]].tolist()))
+    # a blank candidate keeps the row
+    row = N.edit_distance_via_next_edit_distance_row(a, a_len, b, b_len, full_row_output=True)
+    red = N.next_edit_distance_reduce(row, torch.arange(V)[None], torch.tensor(t1), torch.zeros(B, dtype=torch.bool), b, b_len, a_blank_idx=2)
+    assert red[:, 2].tolist() == row[:, -1].tolist()
+    assert N.make_op("EditDistanceOp") is N.edit_distance and N.make_fast_baum_welch_op() is N.fast_baum_welch
+
+
+def test_ctc_best_path_facade():
+    import torch
+    from returnn_b200.torch.util import native_op as N
+
+    torch.manual_seed(0)
+    logits = torch.randn(2, 8, 5)
+    tl = torch.tensor([3, 2], dtype=torch.int32)
+    il = torch.tensor([8, 5], dtype=torch.int32)
+    y = torch.tensor([[1, 2, 1], [3, 3, 0]], dtype=torch.int32)
+    p = N.ctc_best_path(logits=logits, logits_seq_lens=il, targets=y, targets_seq_lens=tl, blank_index=4)
+    assert p.shape == (2, 8) and p[1, 5:].tolist() == [4, 4, 4]
+    for i in range(2):
+        path = p[i, : il[i]].tolist()
+        collapsed = [v for k, v in enumerate(path) if v != 4 and (k == 0 or v != path[k - 1])]
+        assert collapsed == y[i, : tl[i]].tolist()
