@@ -84,3 +84,58 @@ def host_to_device(t, device):
             t = t.pin_memory()
         return t.to(device, non_blocking=True)
     return t.to(device)
+
+
+def tensor_dict_dims_random_seq_len_min_max(tensor_dict, seq_lens=None):
+    """
+    The dynamic dims of all tensors of the dict (each once, in order of appearance) and the ``(min, max)`` range of lengths to draw for
+    each: what :func:`get_random_seq_lens_for_dyn_dims` takes.
+
+    :param seq_lens: a fixed length, a ``(min, max)`` pair, or a dict from data key / Dim / None (default) to either
+    :return: dims, {dim: (min, max)}
+    Parity: returnn/tensor/utils.py:126.
+    """
+    if seq_lens is None:
+        seq_lens = {}
+    if not isinstance(seq_lens, dict):
+        seq_lens = {None: seq_lens}
+
+    def as_range(v):
+        return (int(v), int(v)) if isinstance(v, int) else (int(v[0]), int(v[1]))
+
+    default = as_range(seq_lens.get(None, (2, 11)))
+    dims, ranges = [], {}
+    for key, t in tensor_dict.data.items():
+        for dim in t.dims:
+            if dim.is_batch_dim() or dim.is_static() or dim in ranges:
+                continue
+            dims.append(dim)
+            if dim in seq_lens:
+                ranges[dim] = as_range(seq_lens[dim])
+            elif key in seq_lens:
+                ranges[dim] = as_range(seq_lens[key])
+            else:
+                ranges[dim] = default
+    return dims, ranges
+
+
+def get_random_seq_lens_for_dyn_dims(dims, seq_len_min_max, *, batch_size: int = 1, rnd=1337):
+    """
+    Random lengths ``[batch_size]`` for every dim, without touching the dims (safe to call from a data thread). The first sequence of every
+    dim gets the maximum, so that the padded extent is the same for every seed.
+
+    :return: {dim: int32 array [batch_size]}
+    Parity: returnn/tensor/utils.py:194.
+    """
+    import numpy
+
+    if not isinstance(rnd, numpy.random.RandomState):
+        rnd = numpy.random.RandomState(rnd)
+    out = {}
+    for dim in dims:
+        lo, hi = seq_len_min_max[dim]
+        lens = rnd.randint(lo, hi + 1, size=[batch_size]).astype("int32")
+        if batch_size:
+            lens[0] = hi
+        out[dim] = lens
+    return out

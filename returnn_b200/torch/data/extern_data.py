@@ -125,3 +125,11 @@ def raw_dict_split_batch(extern_data_raw: Dict[str, Any], *, splits: Union[int, 
         res.append(part)
         offset += s
     return res
+
+
+def get_batch_dim_from_extern_data(extern_data: TensorDict) -> Dim:
+    """
+    The batch dim of a collated batch: by construction the first dim of every tensor (``collate_batch``). It need not be the global
+    ``batch_dim`` object and need not even be marked as a batch dim. Parity: returnn/torch/data/extern_data.py:292.
+    """
+    return next(iter(extern_data.data.values())).dims[0]

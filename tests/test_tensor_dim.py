@@ -293,3 +293,33 @@ def test_verify_out_shape_and_sanity_check():
     bad = Tensor("bad", dims=[batch_dim, f], dtype="float32")
     with pytest.raises(Exception):
         bad.raw_tensor = torch.zeros(2, 5)  # size of f is 4
+
+
+def test_data_and_tensor_utilities():
+    from returnn_b200.torch.data.queued_data_iter import QueuedDataIter
+    from returnn_b200.torch.data import tensor_utils as TU
+    from returnn_b200.torch.data.extern_data import get_batch_dim_from_extern_data
+    from returnn_b200.tensor.utils import tensor_dict_dims_random_seq_len_min_max, get_random_seq_lens_for_dyn_dims
+
+    it = QueuedDataIter(iter([1, 2, 3]))
+    assert next(it) == 1
+    it.extend(["a", "b"])
+    assert list(it) == ["a", "b", 2, 3]
+    t = Dim(None, name="time")
+    t.dyn_size_ext = Tensor("lens", dims=[batch_dim], dtype="int32", raw_tensor=numpy.array([2, 3], dtype="int32"))
+    f = Dim(4, name="feat")
+    x = Tensor("data", dims=[batch_dim, t, f], dtype="float32", raw_tensor=numpy.ones((2, 3, 4), dtype="float32"))
+    s2 = Dim(None, name="labels")
+    y = Tensor("classes", dims=[batch_dim, s2], dtype="int32", sparse_dim=Dim(7, name="v"))
+    td = TensorDict()
+    td.data["data"], td.data["classes"] = x, y
+    TU.tensor_dict_numpy_to_torch_(td)
+    assert isinstance(x.raw_tensor, torch.Tensor) and isinstance(t.dyn_size_ext.raw_tensor, torch.Tensor)
+    TU.tensor_dict_torch_to_numpy_(td)
+    assert isinstance(x.raw_tensor, numpy.ndarray) and t.dyn_size_ext.raw_tensor.tolist() == [2, 3]
+    assert get_batch_dim_from_extern_data(td) is batch_dim
+    dims, ranges = tensor_dict_dims_random_seq_len_min_max(td, {"classes": 5, None: (3, 6)})
+    assert dims == [t, s2] and ranges == {t: (3, 6), s2: (5, 5)}
+    lens = get_random_seq_lens_for_dyn_dims(dims, ranges, batch_size=4, rnd=1)
+    assert lens[s2].tolist() == [5] * 4 and lens[t][0] == 6 and all(3 <= v <= 6 for v in lens[t].tolist())
+    assert get_random_seq_lens_for_dyn_dims(dims, ranges, batch_size=4, rnd=1)[t].tolist() == lens[t].tolist()
