@@ -337,19 +337,9 @@ class Updater:
         blacklist = optimizer_opts.get("weight_decay_modules_blacklist", None)
         custom_check = optimizer_opts.get("weight_decay_custom_include_check", None)
         if blacklist is None:
-            blacklist = [rf.LayerNorm, rf.Embedding, rf.BatchNorm, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.BatchNorm1d]
-        resolved = []
-        for b in blacklist:
-            if isinstance(b, str):
-                if b.startswith("rf."):
-                    b = getattr(rf, b[3:])
-                else:
-                    import importlib
-
-                    mod_name, _, cls_name = b.rpartition(".")
-                    b = getattr(importlib.import_module(mod_name), cls_name)
-            resolved.append(b)
-        blacklist_t = tuple(resolved)
+            # also the option's name in the reference
+            blacklist = optimizer_opts.get("weight_decay_modules_blacklist", optimizer_opts.get("blacklist_weight_decay_modules", None))
+        blacklist_t = wrap_user_blacklist_wd_modules(blacklist)
         from .frontend.bridge import RFModuleAsPTModule
 
         wd: Set[str] = set()
@@ -430,3 +420,27 @@ def gradient_noise_(params: Iterable[torch.nn.Parameter], std: float, *, generat
     for g in grads:
         noise = torch.empty_like(g).normal_(0.0, std, generator=generator)
         g.add_(noise)
+
+
+def wrap_user_blacklist_wd_modules(mods) -> Tuple[type, ...]:
+    """
+    The module classes whose parameters get no weight decay, from the user's option: classes, or their names as strings (``"rf.LayerNorm"``,
+    ``"torch.nn.LayerNorm"``, any importable dotted name). None: norm and embedding layers of both module families.
+    Parity: returnn/torch/updater.py:666.
+    """
+    if mods is None:
+        return (rf.LayerNorm, rf.Embedding, rf.BatchNorm, torch.nn.LayerNorm, torch.nn.Embedding, torch.nn.BatchNorm1d)
+    assert isinstance(mods, (list, tuple)), "invalid weight_decay_modules_blacklist %r" % (mods,)
+    res = []
+    for mod in mods:
+        if isinstance(mod, str):
+            if mod.startswith("rf."):
+                mod = getattr(rf, mod[3:])
+            else:
+                import importlib
+
+                mod_name, _, cls_name = mod.rpartition(".")
+                mod = getattr(importlib.import_module(mod_name), cls_name)
+        assert isinstance(mod, type) and issubclass(mod, (rf.Module, torch.nn.Module)), "invalid weight_decay_modules_blacklist entry %r" % (mod,)
+        res.append(mod)
+    return tuple(res)

@@ -73,3 +73,16 @@ def timeout(func_expr: str = "torch.cuda.is_available()", *, timeout_sec: float 
         return None
     except Exception:
         return None
+
+
+def print_relevant_env_vars(*, file=None):
+    """the environment variables that decide which devices a process sees and how the CUDA libraries behave"""
+    import os
+    import sys
+
+    file = file or sys.stdout
+    names = sorted(k for k in os.environ if k.startswith(("CUDA", "NCCL", "TORCH_", "PYTORCH_", "RETURNN_B200_", "NVIDIA_", "OMP_NUM", "LD_LIBRARY")))
+    for k in names:
+        print("%s=%s" % (k, os.environ[k]), file=file)
+    if not names:
+        print("(none of the CUDA / NCCL / torch variables is set)", file=file)

@@ -50,3 +50,8 @@ def all_reduce_differentiable(x: torch.Tensor, op: str = "sum") -> torch.Tensor:
 
 
 all_reduce_sum = all_reduce_differentiable
+
+
+def all_reduce_sum(x: torch.Tensor) -> torch.Tensor:
+    """sum over the ranks, differentiable (the gradient is summed over the ranks as well); identity without a process group"""
+    return all_reduce_differentiable(x, op="sum")

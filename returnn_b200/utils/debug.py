@@ -123,3 +123,93 @@ class PyTracer:
                     if not lst or lst[-1] is not v:
                         lst.append(v)
         return self._trace
+
+
+def init_better_exchook():
+    """the extended exception hook for the main thread and all threads"""
+    from . import better_exchook
+
+    better_exchook.install()
+
+
+def format_signum(signum: int) -> str:
+    """``11 (SIGSEGV)``"""
+    import signal
+
+    try:
+        return "%i (%s)" % (signum, signal.Signals(signum).name)
+    except ValueError:
+        return "%i (unknown)" % signum
+
+
+def signal_handler(signum, frame):
+    """prints the stacks of all threads, then re-raises the signal with the default action"""
+    import os
+    import signal
+    import sys
+
+    print("Signal handler: got signal %s" % format_signum(signum), file=sys.stderr)
+    dump_all_thread_tracebacks(file=sys.stderr)
+    signal.signal(signum, signal.SIG_DFL)
+    os.kill(os.getpid(), signum)
+
+
+def install_signal_handler_if_default(signum: int, exceptions_are_fatal: bool = False) -> bool:
+    """:func:`signal_handler` for ``signum`` unless a handler other than the default is installed already"""
+    import signal
+
+    try:
+        if signal.getsignal(signum) == signal.SIG_DFL:
+            signal.signal(signum, signal_handler)
+            return True
+    except Exception:
+        if exceptions_are_fatal:
+            raise
+    return False
+
+
+def install_lib_sig_segfault():
+    """the native handler that prints a C-level backtrace on SIGSEGV / SIGBUS / SIGILL / SIGFPE / SIGABRT"""
+    return install_native_signal_handler()
+
+
+def setup_warn_with_traceback():
+    """every ``warnings.warn`` prints the Python stack of its origin"""
+    import sys
+    import traceback
+    import warnings
+
+    def warn_with_traceback(message, category, filename, lineno, file=None, line=None):
+        out = file if file is not None and hasattr(file, "write") else sys.stderr
+        traceback.print_stack(file=out)
+        out.write(warnings.formatwarning(message, category, filename, lineno, line))
+
+    warnings.showwarning = warn_with_traceback
+
+
+def init_cuda_not_in_main_proc_check():
+    """after this, initialising CUDA in this process raises (for a parent that must leave the GPUs to its children)"""
+    import torch
+
+    def _refuse(*_a, **_kw):
+        raise RuntimeError("CUDA must not be initialised in this process (init_cuda_not_in_main_proc_check)")
+
+    torch.cuda._lazy_init = _refuse  # type: ignore[assignment]
+
+
+def init_ipython_kernel():
+    """an IPython kernel in a background thread to attach to the running process (needs ``ipykernel``)"""
+    try:
+        import ipykernel.kernelapp  # noqa: F401
+    except ImportError:
+        print("init_ipython_kernel: ipykernel is not installed")
+        return
+    import threading
+    from ipykernel.kernelapp import IPKernelApp
+
+    def run():
+        app = IPKernelApp.instance()
+        app.initialize([])
+        app.start()
+
+    threading.Thread(target=run, name="IPython kernel", daemon=True).start()

@@ -477,3 +477,32 @@ def test_basic_helpers(tmp_path, capsys):
         U.hdf5_strings(h, "labels", ["a", "bcd"])
     assert U.hdf5_dimension(str(tmp_path / "t.hdf"), "numLabels") == 7 and U.hdf5_dimension(str(tmp_path / "t.hdf"), "inputs") == 5
     assert U.hdf5_shape(str(tmp_path / "t.hdf"), "inputs") == (5, 3)
+
+
+def test_small_named_helpers_of_updater_debug_and_diagnosis(capsys):
+    import signal
+    import torch
+    import returnn_b200.frontend as rf
+    from returnn_b200.torch.updater import wrap_user_blacklist_wd_modules
+    from returnn_b200.torch.util.distributed import all_reduce_sum
+    from returnn_b200.torch.util.diagnose_gpu import print_relevant_env_vars
+    from returnn_b200.utils import debug as D
+
+    assert torch.nn.LayerNorm in wrap_user_blacklist_wd_modules(None) and rf.LayerNorm in wrap_user_blacklist_wd_modules(None)
+    assert wrap_user_blacklist_wd_modules(["rf.Embedding", "torch.nn.Conv1d", rf.BatchNorm]) == (rf.Embedding, torch.nn.Conv1d, rf.BatchNorm)
+    with pytest.raises(AssertionError):
+        wrap_user_blacklist_wd_modules(["builtins.dict"])
+    x = torch.ones(3, requires_grad=True)
+    y = all_reduce_sum(x)
+    y.sum().backward()
+    assert y.tolist() == [1.0, 1.0, 1.0] and x.grad.tolist() == [1.0, 1.0, 1.0]
+    print_relevant_env_vars()
+    assert capsys.readouterr().out
+    assert D.format_signum(int(signal.SIGSEGV)) == "%i (SIGSEGV)" % int(signal.SIGSEGV)
+    old = signal.getsignal(signal.SIGUSR2)
+    try:
+        signal.signal(signal.SIGUSR2, signal.SIG_DFL)
+        assert D.install_signal_handler_if_default(signal.SIGUSR2) and signal.getsignal(signal.SIGUSR2) is D.signal_handler
+        assert not D.install_signal_handler_if_default(signal.SIGUSR2)
+    finally:
+        signal.signal(signal.SIGUSR2, old)
