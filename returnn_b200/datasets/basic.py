@@ -863,6 +863,19 @@ def init_dataset(kwargs: Union[Dict[str, Any], str, Callable, Dataset], extra_kw
     return obj
 
 
+def extend_dataset_dict_from_parent_dataset(dataset_dict: Dict[str, Any], parent_dataset: Optional[Dataset]) -> Dict[str, Any]:
+    """
+    What a wrapping dataset hands down to the dataset it creates: options that must agree between the two (the per-rank seed offset), unless
+    the inner description sets them itself. Parity: returnn/datasets/basic.py:1625.
+
+    :return: a copy of ``dataset_dict`` with those options filled in
+    """
+    res = dict(dataset_dict)
+    if parent_dataset is not None and "random_seed_offset" not in res:
+        res["random_seed_offset"] = parent_dataset.random_seed_offset
+    return res
+
+
 def init_dataset_via_str(config_str: str, config=None, cache_byte_size=None, **kwargs) -> Dataset:
     """
     Legacy: ``"<Class>:<args>"`` or a comma-separated list of HDF files.

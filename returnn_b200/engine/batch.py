@@ -5,7 +5,7 @@ Parity: returnn/engine/batch.py:1-381 (BatchSeqCopyPart, Batch, BatchSetGenerato
 """
 
 from __future__ import annotations
-from typing import Iterator, List, Optional
+from typing import Sequence, Iterator, List, Optional
 from ..utils.basic import NumbersDict
 
 
@@ -165,3 +165,59 @@ class BatchSetGenerator:
     def get_current_batch_idx(self) -> int:
         """index of the next batch"""
         return self.current_batch_idx
+
+
+def batch_to_raw_dict(batch: Batch, *, dataset, extern_data=None, data_keys: Sequence[str], enforce_min_len1: bool = False, exclude_data_key=None):
+    """
+    The data of one :class:`Batch` out of the dataset as padded numpy arrays (chunks are sliced out of their sequences, frame-wise batches
+    are laid out one after the other in slice 0). Backend independent: only the copy to a device differs between engines.
+
+    :param extern_data: templates (``TensorDict``) that give the dtypes; the dataset's own dtypes if None
+    :param exclude_data_key: function ``key -> bool``: keys to leave out
+    :return: one ``[slices, max frames, ...]`` array per key, ``"<key>_seq_lens"`` per key with a time axis, ``"seq_idx"``, ``"seq_tag"``, ``"batch_dim"``
+    Parity: returnn/engine/batch.py:290.
+    """
+    import numpy
+
+    keys = [k for k in data_keys if not (exclude_data_key and exclude_data_key(k))]
+    dataset.load_seqs(batch.start_seq, batch.end_seq)
+
+    def dtype_of(k):
+        if extern_data is not None and k in extern_data.data:
+            return extern_data.data[k].dtype
+        return dataset.get_data_dtype(k)
+
+    n = batch.num_slices
+    out, lens = {}, {}
+    for k in keys:
+        if dtype_of(k) == "string":
+            out[k] = [""] * n
+            continue
+        t = int(batch.max_num_frames_per_slice[k])
+        if enforce_min_len1:
+            t = max(t, 1)
+        shape = [n, t] + list(dataset.get_data_shape(k))
+        out[k] = numpy.zeros(shape, dtype=dtype_of(k))
+        lens[k] = numpy.zeros([n], dtype="int32")
+    seq_idx, seq_tag = [-1] * n, [""] * n
+    for part in batch.seqs:
+        q = part.batch_slice
+        seq_idx[q], seq_tag[q] = part.seq_idx, dataset.get_tag(part.seq_idx)
+        for k in keys:
+            data = dataset.get_data(part.seq_idx, k)
+            if isinstance(out[k], list):
+                out[k][q] = data if isinstance(data, str) else str(data)
+                continue
+            s0, s1 = int(part.seq_start_frame[k]), int(part.seq_end_frame[k])
+            o = int(part.batch_frame_offset[k])
+            ln = s1 - s0
+            if ln > 0:
+                chunk = data[s0:s1]
+                out[k][q, o: o + chunk.shape[0]] = chunk  # a chunk that reaches past the sequence end leaves zeros
+            lens[k][q] = max(int(lens[k][q]), o + ln)
+    for k, v in lens.items():
+        out["%s_seq_lens" % k] = v
+    out["seq_idx"] = numpy.array(seq_idx, dtype="int32")
+    out["seq_tag"] = numpy.array(seq_tag)
+    out["batch_dim"] = numpy.array(n, dtype="int32")
+    return out

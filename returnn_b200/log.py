@@ -232,3 +232,29 @@ def wrap_log_streams(alt_stream, also_sys_stdout: bool = False, tmp_replace_attr
         for k, v in old.items():
             setattr(log, k, v)
         sys.stdout = old_stdout
+
+
+class StdoutHandler(logging.StreamHandler):
+    """a stream handler that writes to whatever ``sys.stdout`` is at the time of the record (tests and notebooks replace it)"""
+
+    def __init__(self):
+        super().__init__(sys.stdout)
+
+    @property
+    def stream(self):
+        """the current ``sys.stdout``"""
+        return sys.stdout
+
+    @stream.setter
+    def stream(self, _value):
+        pass  # the base class constructor assigns it; the property above wins
+
+
+class StreamDummy:
+    """discards everything written to it"""
+
+    def write(self, msg):
+        """ignored"""
+
+    def flush(self):
+        """nothing to flush"""

@@ -19,6 +19,17 @@ from typing import Any, Callable, Dict, List, Optional, Sequence, Union
 import copy
 
 
+class WrapEpochValue:
+    """a value of the model description that depends on the pretrain epoch: ``WrapEpochValue(lambda epoch: ...)``"""
+
+    def __init__(self, func):
+        self.func = func
+
+    def get_value(self, epoch: int):
+        """``func(epoch=epoch)``"""
+        return self.func(epoch=epoch)
+
+
 class Pretrain:
     """list of per-step network dicts + repetitions"""
 

@@ -113,3 +113,20 @@ class ReturnnDatasetPerEpochMapDataPipe(torch.utils.data.Dataset):
         corpus_seq_idx = self._dataset.get_corpus_seq_idx(index)
         seq = self._dataset.get_corpus_seq(corpus_seq_idx)
         return seq.features
+
+
+class ReturnnDatasetFullMapDataPipe(torch.utils.data.Dataset):
+    """
+    Map-style view of a whole dataset in its corpus order (``dataset.have_get_corpus_seq()`` must hold): index -> ``{key: array}``.
+    Ordering and shuffling are left to the torch side of the pipeline. Parity: returnn/torch/data/returnn_dataset_wrapper.py:194.
+    """
+
+    def __init__(self, returnn_dataset):
+        assert returnn_dataset.have_get_corpus_seq(), "%r cannot be read by corpus index" % returnn_dataset
+        self._dataset = returnn_dataset
+
+    def __len__(self) -> int:
+        return self._dataset.get_total_num_seqs()
+
+    def __getitem__(self, index: int):
+        return self._dataset.get_corpus_seq(index).features

@@ -698,3 +698,52 @@ def test_nltk_timit_layout_and_sequential_postprocessing(tmp_path):
     assert seq(3, epoch=5) == 11 and not seq.preserves_num_seqs
     add_epoch.preserves_num_seqs = True
     assert Sequential(double, add_epoch).preserves_num_seqs
+
+
+def test_batch_to_raw_dict_and_small_dataset_helpers():
+    import io
+    import logging
+    import sys
+    from returnn_b200.engine.batch import Batch, batch_to_raw_dict
+    from returnn_b200.datasets.basic import init_dataset, extend_dataset_dict_from_parent_dataset
+    from returnn_b200.datasets.util.strings import str_to_numpy_array
+    from returnn_b200.torch.data.returnn_dataset_wrapper import ReturnnDatasetFullMapDataPipe
+    from returnn_b200.pretrain import WrapEpochValue
+    from returnn_b200.log import StdoutHandler, StreamDummy
+
+    seqs = [{"data": numpy.arange(10, dtype="float32").reshape(5, 2), "classes": numpy.array([1, 2, 3], dtype="int32")},
+            {"data": numpy.ones((2, 2), dtype="float32"), "classes": numpy.array([4], dtype="int32")}]
+    ds = init_dataset({"class": "StaticDataset", "data": seqs, "output_dim": {"data": (2, 2), "classes": (5, 1)}})
+    ds.init_seq_order(epoch=1)
+    b = Batch()
+    from returnn_b200.utils.basic import NumbersDict as ND
+
+    b.add_sequence_as_slice(0, ND({"data": 1, "classes": 0}), ND({"data": 3, "classes": 3}))  # a chunk of sequence 0
+    b.add_sequence_as_slice(1, ND({"data": 0, "classes": 0}), ND({"data": 2, "classes": 1}))
+    raw = batch_to_raw_dict(b, dataset=ds, data_keys=["data", "classes"])
+    assert raw["data"].shape == (2, 3, 2) and raw["data"][0].tolist() == [[2, 3], [4, 5], [6, 7]] and raw["data"][1, 2].tolist() == [0, 0]
+    assert raw["data_seq_lens"].tolist() == [3, 2] and raw["classes_seq_lens"].tolist() == [3, 1] and raw["classes"][1].tolist() == [4, 0, 0]
+    assert raw["seq_idx"].tolist() == [0, 1] and int(raw["batch_dim"]) == 2 and len(raw["seq_tag"]) == 2
+    fw = Batch()
+    fw.add_frames(0, ND({"data": 0, "classes": 0}), ND({"data": 5, "classes": 3}))
+    fw.add_frames(1, ND({"data": 0, "classes": 0}), ND({"data": 2, "classes": 1}))
+    raw2 = batch_to_raw_dict(fw, dataset=ds, data_keys=["data"])
+    assert raw2["data"].shape == (1, 7, 2) and raw2["data_seq_lens"].tolist() == [7] and raw2["data"][0, 5].tolist() == [1, 1]
+    parent = init_dataset({"class": "StaticDataset", "data": seqs, "output_dim": {"data": (2, 2), "classes": (5, 1)}, "random_seed_offset": 77})
+    assert extend_dataset_dict_from_parent_dataset({"class": "X"}, parent) == {"class": "X", "random_seed_offset": 77}
+    assert extend_dataset_dict_from_parent_dataset({"class": "X", "random_seed_offset": 1}, parent)["random_seed_offset"] == 1
+    assert str_to_numpy_array("abc").dtype.kind == "U" and str_to_numpy_array("abc").shape == ()
+    pipe = ReturnnDatasetFullMapDataPipe(ds)
+    assert len(pipe) == 2 and pipe[1]["classes"].tolist() == [4]
+    assert WrapEpochValue(lambda epoch: epoch * 2).get_value(3) == 6
+    buf = io.StringIO()
+    old = sys.stdout
+    try:
+        h = StdoutHandler()
+        sys.stdout = buf
+        logging.Logger("t").handle  # noqa: B018
+        h.emit(logging.LogRecord("t", logging.INFO, __file__, 1, "hello %s", ("x",), None))
+    finally:
+        sys.stdout = old
+    assert "hello x" in buf.getvalue()
+    StreamDummy().write("ignored")
