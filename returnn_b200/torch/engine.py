@@ -300,7 +300,14 @@ class Engine(EngineBase):
         elapsed_computation_time = 0.0
         self._pt_model.train()
         self._maybe_reset_dev_memory_caches()
-        accum_grad_multiple_step = self.config.int("accum_grad_multiple_step", 1)
+        # an int, or a function (epoch, epoch_continuous, global_train_step) -> int evaluated every step
+        accum_grad_multiple_step_dyn = None
+        accum_cfg = self.config.typed_dict.get("accum_grad_multiple_step")
+        if accum_cfg is not None and not isinstance(accum_cfg, int):
+            assert callable(accum_cfg), "accum_grad_multiple_step must be an int or a function"
+            accum_grad_multiple_step, accum_grad_multiple_step_dyn = 0, accum_cfg
+        else:
+            accum_grad_multiple_step = self.config.int("accum_grad_multiple_step", 1)
         dist = self._torch_distributed_ctx
         profiler = self._make_profiler()
         total_frames = NumbersDict(0)
@@ -443,6 +450,10 @@ class Engine(EngineBase):
                     f = train_ctx.losses[n].get_inv_norm_factor()
                     inv_list.append(f.raw_tensor.detach().float().reshape(()).to(summed[0].device) if isinstance(f, Tensor) else None)
                 stacked = torch.stack(summed + [x for x in inv_list if x is not None]) if summed else None
+                if accum_grad_multiple_step_dyn is not None:
+                    accum_grad_multiple_step = int(accum_grad_multiple_step_dyn(
+                        epoch=self.epoch, epoch_continuous=(self.epoch - 1 + complete_frac) if complete_frac >= 0 else None,
+                        global_train_step=self.global_train_step, **get_fwd_compat_kwargs()))
                 do_sync = (cur_count_grad_accum + 1) >= accum_grad_multiple_step
                 if dist:
                     dist.prepare_backward(sync=do_sync)
@@ -450,9 +461,7 @@ class Engine(EngineBase):
                     ctx_mgr = self._ddp_pt_model.no_sync() if (self._ddp_pt_model is not None and not do_sync) else contextlib.nullcontext()
                     with ctx_mgr:
                         if isinstance(total_loss, Tensor) and total_loss.raw_tensor.requires_grad:
-                            loss_raw = total_loss.raw_tensor
-                            if accum_grad_multiple_step > 1:
-                                loss_raw = loss_raw / accum_grad_multiple_step
+                            loss_raw = total_loss.raw_tensor  # the gradients of the accumulated steps add up (no division by their number)
                             if self._grad_scaler is not None:
                                 self._grad_scaler.scale(loss_raw).backward()
                             else:
