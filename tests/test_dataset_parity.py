@@ -199,3 +199,57 @@ def test_variable_assignment_targets_follow_the_query():
         value = stores[key]
         close = text.index(")", q)
         assert target[:close].strip() == "" and target[close: close + len(value) + 1] == value + "." and target[close + len(value) + 1:].strip() == ""
+
+
+_TRAJ_CASES = {
+    "adam": [],
+    "adamw_decay_clip": ["++optimizer", "{'class': 'adamw', 'weight_decay': 0.1}", "++gradient_clip_global_norm", "0.5"],
+    "sgd_accum2": ["++optimizer", "{'class': 'sgd'}", "++accum_grad_multiple_step", "2", "++learning_rate", "0.05"],
+}
+
+
+@needs_ref
+@pytest.mark.parametrize("case", sorted(_TRAJ_CASES))
+def test_training_trajectory_equals_reference_engine(tmp_path, case):
+    """
+    Same config, same initial parameters, same data: after two epochs on the CPU the parameters and the scores in the learning-rate file
+    of this engine equal those of the reference engine (data order, batching, loss normalisation, gradient accumulation, clipping, weight
+    decay groups and the optimizer all have to agree for that).
+    """
+    import torch
+
+    cfg = tmp_path / "net.config"
+    cfg.write_text(_CFG)
+    g = torch.Generator().manual_seed(11)
+    init = {"l1.weight": torch.randn(9, 16, generator=g) * 0.3, "l1.bias": torch.zeros(16), "l2.weight": torch.randn(16, 2, generator=g) * 0.3, "l2.bias": torch.zeros(2)}
+    torch.save({"model": init, "epoch": 1, "step": 0}, str(tmp_path / "init.001.pt"))
+    extra = _TRAJ_CASES[case] + ["++import_model_train_epoch1", str(tmp_path / "init.001"), "++learning_rate_control", "constant"]
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    # reference
+    ref_model, ref_lr = str(tmp_path / "ref_model"), str(tmp_path / "ref_lr.txt")
+    script = tmp_path / "ref_train.py"
+    text = _REF_TRAIN % dict(ref=os.path.join(_ROOT, "baseline", "_ref"), deps=os.path.join(_ROOT, "baseline", "deps"), cfg=str(cfg), model=ref_model, lr=ref_lr)
+    text = text.replace('"++log_verbosity", "3"])', '"++log_verbosity", "3"] + %r)' % (extra,))
+    script.write_text(text)
+    p = subprocess.run([sys.executable, str(script)], cwd=str(tmp_path), env=env, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, (p.stdout + p.stderr)[-3000:]
+    # this engine
+    our_model, our_lr = str(tmp_path / "our_model"), str(tmp_path / "our_lr.txt")
+    p2 = subprocess.run([sys.executable, os.path.join(_ROOT, "rnn.py"), str(cfg), "++model", our_model, "++learning_rate_file", our_lr, "++num_epochs", "2",
+                         "++device", "cpu", "++log_verbosity", "3"] + extra, cwd=str(tmp_path), env=dict(env, PYTHONPATH=_ROOT), capture_output=True, text=True,
+                        timeout=600)
+    assert p2.returncode == 0, (p2.stdout + p2.stderr)[-3000:]
+    a = torch.load(ref_model + ".002.pt", map_location="cpu", weights_only=False)
+    b = torch.load(our_model + ".002.pt", map_location="cpu", weights_only=False)
+    assert a["step"] == b["step"] and sorted(a["model"]) == sorted(b["model"])
+    for k in a["model"]:
+        assert not torch.equal(a["model"][k], init[k])  # it did train
+        torch.testing.assert_close(b["model"][k], a["model"][k], atol=2e-5, rtol=2e-4, msg=lambda m, k=k: "%s: %s" % (k, m))
+    from returnn_b200.learning_rate_control import load_learning_rate_control_from_config
+    from returnn_b200.config import Config
+
+    ra = load_learning_rate_control_from_config(Config({"learning_rate_file": ref_lr, "learning_rate": 0.01})).epoch_data
+    rb = load_learning_rate_control_from_config(Config({"learning_rate_file": our_lr, "learning_rate": 0.01})).epoch_data
+    for ep in (1, 2):
+        for key in ("train_loss_ce", "dev_loss_ce"):
+            assert abs(ra[ep].error[key] - rb[ep].error[key]) < 1e-4 * max(1.0, abs(ra[ep].error[key])), (ep, key, ra[ep].error, rb[ep].error)
