@@ -91,29 +91,22 @@ class ChunkingIterDataPipe(torch.utils.data.IterableDataset):
                 else:
                     chunking_data_keys = list(data_keys)
                 assert chunking_data_keys, "chunking: no data key to chunk"
-            ref_key = chunking_data_keys[0]
-            size0 = self._chunk_size[ref_key]
-            step0 = self._chunk_step[ref_key]
-            seq_len0 = data_dict[ref_key].shape[0]
-            n_chunks = max((max(seq_len0 - size0, 0) + step0 - 1) // step0 + 1, 1)
-            # a trailing chunk shorter than min_chunk_size is dropped (unless it is the only one)
-            for c in range(n_chunks):
-                chunk = {}
-                ok = True
-                for k, v in data_dict.items():
-                    if k in chunking_data_keys:
-                        size, step = self._chunk_size[k], self._chunk_step[k]
-                        start = c * step
-                        piece = v[start: start + size]
-                        if c > 0 and len(piece) <= self._min_chunk_size.get(k, self._min_chunk_size.value or 0):
-                            ok = False
-                            break
-                        chunk[k] = piece
-                    else:
-                        chunk[k] = v
-                if not ok:
-                    continue
-                if "seq_tag" in chunk and n_chunks > 1:
+            # A chunk starts at every multiple of the step inside the sequence (so the tail of a sequence also comes as shorter chunks
+            # of its own); chunks shorter than min_chunk_size are left out. All chunked keys must give the same number of chunks.
+            pieces: Dict[str, List[numpy.ndarray]] = {}
+            n_chunks = None
+            for k in chunking_data_keys:
+                size, step = self._chunk_size[k], self._chunk_step[k]
+                min_size = self._min_chunk_size.get(k, self._min_chunk_size.value or 0)
+                v = data_dict[k]
+                ks = [v[start: start + size] for start in range(0, len(v), step)]
+                ks = [p for p in ks if len(p) >= min_size]
+                assert n_chunks is None or n_chunks == len(ks), "chunking: %i chunks for %r, %i for %r" % (len(ks), k, n_chunks, chunking_data_keys[0])
+                n_chunks = len(ks)
+                pieces[k] = ks
+            for c in range(n_chunks or 0):
+                chunk = {k: (pieces[k][c] if k in pieces else v) for k, v in data_dict.items()}
+                if "seq_tag" in chunk:  # for every sequence, also the ones of a single chunk: all samples of a batch carry the same keys
                     chunk["chunk_idx"] = numpy.array(c, dtype="int32")
                 yield chunk
 

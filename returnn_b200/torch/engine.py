@@ -166,7 +166,7 @@ class Engine(EngineBase):
                 self.eval_datasets[name] = init_dataset(opts, default_kwargs={"name": name})
         self._train_dataloader = self._create_data_loader(train_data, train=True) if train_data else None
         for name, ds in self.eval_datasets.items():
-            self._eval_dataloaders[name] = self._create_data_loader(ds, train=False, dataset_name=name)
+            self._eval_dataloaders[name] = self._create_data_loader(ds, train=False, dataset_name=name, chunk=self.config.bool("chunk_eval", True))
         self._start_epoch = self.get_train_start_epoch(self.config)
         self._final_epoch = self.config_get_final_epoch(self.config)
         self.init_network_from_config(config=config)
@@ -800,7 +800,8 @@ class Engine(EngineBase):
         self._maybe_reset_dev_memory_caches()
 
     # -- data loader -------------------------------------------------------------------------------------------------
-    def _create_data_loader(self, dataset: Dataset, *, train: bool = False, dataset_name: Optional[str] = None, dataset_init_epoch: bool = True):
+    def _create_data_loader(self, dataset: Dataset, *, train: bool = False, dataset_name: Optional[str] = None, dataset_init_epoch: bool = True,
+                            chunk: Optional[bool] = None):
         """dataset -> pipes -> DataLoader"""
         loader_opts = dict(self.config.typed_value("torch_dataloader_opts") or {})
         num_workers = loader_opts.get("num_workers", 0)
@@ -820,7 +821,9 @@ class Engine(EngineBase):
             wrapped = data_pipeline.LenFilterDataPipe(wrapped, min_seq_length=self._min_seq_length, max_seq_length=self._max_seq_length)
         chunking = self.config.typed_value("chunking", None)
         min_chunk_size = self.config.typed_value("min_chunk_size", 0)
-        if chunking and train:
+        # training data is chunked; the evaluation data sets of a training run as well (as in the reference, so that their scores are
+        # comparable with the training scores; ``chunk_eval = False`` scores whole sequences); forward / search never
+        if chunking and (train if chunk is None else chunk):
             wrapped = data_pipeline.ChunkingIterDataPipe(wrapped, chunking, min_chunk_size=min_chunk_size)
         batches = data_pipeline.get_batching_iterable_dataset_from_config(dataset=wrapped, config=self.config, train=train)
         online_shuffle_batches = self.config.typed_value("online_shuffle_batches", None)

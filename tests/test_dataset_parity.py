@@ -205,7 +205,13 @@ _TRAJ_CASES = {
     "adam": [],
     "adamw_decay_clip": ["++optimizer", "{'class': 'adamw', 'weight_decay': 0.1}", "++gradient_clip_global_norm", "0.5"],
     "sgd_accum2": ["++optimizer", "{'class': 'sgd'}", "++accum_grad_multiple_step", "2", "++learning_rate", "0.05"],
+    "chunking_random_order": ["++batching", "random", "++max_seqs", "7"],  # plus chunking = "10:5" in the config text (see _TRAJ_CFG_EXTRA)
+    "newbob_decay": ["++learning_rate_control", "newbob_abs", "++newbob_learning_rate_decay", "0.5",  # threshold in _TRAJ_CFG_EXTRA
+                     "++learning_rate_control_relative_error_relative_lr", "False", "++learning_rate_control_min_num_epochs_per_new_lr", "0", "++num_epochs", "3"],
 }
+
+
+_TRAJ_CFG_EXTRA = {"chunking_random_order": 'chunking = "10:5"\n', "newbob_decay": "newbob_error_threshold = -10.0\n"}
 
 
 @needs_ref
@@ -219,11 +225,11 @@ def test_training_trajectory_equals_reference_engine(tmp_path, case):
     import torch
 
     cfg = tmp_path / "net.config"
-    cfg.write_text(_CFG)
+    cfg.write_text(_CFG + _TRAJ_CFG_EXTRA.get(case, ""))
     g = torch.Generator().manual_seed(11)
     init = {"l1.weight": torch.randn(9, 16, generator=g) * 0.3, "l1.bias": torch.zeros(16), "l2.weight": torch.randn(16, 2, generator=g) * 0.3, "l2.bias": torch.zeros(2)}
     torch.save({"model": init, "epoch": 1, "step": 0}, str(tmp_path / "init.001.pt"))
-    extra = _TRAJ_CASES[case] + ["++import_model_train_epoch1", str(tmp_path / "init.001"), "++learning_rate_control", "constant"]
+    extra = ["++import_model_train_epoch1", str(tmp_path / "init.001"), "++learning_rate_control", "constant"] + _TRAJ_CASES[case]
     env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
     # reference
     ref_model, ref_lr = str(tmp_path / "ref_model"), str(tmp_path / "ref_lr.txt")
@@ -251,5 +257,9 @@ def test_training_trajectory_equals_reference_engine(tmp_path, case):
     ra = load_learning_rate_control_from_config(Config({"learning_rate_file": ref_lr, "learning_rate": 0.01})).epoch_data
     rb = load_learning_rate_control_from_config(Config({"learning_rate_file": our_lr, "learning_rate": 0.01})).epoch_data
     for ep in (1, 2):
+        assert ra[ep].learning_rate == pytest.approx(rb[ep].learning_rate), (ep, ra[ep].learning_rate, rb[ep].learning_rate)
         for key in ("train_loss_ce", "dev_loss_ce"):
             assert abs(ra[ep].error[key] - rb[ep].error[key]) < 1e-4 * max(1.0, abs(ra[ep].error[key])), (ep, key, ra[ep].error, rb[ep].error)
+    if case == "newbob_decay":
+        # no epoch can improve by 10: with two epochs of scores the rate halves, in both engines
+        assert ra[3].learning_rate == pytest.approx(rb[3].learning_rate) and rb[3].learning_rate == pytest.approx(0.005)
