@@ -111,6 +111,12 @@ def _padded_hidden(x: torch.Tensor, w_rec: torch.Tensor) -> int:
     return Hp if fn(int(x.shape[0]), int(per), int(Hp)) else 0
 
 
+def _pad_input(x: torch.Tensor, w_ff: torch.Tensor):
+    """input width up to a multiple of 8 (the 16-byte pitch rule of the tensor maps) with zero features and zero weight columns: same product"""
+    n = -(-x.shape[-1] // 8) * 8 - x.shape[-1]
+    return torch.nn.functional.pad(x, (0, n)), torch.nn.functional.pad(w_ff, (0, n))
+
+
 def _pad_params(w_ff, w_rec, bias, H: int, Hp: int):
     """gate-wise zero padding: [4H, in] -> [4Hp, in], [4H, H] -> [4Hp, Hp], [4H] -> [4Hp]"""
     F = torch.nn.functional
@@ -133,6 +139,8 @@ def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_re
     :param lens: [B] int32 (on any device) or None
     :return: y [T, B, H], h_T [B, H], c_T [B, H]
     """
+    if x.is_cuda and x.shape[-1] % 8:
+        x, w_ff = _pad_input(x, w_ff)
     if x.is_cuda:
         from . import lstm_native as _n
 
@@ -165,14 +173,14 @@ def lstm(x: torch.Tensor, lens: Optional[torch.Tensor], w_ff: torch.Tensor, w_re
     if lens is not None:
         packed = torch.nn.utils.rnn.pack_padded_sequence(xx, lens.cpu().to(torch.int64), enforce_sorted=False)
         out, hT, cT = torch.lstm(packed.data, packed.batch_sizes, (h0.unsqueeze(0).to(dt), c0.unsqueeze(0).to(dt)), ws,
-                                 bias is not None, 1, 0.0, False, False)
+                                 bias is not None, 1, 0.0, torch.is_grad_enabled(), False)  # "train": cuDNN keeps what its backward needs
         y, _ = torch.nn.utils.rnn.pad_packed_sequence(
             torch.nn.utils.rnn.PackedSequence(out, packed.batch_sizes, packed.sorted_indices, packed.unsorted_indices), total_length=T)
         if packed.unsorted_indices is not None:
             hT = hT.index_select(1, packed.unsorted_indices)
             cT = cT.index_select(1, packed.unsorted_indices)
     else:
-        y, hT, cT = torch.lstm(xx, (h0.unsqueeze(0).to(dt), c0.unsqueeze(0).to(dt)), ws, bias is not None, 1, 0.0, False, False, False)
+        y, hT, cT = torch.lstm(xx, (h0.unsqueeze(0).to(dt), c0.unsqueeze(0).to(dt)), ws, bias is not None, 1, 0.0, torch.is_grad_enabled(), False, False)
     if reverse:
         y = _reverse_padded(y, lens)
     return y, hT[0], cT[0]
@@ -190,6 +198,9 @@ def blstm(x: torch.Tensor, lens: Optional[torch.Tensor], fw, bw, h0_fw, c0_fw, h
     :param fw: (w_ff, w_rec, bias) of the direction that runs forward in time; ``bw``: of the reversed one
     :return: (y_fw, h_T, c_T), (y_bw, h_T, c_T)
     """
+    if x.is_cuda and x.shape[-1] % 8:
+        x, w_fw = _pad_input(x, fw[0])
+        fw, bw = (w_fw, fw[1], fw[2]), (torch.nn.functional.pad(bw[0], (0, x.shape[-1] - bw[0].shape[1])), bw[1], bw[2])
     if x.is_cuda:
         from . import lstm_native as _n
 

@@ -167,3 +167,30 @@ def test_lstm_hidden_sizes_off_the_kernel_grid_run_zero_padded(T, B, I, H):
         assert float((g.float() - t.grad).abs().max()) / scale < 0.06
     y, h, c = L.lstm(x, lens, *fw, states[0], states[1])
     torch.testing.assert_close(y.float(), yfr, atol=0.05, rtol=0.03)
+
+
+@gpu
+def test_lstm_input_width_off_the_pitch_rule_and_training_through_the_fallback():
+    """9 input features (the 12AX task): the native path takes them zero-padded to 16; gradients flow, also through the cuDNN fallback (hidden 20)"""
+    from returnn_b200.ops import lstm as L
+
+    torch.manual_seed(6)
+    dev = "cuda"
+    for H in (128, 20):
+        T, B, I = 11, 4, 9
+        x = (torch.randn(T, B, I, device=dev) * 0.5).requires_grad_(True)
+        w_ff = (torch.randn(4 * H, I, device=dev) * 0.2).requires_grad_(True)
+        w_rec = (torch.randn(4 * H, H, device=dev) * 0.2).requires_grad_(True)
+        bias = (torch.randn(4 * H, device=dev) * 0.1).requires_grad_(True)
+        h0, c0 = torch.zeros(B, H, device=dev), torch.zeros(B, H, device=dev)
+        lens = torch.tensor([11, 7, 11, 2])
+        y, h, c = L.lstm(x, lens, w_ff, w_rec, bias, h0, c0)
+        y.float().square().sum().backward()
+        got = [t.grad.clone() for t in (x, w_ff, w_rec, bias)]
+        for t in (x, w_ff, w_rec, bias):
+            t.grad = None
+        yr, hr, cr = L.lstm_reference(x, lens, w_ff, w_rec, bias, h0, c0)
+        yr.square().sum().backward()
+        torch.testing.assert_close(y.float(), yr, atol=0.05, rtol=0.03)
+        for g, t in zip(got, (x, w_ff, w_rec, bias)):
+            assert float((g.float() - t.grad).abs().max()) / (float(t.grad.abs().max()) + 1e-6) < 0.06
