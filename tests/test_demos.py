@@ -54,3 +54,16 @@ def test_demo_scripts_run(script):
         assert "epoch 2 seq 4" in res.stdout and "data (" in res.stdout
     else:
         assert "output 'output': (7, 2)" in res.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("config", ["demo-lstm.12ax.config", "demo-blstm-ctc.config", "demo-conformer-ctc.config", "demo-enc-dec-copy.config", "demo-rf.config",
+                                    "demo-torch.config"])
+def test_demo_trains_one_epoch_on_the_gpu(config, tmp_path):
+    """the same configs on the GPU: the generic RF path on the own kernels (LSTM with 9 inputs and 100 units, odd widths, small vocabularies)"""
+    cmd = [sys.executable, os.path.join(_ROOT, "rnn.py"), os.path.join(_ROOT, "demos", config), "++num_epochs", "1", "++device", "cuda", "++log_verbosity", "3",
+           "++model", str(tmp_path / "model")]
+    proc = subprocess.run(cmd, cwd=_ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, timeout=900)
+    out = proc.stdout.decode("utf8", "replace")
+    assert proc.returncode == 0 and "Finished training at epoch 1" in out, out[-3000:]
+    assert (tmp_path / "model.001.pt").exists()
