@@ -21,6 +21,17 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if x.is_cuda and x.dtype == torch.bfloat16 or (x.is_cuda and torch.is_autocast_enabled() and x.is_floating_point()):
         from . import gemm as _gemm
 
+        if _gemm.available(x) and _gemm.ENABLED and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 != 0 and weight.shape[1] >= 64 and activation in (
+                None, "relu"):
+            # An output width off the 16-byte pitch rule (a vocabulary of 10001 classes): zero columns up to the next multiple of 8, the own
+            # GEMM on that, and the extra outputs cut off again. The padded copy of the weight costs a few microseconds; the library's path
+            # for such widths runs at a tenth of the tensor-core rate. (Activations other than relu could map the zero columns to non-zero
+            # values, which the cut removes anyway, but are left to the library path to keep this rule simple.)
+            n = weight.shape[1]
+            pad = -(-n // 8) * 8 - n
+            w_p = torch.nn.functional.pad(weight, (0, pad))
+            b_p = torch.nn.functional.pad(bias, (0, pad)) if bias is not None else None
+            return _gemm.linear_bf16(x, w_p, b_p, activation)[..., :n]
         if _gemm.available(x) and _gemm.ENABLED and x.shape[-1] % 8 == 0 and weight.shape[1] % 8 == 0:
             if x.requires_grad and torch.is_grad_enabled() and weight.requires_grad:
                 # parameters of a flat arena (fused AdamW): read the bf16 copy the optimizer maintains instead of casting the fp32

@@ -343,3 +343,28 @@ def test_rf_matmul_batched_uses_own_gemm():
     assert _lib.launch_count() == n0 + 1 and e.dims == (b_, h, t, t2)
     ref = torch.matmul(q.raw_tensor.float(), k.raw_tensor.float().transpose(-1, -2))
     torch.testing.assert_close(e.raw_tensor.float(), ref, atol=0.1, rtol=0.02)
+
+
+@gpu
+def test_linear_with_output_width_off_the_pitch_rule_runs_on_the_own_gemm():
+    """10001 classes: zero-padded to 10008 on the own GEMM, cut back; values and gradients as torch in fp32"""
+    from returnn_b200.ops import linear as L, _lib, gemm
+
+    torch.manual_seed(8)
+    x = (torch.randn(300, 256, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(256, 1001, device="cuda") * 0.1).requires_grad_(True)
+    b = (torch.randn(1001, device="cuda") * 0.1).requires_grad_(True)
+    n0 = _lib.launch_count()
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        y = L.linear(x, w, b)
+    assert y.shape == (300, 1001) and _lib.launch_count() > n0
+    g = torch.randn(300, 1001, device="cuda")
+    (y.float() * g).sum().backward()
+    gemm.check_status()
+    got = [t.grad.float().clone() for t in (x, w, b)]
+    xf, wf, bf_ = x.detach().float().requires_grad_(True), w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    ref = xf @ wf + bf_
+    (ref * g).sum().backward()
+    torch.testing.assert_close(y.float(), ref, atol=0.05, rtol=0.02)
+    for a, r in zip(got, (xf.grad, wf.grad, bf_.grad)):
+        assert float((a - r).abs().max()) / (float(r.abs().max()) + 1e-6) < 0.02
