@@ -558,3 +558,154 @@ class ExternSprintDataset(SprintDatasetBase):
             self._stop_child()
         except Exception:
             pass
+
+
+class SprintCacheDataset(Dataset):
+    """
+    Reads Sprint archives (single files or bundles) directly: feature caches as float32 ``[T, D]`` and alignment caches as class
+    labels ``[T]`` (mapped through an allophone labeling: state tying or phoneme list). No RASR process is involved.
+
+    ``data`` maps a data key to reader options: ``{"data": {"filename": "features.cache"}, "classes": {"filename": "align.cache",
+    "allophone_labeling": {"silence_phone": "si", "allophone_file": ..., "state_tying_file": ...}}}``; the type ("feat" / "align") is
+    taken from the key or from the presence of ``allophone_labeling`` unless ``data_type`` names it.
+
+    Every key must hold the same entry names; the sequence order (sorting by entry size) works from the table of contents alone.
+
+    Parity: returnn/datasets/sprint.py (``SprintCacheDataset`` :1064, its ``SprintCacheReader`` :1071).
+    """
+
+    class SprintCacheReader:
+        """one archive (or bundle) behind one data key"""
+
+        def __init__(self, data_key: str, filename: str, data_type: Optional[str] = None, allophone_labeling: Optional[dict] = None):
+            from ..sprint.cache import open_file_archive, AllophoneLabeling
+
+            self.data_key = data_key
+            self.sprint_cache = open_file_archive(filename)
+            if not data_type:
+                data_type = {"data": "feat", "classes": "align"}.get(data_key, "align" if allophone_labeling else "feat")
+            assert data_type in ("feat", "align"), "%r: data_type %r" % (data_key, data_type)
+            self.type = data_type
+            self.allophone_labeling = None
+            if allophone_labeling:
+                self.allophone_labeling = AllophoneLabeling(**allophone_labeling)
+                self.sprint_cache.set_allophones(self.allophone_labeling.allophone_file)
+            else:
+                assert data_type != "align", "%r: an alignment needs allophone_labeling" % data_key
+            self.content_keys = [name for name in self.sprint_cache.file_list() if not name.endswith(".attribs")]
+            if data_type == "align":
+                self.num_labels = self.allophone_labeling.num_labels
+                self.dtype = "int8" if self.num_labels < 2**7 else "int16" if self.num_labels < 2**15 else "int32"
+                self.num_dims = 1
+                if self.allophone_labeling.state_tying_by_allo_state_idx:
+                    self.type = "align_raw"  # the tying is keyed by the undivided emission index: no split per frame
+            else:
+                assert self.content_keys, "%r: empty feature cache %r" % (data_key, filename)
+                _, feats = self.sprint_cache.read(self.content_keys[0], "feat")
+                assert len(feats) > 0 and feats[0].ndim == 1
+                self.num_labels = int(feats[0].shape[0])
+                self.num_dims = 2
+                self.dtype = "float32"
+
+        def read(self, name: str) -> numpy.ndarray:
+            """:return: ``[T, D]`` features or ``[T]`` labels of the entry"""
+            res = self.sprint_cache.read(name, typ=self.type)
+            if self.type == "feat":
+                times, feats = res
+                mat = numpy.asarray(feats, dtype=self.dtype)
+                assert mat.shape == (len(times), self.num_labels), "%r: entry %r has shape %r" % (self.data_key, name, mat.shape)
+                return mat
+            assert all(w == 1 for (_, _, _, w) in res), "%r: entry %r is a soft alignment, which is not supported" % (self.data_key, name)
+            if self.type == "align_raw":
+                tying = self.allophone_labeling.state_tying_by_allo_state_idx
+                return numpy.array([tying[e] for (_, e, _, _) in res], dtype=self.dtype)
+            label = self.allophone_labeling.get_label_idx
+            return numpy.array([label(a, s) for (_, a, s, _) in res], dtype=self.dtype)
+
+    def __init__(self, data: Dict[str, dict], **kwargs):
+        super().__init__(**kwargs)
+        self.data = {key: self.SprintCacheReader(data_key=key, **opts) for key, opts in data.items()}
+        assert "data" in self.data, "%s: needs the key 'data'" % self
+        self.seq_list_original = list(self.data["data"].content_keys)
+        self.seq_list_ordered = self.seq_list_original
+        names = sorted(self.seq_list_original)
+        for key, reader in self.data.items():
+            assert sorted(reader.content_keys) == names, "%s: the entries of %r differ from those of 'data'" % (self, key)
+        self.num_outputs = {key: (r.num_labels, r.num_dims) for key, r in self.data.items()}
+        self.num_inputs = self.num_outputs["data"][0]
+        self._num_seqs = len(self.seq_list_original)
+        self._loaded: Dict[int, DatasetSeq] = {}
+        self.epoch = None
+
+    def init_seq_order(self, epoch=None, seq_list=None, seq_order=None):
+        assert seq_list is None and seq_order is None, "%s: no predefined order" % self
+        again = self.epoch is None or self.epoch != epoch
+        super().init_seq_order(epoch=epoch, seq_list=seq_list, seq_order=seq_order)
+        self.epoch = epoch
+        if not again:
+            return False
+        toc = self.data["data"].sprint_cache.ft
+        order = self.get_seq_order_for_epoch(epoch, num_seqs=len(self.seq_list_original), get_seq_len=lambda i: toc[self.seq_list_original[i]].size)
+        self.seq_list_ordered = [self.seq_list_original[i] for i in order]
+        self._num_seqs = len(self.seq_list_ordered)
+        self._loaded.clear()
+        return True
+
+    @property
+    def num_seqs(self) -> int:
+        return self._num_seqs
+
+    def get_total_num_seqs(self, *, fast: bool = False) -> int:
+        return len(self.seq_list_original)
+
+    def get_all_tags(self) -> List[str]:
+        return list(self.seq_list_original)
+
+    def supports_seq_order_sorting(self) -> bool:
+        return True
+
+    def supports_sharding(self) -> bool:
+        return True
+
+    def get_dataset_seq_for_name(self, name: str, seq_idx: int = -1) -> DatasetSeq:
+        """:return: the sequence of this entry name, all keys read"""
+        return DatasetSeq(seq_idx=seq_idx, seq_tag=name, features={key: r.read(name) for key, r in self.data.items()})
+
+    def is_cached(self, start, end):
+        return False
+
+    def _load_seqs(self, start: int, end: int):
+        for i in [i for i in self._loaded if i < start]:
+            del self._loaded[i]
+        for i in range(start, min(end, self._num_seqs)):
+            if i not in self._loaded:
+                self._loaded[i] = self.get_dataset_seq_for_name(self.seq_list_ordered[i], seq_idx=i)
+
+    def _seq(self, seq_idx: int) -> DatasetSeq:
+        if seq_idx not in self._loaded:
+            self._loaded[seq_idx] = self.get_dataset_seq_for_name(self.seq_list_ordered[seq_idx], seq_idx=seq_idx)
+        return self._loaded[seq_idx]
+
+    def get_seq_length(self, seq_idx: int):
+        return self._seq(seq_idx).num_frames
+
+    def get_data(self, seq_idx: int, key: str) -> numpy.ndarray:
+        return self._seq(seq_idx).features[key]
+
+    def get_input_data(self, seq_idx: int) -> numpy.ndarray:
+        return self.get_data(seq_idx, "data")
+
+    def get_targets(self, target: str, seq_idx: int) -> numpy.ndarray:
+        return self.get_data(seq_idx, target)
+
+    def get_data_keys(self) -> List[str]:
+        return list(self.data.keys())
+
+    def get_target_list(self) -> List[str]:
+        return [key for key, r in self.data.items() if r.type != "feat"]
+
+    def get_data_dtype(self, key: str) -> str:
+        return self.data[key].dtype
+
+    def get_tag(self, sorted_seq_idx: int) -> str:
+        return self.seq_list_ordered[sorted_seq_idx]
