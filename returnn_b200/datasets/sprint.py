@@ -126,7 +126,13 @@ class SprintDatasetBase(Dataset):
             self.num_outputs["orth_classes"] = (self.orth_vocab.num_labels, 1)
         self.num_outputs["orth"] = (256, 1)
         self._base_init()
-        self._window_reset()
+        with self._cond:
+            if not self._epoch_open:  # a producer that took its segment order from here has opened the epoch before it knows the dimensions
+                self._window_reset()
+
+    def initialize(self):
+        """no epoch-less first order here: :meth:`init_seq_order` waits for the producer, which may be the very thread that calls this"""
+        self._base_init()
 
     # -- producer side ---------------------------------------------------------------------------------------------------
     def init_sprint_epoch(self, epoch: Optional[int]):
@@ -256,7 +262,9 @@ class SprintDatasetBase(Dataset):
             self.returnn_epoch = epoch
             self.predefined_seq_list_order = list(seq_list) if seq_list is not None else None
             self._cond.notify_all()
-            while not (self._epoch_open or self._epoch_done) and not self.sprint_finalized:
+            # a producer that walks the epochs itself waits for this call and then opens the epoch: the window of its previous epoch
+            # (finished, hence "done") must not be taken for the new one
+            while not ((self._epoch_open or self._epoch_done) and (not self.multiple_epochs or not epoch or (self.sprint_epoch or 0) >= epoch)) and not self.sprint_finalized:
                 self._cond.wait()
             self._wanted_end = 0
         return True

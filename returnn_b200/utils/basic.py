@@ -905,10 +905,27 @@ def is_running_on_cluster() -> bool:
 
 
 def read_pickled_object(p, encoding=None):
-    """unpickle from a pipe/file"""
+    """
+    One object written by ``write_pickled_object``: an int32 length, then that many bytes of pickle.
+    Raises EOFError when the stream ends first. Parity: returnn/util/basic.py ``read_pickled_object``.
+    """
     import pickle
+    import struct
 
-    return pickle.load(p) if encoding is None else pickle.load(p, encoding=encoding)
+    def exactly(n):
+        parts = []
+        while n > 0:
+            b = p.read(n)
+            if not b:
+                raise EOFError("stream ended inside a pickled object")
+            parts.append(b)
+            n -= len(b)
+        return b"".join(parts)
+
+    (size,) = struct.unpack("<i", exactly(4))
+    assert size > 0, "read_pickled_object: size %i" % size
+    data = exactly(size)
+    return pickle.loads(data) if encoding is None else pickle.loads(data, encoding=encoding)
 
 
 def better_repr(o) -> str:
