@@ -286,7 +286,7 @@ def test_interface_inside_a_stand_in_rasr_process(tmp_path):
     (tmp_path / "priors.txt").write_text("0.5 0.25 0.25\n")
 
     def run(*args):
-        res = subprocess.run([sys.executable, str(script)] + list(args), capture_output=True, text=True, timeout=120, cwd=str(tmp_path))
+        res = subprocess.run([sys.executable, str(script)] + list(args), capture_output=True, text=True, timeout=400, cwd=str(tmp_path))
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
         return res.stdout
 
